@@ -1,0 +1,308 @@
+#!/usr/bin/env python
+"""Benchmark of the fused two-pathway multimer attention (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload: the isolated-op configuration — B=8 pairs, H=20, head_dim=32, T=1024, bf16, RoPE on the self
+pathway, chain split uniform in [200,824], 0..64 trailing padded keys, seeded synthetic N(0,1)/sqrt(32) inputs.
+A step is one forward + backward over one batch.  One process per GPU; each rank owns its own batch (pairs
+shard, no data-path collective) so the scaling is weak.  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(B=8, H=20, T=1024, D=32)
+METRIC = "fused_multimer_attention_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+# DRAM bytes (read + write) per launch of the dominant kernel from the ncu capture summarised under profiles/;
+# None until a capture of the current kernel exists.
+NCU_TRAFFIC_BYTES = None
+
+
+def algorithmic_flops(H, T, D, key_pad, fwd=True, bwd=True):
+    """One logit and one P.V term per (query, unpadded key): fwd 4*H*T*Tk*D, bwd 2.5x that (recompute S, dP, dV,
+    dQ, dK)."""
+    tk = (~key_pad).sum(dim=1).double()          # per sample
+    per = (4.0 if fwd else 0.0) + (10.0 if bwd else 0.0)
+    return float((per * H * T * tk * D).sum())
+
+
+def make_inputs(seed):
+    from oracle.multimer_attention import make_op_inputs   # seeded generator shared with the parity tests
+    return make_op_inputs(WORKLOAD["B"], WORKLOAD["H"], WORKLOAD["T"], WORKLOAD["D"], seed=seed)
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.stop_flag = index, [], threading.Event()
+        self.proc = None
+
+    def run(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            for line in self.proc.stdout:
+                self.samples.append([x.strip() for x in line.split(",")])
+                if self.stop_flag.is_set():
+                    break
+        except Exception:
+            pass
+
+    def finish(self):
+        self.stop_flag.set()
+        if self.proc is not None:
+            self.proc.terminate()          # the exact child started above
+        self.join(timeout=2)
+        mhz, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0]))
+                mx = max(mx, float(s[1]))
+                for n, v in zip(names, s[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except (ValueError, IndexError):
+                continue
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def cpu_baseline(seconds_budget=20.0):
+    """The oracle (a port of the reference's PyTorch path) on the host cores, on a bounded sample: one pair (B=1) of the
+    workload, fp32, forward + autograd backward."""
+    from oracle import multimer_attention as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    ts, cid, pad, grad = make_inputs(2002)
+    ts = [t[:1] for t in ts]
+    cid, pad, grad = cid[:1], pad[:1], grad[:1]
+    mask = O.chain_mask_from_ids(cid)
+    flops = algorithmic_flops(WORKLOAD["H"], WORKLOAD["T"], WORKLOAD["D"], pad)
+    times = []
+    t_end = time.perf_counter() + seconds_budget
+    for it in range(4):
+        t0 = time.perf_counter()
+        O.multimer_attention_fwd_bwd(*ts, mask, grad, key_pad=pad)
+        dt = time.perf_counter() - t0
+        if it > 0:
+            times.append(dt)
+        if time.perf_counter() > t_end and times:
+            break
+    sec = statistics.median(times)
+    return {"value": flops / sec / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"1 of {WORKLOAD['B']} pairs (B=1,H=20,T=1024,D=32), fp32, fwd+autograd bwd, "
+                      f"median of {len(times)} after 1 warm-up, {sec:.2f} s each"}, sec
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU implementation of the path (oracle port; the reference itself is Python + Triton and its
+    checkout is not on the GPU box), timed on the host cores with every thread."""
+    if rank != 0:
+        return
+    from oracle import multimer_attention as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    ts, cid, pad, grad = make_inputs(2002)
+    ts = [t[:1] for t in ts]
+    cid, pad, grad = cid[:1], pad[:1], grad[:1]
+    mask = O.chain_mask_from_ids(cid)
+    flops = algorithmic_flops(WORKLOAD["H"], WORKLOAD["T"], WORKLOAD["D"], pad)
+    steps = max(1, min(args.steps, 5))
+    warm = max(1, min(args.warmup, 1))
+    for _ in range(warm):
+        O.multimer_attention_fwd_bwd(*ts, mask, grad, key_pad=pad)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        O.multimer_attention_fwd_bwd(*ts, mask, grad, key_pad=pad)
+    sec = (time.perf_counter() - t0) / steps
+    val = flops / sec / 1e12
+    sample = (f"each step = 1 of {WORKLOAD['B']} pairs (B=1,H=20,T=1024,D=32), fp32, fwd + autograd bwd; "
+              f"{steps} steps after {warm} warm-up (bounded from the requested {args.steps}/{args.warmup})")
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "isolated combined-softmax multimer attention fwd+bwd, B=8 H=20 D=32 T=1024",
+                       "device": "cpu"},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch.distributed as dist
+    import mint_plus_b200 as M
+    from mint_plus_b200 import _lib as L, ops
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    B, H, T, D = (WORKLOAD[k] for k in "BHTD")
+
+    ts, cid, pad, grad = make_inputs(2002 + rank)               # each rank owns its own pairs
+    flops_step = algorithmic_flops(H, T, D, pad)
+    flops_fwd = algorithmic_flops(H, T, D, pad, bwd=False)
+    flops_bwd = algorithmic_flops(H, T, D, pad, fwd=False)
+    host = [t.bfloat16().pin_memory() for t in ts] + [grad.bfloat16().pin_memory()]
+    host_cid, host_pad = cid.pin_memory(), pad.pin_memory()
+    dts = [t.to(dev, non_blocking=True) for t in host[:6]]
+    dgrad = host[6].to(dev)
+    meta = M.mask_meta_from_chain_ids(host_cid.to(dev), host_pad.to(dev))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
+
+    def step_resident():
+        leaves = [t.requires_grad_(True) for t in dts]
+        out = M.multimer_attention(*leaves, meta=meta)
+        return torch.autograd.grad(out, leaves, dgrad)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    lib = L.lib()
+    for _ in range(warmup):
+        step_resident()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    # ---- device-resident inputs: K steps, each bracketed by its own events, L2 flushed between steps
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    launches0 = lib.mintb_kernel_launches()
+    barrier()
+    for s, e in ev:
+        flush.zero_()
+        s.record()
+        step_resident()
+        e.record()
+    barrier()
+    launches = lib.mintb_kernel_launches() - launches0
+    ms_total = sum(s.elapsed_time(e) for s, e in ev)
+
+    # ---- forward / backward C-ABI calls timed apart (for the roofline of the dominant one)
+    leaves = [t.requires_grad_(True) for t in dts]
+    fwd_ms, bwd_ms = [], []
+    for _ in range(min(steps, 20)):
+        flush.zero_()
+        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        a.record()
+        out = M.multimer_attention(*leaves, meta=meta)
+        b.record()
+        torch.autograd.grad(out, leaves, dgrad)
+        c.record()
+        torch.cuda.synchronize()
+        fwd_ms.append(a.elapsed_time(b))
+        bwd_ms.append(b.elapsed_time(c))
+
+    # ---- end to end: pinned host inputs -> device, fwd+bwd through the public API, results -> pinned host
+    out_host = [torch.empty(B, H, T, D, dtype=torch.bfloat16).pin_memory() for _ in range(7)]
+    h2d = sum(t.numel() * t.element_size() for t in host) + host_cid.numel() * 4 + host_pad.numel()
+    d2h = sum(t.numel() * t.element_size() for t in out_host)
+
+    def step_e2e():
+        d = [t.to(dev, non_blocking=True).requires_grad_(True) for t in host[:6]]
+        g = host[6].to(dev, non_blocking=True)
+        o = M.multimer_attention(*d, chain_ids=host_cid.to(dev, non_blocking=True),
+                                 key_padding_mask=host_pad.to(dev, non_blocking=True))
+        grads = torch.autograd.grad(o, d, g)
+        for dst, src in zip(out_host, (o.detach(), *grads)):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    e2e_steps = min(steps, 20)
+    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(e2e_steps)]
+    for s, e in ev2:
+        flush.zero_()
+        s.record()
+        step_e2e()
+        e.record()
+    barrier()
+    e2e_ms = sum(s.elapsed_time(e) for s, e in ev2)
+    clocks = sampler.finish()
+    ops.check_device_status(dev)
+
+    # max over ranks of the timed totals; whole-job work = every rank's flops
+    stats = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device=dev)
+    work = torch.tensor([flops_step], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    ms_total, e2e_ms = stats.tolist()
+    total_flops_step = float(work.item())
+
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_path):
+            peaks, peak_src = json.load(open(peaks_path)), "measured"
+        else:
+            peaks, peak_src = FALLBACK_PEAKS, "fallback"
+        value = total_flops_step * steps / (ms_total * 1e-3) / 1e12
+        fwd_t, bwd_t = statistics.mean(fwd_ms), statistics.mean(bwd_ms)
+        dom = ("attention backward call", flops_bwd, bwd_t) if bwd_t >= fwd_t else ("attention forward call", flops_fwd, fwd_t)
+        achieved = dom[1] / (dom[2] * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_total / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "isolated combined-softmax multimer attention fwd+bwd, B=8 H=20 D=32 T=1024 per GPU",
+                       "rope": "self pathway", "l2": "flushed between timed steps (256 MiB write)",
+                       "flops": "14*H*T*Tk*D per pair, Tk = unpadded keys"},
+            "roofline": {"bound": "tensor", "kernel": dom[0], "achieved": achieved, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES,
+                         "peak_source": peak_src, "fwd_ms": fwd_t, "bwd_ms": bwd_t,
+                         "fwd_tflops": flops_fwd / (fwd_t * 1e-3) / 1e12, "bwd_tflops": flops_bwd / (bwd_t * 1e-3) / 1e12},
+            "e2e": {"value": total_flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"], _ = cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

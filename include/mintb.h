@@ -1,0 +1,123 @@
+/*
+ * mintb — C ABI of the B200 (sm_100a) implementation of MINT's two-pathway combined-softmax
+ * multimer attention and the kernels either side of it.
+ *
+ * The reference (molecular-william/mint_plus) is pure Python + Triton and has no FFI for this path:
+ * its boundary is a set of Python call signatures.  Each entry point below names the reference
+ * function whose device work it replaces (path within the mint_plus checkout : lines).
+ *
+ * Conventions
+ *   - Plain pointers and sizes only.  Every pointer is a DEVICE pointer unless stated otherwise.
+ *   - The caller owns every buffer (inputs, outputs, mask metadata, workspaces); nothing is allocated
+ *     or freed here.  Inputs are read-only.
+ *   - Tensors are contiguous, row-major: q/k/v/out/grad [B][H][T][D]; lse [B][H][T] (float);
+ *     chain_ids [B][T] (int32); key_pad [B][T] (uint8, non-zero = padded key); chain_mask [B][T][T]
+ *     (uint8, non-zero = the two positions belong to different chains -> cross pathway).
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  No entry point
+ *     synchronises the host with the device.
+ *   - Return value: MINTB_OK, or a negative MINTB_E* code for an argument rejected on the host before
+ *     anything was launched; mintb_last_error() then holds a message for the calling thread.
+ *   - `dev_status` (device int32, caller-zeroed, may be NULL): kernels with bounded waits store a
+ *     non-zero code there if a wait ran out, and return; they never trap and never spin forever.
+ */
+#ifndef MINTB_H_
+#define MINTB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define MINTB_API __attribute__((visibility("default")))
+#else
+#define MINTB_API
+#endif
+
+#define MINTB_OK 0
+#define MINTB_EINVAL (-1)       /* bad shape / null pointer / misaligned pointer                   */
+#define MINTB_EUNSUPPORTED (-2) /* valid request this library does not implement (fails loudly)    */
+#define MINTB_EWORKSPACE (-3)   /* workspace smaller than the matching *_workspace_bytes() answer  */
+#define MINTB_ECUDA (-4)        /* a CUDA runtime/driver call failed (launch, descriptor encode)   */
+
+/* dtype of q/k/v/out/grads */
+#define MINTB_F32 0
+#define MINTB_BF16 1
+
+/* flags */
+#define MINTB_FLAG_ROPE 1u         /* rotate Q and K of the SELF pathway (rotary_embedding.py:47-55)                */
+#define MINTB_FLAG_SQRT_SOFTMAX 2u /* sqrt(softmax) coefficients (mu_scaling/layer.py:162-163)                       */
+#define MINTB_FLAG_FORCE_SIMT 4u   /* run the fp32 CUDA-core kernels even where the tcgen05 kernels apply (checking) */
+
+MINTB_API int mintb_version(void);
+MINTB_API const char* mintb_last_error(void);
+/* Number of CUDA kernels this library has launched in this process so far (instrumentation; the reference
+ * has no counterpart). */
+MINTB_API unsigned long long mintb_kernel_launches(void);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Mask metadata.  Replaces the (B,T,T) bool tensor the reference builds every step (esm2.py:89) and
+ * re-reads per head (modules.py:129-141; multi_pathway_attention.py:101-128): one bit per (query,key)
+ * pair, one bit per key for padding (attention.py:230-236), and a class byte per 64x64 tile
+ * (bit0: has an intra-chain pair, bit1: has an inter-chain pair, bit2: has a padded key).
+ * `meta` must hold mintb_mask_meta_bytes(B,T) bytes, 256-byte aligned; build it once per batch.
+ * key_pad may be NULL (no padding).
+ */
+MINTB_API size_t mintb_mask_meta_bytes(int B, int T);
+MINTB_API int mintb_mask_meta_from_chain_ids(const int32_t* chain_ids, const uint8_t* key_pad, void* meta, int B, int T,
+                                   void* stream);
+MINTB_API int mintb_mask_meta_from_mask(const uint8_t* chain_mask, const uint8_t* key_pad, void* meta, int B, int T,
+                              void* stream);
+
+/* RoPE tables cos/sin [T][D/2] (float) from inv_freq [D/2] (float, device), as rotary_embedding.py:47-53
+ * computes them: angle = float(position) * inv_freq. */
+MINTB_API int mintb_rope_tables(const float* inv_freq, float* cos_tab, float* sin_tab, int T, int D, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Attention forward.  Replaces fused_multi_pathway_attention (kernels/multi_pathway_attention.py:184-280)
+ * and the PyTorch path it mirrors (modules.py:94-154): out = (P o ~M) V_self + (P o M) V_cross with
+ * P = softmax_keys(where(M, scale*Q_cross K_cross^T, scale*R(Q_self) R(K_self)^T)), padded keys -inf.
+ * With MINTB_FLAG_ROPE the kernel rotates the self pathway (rope_cos/rope_sin required) — pass raw
+ * projections and scale = D^-0.5; without it the caller has already scaled and rotated
+ * (multi_pathway_attention.py:199-202) — pass scale = 1.
+ * lse [B][H][T] receives log(sum_j exp(logit_ij)) for the backward pass.
+ */
+MINTB_API size_t mintb_attn_fwd_workspace_bytes(int B, int H, int T, int D, int dtype, unsigned flags);
+MINTB_API int mintb_attn_fwd(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
+                   const void* k_cross, const void* v_cross, const void* meta, const float* rope_cos,
+                   const float* rope_sin, void* out, float* lse, void* workspace, size_t workspace_bytes, int B,
+                   int H, int T, int D, int dtype, unsigned flags, float scale, void* stream, int* dev_status);
+
+/* Attention backward.  Replaces fused_multi_pathway_attention_bwd (kernels/multi_pathway_attention_bwd.py:15-59)
+ * with what torch.autograd computes through modules.py:129-144: probabilities are recomputed from lse;
+ * dq/dk of the self pathway are un-rotated and dq is multiplied by scale, so the six results are the
+ * gradients w.r.t. the tensors that were passed to mintb_attn_fwd. */
+MINTB_API size_t mintb_attn_bwd_workspace_bytes(int B, int H, int T, int D, int dtype, unsigned flags);
+MINTB_API int mintb_attn_bwd(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
+                   const void* k_cross, const void* v_cross, const void* meta, const float* rope_cos,
+                   const float* rope_sin, const void* out, const float* lse, const void* d_out, void* dq_self,
+                   void* dk_self, void* dv_self, void* dq_cross, void* dk_cross, void* dv_cross, void* workspace,
+                   size_t workspace_bytes, int B, int H, int T, int D, int dtype, unsigned flags, float scale,
+                   void* stream, int* dev_status);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Combine from materialised logits.  Replaces fused_multimer_combine / fused_multimer_combine_bwd
+ * (kernels/__init__.py:179-286): logits [B][H][T][T] of both pathways already hold -inf on padded keys.
+ * Backward follows autograd: d_intra_logits is zero where the mask selects the cross pathway and vice versa;
+ * its workspace holds the per-row softmax statistics between its two kernels.
+ */
+MINTB_API int mintb_combine_fwd(const void* intra_logits, const void* inter_logits, const uint8_t* chain_mask,
+                      const void* intra_values, const void* inter_values, void* out, int B, int H, int T, int D,
+                      int dtype, void* stream);
+MINTB_API size_t mintb_combine_bwd_workspace_bytes(int B, int H, int T);
+MINTB_API int mintb_combine_bwd(const void* intra_logits, const void* inter_logits, const uint8_t* chain_mask,
+                      const void* intra_values, const void* inter_values, const void* d_out, void* d_intra_logits,
+                      void* d_inter_logits, void* d_intra_values, void* d_inter_values, void* workspace,
+                      size_t workspace_bytes, int B, int H, int T, int D, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MINTB_H_ */

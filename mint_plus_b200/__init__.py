@@ -1,0 +1,21 @@
+"""mint_plus_b200 — B200 (sm_100a) implementation of MINT's two-pathway combined-softmax attention path.
+
+Host code is Python/PyTorch with the reference's call signatures; the arithmetic runs in libmintb.so
+(hand-written CUDA behind the C ABI of include/mintb.h).
+"""
+from .kernels import (differentiable_multi_pathway_attention, differentiable_multimer_combine,
+                      fused_multi_pathway_attention, fused_multimer_combine)
+from .ops import (MaskMeta, check_device_status, mask_meta_from_chain_ids, mask_meta_from_mask,
+                  multimer_attention, multimer_combine, rope_tables)
+from .attention import MultiHeadAttention, MultimerAttention
+from .modules_plus import (TransformerLayer_MINT_plus, VanillaFeedForward, build_mint_plus,
+                           enable_fused_multi_pathway)
+from .rotary_embedding import RotaryEmbedding
+
+__all__ = [
+    "fused_multi_pathway_attention", "differentiable_multi_pathway_attention", "fused_multimer_combine",
+    "differentiable_multimer_combine", "multimer_attention", "multimer_combine", "MaskMeta",
+    "mask_meta_from_chain_ids", "mask_meta_from_mask", "rope_tables", "check_device_status",
+    "MultiHeadAttention", "MultimerAttention", "TransformerLayer_MINT_plus", "VanillaFeedForward",
+    "build_mint_plus", "enable_fused_multi_pathway", "RotaryEmbedding",
+]

@@ -1,0 +1,73 @@
+"""ctypes binding of libmintb.so (the C ABI declared in include/mintb.h).
+
+There is no fallback: if the library is missing, loading raises and every op that needs it fails.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_size_t, c_uint, c_ulonglong, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmintb.so")
+
+OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA = 0, -1, -2, -3, -4
+F32, BF16 = 0, 1
+FLAG_ROPE, FLAG_SQRT_SOFTMAX, FLAG_FORCE_SIMT = 1, 2, 4
+
+_P = c_void_p
+# name -> (restype, argtypes); mirrors include/mintb.h one to one
+PROTOTYPES = {
+    "mintb_version": (c_int, []),
+    "mintb_last_error": (c_char_p, []),
+    "mintb_kernel_launches": (c_ulonglong, []),
+    "mintb_mask_meta_bytes": (c_size_t, [c_int, c_int]),
+    "mintb_mask_meta_from_chain_ids": (c_int, [_P, _P, _P, c_int, c_int, _P]),
+    "mintb_mask_meta_from_mask": (c_int, [_P, _P, _P, c_int, c_int, _P]),
+    "mintb_rope_tables": (c_int, [_P, _P, _P, c_int, c_int, _P]),
+    "mintb_attn_fwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_uint]),
+    "mintb_attn_fwd": (c_int, [_P] * 6 + [_P, _P, _P, _P, _P, _P, c_size_t, c_int, c_int, c_int, c_int, c_int, c_uint,
+                               c_float, _P, _P]),
+    "mintb_attn_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_uint]),
+    "mintb_attn_bwd": (c_int, [_P] * 6 + [_P, _P, _P, _P, _P, _P] + [_P] * 6 + [_P, c_size_t, c_int, c_int, c_int, c_int,
+                               c_int, c_uint, c_float, _P, _P]),
+    "mintb_combine_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
+    "mintb_combine_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "mintb_combine_bwd": (c_int, [_P] * 10 + [_P, c_size_t, c_int, c_int, c_int, c_int, c_int, _P]),
+}
+
+_lib = None
+
+
+class MintbError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """Load libmintb.so once and attach the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise MintbError(
+            f"{LIB_PATH} is missing: build it with `python -m mint_plus_b200.build` "
+            "(nvcc, sm_100a). There is no fallback path.")
+    handle = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(handle, name)          # AttributeError if the library does not export it
+        fn.restype = res
+        fn.argtypes = args
+    _lib = handle
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    """Map a MINTB_* return code to a Python exception (ValueError for rejected arguments)."""
+    if rc == OK:
+        return
+    msg = lib().mintb_last_error().decode("utf-8", "replace")
+    if rc in (EINVAL, EWORKSPACE):
+        raise ValueError(f"{what}: {msg}")
+    if rc == EUNSUPPORTED:
+        raise NotImplementedError(f"{what}: {msg}")
+    raise MintbError(f"{what}: {msg} (code {rc})")

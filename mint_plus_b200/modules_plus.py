@@ -1,0 +1,161 @@
+"""TransformerLayer_MINT_plus / build_mint_plus / enable_fused_multi_pathway with the reference's interface
+(mint_plus/models/modules_plus.py:20-305, mint_plus/models/modules.py:323-335, 398-417).
+
+The layer always takes the fused CUDA attention — in training as well as in eval, since the fused
+operator is differentiable — and passes the key-padding mask to it.  `_use_fused_multi_pathway` is kept
+as an attribute for code that toggles it; False selects the materialised-logits combine kernel.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from . import ops
+from .attention import MultiHeadAttention, MultimerAttention
+from .kernels import fused_multimer_combine
+
+
+def gelu_erf(x):
+    return x * 0.5 * (1.0 + torch.erf(x / math.sqrt(2.0)))
+
+
+class VanillaFeedForward(nn.Module):
+    def __init__(self, embed_dim, ffn_embed_dim, use_erf_gelu: bool = False):
+        super().__init__()
+        self.fc1 = nn.Linear(embed_dim, ffn_embed_dim)
+        self.fc2 = nn.Linear(ffn_embed_dim, embed_dim)
+        self.use_erf_gelu = use_erf_gelu
+
+    def forward(self, x):
+        x = gelu_erf(self.fc1(x)) if self.use_erf_gelu else F.gelu(self.fc1(x))
+        return self.fc2(x)
+
+
+class TransformerLayer_MINT_plus(nn.Module):
+    def __init__(self, embed_dim, ffn_embed_dim, attention_heads, use_rotary_embeddings: bool = True,
+                 use_multimer: bool = False, use_rmsnorm: bool = False, use_erf_gelu: bool = False):
+        super().__init__()
+        self.embed_dim = embed_dim
+        self.ffn_embed_dim = ffn_embed_dim
+        self.attention_heads = attention_heads
+        self.use_rotary_embeddings = use_rotary_embeddings
+        self.use_multimer = use_multimer
+        self.use_rmsnorm = use_rmsnorm
+        self.use_erf_gelu = use_erf_gelu
+        self._use_fused_multi_pathway = True
+        self.self_attn = MultiHeadAttention(embed_dim, attention_heads, use_rotary_embeddings=use_rotary_embeddings,
+                                            use_fused_qkv=True)
+        if use_multimer:
+            self.multimer_attn = MultimerAttention(embed_dim, attention_heads)
+        self.feed_forward = VanillaFeedForward(embed_dim, ffn_embed_dim, use_erf_gelu=use_erf_gelu)
+        norm = (lambda: nn.RMSNorm(embed_dim)) if use_rmsnorm else (lambda: nn.LayerNorm(embed_dim))
+        self.self_attn_layer_norm = norm()
+        self.final_layer_norm = norm()
+
+    def _standard_attention(self, x, attn_mask, padding_mask):
+        return self.self_attn(x=x, key_padding_mask=padding_mask, attn_mask=attn_mask)
+
+    def _multimer_attention_plus(self, x, chain_mask, padding_mask, chain_ids=None):
+        if self._use_fused_multi_pathway:
+            return self._multimer_attention_superfused(x, chain_mask, padding_mask, chain_ids)
+        T, B, E = x.shape
+        sa, ma = self.self_attn, self.multimer_attn
+        intra_logits, intra_values = sa(x=x, key_padding_mask=padding_mask, before_softmax=True)
+        inter_logits, inter_values = ma(x=x, key_padding_mask=padding_mask, before_softmax=True)
+        attn_out = fused_multimer_combine(intra_logits.type_as(intra_values), inter_logits.type_as(inter_values),
+                                          chain_mask, intra_values, inter_values)
+        attn_out = attn_out.permute(2, 0, 1, 3).reshape(T, B, E)
+        return sa.out_proj(attn_out), None
+
+    def _multimer_attention_superfused(self, x, chain_mask, padding_mask, chain_ids=None):
+        """x (T,B,E) -> (T,B,E): both QKV projections, fused two-pathway attention, output projection."""
+        T, B, E = x.shape
+        sa, ma = self.self_attn, self.multimer_attn
+        q_s, k_s, v_s = sa.project_qkv_4d(x)
+        q_c, k_c, v_c = ma.project_qkv_4d(x)
+        if chain_ids is not None and chain_mask is None:
+            mask_kw = dict(meta=_cached_ids_meta(chain_ids, padding_mask))
+        else:
+            mask_kw = dict(chain_mask=chain_mask, key_padding_mask=padding_mask)
+        rope = sa.rot_emb is not None
+        attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=rope,
+                                          inv_freq=sa.rot_emb.inv_freq if rope else None, scale=sa.scaling, **mask_kw)
+        attn_out = attn_out.permute(2, 0, 1, 3).reshape(T, B, E)
+        return sa.out_proj(attn_out), None
+
+    # the PyTorch-named entry of the reference resolves to the same fused path
+    def _multimer_attention(self, x, chain_mask, padding_mask):
+        return self._multimer_attention_plus(x, chain_mask, padding_mask)
+
+    def forward(self, x, self_attn_mask=None, self_attn_padding_mask=None, chain_ids=None):
+        residual = x
+        x = self.self_attn_layer_norm(x)
+        if self.use_multimer:
+            x, attn = self._multimer_attention_plus(x, self_attn_mask, self_attn_padding_mask, chain_ids)
+        else:
+            x, attn = self._standard_attention(x, self_attn_mask, self_attn_padding_mask)
+        x = residual + x
+        residual = x
+        x = self.final_layer_norm(x)
+        x = self.feed_forward(x)
+        x = residual + x
+        return x, attn
+
+
+_ids_meta_cache = []
+
+
+def _cached_ids_meta(chain_ids, padding_mask):
+    for ids, ver, pad, meta in _ids_meta_cache:
+        if ids is chain_ids and ver == chain_ids._version and pad is padding_mask:
+            return meta
+    meta = ops.mask_meta_from_chain_ids(chain_ids, padding_mask)
+    _ids_meta_cache.insert(0, (chain_ids, chain_ids._version, padding_mask, meta))
+    del _ids_meta_cache[2:]
+    return meta
+
+
+def build_mint_plus(model: nn.Module) -> nn.Module:
+    """Replace every layer of `model.layers` by a TransformerLayer_MINT_plus, concatenating the separate
+    q/k/v projection weights of both pathways into fused [Q;K;V] matrices; out_proj, rotary buffer, FFN and
+    norms are shared by reference (modules_plus.py:240-305)."""
+    for i, old in enumerate(model.layers):
+        new = TransformerLayer_MINT_plus(
+            embed_dim=old.embed_dim, ffn_embed_dim=old.ffn_embed_dim, attention_heads=old.attention_heads,
+            use_rotary_embeddings=old.use_rotary_embeddings, use_multimer=old.use_multimer,
+            use_rmsnorm=getattr(old, "use_rmsnorm", False), use_erf_gelu=getattr(old, "use_erf_gelu", False))
+        ref = old.self_attn.out_proj.weight if old.self_attn.out_proj is not None else next(old.parameters())
+        new.to(device=ref.device, dtype=ref.dtype)
+
+        def fuse(dst: nn.Linear, src):
+            if getattr(src, "fused_qkv", None) is not None and getattr(src, "q_proj", None) is None:
+                dst.weight.data.copy_(src.fused_qkv.weight.data)
+                if src.fused_qkv.bias is not None:
+                    dst.bias.data.copy_(src.fused_qkv.bias.data)
+                return
+            dst.weight.data.copy_(torch.cat([src.q_proj.weight, src.k_proj.weight, src.v_proj.weight], dim=0))
+            if src.q_proj.bias is not None:
+                dst.bias.data.copy_(torch.cat([src.q_proj.bias, src.k_proj.bias, src.v_proj.bias], dim=0))
+
+        fuse(new.self_attn.fused_qkv, old.self_attn)
+        new.self_attn.out_proj = old.self_attn.out_proj
+        new.self_attn.rot_emb = old.self_attn.rot_emb
+        if hasattr(old, "multimer_attn") and old.multimer_attn is not None and new.use_multimer:
+            fuse(new.multimer_attn.fused_qkv, old.multimer_attn)
+        new.feed_forward = old.feed_forward
+        new.self_attn_layer_norm = old.self_attn_layer_norm
+        new.final_layer_norm = old.final_layer_norm
+        new.train(old.training)
+        model.layers[i] = new
+    return model
+
+
+def enable_fused_multi_pathway(model: nn.Module, enabled: bool = True):
+    """Toggle the fused (no materialised logits) attention on every layer, including layers wrapped in blocks
+    that expose `.layers` (modules.py:398-417)."""
+    for layer in model.layers:
+        for sub in (layer.layers if hasattr(layer, "layers") else [layer]):
+            sub._use_fused_multi_pathway = enabled

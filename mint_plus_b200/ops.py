@@ -1,0 +1,270 @@
+"""Tensor-facing operators over libmintb: mask metadata, RoPE tables, and the autograd function of the
+combined-softmax multimer attention.  PyTorch supplies device memory, streams and autograd glue only;
+every computation runs in the CUDA library (there is no eager fallback).
+"""
+from __future__ import annotations
+
+import math
+import weakref
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib as L
+
+_DTYPES = {torch.float32: L.F32, torch.bfloat16: L.BF16}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("mint_plus_b200 operators run on CUDA tensors only (no CPU fallback)")
+
+
+def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
+    # torch's caching allocator hands out 512-byte aligned blocks
+    return torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
+
+
+# ----------------------------------------------------------------------------------------------- status word
+_status = {}
+
+
+def _dev_status(device) -> torch.Tensor:
+    key = torch.device(device).index
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise and raise if a kernel reported a bounded wait that ran out."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    code = int(_dev_status(device).item())
+    if code != 0:
+        _dev_status(device).zero_()
+        raise L.MintbError(f"a mintb kernel gave up a bounded wait (device status 0x{code:x})")
+
+
+# ----------------------------------------------------------------------------------------------- mask metadata
+class MaskMeta:
+    """Packed chain/padding mask of one batch (see include/mintb.h): build once, use for every layer and head."""
+
+    def __init__(self, buf: torch.Tensor, B: int, T: int):
+        self.buf, self.B, self.T = buf, B, T
+
+
+def _key_pad_u8(key_padding_mask, B, T):
+    if key_padding_mask is None:
+        return None
+    if tuple(key_padding_mask.shape) != (B, T):
+        raise ValueError(f"key_padding_mask must be (B, T) = ({B}, {T}), got {tuple(key_padding_mask.shape)}")
+    return key_padding_mask.to(torch.uint8).contiguous()
+
+
+def mask_meta_from_chain_ids(chain_ids: torch.Tensor, key_padding_mask: Optional[torch.Tensor] = None) -> MaskMeta:
+    """chain_ids (B,T) integer; key_padding_mask (B,T) bool, True = padded key (esm2.py:85,89)."""
+    _require_cuda(chain_ids, key_padding_mask)
+    B, T = chain_ids.shape
+    cid = chain_ids.to(torch.int32).contiguous()
+    pad = _key_pad_u8(key_padding_mask, B, T)
+    buf = torch.empty(L.lib().mintb_mask_meta_bytes(B, T), dtype=torch.uint8, device=cid.device)
+    with torch.cuda.device(cid.device):
+        L.check(L.lib().mintb_mask_meta_from_chain_ids(_ptr(cid), _ptr(pad), _ptr(buf), B, T, _stream()),
+                "mask_meta_from_chain_ids")
+    return MaskMeta(buf, B, T)
+
+
+def mask_meta_from_mask(chain_mask: torch.Tensor, key_padding_mask: Optional[torch.Tensor] = None) -> MaskMeta:
+    """chain_mask (B,T,T) bool, True = different chains (cross pathway)."""
+    _require_cuda(chain_mask, key_padding_mask)
+    if chain_mask.dim() != 3 or chain_mask.shape[1] != chain_mask.shape[2]:
+        raise ValueError(f"chain_mask must be (B, T, T), got {tuple(chain_mask.shape)}")
+    B, T, _ = chain_mask.shape
+    m = chain_mask.to(torch.uint8).contiguous() if chain_mask.dtype != torch.bool else chain_mask.contiguous().view(torch.uint8)
+    pad = _key_pad_u8(key_padding_mask, B, T)
+    buf = torch.empty(L.lib().mintb_mask_meta_bytes(B, T), dtype=torch.uint8, device=m.device)
+    with torch.cuda.device(m.device):
+        L.check(L.lib().mintb_mask_meta_from_mask(_ptr(m), _ptr(pad), _ptr(buf), B, T, _stream()), "mask_meta_from_mask")
+    return MaskMeta(buf, B, T)
+
+
+_meta_cache = []  # [(weakref(mask), version, weakref(pad) | None, pad version, MaskMeta)], newest first
+
+
+def cached_mask_meta(chain_mask: torch.Tensor, key_padding_mask: Optional[torch.Tensor] = None) -> MaskMeta:
+    """Metadata for a (B,T,T) mask, reused while the same tensor objects are passed again (every layer of a
+    forward pass receives the same mask, esm2.py:124-132)."""
+    for ref_m, ver_m, ref_p, ver_p, meta in _meta_cache:
+        if ref_m() is chain_mask and ver_m == chain_mask._version:
+            if key_padding_mask is None and ref_p is None:
+                return meta
+            if key_padding_mask is not None and ref_p is not None and ref_p() is key_padding_mask \
+                    and ver_p == key_padding_mask._version:
+                return meta
+    meta = mask_meta_from_mask(chain_mask, key_padding_mask)
+    _meta_cache.insert(0, (weakref.ref(chain_mask), chain_mask._version,
+                           None if key_padding_mask is None else weakref.ref(key_padding_mask),
+                           0 if key_padding_mask is None else key_padding_mask._version, meta))
+    del _meta_cache[4:]
+    return meta
+
+
+# ----------------------------------------------------------------------------------------------- RoPE tables
+_rope_cache = {}
+
+
+def default_inv_freq(D: int, device) -> torch.Tensor:
+    """rotary_embedding.py:43: 1 / 10000^(2i/D), fp32."""
+    return (1.0 / (10000 ** (torch.arange(0, D, 2).float() / D))).to(device)
+
+
+def rope_tables(T: int, D: int, device, inv_freq: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin tables (T, D/2) fp32 on `device`, cached per (T, D, device, inv_freq contents)."""
+    device = torch.device(device)
+    inv = default_inv_freq(D, device) if inv_freq is None else inv_freq.detach().to(device=device, dtype=torch.float32).contiguous()
+    if inv.numel() != D // 2:
+        raise ValueError(f"inv_freq must have D/2 = {D // 2} entries")
+    key = (T, D, device.index, inv_freq.data_ptr() if inv_freq is not None else 0,
+           inv_freq._version if inv_freq is not None else 0)
+    hit = _rope_cache.get(key)
+    if hit is not None:
+        return hit
+    cos = torch.empty(T, D // 2, dtype=torch.float32, device=device)
+    sin = torch.empty_like(cos)
+    with torch.cuda.device(device):
+        L.check(L.lib().mintb_rope_tables(_ptr(inv), _ptr(cos), _ptr(sin), T, D, _stream()), "rope_tables")
+    if len(_rope_cache) > 16:
+        _rope_cache.clear()
+    _rope_cache[key] = (cos, sin, inv_freq)   # keeps the buffer alive so its address cannot be reused under this key
+    return _rope_cache[key]
+
+
+# ----------------------------------------------------------------------------------------------- attention
+class _MultimerAttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q_s, k_s, v_s, q_c, k_c, v_c, meta: MaskMeta, cos, sin, scale: float, flags: int):
+        B, H, T, D = q_s.shape
+        dt = _DTYPES[q_s.dtype]
+        lib = L.lib()
+        out = torch.empty_like(q_s)
+        lse = torch.empty(B, H, T, dtype=torch.float32, device=q_s.device)
+        ws_bytes = lib.mintb_attn_fwd_workspace_bytes(B, H, T, D, dt, flags)
+        ws = _workspace(ws_bytes, q_s.device)
+        with torch.cuda.device(q_s.device):
+            rc = lib.mintb_attn_fwd(_ptr(q_s), _ptr(k_s), _ptr(v_s), _ptr(q_c), _ptr(k_c), _ptr(v_c), _ptr(meta.buf),
+                                    _ptr(cos), _ptr(sin), _ptr(out), _ptr(lse), _ptr(ws), ws_bytes, B, H, T, D, dt,
+                                    flags, scale, _stream(), _ptr(_dev_status(q_s.device)))
+        L.check(rc, "mintb_attn_fwd")
+        ctx.save_for_backward(q_s, k_s, v_s, q_c, k_c, v_c, out, lse, cos, sin)
+        ctx.meta, ctx.scale, ctx.flags = meta, scale, flags
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q_s, k_s, v_s, q_c, k_c, v_c, out, lse, cos, sin = ctx.saved_tensors
+        B, H, T, D = q_s.shape
+        dt = _DTYPES[q_s.dtype]
+        lib = L.lib()
+        d_out = d_out.contiguous()
+        grads = [torch.empty_like(q_s) for _ in range(6)]
+        ws_bytes = lib.mintb_attn_bwd_workspace_bytes(B, H, T, D, dt, ctx.flags)
+        ws = _workspace(ws_bytes, q_s.device)
+        with torch.cuda.device(q_s.device):
+            rc = lib.mintb_attn_bwd(_ptr(q_s), _ptr(k_s), _ptr(v_s), _ptr(q_c), _ptr(k_c), _ptr(v_c), _ptr(ctx.meta.buf),
+                                    _ptr(cos), _ptr(sin), _ptr(out), _ptr(lse), _ptr(d_out), *[_ptr(g) for g in grads],
+                                    _ptr(ws), ws_bytes, B, H, T, D, dt, ctx.flags, ctx.scale, _stream(),
+                                    _ptr(_dev_status(q_s.device)))
+        L.check(rc, "mintb_attn_bwd")
+        return (*grads, None, None, None, None, None)
+
+
+def multimer_attention(q_self, k_self, v_self, q_cross, k_cross, v_cross, *, meta: Optional[MaskMeta] = None,
+                       chain_ids=None, chain_mask=None, key_padding_mask=None, rope: bool = True,
+                       inv_freq: Optional[torch.Tensor] = None, scale: Optional[float] = None,
+                       sqrt_softmax: bool = False, force_simt: bool = False) -> torch.Tensor:
+    """Two-pathway combined-softmax attention on (B,H,T,D) projections; differentiable.
+
+    out = (P o ~M) V_self + (P o M) V_cross,  P = softmax_j where(M, s*Qc Kc^T, s*R(Qs) R(Ks)^T), padded keys -inf
+    (modules.py:94-154 of the reference).  With rope=True the raw projections are passed and the kernels rotate
+    the self pathway and apply `scale` (default D^-0.5); with rope=False and scale=1 the caller has done both,
+    which is the calling convention of the reference's fused kernel (multi_pathway_attention.py:199-202).
+    The mask comes from exactly one of `meta`, `chain_ids` (B,T) or `chain_mask` (B,T,T).
+    """
+    ts = (q_self, k_self, v_self, q_cross, k_cross, v_cross)
+    _require_cuda(*ts)
+    if q_self.dim() != 4 or any(t.shape != q_self.shape for t in ts):
+        raise ValueError("q/k/v of both pathways must share one (B, H, T, D) shape")
+    if q_self.dtype not in _DTYPES or any(t.dtype != q_self.dtype for t in ts):
+        raise TypeError("q/k/v must all be float32 or all be bfloat16")
+    B, H, T, D = q_self.shape
+    if meta is None:
+        if (chain_ids is None) == (chain_mask is None):
+            raise ValueError("give exactly one of meta, chain_ids, chain_mask")
+        meta = mask_meta_from_chain_ids(chain_ids, key_padding_mask) if chain_ids is not None \
+            else cached_mask_meta(chain_mask, key_padding_mask)
+    elif chain_ids is not None or chain_mask is not None or key_padding_mask is not None:
+        raise ValueError("meta already carries the chain and padding masks")
+    if (meta.B, meta.T) != (B, T):
+        raise ValueError(f"mask metadata is for (B, T) = ({meta.B}, {meta.T}), tensors have ({B}, {T})")
+    flags = (L.FLAG_ROPE if rope else 0) | (L.FLAG_SQRT_SOFTMAX if sqrt_softmax else 0) | (L.FLAG_FORCE_SIMT if force_simt else 0)
+    cos = sin = None
+    if rope:
+        cos, sin, _ = rope_tables(T, D, q_self.device, inv_freq)
+    if scale is None:
+        scale = D ** -0.5
+    ts = tuple(t.contiguous() for t in ts)
+    return _MultimerAttentionFn.apply(*ts, meta, cos, sin, float(scale), int(flags))
+
+
+# ----------------------------------------------------------------------------------------------- combine from logits
+class _CombineFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, il, el, mask_u8, iv, ev):
+        B, H, T, D = iv.shape
+        out = torch.empty_like(iv)
+        with torch.cuda.device(iv.device):
+            rc = L.lib().mintb_combine_fwd(_ptr(il), _ptr(el), _ptr(mask_u8), _ptr(iv), _ptr(ev), _ptr(out), B, H, T, D,
+                                          _DTYPES[iv.dtype], _stream())
+        L.check(rc, "mintb_combine_fwd")
+        ctx.save_for_backward(il, el, mask_u8, iv, ev)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        il, el, mask_u8, iv, ev = ctx.saved_tensors
+        B, H, T, D = iv.shape
+        d_out = d_out.contiguous()
+        d_il, d_el, d_iv, d_ev = torch.empty_like(il), torch.empty_like(el), torch.empty_like(iv), torch.empty_like(ev)
+        lib = L.lib()
+        ws_bytes = lib.mintb_combine_bwd_workspace_bytes(B, H, T)
+        ws = _workspace(ws_bytes, iv.device)
+        with torch.cuda.device(iv.device):
+            rc = lib.mintb_combine_bwd(_ptr(il), _ptr(el), _ptr(mask_u8), _ptr(iv), _ptr(ev), _ptr(d_out), _ptr(d_il),
+                                       _ptr(d_el), _ptr(d_iv), _ptr(d_ev), _ptr(ws), ws_bytes, B, H, T, D,
+                                       _DTYPES[iv.dtype], _stream())
+        L.check(rc, "mintb_combine_bwd")
+        return d_il, d_el, None, d_iv, d_ev
+
+
+def multimer_combine(intra_logits, inter_logits, chain_mask, intra_values, inter_values) -> torch.Tensor:
+    """Combine from materialised (B,H,T,T) logits (kernels/__init__.py:179-242 of the reference); differentiable."""
+    ts = (intra_logits, inter_logits, intra_values, inter_values)
+    _require_cuda(*ts, chain_mask)
+    B, H, T, D = intra_values.shape
+    if tuple(intra_logits.shape) != (B, H, T, T) or inter_logits.shape != intra_logits.shape \
+            or inter_values.shape != intra_values.shape or tuple(chain_mask.shape) != (B, T, T):
+        raise ValueError("expected logits (B,H,T,T) x2, chain_mask (B,T,T), values (B,H,T,D) x2")
+    if intra_values.dtype not in _DTYPES or any(t.dtype != intra_values.dtype for t in ts):
+        raise TypeError("logits and values must all be float32 or all be bfloat16")
+    m = chain_mask.contiguous().view(torch.uint8) if chain_mask.dtype == torch.bool else chain_mask.to(torch.uint8).contiguous()
+    return _CombineFn.apply(intra_logits.contiguous(), inter_logits.contiguous(), m, intra_values.contiguous(),
+                            inter_values.contiguous())

@@ -1,0 +1,36 @@
+"""RotaryEmbedding with the reference's module interface (mint_plus/models/rotary_embedding.py:27-55).
+
+The module keeps the `inv_freq` buffer (same state-dict key).  Inside the fused attention the rotation is
+done by the CUDA kernels from this buffer; calling the module directly rotates a (..., T, D) tensor with
+plain tensor arithmetic, as the reference does, for callers outside the fused path.
+"""
+from __future__ import annotations
+
+import torch
+
+
+def rotate_half(x):
+    x1, x2 = x.chunk(2, dim=-1)
+    return torch.cat((-x2, x1), dim=-1)
+
+
+def apply_rotary_pos_emb(x, cos, sin):
+    cos = cos[:, : x.shape[-2], :]
+    sin = sin[:, : x.shape[-2], :]
+    return (x * cos) + (rotate_half(x) * sin)
+
+
+class RotaryEmbedding(torch.nn.Module):
+    def __init__(self, dim: int, *_, **__):
+        super().__init__()
+        inv_freq = 1.0 / (10000 ** (torch.arange(0, dim, 2).float() / dim))
+        self.register_buffer("inv_freq", inv_freq)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        seq_len = x.shape[-2]
+        # fp32 tables whatever dtype the module was cast to: a bf16 table is off by radians at T ~ 1000
+        inv = self.inv_freq.float()
+        t = torch.arange(seq_len, device=x.device, dtype=torch.float32)
+        freqs = torch.outer(t, inv)
+        emb = torch.cat((freqs, freqs), dim=-1)
+        return apply_rotary_pos_emb(x, emb.cos()[None], emb.sin()[None])

@@ -1,0 +1,282 @@
+"""Parity of the CUDA attention path (called through the C ABI) with the CPU oracle and the golden vectors."""
+import math
+
+import pytest
+import torch
+
+from conftest import golden_cases, load_golden
+from oracle import multimer_attention as O
+
+pytestmark = pytest.mark.gpu
+
+import mint_plus_b200 as M  # noqa: E402
+from mint_plus_b200 import ops  # noqa: E402
+
+DEV = "cuda"
+# Tolerances.  fp32 kernels vs fp32 oracle: 1e-5 relative (plus a small absolute floor for values near zero).
+# bf16 kernels vs the fp32 oracle evaluated on the same bf16-rounded inputs: 2e-2 max-abs on attention outputs;
+# gradients carry the same bf16 rounding of P, dS and of the stored result, checked relative to their scale.
+F32_RTOL, F32_ATOL = 1e-5, 2e-6
+BF16_OUT_ATOL = 2e-2
+BF16_GRAD_REL = 2e-2
+
+
+def _run(ts, grad, dtype, **kw):
+    leaves = [t.to(DEV, dtype).requires_grad_(True) for t in ts]
+    out = M.multimer_attention(*leaves, **kw)
+    grads = torch.autograd.grad(out, leaves, grad.to(DEV, dtype))
+    ops.check_device_status()
+    return out.detach().float().cpu(), [g.float().cpu() for g in grads]
+
+
+def _assert_grads(got, want, dtype, names=("dq_s", "dk_s", "dv_s", "dq_c", "dk_c", "dv_c")):
+    for g, w, n in zip(got, want, names):
+        if dtype == torch.float32:
+            torch.testing.assert_close(g, w, rtol=1e-4, atol=5e-6, msg=lambda m: f"{n}: {m}")
+        else:
+            scale = w.abs().max().item() + 1e-6
+            err = (g - w).abs().max().item()
+            assert err <= BF16_GRAD_REL * scale, f"{n}: max err {err:.4g} vs scale {scale:.4g}"
+
+
+@pytest.mark.parametrize("force_simt", [True, False])
+@pytest.mark.parametrize("name", golden_cases())
+def test_golden_fp32(name, force_simt):
+    g = load_golden(name)
+    if g["sqrt_softmax"]:
+        pytest.skip("sqrt-softmax is not implemented")
+    ts = [g[k] for k in ("q_s", "k_s", "v_s", "q_c", "k_c", "v_c")]
+    out, grads = _run(ts, g["grad_out"], torch.float32, chain_ids=g["chain_ids"].to(DEV),
+                      key_padding_mask=g["key_pad"].to(DEV), rope=True, force_simt=force_simt)
+    torch.testing.assert_close(out, g["out"], rtol=F32_RTOL, atol=F32_ATOL)
+    _assert_grads(grads, [g[k] for k in ("dq_s", "dk_s", "dv_s", "dq_c", "dk_c", "dv_c")], torch.float32)
+
+
+@pytest.mark.parametrize("force_simt", [True, False])
+@pytest.mark.parametrize("name", golden_cases())
+def test_golden_bf16(name, force_simt):
+    g = load_golden(name)
+    if g["sqrt_softmax"]:
+        pytest.skip("sqrt-softmax is not implemented")
+    ts = [g[k].bfloat16().float() for k in ("q_s", "k_s", "v_s", "q_c", "k_c", "v_c")]
+    go = g["grad_out"].bfloat16().float()
+    mask = O.chain_mask_from_ids(g["chain_ids"])
+    want, wgrads = O.multimer_attention_fwd_bwd(*ts, mask, go, key_pad=g["key_pad"])
+    out, grads = _run(ts, go, torch.bfloat16, chain_ids=g["chain_ids"].to(DEV),
+                      key_padding_mask=g["key_pad"].to(DEV), rope=True, force_simt=force_simt)
+    assert (out - want).abs().max().item() <= BF16_OUT_ATOL
+    # and against the reference's own vectors (inputs differ by bf16 rounding only)
+    assert (out - g["out"]).abs().max().item() <= 2 * BF16_OUT_ATOL
+    _assert_grads(grads, wgrads, torch.bfloat16)
+
+
+# shapes of the reference's own kernel tests (profiles/test_sqrt_softmax.py:101-106) plus ragged ones
+SHAPES = [(2, 4, 64, 16), (4, 20, 128, 32), (2, 20, 256, 32), (2, 3, 200, 64), (1, 2, 77, 32), (1, 1, 1, 16),
+          (2, 2, 129, 64), (1, 2, 383, 32)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_seeded_inputs_against_oracle(shape, dtype):
+    B, H, T, D = shape
+    ts, cid, pad, grad = O.make_op_inputs(B, H, T, D, seed=42 + 100 * B + 10 * H + T, max_pad=min(64, T // 4))
+    if dtype == torch.bfloat16:
+        ts, grad = [t.bfloat16().float() for t in ts], grad.bfloat16().float()
+    want, wgrads = O.multimer_attention_fwd_bwd(*ts, O.chain_mask_from_ids(cid), grad, key_pad=pad)
+    out, grads = _run(ts, grad, dtype, chain_ids=cid.to(DEV), key_padding_mask=pad.to(DEV))
+    if dtype == torch.float32:
+        torch.testing.assert_close(out, want, rtol=F32_RTOL, atol=F32_ATOL)
+    else:
+        assert (out - want).abs().max().item() <= BF16_OUT_ATOL
+    _assert_grads(grads, wgrads, dtype)
+
+
+def _edge_masks(T):
+    cases = {}
+    cid = torch.zeros(1, T, dtype=torch.int32)
+    cases["single_chain"] = (cid.clone(), None)
+    c = cid.clone(); c[:, 64:] = 1
+    cases["split_on_tile_boundary"] = (c, None)
+    c = cid.clone(); c[:, 63:] = 1
+    cases["split_before_boundary"] = (c, None)
+    c = cid.clone(); c[:, 65:] = 1
+    cases["split_after_boundary"] = (c, None)
+    c = cid.clone(); c[:, 1::2] = 1
+    cases["alternating"] = (c, None)
+    c = cid.clone(); c[:, T // 2:] = 1
+    p = torch.zeros(1, T, dtype=torch.bool); p[:, T // 2 - 9:T // 2] = True; p[:, -64:] = True
+    cases["pads_mid_and_full_tail_tile"] = (c, p)
+    p = torch.zeros(1, T, dtype=torch.bool); p[:, 1:] = True
+    cases["one_real_key"] = (c, p)
+    c = torch.arange(T, dtype=torch.int32)[None] // 50
+    cases["many_chains"] = (c, None)
+    return cases
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", list(_edge_masks(200)))
+def test_edge_masks(case, dtype):
+    T, H, D = 200, 2, 32
+    cid, pad = _edge_masks(T)[case]
+    ts, _, _, grad = O.make_op_inputs(1, H, T, D, seed=7)
+    if dtype == torch.bfloat16:
+        ts, grad = [t.bfloat16().float() for t in ts], grad.bfloat16().float()
+    want, wgrads = O.multimer_attention_fwd_bwd(*ts, O.chain_mask_from_ids(cid), grad, key_pad=pad)
+    out, grads = _run(ts, grad, dtype, chain_ids=cid.to(DEV), key_padding_mask=None if pad is None else pad.to(DEV))
+    if dtype == torch.float32:
+        torch.testing.assert_close(out, want, rtol=F32_RTOL, atol=F32_ATOL)
+    else:
+        assert (out - want).abs().max().item() <= BF16_OUT_ATOL
+    _assert_grads(grads, wgrads, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_reference_signature_with_arbitrary_mask(dtype):
+    """fused_multi_pathway_attention: pre-scaled, pre-rotated inputs and a non-symmetric Bernoulli(0.4) mask with
+    the diagonal forced intra (profiles/test_fused_attention.py:60-61 of the reference)."""
+    B, H, T, D = 2, 4, 160, 32
+    g = torch.Generator().manual_seed(3)
+    ts = [torch.randn(B, H, T, D, generator=g) for _ in range(6)]
+    ts[0] *= D ** -0.5
+    ts[3] *= D ** -0.5
+    mask = torch.rand(B, T, T, generator=g) < 0.4
+    mask[:, torch.arange(T), torch.arange(T)] = False
+    grad = torch.randn(B, H, T, D, generator=g)
+    if dtype == torch.bfloat16:
+        ts, grad = [t.bfloat16().float() for t in ts], grad.bfloat16().float()
+    want, wgrads = O.multimer_attention_fwd_bwd(*ts, mask, grad, scale=1.0, rope=False)
+    leaves = [t.to(DEV, dtype).requires_grad_(True) for t in ts]
+    out = M.differentiable_multi_pathway_attention(*leaves, mask.to(DEV))
+    grads = torch.autograd.grad(out, leaves, grad.to(DEV, dtype))
+    ops.check_device_status()
+    if dtype == torch.float32:
+        torch.testing.assert_close(out.float().cpu(), want, rtol=F32_RTOL, atol=F32_ATOL)
+    else:
+        assert (out.float().cpu() - want).abs().max().item() <= BF16_OUT_ATOL
+    _assert_grads([x.float().cpu() for x in grads], wgrads, dtype)
+
+
+def test_mask_metadata_bits_are_exact():
+    B, T = 3, 150
+    g = torch.Generator().manual_seed(9)
+    cid = torch.randint(0, 3, (B, T), generator=g, dtype=torch.int32)
+    pad = torch.rand(B, T, generator=g) < 0.2
+    meta = M.mask_meta_from_chain_ids(cid.to(DEV), pad.to(DEV))
+    mask = O.chain_mask_from_ids(cid)
+    meta2 = M.mask_meta_from_mask(mask.to(DEV), pad.to(DEV))
+    assert torch.equal(meta.buf, meta2.buf)
+    TW = ((T + 31) // 32 + 3) // 4 * 4
+    words = meta.buf[:B * T * TW * 4].view(torch.int32).view(B, T, TW).cpu()
+    bits = ((words[..., None] >> torch.arange(32)) & 1).reshape(B, T, TW * 32)[:, :, :T].bool()
+    assert torch.equal(bits, mask)
+    # an asymmetric mask: the key-major copy is the transpose
+    am = torch.rand(B, T, T, generator=g) < 0.5
+    meta3 = M.mask_meta_from_mask(am.to(DEV))
+    n = (B * T * TW * 4 + 255) // 256 * 256
+    wt = meta3.buf[n:n + B * T * TW * 4].view(torch.int32).view(B, T, TW).cpu()
+    bt = ((wt[..., None] >> torch.arange(32)) & 1).reshape(B, T, TW * 32)[:, :, :T].bool()
+    assert torch.equal(bt, am.transpose(1, 2))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_forward_is_deterministic_and_padded_keys_are_inert(dtype):
+    ts, cid, pad, _ = O.make_op_inputs(2, 4, 300, 32, seed=11, max_pad=40)
+    pad[0, -7:] = True
+    dts = [t.to(DEV, dtype) for t in ts]
+    kw = dict(chain_ids=cid.to(DEV), key_padding_mask=pad.to(DEV))
+    a = M.multimer_attention(*dts, **kw)
+    b = M.multimer_attention(*dts, **kw)
+    assert torch.equal(a, b)
+    poisoned = [t.clone() for t in dts]
+    for idx in (1, 2, 4, 5):                      # K and V of both pathways at padded positions
+        poisoned[idx][pad.to(DEV)[:, None, :].expand(-1, 4, -1)] = 1e4
+    c = M.multimer_attention(*poisoned, **kw)
+    assert torch.equal(a, c)
+    assert torch.isfinite(a).all()
+
+
+@pytest.mark.parametrize("D", [32, 64])
+def test_full_size_properties(D):
+    """Benchmark-size inputs (B8 H20 T1024): rows of P sum to one, V-linearity, tensor-core path vs fp32 path."""
+    B, H, T = 8, 20, 1024
+    ts, cid, pad, grad = O.make_op_inputs(B, H, T, D, seed=2002)
+    dts = [t.to(DEV, torch.bfloat16) for t in ts]
+    kw = dict(chain_ids=cid.to(DEV), key_padding_mask=pad.to(DEV))
+    ones = torch.ones_like(dts[2])
+    s = M.multimer_attention(dts[0], dts[1], ones, dts[3], dts[4], ones, **kw).float()
+    assert (s - 1).abs().max().item() <= 1e-2
+    out = M.multimer_attention(*dts, **kw).float()
+    ref = M.multimer_attention(*dts, force_simt=True, **kw).float()
+    assert (out - ref).abs().max().item() <= BF16_OUT_ATOL
+    half = [dts[0], dts[1], (dts[2].float() * 0.5).bfloat16(), dts[3], dts[4], (dts[5].float() * 0.5).bfloat16()]
+    lin = M.multimer_attention(*half, **kw).float()
+    assert (2 * lin - out).abs().max().item() <= BF16_OUT_ATOL
+    # gradients of the two kernel families agree
+    leaves = [t.clone().requires_grad_(True) for t in dts]
+    go = grad.to(DEV, torch.bfloat16)
+    g1 = torch.autograd.grad(M.multimer_attention(*leaves, **kw), leaves, go)
+    g2 = torch.autograd.grad(M.multimer_attention(*leaves, force_simt=True, **kw), leaves, go)
+    ops.check_device_status()
+    for a, b in zip(g1, g2):
+        scale = b.float().abs().max().item()
+        assert (a.float() - b.float()).abs().max().item() <= BF16_GRAD_REL * scale
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_combine_from_materialised_logits(dtype):
+    B, H, T, D = 2, 3, 70, 32
+    ts, cid, pad, grad = O.make_op_inputs(B, H, T, D, seed=21, max_pad=6)
+    mask = O.chain_mask_from_ids(cid)
+    il = O.combined_logits(ts[0], ts[1], ts[3], ts[4], torch.zeros_like(mask), pad)
+    el = O.combined_logits(ts[0], ts[1], ts[3], ts[4], torch.ones_like(mask), pad)
+    if dtype == torch.bfloat16:
+        il, el, ts, grad = il.bfloat16().float(), el.bfloat16().float(), [t.bfloat16().float() for t in ts], grad.bfloat16().float()
+    leaves = [t.clone().requires_grad_(True) for t in (il, el, ts[2], ts[5])]
+    want = O.combine_from_logits(leaves[0], leaves[1], mask, leaves[2], leaves[3])
+    wg = torch.autograd.grad(want, leaves, grad)
+    dl = [t.detach().to(DEV, dtype).requires_grad_(True) for t in (il, el, ts[2], ts[5])]
+    out = M.differentiable_multimer_combine(dl[0], dl[1], mask.to(DEV), dl[2], dl[3])
+    gg = torch.autograd.grad(out, dl, grad.to(DEV, dtype))
+    if dtype == torch.float32:
+        torch.testing.assert_close(out.cpu(), want.detach(), rtol=F32_RTOL, atol=F32_ATOL)
+        for a, b in zip(gg, wg):
+            torch.testing.assert_close(a.cpu(), b, rtol=1e-4, atol=5e-6)
+    else:
+        assert (out.float().cpu() - want.detach()).abs().max().item() <= BF16_OUT_ATOL
+        for a, b in zip(gg, wg):
+            assert (a.float().cpu() - b).abs().max().item() <= BF16_GRAD_REL * (b.abs().max().item() + 1e-6)
+
+
+def test_layer_forward_backward_matches_oracle_composition():
+    """TransformerLayer_MINT_plus on the GPU vs the same layer evaluated with the oracle attention on the CPU."""
+    torch.manual_seed(5)
+    E, H, T, B = 64, 4, 90, 2
+    layer = M.TransformerLayer_MINT_plus(E, 4 * E, H, use_multimer=True, use_erf_gelu=True).float()
+    x = torch.randn(T, B, E)
+    cid = torch.zeros(B, T, dtype=torch.int32); cid[:, 40:] = 1
+    pad = torch.zeros(B, T, dtype=torch.bool); pad[1, -11:] = True
+    mask = O.chain_mask_from_ids(cid)
+
+    def cpu_forward(x):
+        h = layer.self_attn_layer_norm(x)
+        qs, ks, vs = layer.self_attn.project_qkv_4d(h)
+        qc, kc, vc = layer.multimer_attn.project_qkv_4d(h)
+        a = O.multimer_attention(qs, ks, vs, qc, kc, vc, mask, pad)
+        a = layer.self_attn.out_proj(a.permute(2, 0, 1, 3).reshape(T, B, E))
+        y = x + a
+        return y + layer.feed_forward(layer.final_layer_norm(y))
+
+    xc = x.clone().requires_grad_(True)
+    want = cpu_forward(xc)
+    want.sum().backward()
+    wgrad_x = xc.grad.clone()
+    wgrad_w = layer.multimer_attn.fused_qkv.weight.grad.clone()
+    layer.zero_grad()
+    glayer = layer.to(DEV)
+    xg = x.to(DEV).requires_grad_(True)
+    out, _ = glayer(xg, self_attn_mask=mask.to(DEV), self_attn_padding_mask=pad.to(DEV))
+    out.sum().backward()
+    torch.testing.assert_close(out.detach().cpu(), want.detach(), rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(xg.grad.cpu(), wgrad_x, rtol=1e-3, atol=1e-4)
+    torch.testing.assert_close(glayer.multimer_attn.fused_qkv.weight.grad.cpu(), wgrad_w, rtol=1e-3, atol=1e-4)
+    layer.to("cpu")
