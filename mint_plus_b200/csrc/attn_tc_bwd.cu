@@ -1,0 +1,579 @@
+// tcgen05 backward of the combined-softmax multimer attention (bf16 in, fp32 accumulate).
+//
+// With the forward log-sum-exp known, the two pathways are independent: the self pathway contributes
+// P o ~M and the cross pathway P o M, each computed from its own Q, K, V.  The grid is
+// (key tiles of 128, batch*head, pathway); a CTA owns dK and dV of its key tile in TMEM and walks the query
+// tiles of 128 whose class holds pairs of its pathway:
+//   S^T = K Q^T, dP^T = V dO^T            (lane = key, column = query; two halves of 64 queries)
+//   P^T = exp2(S^T c - lse), masked       dS^T = P^T o (dP^T - delta)
+//   dV += P^T dO, dK += dS^T Q            (A operands read from TMEM, aliased over S^T / dP^T)
+//   dQ_tile = dS K                        (dS through shared memory), added to an fp32 accumulator in HBM
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 compute half 0, warps 6-9 compute half 1.
+// The two compute groups ping-pong: while one works on its half the tensor pipe serves the other.
+// TMEM (512 columns): dK [0,64) dV [64,128) dQ x2 [128,256) S^T halves [256,384) dP^T halves [384,512).
+// dQ is accumulated across CTAs with fp32 atomics, so its low-order bits depend on arrival order;
+// dK and dV are reduced inside one CTA in a fixed order.  All mbarrier waits are bounded.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace mintb {
+
+using namespace ptx;
+
+constexpr int kBwdTile = 128;       // keys per CTA and queries per step
+constexpr int kHalf = 64;           // queries per compute group
+constexpr int kBwdThreads = 320;
+constexpr int kBwdStages = 2;
+constexpr int kBwdMaxTiles = 256;   // T <= 32768
+constexpr uint32_t kTmemAll = 512;
+constexpr int kColDK = 0, kColDV = 64, kColDQ = 128, kColS = 256, kColDP = 384;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn bwd_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+static bool bwd_make_map(CUtensorMap* m, const void* ptr, int D, int T, int BH, int box_rows) {
+  EncodeTiledFn fn = bwd_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[3] = {cuuint64_t(D), cuuint64_t(T), cuuint64_t(BH)};
+  cuuint64_t strides[2] = {cuuint64_t(D) * 2, cuuint64_t(T) * D * 2};
+  cuuint32_t box[3] = {cuuint32_t(D), cuuint32_t(box_rows), 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUtensorMapSwizzle sw = D == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : D == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+__device__ __forceinline__ float bwd_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t bwd_pack(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ void named_barrier(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// ------------------------------------------------------------------------------------------------ pre / post passes
+// delta[bh][i] = sum_d dO[i][d] * O[i][d]; one warp per 4 rows (8 lanes x 16 bytes cover D = 64).
+__global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                                        float* __restrict__ delta, size_t rows, int D) {
+  const int lpr = D / 8;  // lanes per row
+  const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t row = idx / lpr;
+  const int c = int(idx % lpr);
+  float acc = 0.f;
+  if (row < rows) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + row * D + c * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(d_o + row * D + c * 8);
+    const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = __bfloat1622float2(ap[e]), y = __bfloat1622float2(bp[e]);
+      acc = fmaf(x.x, y.x, acc);
+      acc = fmaf(x.y, y.y, acc);
+    }
+  }
+  for (int off = lpr / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < rows && c == 0) delta[row] = acc;
+}
+
+// dq = scale * R^T(acc) for the self pathway (with tables), scale * acc for the cross pathway; fp32 -> bf16.
+__global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __restrict__ acc_s, const float* __restrict__ acc_c,
+                                                             __nv_bfloat16* __restrict__ dq_s, __nv_bfloat16* __restrict__ dq_c,
+                                                             const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                                                             size_t rows, int T, int D, float scale) {
+  const int h = D / 2, cpr = h / 8;
+  const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= rows * cpr) return;
+  const int c = int(idx % cpr);
+  const size_t row = idx / cpr;
+  const int t = int(row % T);
+  float lo[8], hi[8];
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const float* src = (which == 0 ? acc_s : acc_c) + row * D + c * 8;
+    __nv_bfloat16* dst = (which == 0 ? dq_s : dq_c) + row * D + c * 8;
+    *reinterpret_cast<float4*>(lo) = *reinterpret_cast<const float4*>(src);
+    *reinterpret_cast<float4*>(lo + 4) = *reinterpret_cast<const float4*>(src + 4);
+    *reinterpret_cast<float4*>(hi) = *reinterpret_cast<const float4*>(src + h);
+    *reinterpret_cast<float4*>(hi + 4) = *reinterpret_cast<const float4*>(src + h + 4);
+    uint4 olo, ohi;
+    __nv_bfloat16* olp = reinterpret_cast<__nv_bfloat16*>(&olo);
+    __nv_bfloat16* ohp = reinterpret_cast<__nv_bfloat16*>(&ohi);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float a = lo[e], b = hi[e];
+      if (which == 0 && cos_tab != nullptr) {  // R^T: dx_lo = dy_lo c + dy_hi s, dx_hi = dy_hi c - dy_lo s
+        const float cs = cos_tab[size_t(t) * h + c * 8 + e], sn = sin_tab[size_t(t) * h + c * 8 + e];
+        const float na = a * cs + b * sn, nb = b * cs - a * sn;
+        a = na;
+        b = nb;
+      }
+      olp[e] = __float2bfloat16_rn(a * scale);
+      ohp[e] = __float2bfloat16_rn(b * scale);
+    }
+    *reinterpret_cast<uint4*>(dst) = olo;
+    *reinterpret_cast<uint4*>(dst + h) = ohi;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ main kernel
+template <int D>
+struct BwdCfg {
+  static constexpr int kRowBytes = 2 * D;
+  static constexpr int kTileBytes = kBwdTile * kRowBytes;       // K, V, Q_i, dO_i tiles
+  static constexpr int kDsBlock = kBwdTile * 128;               // one half (64 queries) of dS: [128 key rows][128 B]
+  static constexpr int kDsBytes = 2 * kDsBlock;
+  static constexpr size_t kSmemBytes = 1024 + 2 * kTileBytes + size_t(kBwdStages) * 2 * kTileBytes + 2 * kDsBytes + 4096;
+};
+
+struct BwdParams {
+  const uint32_t *bitsT, *kpad;
+  const uint8_t* cls;
+  const float *lse, *delta;
+  const float *cos_tab, *sin_tab;  // null without rope
+  float* dq_acc[2];                // fp32 [B*H][T][D] per pathway
+  __nv_bfloat16 *dk[2], *dv[2];
+  int H, T, TW, NT;
+  float scale, scale_log2;
+  int* status;
+};
+
+template <int NCOL>
+__device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t* r);
+template <>
+__device__ __forceinline__ void tmem_ld_n<32>(uint32_t taddr, uint32_t* r) { tmem_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(r)); }
+template <>
+__device__ __forceinline__ void tmem_ld_n<16>(uint32_t taddr, uint32_t* r) { tmem_ld16(taddr, *reinterpret_cast<uint32_t(*)[16]>(r)); }
+template <>
+__device__ __forceinline__ void tmem_ld_n<8>(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_constant__ CUtensorMap map_ks,
+                   const __grid_constant__ CUtensorMap map_vs, const __grid_constant__ CUtensorMap map_qc,
+                   const __grid_constant__ CUtensorMap map_kc, const __grid_constant__ CUtensorMap map_vc,
+                   const __grid_constant__ CUtensorMap map_do, BwdParams p) {
+  using Cfg = BwdCfg<D>;
+  constexpr int RB = Cfg::kRowBytes;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sK = smem;
+  unsigned char* sV = sK + Cfg::kTileBytes;
+  unsigned char* sQ = sV + Cfg::kTileBytes;                        // [stage][0: Q_i, 1: dO_i]
+  unsigned char* sDS = sQ + size_t(kBwdStages) * 2 * Cfg::kTileBytes;  // [buf][half][128 rows x 128 B]
+  unsigned char* tail = sDS + 2 * Cfg::kDsBytes;
+  float* s_nlse = reinterpret_cast<float*>(tail);                  // [2 groups][2 bufs][64]  (-lse * log2 e)
+  float* s_delta = s_nlse + 256;                                   // [2 groups][2 bufs][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 256);
+  uint64_t* kv_full = bars;            // 1
+  uint64_t* q_full = bars + 1;         // [2]
+  uint64_t* q_empty = bars + 3;        // [2]
+  uint64_t* sdp_full = bars + 5;       // [2 halves]
+  uint64_t* pds_full = bars + 7;       // [2 halves]
+  uint64_t* dq_full = bars + 9;        // [2 bufs]
+  uint64_t* dq_empty = bars + 11;      // [2 bufs]
+  uint64_t* acc_full = bars + 13;      // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint8_t* tq = reinterpret_cast<uint8_t*>(tmem_slot + 2);  // per query tile: 0 skip, else 1 | (needs chain mask) << 1 | (pad) << 2
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int kt = blockIdx.x, bh = blockIdx.y, path = blockIdx.z, b = bh / p.H;
+  const int k0 = kt * kBwdTile;
+  const int nqt = (p.T + kBwdTile - 1) / kBwdTile;
+  const uint8_t want = path == 0 ? kHasIntra : kHasInter;
+
+  for (int i = tid; i < nqt; i += kBwdThreads) {
+    uint8_t c = 0;
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+        if (2 * i + a < p.NT && 2 * kt + e < p.NT) c |= p.cls[(size_t(b) * p.NT + 2 * i + a) * p.NT + 2 * kt + e];
+    uint8_t f = 0;
+    if (c & want) f = 1 | (((c & 3) == 3) ? 2 : 0) | ((c & kHasPad) ? 4 : 0);
+    tq[i] = f;
+  }
+  if (tid == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1);
+      mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 128);
+      mbar_init(&dq_full[s], 1); mbar_init(&dq_empty[s], 256);
+    }
+    mbar_init(acc_full, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, kTmemAll); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = *tmem_slot;
+  int n_active = 0;
+  for (int i = 0; i < nqt; ++i) n_active += tq[i] != 0;
+
+  const CUtensorMap* mq = path == 0 ? &map_qs : &map_qc;
+  const CUtensorMap* mk = path == 0 ? &map_ks : &map_kc;
+  const CUtensorMap* mv = path == 0 ? &map_vs : &map_vc;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0 && n_active > 0) {
+      prefetch_tensormap(mq); prefetch_tensormap(mk); prefetch_tensormap(mv); prefetch_tensormap(&map_do);
+      mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
+      tma_load_3d(sK, mk, kv_full, 0, k0, bh);
+      tma_load_3d(sV, mv, kv_full, 0, k0, bh);
+      int it = 0;
+      for (int i = 0; i < nqt; ++i) {
+        if (tq[i] == 0) continue;
+        const int stage = it % kBwdStages;
+        if (!mbar_wait(&q_empty[stage], ((it / kBwdStages) & 1) ^ 1, p.status, 0x401)) break;
+        unsigned char* dst = sQ + size_t(stage) * 2 * Cfg::kTileBytes;
+        mbar_expect_tx(&q_full[stage], 2 * Cfg::kTileBytes);
+        tma_load_3d(dst, mq, &q_full[stage], 0, i * kBwdTile, bh);
+        tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[stage], 0, i * kBwdTile, bh);
+        ++it;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_active > 0) {
+      constexpr uint32_t idesc_s = idesc_bf16(kBwdTile, kHalf, false, false);   // S^T, dP^T halves: M = 128 keys, N = 64 queries
+      constexpr uint32_t idesc_acc = idesc_bf16(kBwdTile, D, false, true);      // dV, dK: A from TMEM, B = dO / Q rows (N = D contiguous)
+      constexpr uint32_t idesc_dq = idesc_bf16(kBwdTile, D, true, true);        // dQ: A = dS (queries contiguous), B = K (D contiguous)
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), ds_addr = smem_u32(sDS);
+      bool ok = mbar_wait(kv_full, 0, p.status, 0x501);
+      tc_fence_after();
+
+      auto issue_sdp = [&](int it, int h) {   // S^T and dP^T of half h of active tile `it`
+        const uint32_t qs = q_addr + uint32_t(it % kBwdStages) * 2 * Cfg::kTileBytes + h * kHalf * RB;
+        const uint32_t dos = qs + Cfg::kTileBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_ss(tbase + kColS + h * kHalf, desc_k_major(k_addr + k * 32, RB), desc_k_major(qs + k * 32, RB), idesc_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_ss(tbase + kColDP + h * kHalf, desc_k_major(v_addr + k * 32, RB), desc_k_major(dos + k * 32, RB), idesc_s, k > 0);
+        umma_commit(&sdp_full[h]);
+      };
+      auto issue_acc = [&](int it, int h) {   // dV += P^T dO, dK += dS^T Q for half h
+        const uint32_t qs = q_addr + uint32_t(it % kBwdStages) * 2 * Cfg::kTileBytes + h * kHalf * RB;
+        const uint32_t dos = qs + Cfg::kTileBytes;
+#pragma unroll
+        for (int k = 0; k < kHalf / 16; ++k)
+          umma_ts(tbase + kColDV, tbase + kColS + h * kHalf + k * 8, desc_mn_major(dos + k * 16 * RB, RB, 8 * RB), idesc_acc,
+                  it > 0 || h > 0 || k > 0);
+#pragma unroll
+        for (int k = 0; k < kHalf / 16; ++k)
+          umma_ts(tbase + kColDK, tbase + kColDP + h * kHalf + k * 8, desc_mn_major(qs + k * 16 * RB, RB, 8 * RB), idesc_acc,
+                  it > 0 || h > 0 || k > 0);
+      };
+
+      if (ok) ok = mbar_wait(&q_full[0], 0, p.status, 0x502);
+      tc_fence_after();
+      if (ok) { issue_sdp(0, 0); issue_sdp(0, 1); }
+      for (int it = 0; it < n_active && ok; ++it) {
+        const bool has_next = it + 1 < n_active;
+        const int stage = it % kBwdStages;
+        // half 0
+        ok = mbar_wait(&pds_full[0], it & 1, p.status, 0x503);
+        if (!ok) break;
+        tc_fence_after();
+        issue_acc(it, 0);
+        if (has_next) {
+          ok = mbar_wait(&q_full[(it + 1) % kBwdStages], ((it + 1) / kBwdStages) & 1, p.status, 0x504);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sdp(it + 1, 0);
+        }
+        // half 1
+        ok = mbar_wait(&pds_full[1], it & 1, p.status, 0x505);
+        if (!ok) break;
+        tc_fence_after();
+        issue_acc(it, 1);
+        // dQ tile = dS K into buffer it & 1 (drained two tiles ago)
+        ok = mbar_wait(&dq_empty[it & 1], ((it / 2) & 1) ^ 1, p.status, 0x506);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t dsb = ds_addr + uint32_t(it & 1) * Cfg::kDsBytes;
+#pragma unroll
+        for (int k = 0; k < kBwdTile / 16; ++k)
+          umma_ss(tbase + kColDQ + (it & 1) * 64, desc_mn_major(dsb + k * 16 * 128, 128, Cfg::kDsBlock),
+                  desc_mn_major(k_addr + k * 16 * RB, RB, 8 * RB), idesc_dq, k > 0);
+        umma_commit(&dq_full[it & 1]);
+        umma_commit(&q_empty[stage]);
+        if (has_next) issue_sdp(it + 1, 1);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    // ---------------------------------------------------------------- compute groups (lane = key row)
+    const int g = (warp - 2) / 4;                 // half of the query tile this group owns
+    const int quarter = warp % 4;
+    const int r = quarter * 32 + lane;            // key row in the tile == TMEM lane
+    const int tw = ((warp - 2) % 4) * 32 + lane;  // thread index inside the group
+    const int kj = k0 + r;
+    const int krow = kj < p.T ? kj : p.T - 1;
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    const uint32_t tS = tbase + lane_base + kColS + g * kHalf;
+    const uint32_t tDP = tbase + lane_base + kColDP + g * kHalf;
+    const bool key_valid = kj < p.T && !((p.kpad[size_t(b) * p.TW + krow / 32] >> (krow % 32)) & 1u);
+    const uint32_t* mrow = p.bitsT + (size_t(b) * p.T + krow) * p.TW;
+    const uint32_t flip = path == 0 ? 0xffffffffu : 0u;   // keep-bit = mask bit XOR flip
+    const float c2 = p.scale_log2;
+    const float* lse_bh = p.lse + size_t(bh) * p.T;
+    const float* delta_bh = p.delta + size_t(bh) * p.T;
+    float* dq_bh = p.dq_acc[path] + size_t(bh) * p.T * D;
+    bool ok = true;
+    int it = 0;
+
+    auto drain_dq = [&](int jt, int qtile) -> bool {   // add dQ of active tile jt (query tile qtile) to HBM
+      if (!mbar_wait(&dq_full[jt & 1], (jt / 2) & 1, p.status, 0x601)) return false;
+      tc_fence_after();
+      constexpr int NC = D / 2;   // columns per group
+      uint32_t v[NC];
+      tmem_ld_n<NC>(tbase + lane_base + kColDQ + (jt & 1) * 64 + g * NC, v);
+      tmem_ld_wait();
+      const int qi = qtile * kBwdTile + r;
+      if (qi < p.T) {
+        float* dst = dq_bh + size_t(qi) * D + g * NC;
+#pragma unroll
+        for (int e = 0; e < NC; e += 4)
+          atomicAdd(reinterpret_cast<float4*>(dst + e), make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
+                                                                    __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3])));
+      }
+      tc_fence_before();
+      mbar_arrive(&dq_empty[jt & 1]);
+      return true;
+    };
+
+    int prev_tile = -1;
+    for (int i = 0; i < nqt && ok; ++i) {
+      const uint8_t f = tq[i];
+      if (f == 0) continue;
+      // per-query statistics of this half into shared memory (double buffered across tiles)
+      float* nl = s_nlse + (g * 2 + (it & 1)) * 64;
+      float* dl = s_delta + (g * 2 + (it & 1)) * 64;
+      {
+        const int q = i * kBwdTile + g * kHalf + (tw & 63);
+        if (tw < 64) nl[tw] = q < p.T ? -lse_bh[q] * kLog2e : -INFINITY;
+        else dl[tw - 64] = q < p.T ? delta_bh[q] : 0.f;
+      }
+      named_barrier(1 + g, 128);
+      ok = mbar_wait(&sdp_full[g], it & 1, p.status, 0x602);
+      if (!ok) break;
+      tc_fence_after();
+      const bool use_mask = (f & 2) != 0;
+      const uint2 mw = use_mask ? *reinterpret_cast<const uint2*>(mrow + 4 * i + 2 * g) : make_uint2(0, 0);
+      unsigned char* ds_row = sDS + size_t(it & 1) * Cfg::kDsBytes + size_t(g) * Cfg::kDsBlock;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[32], dp[32];
+        tmem_ld32(tS + 32 * half, s);
+        tmem_ld32(tDP + 32 * half, dp);
+        tmem_ld_wait();
+        const uint32_t keep = use_mask ? ((half == 0 ? mw.x : mw.y) ^ flip) : 0xffffffffu;
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float p0 = bwd_ex2(fmaf(__uint_as_float(s[j]), c2, nl[32 * half + j]));
+          float p1 = bwd_ex2(fmaf(__uint_as_float(s[j + 1]), c2, nl[32 * half + j + 1]));
+          if (!(((keep >> j) & 1u) && key_valid)) p0 = 0.f;
+          if (!(((keep >> (j + 1)) & 1u) && key_valid)) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(dp[j]) - dl[32 * half + j]);
+          const float d1 = p1 * (__uint_as_float(dp[j + 1]) - dl[32 * half + j + 1]);
+          pp[j / 2] = bwd_pack(p0, p1);
+          dd[j / 2] = bwd_pack(d0, d1);
+        }
+        tmem_st16(tS + 16 * half, pp);     // P^T over the already-read S^T columns
+        tmem_st16(tDP + 16 * half, dd);    // dS^T likewise
+#pragma unroll
+        for (int cch = 0; cch < 4; ++cch)  // and dS into shared memory for the dQ product: 4 chunks of 8 queries
+          *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 4 * half + cch, 128)) =
+              make_uint4(dd[4 * cch], dd[4 * cch + 1], dd[4 * cch + 2], dd[4 * cch + 3]);
+      }
+      tmem_st_wait();
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&pds_full[g]);
+      if (prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
+      prev_tile = i;
+      ++it;
+    }
+    if (ok && prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
+
+    // ---- epilogue: group 0 writes dK (scaled, un-rotated for the self pathway), group 1 writes dV
+    if (n_active > 0) {
+      if (ok) ok = mbar_wait(acc_full, 0, p.status, 0x603);
+      tc_fence_after();
+    }
+    if (ok && kj < p.T) { /* row guard applied at the stores below */ }
+    if (ok) {
+      float v[D];
+      if (n_active > 0) {
+        const uint32_t src = tbase + lane_base + (g == 0 ? kColDK : kColDV);
+        if constexpr (D >= 32) {
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t t32[32];
+            tmem_ld32(src + c0, t32);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[c0 + j] = __uint_as_float(t32[j]);
+          }
+        } else {
+          uint32_t t16[16];
+          tmem_ld16(src, t16);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(t16[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < D; ++j) v[j] = 0.f;
+      }
+      if (kj < p.T) {
+        __nv_bfloat16* dst = (g == 0 ? p.dk[path] : p.dv[path]) + (size_t(bh) * p.T + kj) * D;
+        if (g == 0) {
+          constexpr int h = D / 2;
+          if (path == 0 && p.cos_tab != nullptr) {
+#pragma unroll
+            for (int d = 0; d < h; ++d) {
+              const float cs = p.cos_tab[size_t(kj) * h + d], sn = p.sin_tab[size_t(kj) * h + d];
+              const float a = v[d], bb = v[d + h];
+              v[d] = a * cs + bb * sn;
+              v[d + h] = bb * cs - a * sn;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < D; ++j) v[j] *= p.scale;
+        }
+#pragma unroll
+        for (int j = 0; j < D; j += 8)
+          *reinterpret_cast<uint4*>(dst + j) = make_uint4(bwd_pack(v[j], v[j + 1]), bwd_pack(v[j + 2], v[j + 3]),
+                                                          bwd_pack(v[j + 4], v[j + 5]), bwd_pack(v[j + 6], v[j + 7]));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tbase, kTmemAll);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+static size_t bwd_rot_bytes(int B, int H, int T, int D) { return align256(size_t(B) * H * T * D * 2); }
+static size_t bwd_acc_bytes(int B, int H, int T, int D) { return align256(size_t(B) * H * T * D * 4); }
+static size_t bwd_delta_bytes(int B, int H, int T) { return align256(size_t(B) * H * T * 4); }
+
+// Workspace: [rotated Q_self | rotated K_self] (rope only) | delta | dQ accumulator self | dQ accumulator cross
+size_t tc_bwd_workspace_bytes(int B, int H, int T, int D, bool rope) {
+  return (rope ? 2 * bwd_rot_bytes(B, H, T, D) : 0) + bwd_delta_bytes(B, H, T) + 2 * bwd_acc_bytes(B, H, T, D);
+}
+
+void launch_rope_rotate(const AttnArgs& a, __nv_bfloat16* qr, __nv_bfloat16* kr);  // attn_tc.cu
+
+template <int D>
+static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, float* delta, float* acc_s, float* acc_c) {
+  using Cfg = BwdCfg<D>;
+  const int BH = a.B * a.H;
+  CUtensorMap mqs, mks, mvs, mqc, mkc, mvc, mdo;
+  if (!bwd_make_map(&mqs, q_s, D, a.T, BH, kBwdTile) || !bwd_make_map(&mks, k_s, D, a.T, BH, kBwdTile) ||
+      !bwd_make_map(&mvs, a.v_s, D, a.T, BH, kBwdTile) || !bwd_make_map(&mqc, a.q_c, D, a.T, BH, kBwdTile) ||
+      !bwd_make_map(&mkc, a.k_c, D, a.T, BH, kBwdTile) || !bwd_make_map(&mvc, a.v_c, D, a.T, BH, kBwdTile) ||
+      !bwd_make_map(&mdo, a.d_out, D, a.T, BH, kBwdTile)) {
+    set_error("mintb_attn_bwd: cuTensorMapEncodeTiled failed");
+    return MINTB_ECUDA;
+  }
+  cudaError_t e = cudaFuncSetAttribute(attn_bwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Cfg::kSmemBytes));
+  if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
+  BwdParams p{};
+  p.bitsT = a.meta.bitsT; p.kpad = a.meta.kpad; p.cls = a.meta.cls;
+  p.lse = a.lse; p.delta = delta;
+  p.cos_tab = a.rope ? a.rope_cos : nullptr;
+  p.sin_tab = a.rope ? a.rope_sin : nullptr;
+  p.dq_acc[0] = acc_s; p.dq_acc[1] = acc_c;
+  p.dk[0] = static_cast<__nv_bfloat16*>(a.dk_s); p.dk[1] = static_cast<__nv_bfloat16*>(a.dk_c);
+  p.dv[0] = static_cast<__nv_bfloat16*>(a.dv_s); p.dv[1] = static_cast<__nv_bfloat16*>(a.dv_c);
+  p.H = a.H; p.T = a.T; p.TW = a.meta.TW; p.NT = a.meta.NT;
+  p.scale = a.scale; p.scale_log2 = a.scale * kLog2e;
+  p.status = a.dev_status;
+  dim3 grid((a.T + kBwdTile - 1) / kBwdTile, BH, 2);
+  attn_bwd_tc_kernel<D><<<grid, kBwdThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, p);
+  count_launches(1);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("attention backward launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
+  return MINTB_OK;
+}
+
+int launch_attn_bwd_tc(const AttnArgs& a) {
+  if ((a.T + kBwdTile - 1) / kBwdTile > kBwdMaxTiles) { set_error("mintb_attn_bwd: T = %d is too long", a.T); return MINTB_EUNSUPPORTED; }
+  char* ws = static_cast<char*>(a.workspace);
+  const void* q_s = a.q_s;
+  const void* k_s = a.k_s;
+  const size_t rows = size_t(a.B) * a.H * a.T;
+  if (a.rope) {
+    __nv_bfloat16* qr = reinterpret_cast<__nv_bfloat16*>(ws);
+    __nv_bfloat16* kr = reinterpret_cast<__nv_bfloat16*>(ws + bwd_rot_bytes(a.B, a.H, a.T, a.D));
+    launch_rope_rotate(a, qr, kr);
+    q_s = qr;
+    k_s = kr;
+    ws += 2 * bwd_rot_bytes(a.B, a.H, a.T, a.D);
+  }
+  float* delta = reinterpret_cast<float*>(ws);
+  ws += bwd_delta_bytes(a.B, a.H, a.T);
+  float* acc_s = reinterpret_cast<float*>(ws);
+  float* acc_c = reinterpret_cast<float*>(ws + bwd_acc_bytes(a.B, a.H, a.T, a.D));
+  cudaError_t e = cudaMemsetAsync(acc_s, 0, 2 * bwd_acc_bytes(a.B, a.H, a.T, a.D), a.stream);
+  if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
+  {
+    const size_t n = rows * (a.D / 8);
+    bwd_delta_kernel<<<unsigned((n + 255) / 256), 256, 0, a.stream>>>(static_cast<const __nv_bfloat16*>(a.out),
+                                                                     static_cast<const __nv_bfloat16*>(a.d_out), delta, rows, a.D);
+    count_launches(1);
+  }
+  int rc = MINTB_EUNSUPPORTED;
+  switch (a.D) {
+    case 16: rc = bwd_tc_t<16>(a, q_s, k_s, delta, acc_s, acc_c); break;
+    case 32: rc = bwd_tc_t<32>(a, q_s, k_s, delta, acc_s, acc_c); break;
+    case 64: rc = bwd_tc_t<64>(a, q_s, k_s, delta, acc_s, acc_c); break;
+    default: set_error("mintb_attn_bwd: unsupported head_dim %d", a.D);
+  }
+  if (rc != MINTB_OK) return rc;
+  {
+    const size_t n = rows * (a.D / 16);
+    bwd_dq_convert_kernel<<<unsigned((n + 255) / 256), 256, 0, a.stream>>>(
+        acc_s, acc_c, static_cast<__nv_bfloat16*>(a.dq_s), static_cast<__nv_bfloat16*>(a.dq_c),
+        a.rope ? a.rope_cos : nullptr, a.rope ? a.rope_sin : nullptr, rows, a.T, a.D, a.scale);
+    count_launches(1);
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("attention backward launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
+  return MINTB_OK;
+}
+
+}  // namespace mintb

@@ -34,9 +34,10 @@ def _assert_grads(got, want, dtype, names=("dq_s", "dk_s", "dv_s", "dq_c", "dk_c
         if dtype == torch.float32:
             torch.testing.assert_close(g, w, rtol=1e-4, atol=5e-6, msg=lambda m: f"{n}: {m}")
         else:
-            scale = w.abs().max().item() + 1e-6
+            scale = w.abs().max().item()
             err = (g - w).abs().max().item()
-            assert err <= BF16_GRAD_REL * scale, f"{n}: max err {err:.4g} vs scale {scale:.4g}"
+            # relative to the gradient's scale, with an absolute floor for gradients that are exactly zero
+            assert err <= BF16_GRAD_REL * scale + 1e-5, f"{n}: max err {err:.4g} vs scale {scale:.4g}"
 
 
 @pytest.mark.parametrize("force_simt", [True, False])
@@ -164,8 +165,12 @@ def test_mask_metadata_bits_are_exact():
     meta = M.mask_meta_from_chain_ids(cid.to(DEV), pad.to(DEV))
     mask = O.chain_mask_from_ids(cid)
     meta2 = M.mask_meta_from_mask(mask.to(DEV), pad.to(DEV))
-    assert torch.equal(meta.buf, meta2.buf)
     TW = ((T + 31) // 32 + 3) // 4 * 4
+    a256 = lambda x: (x + 255) // 256 * 256
+    nbits, nkpad, ncls = B * T * TW * 4, B * TW * 4, B * ((T + 63) // 64) ** 2
+    regions = [(0, nbits), (a256(nbits), nbits), (2 * a256(nbits), nkpad), (2 * a256(nbits) + a256(nkpad), ncls)]
+    for off, n in regions:                       # the gaps between the 256-byte aligned arrays are never written
+        assert torch.equal(meta.buf[off:off + n], meta2.buf[off:off + n])
     words = meta.buf[:B * T * TW * 4].view(torch.int32).view(B, T, TW).cpu()
     bits = ((words[..., None] >> torch.arange(32)) & 1).reshape(B, T, TW * 32)[:, :, :T].bool()
     assert torch.equal(bits, mask)
