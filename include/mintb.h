@@ -90,6 +90,26 @@ MINTB_API int mintb_attn_fwd(const void* q_self, const void* k_self, const void*
                    const float* rope_sin, void* out, float* lse, void* workspace, size_t workspace_bytes, int B,
                    int H, int T, int D, int dtype, unsigned flags, float scale, void* stream, int* dev_status);
 
+/* No-allocation forward.  It has no counterpart in the reference.  Some callers of this library cannot allocate device
+ * memory at the point where they call it: code that runs while a CUDA graph is being captured, real-time or
+ * fixed-memory-budget hosts that forbid cudaMalloc after start-up, and host languages whose bindings hand over
+ * pre-pinned buffers only.  For them this variant of mintb_attn_fwd (bf16 tensor-core path) keeps the scratch it needs
+ * with MINTB_FLAG_ROPE - the rotated copies of q_self and k_self - in an array of MINTB_STATIC_SCRATCH_BYTES inside the
+ * library image, so the caller passes inputs and outputs only and nothing is allocated or freed, here or in any
+ * library routine it calls.  Limits and rules:
+ *   - 2 * B*H*T*D * 2 bytes must fit the array (B*H*T*D <= 8 Mi elements with rope); larger calls return
+ *     MINTB_EWORKSPACE with a message and launch nothing.  Every GPU that loads the library holds the array until exit.
+ *   - The first call on each device looks the array's device address up (with that device current); make that first
+ *     call outside any stream capture.
+ *   - All calls on a device share the one array.  Nothing in it has to start at zero (each call rewrites what it
+ *     reads), but two calls that overlap on the GPU - different streams, or threads - race on it: serialise them.
+ */
+#define MINTB_STATIC_SCRATCH_BYTES (32u << 20)
+MINTB_API int mintb_attn_fwd_static(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
+                                    const void* k_cross, const void* v_cross, const void* meta, const float* rope_cos,
+                                    const float* rope_sin, void* out, float* lse, int B, int H, int T, int D, int dtype,
+                                    unsigned flags, float scale, void* stream, int* dev_status);
+
 /* Attention backward.  Replaces fused_multi_pathway_attention_bwd (kernels/multi_pathway_attention_bwd.py:15-59)
  * with what torch.autograd computes through modules.py:129-144: probabilities are recomputed from lse;
  * dq/dk of the self pathway are un-rotated and dq is multiplied by scale, so the six results are the

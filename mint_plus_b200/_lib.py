@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libmintb.so")
 OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA = 0, -1, -2, -3, -4
 F32, BF16 = 0, 1
 FLAG_ROPE, FLAG_SQRT_SOFTMAX, FLAG_FORCE_SIMT = 1, 2, 4
+STATIC_SCRATCH_BYTES = 32 << 20
 
 _P = c_void_p
 # name -> (restype, argtypes); mirrors include/mintb.h one to one
@@ -28,6 +29,8 @@ PROTOTYPES = {
     "mintb_attn_fwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_uint]),
     "mintb_attn_fwd": (c_int, [_P] * 6 + [_P, _P, _P, _P, _P, _P, c_size_t, c_int, c_int, c_int, c_int, c_int, c_uint,
                                c_float, _P, _P]),
+    "mintb_attn_fwd_static": (c_int, [_P] * 6 + [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_uint, c_float, _P,
+                                      _P]),
     "mintb_attn_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_uint]),
     "mintb_attn_bwd": (c_int, [_P] * 6 + [_P, _P, _P, _P, _P, _P] + [_P] * 6 + [_P, c_size_t, c_int, c_int, c_int, c_int,
                                c_int, c_uint, c_float, _P, _P]),

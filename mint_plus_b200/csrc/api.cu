@@ -157,6 +157,21 @@ static int fill_common(AttnArgs& a, const char* who, const void* q_s, const void
   return MINTB_OK;
 }
 
+}  // extern "C"
+
+namespace mintb {
+// The argument checks of mintb_attn_fwd for entry points defined in other files.
+int check_attn_args(AttnArgs& a, const char* who, const void* q_s, const void* k_s, const void* v_s, const void* q_c,
+                    const void* k_c, const void* v_c, const void* meta, const float* rope_cos, const float* rope_sin,
+                    void* workspace, size_t workspace_bytes, size_t need, int B, int H, int T, int D, int dtype,
+                    unsigned flags, float scale, void* stream, int* dev_status) {
+  return fill_common(a, who, q_s, k_s, v_s, q_c, k_c, v_c, meta, rope_cos, rope_sin, workspace, workspace_bytes, need, B,
+                     H, T, D, dtype, flags, scale, stream, dev_status);
+}
+}  // namespace mintb
+
+extern "C" {
+
 int mintb_attn_fwd(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
                    const void* k_cross, const void* v_cross, const void* meta, const float* rope_cos,
                    const float* rope_sin, void* out, float* lse, void* workspace, size_t workspace_bytes, int B,

@@ -10,6 +10,8 @@
 // A pure tile uses one buffer (alternating, so the next QK^T overlaps this tile's softmax); a mixed tile
 // puts the self logits in buffer 0 and the cross logits in buffer 1 and issues two P V products.
 // Every wait on an mbarrier is bounded; on expiry the role records a code in *dev_status and unwinds.
+#include <mutex>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -551,4 +553,70 @@ int launch_attn_fwd_tc(const AttnArgs& a) {
   return MINTB_EUNSUPPORTED;
 }
 
+// ------------------------------------------------------------------------------------------------ no-allocation forward
+// Scratch for mintb_attn_fwd_static: the rotated copies of Q_self and K_self that the forward pass with RoPE reads.
+// It is part of the loaded module, so every GPU that loads this library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_fwd_static_scratch[MINTB_STATIC_SCRATCH_BYTES];
+
+// `g_fwd_static_scratch` names the array for DEVICE code only.  Host code must ask the runtime for the array's address on
+// the device that is current; the answer differs per device and is cached here after the first call on each device.
+static int static_scratch_ptr(void** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void* ptrs[kMaxDevices] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error("mintb_attn_fwd_static: cudaGetDevice failed or device index %d is out of range", dev);
+    return MINTB_ECUDA;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_fwd_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("mintb_attn_fwd_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return MINTB_ECUDA;
+    }
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return MINTB_OK;
+}
+
 }  // namespace mintb
+
+extern "C" int mintb_attn_fwd_static(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
+                                     const void* k_cross, const void* v_cross, const void* meta, const float* rope_cos,
+                                     const float* rope_sin, void* out, float* lse, int B, int H, int T, int D, int dtype,
+                                     unsigned flags, float scale, void* stream, int* dev_status) {
+  using namespace mintb;
+  if (dtype != MINTB_BF16 || (flags & MINTB_FLAG_FORCE_SIMT)) {
+    set_error("mintb_attn_fwd_static: only the bf16 tensor-core forward has a no-allocation variant");
+    return MINTB_EUNSUPPORTED;
+  }
+  AttnArgs a{};
+  // the shared argument checks first (no workspace is passed in, so none is checked there)
+  int rc = check_attn_args(a, "mintb_attn_fwd_static", q_self, k_self, v_self, q_cross, k_cross, v_cross, meta, rope_cos,
+                           rope_sin, nullptr, 0, 0, B, H, T, D, dtype, flags, scale, stream, dev_status);
+  if (rc != MINTB_OK) return rc;
+  if (out == nullptr || lse == nullptr || (reinterpret_cast<uintptr_t>(out) & 15) != 0) {
+    set_error("mintb_attn_fwd_static: out (16-byte aligned) and lse are required");
+    return MINTB_EINVAL;
+  }
+  const size_t need = tc_fwd_workspace_bytes(B, H, T, D, a.rope);
+  if (need > size_t(MINTB_STATIC_SCRATCH_BYTES)) {
+    set_error("mintb_attn_fwd_static: B*H*T*D = %zu needs %zu bytes of scratch, the built-in array holds %zu; "
+              "use mintb_attn_fwd with a caller-provided workspace",
+              size_t(B) * H * T * D, need, size_t(MINTB_STATIC_SCRATCH_BYTES));
+    return MINTB_EWORKSPACE;
+  }
+  void* scratch = nullptr;
+  rc = static_scratch_ptr(&scratch);
+  if (rc != MINTB_OK) return rc;
+  a.out = out;
+  a.lse = lse;
+  a.workspace = scratch;   // every byte the kernels read from it is written by the rotation pass of this same call
+  a.workspace_bytes = size_t(MINTB_STATIC_SCRATCH_BYTES);
+  return launch_attn_fwd_tc(a);
+}

@@ -80,6 +80,12 @@ struct AttnArgs {
 void set_error(const char* fmt, ...);
 void count_launches(int n);  // process-wide tally of kernels launched by this library
 
+// api.cu
+int check_attn_args(AttnArgs& a, const char* who, const void* q_s, const void* k_s, const void* v_s, const void* q_c,
+                    const void* k_c, const void* v_c, const void* meta, const float* rope_cos, const float* rope_sin,
+                    void* workspace, size_t workspace_bytes, size_t need, int B, int H, int T, int D, int dtype,
+                    unsigned flags, float scale, void* stream, int* dev_status);
+
 // prep.cu
 cudaError_t launch_meta_from_chain_ids(const int32_t* chain_ids, const uint8_t* key_pad, void* meta, int B, int T,
                                        cudaStream_t s);
