@@ -1,14 +1,15 @@
 // tcgen05 kernels of the combined-softmax multimer attention (bf16 in, fp32 accumulate), forward pass.
 //
-// One CTA owns a tile of 128 query rows of one (batch, head) and walks the key tiles of 64.  Warp roles:
-//   warp 0     TMA producer: Q tiles once, then per key tile only the K/V tiles its class needs
+// One CTA owns a tile of 128 query rows of one (batch, head) and walks a list of key runs ("entries") that share a class:
+// pure entries (one pathway) of up to 128 keys (64 at head_dim 64), mixed entries of 64 (32) keys.  Warp roles:
+//   warp 0     TMA producer: Q tiles once, then per entry only the K/V tiles its class needs
 //              (intra-only: K_self,V_self; inter-only: K_cross,V_cross; mixed: all four)
-//   warp 1     tcgen05.mma issuer: S = Q K^T into a TMEM buffer, then O += P V with P read from TMEM
-//   warps 2-5  softmax: one thread per query row (TMEM lane), online softmax over the combined logits,
-//              P written back into the S buffer as packed bf16, lazy rescale of O, epilogue
-// TMEM (256 columns, two CTAs per SM): O [0,64), S/P buffer 0 [64,128), buffer 1 [128,192).
-// A pure tile uses one buffer (alternating, so the next QK^T overlaps this tile's softmax); a mixed tile
-// puts the self logits in buffer 0 and the cross logits in buffer 1 and issues two P V products.
+//   warp 1     tcgen05.mma issuer: S = Q K^T into TMEM, then O += P V with P read from TMEM
+//   warps 2-9  softmax: two threads per query row (TMEM lane), each with its own online-softmax state over one half of
+//              the entry's keys and its own O accumulator; lazy rescale of O; the halves are merged in the epilogue
+// TMEM (256 columns, two CTAs per SM): S (logits, fp32), P (probabilities, packed bf16), O half 0, O half 1.
+// S is released as soon as the softmax threads have read it, so the next Q K^T overlaps this entry's exponentials;
+// a mixed entry holds the self logits in the low half of S and the cross logits in the high half.
 // Every wait on an mbarrier is bounded; on expiry the role records a code in *dev_status and unwinds.
 #include <mutex>
 
@@ -19,12 +20,23 @@ namespace mintb {
 
 using namespace ptx;
 
+// Optional per-warp timeline of one CTA (debug builds with -DMINTB_TRACE only; compiled out otherwise).
+#ifdef MINTB_TRACE
+__device__ unsigned long long g_trace[32 * 512];
+#define MINTB_TRACE_DECL int tr_n = 0; const bool tr_on = (blockIdx.x == 3 && blockIdx.y == 7 && (threadIdx.x % 32) == 0);
+#define MINTB_TRACE_EV(code) do { if (tr_on && tr_n < 510) g_trace[(threadIdx.x / 32) * 512 + (++tr_n)] = ((unsigned long long)clock64() << 8) | (unsigned)(code); } while (0)
+#define MINTB_TRACE_END do { if (tr_on) g_trace[(threadIdx.x / 32) * 512] = tr_n; } while (0)
+#else
+#define MINTB_TRACE_DECL
+#define MINTB_TRACE_EV(code)
+#define MINTB_TRACE_END
+#endif
+
 constexpr int kBM = 128;          // query rows per CTA
-constexpr int kBN = 64;           // keys per tile
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;   // producer warp, MMA warp, 8 softmax warps
 constexpr int kTmemCols = 256;
-constexpr int kColO = 0, kColS0 = 64, kColS1 = 128;
-constexpr int kMaxKeyTiles = 512;  // T <= 32768
+constexpr int kMaxKeyTiles = 512;  // entries per query tile (T <= 16384)
+constexpr unsigned kStaggerNs = 350;       // initial offset between the two softmax groups of a CTA
 constexpr float kRescaleThreshold = 8.f;  // log2 units: P stays below 2^8 between rescales
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -63,6 +75,29 @@ __device__ __forceinline__ float ex2(float x) {
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// Packed fp32x2 arithmetic (two lanes per instruction on the FMA pipe) and the three-input maximum.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
 
@@ -106,13 +141,24 @@ __global__ void __launch_bounds__(256) rope_rotate_kernel(const __nv_bfloat16* _
 }
 
 // ------------------------------------------------------------------------------------------------ forward
+// Work list of one CTA: runs of keys ("entries") that share a class.  A pure entry (one pathway) covers kN keys when two
+// adjacent 64-key tiles of the same pathway can be merged, else kN/2... see build below; a mixed entry covers kBox keys and
+// holds the self logits in S columns [0, kBox) and the cross logits in [kBox, 2 kBox).
 template <int D>
 struct FwdCfg {
-  static constexpr int kStages = D == 64 ? 2 : 3;
+  static constexpr int kN = D == 64 ? 64 : 128;    // most keys per entry (S columns)
+  static constexpr int kBox = kN / 2;              // keys per TMA box; keys of a mixed entry
+  static constexpr int kStages = 4;
   static constexpr int kRowBytes = 2 * D;
   static constexpr int kQBytes = kBM * kRowBytes;
-  static constexpr int kKvBytes = kBN * kRowBytes;
-  static constexpr size_t kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + size_t(kStages) * 4 * kKvBytes + 1024 /*barriers, tile classes*/;
+  static constexpr int kBoxBytes = kBox * kRowBytes;
+  // A stage holds [K | V] of a pure entry (kN rows each) or [K_self, K_cross | V_self, V_cross] of a mixed one (kBox rows each)
+  static constexpr int kSlotBytes = kN * kRowBytes;
+  static constexpr int kStageBytes = 2 * kSlotBytes;
+  static constexpr int kColS = 0, kColP = kN;                // S: kN fp32 columns; P: kN/2 columns of packed bf16
+  static constexpr int kColO = D == 64 ? 128 : 192;          // O of key-half 0, then O of key-half 1
+  static constexpr int kOStride = D == 64 ? 64 : 32;
+  static constexpr size_t kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + size_t(kStages) * kStageBytes + 6144 /*tail*/;
 };
 
 struct FwdParams {
@@ -125,32 +171,88 @@ struct FwdParams {
   int* status;
 };
 
+// entry flags (low three bits are the class bits kHasIntra | kHasInter | kHasPad)
+constexpr uint8_t kEntryFull = 8;   // covers kN keys (else kBox)
+
+// One chunk of W (32 or 16) logits of one query row: mask, running max, lazy rescale, exp2, row sum, packed bf16 out.
+// `s` holds the selected logits on entry.  Returns the packed probabilities in `pk` (W / 2 words).
+template <int W>
+__device__ __forceinline__ void softmax_chunk(float (&s)[W], uint32_t pad_bits, bool has_pad, float c2, uint64_t c22,
+                                              float& m_ref, float& l, float& alpha_out, bool& rescale_out,
+                                              uint32_t (&pk)[W / 2]) {
+  if (has_pad) {
+#pragma unroll
+    for (int j = 0; j < W; ++j)
+      if ((pad_bits >> j) & 1u) s[j] = -INFINITY;
+  }
+  float m0 = fmaxf(s[0], s[1]), m1 = fmaxf(s[2], s[3]), m2 = fmaxf(s[4], s[5]), m3 = fmaxf(s[6], s[7]);
+#pragma unroll
+  for (int j = 8; j < W; j += 8) {
+    m0 = fmax3(m0, s[j], s[j + 1]); m1 = fmax3(m1, s[j + 2], s[j + 3]);
+    m2 = fmax3(m2, s[j + 4], s[j + 5]); m3 = fmax3(m3, s[j + 6], s[j + 7]);
+  }
+  const float m_tile = fmaxf(fmax3(m0, m1, m2), m3) * c2;   // c2 > 0; -inf if every key of the chunk is padded
+  alpha_out = 1.f;
+  rescale_out = false;
+  if (m_tile > m_ref + kRescaleThreshold) {   // also the first finite maximum (m_ref = -inf)
+    alpha_out = ex2(m_ref - m_tile);           // 0 when nothing has been accumulated yet
+    m_ref = m_tile;
+    l *= alpha_out;
+    rescale_out = true;
+  }
+  // exp2(s c - m_ref); while every key seen so far is padded (m_ref = -inf) use 0 as reference: exp2(-inf) = 0
+  const float nm = m_ref == -INFINITY ? 0.f : -m_ref;
+  const uint64_t nm2 = pack2(nm, nm);
+  uint64_t la = pack2(0.f, 0.f), lb = la;
+#pragma unroll
+  for (int j = 0; j < W / 2; j += 2) {
+    float p0, p1, p2, p3;
+    unpack2(ffma2(pack2(s[2 * j], s[2 * j + 1]), c22, nm2), p0, p1);
+    unpack2(ffma2(pack2(s[2 * j + 2], s[2 * j + 3]), c22, nm2), p2, p3);
+    p0 = ex2(p0); p1 = ex2(p1); p2 = ex2(p2); p3 = ex2(p3);
+    la = fadd2(la, pack2(p0, p1));
+    lb = fadd2(lb, pack2(p2, p3));
+    pk[j] = pack_bf16(p0, p1);
+    pk[j + 1] = pack_bf16(p2, p3);
+  }
+  float l0, l1;
+  unpack2(fadd2(la, lb), l0, l1);
+  l += l0 + l1;
+}
+
 template <int D>
 __global__ void __launch_bounds__(kTcThreads, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_constant__ CUtensorMap map_ks,
                    const __grid_constant__ CUtensorMap map_vs, const __grid_constant__ CUtensorMap map_qc,
                    const __grid_constant__ CUtensorMap map_kc, const __grid_constant__ CUtensorMap map_vc, FwdParams p) {
   using Cfg = FwdCfg<D>;
-  constexpr int kStages = Cfg::kStages, RB = Cfg::kRowBytes;
+  constexpr int kStages = Cfg::kStages, RB = Cfg::kRowBytes, kN = Cfg::kN, kBox = Cfg::kBox;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQs = smem;
   unsigned char* sQc = smem + Cfg::kQBytes;
-  unsigned char* sKV = smem + 2 * Cfg::kQBytes;  // [stage][slot: 0 K_self, 1 K_cross, 2 V_self, 3 V_cross]
-  unsigned char* tail = sKV + size_t(kStages) * 4 * Cfg::kKvBytes;
+  unsigned char* sKV = smem + 2 * Cfg::kQBytes;  // [stage][K slot | V slot]
+  unsigned char* tail = sKV + size_t(kStages) * Cfg::kStageBytes;
   uint64_t* bar_q = reinterpret_cast<uint64_t*>(tail);
-  uint64_t* kv_full = bar_q + 1;
-  uint64_t* kv_empty = kv_full + kStages;
-  uint64_t* s_full = kv_empty + kStages;  // [2]
-  uint64_t* p_full = s_full + 2;          // [2]
-  uint64_t* o_ready = p_full + 2;
+  uint64_t* kv_full = bar_q + 1;          // [kStages]
+  uint64_t* kv_empty = kv_full + kStages; // [kStages]
+  uint64_t* s_full = kv_empty + kStages;  // MMA -> softmax: logits of the entry are in TMEM
+  uint64_t* s_free = s_full + 1;          // softmax -> MMA: every thread has read its logits (256 arrivals)
+  uint64_t* p_full = s_free + 1;          // softmax -> MMA: probabilities are in TMEM (256 arrivals)
+  uint64_t* o_ready = p_full + 1;         // MMA -> softmax: P V of the entry has completed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
-  uint8_t* tcls = reinterpret_cast<uint8_t*>(tmem_slot + 2);  // class per key tile, 0 = skip
+  int* n_entries_s = reinterpret_cast<int*>(tmem_slot + 1);
+  float* hstat = reinterpret_cast<float*>(tmem_slot + 2);          // [2][128] running maxima, [2][128] row sums
+  uint16_t* ent_k = reinterpret_cast<uint16_t*>(hstat + 512);      // first key of the entry / 32
+  uint8_t* ent_c = reinterpret_cast<uint8_t*>(ent_k + kMaxKeyTiles);
+  uint8_t* tcls = ent_c + kMaxKeyTiles;                            // class per 64-key tile, 0 = skip
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int qt = blockIdx.x, bh = blockIdx.y, b = bh / p.H;
   const int q0 = qt * kBM;
   const int nkt = p.NT;  // key tiles of 64 == class-table columns
+  MINTB_TRACE_DECL
+  MINTB_TRACE_EV(1);
 
   // tile classes of this query tile: OR of its two 64-row halves
   for (int kt = tid; kt < nkt; kt += kTcThreads) {
@@ -162,16 +264,49 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   if (tid == 0) {
     mbar_init(bar_q, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
-    mbar_init(&p_full[0], 128); mbar_init(&p_full[1], 128);
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 256);
+    mbar_init(p_full, 256);
     mbar_init(o_ready, 1);
     fence_mbar_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+  __syncthreads();
+  if (tid == 32 * 2) {   // one thread turns the class row into the entry list
+    int n = 0;
+    for (int kt = 0; kt < nkt; ++kt) {
+      const uint8_t c = tcls[kt];
+      if (c == 0) continue;
+      const bool mixed = (c & 3) == 3;
+      if constexpr (kN == 128) {
+        if (!mixed && kt + 1 < nkt && tcls[kt + 1] != 0 && (tcls[kt + 1] & 3) == (c & 3)) {
+          ent_k[n] = uint16_t(2 * kt);
+          ent_c[n++] = uint8_t(c | tcls[kt + 1] | kEntryFull);
+          ++kt;
+        } else {
+          ent_k[n] = uint16_t(2 * kt);
+          ent_c[n++] = c;
+        }
+      } else {
+        if (!mixed) {
+          ent_k[n] = uint16_t(2 * kt);
+          ent_c[n++] = uint8_t(c | kEntryFull);
+        } else {   // two 32-key entries
+          ent_k[n] = uint16_t(2 * kt);
+          ent_c[n++] = c;
+          ent_k[n] = uint16_t(2 * kt + 1);
+          ent_c[n++] = c;
+        }
+      }
+    }
+    *n_entries_s = n;
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = *tmem_slot;
+  const int n_ent = *n_entries_s;
+  MINTB_TRACE_EV(2);
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -182,307 +317,340 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       mbar_expect_tx(bar_q, 2 * Cfg::kQBytes);
       tma_load_3d(sQs, &map_qs, bar_q, 0, q0, bh);
       tma_load_3d(sQc, &map_qc, bar_q, 0, q0, bh);
-      int it = 0;
-      for (int kt = 0; kt < nkt; ++kt) {
-        const uint8_t c = tcls[kt];
-        if (c == 0) continue;
+      for (int it = 0; it < n_ent; ++it) {
         const int stage = it % kStages;
         if (!mbar_wait(&kv_empty[stage], ((it / kStages) & 1) ^ 1, p.status, 0x101)) break;
-        unsigned char* slot = sKV + size_t(stage) * 4 * Cfg::kKvBytes;
-        const int n = ((c & kHasIntra) ? 2 : 0) + ((c & kHasInter) ? 2 : 0);
-        mbar_expect_tx(&kv_full[stage], n * Cfg::kKvBytes);
-        if (c & kHasIntra) {
-          tma_load_3d(slot + 0 * Cfg::kKvBytes, &map_ks, &kv_full[stage], 0, kt * kBN, bh);
-          tma_load_3d(slot + 2 * Cfg::kKvBytes, &map_vs, &kv_full[stage], 0, kt * kBN, bh);
+        MINTB_TRACE_EV(10);
+        const uint8_t c = ent_c[it];
+        const int k0 = int(ent_k[it]) * 32;
+        unsigned char* kslot = sKV + size_t(stage) * Cfg::kStageBytes;
+        unsigned char* vslot = kslot + Cfg::kSlotBytes;
+        if ((c & 3) == 3) {   // mixed: one box of each of the four tensors
+          mbar_expect_tx(&kv_full[stage], 4 * Cfg::kBoxBytes);
+          tma_load_3d(kslot, &map_ks, &kv_full[stage], 0, k0, bh);
+          tma_load_3d(kslot + Cfg::kBoxBytes, &map_kc, &kv_full[stage], 0, k0, bh);
+          tma_load_3d(vslot, &map_vs, &kv_full[stage], 0, k0, bh);
+          tma_load_3d(vslot + Cfg::kBoxBytes, &map_vc, &kv_full[stage], 0, k0, bh);
+        } else {
+          const CUtensorMap* mk = (c & kHasIntra) ? &map_ks : &map_kc;
+          const CUtensorMap* mv = (c & kHasIntra) ? &map_vs : &map_vc;
+          const int boxes = (c & kEntryFull) ? 2 : 1;
+          mbar_expect_tx(&kv_full[stage], 2 * boxes * Cfg::kBoxBytes);
+          for (int bx = 0; bx < boxes; ++bx) {
+            tma_load_3d(kslot + bx * Cfg::kBoxBytes, mk, &kv_full[stage], 0, k0 + bx * kBox, bh);
+            tma_load_3d(vslot + bx * Cfg::kBoxBytes, mv, &kv_full[stage], 0, k0 + bx * kBox, bh);
+          }
         }
-        if (c & kHasInter) {
-          tma_load_3d(slot + 1 * Cfg::kKvBytes, &map_kc, &kv_full[stage], 0, kt * kBN, bh);
-          tma_load_3d(slot + 3 * Cfg::kKvBytes, &map_vc, &kv_full[stage], 0, kt * kBN, bh);
-        }
-        ++it;
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = idesc_bf16(kBM, kBN, false, false);
+    // One thread issues everything and its instruction count per entry is on the critical path: descriptors are kept as
+    // (constant high word, running low word).  Order per entry: as soon as the softmax threads have READ S(it) the next
+    // Q K^T is issued into the same columns (P lives elsewhere), then P V (it) once the probabilities have arrived.
+    if (lane == 0 && n_ent > 0) {
+      constexpr uint32_t idesc_qk_full = idesc_bf16(kBM, kN, false, false);
+      constexpr uint32_t idesc_qk_half = idesc_bf16(kBM, kBox, false, false);
       constexpr uint32_t idesc_pv = idesc_bf16(kBM, D, false, true);
-      const uint32_t qs_addr = smem_u32(sQs), qc_addr = smem_u32(sQc), kv_addr = smem_u32(sKV);
-      const uint32_t col_s[2] = {tbase + kColS0, tbase + kColS1};
+      constexpr uint32_t kHi = desc_hi32(8 * RB, swizzle_for_row_bytes(RB));      // K-major and MN-major tiles alike
+      constexpr uint32_t kLboK = desc_lbo32(16), kLboV = desc_lbo32(8 * RB);
+      constexpr uint32_t kSlot = Cfg::kSlotBytes >> 4, kBoxU = Cfg::kBoxBytes >> 4, kStageUnits = Cfg::kStageBytes >> 4;
+      constexpr uint32_t kVStep = (16 * RB) >> 4;
+      const uint32_t lo_qs = desc_addr32(smem_u32(sQs)) + kLboK, lo_qc = desc_addr32(smem_u32(sQc)) + kLboK;
+      const uint32_t lo_kv = desc_addr32(smem_u32(sKV));
+      const uint32_t col_s = tbase + Cfg::kColS, col_p = tbase + Cfg::kColP, col_o = tbase + Cfg::kColO;
       bool ok = mbar_wait(bar_q, 0, p.status, 0x201);
       tc_fence_after();
 
-      // issue S = Q K^T of active tile `it` (class c); the stage must be full
-      auto issue_qk = [&](int it, uint8_t c) -> bool {
-        const int stage = it % kStages;
+      auto issue_qk = [&](int it) -> bool {
+        const uint32_t stage = uint32_t(it % kStages);
         if (!mbar_wait(&kv_full[stage], (it / kStages) & 1, p.status, 0x202)) return false;
+        MINTB_TRACE_EV(20);
         tc_fence_after();
-        const uint32_t slot = kv_addr + uint32_t(stage) * 4 * Cfg::kKvBytes;
-        const bool mixed = (c & 3) == 3;
-        if (mixed || (c & kHasIntra)) {
-          const int buf = mixed ? 0 : (it & 1);
+        const uint8_t c = ent_c[it];
+        const uint32_t slot = lo_kv + stage * kStageUnits + kLboK;
+        if ((c & 3) == 3) {   // mixed: self logits in columns [0, kBox), cross logits in [kBox, 2 kBox)
 #pragma unroll
           for (int k = 0; k < D / 16; ++k)
-            umma_ss(col_s[buf], desc_k_major(qs_addr + k * 32, RB), desc_k_major(slot + 0 * Cfg::kKvBytes + k * 32, RB), idesc_qk, k > 0);
-          umma_commit(&s_full[buf]);
-        }
-        if (mixed || (c & kHasInter)) {
-          const int buf = mixed ? 1 : (it & 1);
+            umma_ss(col_s, make_desc(kHi, lo_qs + 2 * k), make_desc(kHi, slot + 2 * k), idesc_qk_half, k > 0);
 #pragma unroll
           for (int k = 0; k < D / 16; ++k)
-            umma_ss(col_s[buf], desc_k_major(qc_addr + k * 32, RB), desc_k_major(slot + 1 * Cfg::kKvBytes + k * 32, RB), idesc_qk, k > 0);
-          umma_commit(&s_full[buf]);
+            umma_ss(col_s + kBox, make_desc(kHi, lo_qc + 2 * k), make_desc(kHi, slot + kBoxU + 2 * k), idesc_qk_half, k > 0);
+        } else {
+          const uint32_t a_lo = (c & kHasIntra) ? lo_qs : lo_qc;
+          const uint32_t idesc = (c & kEntryFull) ? idesc_qk_full : idesc_qk_half;
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) umma_ss(col_s, make_desc(kHi, a_lo + 2 * k), make_desc(kHi, slot + 2 * k), idesc, k > 0);
         }
+        umma_commit(s_full);
         return true;
       };
 
-      // next active tile after kt (or nkt)
-      auto next_active = [&](int kt) { while (kt < nkt && tcls[kt] == 0) ++kt; return kt; };
-      int kt = next_active(0);
-      int it = 0;
-      uint32_t p_uses[2] = {0, 0};
-      bool qk_issued = false;  // S of tile `it` already issued
-      while (ok && kt < nkt) {
-        const uint8_t c = tcls[kt];
-        const bool mixed = (c & 3) == 3;
-        if (!qk_issued) ok = issue_qk(it, c);
+      if (ok) ok = issue_qk(0);
+      for (int it = 0; it < n_ent && ok; ++it) {
+        if (it + 1 < n_ent) {
+          ok = mbar_wait(s_free, it & 1, p.status, 0x205);   // S(it) has been read: its columns may be overwritten
+          if (!ok) break;
+          tc_fence_after();
+          ok = issue_qk(it + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(p_full, it & 1, p.status, 0x203);
         if (!ok) break;
-        const int kt_next = next_active(kt + 1);
-        const uint8_t c_next = kt_next < nkt ? tcls[kt_next] : 0;
-        const bool next_mixed = (c_next & 3) == 3;
-        qk_issued = false;
-        if (c_next != 0 && !mixed && !next_mixed) {  // other buffer is free: overlap next QK^T with this softmax
-          ok = issue_qk(it + 1, c_next);
-          qk_issued = true;
-          if (!ok) break;
-        }
-        // O += P V
-        const int stage = it % kStages;
-        const uint32_t slot = kv_addr + uint32_t(stage) * 4 * Cfg::kKvBytes;
-        bool acc = it > 0;
-        if (mixed || (c & kHasIntra)) {
-          const int buf = mixed ? 0 : (it & 1);
-          ok = mbar_wait(&p_full[buf], p_uses[buf] & 1, p.status, 0x203);
-          if (!ok) break;
-          ++p_uses[buf];
-          tc_fence_after();
+        MINTB_TRACE_EV(21);
+        tc_fence_after();
+        const uint8_t c = ent_c[it];
+        const uint32_t v_lo = lo_kv + uint32_t(it % kStages) * kStageUnits + kSlot + kLboV;
+        const bool acc = it > 0;
+        if ((c & 3) == 3) {
+          // keys [0, kBox/2) of the entry belong to softmax half 0 (O half 0), the rest to half 1
 #pragma unroll
-          for (int k = 0; k < kBN / 16; ++k) {
-            umma_ts(tbase + kColO, col_s[buf] + k * 8, desc_mn_major(slot + 2 * Cfg::kKvBytes + k * 16 * RB, RB, 8 * RB), idesc_pv, acc);
-            acc = true;
+          for (int k = 0; k < kBox / 16; ++k)
+            umma_ts(col_o + (k >= kBox / 32 ? Cfg::kOStride : 0), col_p + k * 8, make_desc(kHi, v_lo + k * kVStep), idesc_pv,
+                    acc || (k % (kBox / 32)) != 0);
+#pragma unroll
+          for (int k = 0; k < kBox / 16; ++k)
+            umma_ts(col_o + (k >= kBox / 32 ? Cfg::kOStride : 0), col_p + kBox / 2 + k * 8,
+                    make_desc(kHi, v_lo + kBoxU + k * kVStep), idesc_pv, true);
+        } else {
+          const uint32_t vv = v_lo;
+          if (c & kEntryFull) {
+#pragma unroll
+            for (int k = 0; k < kN / 16; ++k)
+              umma_ts(col_o + (k >= kN / 32 ? Cfg::kOStride : 0), col_p + k * 8, make_desc(kHi, vv + k * kVStep), idesc_pv,
+                      acc || (k % (kN / 32)) != 0);
+          } else {
+#pragma unroll
+            for (int k = 0; k < kBox / 16; ++k)
+              umma_ts(col_o + (k >= kBox / 32 ? Cfg::kOStride : 0), col_p + k * 8, make_desc(kHi, vv + k * kVStep), idesc_pv,
+                      acc || (k % (kBox / 32)) != 0);
           }
         }
-        if (mixed || (c & kHasInter)) {
-          const int buf = mixed ? 1 : (it & 1);
-          ok = mbar_wait(&p_full[buf], p_uses[buf] & 1, p.status, 0x204);
-          if (!ok) break;
-          ++p_uses[buf];
-          tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < kBN / 16; ++k) {
-            umma_ts(tbase + kColO, col_s[buf] + k * 8, desc_mn_major(slot + 3 * Cfg::kKvBytes + k * 16 * RB, RB, 8 * RB), idesc_pv, acc);
-            acc = true;
-          }
-        }
-        umma_commit(&kv_empty[stage]);
         umma_commit(o_ready);
-        kt = kt_next;
-        ++it;
+        umma_commit(&kv_empty[it % kStages]);
+        MINTB_TRACE_EV(22);
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax warps (one thread per query row)
+    // ---------------------------------------------------------------- softmax warps: two threads per query row
+    // Thread (row, ch) owns half ch of the keys of every entry of its row, with its OWN running maximum, row sum and O
+    // accumulator (the P V product of key-half ch lands in O half ch), so the two threads of a row never synchronise inside
+    // the loop; the two partial softmax states are merged once, in the epilogue.
+    const int sw = warp - 2;                      // 0..7
     const int quarter = warp % 4;                 // TMEM lane quarter this warp may access
+    const int ch = sw / 4;                        // key half
     const int row = quarter * 32 + lane;          // row within the query tile == TMEM lane
     const int qi = q0 + row;
     const int qrow = qi < p.T ? qi : p.T - 1;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    const uint32_t tO = tbase + lane_base + kColO;
-    const uint32_t tS[2] = {tbase + lane_base + kColS0, tbase + lane_base + kColS1};
+    const uint32_t tO = tbase + lane_base + Cfg::kColO + Cfg::kOStride * ch;
+    const uint32_t tS = tbase + lane_base + Cfg::kColS;
+    const uint32_t tP = tbase + lane_base + Cfg::kColP;
     const uint32_t* mrow = p.bits + (size_t(b) * p.T + qrow) * p.TW;
     const uint32_t* prow = p.kpad + size_t(b) * p.TW;
     const float c2 = p.scale_log2;
+    const uint64_t c22 = pack2(c2, c2);
     float m_ref = -INFINITY, l = 0.f;
-    uint32_t s_uses[2] = {0, 0};
-    int it = 0;
     bool ok = true;
-    for (int kt = 0; kt < nkt && ok; ++kt) {
-      const uint8_t c = tcls[kt];
-      if (c == 0) continue;
-      const bool mixed = (c & 3) == 3;
-      float s[kBN];
-      if (!mixed) {
-        const int buf = it & 1;
-        ok = mbar_wait(&s_full[buf], s_uses[buf] & 1, p.status, 0x301);
-        if (!ok) break;
-        ++s_uses[buf];
-        tc_fence_after();
-        uint32_t r0[32], r1[32];
-        tmem_ld32(tS[buf], r0);
-        tmem_ld32(tS[buf] + 32, r1);
+
+    // rescale this thread's O accumulator by alpha (rare: the running maximum grew by more than the threshold)
+    auto rescale_o = [&](float alpha) {
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 16) {
+        uint32_t o[16];
+        tmem_ld16(tO + c0, o);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) { s[j] = __uint_as_float(r0[j]); s[32 + j] = __uint_as_float(r1[j]); }
-      } else {
-        ok = mbar_wait(&s_full[0], s_uses[0] & 1, p.status, 0x302) && mbar_wait(&s_full[1], s_uses[1] & 1, p.status, 0x303);
-        if (!ok) break;
-        ++s_uses[0]; ++s_uses[1];
-        tc_fence_after();
-        const uint2 cw = *reinterpret_cast<const uint2*>(mrow + 2 * kt);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t rs[32], rc[32];
-          tmem_ld32(tS[0] + 32 * half, rs);
-          tmem_ld32(tS[1] + 32 * half, rc);
-          tmem_ld_wait();
-          const uint32_t w = half == 0 ? cw.x : cw.y;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) s[32 * half + j] = __uint_as_float(((w >> j) & 1u) ? rc[j] : rs[j]);
-        }
+        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+        tmem_st16(tO + c0, o);
       }
-      if (c & kHasPad) {
-        const uint2 pw = *reinterpret_cast<const uint2*>(prow + 2 * kt);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          if ((pw.x >> j) & 1u) s[j] = -INFINITY;
-          if ((pw.y >> j) & 1u) s[32 + j] = -INFINITY;
-        }
-      }
-      float tmax = s[0];
-#pragma unroll
-      for (int j = 1; j < kBN; ++j) tmax = fmaxf(tmax, s[j]);
-      const float m_tile = tmax * c2;  // c2 > 0; -inf only if every key of the tile is padded for this row's mask
-      float alpha = 1.f;
-      bool rescale = false;
-      if (it == 0) {
-        m_ref = m_tile;
-      } else if (m_tile > m_ref + kRescaleThreshold) {
-        alpha = ex2(m_ref - m_tile);   // m_ref = -inf (nothing seen yet) gives 0
-        m_ref = m_tile;
-        l *= alpha;
-        rescale = true;
-      }
-      // Every phase of o_ready is observed, tile by tile (a parity wait cannot tell phases two apart):
-      // early when O has to be rescaled, otherwise just before P is handed over.
+    };
+
+    for (int it = 0; it < n_ent && ok; ++it) {
+      const uint8_t c = ent_c[it];
+      const int kw = int(ent_k[it]);              // first key of the entry / 32
+      const bool mixed = (c & 3) == 3;
+      const bool has_pad = (c & kHasPad) != 0;
+      ok = mbar_wait(s_full, it & 1, p.status, 0x301);
+      if (!ok) break;
+      if (it == 0 && ch == 1) __nanosleep(kStaggerNs);   // the two key halves run out of phase (see kStaggerNs)
+      MINTB_TRACE_EV(30);
+      tc_fence_after();
+      // Every phase of o_ready is observed, entry by entry (a parity wait cannot tell phases two apart): before O is
+      // rescaled or, at the latest, before P (single-buffered) is overwritten.
       bool o_seen = it == 0;
-      if (it > 0 && __any_sync(0xffffffffu, rescale)) {
-        ok = mbar_wait(o_ready, (it - 1) & 1, p.status, 0x304);
-        if (!ok) break;
+      auto see_o = [&]() -> bool {
+        if (o_seen) return true;
         o_seen = true;
+        if (!mbar_wait(o_ready, (it - 1) & 1, p.status, 0x304)) return false;
         tc_fence_after();
-        if constexpr (D >= 32) {
-#pragma unroll
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t o[32];
-            tmem_ld32(tO + c0, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-            tmem_st32(tO + c0, o);
-          }
-        } else {
-          uint32_t o[16];
-          tmem_ld16(tO, o);
+        return true;
+      };
+
+      if (!mixed && (c & kEntryFull) && kN == 128) {
+        // 128 keys: this thread's 64 logits in two chunks of 32
+        float alpha; bool resc;
+        uint32_t pk[16];
+        {
+          float s[32];
+          uint32_t r[32];
+          tmem_ld32(tS + 64 * ch, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-          tmem_st16(tO, o);
+          for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(r[j]);
+          softmax_chunk<32>(s, has_pad ? prow[kw + 2 * ch] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
         }
-      }
-      // A row that has seen only padded keys so far keeps m_ref = -inf; use 0 as the reference so exp2 gives 0, not NaN.
-      const float mr = m_ref == -INFINITY ? 0.f : m_ref;
-      float lsum = 0.f;
-      if (!mixed) {
-        uint32_t pk[32];
+        if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
+        uint32_t pk2[16];
+        {
+          float s[32];
+          uint32_t r[32];
+          tmem_ld32(tS + 64 * ch + 32, r);
+          tmem_ld_wait();
+          tc_fence_before();
+          mbar_arrive(s_free);                       // both chunks are in registers: S may be overwritten
+          MINTB_TRACE_EV(31);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float p0 = ex2(fmaf(s[2 * j], c2, -mr)), p1 = ex2(fmaf(s[2 * j + 1], c2, -mr));
-          lsum += p0 + p1;
-          pk[j] = pack_bf16(p0, p1);
+          for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(r[j]);
+          softmax_chunk<32>(s, has_pad ? prow[kw + 2 * ch + 1] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk2);
         }
-        tmem_st32(tS[it & 1], pk);
-      } else {
-        const uint2 cw = *reinterpret_cast<const uint2*>(mrow + 2 * kt);
-        uint32_t pi[32], pe[32];
+        // a rescale decided by the second chunk also applies to what the first chunk contributes: fold it into pk
+        if (__any_sync(0xffffffffu, resc)) {
+          if (it > 0) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
+          if (resc) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float p0 = ex2(fmaf(s[2 * j], c2, -mr)), p1 = ex2(fmaf(s[2 * j + 1], c2, -mr));
-          lsum += p0 + p1;
-          const uint32_t w = (2 * j) < 32 ? cw.x : cw.y;
-          const bool x0 = (w >> ((2 * j) & 31)) & 1u, x1 = (w >> ((2 * j + 1) & 31)) & 1u;
-          pi[j] = pack_bf16(x0 ? 0.f : p0, x1 ? 0.f : p1);
-          pe[j] = pack_bf16(x0 ? p0 : 0.f, x1 ? p1 : 0.f);
+            for (int j = 0; j < 16; ++j) {
+              const float a0 = __uint_as_float(pk[j] << 16) * alpha, a1 = __uint_as_float(pk[j] & 0xffff0000u) * alpha;
+              pk[j] = pack_bf16(a0, a1);
+            }
+          }
         }
-        tmem_st32(tS[0], pi);
-        tmem_st32(tS[1], pe);
-      }
-      l += lsum;
-      tmem_st_wait();
-      if (!o_seen) {
-        ok = mbar_wait(o_ready, (it - 1) & 1, p.status, 0x306);
+        MINTB_TRACE_EV(32);
+        ok = see_o();
         if (!ok) break;
-      }
-      tc_fence_before();
-      if (!mixed) {
-        mbar_arrive(&p_full[it & 1]);
+        tmem_st16(tP + 32 * ch, pk);
+        tmem_st16(tP + 32 * ch + 16, pk2);
+      } else if (!mixed) {
+        // kBox (D <= 32: 64) or kN (D = 64: 64) keys: 32 logits per thread;  D = 64 half entries do not occur for pure tiles
+        constexpr int W = 32;
+        float alpha; bool resc;
+        uint32_t pk[W / 2];
+        {
+          float s[W];
+          uint32_t r[W];
+          tmem_ld32(tS + W * ch, r);
+          tmem_ld_wait();
+          tc_fence_before();
+          mbar_arrive(s_free);
+          MINTB_TRACE_EV(31);
+#pragma unroll
+          for (int j = 0; j < W; ++j) s[j] = __uint_as_float(r[j]);
+          softmax_chunk<W>(s, has_pad ? prow[kw + ch] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
+        }
+        if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
+        MINTB_TRACE_EV(32);
+        ok = see_o();
+        if (!ok) break;
+        tmem_st16(tP + (W / 2) * ch, pk);
       } else {
-        mbar_arrive(&p_full[0]);
-        mbar_arrive(&p_full[1]);
+        // mixed entry of kBox keys: W = kBox / 2 logits per thread, selected between the self and cross logits
+        constexpr int W = kBox / 2;   // 32 (D <= 32) or 16 (D = 64)
+        float alpha; bool resc;
+        uint32_t pk[W / 2];
+        // mask and padding bits of this thread's W keys: key index of bit 0 is 32 kw + W ch
+        const int bit0 = W * ch;                       // offset inside the entry (entry starts on a 32-key boundary)
+        const uint32_t cw = (mrow[kw + bit0 / 32] >> (bit0 % 32)) & (W == 32 ? 0xffffffffu : 0xffffu);
+        const uint32_t pw = has_pad ? (prow[kw + bit0 / 32] >> (bit0 % 32)) : 0u;
+        {
+          float s[W];
+          uint32_t rs[W], rc[W];
+          tmem_ld_n<W>(tS + W * ch, rs);
+          tmem_ld_n<W>(tS + kBox + W * ch, rc);
+          tmem_ld_wait();
+          tc_fence_before();
+          mbar_arrive(s_free);
+          MINTB_TRACE_EV(31);
+#pragma unroll
+          for (int j = 0; j < W; ++j) s[j] = __uint_as_float(((cw >> j) & 1u) ? rc[j] : rs[j]);
+          softmax_chunk<W>(s, pw, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
+        }
+        if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
+        // split by pathway: P o ~M multiplies V_self, P o M multiplies V_cross
+        uint32_t pi[W / 2], pe[W / 2];
+#pragma unroll
+        for (int j = 0; j < W / 2; ++j) {
+          const uint32_t lo_x = (cw >> (2 * j)) & 1u, hi_x = (cw >> (2 * j + 1)) & 1u;
+          const uint32_t keep_e = (lo_x ? 0x0000ffffu : 0u) | (hi_x ? 0xffff0000u : 0u);
+          pe[j] = pk[j] & keep_e;
+          pi[j] = pk[j] & ~keep_e;
+        }
+        MINTB_TRACE_EV(32);
+        ok = see_o();
+        if (!ok) break;
+        tmem_st_n<W / 2>(tP + (W / 2) * ch, pi);
+        tmem_st_n<W / 2>(tP + kBox / 2 + (W / 2) * ch, pe);
       }
-      ++it;
+      tmem_st_wait();
+      MINTB_TRACE_EV(33);
+      tc_fence_before();
+      mbar_arrive(p_full);
+      MINTB_TRACE_EV(36);
     }
-    // ---- epilogue: O / l -> bf16, lse
-    if (ok && it > 0) ok = mbar_wait(o_ready, (it - 1) & 1, p.status, 0x305);
+    // ---- epilogue: merge the two softmax states of each row, O / l -> bf16, lse
+    float* hm = hstat;          // [2][128] running maxima
+    float* hl = hstat + 256;    // [2][128] row sums
+    hm[ch * 128 + row] = m_ref;
+    hl[ch * 128 + row] = l;
+    named_bar_sync(1, 256);
+    const float m_other = hm[(ch ^ 1) * 128 + row], l_other = hl[(ch ^ 1) * 128 + row];
+    if (ok && n_ent > 0) ok = mbar_wait(o_ready, (n_ent - 1) & 1, p.status, 0x305);
     tc_fence_after();
     if (ok) {
-      const float inv = 1.f / l;  // no unpadded key at all: l = 0 and the row becomes NaN, as in the PyTorch path
-      __nv_bfloat16* orow = p.out + (size_t(bh) * p.T + qi) * D;
-      if (it == 0) {
-        if (qi < p.T) {
+      constexpr int NC = D / 2;   // output columns written by this thread
+      __nv_bfloat16* orow = p.out + (size_t(bh) * p.T + qi) * D + ch * NC;
+      if (n_ent == 0) {
+        if (qi < p.T) {   // no unpadded key at all: NaN, as the softmax of an all -inf row gives in the PyTorch path
           const uint32_t nan2 = 0x7FC07FC0u;
 #pragma unroll
-          for (int d = 0; d < D; d += 8) *reinterpret_cast<uint4*>(orow + d) = make_uint4(nan2, nan2, nan2, nan2);
-          p.lse[size_t(bh) * p.T + qi] = -INFINITY;
+          for (int d = 0; d < NC; d += 8) *reinterpret_cast<uint4*>(orow + d) = make_uint4(nan2, nan2, nan2, nan2);
+          if (ch == 0) p.lse[size_t(bh) * p.T + qi] = -INFINITY;
         }
       } else {
-        if constexpr (D >= 32) {
+        const float m_all = fmaxf(m_ref, m_other);                 // finite: an active tile has an unpadded key
+        const float w_self = ex2(m_ref - m_all), w_other = ex2(m_other - m_all);   // exp2(-inf) = 0 for an empty half
+        const float l_all = l * w_self + l_other * w_other;
+        const float inv = 1.f / l_all;
+        const float f_self = w_self * inv, f_other = w_other * inv;
+        constexpr int CH = NC > 16 ? 16 : NC;   // columns per pass (keeps the register footprint small)
 #pragma unroll
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t o[32];
-            tmem_ld32(tO + c0, o);
-            tmem_ld_wait();
-            if (qi < p.T) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 v;
-                v.x = pack_bf16(__uint_as_float(o[j + 0]) * inv, __uint_as_float(o[j + 1]) * inv);
-                v.y = pack_bf16(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
-                v.z = pack_bf16(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
-                v.w = pack_bf16(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
-                *reinterpret_cast<uint4*>(orow + c0 + j) = v;
-              }
-            }
-          }
-        } else {
-          uint32_t o[16];
-          tmem_ld16(tO, o);
+        for (int c0 = 0; c0 < NC; c0 += CH) {
+          uint32_t oa[CH], ob[CH];
+          tmem_ld_n<CH>(tO + ch * NC + c0, oa);                                                              // own accumulator
+          tmem_ld_n<CH>(tbase + lane_base + Cfg::kColO + Cfg::kOStride * (ch ^ 1) + ch * NC + c0, ob);       // the other half's
           tmem_ld_wait();
           if (qi < p.T) {
+            float v[CH];
 #pragma unroll
-            for (int j = 0; j < 16; j += 8) {
-              uint4 v;
-              v.x = pack_bf16(__uint_as_float(o[j + 0]) * inv, __uint_as_float(o[j + 1]) * inv);
-              v.y = pack_bf16(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
-              v.z = pack_bf16(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
-              v.w = pack_bf16(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + j) = v;
+            for (int j = 0; j < CH; ++j) {
+              // an empty half holds whatever was in TMEM: its weight is exactly 0, but 0 * NaN must not leak
+              const float a = w_self > 0.f ? __uint_as_float(oa[j]) * f_self : 0.f;
+              const float bb = w_other > 0.f ? __uint_as_float(ob[j]) * f_other : 0.f;
+              v[j] = a + bb;
             }
+#pragma unroll
+            for (int j = 0; j < CH; j += 8)
+              *reinterpret_cast<uint4*>(orow + c0 + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                                                                    pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
           }
         }
-        if (qi < p.T) p.lse[size_t(bh) * p.T + qi] = (m_ref + log2f(l)) * kLn2;
+        if (qi < p.T) {
+          if (ch == 0) p.lse[size_t(bh) * p.T + qi] = (m_all + log2f(l_all)) * kLn2;
+        }
       }
     }
   }
+  MINTB_TRACE_EV(3);
+  MINTB_TRACE_END;
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -490,6 +658,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     tmem_dealloc(tbase, kTmemCols);
   }
 }
+
+#ifdef MINTB_TRACE
+extern "C" __attribute__((visibility("default"))) int mintb_trace_read(unsigned long long* dst) {
+  return int(cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace)));
+}
+#endif
 
 // ------------------------------------------------------------------------------------------------ host side
 bool tc_supported(int D, int dtype) { return dtype == MINTB_BF16 && (D == 16 || D == 32 || D == 64); }
@@ -503,9 +677,9 @@ static int fwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s) {
   using Cfg = FwdCfg<D>;
   const int BH = a.B * a.H;
   CUtensorMap mqs, mks, mvs, mqc, mkc, mvc;
-  if (!make_map(&mqs, q_s, D, a.T, BH, kBM) || !make_map(&mks, k_s, D, a.T, BH, kBN) ||
-      !make_map(&mvs, a.v_s, D, a.T, BH, kBN) || !make_map(&mqc, a.q_c, D, a.T, BH, kBM) ||
-      !make_map(&mkc, a.k_c, D, a.T, BH, kBN) || !make_map(&mvc, a.v_c, D, a.T, BH, kBN)) {
+  if (!make_map(&mqs, q_s, D, a.T, BH, kBM) || !make_map(&mks, k_s, D, a.T, BH, Cfg::kBox) ||
+      !make_map(&mvs, a.v_s, D, a.T, BH, Cfg::kBox) || !make_map(&mqc, a.q_c, D, a.T, BH, kBM) ||
+      !make_map(&mkc, a.k_c, D, a.T, BH, Cfg::kBox) || !make_map(&mvc, a.v_c, D, a.T, BH, Cfg::kBox)) {
     set_error("mintb_attn_fwd: cuTensorMapEncodeTiled failed");
     return MINTB_ECUDA;
   }
@@ -533,7 +707,7 @@ void launch_rope_rotate(const AttnArgs& a, __nv_bfloat16* qr, __nv_bfloat16* kr)
 }
 
 int launch_attn_fwd_tc(const AttnArgs& a) {
-  if (a.meta.NT > kMaxKeyTiles) { set_error("mintb_attn_fwd: T = %d exceeds %d", a.T, kMaxKeyTiles * kBN); return MINTB_EUNSUPPORTED; }
+  if (2 * a.meta.NT > kMaxKeyTiles) { set_error("mintb_attn_fwd: T = %d exceeds %d", a.T, kMaxKeyTiles * 32); return MINTB_EUNSUPPORTED; }
   const void* q_s = a.q_s;
   const void* k_s = a.k_s;
   if (a.rope) {

@@ -4,13 +4,13 @@
 // P o ~M and the cross pathway P o M, each computed from its own Q, K, V.  The grid is
 // (key tiles of 128, batch*head, pathway); a CTA owns dK and dV of its key tile in TMEM and walks the query
 // tiles of 128 whose class holds pairs of its pathway:
-//   S^T = K Q^T, dP^T = V dO^T            (lane = key, column = query; two halves of 64 queries)
+//   S^T = K Q^T, dP^T = V dO^T            (lane = key, column = query; two halves of 64 queries, one TMEM buffer each)
 //   P^T = exp2(S^T c - lse), masked       dS^T = P^T o (dP^T - delta)
 //   dV += P^T dO, dK += dS^T Q            (A operands read from TMEM, aliased over S^T / dP^T)
 //   dQ_tile = dS K                        (dS through shared memory), added to an fp32 accumulator in HBM
-// Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 compute half 0, warps 6-9 compute half 1.
-// The two compute groups ping-pong: while one works on its half the tensor pipe serves the other.
-// TMEM (512 columns): dK [0,64) dV [64,128) dQ x2 [128,256) S^T halves [256,384) dP^T halves [384,512).
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-17 compute (thread = key row x 16 query columns of the
+// half in flight).  The halves ping-pong: while one is computed the tensor pipe refills the other buffer.
+// TMEM (512 columns): dK [0,64) dV [64,128) dQ x2 [128,256) buffer 0 {S^T, dP^T} [256,384) buffer 1 [384,512).
 // dQ is accumulated across CTAs with fp32 atomics, so its low-order bits depend on arrival order;
 // dK and dV are reduced inside one CTA in a fixed order.  All mbarrier waits are bounded.
 #include "common.cuh"
@@ -22,11 +22,11 @@ using namespace ptx;
 
 constexpr int kBwdTile = 128;       // keys per CTA and queries per step
 constexpr int kHalf = 64;           // queries per compute group
-constexpr int kBwdThreads = 320;
+constexpr int kBwdThreads = 576;   // producer warp, MMA warp, 16 compute warps
 constexpr int kBwdStages = 2;
 constexpr int kBwdMaxTiles = 256;   // T <= 32768
 constexpr uint32_t kTmemAll = 512;
-constexpr int kColDK = 0, kColDV = 64, kColDQ = 128, kColS = 256, kColDP = 384;
+constexpr int kColDK = 0, kColDV = 64, kColDQ = 128, kColBuf = 256;   // buffer b: S^T at kColBuf + 128 b, dP^T 64 further
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -65,20 +65,47 @@ __device__ __forceinline__ uint32_t bwd_pack(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 __device__ __forceinline__ void named_barrier(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 // ------------------------------------------------------------------------------------------------ pre / post passes
-// delta[bh][i] = sum_d dO[i][d] * O[i][d]; one warp per 4 rows (8 lanes x 16 bytes cover D = 64).
-__global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                                                        float* __restrict__ delta, size_t rows, int D) {
+// Per-query statistics for the backward pass: stats[bh][i] = (-lse * log2 e, -delta), delta = sum_d dO[i][d] * O[i][d].
+// Rows are padded to a multiple of 128 per (batch, head); the pad entries are (-inf, 0), which makes exp2 give 0 there.
+__global__ void __launch_bounds__(256) bwd_stats_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                                        const float* __restrict__ lse, float2* __restrict__ stats, int BH, int T,
+                                                        int Tpad, int D) {
   const int lpr = D / 8;  // lanes per row
   const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  const size_t row = idx / lpr;
+  const size_t prow = idx / lpr;          // row in the padded layout
   const int c = int(idx % lpr);
+  const size_t bh = prow / Tpad;
+  const int t = int(prow % Tpad);
+  const bool live = bh < size_t(BH) && t < T;
   float acc = 0.f;
-  if (row < rows) {
+  if (live) {
+    const size_t row = bh * T + t;
     const uint4 a = *reinterpret_cast<const uint4*>(o + row * D + c * 8);
     const uint4 b = *reinterpret_cast<const uint4*>(d_o + row * D + c * 8);
     const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
@@ -91,7 +118,8 @@ __global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __r
     }
   }
   for (int off = lpr / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (row < rows && c == 0) delta[row] = acc;
+  if (bh < size_t(BH) && c == 0)
+    stats[prow] = live ? make_float2(-lse[bh * T + t] * kLog2e, -acc) : make_float2(-INFINITY, 0.f);
 }
 
 // dq = scale * R^T(acc) for the self pathway (with tables), scale * acc for the cross pathway; fp32 -> bf16.
@@ -147,28 +175,14 @@ struct BwdCfg {
 struct BwdParams {
   const uint32_t *bitsT, *kpad;
   const uint8_t* cls;
-  const float *lse, *delta;
+  const float2* stats;             // [B*H][Tpad] (-lse * log2 e, -delta), Tpad = T rounded up to 128
   const float *cos_tab, *sin_tab;  // null without rope
   float* dq_acc[2];                // fp32 [B*H][T][D] per pathway
   __nv_bfloat16 *dk[2], *dv[2];
-  int H, T, TW, NT;
+  int H, T, Tpad, TW, NT;
   float scale, scale_log2;
   int* status;
 };
-
-template <int NCOL>
-__device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t* r);
-template <>
-__device__ __forceinline__ void tmem_ld_n<32>(uint32_t taddr, uint32_t* r) { tmem_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(r)); }
-template <>
-__device__ __forceinline__ void tmem_ld_n<16>(uint32_t taddr, uint32_t* r) { tmem_ld16(taddr, *reinterpret_cast<uint32_t(*)[16]>(r)); }
-template <>
-__device__ __forceinline__ void tmem_ld_n<8>(uint32_t taddr, uint32_t* r) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr)
-               : "memory");
-}
 
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -185,9 +199,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   unsigned char* sQ = sV + Cfg::kTileBytes;                        // [stage][0: Q_i, 1: dO_i]
   unsigned char* sDS = sQ + size_t(kBwdStages) * 2 * Cfg::kTileBytes;  // [buf][half][128 rows x 128 B]
   unsigned char* tail = sDS + 2 * Cfg::kDsBytes;
-  float* s_nlse = reinterpret_cast<float*>(tail);                  // [2 groups][2 bufs][64]  (-lse * log2 e)
-  float* s_delta = s_nlse + 256;                                   // [2 groups][2 bufs][64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 256);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
   uint64_t* kv_full = bars;            // 1
   uint64_t* q_full = bars + 1;         // [2]
   uint64_t* q_empty = bars + 3;        // [2]
@@ -220,8 +232,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1);
-      mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 128);
-      mbar_init(&dq_full[s], 1); mbar_init(&dq_empty[s], 256);
+      mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 512);
+      mbar_init(&dq_full[s], 1); mbar_init(&dq_empty[s], 512);
     }
     mbar_init(acc_full, 1);
     fence_mbar_init();
@@ -272,10 +284,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         const uint32_t dos = qs + Cfg::kTileBytes;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma_ss(tbase + kColS + h * kHalf, desc_k_major(k_addr + k * 32, RB), desc_k_major(qs + k * 32, RB), idesc_s, k > 0);
+          umma_ss(tbase + kColBuf + h * 128, desc_k_major(k_addr + k * 32, RB), desc_k_major(qs + k * 32, RB), idesc_s, k > 0);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma_ss(tbase + kColDP + h * kHalf, desc_k_major(v_addr + k * 32, RB), desc_k_major(dos + k * 32, RB), idesc_s, k > 0);
+          umma_ss(tbase + kColBuf + h * 128 + 64, desc_k_major(v_addr + k * 32, RB), desc_k_major(dos + k * 32, RB), idesc_s, k > 0);
         umma_commit(&sdp_full[h]);
       };
       auto issue_acc = [&](int it, int h) {   // dV += P^T dO, dK += dS^T Q for half h
@@ -283,11 +295,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         const uint32_t dos = qs + Cfg::kTileBytes;
 #pragma unroll
         for (int k = 0; k < kHalf / 16; ++k)
-          umma_ts(tbase + kColDV, tbase + kColS + h * kHalf + k * 8, desc_mn_major(dos + k * 16 * RB, RB, 8 * RB), idesc_acc,
+          umma_ts(tbase + kColDV, tbase + kColBuf + h * 128 + k * 16, desc_mn_major(dos + k * 16 * RB, RB, 8 * RB), idesc_acc,
                   it > 0 || h > 0 || k > 0);
 #pragma unroll
         for (int k = 0; k < kHalf / 16; ++k)
-          umma_ts(tbase + kColDK, tbase + kColDP + h * kHalf + k * 8, desc_mn_major(qs + k * 16 * RB, RB, 8 * RB), idesc_acc,
+          umma_ts(tbase + kColDK, tbase + kColBuf + h * 128 + 64 + k * 16, desc_mn_major(qs + k * 16 * RB, RB, 8 * RB), idesc_acc,
                   it > 0 || h > 0 || k > 0);
       };
 
@@ -329,22 +341,23 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       if (ok) umma_commit(acc_full);
     }
   } else {
-    // ---------------------------------------------------------------- compute groups (lane = key row)
-    const int g = (warp - 2) / 4;                 // half of the query tile this group owns
+    // ---------------------------------------------------------------- compute warps (lane = key row)
+    // 16 warps work on ONE 64-query half at a time: thread = key row x 16 query columns (group g = 0..3).  The halves
+    // alternate between the two TMEM buffers, so while half `sub` is computed the tensor pipe fills the other buffer.
+    // Everything here is elementwise: no exchange between threads.
+    const int cwp = warp - 2;                     // 0..15
+    const int grp = cwp / 4;
     const int quarter = warp % 4;
     const int r = quarter * 32 + lane;            // key row in the tile == TMEM lane
-    const int tw = ((warp - 2) % 4) * 32 + lane;  // thread index inside the group
     const int kj = k0 + r;
     const int krow = kj < p.T ? kj : p.T - 1;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    const uint32_t tS = tbase + lane_base + kColS + g * kHalf;
-    const uint32_t tDP = tbase + lane_base + kColDP + g * kHalf;
+    const uint32_t tBuf = tbase + lane_base + kColBuf + 16 * grp;   // + 128 sub: S^T columns of this thread; dP^T 64 further
     const bool key_valid = kj < p.T && !((p.kpad[size_t(b) * p.TW + krow / 32] >> (krow % 32)) & 1u);
     const uint32_t* mrow = p.bitsT + (size_t(b) * p.T + krow) * p.TW;
-    const uint32_t flip = path == 0 ? 0xffffffffu : 0u;   // keep-bit = mask bit XOR flip
-    const float c2 = p.scale_log2;
-    const float* lse_bh = p.lse + size_t(bh) * p.T;
-    const float* delta_bh = p.delta + size_t(bh) * p.T;
+    const uint32_t flip = path == 0 ? 0xffffu : 0u;   // keep-bit = mask bit XOR flip
+    const uint64_t c22 = pack2(p.scale_log2, p.scale_log2);
+    const float4* stats_bh = reinterpret_cast<const float4*>(p.stats + size_t(bh) * p.Tpad);   // two queries per float4
     float* dq_bh = p.dq_acc[path] + size_t(bh) * p.T * D;
     bool ok = true;
     int it = 0;
@@ -352,13 +365,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     auto drain_dq = [&](int jt, int qtile) -> bool {   // add dQ of active tile jt (query tile qtile) to HBM
       if (!mbar_wait(&dq_full[jt & 1], (jt / 2) & 1, p.status, 0x601)) return false;
       tc_fence_after();
-      constexpr int NC = D / 2;   // columns per group
+      constexpr int NC = D / 4;   // columns per group
       uint32_t v[NC];
-      tmem_ld_n<NC>(tbase + lane_base + kColDQ + (jt & 1) * 64 + g * NC, v);
+      tmem_ld_n<NC>(tbase + lane_base + kColDQ + (jt & 1) * 64 + grp * NC, v);
       tmem_ld_wait();
       const int qi = qtile * kBwdTile + r;
       if (qi < p.T) {
-        float* dst = dq_bh + size_t(qi) * D + g * NC;
+        float* dst = dq_bh + size_t(qi) * D + grp * NC;
 #pragma unroll
         for (int e = 0; e < NC; e += 4)
           atomicAdd(reinterpret_cast<float4*>(dst + e), make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
@@ -373,107 +386,104 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     for (int i = 0; i < nqt && ok; ++i) {
       const uint8_t f = tq[i];
       if (f == 0) continue;
-      // per-query statistics of this half into shared memory (double buffered across tiles)
-      float* nl = s_nlse + (g * 2 + (it & 1)) * 64;
-      float* dl = s_delta + (g * 2 + (it & 1)) * 64;
-      {
-        const int q = i * kBwdTile + g * kHalf + (tw & 63);
-        if (tw < 64) nl[tw] = q < p.T ? -lse_bh[q] * kLog2e : -INFINITY;
-        else dl[tw - 64] = q < p.T ? delta_bh[q] : 0.f;
-      }
-      named_barrier(1 + g, 128);
-      ok = mbar_wait(&sdp_full[g], it & 1, p.status, 0x602);
-      if (!ok) break;
-      tc_fence_after();
-      const bool use_mask = (f & 2) != 0;
-      const uint2 mw = use_mask ? *reinterpret_cast<const uint2*>(mrow + 4 * i + 2 * g) : make_uint2(0, 0);
-      unsigned char* ds_row = sDS + size_t(it & 1) * Cfg::kDsBytes + size_t(g) * Cfg::kDsBlock;
+#pragma unroll 1
+      for (int sub = 0; sub < 2 && ok; ++sub) {
+        // statistics of this thread's 16 queries (L1/L2 hits, issued before the wait) and its 16 mask bits
+        const float4* st = stats_bh + (i * kBwdTile + sub * kHalf + 16 * grp) / 2;
+        float4 sq[8];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(tS + 32 * half, s);
-        tmem_ld32(tDP + 32 * half, dp);
+        for (int j = 0; j < 8; ++j) sq[j] = __ldg(st + j);
+        uint32_t keep = 0xffffu;
+        if (f & 2) keep = ((mrow[4 * i + 2 * sub + grp / 2] >> (16 * (grp & 1))) & 0xffffu) ^ flip;
+        if (!key_valid) keep = 0u;
+        const bool all = keep == 0xffffu;
+        ok = mbar_wait(&sdp_full[sub], it & 1, p.status, 0x602);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sv[16], dpv[16];
+        tmem_ld16(tBuf + 128 * sub, sv);
+        tmem_ld16(tBuf + 128 * sub + 64, dpv);
         tmem_ld_wait();
-        const uint32_t keep = use_mask ? ((half == 0 ? mw.x : mw.y) ^ flip) : 0xffffffffu;
-        uint32_t pp[16], dd[16];
+        uint32_t pp[8], dd[8];
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float p0 = bwd_ex2(fmaf(__uint_as_float(s[j]), c2, nl[32 * half + j]));
-          float p1 = bwd_ex2(fmaf(__uint_as_float(s[j + 1]), c2, nl[32 * half + j + 1]));
-          if (!(((keep >> j) & 1u) && key_valid)) p0 = 0.f;
-          if (!(((keep >> (j + 1)) & 1u) && key_valid)) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(dp[j]) - dl[32 * half + j]);
-          const float d1 = p1 * (__uint_as_float(dp[j + 1]) - dl[32 * half + j + 1]);
+        for (int j = 0; j < 16; j += 2) {
+          const float4 q2 = sq[j / 2];   // (nl0, nd0, nl1, nd1)
+          float p0, p1;
+          unpack2(ffma2(pack2(__uint_as_float(sv[j]), __uint_as_float(sv[j + 1])), c22, pack2(q2.x, q2.z)), p0, p1);
+          p0 = bwd_ex2(p0);
+          p1 = bwd_ex2(p1);
+          if (!all) {
+            if (!((keep >> j) & 1u)) p0 = 0.f;
+            if (!((keep >> (j + 1)) & 1u)) p1 = 0.f;
+          }
+          float d0, d1;
+          unpack2(fmul2(pack2(p0, p1), fadd2(pack2(__uint_as_float(dpv[j]), __uint_as_float(dpv[j + 1])), pack2(q2.y, q2.w))), d0, d1);
           pp[j / 2] = bwd_pack(p0, p1);
           dd[j / 2] = bwd_pack(d0, d1);
         }
-        tmem_st16(tS + 16 * half, pp);     // P^T over the already-read S^T columns
-        tmem_st16(tDP + 16 * half, dd);    // dS^T likewise
-#pragma unroll
-        for (int cch = 0; cch < 4; ++cch)  // and dS into shared memory for the dQ product: 4 chunks of 8 queries
-          *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 4 * half + cch, 128)) =
-              make_uint4(dd[4 * cch], dd[4 * cch + 1], dd[4 * cch + 2], dd[4 * cch + 3]);
+        tmem_st8(tBuf + 128 * sub, pp);         // P^T over the S^T columns this thread has read
+        tmem_st8(tBuf + 128 * sub + 64, dd);    // dS^T likewise
+        // and dS into shared memory for the dQ product: 2 chunks of 8 queries in block `sub` of buffer it & 1
+        unsigned char* ds_row = sDS + size_t(it & 1) * Cfg::kDsBytes + size_t(sub) * Cfg::kDsBlock;
+        *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 2 * grp, 128)) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
+        *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 2 * grp + 1, 128)) = make_uint4(dd[4], dd[5], dd[6], dd[7]);
+        tmem_st_wait();
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(&pds_full[sub]);
       }
-      tmem_st_wait();
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(&pds_full[g]);
+      if (!ok) break;
       if (prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
       prev_tile = i;
       ++it;
     }
     if (ok && prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
 
-    // ---- epilogue: group 0 writes dK (scaled, un-rotated for the self pathway), group 1 writes dV
+    // ---- epilogue: groups 0,1 write the two column halves of dK (scaled, un-rotated for the self pathway),
+    //      groups 2,3 those of dV
     if (n_active > 0) {
       if (ok) ok = mbar_wait(acc_full, 0, p.status, 0x603);
       tc_fence_after();
     }
-    if (ok && kj < p.T) { /* row guard applied at the stores below */ }
     if (ok) {
-      float v[D];
+      constexpr int hD = D / 2;
+      const bool is_dk = grp < 2;
+      const int half_col = grp & 1;
+      float lo[hD], hi[hD];   // lower / upper half of the row (dK needs both for the rotation; dV only its own)
       if (n_active > 0) {
-        const uint32_t src = tbase + lane_base + (g == 0 ? kColDK : kColDV);
-        if constexpr (D >= 32) {
+        const uint32_t src = tbase + lane_base + (is_dk ? kColDK : kColDV);
+        uint32_t t0[hD], t1[hD];
+        if (is_dk || half_col == 0) tmem_ld_n<hD>(src, t0);
+        if (is_dk || half_col == 1) tmem_ld_n<hD>(src + hD, t1);
+        tmem_ld_wait();
 #pragma unroll
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t t32[32];
-            tmem_ld32(src + c0, t32);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[c0 + j] = __uint_as_float(t32[j]);
-          }
-        } else {
-          uint32_t t16[16];
-          tmem_ld16(src, t16);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(t16[j]);
-        }
+        for (int j = 0; j < hD; ++j) { lo[j] = __uint_as_float(t0[j]); hi[j] = __uint_as_float(t1[j]); }
       } else {
 #pragma unroll
-        for (int j = 0; j < D; ++j) v[j] = 0.f;
+        for (int j = 0; j < hD; ++j) lo[j] = hi[j] = 0.f;
       }
       if (kj < p.T) {
-        __nv_bfloat16* dst = (g == 0 ? p.dk[path] : p.dv[path]) + (size_t(bh) * p.T + kj) * D;
-        if (g == 0) {
-          constexpr int h = D / 2;
-          if (path == 0 && p.cos_tab != nullptr) {
+        float outv[hD];
+        if (is_dk) {
+          const bool rot = path == 0 && p.cos_tab != nullptr;
 #pragma unroll
-            for (int d = 0; d < h; ++d) {
-              const float cs = p.cos_tab[size_t(kj) * h + d], sn = p.sin_tab[size_t(kj) * h + d];
-              const float a = v[d], bb = v[d + h];
-              v[d] = a * cs + bb * sn;
-              v[d + h] = bb * cs - a * sn;
+          for (int d = 0; d < hD; ++d) {
+            float v = half_col == 0 ? lo[d] : hi[d];
+            if (rot) {   // R^T: dx_lo = dy_lo c + dy_hi s, dx_hi = dy_hi c - dy_lo s
+              const float cs = p.cos_tab[size_t(kj) * hD + d], sn = p.sin_tab[size_t(kj) * hD + d];
+              v = half_col == 0 ? lo[d] * cs + hi[d] * sn : hi[d] * cs - lo[d] * sn;
             }
+            outv[d] = v * p.scale;
           }
+        } else {
 #pragma unroll
-          for (int j = 0; j < D; ++j) v[j] *= p.scale;
+          for (int d = 0; d < hD; ++d) outv[d] = half_col == 0 ? lo[d] : hi[d];
         }
+        __nv_bfloat16* dst = (is_dk ? p.dk[path] : p.dv[path]) + (size_t(bh) * p.T + kj) * D + half_col * hD;
 #pragma unroll
-        for (int j = 0; j < D; j += 8)
-          *reinterpret_cast<uint4*>(dst + j) = make_uint4(bwd_pack(v[j], v[j + 1]), bwd_pack(v[j + 2], v[j + 3]),
-                                                          bwd_pack(v[j + 4], v[j + 5]), bwd_pack(v[j + 6], v[j + 7]));
+        for (int j = 0; j < hD; j += 8)
+          *reinterpret_cast<uint4*>(dst + j) = make_uint4(bwd_pack(outv[j], outv[j + 1]), bwd_pack(outv[j + 2], outv[j + 3]),
+                                                          bwd_pack(outv[j + 4], outv[j + 5]), bwd_pack(outv[j + 6], outv[j + 7]));
       }
     }
   }
@@ -488,17 +498,18 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
 // ------------------------------------------------------------------------------------------------ host side
 static size_t bwd_rot_bytes(int B, int H, int T, int D) { return align256(size_t(B) * H * T * D * 2); }
 static size_t bwd_acc_bytes(int B, int H, int T, int D) { return align256(size_t(B) * H * T * D * 4); }
-static size_t bwd_delta_bytes(int B, int H, int T) { return align256(size_t(B) * H * T * 4); }
+static int bwd_tpad(int T) { return (T + kBwdTile - 1) / kBwdTile * kBwdTile; }
+static size_t bwd_stats_bytes(int B, int H, int T) { return align256(size_t(B) * H * bwd_tpad(T) * 8); }
 
-// Workspace: [rotated Q_self | rotated K_self] (rope only) | delta | dQ accumulator self | dQ accumulator cross
+// Workspace: [rotated Q_self | rotated K_self] (rope only) | stats | dQ accumulator self | dQ accumulator cross
 size_t tc_bwd_workspace_bytes(int B, int H, int T, int D, bool rope) {
-  return (rope ? 2 * bwd_rot_bytes(B, H, T, D) : 0) + bwd_delta_bytes(B, H, T) + 2 * bwd_acc_bytes(B, H, T, D);
+  return (rope ? 2 * bwd_rot_bytes(B, H, T, D) : 0) + bwd_stats_bytes(B, H, T) + 2 * bwd_acc_bytes(B, H, T, D);
 }
 
 void launch_rope_rotate(const AttnArgs& a, __nv_bfloat16* qr, __nv_bfloat16* kr);  // attn_tc.cu
 
 template <int D>
-static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, float* delta, float* acc_s, float* acc_c) {
+static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const float2* stats, float* acc_s, float* acc_c) {
   using Cfg = BwdCfg<D>;
   const int BH = a.B * a.H;
   CUtensorMap mqs, mks, mvs, mqc, mkc, mvc, mdo;
@@ -513,13 +524,13 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, float* 
   if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   BwdParams p{};
   p.bitsT = a.meta.bitsT; p.kpad = a.meta.kpad; p.cls = a.meta.cls;
-  p.lse = a.lse; p.delta = delta;
+  p.stats = stats;
   p.cos_tab = a.rope ? a.rope_cos : nullptr;
   p.sin_tab = a.rope ? a.rope_sin : nullptr;
   p.dq_acc[0] = acc_s; p.dq_acc[1] = acc_c;
   p.dk[0] = static_cast<__nv_bfloat16*>(a.dk_s); p.dk[1] = static_cast<__nv_bfloat16*>(a.dk_c);
   p.dv[0] = static_cast<__nv_bfloat16*>(a.dv_s); p.dv[1] = static_cast<__nv_bfloat16*>(a.dv_c);
-  p.H = a.H; p.T = a.T; p.TW = a.meta.TW; p.NT = a.meta.NT;
+  p.H = a.H; p.T = a.T; p.Tpad = bwd_tpad(a.T); p.TW = a.meta.TW; p.NT = a.meta.NT;
   p.scale = a.scale; p.scale_log2 = a.scale * kLog2e;
   p.status = a.dev_status;
   dim3 grid((a.T + kBwdTile - 1) / kBwdTile, BH, 2);
@@ -544,23 +555,25 @@ int launch_attn_bwd_tc(const AttnArgs& a) {
     k_s = kr;
     ws += 2 * bwd_rot_bytes(a.B, a.H, a.T, a.D);
   }
-  float* delta = reinterpret_cast<float*>(ws);
-  ws += bwd_delta_bytes(a.B, a.H, a.T);
+  float2* stats = reinterpret_cast<float2*>(ws);
+  ws += bwd_stats_bytes(a.B, a.H, a.T);
   float* acc_s = reinterpret_cast<float*>(ws);
   float* acc_c = reinterpret_cast<float*>(ws + bwd_acc_bytes(a.B, a.H, a.T, a.D));
   cudaError_t e = cudaMemsetAsync(acc_s, 0, 2 * bwd_acc_bytes(a.B, a.H, a.T, a.D), a.stream);
   if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   {
-    const size_t n = rows * (a.D / 8);
-    bwd_delta_kernel<<<unsigned((n + 255) / 256), 256, 0, a.stream>>>(static_cast<const __nv_bfloat16*>(a.out),
-                                                                     static_cast<const __nv_bfloat16*>(a.d_out), delta, rows, a.D);
+    const int tpad = bwd_tpad(a.T);
+    const size_t n = size_t(a.B) * a.H * tpad * (a.D / 8);
+    bwd_stats_kernel<<<unsigned((n + 255) / 256), 256, 0, a.stream>>>(static_cast<const __nv_bfloat16*>(a.out),
+                                                                     static_cast<const __nv_bfloat16*>(a.d_out), a.lse, stats,
+                                                                     a.B * a.H, a.T, tpad, a.D);
     count_launches(1);
   }
   int rc = MINTB_EUNSUPPORTED;
   switch (a.D) {
-    case 16: rc = bwd_tc_t<16>(a, q_s, k_s, delta, acc_s, acc_c); break;
-    case 32: rc = bwd_tc_t<32>(a, q_s, k_s, delta, acc_s, acc_c); break;
-    case 64: rc = bwd_tc_t<64>(a, q_s, k_s, delta, acc_s, acc_c); break;
+    case 16: rc = bwd_tc_t<16>(a, q_s, k_s, stats, acc_s, acc_c); break;
+    case 32: rc = bwd_tc_t<32>(a, q_s, k_s, stats, acc_s, acc_c); break;
+    case 64: rc = bwd_tc_t<64>(a, q_s, k_s, stats, acc_s, acc_c); break;
     default: set_error("mintb_attn_bwd: unsupported head_dim %d", a.D);
   }
   if (rc != MINTB_OK) return rc;

@@ -30,6 +30,17 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Non-blocking test of a phase, and a potentially blocking one (the hardware may suspend the thread for a short,
+// implementation-defined time while the phase is pending).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -39,14 +50,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 
-// Bounded wait: gives up after `kSpinLimit` polls, records `code` in *status (if non-null) and returns false.
-// Callers unwind (skip the rest of their work, still release TMEM) instead of spinning forever.
-constexpr uint32_t kSpinLimit = 1u << 24;
+// Bounded wait: gives up once `kWaitLimitNs` of wall time have passed (checked every 1024 polls), records `code` in
+// *status (if non-null) and returns false.  Callers unwind (skip the rest of their work, still release TMEM)
+// instead of spinning forever.  The common case - the phase has already completed - costs one test.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+  if (mbar_test_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (int it = 0; it < 1024; ++it)   // ordinary waits end here; the timer (slow to read) is not touched
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 4096) __nanosleep(64);
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int it = 0; it < 1024; ++it)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > kWaitLimitNs) break;
   }
   if (status != nullptr) atomicCAS(status, 0, code);
   return false;
@@ -142,6 +166,40 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       ::"r"(taddr), MINTB_W8(r, 0), MINTB_W8(r, 8)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : MINTB_R8(r, 0)
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), MINTB_W8(r, 0)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr)
+               : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t (&r)[N]) {
+  static_assert(N == 4 || N == 8 || N == 16 || N == 32, "4, 8, 16 or 32 columns");
+  if constexpr (N == 32) tmem_ld32(taddr, r);
+  else if constexpr (N == 16) tmem_ld16(taddr, r);
+  else if constexpr (N == 8) tmem_ld8(taddr, r);
+  else tmem_ld4(taddr, r);
+}
+template <int N>
+__device__ __forceinline__ void tmem_st_n(uint32_t taddr, const uint32_t (&r)[N]) {
+  static_assert(N == 8 || N == 16 || N == 32, "8, 16 or 32 columns");
+  if constexpr (N == 32) tmem_st32(taddr, r);
+  else if constexpr (N == 16) tmem_st16(taddr, r);
+  else tmem_st8(taddr, r);
+}
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -162,6 +220,15 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   d |= uint64_t(layout) << 61;
   return d;
 }
+// The same descriptor split into 32-bit words for issue loops: a constant high word (stride offset, version, layout)
+// and a low word = address field + leading-offset field, which advances by (bytes >> 4).
+__host__ __device__ constexpr uint32_t desc_hi32(uint32_t sbo_bytes, uint32_t layout) {
+  return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (layout << 29);
+}
+__host__ __device__ constexpr uint32_t desc_lbo32(uint32_t lbo_bytes) { return ((lbo_bytes >> 4) & 0x3FFF) << 16; }
+__device__ __forceinline__ uint32_t desc_addr32(uint32_t saddr) { return (saddr >> 4) & 0x3FFF; }
+__device__ __forceinline__ uint64_t make_desc(uint32_t hi, uint32_t lo) { return (uint64_t(hi) << 32) | lo; }
+
 // Operand whose reduction (K) dimension is contiguous: rows of `row_bytes` stacked at `row_bytes`, eight rows per
 // swizzle atom.  One MMA consumes 32 bytes of each row; advance the start address by 32 bytes per K step.
 __device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr, int row_bytes) {
