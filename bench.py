@@ -29,9 +29,9 @@ WORKLOAD = dict(B=8, H=20, T=1024, D=32)
 METRIC = "fused_multimer_attention_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-# DRAM bytes (read + write) per launch of the dominant kernel from the ncu capture summarised under profiles/;
-# None until a capture of the current kernel exists.
-NCU_TRAFFIC_BYTES = None
+# DRAM bytes (read + write) per launch of the dominant kernel (attn_bwd_tc_kernel<32> on this workload) from the ncu
+# capture summarised in profiles/attn_tc_kernels_B8_H20_T1024_D32.md: 121.5 MB read + 40.6 MB written.
+NCU_TRAFFIC_BYTES = 162.1e6
 
 
 def algorithmic_flops(H, T, D, key_pad, fwd=True, bwd=True):
@@ -90,13 +90,11 @@ class ClockSampler(threading.Thread):
 
 
 def cpu_baseline(seconds_budget=20.0):
-    """The oracle (a port of the reference's PyTorch path) on the host cores, on a bounded sample: one pair (B=1) of the
-    workload, fp32, forward + autograd backward."""
+    """The oracle (a port of the reference's PyTorch path) on the host cores, on a bounded sample: a few steps of the
+    same batch (8 pairs), fp32, forward + autograd backward."""
     from oracle import multimer_attention as O
     torch.set_num_threads(os.cpu_count() or 1)
     ts, cid, pad, grad = make_inputs(2002)
-    ts = [t[:1] for t in ts]
-    cid, pad, grad = cid[:1], pad[:1], grad[:1]
     mask = O.chain_mask_from_ids(cid)
     flops = algorithmic_flops(WORKLOAD["H"], WORKLOAD["T"], WORKLOAD["D"], pad)
     times = []
@@ -111,8 +109,8 @@ def cpu_baseline(seconds_budget=20.0):
             break
     sec = statistics.median(times)
     return {"value": flops / sec / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"1 of {WORKLOAD['B']} pairs (B=1,H=20,T=1024,D=32), fp32, fwd+autograd bwd, "
-                      f"median of {len(times)} after 1 warm-up, {sec:.2f} s each"}, sec
+            "sample": f"the benchmark batch (B=8,H=20,T=1024,D=32), fp32, fwd+autograd bwd, "
+                      f"median of {len(times)} steps after 1 warm-up, {sec:.2f} s each"}, sec
 
 
 def run_reference(args, rank, world):
@@ -123,8 +121,6 @@ def run_reference(args, rank, world):
     from oracle import multimer_attention as O
     torch.set_num_threads(os.cpu_count() or 1)
     ts, cid, pad, grad = make_inputs(2002)
-    ts = [t[:1] for t in ts]
-    cid, pad, grad = cid[:1], pad[:1], grad[:1]
     mask = O.chain_mask_from_ids(cid)
     flops = algorithmic_flops(WORKLOAD["H"], WORKLOAD["T"], WORKLOAD["D"], pad)
     steps = max(1, min(args.steps, 5))
@@ -136,7 +132,7 @@ def run_reference(args, rank, world):
         O.multimer_attention_fwd_bwd(*ts, mask, grad, key_pad=pad)
     sec = (time.perf_counter() - t0) / steps
     val = flops / sec / 1e12
-    sample = (f"each step = 1 of {WORKLOAD['B']} pairs (B=1,H=20,T=1024,D=32), fp32, fwd + autograd bwd; "
+    sample = (f"each step = the benchmark batch (B=8,H=20,T=1024,D=32), fp32, fwd + autograd bwd; "
               f"{steps} steps after {warm} warm-up (bounded from the requested {args.steps}/{args.warmup})")
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
             "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -202,35 +198,68 @@ def main():
     for _ in range(warmup):
         step_resident()
     barrier()
+
+    # The step is launch-bound on the host (nine small launches around two ~100-300 us kernels), so the timed loop
+    # replays a CUDA graph of one forward (+ backward) captured through the same public API.
+    def capture(fn):
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()                                     # warm the allocator on the capture stream
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g):
+            keep = fn()
+        return g, keep
+
+    def fwd_only():
+        with torch.no_grad():
+            return M.multimer_attention(*[t.detach() for t in dts], meta=meta)
+
+    use_graph = True
+    try:
+        g_step, _k1 = capture(step_resident)
+        g_fwd, _k2 = capture(fwd_only)
+        run_step, run_fwd = g_step.replay, g_fwd.replay
+        launches0 = lib.mintb_kernel_launches()
+        step_resident()
+        launches_per_step = lib.mintb_kernel_launches() - launches0
+    except Exception as exc:                          # capture not possible: time the eager launches
+        use_graph = False
+        sys.stderr.write(f"bench: CUDA graph capture failed ({exc}); timing eager launches\n")
+        run_step, run_fwd = step_resident, fwd_only
+        launches0 = lib.mintb_kernel_launches()
+        step_resident()
+        launches_per_step = lib.mintb_kernel_launches() - launches0
+    for _ in range(3):
+        run_step()
+    barrier()
     sampler = ClockSampler(local)
     sampler.start()
     # ---- device-resident inputs: K steps, each bracketed by its own events, L2 flushed between steps
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    launches0 = lib.mintb_kernel_launches()
     barrier()
     for s, e in ev:
         flush.zero_()
         s.record()
-        step_resident()
+        run_step()
         e.record()
     barrier()
-    launches = lib.mintb_kernel_launches() - launches0
+    launches = launches_per_step * steps
     ms_total = sum(s.elapsed_time(e) for s, e in ev)
 
-    # ---- forward / backward C-ABI calls timed apart (for the roofline of the dominant one)
-    leaves = [t.requires_grad_(True) for t in dts]
-    fwd_ms, bwd_ms = [], []
+    # ---- the forward call alone (same method); the backward call is the difference
+    fwd_ms = []
     for _ in range(min(steps, 20)):
         flush.zero_()
-        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        out = M.multimer_attention(*leaves, meta=meta)
+        run_fwd()
         b.record()
-        torch.autograd.grad(out, leaves, dgrad)
-        c.record()
         torch.cuda.synchronize()
         fwd_ms.append(a.elapsed_time(b))
-        bwd_ms.append(b.elapsed_time(c))
+    bwd_ms = [ms_total / steps - statistics.mean(fwd_ms)]
 
     # ---- end to end: pinned host inputs -> device, fwd+bwd through the public API, results -> pinned host
     out_host = [torch.empty(B, H, T, D, dtype=torch.bfloat16).pin_memory() for _ in range(7)]
@@ -286,6 +315,7 @@ def main():
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "isolated combined-softmax multimer attention fwd+bwd, B=8 H=20 D=32 T=1024 per GPU",
                        "rope": "self pathway", "l2": "flushed between timed steps (256 MiB write)",
+                       "launch": "CUDA graph replay of one step" if use_graph else "eager launches",
                        "flops": "14*H*T*Tk*D per pair, Tk = unpadded keys"},
             "roofline": {"bound": "tensor", "kernel": dom[0], "achieved": achieved, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES,

@@ -272,34 +272,46 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   }
   if (warp == 1) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
   __syncthreads();
-  if (tid == 32 * 2) {   // one thread turns the class row into the entry list
+  if (warp == 0 && lane == 0) {   // the Q tiles do not depend on the entry list: start them now
+    prefetch_tensormap(&map_qs); prefetch_tensormap(&map_qc);
+    mbar_expect_tx(bar_q, 2 * Cfg::kQBytes);
+    tma_load_3d(sQs, &map_qs, bar_q, 0, q0, bh);
+    tma_load_3d(sQc, &map_qc, bar_q, 0, q0, bh);
+  }
+  if (warp == 2) {   // one warp turns the class row into the entry list, 32 tiles per pass
     int n = 0;
-    for (int kt = 0; kt < nkt; ++kt) {
-      const uint8_t c = tcls[kt];
-      if (c == 0) continue;
-      const bool mixed = (c & 3) == 3;
-      if constexpr (kN == 128) {
-        if (!mixed && kt + 1 < nkt && tcls[kt + 1] != 0 && (tcls[kt + 1] & 3) == (c & 3)) {
-          ent_k[n] = uint16_t(2 * kt);
-          ent_c[n++] = uint8_t(c | tcls[kt + 1] | kEntryFull);
-          ++kt;
+    for (int base = 0; base < nkt; base += 32) {
+      const int kt = base + lane;
+      const uint8_t c = kt < nkt ? tcls[kt] : uint8_t(0);
+      const uint8_t cn = (kt + 1 < nkt && lane < 31) ? tcls[kt + 1] : uint8_t(0);   // a pass boundary also ends a run
+      const bool mixed = (c & 3) == 3, pure = c != 0 && !mixed;
+      const uint8_t cp = lane > 0 ? tcls[kt - 1] : uint8_t(0);
+      // runs of pure tiles of one pathway: a tile starts a run unless its predecessor is a pure tile of the same pathway
+      const bool run_start = pure && !(cp != 0 && (cp & 3) == (c & 3));
+      const unsigned starts = __ballot_sync(0xffffffffu, run_start);
+      const unsigned below = starts & (0xffffffffu >> (31 - lane));               // run starts at or before this lane
+      const int off = pure ? lane - (31 - __clz(below)) : 0;                      // position inside the run
+      const bool can_pair = kN == 128 && pure && cn != 0 && (cn & 3) == (c & 3);
+      int cnt = 0;
+      uint8_t flags = c;
+      if (mixed) cnt = kN == 128 ? 1 : 2;
+      else if (pure) {
+        if constexpr (kN == 128) {
+          if ((off & 1) == 0) { cnt = 1; if (can_pair) flags = uint8_t(c | cn | kEntryFull); }
         } else {
-          ent_k[n] = uint16_t(2 * kt);
-          ent_c[n++] = c;
-        }
-      } else {
-        if (!mixed) {
-          ent_k[n] = uint16_t(2 * kt);
-          ent_c[n++] = uint8_t(c | kEntryFull);
-        } else {   // two 32-key entries
-          ent_k[n] = uint16_t(2 * kt);
-          ent_c[n++] = c;
-          ent_k[n] = uint16_t(2 * kt + 1);
-          ent_c[n++] = c;
+          cnt = 1;
+          flags = uint8_t(c | kEntryFull);
         }
       }
+      // exclusive prefix sum of cnt over the lanes (cnt is 0, 1 or 2)
+      const unsigned b1 = __ballot_sync(0xffffffffu, cnt & 1), b2 = __ballot_sync(0xffffffffu, cnt & 2);
+      const unsigned lt = (1u << lane) - 1u;
+      const int pos = n + __popc(b1 & lt) + 2 * __popc(b2 & lt);
+      if (cnt >= 1) { ent_k[pos] = uint16_t(2 * kt); ent_c[pos] = flags; }
+      if (cnt == 2) { ent_k[pos + 1] = uint16_t(2 * kt + 1); ent_c[pos + 1] = flags; }
+      n += __popc(b1) + 2 * __popc(b2);
     }
-    *n_entries_s = n;
+    if (lane == 0) *n_entries_s = n;
   }
   tc_fence_before();
   __syncthreads();
@@ -311,12 +323,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      prefetch_tensormap(&map_qs); prefetch_tensormap(&map_qc);
       prefetch_tensormap(&map_ks); prefetch_tensormap(&map_vs);
       prefetch_tensormap(&map_kc); prefetch_tensormap(&map_vc);
-      mbar_expect_tx(bar_q, 2 * Cfg::kQBytes);
-      tma_load_3d(sQs, &map_qs, bar_q, 0, q0, bh);
-      tma_load_3d(sQc, &map_qc, bar_q, 0, q0, bh);
       for (int it = 0; it < n_ent; ++it) {
         const int stage = it % kStages;
         if (!mbar_wait(&kv_empty[stage], ((it / kStages) & 1) ^ 1, p.status, 0x101)) break;

@@ -8,9 +8,9 @@
 //   P^T = exp2(S^T c - lse), masked       dS^T = P^T o (dP^T - delta)
 //   dV += P^T dO, dK += dS^T Q            (A operands read from TMEM, aliased over S^T / dP^T)
 //   dQ_tile = dS K                        (dS through shared memory), added to an fp32 accumulator in HBM
-// Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-17 compute (thread = key row x 16 query columns of the
-// half in flight).  The halves ping-pong: while one is computed the tensor pipe refills the other buffer.
-// TMEM (512 columns): dK [0,64) dV [64,128) dQ x2 [128,256) buffer 0 {S^T, dP^T} [256,384) buffer 1 [384,512).
+// Warp roles: warps 0-3 MMA issuers, one per family of products (warp 0 also issues the TMA loads), warps 4-19 compute
+// (thread = key row x 16 query columns of the half in flight).  The halves ping-pong: while one is computed the tensor pipe refills the other buffer.
+// TMEM (512 columns): dK, dV, two dQ tiles, then two (head_dim 64) or three (head_dim <= 32) buffers {S^T half, dP^T half}.
 // dQ is accumulated across CTAs with fp32 atomics, so its low-order bits depend on arrival order;
 // dK and dV are reduced inside one CTA in a fixed order.  All mbarrier waits are bounded.
 #include "common.cuh"
@@ -20,13 +20,24 @@ namespace mintb {
 
 using namespace ptx;
 
+// Optional per-warp timeline of one CTA (debug builds with -DMINTB_TRACE only; compiled out otherwise).
+#ifdef MINTB_TRACE
+__device__ unsigned long long g_trace_bwd[32 * 512];
+#define MINTB_BTRACE_DECL int tr_n = 0; const bool tr_on = (blockIdx.x == 2 && blockIdx.y == 7 && blockIdx.z == 0 && (threadIdx.x % 32) == 0);
+#define MINTB_BTRACE_EV(code) do { if (tr_on && tr_n < 510) g_trace_bwd[(threadIdx.x / 32) * 512 + (++tr_n)] = ((unsigned long long)clock64() << 8) | (unsigned)(code); } while (0)
+#define MINTB_BTRACE_END do { if (tr_on) g_trace_bwd[(threadIdx.x / 32) * 512] = tr_n; } while (0)
+#else
+#define MINTB_BTRACE_DECL
+#define MINTB_BTRACE_EV(code)
+#define MINTB_BTRACE_END
+#endif
+
 constexpr int kBwdTile = 128;       // keys per CTA and queries per step
 constexpr int kHalf = 64;           // queries per compute group
-constexpr int kBwdThreads = 576;   // producer warp, MMA warp, 16 compute warps
-constexpr int kBwdStages = 2;
+constexpr int kBwdThreads = 640;   // 4 MMA-issuing warps (one also issues the TMA loads), 16 compute warps
 constexpr int kBwdMaxTiles = 256;   // T <= 32768
 constexpr uint32_t kTmemAll = 512;
-constexpr int kColDK = 0, kColDV = 64, kColDQ = 128, kColBuf = 256;   // buffer b: S^T at kColBuf + 128 b, dP^T 64 further
+constexpr unsigned kBwdStaggerNs = 250;   // initial offset between the two pairs of compute groups
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -169,7 +180,13 @@ struct BwdCfg {
   static constexpr int kTileBytes = kBwdTile * kRowBytes;       // K, V, Q_i, dO_i tiles
   static constexpr int kDsBlock = kBwdTile * 128;               // one half (64 queries) of dS: [128 key rows][128 B]
   static constexpr int kDsBytes = 2 * kDsBlock;
-  static constexpr size_t kSmemBytes = 1024 + 2 * kTileBytes + size_t(kBwdStages) * 2 * kTileBytes + 2 * kDsBytes + 4096;
+  // TMEM: dK, dV, two dQ tiles, then kNBuf buffers of {S^T half (64 columns), dP^T half (64 columns)}.
+  // Small heads leave room for a third buffer, which lets the products run two halves ahead of the compute warps.
+  static constexpr int kNBuf = D <= 32 ? 3 : 2;
+  static constexpr int kQStages = D <= 32 ? 3 : 2;              // stages of {Q_i, dO_i}
+  static constexpr int kAcc = D <= 32 ? 32 : 64;                // columns reserved per accumulator
+  static constexpr int kColDK = 0, kColDV = kAcc, kColDQ = 2 * kAcc, kColBuf = 4 * kAcc;
+  static constexpr size_t kSmemBytes = 1024 + 2 * kTileBytes + size_t(kQStages) * 2 * kTileBytes + 2 * kDsBytes + 4096;
 };
 
 struct BwdParams {
@@ -184,6 +201,15 @@ struct BwdParams {
   int* status;
 };
 
+// ring counter with phase bit: position in [0, N), phase flips on wrap
+template <int N>
+struct Ring {
+  uint32_t pos = 0, phase = 0;
+  __device__ __forceinline__ void advance() {
+    if (++pos == N) { pos = 0; phase ^= 1; }
+  }
+};
+
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_constant__ CUtensorMap map_ks,
@@ -191,28 +217,32 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
                    const __grid_constant__ CUtensorMap map_kc, const __grid_constant__ CUtensorMap map_vc,
                    const __grid_constant__ CUtensorMap map_do, BwdParams p) {
   using Cfg = BwdCfg<D>;
-  constexpr int RB = Cfg::kRowBytes;
+  constexpr int RB = Cfg::kRowBytes, kNBuf = Cfg::kNBuf, kQStages = Cfg::kQStages;
+  constexpr int kColDK = Cfg::kColDK, kColDV = Cfg::kColDV, kColDQ = Cfg::kColDQ, kColBuf = Cfg::kColBuf, kAcc = Cfg::kAcc;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sK = smem;
   unsigned char* sV = sK + Cfg::kTileBytes;
-  unsigned char* sQ = sV + Cfg::kTileBytes;                        // [stage][0: Q_i, 1: dO_i]
-  unsigned char* sDS = sQ + size_t(kBwdStages) * 2 * Cfg::kTileBytes;  // [buf][half][128 rows x 128 B]
+  unsigned char* sQ = sV + Cfg::kTileBytes;                          // [stage][0: Q_i, 1: dO_i]
+  unsigned char* sDS = sQ + size_t(kQStages) * 2 * Cfg::kTileBytes;  // [buf][half][128 rows x 128 B]
   unsigned char* tail = sDS + 2 * Cfg::kDsBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
   uint64_t* kv_full = bars;            // 1
-  uint64_t* q_full = bars + 1;         // [2]
-  uint64_t* q_empty = bars + 3;        // [2]
-  uint64_t* sdp_full = bars + 5;       // [2 halves]
-  uint64_t* pds_full = bars + 7;       // [2 halves]
-  uint64_t* dq_full = bars + 9;        // [2 bufs]
-  uint64_t* dq_empty = bars + 11;      // [2 bufs]
-  uint64_t* acc_full = bars + 13;      // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* acc_full = bars + 1;       // 1
+  uint64_t* q_full = bars + 2;         // [3]
+  uint64_t* q_empty = bars + 5;        // [3]
+  uint64_t* sdp_full = bars + 8;       // [3 buffers]
+  uint64_t* pds_full = bars + 11;      // [3 buffers]
+  uint64_t* buf_free = bars + 14;      // [3 buffers]
+  uint64_t* dq_full = bars + 17;       // [2]
+  uint64_t* dq_empty = bars + 19;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   uint8_t* tq = reinterpret_cast<uint8_t*>(tmem_slot + 2);  // per query tile: 0 skip, else 1 | (needs chain mask) << 1 | (pad) << 2
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int kt = blockIdx.x, bh = blockIdx.y, path = blockIdx.z, b = bh / p.H;
+  MINTB_BTRACE_DECL
+  MINTB_BTRACE_EV(1);
   const int k0 = kt * kBwdTile;
   const int nqt = (p.T + kBwdTile - 1) / kBwdTile;
   const uint8_t want = path == 0 ? kHasIntra : kHasInter;
@@ -230,12 +260,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   }
   if (tid == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1);
+    mbar_init(acc_full, 2);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 2);      // released by the dV and the dK stream
       mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 512);
-      mbar_init(&dq_full[s], 1); mbar_init(&dq_empty[s], 512);
+      mbar_init(&buf_free[s], 2);                                // dV and dK of a half have read P^T, dS^T
     }
-    mbar_init(acc_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&dq_full[s], 1); mbar_init(&dq_empty[s], 512); }
     fence_mbar_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, kTmemAll); tmem_relinquish(); }
@@ -243,116 +274,158 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = *tmem_slot;
+  MINTB_BTRACE_EV(2);
   int n_active = 0;
   for (int i = 0; i < nqt; ++i) n_active += tq[i] != 0;
+  const int n_sub = 2 * n_active;   // 64-query halves, numbered u = 2 * tile + half; half u lives in buffer u % kNBuf
 
   const CUtensorMap* mq = path == 0 ? &map_qs : &map_qc;
   const CUtensorMap* mk = path == 0 ? &map_ks : &map_kc;
   const CUtensorMap* mv = path == 0 ? &map_vs : &map_vc;
 
-  if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer
+  if (warp == 1) {
+    // ---------------------------------------------------------------- MMA stream A: S^T = K Q^T and dP^T = V dO^T
+    // Issuing one tcgen05.mma costs its thread some 50 cycles whatever the tile size, and at small head sizes the
+    // products are tiny, so the four families of products are issued by four warps in parallel (disjoint accumulators).
     if (lane == 0 && n_active > 0) {
+      constexpr uint32_t idesc_s = idesc_bf16(kBwdTile, kHalf, false, false);   // M = 128 keys, N = 64 queries
+      constexpr uint32_t kHi = desc_hi32(8 * RB, swizzle_for_row_bytes(RB));
+      constexpr uint32_t kLbo = desc_lbo32(16);
+      const uint32_t k_lo = desc_addr32(smem_u32(sK)) + kLbo, v_lo = desc_addr32(smem_u32(sV)) + kLbo;
+      const uint32_t q_lo = desc_addr32(smem_u32(sQ)) + kLbo;
+      constexpr uint32_t kTileU = Cfg::kTileBytes >> 4, kHalfU = (kHalf * RB) >> 4;
+      bool ok = mbar_wait(kv_full, 0, p.status, 0x501);
+      Ring<kQStages> qr;     // query tile of the half being issued
+      Ring<kNBuf> ib;        // buffer of the half being issued
+      Ring<kNBuf> wb;        // buffer whose release is awaited next
+      auto issue_sdp = [&](int u) -> bool {   // both products of half u
+        const int h = u & 1;
+        if (h == 0 && !mbar_wait(&q_full[qr.pos], qr.phase, p.status, 0x502)) return false;
+        tc_fence_after();
+        const uint32_t qs = q_lo + qr.pos * 2 * kTileU + h * kHalfU;
+        const uint32_t dos = qs + kTileU;
+        const uint32_t col = tbase + kColBuf + ib.pos * 128;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma_ss(col, make_desc(kHi, k_lo + 2 * k), make_desc(kHi, qs + 2 * k), idesc_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma_ss(col + 64, make_desc(kHi, v_lo + 2 * k), make_desc(kHi, dos + 2 * k), idesc_s, k > 0);
+        umma_commit(&sdp_full[ib.pos]);
+        ib.advance();
+        if (h == 1) qr.advance();
+        return true;
+      };
+      int issued = 0;
+      for (; issued < kNBuf && issued < n_sub && ok; ++issued) ok = issue_sdp(issued);
+      for (int u = 0; issued < n_sub && ok; ++u, ++issued) {
+        ok = mbar_wait(&buf_free[wb.pos], wb.phase, p.status, 0x505);   // dV and dK of half u have consumed P^T, dS^T
+        if (!ok) break;
+        MINTB_BTRACE_EV(10);
+        wb.advance();
+        ok = issue_sdp(issued);
+        MINTB_BTRACE_EV(11);
+      }
+    }
+  } else if (warp == 2 || warp == 3) {
+    // ---------------------------------------------------------------- MMA streams V and K: dV += P^T dO, dK += dS^T Q
+    if (lane == 0 && n_active > 0) {
+      constexpr uint32_t idesc_acc = idesc_bf16(kBwdTile, D, false, true);      // A from TMEM, B rows of dO / Q (N = D contiguous)
+      constexpr uint32_t kHi = desc_hi32(8 * RB, swizzle_for_row_bytes(RB));
+      constexpr uint32_t kLbo = desc_lbo32(8 * RB);
+      constexpr uint32_t kTileU = Cfg::kTileBytes >> 4, kHalfU = (kHalf * RB) >> 4, kStep = (16 * RB) >> 4;
+      const bool is_v = warp == 2;
+      // dV reads P^T (over S^T) and dO; dK reads dS^T (over dP^T, 64 columns further) and Q
+      const uint32_t b_lo = desc_addr32(smem_u32(sQ)) + kLbo + (is_v ? kTileU : 0u);
+      const uint32_t a_col = tbase + kColBuf + (is_v ? 0u : 64u);
+      const uint32_t d_col = tbase + (is_v ? kColDV : kColDK);
+      bool ok = true;
+      Ring<kQStages> qr;
+      Ring<kNBuf> br;
+      for (int it = 0; it < n_active && ok; ++it) {
+        ok = mbar_wait(&q_full[qr.pos], qr.phase, p.status, 0x511);
+        for (int h = 0; h < 2 && ok; ++h) {
+          ok = mbar_wait(&pds_full[br.pos], br.phase, p.status, 0x512);
+          if (!ok) break;
+          MINTB_BTRACE_EV(20);
+          tc_fence_after();
+          const uint32_t rows = b_lo + qr.pos * 2 * kTileU + h * kHalfU;
+#pragma unroll
+          for (int k = 0; k < kHalf / 16; ++k)
+            umma_ts(d_col, a_col + br.pos * 128 + k * 16, make_desc(kHi, rows + k * kStep), idesc_acc, it > 0 || h > 0 || k > 0);
+          umma_commit(&buf_free[br.pos]);
+          MINTB_BTRACE_EV(21);
+          br.advance();
+        }
+        if (ok) umma_commit(&q_empty[qr.pos]);
+        qr.advance();
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else if (warp == 0) {
+    // ---------------------------------------------------------------- TMA loads and MMA stream Q: dQ tile = dS K
+    // One thread does both: it loads K, V and the first query tiles, then per tile issues the dQ product and
+    // refills the stage that tile has just released with the tile kQStages steps ahead.
+    if (lane == 0 && n_active > 0) {
+      constexpr uint32_t idesc_dq = idesc_bf16(kBwdTile, D, true, true);        // A = dS (queries contiguous), B = K (D contiguous)
+      constexpr uint32_t kHiA = desc_hi32(8 * 128, kSw128), kHiB = desc_hi32(8 * RB, swizzle_for_row_bytes(RB));
+      const uint32_t ds_lo = desc_addr32(smem_u32(sDS)) + desc_lbo32(Cfg::kDsBlock);
+      const uint32_t kb_lo = desc_addr32(smem_u32(sK)) + desc_lbo32(8 * RB);
+      constexpr uint32_t kDsU = Cfg::kDsBytes >> 4, kAStep = (16 * 128) >> 4, kBStep = (16 * RB) >> 4;
       prefetch_tensormap(mq); prefetch_tensormap(mk); prefetch_tensormap(mv); prefetch_tensormap(&map_do);
       mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
       tma_load_3d(sK, mk, kv_full, 0, k0, bh);
       tma_load_3d(sV, mv, kv_full, 0, k0, bh);
-      int it = 0;
-      for (int i = 0; i < nqt; ++i) {
-        if (tq[i] == 0) continue;
-        const int stage = it % kBwdStages;
-        if (!mbar_wait(&q_empty[stage], ((it / kBwdStages) & 1) ^ 1, p.status, 0x401)) break;
-        unsigned char* dst = sQ + size_t(stage) * 2 * Cfg::kTileBytes;
-        mbar_expect_tx(&q_full[stage], 2 * Cfg::kTileBytes);
-        tma_load_3d(dst, mq, &q_full[stage], 0, i * kBwdTile, bh);
-        tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[stage], 0, i * kBwdTile, bh);
-        ++it;
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0 && n_active > 0) {
-      constexpr uint32_t idesc_s = idesc_bf16(kBwdTile, kHalf, false, false);   // S^T, dP^T halves: M = 128 keys, N = 64 queries
-      constexpr uint32_t idesc_acc = idesc_bf16(kBwdTile, D, false, true);      // dV, dK: A from TMEM, B = dO / Q rows (N = D contiguous)
-      constexpr uint32_t idesc_dq = idesc_bf16(kBwdTile, D, true, true);        // dQ: A = dS (queries contiguous), B = K (D contiguous)
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), ds_addr = smem_u32(sDS);
-      bool ok = mbar_wait(kv_full, 0, p.status, 0x501);
-      tc_fence_after();
-
-      auto issue_sdp = [&](int it, int h) {   // S^T and dP^T of half h of active tile `it`
-        const uint32_t qs = q_addr + uint32_t(it % kBwdStages) * 2 * Cfg::kTileBytes + h * kHalf * RB;
-        const uint32_t dos = qs + Cfg::kTileBytes;
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_ss(tbase + kColBuf + h * 128, desc_k_major(k_addr + k * 32, RB), desc_k_major(qs + k * 32, RB), idesc_s, k > 0);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_ss(tbase + kColBuf + h * 128 + 64, desc_k_major(v_addr + k * 32, RB), desc_k_major(dos + k * 32, RB), idesc_s, k > 0);
-        umma_commit(&sdp_full[h]);
+      int next_q = 0;        // next query tile index to look at
+      Ring<kQStages> lr;     // stage the next load goes to
+      auto load_next = [&]() {   // issue the loads of the next active query tile
+        while (next_q < nqt && tq[next_q] == 0) ++next_q;
+        if (next_q >= nqt) return;
+        unsigned char* dst = sQ + size_t(lr.pos) * 2 * Cfg::kTileBytes;
+        mbar_expect_tx(&q_full[lr.pos], 2 * Cfg::kTileBytes);
+        tma_load_3d(dst, mq, &q_full[lr.pos], 0, next_q * kBwdTile, bh);
+        tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[lr.pos], 0, next_q * kBwdTile, bh);
+        ++next_q;
+        lr.advance();
       };
-      auto issue_acc = [&](int it, int h) {   // dV += P^T dO, dK += dS^T Q for half h
-        const uint32_t qs = q_addr + uint32_t(it % kBwdStages) * 2 * Cfg::kTileBytes + h * kHalf * RB;
-        const uint32_t dos = qs + Cfg::kTileBytes;
-#pragma unroll
-        for (int k = 0; k < kHalf / 16; ++k)
-          umma_ts(tbase + kColDV, tbase + kColBuf + h * 128 + k * 16, desc_mn_major(dos + k * 16 * RB, RB, 8 * RB), idesc_acc,
-                  it > 0 || h > 0 || k > 0);
-#pragma unroll
-        for (int k = 0; k < kHalf / 16; ++k)
-          umma_ts(tbase + kColDK, tbase + kColBuf + h * 128 + 64 + k * 16, desc_mn_major(qs + k * 16 * RB, RB, 8 * RB), idesc_acc,
-                  it > 0 || h > 0 || k > 0);
-      };
-
-      if (ok) ok = mbar_wait(&q_full[0], 0, p.status, 0x502);
-      tc_fence_after();
-      if (ok) { issue_sdp(0, 0); issue_sdp(0, 1); }
+      for (int s = 0; s < kQStages; ++s) load_next();
+      bool ok = mbar_wait(kv_full, 0, p.status, 0x521);
+      Ring<kNBuf> br;        // buffers of the two halves of the tile
+      Ring<kQStages> er;     // stage released by the tile
       for (int it = 0; it < n_active && ok; ++it) {
-        const bool has_next = it + 1 < n_active;
-        const int stage = it % kBwdStages;
-        // half 0
-        ok = mbar_wait(&pds_full[0], it & 1, p.status, 0x503);
+        ok = mbar_wait(&pds_full[br.pos], br.phase, p.status, 0x522);
+        br.advance();
+        if (ok) ok = mbar_wait(&pds_full[br.pos], br.phase, p.status, 0x523);
+        br.advance();
+        if (ok) ok = mbar_wait(&dq_empty[it & 1], ((it / 2) & 1) ^ 1, p.status, 0x524);   // buffer drained two tiles ago
         if (!ok) break;
+        MINTB_BTRACE_EV(30);
         tc_fence_after();
-        issue_acc(it, 0);
-        if (has_next) {
-          ok = mbar_wait(&q_full[(it + 1) % kBwdStages], ((it + 1) / kBwdStages) & 1, p.status, 0x504);
-          if (!ok) break;
-          tc_fence_after();
-          issue_sdp(it + 1, 0);
-        }
-        // half 1
-        ok = mbar_wait(&pds_full[1], it & 1, p.status, 0x505);
-        if (!ok) break;
-        tc_fence_after();
-        issue_acc(it, 1);
-        // dQ tile = dS K into buffer it & 1 (drained two tiles ago)
-        ok = mbar_wait(&dq_empty[it & 1], ((it / 2) & 1) ^ 1, p.status, 0x506);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t dsb = ds_addr + uint32_t(it & 1) * Cfg::kDsBytes;
+        const uint32_t a_lo = ds_lo + uint32_t(it & 1) * kDsU;
 #pragma unroll
         for (int k = 0; k < kBwdTile / 16; ++k)
-          umma_ss(tbase + kColDQ + (it & 1) * 64, desc_mn_major(dsb + k * 16 * 128, 128, Cfg::kDsBlock),
-                  desc_mn_major(k_addr + k * 16 * RB, RB, 8 * RB), idesc_dq, k > 0);
+          umma_ss(tbase + kColDQ + (it & 1) * kAcc, make_desc(kHiA, a_lo + k * kAStep), make_desc(kHiB, kb_lo + k * kBStep), idesc_dq, k > 0);
         umma_commit(&dq_full[it & 1]);
-        umma_commit(&q_empty[stage]);
-        if (has_next) issue_sdp(it + 1, 1);
+        MINTB_BTRACE_EV(31);
+        if (it + kQStages < n_active) {   // this tile's stage is released by its dV and dK streams
+          ok = mbar_wait(&q_empty[er.pos], er.phase, p.status, 0x525);
+          if (ok) load_next();
+        }
+        er.advance();
       }
-      if (ok) umma_commit(acc_full);
     }
   } else {
     // ---------------------------------------------------------------- compute warps (lane = key row)
-    // 16 warps work on ONE 64-query half at a time: thread = key row x 16 query columns (group g = 0..3).  The halves
-    // alternate between the two TMEM buffers, so while half `sub` is computed the tensor pipe fills the other buffer.
+    // 16 warps work on ONE 64-query half at a time: thread = key row x 16 query columns (group grp = 0..3).  The
+    // products run up to kNBuf halves ahead, and groups 2,3 start a fraction of a half later than groups 0,1 so that the
+    // exp2-heavy part of one pair of groups overlaps the TMEM traffic and barrier work of the other.
     // Everything here is elementwise: no exchange between threads.
-    const int cwp = warp - 2;                     // 0..15
+    const int cwp = warp - 4;                     // 0..15
     const int grp = cwp / 4;
     const int quarter = warp % 4;
     const int r = quarter * 32 + lane;            // key row in the tile == TMEM lane
     const int kj = k0 + r;
     const int krow = kj < p.T ? kj : p.T - 1;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    const uint32_t tBuf = tbase + lane_base + kColBuf + 16 * grp;   // + 128 sub: S^T columns of this thread; dP^T 64 further
+    const uint32_t tBuf = tbase + lane_base + kColBuf + 16 * grp;   // + 128 * buffer: S^T columns of this thread; dP^T 64 further
     const bool key_valid = kj < p.T && !((p.kpad[size_t(b) * p.TW + krow / 32] >> (krow % 32)) & 1u);
     const uint32_t* mrow = p.bitsT + (size_t(b) * p.T + krow) * p.TW;
     const uint32_t flip = path == 0 ? 0xffffu : 0u;   // keep-bit = mask bit XOR flip
@@ -361,13 +434,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     float* dq_bh = p.dq_acc[path] + size_t(bh) * p.T * D;
     bool ok = true;
     int it = 0;
+    Ring<kNBuf> br;
 
     auto drain_dq = [&](int jt, int qtile) -> bool {   // add dQ of active tile jt (query tile qtile) to HBM
       if (!mbar_wait(&dq_full[jt & 1], (jt / 2) & 1, p.status, 0x601)) return false;
       tc_fence_after();
       constexpr int NC = D / 4;   // columns per group
       uint32_t v[NC];
-      tmem_ld_n<NC>(tbase + lane_base + kColDQ + (jt & 1) * 64 + grp * NC, v);
+      tmem_ld_n<NC>(tbase + lane_base + kColDQ + (jt & 1) * kAcc + grp * NC, v);
       tmem_ld_wait();
       const int qi = qtile * kBwdTile + r;
       if (qi < p.T) {
@@ -386,24 +460,35 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     for (int i = 0; i < nqt && ok; ++i) {
       const uint8_t f = tq[i];
       if (f == 0) continue;
+      // the 32 mask bits that cover this thread's columns in both halves: half `sub` uses word 2 sub + grp / 2
+      uint32_t mw0 = 0, mw1 = 0;
+      if (f & 2) {
+        mw0 = mrow[4 * i + grp / 2];
+        mw1 = mrow[4 * i + 2 + grp / 2];
+      }
 #pragma unroll 1
       for (int sub = 0; sub < 2 && ok; ++sub) {
-        // statistics of this thread's 16 queries (L1/L2 hits, issued before the wait) and its 16 mask bits
+        // statistics of this thread's 16 queries (L1/L2 hits, issued before the wait)
         const float4* st = stats_bh + (i * kBwdTile + sub * kHalf + 16 * grp) / 2;
         float4 sq[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) sq[j] = __ldg(st + j);
         uint32_t keep = 0xffffu;
-        if (f & 2) keep = ((mrow[4 * i + 2 * sub + grp / 2] >> (16 * (grp & 1))) & 0xffffu) ^ flip;
+        if (f & 2) keep = (((sub ? mw1 : mw0) >> (16 * (grp & 1))) & 0xffffu) ^ flip;
         if (!key_valid) keep = 0u;
         const bool all = keep == 0xffffu;
-        ok = mbar_wait(&sdp_full[sub], it & 1, p.status, 0x602);
+        MINTB_BTRACE_EV(40);
+        ok = mbar_wait(&sdp_full[br.pos], br.phase, p.status, 0x602);
         if (!ok) break;
+        if (it == 0 && sub == 0 && grp >= 2) __nanosleep(kBwdStaggerNs);
+        MINTB_BTRACE_EV(41);
         tc_fence_after();
+        const uint32_t tS = tBuf + br.pos * 128;
         uint32_t sv[16], dpv[16];
-        tmem_ld16(tBuf + 128 * sub, sv);
-        tmem_ld16(tBuf + 128 * sub + 64, dpv);
+        tmem_ld16(tS, sv);
+        tmem_ld16(tS + 64, dpv);
         tmem_ld_wait();
+        MINTB_BTRACE_EV(42);
         uint32_t pp[8], dd[8];
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
@@ -421,19 +506,23 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           pp[j / 2] = bwd_pack(p0, p1);
           dd[j / 2] = bwd_pack(d0, d1);
         }
-        tmem_st8(tBuf + 128 * sub, pp);         // P^T over the S^T columns this thread has read
-        tmem_st8(tBuf + 128 * sub + 64, dd);    // dS^T likewise
+        tmem_st8(tS, pp);         // P^T over the S^T columns this thread has read
+        tmem_st8(tS + 64, dd);    // dS^T likewise
         // and dS into shared memory for the dQ product: 2 chunks of 8 queries in block `sub` of buffer it & 1
         unsigned char* ds_row = sDS + size_t(it & 1) * Cfg::kDsBytes + size_t(sub) * Cfg::kDsBlock;
         *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 2 * grp, 128)) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
         *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 2 * grp + 1, 128)) = make_uint4(dd[4], dd[5], dd[6], dd[7]);
+        MINTB_BTRACE_EV(43);
         tmem_st_wait();
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(&pds_full[sub]);
+        mbar_arrive(&pds_full[br.pos]);
+        MINTB_BTRACE_EV(44);
+        br.advance();
       }
       if (!ok) break;
       if (prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
+      MINTB_BTRACE_EV(45);
       prev_tile = i;
       ++it;
     }
@@ -487,6 +576,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       }
     }
   }
+  MINTB_BTRACE_EV(3);
+  MINTB_BTRACE_END;
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -494,6 +585,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     tmem_dealloc(tbase, kTmemAll);
   }
 }
+
+#ifdef MINTB_TRACE
+extern "C" __attribute__((visibility("default"))) int mintb_trace_read_bwd(unsigned long long* dst) {
+  return int(cudaMemcpyFromSymbol(dst, g_trace_bwd, sizeof(g_trace_bwd)));
+}
+#endif
 
 // ------------------------------------------------------------------------------------------------ host side
 static size_t bwd_rot_bytes(int B, int H, int T, int D) { return align256(size_t(B) * H * T * D * 2); }

@@ -130,14 +130,14 @@ def default_inv_freq(D: int, device) -> torch.Tensor:
 def rope_tables(T: int, D: int, device, inv_freq: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """cos/sin tables (T, D/2) fp32 on `device`, cached per (T, D, device, inv_freq contents)."""
     device = torch.device(device)
-    inv = default_inv_freq(D, device) if inv_freq is None else inv_freq.detach().to(device=device, dtype=torch.float32).contiguous()
-    if inv.numel() != D // 2:
-        raise ValueError(f"inv_freq must have D/2 = {D // 2} entries")
     key = (T, D, device.index, inv_freq.data_ptr() if inv_freq is not None else 0,
            inv_freq._version if inv_freq is not None else 0)
     hit = _rope_cache.get(key)
     if hit is not None:
         return hit
+    inv = default_inv_freq(D, device) if inv_freq is None else inv_freq.detach().to(device=device, dtype=torch.float32).contiguous()
+    if inv.numel() != D // 2:
+        raise ValueError(f"inv_freq must have D/2 = {D // 2} entries")
     cos = torch.empty(T, D // 2, dtype=torch.float32, device=device)
     sin = torch.empty_like(cos)
     with torch.cuda.device(device):
