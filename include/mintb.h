@@ -45,6 +45,7 @@ extern "C" {
 /* dtype of q/k/v/out/grads */
 #define MINTB_F32 0
 #define MINTB_BF16 1
+#define MINTB_E4M3 2 /* operands / outputs of the projection GEMMs only */
 
 /* flags */
 #define MINTB_FLAG_ROPE 1u         /* rotate Q and K of the SELF pathway (rotary_embedding.py:47-55)                */
@@ -136,6 +137,29 @@ MINTB_API int mintb_combine_bwd(const void* intra_logits, const void* inter_logi
                       const void* intra_values, const void* inter_values, const void* d_out, void* d_intra_logits,
                       void* d_inter_logits, void* d_intra_values, void* d_inter_values, void* workspace,
                       size_t workspace_bytes, int B, int H, int T, int D, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Projection GEMMs (tcgen05, bf16 or e4m3 operands, fp32 accumulate) with fused epilogues.
+ * x [M][K] and w [N][K] are K-contiguous (nn.Linear layout); K * element size must be a multiple of 16 bytes.
+ *
+ * mintb_linear_fwd: out[M][N] = act(alpha * x w^T + bias), act = erf-GELU if `gelu` (modules.py:16-23,323-335), stored as
+ * bf16 or, multiplied by out_scale and saturated to +-448, as e4m3.  Replaces nn.Linear / te.Linear forward for out_proj,
+ * fc1(+GELU), fc2 (attention.py:68, modules.py:326-334, mu_scaling/__init__.py:83-124).  For e4m3 operands alpha is the
+ * product of the two per-tensor dequantisation scales times any static output multiplier (alt/munit_scaling.py:22-34).
+ *
+ * mintb_qkv_fwd: the fused QKV projection of one pathway (attention.py:97-117, 304-323): x is (T,B,E) flattened to
+ * [T*B][E], w [3E][E] with rows ordered [Q;K;V]; q, k, v are written head-major (B,H,T,D) directly (no permute copy),
+ * the q third multiplied by q_scale, and the q and k thirds rotated by RoPE when the tables are given.
+ *
+ * mintb_quantize_e4m3: out[i] = saturate(x[i] * inv_scale) from bf16 (the per-tensor scaled cast of the FP8 path).
+ */
+MINTB_API int mintb_linear_fwd(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, int in_dtype,
+                               int bias_dtype, int out_dtype, int gelu, float alpha, float out_scale, void* stream,
+                               int* dev_status);
+MINTB_API int mintb_qkv_fwd(const void* x, const void* w, const void* bias, void* q, void* k, void* v, int T, int B, int H,
+                            int D, int in_dtype, int bias_dtype, float alpha, float q_scale, const float* rope_cos,
+                            const float* rope_sin, void* stream, int* dev_status);
+MINTB_API int mintb_quantize_e4m3(const void* x, void* out, size_t n, float inv_scale, void* stream);
 
 #ifdef __cplusplus
 }

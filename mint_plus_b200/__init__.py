@@ -11,11 +11,13 @@ from .attention import MultiHeadAttention, MultimerAttention
 from .modules_plus import (TransformerLayer_MINT_plus, VanillaFeedForward, build_mint_plus,
                            enable_fused_multi_pathway)
 from .rotary_embedding import RotaryEmbedding
+from .mu_scaling import Fp8Linear, apply_fp8_to_model, calibrate_fp8, unit_variance_init_
 
 __all__ = [
     "fused_multi_pathway_attention", "differentiable_multi_pathway_attention", "fused_multimer_combine",
     "differentiable_multimer_combine", "multimer_attention", "multimer_combine", "MaskMeta",
     "mask_meta_from_chain_ids", "mask_meta_from_mask", "rope_tables", "check_device_status",
     "MultiHeadAttention", "MultimerAttention", "TransformerLayer_MINT_plus", "VanillaFeedForward",
-    "build_mint_plus", "enable_fused_multi_pathway", "RotaryEmbedding",
+    "build_mint_plus", "enable_fused_multi_pathway", "RotaryEmbedding", "Fp8Linear", "apply_fp8_to_model", "calibrate_fp8",
+    "unit_variance_init_",
 ]

@@ -1,0 +1,437 @@
+// tcgen05 GEMM for the projections around the attention: out = epilogue(alpha * x W^T + bias).
+//
+//   x [M][K] and W [N][K] are both K-contiguous (nn.Linear layout), bf16 (kind::f16) or e4m3 (kind::f8f6f4), fp32 accumulate.
+//   Persistent CTAs walk 128 x 256 output tiles (N fastest, so the CTAs running together share rows of x in L2).
+//   warp 0  TMA producer: 128-byte-wide K slabs of x (128 rows) and W (256 rows) into a 4-stage ring, 128B swizzle
+//   warp 1  MMA issuer: four tcgen05.mma (M128 N256) per slab into one of two 256-column TMEM accumulators
+//   warps 2-5  epilogue: one thread per output row; 32 columns at a time: alpha, bias, erf-GELU, cast, store —
+//              row-major, or scattered head-major into (B,H,T,D) q/k/v with optional scale and RoPE (the QKV projection),
+//              while the MMA warp already fills the other accumulator.
+// Every mbarrier wait is bounded (see ptx.cuh).
+#include "common.cuh"
+#include "ptx.cuh"
+
+#include <cuda_fp8.h>
+
+namespace mintb {
+
+using namespace ptx;
+
+constexpr int kGM = 128, kGN = 256, kGStages = 4, kGThreads = 192;
+constexpr int kSlabBytes = 128;                       // bytes of K per stage and row (64 bf16 or 128 e4m3)
+constexpr int kABytes = kGM * kSlabBytes, kBBytes = kGN * kSlabBytes, kGStageBytes = kABytes + kBBytes;
+constexpr size_t kGemmSmem = 1024 + size_t(kGStages) * kGStageBytes + 256 + 2 * kGN * sizeof(float);
+
+enum GemmEpilogue : int { kEpiBias = 0, kEpiBiasGelu = 1, kEpiHeadMajor = 2 };
+
+struct GemmParams {
+  int M, N, K;                 // K in elements
+  int in_dtype;                // MINTB_BF16 or MINTB_E4M3
+  int out_dtype;               // MINTB_BF16 or MINTB_E4M3 (row-major epilogues)
+  int bias_dtype;              // MINTB_F32 or MINTB_BF16
+  int epilogue;
+  float alpha;                 // multiplies the accumulator (product of the operands' dequantisation scales)
+  float out_scale;             // multiplies the result before the cast to e4m3
+  const void* bias;            // [N] or null
+  void* out;                   // row-major [M][N]
+  // head-major scatter: row m = t * B + b, column n = which * E + h * D + d  ->  dst[which][((b * H + h) * T + t) * D + d]
+  __nv_bfloat16* qkv[3];
+  int B, T, H, D;
+  float q_scale;               // multiplies the q third (1 to leave the scaling to the attention kernel)
+  const float *rope_cos, *rope_sin;   // [T][D/2]; rotate the q and k thirds when non-null
+  int* status;
+};
+
+__device__ __forceinline__ float gelu_erf_f(float x) { return x * 0.5f * (1.f + erff(x * 0.70710678118654752f)); }
+
+__device__ __forceinline__ float load_bias(const void* bias, int dtype, int n) {
+  return dtype == MINTB_F32 ? static_cast<const float*>(bias)[n] : __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n]);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// EPI: epilogue kind; HD: head_dim of the head-major epilogue (0 otherwise)
+template <int EPI, int HD>
+__global__ void __launch_bounds__(kGThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* tail = smem + size_t(kGStages) * kGStageBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(tail);   // [kGStages]
+  uint64_t* empty = full + kGStages;                     // [kGStages]
+  uint64_t* acc_full = empty + kGStages;                 // [2]
+  uint64_t* acc_empty = acc_full + 2;                    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  float* s_bias = reinterpret_cast<float*>(tmem_slot + 2);   // [2][kGN] bias of the tile in flight (double buffered)
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int tiles_m = (p.M + kGM - 1) / kGM, tiles_n = (p.N + kGN - 1) / kGN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int elems_per_slab = p.in_dtype == MINTB_E4M3 ? 128 : 64;
+  const int n_slabs = (p.K + elems_per_slab - 1) / elems_per_slab;
+
+  if (tid == 0) {
+    for (int s = 0; s < kGStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 128); }
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const int m0 = (t / tiles_n) * kGM, n0 = (t % tiles_n) * kGN;
+        for (int kb = 0; kb < n_slabs; ++kb) {
+          ok = mbar_wait(&empty[stage], phase ^ 1, p.status, 0x701);
+          if (!ok) break;
+          unsigned char* a = smem + size_t(stage) * kGStageBytes;
+          mbar_expect_tx(&full[stage], kGStageBytes);
+          tma_load_2d(a, &map_a, &full[stage], kb * elems_per_slab, m0);
+          tma_load_2d(a + kABytes, &map_b, &full[stage], kb * elems_per_slab, n0);
+          if (++stage == kGStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const bool f8 = p.in_dtype == MINTB_E4M3;
+      const uint32_t idesc = f8 ? idesc_e4m3(kGM, kGN) : idesc_bf16(kGM, kGN, false, false);
+      constexpr uint32_t kHi = desc_hi32(8 * kSlabBytes, kSw128);
+      const uint32_t a_lo0 = desc_addr32(smem_u32(smem)) + desc_lbo32(16);
+      uint32_t stage = 0, phase = 0, ab = 0, ab_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        ok = mbar_wait(&acc_empty[ab], ab_phase ^ 1, p.status, 0x702);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d = tbase + ab * kGN;
+        for (int kb = 0; kb < n_slabs; ++kb) {
+          ok = mbar_wait(&full[stage], phase, p.status, 0x703);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + stage * (kGStageBytes >> 4), b_lo = a_lo + (kABytes >> 4);
+          if (f8) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_ss_f8(d, make_desc(kHi, a_lo + 2 * k), make_desc(kHi, b_lo + 2 * k), idesc, kb > 0 || k > 0);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_ss(d, make_desc(kHi, a_lo + 2 * k), make_desc(kHi, b_lo + 2 * k), idesc, kb > 0 || k > 0);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == kGStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&acc_full[ab]);
+        if (++ab == 2) { ab = 0; ab_phase ^= 1; }
+      }
+    }
+  } else {
+    const int quarter = warp % 4;
+    const int row = quarter * 32 + lane;
+    const int et = (warp - 2) * 32 + lane;   // thread index among the 128 epilogue threads
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    uint32_t ab = 0, ab_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      const int m0 = (t / tiles_n) * kGM, n0 = (t % tiles_n) * kGN;
+      const int m = m0 + row;
+      float* bias_t = s_bias + ab * kGN;
+      for (int j = et; j < kGN; j += 128) bias_t[j] = (p.bias != nullptr && n0 + j < p.N) ? load_bias(p.bias, p.bias_dtype, n0 + j) : 0.f;
+      named_bar_sync(1, 128);
+      ok = mbar_wait(&acc_full[ab], ab_phase, p.status, 0x704);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tacc = tbase + lane_base + ab * kGN;
+      int hm_b = 0, hm_t = 0;   // head-major: decode the row once
+      if constexpr (EPI == kEpiHeadMajor) { hm_t = m / p.B; hm_b = m % p.B; }
+#pragma unroll 1
+      for (int c0 = 0; c0 < kGN; c0 += 32) {
+        if (n0 + c0 >= p.N) break;   // uniform
+        uint32_t r[32];
+        tmem_ld32(tacc + c0, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = fmaf(__uint_as_float(r[j]), p.alpha, bias_t[c0 + j]);
+        if constexpr (EPI == kEpiHeadMajor) {
+          // column n = which * E + h * HD + d.  E is a multiple of 32 (of 64 when HD = 64), so a 32-column chunk lies in one
+          // third and covers whole heads (HD = 16: two, HD = 32: one) or one half of a head (HD = 64).
+          const int E = p.H * HD;
+          const int n = n0 + c0;
+          const int which = n / E, e = n % E;
+          const bool rot = p.rope_cos != nullptr && which < 2;
+          if (which == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= p.q_scale;
+          }
+          if constexpr (HD <= 32) {
+            constexpr int hd = HD / 2;
+            if (rot) {
+#pragma unroll
+              for (int h0 = 0; h0 < 32; h0 += HD) {
+#pragma unroll
+                for (int j = 0; j < hd; ++j) {
+                  const float cs = p.rope_cos[size_t(hm_t) * hd + j], sn = p.rope_sin[size_t(hm_t) * hd + j];
+                  const float a = v[h0 + j], bb = v[h0 + j + hd];
+                  v[h0 + j] = a * cs - bb * sn;
+                  v[h0 + j + hd] = bb * cs + a * sn;
+                }
+              }
+            }
+            if (m < p.M) {
+#pragma unroll
+              for (int h0 = 0; h0 < 32; h0 += HD) {
+                __nv_bfloat16* dst = p.qkv[which] + ((size_t(hm_b) * p.H + (e + h0) / HD) * p.T + hm_t) * HD;
+#pragma unroll
+                for (int j = 0; j < HD; j += 8)
+                  *reinterpret_cast<uint4*>(dst + j) =
+                      make_uint4(pack_bf16x2(v[h0 + j], v[h0 + j + 1]), pack_bf16x2(v[h0 + j + 2], v[h0 + j + 3]),
+                                 pack_bf16x2(v[h0 + j + 4], v[h0 + j + 5]), pack_bf16x2(v[h0 + j + 6], v[h0 + j + 7]));
+              }
+            }
+          } else {
+            // HD = 64: this chunk is the lower or the upper half of one head; the rotation needs the partner half,
+            // which is read from TMEM as well (same tile: pairs of chunks are 64-column aligned)
+            const bool upper = (e % 64) != 0;
+            if (rot) {
+              const int c2 = upper ? c0 - 32 : c0 + 32;
+              uint32_t r2[32];
+              tmem_ld32(tacc + c2, r2);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float x = fmaf(__uint_as_float(r2[j]), p.alpha, bias_t[c2 + j]);
+                if (which == 0) x *= p.q_scale;
+                const float cs = p.rope_cos[size_t(hm_t) * 32 + j], sn = p.rope_sin[size_t(hm_t) * 32 + j];
+                v[j] = upper ? v[j] * cs + x * sn : v[j] * cs - x * sn;
+              }
+            }
+            if (m < p.M) {
+              __nv_bfloat16* dst = p.qkv[which] + ((size_t(hm_b) * p.H + e / 64) * p.T + hm_t) * 64 + (upper ? 32 : 0);
+#pragma unroll
+              for (int j = 0; j < 32; j += 8)
+                *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                                                                pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+            }
+          }
+        } else {
+          if constexpr (EPI == kEpiBiasGelu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_erf_f(v[j]);
+          }
+          const int n = n0 + c0;
+          if (m < p.M) {
+            if (p.out_dtype == MINTB_BF16) {
+              __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + size_t(m) * p.N + n;
+              if (n + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8)
+                  *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                                                                  pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (n + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+              }
+            } else {
+              __nv_fp8_storage_t* dst = static_cast<__nv_fp8_storage_t*>(p.out) + size_t(m) * p.N + n;
+              if (n + 32 <= p.N && (p.N & 15) == 0) {   // 16-byte stores need 16-byte aligned rows
+                uint4 o[2];
+                __nv_fp8_storage_t* op = reinterpret_cast<__nv_fp8_storage_t*>(o);
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  op[j] = __nv_cvt_float_to_fp8(fminf(fmaxf(v[j] * p.out_scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+                *reinterpret_cast<uint4*>(dst) = o[0];
+                *reinterpret_cast<uint4*>(dst + 16) = o[1];
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (n + j < p.N)
+                    dst[j] = __nv_cvt_float_to_fp8(fminf(fmaxf(v[j] * p.out_scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[ab]);
+      if (++ab == 2) { ab = 0; ab_phase ^= 1; }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tbase, 512);
+  }
+}
+
+// x (bf16) -> e4m3 with a per-tensor scale: q = sat(x * inv_scale); 16 elements per thread.
+__global__ void __launch_bounds__(256) quantize_e4m3_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_storage_t* __restrict__ out,
+                                                            size_t n, float inv_scale) {
+  const size_t i = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) * 16;
+  if (i >= n) return;
+  if (i + 16 <= n) {
+    const uint4 a = *reinterpret_cast<const uint4*>(x + i), b = *reinterpret_cast<const uint4*>(x + i + 8);
+    const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(&a);
+    const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(&b);
+    uint4 o;
+    __nv_fp8_storage_t* op = reinterpret_cast<__nv_fp8_storage_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      op[j] = __nv_cvt_float_to_fp8(fminf(fmaxf(__bfloat162float(ap[j]) * inv_scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+      op[8 + j] = __nv_cvt_float_to_fp8(fminf(fmaxf(__bfloat162float(bp[j]) * inv_scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+    }
+    *reinterpret_cast<uint4*>(out + i) = o;
+  } else {
+    for (size_t j = i; j < n; ++j)
+      out[j] = __nv_cvt_float_to_fp8(fminf(fmaxf(__bfloat162float(x[j]) * inv_scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn gemm_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// [rows][K] matrix, K contiguous; box = (128 bytes of K, box_rows); out-of-range parts read as zero.
+static bool gemm_map(CUtensorMap* m, const void* ptr, int rows, int K, int dtype, int box_rows) {
+  EncodeTiledFn fn = gemm_encode_fn();
+  if (fn == nullptr) return false;
+  const int esz = dtype == MINTB_E4M3 ? 1 : 2;
+  cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(K) * esz};
+  cuuint32_t box[2] = {cuuint32_t(kSlabBytes / esz), cuuint32_t(box_rows)};
+  cuuint32_t es[2] = {1, 1};
+  return fn(m, dtype == MINTB_E4M3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+            strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_gemm(const GemmParams& p, const void* x, const void* w, cudaStream_t stream) {
+  CUtensorMap ma, mb;
+  if (!gemm_map(&ma, x, p.M, p.K, p.in_dtype, kGM) || !gemm_map(&mb, w, p.N, p.K, p.in_dtype, kGN)) {
+    set_error("mintb gemm: cuTensorMapEncodeTiled failed");
+    return MINTB_ECUDA;
+  }
+  void (*kern)(CUtensorMap, CUtensorMap, GemmParams) = nullptr;
+  if (p.epilogue == kEpiBias) kern = gemm_tc_kernel<kEpiBias, 0>;
+  else if (p.epilogue == kEpiBiasGelu) kern = gemm_tc_kernel<kEpiBiasGelu, 0>;
+  else if (p.D == 16) kern = gemm_tc_kernel<kEpiHeadMajor, 16>;
+  else if (p.D == 32) kern = gemm_tc_kernel<kEpiHeadMajor, 32>;
+  else kern = gemm_tc_kernel<kEpiHeadMajor, 64>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kGemmSmem));
+  if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = ((p.M + kGM - 1) / kGM) * ((p.N + kGN - 1) / kGN);
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, kGThreads, kGemmSmem, stream>>>(ma, mb, p);
+  count_launches(1);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("gemm launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
+  return MINTB_OK;
+}
+
+cudaError_t launch_quantize_e4m3(const void* x, void* out, size_t n, float inv_scale, cudaStream_t s) {
+  const size_t threads = (n + 15) / 16;
+  quantize_e4m3_kernel<<<unsigned((threads + 255) / 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                     static_cast<__nv_fp8_storage_t*>(out), n, inv_scale);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
+}  // namespace mintb
+
+using namespace mintb;
+
+static int check_gemm(const char* who, const void* x, const void* w, int M, int N, int K, int in_dtype) {
+  if (x == nullptr || w == nullptr || M <= 0 || N <= 0 || K <= 0) {
+    set_error("%s: x, w and positive M, N, K are required", who);
+    return MINTB_EINVAL;
+  }
+  if (in_dtype != MINTB_BF16 && in_dtype != MINTB_E4M3) {
+    set_error("%s: operands must be bf16 or e4m3", who);
+    return MINTB_EUNSUPPORTED;
+  }
+  const int esz = in_dtype == MINTB_E4M3 ? 1 : 2;
+  if ((size_t(K) * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) {
+    set_error("%s: rows of x and w must be 16-byte aligned (K * element size a multiple of 16)", who);
+    return MINTB_EINVAL;
+  }
+  return MINTB_OK;
+}
+
+extern "C" int mintb_linear_fwd(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, int in_dtype,
+                                int bias_dtype, int out_dtype, int gelu, float alpha, float out_scale, void* stream,
+                                int* dev_status) {
+  int rc = check_gemm("mintb_linear_fwd", x, w, M, N, K, in_dtype);
+  if (rc != MINTB_OK) return rc;
+  if (out == nullptr || (out_dtype != MINTB_BF16 && out_dtype != MINTB_E4M3) || (reinterpret_cast<uintptr_t>(out) & 15) ||
+      (out_dtype == MINTB_BF16 && N % 8 != 0)) {
+    set_error("mintb_linear_fwd: out must be a 16-byte aligned bf16 (N a multiple of 8) or e4m3 buffer");
+    return MINTB_EINVAL;
+  }
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.in_dtype = in_dtype; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype;
+  p.epilogue = gelu ? kEpiBiasGelu : kEpiBias;
+  p.alpha = alpha; p.out_scale = out_scale; p.bias = bias; p.out = out; p.status = dev_status;
+  return launch_gemm(p, x, w, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mintb_qkv_fwd(const void* x, const void* w, const void* bias, void* q, void* k, void* v, int T, int B, int H, int D,
+                             int in_dtype, int bias_dtype, float alpha, float q_scale, const float* rope_cos,
+                             const float* rope_sin, void* stream, int* dev_status) {
+  const int E = H * D;
+  int rc = check_gemm("mintb_qkv_fwd", x, w, T * B, 3 * E, E, in_dtype);
+  if (rc != MINTB_OK) return rc;
+  if (q == nullptr || k == nullptr || v == nullptr || (D != 16 && D != 32 && D != 64) || T <= 0 || B <= 0 || H <= 0 ||
+      E % (D == 64 ? 64 : 32) != 0) {
+    set_error("mintb_qkv_fwd: q, k, v, head_dim 16, 32 or 64 and H * D a multiple of 32 (64 at head_dim 64) are required");
+    return MINTB_EINVAL;
+  }
+  if ((rope_cos == nullptr) != (rope_sin == nullptr)) {
+    set_error("mintb_qkv_fwd: give both RoPE tables or neither");
+    return MINTB_EINVAL;
+  }
+  GemmParams p{};
+  p.M = T * B; p.N = 3 * E; p.K = E; p.in_dtype = in_dtype; p.out_dtype = MINTB_BF16; p.bias_dtype = bias_dtype;
+  p.epilogue = kEpiHeadMajor;
+  p.alpha = alpha; p.out_scale = 1.f; p.bias = bias; p.out = nullptr;
+  p.qkv[0] = static_cast<__nv_bfloat16*>(q); p.qkv[1] = static_cast<__nv_bfloat16*>(k); p.qkv[2] = static_cast<__nv_bfloat16*>(v);
+  p.B = B; p.T = T; p.H = H; p.D = D; p.q_scale = q_scale; p.rope_cos = rope_cos; p.rope_sin = rope_sin;
+  p.status = dev_status;
+  return launch_gemm(p, x, w, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mintb_quantize_e4m3(const void* x, void* out, size_t n, float inv_scale, void* stream) {
+  if (x == nullptr || out == nullptr || n == 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) {
+    set_error("mintb_quantize_e4m3: 16-byte aligned x and out and n > 0 are required");
+    return MINTB_EINVAL;
+  }
+  cudaError_t e = launch_quantize_e4m3(x, out, n, inv_scale, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) { set_error("quantize launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
+  return MINTB_OK;
+}

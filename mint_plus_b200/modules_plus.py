@@ -18,6 +18,14 @@ from .attention import MultiHeadAttention, MultimerAttention
 from .kernels import fused_multimer_combine
 
 
+def _linear(mod, x, gelu=False):
+    """A projection module applied to a bf16 CUDA tensor: Fp8Linear on the e4m3 GEMM, nn.Linear on the bf16 GEMM."""
+    from .mu_scaling import Fp8Linear
+    if isinstance(mod, Fp8Linear):
+        return mod(x, gelu=gelu)
+    return ops.linear(x, mod.weight, mod.bias, gelu=gelu)
+
+
 def gelu_erf(x):
     return x * 0.5 * (1.0 + torch.erf(x / math.sqrt(2.0)))
 
@@ -30,6 +38,10 @@ class VanillaFeedForward(nn.Module):
         self.use_erf_gelu = use_erf_gelu
 
     def forward(self, x):
+        # bf16 on the GPU: both projections run on the tcgen05 GEMM, bias and erf-GELU in its epilogue
+        # (F.gelu's default is the exact erf form too, so both flags give the same function)
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            return _linear(self.fc2, _linear(self.fc1, x, gelu=True))
         x = gelu_erf(self.fc1(x)) if self.use_erf_gelu else F.gelu(self.fc1(x))
         return self.fc2(x)
 
@@ -74,16 +86,28 @@ class TransformerLayer_MINT_plus(nn.Module):
         """x (T,B,E) -> (T,B,E): both QKV projections, fused two-pathway attention, output projection."""
         T, B, E = x.shape
         sa, ma = self.self_attn, self.multimer_attn
-        q_s, k_s, v_s = sa.project_qkv_4d(x)
-        q_c, k_c, v_c = ma.project_qkv_4d(x)
         if chain_ids is not None and chain_mask is None:
             mask_kw = dict(meta=_cached_ids_meta(chain_ids, padding_mask))
         else:
             mask_kw = dict(chain_mask=chain_mask, key_padding_mask=padding_mask)
         rope = sa.rot_emb is not None
-        attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=rope,
-                                          inv_freq=sa.rot_emb.inv_freq if rope else None, scale=sa.scaling, **mask_kw)
+        fast = (x.is_cuda and x.dtype == torch.bfloat16 and isinstance(getattr(sa, "fused_qkv", None), nn.Linear)
+                and isinstance(ma.fused_qkv, nn.Linear))
+        if fast:
+            # bf16 on the GPU: the QKV GEMMs write q, k, v head-major and rotate the self pathway in their epilogue, so the
+            # attention kernel gets ready-made operands (no permute copies, no rotation pass)
+            tabs = ops.rope_tables(T, sa.head_dim, x.device, sa.rot_emb.inv_freq)[:2] if rope else None
+            q_s, k_s, v_s = ops.qkv_project(x, sa.fused_qkv.weight, sa.fused_qkv.bias, sa.num_heads, rope=tabs)
+            q_c, k_c, v_c = ops.qkv_project(x, ma.fused_qkv.weight, ma.fused_qkv.bias, ma.num_heads)
+            attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=False, scale=sa.scaling, **mask_kw)
+        else:
+            q_s, k_s, v_s = sa.project_qkv_4d(x)
+            q_c, k_c, v_c = ma.project_qkv_4d(x)
+            attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=rope,
+                                              inv_freq=sa.rot_emb.inv_freq if rope else None, scale=sa.scaling, **mask_kw)
         attn_out = attn_out.permute(2, 0, 1, 3).reshape(T, B, E)
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            return _linear(sa.out_proj, attn_out), None
         return sa.out_proj(attn_out), None
 
     # the PyTorch-named entry of the reference resolves to the same fused path

@@ -268,3 +268,149 @@ def multimer_combine(intra_logits, inter_logits, chain_mask, intra_values, inter
     m = chain_mask.contiguous().view(torch.uint8) if chain_mask.dtype == torch.bool else chain_mask.to(torch.uint8).contiguous()
     return _CombineFn.apply(intra_logits.contiguous(), inter_logits.contiguous(), m, intra_values.contiguous(),
                             inter_values.contiguous())
+
+
+# ----------------------------------------------------------------------------------------------- projection GEMMs
+_BIAS_DT = {torch.float32: L.F32, torch.bfloat16: L.BF16}
+
+
+def _bias_arg(bias):
+    if bias is None:
+        return None, L.F32
+    if bias.dtype not in _BIAS_DT:
+        raise TypeError("bias must be float32 or bfloat16")
+    return bias.contiguous(), _BIAS_DT[bias.dtype]
+
+
+def gemm_bf16(x2d: torch.Tensor, w: torch.Tensor, bias=None, gelu: bool = False) -> torch.Tensor:
+    """act(x2d @ w.T + bias) on the tcgen05 GEMM: x2d [M,K] bf16, w [N,K] bf16 -> [M,N] bf16 (no autograd)."""
+    _require_cuda(x2d, w, bias)
+    M, K = x2d.shape
+    N = w.shape[0]
+    b, bdt = _bias_arg(bias)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x2d.device)
+    with torch.cuda.device(x2d.device):
+        rc = L.lib().mintb_linear_fwd(_ptr(x2d), _ptr(w), _ptr(b), _ptr(out), M, N, K, L.BF16, bdt, L.BF16, int(gelu), 1.0, 1.0,
+                                      _stream(), _ptr(_dev_status(x2d.device)))
+    L.check(rc, "mintb_linear_fwd")
+    return out
+
+
+def quantize_e4m3(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """Per-tensor scaled cast bf16 -> e4m3: saturate(x / scale) (no autograd)."""
+    _require_cuda(x)
+    x = x.contiguous()
+    out = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    with torch.cuda.device(x.device):
+        L.check(L.lib().mintb_quantize_e4m3(_ptr(x), _ptr(out), x.numel(), 1.0 / scale, _stream()), "mintb_quantize_e4m3")
+    return out
+
+
+def gemm_e4m3(xq: torch.Tensor, wq: torch.Tensor, alpha: float, bias=None, gelu: bool = False,
+              out_e4m3_scale: Optional[float] = None) -> torch.Tensor:
+    """act(alpha * xq @ wq.T + bias) with e4m3 operands; bf16 result, or e4m3 (result / out_e4m3_scale, saturated)."""
+    _require_cuda(xq, wq, bias)
+    M, K = xq.shape
+    N = wq.shape[0]
+    b, bdt = _bias_arg(bias)
+    to_f8 = out_e4m3_scale is not None
+    out = torch.empty(M, N, dtype=torch.float8_e4m3fn if to_f8 else torch.bfloat16, device=xq.device)
+    with torch.cuda.device(xq.device):
+        rc = L.lib().mintb_linear_fwd(_ptr(xq), _ptr(wq), _ptr(b), _ptr(out), M, N, K, L.E4M3, bdt, L.E4M3 if to_f8 else L.BF16,
+                                      int(gelu), float(alpha), 1.0 / out_e4m3_scale if to_f8 else 1.0, _stream(),
+                                      _ptr(_dev_status(xq.device)))
+    L.check(rc, "mintb_linear_fwd")
+    return out
+
+
+def _gelu_erf_grad(z: torch.Tensor) -> torch.Tensor:
+    zf = z.float()
+    return 0.5 * (1.0 + torch.erf(zf * 0.7071067811865476)) + zf * torch.exp(-0.5 * zf * zf) * 0.3989422804014327
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = act(x W^T + b) with the forward on the tcgen05 GEMM.  The backward products (dgrad, wgrad) are plain library
+    GEMMs; with GELU the pre-activation is recomputed rather than stored."""
+
+    @staticmethod
+    def forward(ctx, x2d, w, bias, gelu):
+        wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        ctx.save_for_backward(x2d, w, bias)
+        ctx.gelu = gelu
+        return gemm_bf16(x2d, wb.contiguous(), bias, gelu)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2d, w, bias = ctx.saved_tensors
+        wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        dz = dy
+        if ctx.gelu:
+            z = gemm_bf16(x2d, wb.contiguous(), bias, False)
+            dz = (dy.float() * _gelu_erf_grad(z)).to(torch.bfloat16)
+        dx = dz @ wb if ctx.needs_input_grad[0] else None
+        dw = (dz.t() @ x2d).to(w.dtype) if ctx.needs_input_grad[1] else None
+        db = dz.float().sum(0).to(bias.dtype) if (bias is not None and ctx.needs_input_grad[2]) else None
+        return dx, dw, db, None
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, gelu: bool = False) -> torch.Tensor:
+    """nn.Linear forward (optionally followed by erf-GELU) for bf16 CUDA activations; differentiable."""
+    if x.dtype != torch.bfloat16:
+        raise TypeError("ops.linear takes bfloat16 activations")
+    x2d = x.reshape(-1, x.shape[-1]).contiguous()
+    y = _LinearFn.apply(x2d, weight, bias, gelu)
+    return y.view(*x.shape[:-1], weight.shape[0])
+
+
+def _rope_rotate_torch(t, cos, sin, inverse=False):
+    """(B,H,T,D) rotation with (T, D/2) tables; inverse applies the transpose."""
+    h = t.shape[-1] // 2
+    lo, hi = t[..., :h].float(), t[..., h:].float()
+    s = -sin if inverse else sin
+    return torch.cat((lo * cos - hi * s, hi * cos + lo * s), dim=-1).to(t.dtype)
+
+
+class _QkvFn(torch.autograd.Function):
+    """Fused QKV projection of one pathway with head-major outputs (and RoPE on q, k when tables are given)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, H, cos, sin, q_scale):
+        T, B, E = x.shape
+        D = E // H
+        wb = (w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)).contiguous()
+        b, bdt = _bias_arg(bias)
+        x2d = x.reshape(T * B, E).contiguous()
+        q, k, v = (torch.empty(B, H, T, D, dtype=torch.bfloat16, device=x.device) for _ in range(3))
+        with torch.cuda.device(x.device):
+            rc = L.lib().mintb_qkv_fwd(_ptr(x2d), _ptr(wb), _ptr(b), _ptr(q), _ptr(k), _ptr(v), T, B, H, D, L.BF16, bdt, 1.0,
+                                       float(q_scale), _ptr(cos), _ptr(sin), _stream(), _ptr(_dev_status(x.device)))
+        L.check(rc, "mintb_qkv_fwd")
+        ctx.save_for_backward(x2d, w, bias, cos, sin)
+        ctx.dims = (T, B, H, D, q_scale)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        x2d, w, bias, cos, sin = ctx.saved_tensors
+        T, B, H, D, q_scale = ctx.dims
+        if cos is not None:
+            dq, dk = _rope_rotate_torch(dq, cos, sin, True), _rope_rotate_torch(dk, cos, sin, True)
+        if q_scale != 1.0:
+            dq = dq * q_scale
+        # (B,H,T,D) x3 -> [T*B, 3E]
+        g = torch.cat([t.permute(2, 0, 1, 3).reshape(T * B, H * D) for t in (dq, dk, dv)], dim=1).to(torch.bfloat16)
+        wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        dx = (g @ wb).view(T, B, H * D) if ctx.needs_input_grad[0] else None
+        dw = (g.t() @ x2d).to(w.dtype) if ctx.needs_input_grad[1] else None
+        db = g.float().sum(0).to(bias.dtype) if (bias is not None and ctx.needs_input_grad[2]) else None
+        return dx, dw, db, None, None, None, None
+
+
+def qkv_project(x: torch.Tensor, weight: torch.Tensor, bias, num_heads: int, rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                q_scale: float = 1.0):
+    """x (T,B,E) bf16, weight (3E,E) with rows [Q;K;V] -> q, k, v (B,H,T,D) bf16, written head-major by the GEMM epilogue
+    (attention.py:97-117, 304-323 of the reference without the three permute copies).  `rope` = (cos, sin) tables rotates q, k."""
+    if x.dtype != torch.bfloat16 or x.dim() != 3:
+        raise TypeError("qkv_project takes a (T, B, E) bfloat16 tensor")
+    cos, sin = rope if rope is not None else (None, None)
+    return _QkvFn.apply(x, weight, bias, num_heads, cos, sin, q_scale)

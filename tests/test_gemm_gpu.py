@@ -1,0 +1,165 @@
+"""The tcgen05 projection GEMMs (bf16 and e4m3, fused epilogues), called through the C ABI, against CPU restatements."""
+import pytest
+import torch
+
+from oracle import multimer_attention as O
+
+pytestmark = pytest.mark.gpu
+
+import mint_plus_b200 as M  # noqa: E402
+from mint_plus_b200 import ops  # noqa: E402
+
+DEV = "cuda"
+
+
+def _ref_linear(x, w, b, gelu):
+    y = x.float() @ w.float().t()
+    if b is not None:
+        y = y + b.float()
+    return O.gelu_erf(y) if gelu else y
+
+
+# (M, N, K): multiples of the 128 x 256 tile, ragged edges in every dimension, K shorter and longer than one 64-element slab
+SHAPES = [(128, 256, 64), (300, 320, 320), (130, 264, 200), (1024, 3840, 1280), (77, 8, 8), (512, 1280, 5120)]
+
+
+@pytest.mark.parametrize("gelu", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_bf16_linear_matches_fp32_reference(shape, gelu):
+    Mr, N, K = shape
+    g = torch.Generator().manual_seed(Mr + N + K)
+    x = torch.randn(Mr, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(N, generator=g)
+    want = _ref_linear(x, w, b, gelu)
+    got = ops.gemm_bf16(x.to(DEV), w.to(DEV), b.to(DEV), gelu).float().cpu()
+    ops.check_device_status()
+    # fp32 accumulation of bf16 products, result rounded to bf16: relative error ~2^-9 of the magnitude
+    torch.testing.assert_close(got, want, rtol=1e-2, atol=1e-2)
+    got_nb = ops.gemm_bf16(x.to(DEV), w.to(DEV), None, gelu).float().cpu()
+    torch.testing.assert_close(got_nb, _ref_linear(x, w, None, gelu), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 256), (300, 320, 320), (1024, 1280, 1280), (100, 72, 144)])
+def test_e4m3_linear_matches_cpu_restatement(shape):
+    Mr, N, K = shape
+    g = torch.Generator().manual_seed(7 * Mr + N)
+    x = torch.randn(Mr, K, generator=g).bfloat16()
+    w = torch.randn(N, K, generator=g).bfloat16()
+    b = torch.randn(N, generator=g)
+    xs, ws = 1.0, float(w.float().abs().amax()) / 448.0
+    # CPU restatement on the scaled tensors (alt/munit_scaling.py:22-34): clamp, e4m3 cast, fp32 matmul, scale back, bias
+    want = O.fp8_e4m3_linear(x.float() / xs, w.float() / ws, None, out_scale=xs * ws) + b
+    xq = ops.quantize_e4m3(x.to(DEV), xs)
+    wq = ops.quantize_e4m3(w.to(DEV), ws)
+    # the casts themselves are exact restatements
+    assert torch.equal(xq.float().cpu(), (x.float() / xs).clamp(-448, 448).to(torch.float8_e4m3fn).float())
+    assert torch.equal(wq.float().cpu(), (w.float() / ws).clamp(-448, 448).to(torch.float8_e4m3fn).float())
+    got = ops.gemm_e4m3(xq, wq, xs * ws, b.to(DEV)).float().cpu()
+    ops.check_device_status()
+    # equal up to fp32 summation order and the final bf16 rounding
+    torch.testing.assert_close(got, want, rtol=8e-3, atol=8e-3 * float(want.abs().max()) / 16)
+    # e4m3 output with its own scale (the cast a following FP8 GEMM would consume)
+    out_scale = float(want.abs().amax()) / 448.0
+    got8 = ops.gemm_e4m3(xq, wq, xs * ws, b.to(DEV), out_e4m3_scale=out_scale).float().cpu() * out_scale
+    assert (got8 - want).abs().max().item() <= 0.07 * float(want.abs().max())     # e4m3 has 3 mantissa bits
+
+
+@pytest.mark.parametrize("rope", [False, True])
+@pytest.mark.parametrize("dims", [(50, 3, 20, 16), (96, 2, 20, 32), (130, 2, 4, 64), (33, 1, 10, 32)])
+def test_qkv_projection_head_major_with_rope(dims, rope):
+    T, B, H, D = dims
+    E = H * D
+    g = torch.Generator().manual_seed(T + D)
+    x = torch.randn(T, B, E, generator=g).bfloat16()
+    w = (torch.randn(3 * E, E, generator=g) / E ** 0.5).bfloat16()
+    b = (0.1 * torch.randn(3 * E, generator=g))
+    q, k, v = O.project_qkv_4d(x.float(), w.float(), b, H)
+    if rope:
+        q, k = O.apply_rope(q), O.apply_rope(k)
+    tabs = ops.rope_tables(T, D, torch.device(DEV))[:2] if rope else None
+    gq, gk, gv = ops.qkv_project(x.to(DEV), w.to(DEV), b.to(DEV), H, rope=tabs)
+    ops.check_device_status()
+    for got, want in ((gq, q), (gk, k), (gv, v)):
+        assert got.shape == (B, H, T, D) and got.is_contiguous()
+        torch.testing.assert_close(got.float().cpu(), want, rtol=1e-2, atol=2e-2)
+
+
+def test_linear_and_qkv_gradients_match_autograd():
+    g = torch.Generator().manual_seed(3)
+    T, B, H, D = 40, 2, 4, 32
+    E = H * D
+    x = torch.randn(T, B, E, generator=g).bfloat16()
+    w = (torch.randn(3 * E, E, generator=g) / E ** 0.5).bfloat16()
+    b = 0.1 * torch.randn(3 * E, generator=g)
+    go = [torch.randn(B, H, T, D, generator=g).bfloat16() for _ in range(3)]
+    # reference through the oracle projection + rope in fp32
+    xr, wr, br = x.float().requires_grad_(True), w.float().requires_grad_(True), b.clone().requires_grad_(True)
+    q, k, v = O.project_qkv_4d(xr, wr, br, H)
+    q, k = O.apply_rope(q), O.apply_rope(k)
+    torch.autograd.backward([q, k, v], [t.float() for t in go])
+    xd, wd, bd = x.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True), b.to(DEV).requires_grad_(True)
+    tabs = ops.rope_tables(T, D, torch.device(DEV))[:2]
+    outs = ops.qkv_project(xd, wd, bd, H, rope=tabs)
+    torch.autograd.backward(list(outs), [t.to(DEV) for t in go])
+    for got, want in ((xd.grad, xr.grad), (wd.grad, wr.grad), (bd.grad, br.grad)):
+        err = (got.float().cpu() - want).abs().max().item()
+        assert err <= 3e-2 * want.abs().max().item() + 1e-3
+    # linear + GELU
+    xl = torch.randn(70, E, generator=g).bfloat16()
+    wl = (torch.randn(2 * E, E, generator=g) / E ** 0.5).bfloat16()
+    bl = 0.1 * torch.randn(2 * E, generator=g)
+    gy = torch.randn(70, 2 * E, generator=g).bfloat16()
+    xr, wr, br = xl.float().requires_grad_(True), wl.float().requires_grad_(True), bl.clone().requires_grad_(True)
+    _ref_linear(xr, wr, br, True).backward(gy.float())
+    xd, wd, bd = xl.to(DEV).requires_grad_(True), wl.to(DEV).requires_grad_(True), bl.to(DEV).requires_grad_(True)
+    ops.linear(xd, wd, bd, gelu=True).backward(gy.to(DEV))
+    for got, want in ((xd.grad, xr.grad), (wd.grad, wr.grad), (bd.grad, br.grad)):
+        err = (got.float().cpu() - want).abs().max().item()
+        assert err <= 3e-2 * want.abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_bf16_layer_forward_backward_against_oracle_composition(fp8):
+    """TransformerLayer_MINT_plus in bf16 on the GPU (GEMM epilogues + fused attention; e4m3 projections when `fp8`)
+    against the same layer evaluated in fp32 with the oracle attention on the CPU."""
+    torch.manual_seed(11)
+    E, H, T, B = 128, 4, 150, 2
+    layer = M.TransformerLayer_MINT_plus(E, 4 * E, H, use_multimer=True, use_erf_gelu=True).float()
+    for p in layer.parameters():                      # bf16-representable weights so both sides see the same numbers
+        p.data = p.data.bfloat16().float()
+    x = torch.randn(T, B, E).bfloat16().float()
+    cid = torch.zeros(B, T, dtype=torch.int32); cid[:, 70:] = 1
+    pad = torch.zeros(B, T, dtype=torch.bool); pad[1, -13:] = True
+    mask = O.chain_mask_from_ids(cid)
+
+    def cpu_forward(xx):
+        h = layer.self_attn_layer_norm(xx)
+        qs, ks, vs = layer.self_attn.project_qkv_4d(h)
+        qc, kc, vc = layer.multimer_attn.project_qkv_4d(h)
+        a = O.multimer_attention(qs, ks, vs, qc, kc, vc, mask, pad)
+        a = layer.self_attn.out_proj(a.permute(2, 0, 1, 3).reshape(T, B, E))
+        y = xx + a
+        return y + layer.feed_forward(layer.final_layer_norm(y))
+
+    xc = x.clone().requires_grad_(True)
+    want = cpu_forward(xc)
+    want.sum().backward()
+    wgx = xc.grad.clone()
+    layer.zero_grad()
+    glayer = layer.to(DEV).to(torch.bfloat16)
+    if fp8:
+        holder = torch.nn.Module()
+        holder.layers = torch.nn.ModuleList([glayer])
+        M.apply_fp8_to_model(holder)
+        assert isinstance(glayer.feed_forward.fc1, M.Fp8Linear) and isinstance(glayer.self_attn.fused_qkv, M.Fp8Linear)
+        assert holder._fp8_config == {"enabled": True, "static_scale": True}
+    xg = x.to(DEV, torch.bfloat16).requires_grad_(True)
+    out, _ = glayer(xg, self_attn_mask=mask.to(DEV), self_attn_padding_mask=pad.to(DEV))
+    out.sum().backward()
+    ops.check_device_status()
+    tol = 0.25 if fp8 else 0.06          # e4m3 has 3 mantissa bits; bf16 8
+    scale = want.abs().max().item()
+    assert (out.float().cpu() - want.detach()).abs().max().item() <= tol * scale
+    assert (xg.grad.float().cpu() - wgx).abs().max().item() <= tol * wgx.abs().max().item() + 0.05
+    layer.to("cpu").float()
