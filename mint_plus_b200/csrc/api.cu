@@ -114,10 +114,6 @@ static int fill_common(AttnArgs& a, const char* who, const void* q_s, const void
                        int T, int D, int dtype, unsigned flags, float scale, void* stream, int* dev_status) {
   int rc = check_shape(B, H, T, D, dtype, who);
   if (rc != MINTB_OK) return rc;
-  if (flags & MINTB_FLAG_SQRT_SOFTMAX) {
-    set_error("%s: sqrt-softmax is not implemented", who);
-    return MINTB_EUNSUPPORTED;
-  }
   if (flags & ~(MINTB_FLAG_ROPE | MINTB_FLAG_SQRT_SOFTMAX | MINTB_FLAG_FORCE_SIMT)) {
     set_error("%s: unknown flag bits 0x%x", who, flags);
     return MINTB_EINVAL;
@@ -151,6 +147,7 @@ static int fill_common(AttnArgs& a, const char* who, const void* q_s, const void
   a.workspace = workspace; a.workspace_bytes = workspace_bytes;
   a.B = B; a.H = H; a.T = T; a.D = D; a.dtype = dtype;
   a.rope = (flags & MINTB_FLAG_ROPE) != 0;
+  a.sqrt_softmax = (flags & MINTB_FLAG_SQRT_SOFTMAX) != 0;
   a.scale = scale;
   a.stream = static_cast<cudaStream_t>(stream);
   a.dev_status = dev_status;

@@ -53,6 +53,7 @@ struct SimtParams {
   float* delta;  // [B][H][T]
   int B, H, T, TW;
   float scale;
+  int sqrt_sm;  // square-root softmax: out = sum_j sqrt(p_j) v_j (mu_scaling/layer.py:162-163)
 };
 
 // ------------------------------------------------------------------------------------------------ forward
@@ -115,14 +116,22 @@ __global__ void __launch_bounds__(kSimtThreads) attn_fwd_simt_kernel(SimtParams 
       tmax = fmaxf(tmax, s[jj]);
     }
     const float m_new = fmaxf(m, tmax);  // tile has at least one valid key, so m_new is finite
+    // square-root softmax accumulates sqrt(p) v: the terms are exp2((s - m) / 2), the row sum stays sum exp2(s - m)
     const float alpha = exp2f(m - m_new);
+    const float alpha_acc = p.sqrt_sm ? exp2f(0.5f * (m - m_new)) : alpha;
     l *= alpha;
 #pragma unroll
-    for (int d = 0; d < 8; ++d) acc[d] *= alpha;
+    for (int d = 0; d < 8; ++d) acc[d] *= alpha_acc;
 #pragma unroll
     for (int jj = 0; jj < KT; ++jj) {
-      const float pj = exp2f(s[jj] - m_new);
-      l += pj;
+      float pj;
+      if (p.sqrt_sm) {
+        pj = exp2f(0.5f * (s[jj] - m_new));
+        l = fmaf(pj, pj, l);
+      } else {
+        pj = exp2f(s[jj] - m_new);
+        l += pj;
+      }
       const float* vv = ((cross >> jj) & 1u) ? &sv_c[jj][g * 8] : &sv_s[jj][g * 8];
 #pragma unroll
       for (int d = 0; d < 8; ++d) acc[d] = fmaf(pj, vv[d], acc[d]);
@@ -131,7 +140,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_fwd_simt_kernel(SimtParams 
   }
   if (i < p.T) {
     // A row whose keys are all padded gives 0/0 = NaN, as the softmax of an all -inf row does in PyTorch.
-    const float inv = 1.f / l;
+    const float inv = p.sqrt_sm ? rsqrtf(l) : 1.f / l;
     T* o = static_cast<T*>(p.out) + head + size_t(i) * D + g * 8;
 #pragma unroll
     for (int d = 0; d < 8; ++d) st_f(o + d, acc[d] * inv);
@@ -209,8 +218,14 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dq_simt_kernel(SimtPara
       }
       sp = group_sum<G>(sp);
       dp = group_sum<G>(dp);
-      const float pj = exp2f(sp * c2 - lse2);
-      const float ds = pj * (dp - delta);
+      // softmax: ds = p (dp - delta).  square-root softmax, r = sqrt(p): ds = r (dp - r delta) / 2
+      float ds;
+      if (p.sqrt_sm) {
+        const float rj = exp2f(0.5f * (sp * c2 - lse2));
+        ds = 0.5f * rj * (dp - rj * delta);
+      } else {
+        ds = exp2f(sp * c2 - lse2) * (dp - delta);
+      }
       if (x) {
 #pragma unroll
         for (int d = 0; d < 8; ++d) dqc[d] = fmaf(ds, kk[d], dqc[d]);
@@ -310,8 +325,15 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkv_simt_kernel(SimtPar
       sp = group_sum<G>(sp);
       dp = group_sum<G>(dp);
       // A padded key has probability zero; every thread still takes part in the shuffles above.
-      const float pj = key_valid ? exp2f(sp * c2 - slse2[ii]) : 0.f;
-      const float ds = pj * (dp - sdelta[ii]) * p.scale;
+      // (pj multiplies dO in dV: p for the softmax, sqrt(p) for the square-root softmax)
+      float pj, ds;
+      if (p.sqrt_sm) {
+        pj = key_valid ? exp2f(0.5f * (sp * c2 - slse2[ii])) : 0.f;
+        ds = 0.5f * pj * (dp - pj * sdelta[ii]) * p.scale;
+      } else {
+        pj = key_valid ? exp2f(sp * c2 - slse2[ii]) : 0.f;
+        ds = pj * (dp - sdelta[ii]) * p.scale;
+      }
       if (x) {
 #pragma unroll
         for (int d = 0; d < 8; ++d) {
@@ -362,6 +384,7 @@ static SimtParams make_params(const AttnArgs& a) {
   p.delta = static_cast<float*>(a.workspace);
   p.B = a.B; p.H = a.H; p.T = a.T; p.TW = a.meta.TW;
   p.scale = a.scale;
+  p.sqrt_sm = a.sqrt_softmax ? 1 : 0;
   return p;
 }
 

@@ -176,7 +176,10 @@ constexpr uint8_t kEntryFull = 8;   // covers kN keys (else kBox)
 
 // One chunk of W (32 or 16) logits of one query row: mask, running max, lazy rescale, exp2, row sum, packed bf16 out.
 // `s` holds the selected logits on entry.  Returns the packed probabilities in `pk` (W / 2 words).
-template <int W>
+// With SQ (square-root softmax, out = sum_j sqrt(p_j) v_j) the stored terms are exp2((s c - m_ref) / 2) — `c22` then holds
+// c / 2 — the row sum adds their squares, and `alpha_out`, which rescales O and terms already packed, is the square root
+// of the factor applied to the row sum.
+template <int W, bool SQ>
 __device__ __forceinline__ void softmax_chunk(float (&s)[W], uint32_t pad_bits, bool has_pad, float c2, uint64_t c22,
                                               float& m_ref, float& l, float& alpha_out, bool& rescale_out,
                                               uint32_t (&pk)[W / 2]) {
@@ -195,13 +198,14 @@ __device__ __forceinline__ void softmax_chunk(float (&s)[W], uint32_t pad_bits, 
   alpha_out = 1.f;
   rescale_out = false;
   if (m_tile > m_ref + kRescaleThreshold) {   // also the first finite maximum (m_ref = -inf)
-    alpha_out = ex2(m_ref - m_tile);           // 0 when nothing has been accumulated yet
+    const float a = ex2(m_ref - m_tile);       // 0 when nothing has been accumulated yet
+    alpha_out = SQ ? ex2(0.5f * (m_ref - m_tile)) : a;
     m_ref = m_tile;
-    l *= alpha_out;
+    l *= a;
     rescale_out = true;
   }
   // exp2(s c - m_ref); while every key seen so far is padded (m_ref = -inf) use 0 as reference: exp2(-inf) = 0
-  const float nm = m_ref == -INFINITY ? 0.f : -m_ref;
+  const float nm = m_ref == -INFINITY ? 0.f : (SQ ? -0.5f * m_ref : -m_ref);
   const uint64_t nm2 = pack2(nm, nm);
   uint64_t la = pack2(0.f, 0.f), lb = la;
 #pragma unroll
@@ -210,8 +214,14 @@ __device__ __forceinline__ void softmax_chunk(float (&s)[W], uint32_t pad_bits, 
     unpack2(ffma2(pack2(s[2 * j], s[2 * j + 1]), c22, nm2), p0, p1);
     unpack2(ffma2(pack2(s[2 * j + 2], s[2 * j + 3]), c22, nm2), p2, p3);
     p0 = ex2(p0); p1 = ex2(p1); p2 = ex2(p2); p3 = ex2(p3);
-    la = fadd2(la, pack2(p0, p1));
-    lb = fadd2(lb, pack2(p2, p3));
+    if (SQ) {
+      const uint64_t a = pack2(p0, p1), b = pack2(p2, p3);
+      la = ffma2(a, a, la);
+      lb = ffma2(b, b, lb);
+    } else {
+      la = fadd2(la, pack2(p0, p1));
+      lb = fadd2(lb, pack2(p2, p3));
+    }
     pk[j] = pack_bf16(p0, p1);
     pk[j + 1] = pack_bf16(p2, p3);
   }
@@ -220,7 +230,7 @@ __device__ __forceinline__ void softmax_chunk(float (&s)[W], uint32_t pad_bits, 
   l += l0 + l1;
 }
 
-template <int D>
+template <int D, bool SQ>
 __global__ void __launch_bounds__(kTcThreads, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_constant__ CUtensorMap map_ks,
                    const __grid_constant__ CUtensorMap map_vs, const __grid_constant__ CUtensorMap map_qc,
@@ -457,7 +467,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     const uint32_t* mrow = p.bits + (size_t(b) * p.T + qrow) * p.TW;
     const uint32_t* prow = p.kpad + size_t(b) * p.TW;
     const float c2 = p.scale_log2;
-    const uint64_t c22 = pack2(c2, c2);
+    const uint64_t c22 = SQ ? pack2(0.5f * c2, 0.5f * c2) : pack2(c2, c2);   // multiplies the logits inside exp2
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
 
@@ -506,7 +516,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(r[j]);
-          softmax_chunk<32>(s, has_pad ? prow[kw + 2 * ch] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
+          softmax_chunk<32, SQ>(s, has_pad ? prow[kw + 2 * ch] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
         }
         if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
         uint32_t pk2[16];
@@ -520,7 +530,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           MINTB_TRACE_EV(31);
 #pragma unroll
           for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(r[j]);
-          softmax_chunk<32>(s, has_pad ? prow[kw + 2 * ch + 1] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk2);
+          softmax_chunk<32, SQ>(s, has_pad ? prow[kw + 2 * ch + 1] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk2);
         }
         // a rescale decided by the second chunk also applies to what the first chunk contributes: fold it into pk
         if (__any_sync(0xffffffffu, resc)) {
@@ -553,7 +563,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           MINTB_TRACE_EV(31);
 #pragma unroll
           for (int j = 0; j < W; ++j) s[j] = __uint_as_float(r[j]);
-          softmax_chunk<W>(s, has_pad ? prow[kw + ch] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
+          softmax_chunk<W, SQ>(s, has_pad ? prow[kw + ch] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
         }
         if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
         MINTB_TRACE_EV(32);
@@ -580,7 +590,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           MINTB_TRACE_EV(31);
 #pragma unroll
           for (int j = 0; j < W; ++j) s[j] = __uint_as_float(((cw >> j) & 1u) ? rc[j] : rs[j]);
-          softmax_chunk<W>(s, pw, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
+          softmax_chunk<W, SQ>(s, pw, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
         }
         if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
         // split by pathway: P o ~M multiplies V_self, P o M multiplies V_cross
@@ -627,8 +637,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         const float m_all = fmaxf(m_ref, m_other);                 // finite: an active tile has an unpadded key
         const float w_self = ex2(m_ref - m_all), w_other = ex2(m_other - m_all);   // exp2(-inf) = 0 for an empty half
         const float l_all = l * w_self + l_other * w_other;
-        const float inv = 1.f / l_all;
-        const float f_self = w_self * inv, f_other = w_other * inv;
+        // softmax: O / l.  square-root softmax: the accumulators hold sum exp2((s - m) / 2) v, so they are brought to the
+        // common maximum by the square roots of the weights and divided by sqrt(l)
+        const float inv = SQ ? rsqrtf(l_all) : 1.f / l_all;
+        const float f_self = (SQ ? ex2(0.5f * (m_ref - m_all)) : w_self) * inv;
+        const float f_other = (SQ ? ex2(0.5f * (m_other - m_all)) : w_other) * inv;
         constexpr int CH = NC > 16 ? 16 : NC;   // columns per pass (keeps the register footprint small)
 #pragma unroll
         for (int c0 = 0; c0 < NC; c0 += CH) {
@@ -680,7 +693,7 @@ static size_t rot_bytes(int B, int H, int T, int D) { return align256(size_t(B) 
 
 size_t tc_fwd_workspace_bytes(int B, int H, int T, int D, bool rope) { return rope ? 2 * rot_bytes(B, H, T, D) : 0; }
 
-template <int D>
+template <int D, bool SQ>
 static int fwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s) {
   using Cfg = FwdCfg<D>;
   const int BH = a.B * a.H;
@@ -692,13 +705,13 @@ static int fwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s) {
     return MINTB_ECUDA;
   }
   {  // per device and cheap, so set on every call
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Cfg::kSmemBytes));
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, SQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Cfg::kSmemBytes));
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   }
   FwdParams p{a.meta.bits, a.meta.kpad, a.meta.cls, static_cast<__nv_bfloat16*>(a.out), a.lse, a.H, a.T, a.meta.TW, a.meta.NT,
               a.scale * kLog2e, a.dev_status};
   dim3 grid((a.T + kBM - 1) / kBM, BH);
-  attn_fwd_tc_kernel<D><<<grid, kTcThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, p);
+  attn_fwd_tc_kernel<D, SQ><<<grid, kTcThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, p);
   count_launches(1);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("attention forward launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
@@ -727,9 +740,9 @@ int launch_attn_fwd_tc(const AttnArgs& a) {
     k_s = kr;
   }
   switch (a.D) {
-    case 16: return fwd_tc_t<16>(a, q_s, k_s);
-    case 32: return fwd_tc_t<32>(a, q_s, k_s);
-    case 64: return fwd_tc_t<64>(a, q_s, k_s);
+    case 16: return a.sqrt_softmax ? fwd_tc_t<16, true>(a, q_s, k_s) : fwd_tc_t<16, false>(a, q_s, k_s);
+    case 32: return a.sqrt_softmax ? fwd_tc_t<32, true>(a, q_s, k_s) : fwd_tc_t<32, false>(a, q_s, k_s);
+    case 64: return a.sqrt_softmax ? fwd_tc_t<64, true>(a, q_s, k_s) : fwd_tc_t<64, false>(a, q_s, k_s);
   }
   set_error("mintb_attn_fwd: unsupported head_dim %d", a.D);
   return MINTB_EUNSUPPORTED;

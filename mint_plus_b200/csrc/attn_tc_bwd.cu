@@ -104,9 +104,10 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
 // ------------------------------------------------------------------------------------------------ pre / post passes
 // Per-query statistics for the backward pass: stats[bh][i] = (-lse * log2 e, -delta), delta = sum_d dO[i][d] * O[i][d].
 // Rows are padded to a multiple of 128 per (batch, head); the pad entries are (-inf, 0), which makes exp2 give 0 there.
+// `factor` is 1, or 1/2 for the square-root softmax (whose kernel works with sqrt(p) = exp2((s c - lse) / 2) and delta / 2).
 __global__ void __launch_bounds__(256) bwd_stats_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                                         const float* __restrict__ lse, float2* __restrict__ stats, int BH, int T,
-                                                        int Tpad, int D) {
+                                                        int Tpad, int D, float factor) {
   const int lpr = D / 8;  // lanes per row
   const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   const size_t prow = idx / lpr;          // row in the padded layout
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const __nv_bfloat16* __r
   }
   for (int off = lpr / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (bh < size_t(BH) && c == 0)
-    stats[prow] = live ? make_float2(-lse[bh * T + t] * kLog2e, -acc) : make_float2(-INFINITY, 0.f);
+    stats[prow] = live ? make_float2(-lse[bh * T + t] * kLog2e * factor, -acc * factor) : make_float2(-INFINITY, 0.f);
 }
 
 // dq = scale * R^T(acc) for the self pathway (with tables), scale * acc for the cross pathway; fp32 -> bf16.
@@ -210,7 +211,7 @@ struct Ring {
   }
 };
 
-template <int D>
+template <int D, bool SQ>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_constant__ CUtensorMap map_ks,
                    const __grid_constant__ CUtensorMap map_vs, const __grid_constant__ CUtensorMap map_qc,
@@ -502,7 +503,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
             if (!((keep >> (j + 1)) & 1u)) p1 = 0.f;
           }
           float d0, d1;
-          unpack2(fmul2(pack2(p0, p1), fadd2(pack2(__uint_as_float(dpv[j]), __uint_as_float(dpv[j + 1])), pack2(q2.y, q2.w))), d0, d1);
+          const uint64_t p2 = pack2(p0, p1), dp2 = pack2(__uint_as_float(dpv[j]), __uint_as_float(dpv[j + 1])), nd2 = pack2(q2.y, q2.w);
+          if (SQ)   // r = sqrt(p) is what p0, p1 hold: dS = r (dP / 2 - r delta / 2), and r itself multiplies dO in dV
+            unpack2(fmul2(p2, ffma2(p2, nd2, fmul2(dp2, pack2(0.5f, 0.5f)))), d0, d1);
+          else      // dS = p (dP - delta)
+            unpack2(fmul2(p2, fadd2(dp2, nd2)), d0, d1);
           pp[j / 2] = bwd_pack(p0, p1);
           dd[j / 2] = bwd_pack(d0, d1);
         }
@@ -605,7 +610,7 @@ size_t tc_bwd_workspace_bytes(int B, int H, int T, int D, bool rope) {
 
 void launch_rope_rotate(const AttnArgs& a, __nv_bfloat16* qr, __nv_bfloat16* kr);  // attn_tc.cu
 
-template <int D>
+template <int D, bool SQ>
 static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const float2* stats, float* acc_s, float* acc_c) {
   using Cfg = BwdCfg<D>;
   const int BH = a.B * a.H;
@@ -617,7 +622,7 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const f
     set_error("mintb_attn_bwd: cuTensorMapEncodeTiled failed");
     return MINTB_ECUDA;
   }
-  cudaError_t e = cudaFuncSetAttribute(attn_bwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Cfg::kSmemBytes));
+  cudaError_t e = cudaFuncSetAttribute(attn_bwd_tc_kernel<D, SQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Cfg::kSmemBytes));
   if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   BwdParams p{};
   p.bitsT = a.meta.bitsT; p.kpad = a.meta.kpad; p.cls = a.meta.cls;
@@ -628,10 +633,11 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const f
   p.dk[0] = static_cast<__nv_bfloat16*>(a.dk_s); p.dk[1] = static_cast<__nv_bfloat16*>(a.dk_c);
   p.dv[0] = static_cast<__nv_bfloat16*>(a.dv_s); p.dv[1] = static_cast<__nv_bfloat16*>(a.dv_c);
   p.H = a.H; p.T = a.T; p.Tpad = bwd_tpad(a.T); p.TW = a.meta.TW; p.NT = a.meta.NT;
-  p.scale = a.scale; p.scale_log2 = a.scale * kLog2e;
+  p.scale = a.scale;
+  p.scale_log2 = a.scale * kLog2e * (SQ ? 0.5f : 1.f);   // multiplies the logits inside exp2
   p.status = a.dev_status;
   dim3 grid((a.T + kBwdTile - 1) / kBwdTile, BH, 2);
-  attn_bwd_tc_kernel<D><<<grid, kBwdThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, p);
+  attn_bwd_tc_kernel<D, SQ><<<grid, kBwdThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, p);
   count_launches(1);
   e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("attention backward launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
@@ -663,14 +669,19 @@ int launch_attn_bwd_tc(const AttnArgs& a) {
     const size_t n = size_t(a.B) * a.H * tpad * (a.D / 8);
     bwd_stats_kernel<<<unsigned((n + 255) / 256), 256, 0, a.stream>>>(static_cast<const __nv_bfloat16*>(a.out),
                                                                      static_cast<const __nv_bfloat16*>(a.d_out), a.lse, stats,
-                                                                     a.B * a.H, a.T, tpad, a.D);
+                                                                     a.B * a.H, a.T, tpad, a.D, a.sqrt_softmax ? 0.5f : 1.f);
     count_launches(1);
   }
   int rc = MINTB_EUNSUPPORTED;
   switch (a.D) {
-    case 16: rc = bwd_tc_t<16>(a, q_s, k_s, stats, acc_s, acc_c); break;
-    case 32: rc = bwd_tc_t<32>(a, q_s, k_s, stats, acc_s, acc_c); break;
-    case 64: rc = bwd_tc_t<64>(a, q_s, k_s, stats, acc_s, acc_c); break;
+#define MINTB_BWD_CASE(DD)                                                                                       \
+  case DD:                                                                                                       \
+    rc = a.sqrt_softmax ? bwd_tc_t<DD, true>(a, q_s, k_s, stats, acc_s, acc_c) : bwd_tc_t<DD, false>(a, q_s, k_s, stats, acc_s, acc_c); \
+    break;
+    MINTB_BWD_CASE(16)
+    MINTB_BWD_CASE(32)
+    MINTB_BWD_CASE(64)
+#undef MINTB_BWD_CASE
     default: set_error("mintb_attn_bwd: unsupported head_dim %d", a.D);
   }
   if (rc != MINTB_OK) return rc;

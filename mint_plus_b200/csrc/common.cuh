@@ -72,6 +72,7 @@ struct AttnArgs {
   int B, H, T, D;
   int dtype;
   bool rope;
+  bool sqrt_softmax;
   float scale;
   cudaStream_t stream;
   int* dev_status;

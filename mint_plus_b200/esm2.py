@@ -1,0 +1,186 @@
+"""MINT model with the reference's constructor, forward signature, outputs and state-dict keys
+(mint_plus/models/esm2.py:14-145, 146-256; registry mint_plus/models/__init__.py:4-60).
+
+What differs from the reference forward: the (B,T,T) chain mask is not built when every layer is a two-pathway layer
+of this package — the layers get `chain_ids` and derive the compact mask metadata from them once per batch — and
+`layer_factory` lets a builder choose the layer class.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Optional
+
+import torch
+from torch import nn
+from torch.utils.checkpoint import checkpoint
+
+from .modules import RobertaLMHead, TransformerLayer_MINT
+from .modules_plus import _TwoPathwayLayer
+
+MODEL_REGISTRY = {
+    "8M": dict(name="esm2_t6_8M_UR50D", num_layers=6, embed_dim=320, attention_heads=20, intermediate_size=1280),
+    "35M": dict(name="esm2_t12_35M_UR50D", num_layers=12, embed_dim=480, attention_heads=20, intermediate_size=1920),
+    "150M": dict(name="esm2_t30_150M_UR50D", num_layers=30, embed_dim=640, attention_heads=20, intermediate_size=2560),
+    "650M": dict(name="esm2_t33_650M_UR50D", num_layers=33, embed_dim=1280, attention_heads=20, intermediate_size=5120),
+    "3B": dict(name="esm2_t36_3B_UR50D", num_layers=36, embed_dim=1792, attention_heads=16, intermediate_size=7168),
+    "15B": dict(name="esm2_t48_15B_UR50D", num_layers=48, embed_dim=5120, attention_heads=20, intermediate_size=20480),
+}
+
+
+class Alphabet:
+    """The ESM-1b token table: 33 entries, <cls>=0, <pad>=1, <eos>=2, <unk>=3, amino acids from 4, <mask>=32."""
+
+    toks = ["<cls>", "<pad>", "<eos>", "<unk>", "L", "A", "G", "V", "S", "E", "R", "T", "I", "D", "P", "K", "Q", "N", "F",
+            "Y", "M", "H", "W", "C", "X", "B", "U", "Z", "O", ".", "-", "<null_1>", "<mask>"]
+
+    def __init__(self):
+        self.tok_to_idx = {t: i for i, t in enumerate(self.toks)}
+        self.padding_idx, self.cls_idx, self.eos_idx = 1, 0, 2
+        self.unk_idx, self.mask_idx = 3, 32
+        self.prepend_bos = self.append_eos = True
+
+    def __len__(self):
+        return len(self.toks)
+
+    @classmethod
+    def from_architecture(cls, name: str) -> "Alphabet":
+        if name not in ("ESM-1b", "roberta_large"):
+            raise ValueError(f"unknown alphabet {name!r}")
+        return cls()
+
+    def encode(self, sequence: str) -> List[int]:
+        return [self.tok_to_idx.get(ch, self.unk_idx) for ch in sequence]
+
+
+class MINT(nn.Module):
+    def __init__(self, num_layers: int = 33, embed_dim: int = 1280, attention_heads: int = 20, alphabet="ESM-1b",
+                 token_dropout: bool = True, use_multimer: bool = True, use_rmsnorm: bool = False,
+                 use_erf_gelu: bool = False, fp8: bool = False,
+                 layer_factory: Optional[Callable[[], nn.Module]] = None):
+        super().__init__()
+        self.num_layers, self.embed_dim, self.attention_heads = num_layers, embed_dim, attention_heads
+        if not isinstance(alphabet, Alphabet):
+            alphabet = Alphabet.from_architecture(alphabet)
+        self.alphabet = alphabet
+        self.alphabet_size = len(alphabet)
+        self.padding_idx, self.mask_idx = alphabet.padding_idx, alphabet.mask_idx
+        self.cls_idx, self.eos_idx = alphabet.cls_idx, alphabet.eos_idx
+        self.prepend_bos, self.append_eos = alphabet.prepend_bos, alphabet.append_eos
+        self.token_dropout = token_dropout
+        self.use_multimer = use_multimer
+        self.use_rmsnorm = use_rmsnorm
+        self.use_erf_gelu = use_erf_gelu
+        self.checkpoint_layers = True
+        self._init_submodules(layer_factory)
+
+    def _init_submodules(self, layer_factory=None):
+        self.embed_tokens = nn.Embedding(self.alphabet_size, self.embed_dim, padding_idx=self.padding_idx)
+        if layer_factory is None:
+            def layer_factory():
+                return TransformerLayer_MINT(self.embed_dim, 4 * self.embed_dim, self.attention_heads,
+                                             use_rmsnorm=self.use_rmsnorm, use_rotary_embeddings=True,
+                                             use_multimer=self.use_multimer, use_erf_gelu=self.use_erf_gelu)
+        self.layers = nn.ModuleList([layer_factory() for _ in range(self.num_layers)])
+        self.emb_layer_norm_after = nn.RMSNorm(self.embed_dim) if self.use_rmsnorm else nn.LayerNorm(self.embed_dim)
+        self.lm_head = RobertaLMHead(embed_dim=self.embed_dim, output_dim=self.alphabet_size,
+                                     weight=self.embed_tokens.weight)
+
+    def _needs_dense_mask(self) -> bool:
+        """The (B,T,T) mask is only built for layers that cannot take chain ids (foreign layer classes, single-pathway
+        layers, or the materialised-logits combine)."""
+        for layer in self.layers:
+            for sub in (layer.layers if hasattr(layer, "layers") else [layer]):
+                if not (isinstance(sub, _TwoPathwayLayer) and sub.use_multimer and sub._use_fused_multi_pathway):
+                    return True
+        return False
+
+    def forward(self, tokens: torch.Tensor, chain_ids: Optional[torch.Tensor] = None,
+                repr_layers: List[int] = []) -> Dict[str, torch.Tensor]:
+        assert tokens.ndim == 2
+        padding_mask = tokens.eq(self.padding_idx)                    # B, T
+        if chain_ids is None:
+            chain_ids = torch.zeros_like(tokens)
+        self_attn_mask = None
+        if self._needs_dense_mask():
+            self_attn_mask = ~torch.eq(chain_ids.unsqueeze(-1), chain_ids.unsqueeze(-2))      # B, T, T; True = other chain
+            if not self.use_multimer:
+                self_attn_mask = None                                 # a single-pathway model attends everywhere
+
+        x = self.embed_tokens(tokens)
+        if self.token_dropout and self.training:
+            x = x.masked_fill((tokens == self.mask_idx).unsqueeze(-1), 0.0)
+            mask_ratio_train = 0.15 * 0.8
+            src_lengths = (~padding_mask).sum(-1)
+            mask_ratio_observed = (tokens == self.mask_idx).sum(-1).to(x.dtype) / src_lengths
+            x = x * (1 - mask_ratio_train) / (1 - mask_ratio_observed)[:, None, None]
+        x = x * (1 - padding_mask.unsqueeze(-1).type_as(x))
+
+        repr_layers = set(repr_layers)
+        hidden_representations = {}
+        if 0 in repr_layers:
+            hidden_representations[0] = x
+        x = x.transpose(0, 1)                                          # (B,T,E) -> (T,B,E)
+
+        use_ckpt = self.checkpoint_layers and self.training and torch.is_grad_enabled()
+        if use_ckpt and not x.requires_grad:
+            x.requires_grad_(True)
+        layer_idx = -1
+        for layer_idx, layer in enumerate(self.layers):
+            if use_ckpt:
+                x, _ = checkpoint(layer, x, self_attn_padding_mask=padding_mask, self_attn_mask=self_attn_mask,
+                                  chain_ids=chain_ids, use_reentrant=False)
+            else:
+                x, _ = layer(x, self_attn_padding_mask=padding_mask, self_attn_mask=self_attn_mask, chain_ids=chain_ids)
+            if (layer_idx + 1) in repr_layers:
+                hidden_representations[layer_idx + 1] = x.transpose(0, 1)
+
+        x = self.emb_layer_norm_after(x)
+        x = x.transpose(0, 1)                                          # (T,B,E) -> (B,T,E)
+        if (layer_idx + 1) in repr_layers:
+            hidden_representations[layer_idx + 1] = x
+        logits = self.lm_head(x)
+        return {"logits": logits, "representations": hidden_representations}
+
+    @classmethod
+    def from_config(cls, model_size: str, fp8: bool = False, use_erf_gelu: bool = False) -> "MINT":
+        if model_size not in MODEL_REGISTRY:
+            raise ValueError(f"Unknown model size: {model_size}. Available: {list(MODEL_REGISTRY)}")
+        cfg = MODEL_REGISTRY[model_size]
+        return cls(num_layers=cfg["num_layers"], embed_dim=cfg["embed_dim"], attention_heads=cfg["attention_heads"],
+                   fp8=fp8, use_erf_gelu=use_erf_gelu)
+
+    def _upgrade_state_dict(self, state_dict: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        """Map HuggingFace-ESM key names (`esm.encoder.layer.N.attention.self.query...`) to this model's
+        (esm2.py:205-246 of the reference)."""
+        rules = (("attention.self.query", "self_attn.q_proj"), ("attention.self.key", "self_attn.k_proj"),
+                 ("attention.self.value", "self_attn.v_proj"), ("attention.output.dense", "self_attn.out_proj"),
+                 ("attention.Layer", "self_attn_layer_norm"), ("LayerNorm", "final_layer_norm"),
+                 ("intermediate", "feed_forward.fc1"), ("output", "feed_forward.fc2"))
+        out = {}
+        for key, value in state_dict.items():
+            new_key = key
+            for prefix in ("esm.", "encoder."):
+                if new_key.startswith(prefix):
+                    new_key = new_key[len(prefix):]
+            parts = new_key.split(".")
+            if len(parts) > 1 and parts[0] in ("layer", "layers") and parts[1].isdigit():
+                for pattern, target in rules:
+                    if pattern in new_key:
+                        new_key = f"layers.{parts[1]}.{target}.{parts[-1]}"
+                        break
+            elif "word_embeddings.weight" in new_key:
+                new_key = "embed_tokens.weight"
+            elif "lm_head.decoder.weight" in new_key:
+                new_key = "lm_head.weight"
+            out[new_key] = value
+        return out
+
+    def load_pretrained_weights(self, checkpoint_path: str, strict: bool = False, dtype: torch.dtype = torch.float32,
+                                alternating: bool = False):
+        ckpt = torch.load(checkpoint_path, map_location="cpu")
+        state_dict = ckpt.get("model", ckpt.get("state_dict", ckpt)) if isinstance(ckpt, dict) else ckpt
+        state_dict = self._upgrade_state_dict(state_dict)
+        if dtype != torch.float32:
+            state_dict = {k: v.to(dtype=dtype) for k, v in state_dict.items()}
+        if "lm_head.decoder.weight" in state_dict and "lm_head.weight" not in state_dict:
+            state_dict["lm_head.weight"] = state_dict["lm_head.decoder.weight"]
+        return self.load_state_dict(state_dict, strict=strict)

@@ -1,0 +1,42 @@
+"""TransformerLayer_MINT and RobertaLMHead with the reference's interface and state-dict keys
+(mint_plus/models/modules.py:25-195, 338-369).
+
+The base layer keeps three separate q/k/v projections per pathway (`self_attn.q_proj` ..., `multimer_attn.q_proj` ...,
+the cross pathway without an output projection) so that reference checkpoints load by name.  Its attention runs on the
+same fused CUDA operator as the `_plus` layer; the three weights of a pathway are concatenated to [Q;K;V] on the fly.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+from torch.nn import LayerNorm as ESM1bLayerNorm  # noqa: F401  (name kept for importers)
+
+from .attention import MultiHeadAttention
+from .modules_plus import VanillaFeedForward, _PreLnLayer, gelu_erf  # noqa: F401
+
+
+class TransformerLayer_MINT(_PreLnLayer):
+    def __init__(self, embed_dim, ffn_embed_dim, attention_heads, use_rotary_embeddings: bool = True,
+                 use_multimer: bool = False, use_rmsnorm: bool = False, use_erf_gelu: bool = False):
+        super().__init__()
+        self.self_attn = MultiHeadAttention(embed_dim, attention_heads, use_rotary_embeddings=use_rotary_embeddings)
+        if use_multimer:
+            self.multimer_attn = MultiHeadAttention(embed_dim, attention_heads, use_rotary_embeddings=False, no_proj=True)
+        self._init_common(embed_dim, ffn_embed_dim, attention_heads, use_rotary_embeddings, use_multimer, use_rmsnorm,
+                          use_erf_gelu)
+
+
+class RobertaLMHead(nn.Module):
+    """dense -> GELU -> LayerNorm -> tied output projection + bias (modules.py:338-369)."""
+
+    def __init__(self, embed_dim: int, output_dim: int, weight: torch.Tensor):
+        super().__init__()
+        self.dense = nn.Linear(embed_dim, embed_dim)
+        self.layer_norm = nn.LayerNorm(embed_dim)
+        self.weight = weight
+        self.bias = nn.Parameter(torch.zeros(output_dim))
+
+    def forward(self, features):
+        x = self.layer_norm(F.gelu(self.dense(features)))
+        return F.linear(x, self.weight) + self.bias

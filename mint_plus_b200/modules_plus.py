@@ -46,26 +46,31 @@ class VanillaFeedForward(nn.Module):
         return self.fc2(x)
 
 
-class TransformerLayer_MINT_plus(nn.Module):
-    def __init__(self, embed_dim, ffn_embed_dim, attention_heads, use_rotary_embeddings: bool = True,
-                 use_multimer: bool = False, use_rmsnorm: bool = False, use_erf_gelu: bool = False):
-        super().__init__()
-        self.embed_dim = embed_dim
-        self.ffn_embed_dim = ffn_embed_dim
-        self.attention_heads = attention_heads
-        self.use_rotary_embeddings = use_rotary_embeddings
-        self.use_multimer = use_multimer
-        self.use_rmsnorm = use_rmsnorm
-        self.use_erf_gelu = use_erf_gelu
-        self._use_fused_multi_pathway = True
-        self.self_attn = MultiHeadAttention(embed_dim, attention_heads, use_rotary_embeddings=use_rotary_embeddings,
-                                            use_fused_qkv=True)
-        if use_multimer:
-            self.multimer_attn = MultimerAttention(embed_dim, attention_heads)
-        self.feed_forward = VanillaFeedForward(embed_dim, ffn_embed_dim, use_erf_gelu=use_erf_gelu)
-        norm = (lambda: nn.RMSNorm(embed_dim)) if use_rmsnorm else (lambda: nn.LayerNorm(embed_dim))
-        self.self_attn_layer_norm = norm()
-        self.final_layer_norm = norm()
+def _qkv_operands(attn):
+    """(weight [3E,E], bias, fp8 triple or None) of one pathway's Q/K/V projections, whether the module holds one fused
+    Linear or three separate ones (rows ordered [Q;K;V] either way), or None when the modules are of mixed kinds."""
+    from .mu_scaling import Fp8Linear, fused_fp8_weight
+    fused = getattr(attn, "fused_qkv", None)
+    mods = [fused] if fused is not None else [attn.q_proj, attn.k_proj, attn.v_proj]
+    if all(isinstance(m, Fp8Linear) for m in mods):
+        kind = "fp8"
+    elif all(type(m) is nn.Linear for m in mods):
+        kind = "bf16"
+    else:
+        return None
+    if len(mods) == 1:
+        w, b = mods[0].weight, mods[0].bias
+    else:
+        w = torch.cat([m.weight for m in mods], dim=0)
+        b = torch.cat([m.bias for m in mods], dim=0) if mods[0].bias is not None else None
+    return w, b, (fused_fp8_weight(attn, mods) if kind == "fp8" else None)
+
+
+class _TwoPathwayLayer(nn.Module):
+    """The attention half shared by the Pre-LN layers and the muS layer: both QKV projections, the fused two-pathway
+    attention (or the materialised-logits combine when `_use_fused_multi_pathway` is False), the output projection."""
+
+    _use_sqrt_softmax = False
 
     def _standard_attention(self, x, attn_mask, padding_mask):
         return self.self_attn(x=x, key_padding_mask=padding_mask, attn_mask=attn_mask)
@@ -73,8 +78,12 @@ class TransformerLayer_MINT_plus(nn.Module):
     def _multimer_attention_plus(self, x, chain_mask, padding_mask, chain_ids=None):
         if self._use_fused_multi_pathway:
             return self._multimer_attention_superfused(x, chain_mask, padding_mask, chain_ids)
+        if self._use_sqrt_softmax:
+            raise NotImplementedError("square-root softmax needs the fused attention (enable_fused_multi_pathway)")
         T, B, E = x.shape
         sa, ma = self.self_attn, self.multimer_attn
+        if chain_mask is None:
+            chain_mask = chain_ids.unsqueeze(-1) != chain_ids.unsqueeze(-2)
         intra_logits, intra_values = sa(x=x, key_padding_mask=padding_mask, before_softmax=True)
         inter_logits, inter_values = ma(x=x, key_padding_mask=padding_mask, before_softmax=True)
         attn_out = fused_multimer_combine(intra_logits.type_as(intra_values), inter_logits.type_as(inter_values),
@@ -91,20 +100,24 @@ class TransformerLayer_MINT_plus(nn.Module):
         else:
             mask_kw = dict(chain_mask=chain_mask, key_padding_mask=padding_mask)
         rope = sa.rot_emb is not None
-        fast = (x.is_cuda and x.dtype == torch.bfloat16 and isinstance(getattr(sa, "fused_qkv", None), nn.Linear)
-                and isinstance(ma.fused_qkv, nn.Linear))
-        if fast:
-            # bf16 on the GPU: the QKV GEMMs write q, k, v head-major and rotate the self pathway in their epilogue, so the
-            # attention kernel gets ready-made operands (no permute copies, no rotation pass)
+        sqrt_sm = bool(self._use_sqrt_softmax)
+        ops_s = ops_c = None
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            ops_s, ops_c = _qkv_operands(sa), _qkv_operands(ma)
+        if ops_s is not None and ops_c is not None:
+            # bf16 activations on the GPU: the QKV GEMMs (bf16 or e4m3 operands) write q, k, v head-major and rotate the self
+            # pathway in their epilogue, so the attention kernel gets ready-made operands (no permute copies, no rotation pass)
             tabs = ops.rope_tables(T, sa.head_dim, x.device, sa.rot_emb.inv_freq)[:2] if rope else None
-            q_s, k_s, v_s = ops.qkv_project(x, sa.fused_qkv.weight, sa.fused_qkv.bias, sa.num_heads, rope=tabs)
-            q_c, k_c, v_c = ops.qkv_project(x, ma.fused_qkv.weight, ma.fused_qkv.bias, ma.num_heads)
-            attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=False, scale=sa.scaling, **mask_kw)
+            q_s, k_s, v_s = ops.qkv_project(x, ops_s[0], ops_s[1], sa.num_heads, rope=tabs, fp8=ops_s[2])
+            q_c, k_c, v_c = ops.qkv_project(x, ops_c[0], ops_c[1], ma.num_heads, fp8=ops_c[2])
+            attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=False, scale=sa.scaling,
+                                              sqrt_softmax=sqrt_sm, **mask_kw)
         else:
             q_s, k_s, v_s = sa.project_qkv_4d(x)
             q_c, k_c, v_c = ma.project_qkv_4d(x)
             attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=rope,
-                                              inv_freq=sa.rot_emb.inv_freq if rope else None, scale=sa.scaling, **mask_kw)
+                                              inv_freq=sa.rot_emb.inv_freq if rope else None, scale=sa.scaling,
+                                              sqrt_softmax=sqrt_sm, **mask_kw)
         attn_out = attn_out.permute(2, 0, 1, 3).reshape(T, B, E)
         if x.is_cuda and x.dtype == torch.bfloat16:
             return _linear(sa.out_proj, attn_out), None
@@ -113,6 +126,25 @@ class TransformerLayer_MINT_plus(nn.Module):
     # the PyTorch-named entry of the reference resolves to the same fused path
     def _multimer_attention(self, x, chain_mask, padding_mask):
         return self._multimer_attention_plus(x, chain_mask, padding_mask)
+
+
+class _PreLnLayer(_TwoPathwayLayer):
+    """x -> LN -> attention -> +residual -> LN -> FFN -> +residual (modules.py:179-195, modules_plus.py:72-96)."""
+
+    def _init_common(self, embed_dim, ffn_embed_dim, attention_heads, use_rotary_embeddings, use_multimer, use_rmsnorm,
+                     use_erf_gelu):
+        self.embed_dim = embed_dim
+        self.ffn_embed_dim = ffn_embed_dim
+        self.attention_heads = attention_heads
+        self.use_rotary_embeddings = use_rotary_embeddings
+        self.use_multimer = use_multimer
+        self.use_rmsnorm = use_rmsnorm
+        self.use_erf_gelu = use_erf_gelu
+        self._use_fused_multi_pathway = True
+        self.feed_forward = VanillaFeedForward(embed_dim, ffn_embed_dim, use_erf_gelu=use_erf_gelu)
+        norm = (lambda: nn.RMSNorm(embed_dim)) if use_rmsnorm else (lambda: nn.LayerNorm(embed_dim))
+        self.self_attn_layer_norm = norm()
+        self.final_layer_norm = norm()
 
     def forward(self, x, self_attn_mask=None, self_attn_padding_mask=None, chain_ids=None):
         residual = x
@@ -127,6 +159,20 @@ class TransformerLayer_MINT_plus(nn.Module):
         x = self.feed_forward(x)
         x = residual + x
         return x, attn
+
+
+class TransformerLayer_MINT_plus(_PreLnLayer):
+    """Pre-LN layer with one fused Linear(E, 3E) per pathway (modules_plus.py:20-64)."""
+
+    def __init__(self, embed_dim, ffn_embed_dim, attention_heads, use_rotary_embeddings: bool = True,
+                 use_multimer: bool = False, use_rmsnorm: bool = False, use_erf_gelu: bool = False):
+        super().__init__()
+        self.self_attn = MultiHeadAttention(embed_dim, attention_heads, use_rotary_embeddings=use_rotary_embeddings,
+                                            use_fused_qkv=True)
+        if use_multimer:
+            self.multimer_attn = MultimerAttention(embed_dim, attention_heads)
+        self._init_common(embed_dim, ffn_embed_dim, attention_heads, use_rotary_embeddings, use_multimer, use_rmsnorm,
+                          use_erf_gelu)
 
 
 _ids_meta_cache = []

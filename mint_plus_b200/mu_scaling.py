@@ -11,38 +11,43 @@ the casts).
 """
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
 from torch import nn
 
 from . import ops
+from .attention import MultiHeadAttention
+from .modules_plus import VanillaFeedForward, _TwoPathwayLayer
 
 E4M3_MAX = 448.0
 
 
 class _Fp8LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x2d, weight, bias, wq, w_scale, x_scale, gelu):
+    def forward(ctx, x2d, weight, bias, wq, w_scale, x_scale, gelu, out_scale):
         xq = ops.quantize_e4m3(x2d, x_scale)
         ctx.save_for_backward(x2d, weight, bias)
         ctx.gelu = gelu
-        ctx.scales = (wq, w_scale, x_scale)
-        return ops.gemm_e4m3(xq, wq, x_scale * w_scale, bias, gelu)
+        ctx.scales = (wq, w_scale, x_scale, out_scale)
+        return ops.gemm_e4m3(xq, wq, x_scale * w_scale * out_scale, bias, gelu)
 
     @staticmethod
     def backward(ctx, dy):
         x2d, weight, bias = ctx.saved_tensors
         wb = weight if weight.dtype == torch.bfloat16 else weight.to(torch.bfloat16)
         dz = dy
+        wq, w_scale, x_scale, out_scale = ctx.scales
         if ctx.gelu:
-            wq, w_scale, x_scale = ctx.scales
-            z = ops.gemm_e4m3(ops.quantize_e4m3(x2d, x_scale), wq, x_scale * w_scale, bias, False)
+            z = ops.gemm_e4m3(ops.quantize_e4m3(x2d, x_scale), wq, x_scale * w_scale * out_scale, bias, False)
             dz = (dy.float() * ops._gelu_erf_grad(z)).to(torch.bfloat16)
+        db = dz.float().sum(0).to(bias.dtype) if (bias is not None and ctx.needs_input_grad[2]) else None
+        if out_scale != 1.0:            # static output multiplier of the product (not of the bias)
+            dz = dz * out_scale
         dx = dz @ wb if ctx.needs_input_grad[0] else None
         dw = (dz.t() @ x2d).to(weight.dtype) if ctx.needs_input_grad[1] else None
-        db = dz.float().sum(0).to(bias.dtype) if (bias is not None and ctx.needs_input_grad[2]) else None
-        return dx, dw, db, None, None, None, None
+        return dx, dw, db, None, None, None, None, None
 
 
 class Fp8Linear(nn.Module):
@@ -54,6 +59,7 @@ class Fp8Linear(nn.Module):
         self.weight = nn.Parameter(torch.empty(out_features, in_features))
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
         self.x_scale = float(x_scale)
+        self.out_scale = 1.0        # static multiplier of x W^T (muS: 1/sqrt(fan_in)); 1.0 = plain linear
         self._wq: Optional[torch.Tensor] = None
         self._wq_key = None
         self._w_scale = 1.0
@@ -83,11 +89,28 @@ class Fp8Linear(nn.Module):
             raise RuntimeError("Fp8Linear runs on CUDA tensors only (no CPU fallback)")
         wq, w_scale = self._quantized_weight()
         x2d = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
-        y = _Fp8LinearFn.apply(x2d, self.weight, self.bias, wq, w_scale, self.x_scale, gelu)
+        y = _Fp8LinearFn.apply(x2d, self.weight, self.bias, wq, w_scale, self.x_scale, gelu, self.out_scale)
         return y.view(*x.shape[:-1], self.out_features)
 
     def extra_repr(self):
         return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, x_scale={self.x_scale}"
+
+
+def fused_fp8_weight(owner: nn.Module, mods):
+    """(e4m3 [3E][E] weight, its scale, activation scale) of the Q/K/V projections `mods` (one fused Fp8Linear or three
+    separate ones) for the head-major QKV GEMM.  Three separate weights share one scale (the largest amax of the three);
+    the quantised concatenation is cached on `owner` until one of the weights changes."""
+    if len(mods) == 1:
+        wq, w_scale = mods[0]._quantized_weight()
+        return wq, w_scale, mods[0].x_scale, mods[0].out_scale
+    key = tuple((m.weight.data_ptr(), m.weight._version) for m in mods)
+    cached = getattr(owner, "_fp8_qkv_cache", None)
+    if cached is None or cached[0] != key:
+        w = torch.cat([m.weight.detach() for m in mods], dim=0)
+        w_scale = max(float(w.abs().amax()), 1e-12) / E4M3_MAX
+        cached = (key, ops.quantize_e4m3(w.to(torch.bfloat16).contiguous(), w_scale), w_scale)
+        owner._fp8_qkv_cache = cached
+    return cached[1], cached[2], max(m.x_scale for m in mods), mods[0].out_scale
 
 
 def _sublayers(model):
@@ -136,6 +159,101 @@ def calibrate_fp8(model: nn.Module, *forward_args, margin: float = 1.0, **forwar
             h.remove()
     for m, amax in seen.items():
         m.x_scale = max(amax * margin, 1e-12) / E4M3_MAX
+    return model
+
+
+def compute_tau(num_layers: int) -> float:
+    """Residual coefficient for a depth: 0.5 / sqrt(L) (mu_scaling/optim.py:20-41)."""
+    return 0.5 / math.sqrt(max(1, num_layers))
+
+
+class TransformerLayer_MINT_mu(_TwoPathwayLayer):
+    """muS Res-Post-LN layer: x = sqrt(1-tau) x + sqrt(tau) attn(x); x = sqrt(1-tau) x + sqrt(tau) ffn(x); x = LN(x)
+    (mu_scaling/layer.py:50-123, 240-280).  Same constructor and sub-module names as the reference, no
+    `self_attn_layer_norm`; `tau` is a buffer so that it travels with the state dict."""
+
+    def __init__(self, embed_dim: int, ffn_embed_dim: int, attention_heads: int, use_rotary_embeddings: bool = True,
+                 use_multimer: bool = False, use_rmsnorm: bool = False, use_erf_gelu: bool = False,
+                 tau: Optional[float] = None, num_layers: Optional[int] = None, use_sqrt_softmax: bool = True):
+        super().__init__()
+        self.embed_dim = embed_dim
+        self.ffn_embed_dim = ffn_embed_dim
+        self.attention_heads = attention_heads
+        self.use_rotary_embeddings = use_rotary_embeddings
+        self.use_multimer = use_multimer
+        self.use_erf_gelu = use_erf_gelu
+        self._use_fused_multi_pathway = True
+        self._use_sqrt_softmax = use_sqrt_softmax
+        if tau is None:
+            tau = compute_tau(num_layers or 30)
+        self.self_attn = MultiHeadAttention(embed_dim, attention_heads, use_rotary_embeddings=use_rotary_embeddings)
+        self.multimer_attn = None
+        if use_multimer:
+            self.multimer_attn = MultiHeadAttention(embed_dim, attention_heads, use_rotary_embeddings=False, no_proj=True)
+        self.feed_forward = VanillaFeedForward(embed_dim, ffn_embed_dim, use_erf_gelu=use_erf_gelu)
+        self.final_layer_norm = nn.LayerNorm(embed_dim)
+        self.register_buffer("_tau", torch.tensor(tau, dtype=torch.float32))
+        self._tau_f = float(tau)
+
+    def forward(self, x, self_attn_mask=None, self_attn_padding_mask=None, chain_ids=None):
+        tau = self._tau_f                       # host copy of the buffer: no device read-back per call
+        keep, add = math.sqrt(1.0 - tau), math.sqrt(tau)
+        if self.use_multimer:
+            attn_out, _ = self._multimer_attention_plus(x, self_attn_mask, self_attn_padding_mask, chain_ids)
+        else:
+            attn_out, _ = self._standard_attention(x, self_attn_mask, self_attn_padding_mask)
+        x = keep * x + add * attn_out
+        x = keep * x + add * self.feed_forward(x)
+        return self.final_layer_norm(x), None
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+        self._tau_f = float(self._tau)
+
+
+def build_mint_mu(model_size: str = "150M", use_multimer: bool = True, tau: Optional[float] = None,
+                  use_sqrt_softmax: bool = True, use_fp8: bool = False, fp8_static_scale: bool = True,
+                  warm_start_esm2: bool = False, checkpoint_block_size: int = 0, use_fused_multi_pathway: bool = True,
+                  num_layers: Optional[int] = None, embed_dim: Optional[int] = None,
+                  attention_heads: Optional[int] = None, unit_scaled: bool = False):
+    """MINT with muS layers (mu_scaling/__init__.py:142-250): Res-Post-LN, tau-weighted residuals, optional square-root
+    softmax, optional FP8 projections.  The model is returned on the CPU with default initialisation.
+
+    `num_layers`/`embed_dim`/`attention_heads` override the registry entry (for shapes the registry does not hold).
+    `unit_scaled=True` applies `unit_variance_init_` and gives every projection the static 1/sqrt(fan_in) output
+    multiplier that keeps unit-variance activations (mu_scaling/init.py:59-72 describes it; the reference builder leaves
+    it switched off).  Warm start from ESM-2 files and block checkpointing are outside this package."""
+    from .esm2 import MINT, MODEL_REGISTRY
+    if warm_start_esm2 or checkpoint_block_size:
+        raise NotImplementedError("warm_start_esm2 / checkpoint_block_size are not part of this package")
+    cfg = MODEL_REGISTRY[model_size]
+    L_ = num_layers or cfg["num_layers"]
+    E_ = embed_dim or cfg["embed_dim"]
+    H_ = attention_heads or cfg["attention_heads"]
+    if tau is None:
+        tau = compute_tau(L_)
+    model = MINT(num_layers=L_, embed_dim=E_, attention_heads=H_, use_multimer=use_multimer,
+                 layer_factory=lambda: TransformerLayer_MINT_mu(E_, 4 * E_, H_, use_rotary_embeddings=True,
+                                                                use_multimer=use_multimer, tau=tau, num_layers=L_,
+                                                                use_sqrt_softmax=use_sqrt_softmax))
+    for layer in model.layers:
+        layer._use_fused_multi_pathway = use_fused_multi_pathway
+    if unit_scaled:
+        unit_variance_init_(model)
+    if use_fp8:
+        apply_fp8_to_model(model, static_scale=fp8_static_scale)
+    if unit_scaled:
+        set_unit_output_scales(model)
+    model._mu_config = {"tau": tau, "use_sqrt_softmax": use_sqrt_softmax, "use_fp8": use_fp8, "unit_scaled": unit_scaled}
+    return model
+
+
+def set_unit_output_scales(model: nn.Module) -> nn.Module:
+    """Give every Fp8Linear of the layers the static output multiplier 1/sqrt(fan_in) (alt/munit_scaling.py:22-34)."""
+    for sub in _sublayers(model):
+        for m in sub.modules():
+            if isinstance(m, Fp8Linear):
+                m.out_scale = 1.0 / math.sqrt(m.in_features)
     return model
 
 

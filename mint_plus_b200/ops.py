@@ -374,25 +374,29 @@ class _QkvFn(torch.autograd.Function):
     """Fused QKV projection of one pathway with head-major outputs (and RoPE on q, k when tables are given)."""
 
     @staticmethod
-    def forward(ctx, x, w, bias, H, cos, sin, q_scale):
+    def forward(ctx, x, w, bias, H, cos, sin, q_scale, wq=None, w_scale=1.0, x_scale=1.0, out_scale=1.0):
         T, B, E = x.shape
         D = E // H
-        wb = (w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)).contiguous()
         b, bdt = _bias_arg(bias)
         x2d = x.reshape(T * B, E).contiguous()
+        if wq is None:      # bf16 operands
+            a_op, b_op, in_dt, alpha = x2d, (w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)).contiguous(), L.BF16, 1.0
+        else:               # e4m3 operands, one scale per tensor; the product of the scales is folded into alpha
+            a_op, b_op, in_dt, alpha = quantize_e4m3(x2d, x_scale), wq, L.E4M3, float(x_scale) * float(w_scale) * float(out_scale)
         q, k, v = (torch.empty(B, H, T, D, dtype=torch.bfloat16, device=x.device) for _ in range(3))
         with torch.cuda.device(x.device):
-            rc = L.lib().mintb_qkv_fwd(_ptr(x2d), _ptr(wb), _ptr(b), _ptr(q), _ptr(k), _ptr(v), T, B, H, D, L.BF16, bdt, 1.0,
-                                       float(q_scale), _ptr(cos), _ptr(sin), _stream(), _ptr(_dev_status(x.device)))
+            rc = L.lib().mintb_qkv_fwd(_ptr(a_op), _ptr(b_op), _ptr(b), _ptr(q), _ptr(k), _ptr(v), T, B, H, D, in_dt, bdt,
+                                       float(alpha), float(q_scale), _ptr(cos), _ptr(sin), _stream(),
+                                       _ptr(_dev_status(x.device)))
         L.check(rc, "mintb_qkv_fwd")
         ctx.save_for_backward(x2d, w, bias, cos, sin)
-        ctx.dims = (T, B, H, D, q_scale)
+        ctx.dims = (T, B, H, D, q_scale, float(out_scale))
         return q, k, v
 
     @staticmethod
     def backward(ctx, dq, dk, dv):
         x2d, w, bias, cos, sin = ctx.saved_tensors
-        T, B, H, D, q_scale = ctx.dims
+        T, B, H, D, q_scale, out_scale = ctx.dims
         if cos is not None:
             dq, dk = _rope_rotate_torch(dq, cos, sin, True), _rope_rotate_torch(dk, cos, sin, True)
         if q_scale != 1.0:
@@ -400,17 +404,22 @@ class _QkvFn(torch.autograd.Function):
         # (B,H,T,D) x3 -> [T*B, 3E]
         g = torch.cat([t.permute(2, 0, 1, 3).reshape(T * B, H * D) for t in (dq, dk, dv)], dim=1).to(torch.bfloat16)
         wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        db = g.float().sum(0).to(bias.dtype) if (bias is not None and ctx.needs_input_grad[2]) else None
+        if out_scale != 1.0:        # static output multiplier of the product (not of the bias)
+            g = g * out_scale
         dx = (g @ wb).view(T, B, H * D) if ctx.needs_input_grad[0] else None
         dw = (g.t() @ x2d).to(w.dtype) if ctx.needs_input_grad[1] else None
-        db = g.float().sum(0).to(bias.dtype) if (bias is not None and ctx.needs_input_grad[2]) else None
-        return dx, dw, db, None, None, None, None
+        return dx, dw, db, None, None, None, None, None, None, None, None
 
 
 def qkv_project(x: torch.Tensor, weight: torch.Tensor, bias, num_heads: int, rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-                q_scale: float = 1.0):
+                q_scale: float = 1.0, fp8: Optional[Tuple[torch.Tensor, float, float, float]] = None):
     """x (T,B,E) bf16, weight (3E,E) with rows [Q;K;V] -> q, k, v (B,H,T,D) bf16, written head-major by the GEMM epilogue
-    (attention.py:97-117, 304-323 of the reference without the three permute copies).  `rope` = (cos, sin) tables rotates q, k."""
+    (attention.py:97-117, 304-323 of the reference without the three permute copies).  `rope` = (cos, sin) tables rotates q, k.
+    `fp8` = (e4m3 weight, weight scale, activation scale, static output multiplier) runs the product on e4m3 operands; `weight` stays the master copy
+    that receives the gradient."""
     if x.dtype != torch.bfloat16 or x.dim() != 3:
         raise TypeError("qkv_project takes a (T, B, E) bfloat16 tensor")
     cos, sin = rope if rope is not None else (None, None)
-    return _QkvFn.apply(x, weight, bias, num_heads, cos, sin, q_scale)
+    wq, w_scale, x_scale, out_scale = fp8 if fp8 is not None else (None, 1.0, 1.0, 1.0)
+    return _QkvFn.apply(x, weight, bias, num_heads, cos, sin, q_scale, wq, w_scale, x_scale, out_scale)

@@ -92,7 +92,10 @@ def multimer_attention(q_self, k_self, v_self, q_cross, k_cross, v_cross, chain_
     logits = combined_logits(q_self, k_self, q_cross, k_cross, chain_mask, key_pad, scale, rope)
     probs = F.softmax(logits, dim=-1, dtype=torch.float32)
     if sqrt_softmax:
-        probs = probs.sqrt()
+        # sqrt(p) with the derivative at p = 0 (padded keys) taken as 0; autograd through a plain sqrt gives 0 * inf = NaN
+        # there, which is what the reference's PyTorch path produces when a batch holds padding (mu_scaling/layer.py:162-163)
+        live = probs > 0
+        probs = torch.where(live, probs, torch.ones_like(probs)).sqrt() * live
     probs = probs.to(v_self.dtype)
     m = chain_mask[:, None]
     out = torch.matmul(probs.masked_fill(m, 0.0), v_self) + torch.matmul(probs.masked_fill(~m, 0.0), v_cross)

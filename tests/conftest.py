@@ -29,7 +29,7 @@ def pytest_collection_modifyitems(config, items):
 
 
 def golden_cases():
-    return sorted(f[:-4] for f in os.listdir(GOLDEN) if f.endswith(".npz"))
+    return sorted(f[:-4] for f in os.listdir(GOLDEN) if f.startswith("attn_") and f.endswith(".npz"))
 
 
 def load_golden(name):

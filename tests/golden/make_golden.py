@@ -143,6 +143,57 @@ CASES = [
 ]
 
 
+def _fp32_softmax_attention(self, x, chain_mask, padding_mask, chain_ids=None):
+    """The base layer's PyTorch attention (mint_plus/models/modules.py:94-154) with the softmax in float32 followed by a
+    cast back, as the reference's own muS layer does it (mu_scaling/layer.py:159-165).  The base layer hard-codes a bfloat16
+    softmax that cannot run on float32 tensors, and its default path launches Triton kernels, which need a GPU."""
+    import torch.nn.functional as F
+    intra_logits, intra_values = self.self_attn(x=x, key_padding_mask=padding_mask, before_softmax=True)
+    inter_logits, inter_values = self.multimer_attn(x=x, key_padding_mask=padding_mask, before_softmax=True)
+    m = chain_mask.unsqueeze(1)
+    probs = F.softmax(torch.where(m, inter_logits, intra_logits), dim=-1, dtype=torch.float32).type_as(intra_values)
+    out = torch.matmul(probs.masked_fill(m, 0.0), intra_values) + torch.matmul(probs.masked_fill(~m, 0.0), inter_values)
+    out = out.transpose(1, 2).contiguous()
+    out = out.view(*out.shape[:2], -1)
+    return self.self_attn.out_proj(out).transpose(0, 1).contiguous(), None
+
+
+def run_model_case(name, kind, seed, batch_seed, B, T, lo, hi, sqrt_softmax=False):
+    """Whole-model forward of the reference MINT-8M (6 layers, d=320, 20 heads, fp32, eval) on a seeded batch; the weights
+    are the name-keyed values of oracle/seeded_weights.py, so only tokens, chain ids and outputs are stored."""
+    sys.path.insert(0, os.path.join(HERE, "..", ".."))
+    from oracle.seeded_weights import c1_batch, fill_state_dict_
+    from mint_plus.models.esm2 import MINT
+    from mint_plus.models.modules import TransformerLayer_MINT
+    if kind == "base":
+        TransformerLayer_MINT._multimer_attention_plus = _fp32_softmax_attention
+        model = MINT(num_layers=6, embed_dim=320, attention_heads=20, use_multimer=True, use_erf_gelu=True)
+    else:
+        from mint_plus.models.mu_scaling import build_mint_mu
+        model = build_mint_mu("8M", use_sqrt_softmax=sqrt_softmax)
+    fill_state_dict_(model, seed)
+    model.eval()
+    tokens, chain_ids = c1_batch(batch_seed, B, T, lo, hi)
+    with torch.no_grad():
+        res = model(tokens, chain_ids, repr_layers=[3, 6])
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), tokens=tokens.numpy().astype(np.int16),
+                        chain_ids=chain_ids.numpy().astype(np.int8), logits=res["logits"].numpy(),
+                        repr3=res["representations"][3][:, ::8].contiguous().numpy(),
+                        repr6=res["representations"][6][:, ::8].contiguous().numpy(),
+                        meta=np.array([seed, batch_seed, B, T, lo, hi, int(sqrt_softmax)]),
+                        keys=np.array(sorted(model.state_dict().keys())))
+    print(name, "logits", tuple(res["logits"].shape), "abs max", float(res["logits"].abs().max()))
+
+
+MODEL_CASES = [
+    # name                kind    weight seed  batch seed  B  T    lo  hi   sqrt
+    ("mint8m_c1",          "base", 1234,        1001,       4, 512, 64, 200, False),   # BASELINE config 1
+    ("mint8m_small",       "base", 1235,        1002,       2, 96,  10, 40,  False),
+    ("mint8m_mu",          "mu",   1236,        1003,       2, 160, 20, 70,  False),
+    ("mint8m_mu_sqrt",     "mu",   1237,        1004,       2, 160, 20, 70,  True),
+]
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path to the mint_plus checkout")
@@ -151,6 +202,8 @@ def main():
     torch.set_grad_enabled(True)
     for c in CASES:
         run_case(*c)
+    for c in MODEL_CASES:
+        run_model_case(*c)
 
 
 if __name__ == "__main__":

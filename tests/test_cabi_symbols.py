@@ -47,7 +47,7 @@ def test_rejected_arguments_return_codes_without_touching_a_gpu():
     assert lib.mintb_attn_fwd(*args, 0, 1, 16, 32, L.F32, 0, 1.0, None, None) == L.EINVAL           # B = 0
     assert lib.mintb_attn_fwd(*args, 1, 1, 16, 32, 7, 0, 1.0, None, None) == L.EINVAL               # dtype
     assert lib.mintb_attn_fwd(*args, 1, 1, 16, 32, L.F32, L.FLAG_ROPE, 1.0, None, None) == L.EINVAL  # rope w/o tables
-    assert lib.mintb_attn_fwd(*args, 1, 1, 16, 32, L.F32, L.FLAG_SQRT_SOFTMAX, 1.0, None, None) == L.EUNSUPPORTED
+    assert lib.mintb_attn_fwd(*args, 1, 1, 16, 32, L.F32, 0x100, 1.0, None, None) == L.EINVAL                # unknown flag bit
     assert lib.mintb_attn_fwd(*args, 1, 1, 16, 32, L.F32, 0, -1.0, None, None) == L.EINVAL          # scale
     bad = [ctypes.c_void_p(256 * 1024 + 2)] + [fake] * 5 + [fake, None, None, fake, fake, None, 0]
     assert lib.mintb_attn_fwd(*bad, 1, 1, 16, 32, L.F32, 0, 1.0, None, None) == L.EINVAL            # misaligned q

@@ -1,0 +1,141 @@
+"""Whole-model parity: the MINT mirror against logits the reference MINT produced on the same name-seeded weights
+(tests/golden/mint8m_*.npz, made by tests/golden/make_golden.py).
+
+CPU tests route the attention call to the oracle (test infrastructure) to check the host logic around it — embedding,
+pad zeroing, layer glue, LM head, state-dict names; GPU tests run the product path end to end."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import mint_plus_b200 as M
+from mint_plus_b200 import modules_plus, ops
+from oracle import multimer_attention as O
+from oracle.seeded_weights import c1_batch, fill_state_dict_
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+CASES = ["mint8m_small", "mint8m_mu", "mint8m_mu_sqrt", "mint8m_c1"]
+
+
+def _load(name):
+    z = np.load(os.path.join(GOLD, name + ".npz"))
+    seed, batch_seed, B, T, lo, hi, sqrt_sm = (int(v) for v in z["meta"])
+    tokens, chain_ids = c1_batch(batch_seed, B, T, lo, hi)
+    assert np.array_equal(tokens.numpy(), z["tokens"].astype(np.int64))          # the batch is reproducible from its seed
+    assert np.array_equal(chain_ids.numpy(), z["chain_ids"].astype(np.int64))
+    return z, seed, tokens, chain_ids, bool(sqrt_sm)
+
+
+def _build(name, seed, sqrt_sm):
+    if "_mu" in name:
+        model = M.build_mint_mu("8M", use_sqrt_softmax=sqrt_sm)
+    else:
+        model = M.MINT(num_layers=6, embed_dim=320, attention_heads=20, use_multimer=True, use_erf_gelu=True)
+    fill_state_dict_(model, seed)
+    return model.eval()
+
+
+@pytest.fixture
+def oracle_attention(monkeypatch):
+    """Replace the CUDA attention by the oracle so that the model's host logic can run without a GPU."""
+    def fake_meta(chain_ids, padding_mask):
+        return chain_ids, padding_mask
+
+    def fake_attention(q_s, k_s, v_s, q_c, k_c, v_c, *, meta=None, chain_mask=None, key_padding_mask=None, rope=True,
+                       inv_freq=None, scale=None, sqrt_softmax=False, **kw):
+        if meta is not None:
+            ids, key_padding_mask = meta
+            chain_mask = ids.unsqueeze(-1) != ids.unsqueeze(-2)
+        return O.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, chain_mask, key_padding_mask, scale=scale, rope=rope,
+                                    sqrt_softmax=sqrt_softmax)
+
+    monkeypatch.setattr(modules_plus, "_cached_ids_meta", fake_meta)
+    monkeypatch.setattr(ops, "multimer_attention", fake_attention)
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_state_dict_keys_equal_the_reference_models(name):
+    z, seed, _, _, sqrt_sm = _load(name)
+    assert sorted(_build(name, seed, sqrt_sm).state_dict().keys()) == [str(k) for k in z["keys"]]
+
+
+@pytest.mark.parametrize("name", CASES[:3])
+def test_host_logic_matches_reference_logits_with_oracle_attention(name, oracle_attention):
+    z, seed, tokens, chain_ids, sqrt_sm = _load(name)
+    model = _build(name, seed, sqrt_sm)
+    with torch.no_grad():
+        res = model(tokens, chain_ids, repr_layers=[3, 6])
+    np.testing.assert_allclose(res["logits"].numpy(), z["logits"], rtol=1e-4, atol=2e-5)
+    np.testing.assert_allclose(res["representations"][3][:, ::8].numpy(), z["repr3"], rtol=1e-4, atol=2e-5)
+    np.testing.assert_allclose(res["representations"][6][:, ::8].numpy(), z["repr6"], rtol=1e-4, atol=2e-5)
+
+
+def test_product_path_refuses_cpu_tensors():
+    model = _build("mint8m_small", 1, False)
+    tokens, chain_ids = c1_batch(7, 1, 32, 4, 8)
+    with pytest.raises((RuntimeError, ValueError, TypeError)):
+        model(tokens, chain_ids)
+
+
+def test_token_dropout_rescale_and_checkpointing_in_training_mode(oracle_attention):
+    torch.manual_seed(0)
+    model = M.MINT(num_layers=2, embed_dim=64, attention_heads=4, use_multimer=True).train()
+    tokens, chain_ids = c1_batch(9, 2, 48, 5, 15)
+    tokens[0, 3] = model.mask_idx
+    out = model(tokens, chain_ids)["logits"]
+    out.float().pow(2).mean().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+    # rows that hold a <mask> are rescaled by (1 - 0.12) / (1 - observed ratio) (esm2.py:94-99 of the reference)
+    emb = model.embed_tokens(tokens)
+    n = (tokens[0] != model.padding_idx).sum()
+    x0 = emb[0, 0] * (1 - 0.12) / (1 - 1.0 / n)
+    rep = model(tokens, chain_ids, repr_layers=[0])["representations"][0]
+    torch.testing.assert_close(rep[0, 0], x0)
+    assert rep[0, 3].abs().max() == 0
+
+
+# ------------------------------------------------------------------------------------------------ GPU
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", CASES)
+def test_model_fp32_matches_reference_logits(name):
+    z, seed, tokens, chain_ids, sqrt_sm = _load(name)
+    model = _build(name, seed, sqrt_sm).cuda()
+    with torch.no_grad():
+        res = model(tokens.cuda(), chain_ids.cuda(), repr_layers=[3, 6])
+    ops.check_device_status()
+    got, want = res["logits"].cpu().numpy(), z["logits"]
+    # fp32 tolerance: 1e-5 relative to the logits' scale (values are O(1..5))
+    assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max()) * 4, np.abs(got - want).max()
+    np.testing.assert_allclose(res["representations"][6][:, ::8].cpu().numpy(), z["repr6"], rtol=1e-4, atol=4e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", CASES)
+def test_model_bf16_tracks_reference_logits(name):
+    z, seed, tokens, chain_ids, sqrt_sm = _load(name)
+    model = _build(name, seed, sqrt_sm).cuda().to(torch.bfloat16)
+    for layer in model.layers:                       # rotary tables stay fp32, as under bf16-mixed training
+        layer.self_attn.rot_emb.inv_freq = layer.self_attn.rot_emb.inv_freq.float()
+    with torch.no_grad():
+        res = model(tokens.cuda(), chain_ids.cuda())
+    ops.check_device_status()
+    got, want = res["logits"].float().cpu().numpy(), z["logits"]
+    valid = (tokens != 1).numpy()
+    err = np.abs(got - want)[valid]
+    assert err.max() < 0.25 and err.mean() < 0.03, (err.max(), err.mean())
+
+
+@pytest.mark.gpu
+def test_model_bf16_training_step_gives_finite_gradients():
+    torch.manual_seed(0)
+    model = M.MINT(num_layers=2, embed_dim=320, attention_heads=20, use_multimer=True).cuda().to(torch.bfloat16).train()
+    tokens, chain_ids = c1_batch(11, 2, 256, 30, 100)
+    out = model(tokens.cuda(), chain_ids.cuda())["logits"]
+    loss = torch.nn.functional.cross_entropy(out.float().view(-1, 33), tokens.cuda().view(-1), ignore_index=1)
+    loss.backward()
+    ops.check_device_status()
+    assert torch.isfinite(loss)
+    for n, p in model.named_parameters():
+        assert p.grad is not None and torch.isfinite(p.grad).all(), n
