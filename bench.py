@@ -113,6 +113,15 @@ def cpu_baseline(seconds_budget=20.0):
                       f"median of {len(times)} steps after 1 warm-up, {sec:.2f} s each"}, sec
 
 
+def load_peaks():
+    """Roofline denominators: the measured figures file if present, else the stated fallback."""
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        with open(peaks_path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
 def run_reference(args, rank, world):
     """The reference's CPU implementation of the path (oracle port; the reference itself is Python + Triton and its
     checkout is not on the GPU box), timed on the host cores with every thread."""
@@ -153,11 +162,31 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="attn",
+                    help="attn (default: the isolated attention op) or a whole-model workload of bench_model.py: "
+                         "mint650m_fp8, mint150m_lora, mint3b_infer, mint8m_fwd")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload != "attn":
+        import bench_model
+        if args.workload not in bench_model.WORKLOADS:
+            raise SystemExit(f"unknown workload {args.workload!r}; choose attn or one of {sorted(bench_model.WORKLOADS)}")
+        if args.impl == "reference":
+            bench_model.run_reference(args.workload, args, rank)
+            return
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        peaks, peak_src = load_peaks()
+        bench_model.run(args.workload, args, rank, world, local, ClockSampler, peaks, peak_src)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
@@ -300,11 +329,7 @@ def main():
     total_flops_step = float(work.item())
 
     if rank == 0:
-        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        if os.path.exists(peaks_path):
-            peaks, peak_src = json.load(open(peaks_path)), "measured"
-        else:
-            peaks, peak_src = FALLBACK_PEAKS, "fallback"
+        peaks, peak_src = load_peaks()
         value = total_flops_step * steps / (ms_total * 1e-3) / 1e12
         fwd_t, bwd_t = statistics.mean(fwd_ms), statistics.mean(bwd_ms)
         dom = ("attention backward call", flops_bwd, bwd_t) if bwd_t >= fwd_t else ("attention forward call", flops_fwd, fwd_t)

@@ -1,0 +1,326 @@
+"""Whole-model workloads of bench.py (`--workload mint650m_fp8 | mint150m_lora | mint3b_infer | mint8m_fwd`).
+
+Each is one of the reference's model-level configurations on seeded synthetic protein pairs (tokens uniform over the 20
+amino-acid ids, `<cls> A <eos> <cls> B <eos>`, padded with id 1; chain ids 0/1), random-init weights of the named
+architecture.  A step is one forward (+ backward) over the rank's batch of pairs; the metric is pairs per second over all
+ranks.  Pairs shard across ranks with no data-path collective; training workloads add one flat all-reduce of the trainable
+gradients per step.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import statistics
+import time
+
+import torch
+
+WORKLOADS = {
+    # BASELINE configuration 4
+    "mint650m_fp8": dict(layers=33, embed=1280, heads=20, pairs=16, T=2048, lo=100, hi=900, seed=4004, train=True,
+                         kind="mu_fp8", dtype="e4m3 GEMMs / bf16 attention",
+                         desc="MINT-650M muS Res-Post-LN, e4m3 projections, bf16 attention, fwd+bwd, 16 pairs padded to 2048"),
+    # BASELINE configuration 3
+    "mint150m_lora": dict(layers=30, embed=640, heads=20, pairs=32, T=1024, lo=50, hi=500, seed=3003, train=True,
+                          kind="lora", dtype="bf16",
+                          desc="MINT-150M frozen base + LoRA r=8 on q/k/v/out, bf16, training step, 32 pairs padded to 1024"),
+    # BASELINE configuration 5
+    "mint3b_infer": dict(layers=36, embed=2560, heads=40, pairs=64, T=2048, lo=30, hi=80, lo2=800, hi2=1900, seed=5005,
+                         train=False, kind="plus", dtype="bf16",
+                         desc="MINT 36x2560 (40 heads) inference forward, bf16, 64 pairs with skewed chain lengths padded to 2048"),
+    # BASELINE configuration 1 (a latency line; its parity is a test)
+    "mint8m_fwd": dict(layers=6, embed=320, heads=20, pairs=4, T=512, lo=64, hi=200, seed=1001, train=False,
+                       kind="base_fp32", dtype="f32",
+                       desc="MINT-8M forward, fp32, 4 pairs padded to 512"),
+}
+
+
+def make_pairs(cfg, rank=0):
+    g = torch.Generator().manual_seed(cfg["seed"] + 7919 * rank)
+    B, T = cfg["pairs"], cfg["T"]
+    tokens = torch.full((B, T), 1, dtype=torch.int64)
+    chain_ids = torch.zeros(B, T, dtype=torch.int64)
+    for b in range(B):
+        la = int(torch.randint(cfg["lo"], cfg["hi"] + 1, (1,), generator=g))
+        lb = int(torch.randint(cfg.get("lo2", cfg["lo"]), cfg.get("hi2", cfg["hi"]) + 1, (1,), generator=g))
+        a = torch.randint(4, 24, (la,), generator=g)
+        c = torch.randint(4, 24, (lb,), generator=g)
+        row = torch.cat([torch.tensor([0]), a, torch.tensor([2, 0]), c, torch.tensor([2])])
+        tokens[b, :row.numel()] = row
+        chain_ids[b, la + 2:] = 1
+    return tokens, chain_ids
+
+
+def mlm_corrupt(tokens, seed, mask_idx=32):
+    """15 % of the non-special positions become targets; of those 80 % -> <mask>, 10 % -> random amino acid, 10 % kept
+    (training/wrapper.py:57-73 of the reference)."""
+    g = torch.Generator().manual_seed(seed)
+    special = (tokens < 4)
+    pick = (torch.rand(tokens.shape, generator=g) < 0.15) & ~special
+    labels = torch.where(pick, tokens, torch.full_like(tokens, -100))
+    r = torch.rand(tokens.shape, generator=g)
+    out = tokens.clone()
+    out[pick & (r < 0.8)] = mask_idx
+    rnd = torch.randint(4, 24, tokens.shape, generator=g)
+    swap = pick & (r >= 0.8) & (r < 0.9)
+    out[swap] = rnd[swap]
+    return out, labels
+
+
+def build_model(cfg, device):
+    import mint_plus_b200 as M
+    from mint_plus_b200.lora import apply_lora
+    torch.manual_seed(cfg["seed"])
+    L_, E_, H_ = cfg["layers"], cfg["embed"], cfg["heads"]
+    kind = cfg["kind"]
+    with torch.device(device):          # parameters are created (and initialised) on the GPU
+        if kind == "mu_fp8":
+            model = M.build_mint_mu("650M", num_layers=L_, embed_dim=E_, attention_heads=H_, use_fp8=True, unit_scaled=True)
+        elif kind == "lora":
+            model = M.MINT(num_layers=L_, embed_dim=E_, attention_heads=H_, use_multimer=True)
+        elif kind == "plus":
+            model = M.MINT(num_layers=L_, embed_dim=E_, attention_heads=H_, use_multimer=True,
+                           layer_factory=lambda: M.TransformerLayer_MINT_plus(E_, 4 * E_, H_, use_multimer=True))
+        else:
+            model = M.MINT(num_layers=L_, embed_dim=E_, attention_heads=H_, use_multimer=True, use_erf_gelu=True)
+    if kind != "base_fp32":
+        model = model.to(torch.bfloat16)
+    model = model.to(device)
+    for layer in model.layers:           # rotary tables in fp32 whatever the model dtype (as under bf16-mixed training)
+        rot = layer.self_attn.rot_emb
+        if rot is not None:
+            rot.inv_freq = rot.inv_freq.float()
+    if kind == "lora":
+        apply_lora(model, r=8, alpha=16.0)
+        with torch.no_grad():           # B = 0 would make dA identically zero at step 0: draw B ~ N(0, 0.02) instead
+            for n, p in model.named_parameters():
+                if n.endswith("lora_B"):
+                    p.normal_(0.0, 0.02)
+    model.train(cfg["train"])
+    return model
+
+
+def algorithmic_flops(cfg, tokens):
+    """GEMMs: 30 E^2 per token per layer forward (both QKV projections, out_proj, FFN), x3 with dgrad+wgrad, x2 when the
+    weights are frozen (LoRA; the low-rank terms are left out).  Attention: 4 H T Tk D forward, 14 with backward, Tk = the
+    sample's unpadded keys, every query row of the padded length counted as the reference computes them."""
+    L_, E_, H_ = cfg["layers"], cfg["embed"], cfg["heads"]
+    D = E_ // H_
+    B, T = tokens.shape
+    tk = (tokens != 1).sum(1).double()
+    gemm_fwd = 30.0 * E_ * E_ * B * T * L_
+    attn_fwd = float((4.0 * H_ * T * tk * D).sum()) * L_
+    if not cfg["train"]:
+        return gemm_fwd + attn_fwd, gemm_fwd, attn_fwd
+    gemm = gemm_fwd * (2.0 if cfg["kind"] == "lora" else 3.0)
+    return gemm + 3.5 * attn_fwd, gemm, 3.5 * attn_fwd
+
+
+def cpu_baseline(cfg, seconds_budget=25.0):
+    """The same model restated on the host cores: the package's host-side model with its attention call routed to the
+    oracle, fp32.  One layer on one pair is timed (forward, plus backward for training workloads) and scaled by layers x
+    pairs — an extrapolation, stated as such."""
+    import mint_plus_b200 as M
+    from mint_plus_b200 import modules_plus, ops
+    from oracle import multimer_attention as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    E_, H_, T = cfg["embed"], cfg["heads"], cfg["T"]
+    sub = dict(cfg, pairs=1)
+    tokens, chain_ids = make_pairs(sub)
+    layer = M.TransformerLayer_MINT(E_, 4 * E_, H_, use_multimer=True)
+    layer.train(cfg["train"])
+    pad = tokens.eq(1)
+    mask = chain_ids.unsqueeze(-1) != chain_ids.unsqueeze(-2)
+
+    def oracle_attention(q_s, k_s, v_s, q_c, k_c, v_c, *, chain_mask=None, key_padding_mask=None, rope=True, scale=None,
+                         sqrt_softmax=False, **kw):
+        return O.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, chain_mask, key_padding_mask, scale=scale, rope=rope,
+                                    sqrt_softmax=sqrt_softmax)
+
+    saved = ops.multimer_attention
+    ops.multimer_attention = oracle_attention
+    try:
+        x = torch.randn(T, 1, E_, requires_grad=cfg["train"])
+        times = []
+        t_end = time.perf_counter() + seconds_budget
+        for it in range(4):
+            t0 = time.perf_counter()
+            with torch.set_grad_enabled(cfg["train"]):
+                y, _ = layer(x, self_attn_mask=mask, self_attn_padding_mask=pad)
+                if cfg["train"]:
+                    y.square().mean().backward()
+            dt = time.perf_counter() - t0
+            if it > 0 or time.perf_counter() > t_end:
+                times.append(dt)
+            if time.perf_counter() > t_end:
+                break
+    finally:
+        ops.multimer_attention = saved
+    sec_layer_pair = statistics.median(times)
+    sec_pair = sec_layer_pair * cfg["layers"]
+    return {"value": 1.0 / sec_pair, "unit": "pairs/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"one layer on one pair (T={T}, E={E_}), fp32, {'fwd+bwd' if cfg['train'] else 'fwd'}: "
+                      f"{sec_layer_pair:.2f} s (median of {len(times)}), extrapolated x{cfg['layers']} layers"}
+
+
+def run_reference(name, args, rank):
+    if rank != 0:
+        return
+    cfg = WORKLOADS[name]
+    base = cpu_baseline(cfg, seconds_budget=min(60.0, 10.0 * max(1, args.steps)))
+    line = {"impl": "reference", "metric": "ppi_pairs_per_sec", "value": base["value"], "unit": "pairs/s",
+            "n_gpus": args.gpus, "steps": 1, "warmup": 1, "ms_per_step": 1e3 * cfg["pairs"] / base["value"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": cfg["desc"], "device": "cpu"}, "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "pairs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run(name, args, rank, world, local, ClockSampler, peaks, peak_src):
+    import torch.distributed as dist
+    from mint_plus_b200 import _lib as L, ops
+    from mint_plus_b200.distributed import FlatGradAllReduce, reduce_max, reduce_sum
+
+    cfg = WORKLOADS[name]
+    dev = torch.device("cuda", local)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    model = build_model(cfg, dev)
+    tokens, chain_ids = make_pairs(cfg, rank)
+    labels = None
+    if cfg["train"]:
+        tokens_in, labels = mlm_corrupt(tokens, cfg["seed"] + rank)
+    else:
+        tokens_in = tokens
+    h_tok, h_cid = tokens_in.pin_memory(), chain_ids.pin_memory()
+    h_lab = labels.pin_memory() if labels is not None else None
+    flops_step, flops_gemm, flops_attn = algorithmic_flops(cfg, tokens)
+    trainable = [p for p in model.parameters() if p.requires_grad] if cfg["train"] else []
+    sync_grads = FlatGradAllReduce(trainable, dtype=torch.float32 if cfg["kind"] == "lora" else torch.bfloat16) \
+        if (cfg["train"] and world > 1) else None
+    lib = L.lib()
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+    out_host = None
+
+    def step(tok, cid, lab):
+        if cfg["train"]:
+            for p in trainable:
+                p.grad = None
+            logits = model(tok, cid)["logits"]
+            loss = torch.nn.functional.cross_entropy(logits.float().view(-1, logits.shape[-1]), lab.view(-1), ignore_index=-100)
+            loss.backward()
+            if sync_grads is not None:
+                sync_grads()
+            return loss.detach()
+        with torch.no_grad():
+            res = model(tok, cid, repr_layers=[cfg["layers"]])
+            return res["representations"][cfg["layers"]]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    d_tok, d_cid = h_tok.to(dev), h_cid.to(dev)
+    d_lab = h_lab.to(dev) if h_lab is not None else None
+    for _ in range(warmup):
+        step(d_tok, d_cid, d_lab)
+    barrier()
+    launches0 = lib.mintb_kernel_launches()
+    step(d_tok, d_cid, d_lab)
+    launches_per_step = lib.mintb_kernel_launches() - launches0
+    barrier()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    barrier()
+    for s, e in ev:             # every step touches gigabytes of activations and weights: far more than the 126 MB L2
+        s.record()
+        step(d_tok, d_cid, d_lab)
+        e.record()
+    barrier()
+    ms_total = sum(s.elapsed_time(e) for s, e in ev)
+
+    # end to end: tokens, chain ids (and labels) from pinned host memory; loss / mean-pooled embedding back to the host
+    e2e_steps = min(steps, 10)
+    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(e2e_steps)]
+    h2d = h_tok.numel() * 8 + h_cid.numel() * 8 + (h_lab.numel() * 8 if h_lab is not None else 0)
+    d2h = 4
+    if not cfg["train"]:
+        out_host = torch.empty(cfg["pairs"], cfg["embed"], dtype=torch.float32).pin_memory()
+        d2h = out_host.numel() * 4
+    barrier()
+    for s, e in ev2:
+        s.record()
+        tok, cid = h_tok.to(dev, non_blocking=True), h_cid.to(dev, non_blocking=True)
+        lab = h_lab.to(dev, non_blocking=True) if h_lab is not None else None
+        r = step(tok, cid, lab)
+        if cfg["train"]:
+            loss_host.copy_(r.float().view(1), non_blocking=True)
+        else:                                                       # embedding extraction: mean over unpadded positions
+            keep = (tok != 1).unsqueeze(-1)
+            out_host.copy_(((r.float() * keep).sum(1) / keep.sum(1)), non_blocking=True)
+        e.record()
+    barrier()
+    e2e_ms = sum(s.elapsed_time(e) for s, e in ev2)
+    clocks = sampler.finish()
+    ops.check_device_status(dev)
+
+    # the largest projection GEMM of the model in isolation (fc1: [pairs*T, E] x [4E, E]^T), for the roofline entry
+    E_ = cfg["embed"]
+    Mtok = cfg["pairs"] * cfg["T"]
+    gemm = None
+    if cfg["kind"] != "base_fp32":
+        x = torch.randn(Mtok, E_, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(4 * E_, E_, device=dev, dtype=torch.bfloat16) / math.sqrt(E_)
+        b = torch.zeros(4 * E_, device=dev, dtype=torch.bfloat16)
+        if cfg["kind"] == "mu_fp8":
+            xq, wq = ops.quantize_e4m3(x, 1.0), ops.quantize_e4m3(w, 1.0)
+            fn = lambda: ops.gemm_e4m3(xq, wq, 1.0, b, True)
+            peak, peak_name = peaks.get("fp8_tflops", 2.0 * peaks["bf16_tflops"]), "2 x measured bf16 peak (no measured e4m3 figure)"
+            if "fp8_tflops" in peaks:
+                peak_name = "measured e4m3 peak"
+        else:
+            fn = lambda: ops.gemm_bf16(x, w, b, True)
+            peak, peak_name = peaks["bf16_tflops"], f"{peak_src} bf16 peak"
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        evs = []
+        for _ in range(10):
+            a, c = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); c.record()
+            evs.append((a, c))
+        torch.cuda.synchronize()
+        g_ms = statistics.median(a.elapsed_time(c) for a, c in evs)
+        g_tf = 2.0 * Mtok * E_ * 4 * E_ / (g_ms * 1e-3) / 1e12
+        gemm = {"ms": g_ms, "tflops": g_tf, "peak": peak, "peak_name": peak_name}
+
+    ms_total, e2e_ms = reduce_max([ms_total, e2e_ms], dev)
+    pairs_total, flops_total = reduce_sum([cfg["pairs"], flops_step], dev)
+    if rank == 0:
+        value = pairs_total * steps / (ms_total * 1e-3)
+        tf = flops_total * steps / (ms_total * 1e-3) / 1e12 / world            # per GPU
+        roof = {"bound": "tensor", "kernel": "whole step (all kernels and library calls)", "achieved": tf,
+                "peak": peaks["bf16_tflops_sustained"] if "bf16_tflops_sustained" in peaks else peaks["bf16_tflops"],
+                "unit": "TFLOP/s", "traffic": None, "peak_source": peak_src + " (sustained bf16)",
+                "flops_per_step": flops_step, "gemm_flops": flops_gemm, "attention_flops": flops_attn}
+        roof["frac"] = roof["achieved"] / roof["peak"]
+        if gemm is not None:
+            roof["largest_gemm"] = {"shape": [Mtok, 4 * E_, E_], "epilogue": "bias + erf-GELU", **gemm,
+                                    "frac": gemm["tflops"] / gemm["peak"]}
+        line = {"metric": "ppi_pairs_per_sec", "value": value, "unit": "pairs/s", "n_gpus": world, "steps": steps,
+                "warmup": warmup, "ms_per_step": ms_total / steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
+                "config": {"workload": cfg["desc"] + " per GPU", "l2": "working set per step far exceeds L2 (no flush)",
+                           "launch": "eager", "checkpointing": "per layer" if cfg["train"] else "none",
+                           "grad_allreduce_bytes": sync_grads.nbytes if sync_grads is not None else 0},
+                "roofline": roof,
+                "e2e": {"value": pairs_total * e2e_steps / (e2e_ms * 1e-3), "unit": "pairs/s", "h2d_bytes_per_step": h2d,
+                        "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
+                "gpu_launches": int(launches_per_step * steps), "clocks": clocks}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(cfg)
+        print(json.dumps(line), flush=True)

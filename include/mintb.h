@@ -146,6 +146,7 @@ MINTB_API int mintb_combine_bwd(const void* intra_logits, const void* inter_logi
  * bf16 or, multiplied by out_scale and saturated to +-448, as e4m3.  Replaces nn.Linear / te.Linear forward for out_proj,
  * fc1(+GELU), fc2 (attention.py:68, modules.py:326-334, mu_scaling/__init__.py:83-124).  For e4m3 operands alpha is the
  * product of the two per-tensor dequantisation scales times any static output multiplier (alt/munit_scaling.py:22-34).
+ * With `gelu`, a non-null `preact_out` (bf16 [M][N]) also receives alpha * x w^T + bias, which the GELU backward reads.
  *
  * mintb_qkv_fwd: the fused QKV projection of one pathway (attention.py:97-117, 304-323): x is (T,B,E) flattened to
  * [T*B][E], w [3E][E] with rows ordered [Q;K;V]; q, k, v are written head-major (B,H,T,D) directly (no permute copy),
@@ -153,13 +154,40 @@ MINTB_API int mintb_combine_bwd(const void* intra_logits, const void* inter_logi
  *
  * mintb_quantize_e4m3: out[i] = saturate(x[i] * inv_scale) from bf16 (the per-tensor scaled cast of the FP8 path).
  */
-MINTB_API int mintb_linear_fwd(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, int in_dtype,
-                               int bias_dtype, int out_dtype, int gelu, float alpha, float out_scale, void* stream,
+MINTB_API int mintb_linear_fwd(const void* x, const void* w, const void* bias, void* out, void* preact_out, int M, int N, int K,
+                               int in_dtype, int bias_dtype, int out_dtype, int gelu, float alpha, float out_scale, void* stream,
                                int* dev_status);
 MINTB_API int mintb_qkv_fwd(const void* x, const void* w, const void* bias, void* q, void* k, void* v, int T, int B, int H,
                             int D, int in_dtype, int bias_dtype, float alpha, float q_scale, const float* rope_cos,
                             const float* rope_sin, void* stream, int* dev_status);
 MINTB_API int mintb_quantize_e4m3(const void* x, void* out, size_t n, float inv_scale, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * HBM-bound glue of the layer around the GEMMs and the attention (bf16 tensors [rows][E] / [M][N], fp32 arithmetic).
+ *
+ * mintb_add_layernorm_fwd: s = a x + b r (r may be null), y = LayerNorm(s) * gamma + beta over the last dimension.
+ *   Replaces the residual add + ESM1bLayerNorm pairs of the Pre-LN layer (modules.py:179-195: a = b = 1) and the weighted
+ *   residuals + final norm of the muS layer (mu_scaling/layer.py:259-280: a = sqrt(1 - tau), b = sqrt(tau)).  gamma null:
+ *   no normalisation, only s_out is written.  Otherwise y_out is written, s_out if non-null, and stats[rows] = (mean, rstd)
+ *   (2 floats per row) if non-null.  E must be a multiple of 8, at most 2560; gamma / beta are f32 or bf16 (param_dtype).
+ * mintb_add_layernorm_bwd: ds = dLayerNorm(dy) + ds_in (either part may be absent), dx = a ds, dr = b ds (dr may be null),
+ *   dgamma / dbeta (fp32 [E]) summed in a fixed order through the workspace.
+ * mintb_gelu_bwd_colsum: with z: dz = dy * gelu'(z) (erf form, modules.py:16-23) and db[N] = column sums of dz (db may be
+ *   null); without z: db = column sums of dy (the bias gradient of a projection).  N a multiple of 8.
+ * mintb_qkv_grad_pack: the gradients of head-major q, k, v (B,H,T,D) gathered into one [T*B][3E] matrix with columns
+ *   [dQ | dK | dV], dq multiplied by q_scale and dq, dk un-rotated (transpose of the RoPE rotation) when tables are given:
+ *   the inverse of mintb_qkv_fwd's epilogue, feeding the dgrad / wgrad products of the fused QKV projection.
+ */
+MINTB_API int mintb_add_layernorm_fwd(const void* x, const void* r, float a, float b, const void* gamma, const void* beta,
+                                      int param_dtype, void* s_out, void* y_out, float* stats, int rows, int E, float eps,
+                                      void* stream);
+MINTB_API size_t mintb_add_layernorm_bwd_workspace_bytes(int rows, int E);
+MINTB_API int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const void* x, const void* r, float a, float b,
+                                      const void* gamma, int param_dtype, const float* stats, void* dx, void* dr, float* dgamma,
+                                      float* dbeta, void* workspace, size_t workspace_bytes, int rows, int E, void* stream);
+MINTB_API int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, int M, int N, void* stream);
+MINTB_API int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g, const float* rope_cos,
+                                  const float* rope_sin, int T, int B, int H, int D, float q_scale, void* stream);
 
 #ifdef __cplusplus
 }

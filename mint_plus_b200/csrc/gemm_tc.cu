@@ -34,6 +34,7 @@ struct GemmParams {
   float out_scale;             // multiplies the result before the cast to e4m3
   const void* bias;            // [N] or null
   void* out;                   // row-major [M][N]
+  __nv_bfloat16* preact;       // GELU epilogue: when non-null, alpha * x w^T + bias is also stored here (bf16 [M][N])
   // head-major scatter: row m = t * B + b, column n = which * E + h * D + d  ->  dst[which][((b * H + h) * T + t) * D + d]
   __nv_bfloat16* qkv[3];
   int B, T, H, D;
@@ -226,11 +227,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           }
         } else {
+          const int n = n0 + c0;
           if constexpr (EPI == kEpiBiasGelu) {
+            if (p.preact != nullptr && m < p.M) {   // the backward pass reads the pre-activation instead of recomputing it
+              __nv_bfloat16* dst = p.preact + size_t(m) * p.N + n;
+              if (n + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8)
+                  *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                                                                  pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (n + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+              }
+            }
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = gelu_erf_f(v[j]);
           }
-          const int n = n0 + c0;
           if (m < p.M) {
             if (p.out_dtype == MINTB_BF16) {
               __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + size_t(m) * p.N + n;
@@ -384,8 +398,8 @@ static int check_gemm(const char* who, const void* x, const void* w, int M, int 
   return MINTB_OK;
 }
 
-extern "C" int mintb_linear_fwd(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, int in_dtype,
-                                int bias_dtype, int out_dtype, int gelu, float alpha, float out_scale, void* stream,
+extern "C" int mintb_linear_fwd(const void* x, const void* w, const void* bias, void* out, void* preact_out, int M, int N, int K,
+                                int in_dtype, int bias_dtype, int out_dtype, int gelu, float alpha, float out_scale, void* stream,
                                 int* dev_status) {
   int rc = check_gemm("mintb_linear_fwd", x, w, M, N, K, in_dtype);
   if (rc != MINTB_OK) return rc;
@@ -394,10 +408,15 @@ extern "C" int mintb_linear_fwd(const void* x, const void* w, const void* bias, 
     set_error("mintb_linear_fwd: out must be a 16-byte aligned bf16 (N a multiple of 8) or e4m3 buffer");
     return MINTB_EINVAL;
   }
+  if (preact_out != nullptr && (!gelu || N % 8 != 0 || (reinterpret_cast<uintptr_t>(preact_out) & 15))) {
+    set_error("mintb_linear_fwd: preact_out goes with gelu, N a multiple of 8 and a 16-byte aligned buffer");
+    return MINTB_EINVAL;
+  }
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.in_dtype = in_dtype; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype;
   p.epilogue = gelu ? kEpiBiasGelu : kEpiBias;
   p.alpha = alpha; p.out_scale = out_scale; p.bias = bias; p.out = out; p.status = dev_status;
+  p.preact = static_cast<__nv_bfloat16*>(preact_out);
   return launch_gemm(p, x, w, static_cast<cudaStream_t>(stream));
 }
 

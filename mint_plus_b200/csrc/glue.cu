@@ -1,0 +1,464 @@
+// HBM-bound kernels around the projection GEMMs and the attention (bf16 tensors, fp32 arithmetic):
+//
+//   add_layernorm_fwd / _bwd   s = a x + b r, y = LayerNorm(s) gamma + beta  — the residual-and-norm glue of the Pre-LN layer
+//                              (a = b = 1; modules.py:179-195 of the reference) and of the muS layer (a = sqrt(1 - tau),
+//                              b = sqrt(tau); mu_scaling/layer.py:259-280); without gamma it is the scaled residual add alone.
+//   gelu_bwd_colsum            dz = dy * gelu'(z) and the bias gradient sum_rows(dz) in the same pass; without z the column
+//                              sum of dy alone (bias gradient of a plain projection).
+//   qkv_grad_pack              gradients of the head-major q, k, v (B,H,T,D) -> one row-major [T*B][3E] matrix for the
+//                              dgrad / wgrad products: un-rotates dq and dk of the self pathway (transpose of the RoPE
+//                              rotation) and applies the q scale.
+//
+// Every kernel reads each input once and writes each output once, 16 bytes per thread and access, rows walked by whole warps.
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace mintb {
+namespace {
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+__device__ __forceinline__ float ld_param(const void* p, int dtype, int i) {
+  return dtype == MINTB_F32 ? static_cast<const float*>(p)[i] : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+constexpr int kLnWarps = 4;
+
+struct LnParams {
+  const __nv_bfloat16 *x, *r;       // r may be null (then s = a x)
+  float a, b;
+  const void *gamma, *beta;         // null: no normalisation, only s
+  int param_dtype;                  // MINTB_F32 or MINTB_BF16
+  __nv_bfloat16 *s_out, *y_out;     // either may be null
+  float2* stats;                    // [rows] (mean, rstd); written by forward, read by backward
+  const __nv_bfloat16 *dy, *ds_in;  // backward inputs (either may be null)
+  __nv_bfloat16 *dx, *dr;           // backward outputs (dr may be null)
+  float* partial;                   // backward: [gridDim.x][2][E] sums of dy * xhat and of dy
+  int rows, E;
+  float eps;
+};
+
+// MAXV: 16-byte vectors per lane (E <= MAXV * 256)
+template <int MAXV>
+__global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_fwd_kernel(LnParams p) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int nvec = p.E / 8;
+  const float inv_e = 1.f / float(p.E);
+  for (int row = blockIdx.x * kLnWarps + warp; row < p.rows; row += gridDim.x * kLnWarps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(p.x + size_t(row) * p.E);
+    const uint4* rr = p.r != nullptr ? reinterpret_cast<const uint4*>(p.r + size_t(row) * p.E) : nullptr;
+    float v[MAXV][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        float xv[8];
+        unpack8(__ldg(xr + vi), xv);
+        if (rr != nullptr) {
+          float rv[8];
+          unpack8(__ldg(rr + vi), rv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[k][j] = fmaf(p.a, xv[j], p.b * rv[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[k][j] = p.a * xv[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum += v[k][j];
+        if (p.s_out != nullptr) reinterpret_cast<uint4*>(p.s_out + size_t(row) * p.E)[vi] = pack8(v[k]);
+      }
+    }
+    if (p.gamma == nullptr) continue;
+    const float mean = warp_sum_f(sum) * inv_e;
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      if (lane + 32 * k < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = v[k][j] - mean;
+          sq = fmaf(d, d, sq);
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum_f(sq) * inv_e + p.eps);
+    if (lane == 0 && p.stats != nullptr) p.stats[row] = make_float2(mean, rstd);
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          o[j] = fmaf((v[k][j] - mean) * rstd, ld_param(p.gamma, p.param_dtype, vi * 8 + j),
+                      p.beta != nullptr ? ld_param(p.beta, p.param_dtype, vi * 8 + j) : 0.f);
+        reinterpret_cast<uint4*>(p.y_out + size_t(row) * p.E)[vi] = pack8(o);
+      }
+    }
+  }
+}
+
+// ds = LayerNorm'(dy) + ds_in;  dx = a ds;  dr = b ds;  per-CTA partial sums for dgamma / dbeta.
+// LayerNorm backward per row: g = dy gamma, xhat = (s - mean) rstd, ds = rstd (g - mean(g) - xhat mean(g xhat)).
+template <int MAXV>
+__global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_bwd_kernel(LnParams p) {
+  extern __shared__ float ln_smem[];   // [kLnWarps][2][E] when normalising
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int nvec = p.E / 8;
+  const float inv_e = 1.f / float(p.E);
+  const bool norm = p.gamma != nullptr;
+  float* acc_g = ln_smem + size_t(warp) * 2 * p.E;   // sum dy * xhat
+  float* acc_b = acc_g + p.E;                        // sum dy
+  if (norm) {
+    for (int i = lane; i < 2 * p.E; i += 32) acc_g[i] = 0.f;
+    __syncwarp();
+  }
+  for (int row = blockIdx.x * kLnWarps + warp; row < p.rows; row += gridDim.x * kLnWarps) {
+    const size_t off = size_t(row) * p.E;
+    float ds[MAXV][8];
+    if (norm) {
+      const float2 st = p.stats[row];
+      float xh[MAXV][8];
+      float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+      for (int k = 0; k < MAXV; ++k) {
+        const int vi = lane + 32 * k;
+        if (vi < nvec) {
+          float xv[8], dyv[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(p.x + off) + vi), xv);
+          unpack8(__ldg(reinterpret_cast<const uint4*>(p.dy + off) + vi), dyv);
+          if (p.r != nullptr) {
+            float rv[8];
+            unpack8(__ldg(reinterpret_cast<const uint4*>(p.r + off) + vi), rv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) xv[j] = fmaf(p.a, xv[j], p.b * rv[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) xv[j] *= p.a;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float xhat = (xv[j] - st.x) * st.y;
+            const float g = dyv[j] * ld_param(p.gamma, p.param_dtype, vi * 8 + j);
+            xh[k][j] = xhat;
+            ds[k][j] = g;
+            c1 += g;
+            c2 = fmaf(g, xhat, c2);
+            // this lane alone touches these entries; element e = 8 vi + j sits at j * nvec + vi (no bank conflicts)
+            acc_g[j * nvec + vi] = fmaf(dyv[j], xhat, acc_g[j * nvec + vi]);
+            acc_b[j * nvec + vi] += dyv[j];
+          }
+        }
+      }
+      c1 = warp_sum_f(c1) * inv_e;
+      c2 = warp_sum_f(c2) * inv_e;
+#pragma unroll
+      for (int k = 0; k < MAXV; ++k) {
+        if (lane + 32 * k < nvec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ds[k][j] = st.y * (ds[k][j] - c1 - xh[k][j] * c2);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ds[k][j] = 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        if (p.ds_in != nullptr) {
+          float e[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(p.ds_in + off) + vi), e);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ds[k][j] += e[j];
+        }
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = p.a * ds[k][j];
+        reinterpret_cast<uint4*>(p.dx + off)[vi] = pack8(o);
+        if (p.dr != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = p.b * ds[k][j];
+          reinterpret_cast<uint4*>(p.dr + off)[vi] = pack8(o);
+        }
+      }
+    }
+  }
+  if (norm) {
+    __syncthreads();
+    float* dst = p.partial + size_t(blockIdx.x) * 2 * p.E;
+    for (int i = threadIdx.x; i < 2 * p.E; i += kLnWarps * 32) {
+      const int which = i / p.E, e = i % p.E;
+      const int src = which * p.E + (e % 8) * nvec + e / 8;
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < kLnWarps; ++w) t += ln_smem[size_t(w) * 2 * p.E + src];
+      dst[i] = t;
+    }
+  }
+}
+
+// dgamma[e] = sum over CTAs of partial[c][0][e], dbeta likewise; fixed order.
+__global__ void __launch_bounds__(256) ln_param_grad_kernel(const float* __restrict__ partial, int n_parts, int E, float* __restrict__ dgamma,
+                                                            float* __restrict__ dbeta) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 2 * E) return;
+  float t = 0.f;
+  for (int c = 0; c < n_parts; ++c) t += partial[size_t(c) * 2 * E + i];
+  if (i < E) dgamma[i] = t; else dbeta[i - E] = t;
+}
+
+// ------------------------------------------------------------------------------------------------ GELU backward + column sums
+constexpr int kColRows = 256;   // rows per CTA strip
+
+__device__ __forceinline__ float gelu_erf_grad(float z) {
+  return 0.5f * (1.f + erff(z * 0.70710678118654752f)) + z * __expf(-0.5f * z * z) * 0.3989422804014327f;
+}
+
+// Thread = 8 consecutive columns; CTA = 128 column groups x a strip of kColRows rows.  db gets one atomicAdd per thread.
+__global__ void __launch_bounds__(128) gelu_bwd_colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ z,
+                                                              __nv_bfloat16* __restrict__ dz, float* __restrict__ db, int M, int N) {
+  const int cg = blockIdx.x * 128 + threadIdx.x;   // column group
+  if (cg * 8 >= N) return;
+  const int m0 = blockIdx.y * kColRows, m1 = min(M, m0 + kColRows);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int m = m0; m < m1; ++m) {
+    const size_t off = size_t(m) * N + size_t(cg) * 8;
+    float g[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(dy + off)), g);
+    if (z != nullptr) {
+      float zv[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(z + off)), zv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] *= gelu_erf_grad(zv[j]);
+      const uint4 packed = pack8(g);
+      *reinterpret_cast<uint4*>(dz + off) = packed;
+      unpack8(packed, g);   // the bias gradient sums what the products will read
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += g[j];
+  }
+  if (db != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(db + size_t(cg) * 8 + j, acc[j]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ QKV gradient pack
+// g[(t * B + b)][which * E + h * D + d] = f(dsrc[which][b][h][t][d]), f = q scale and the transposed rotation for dq, dk.
+// Thread = one (row, which, head, 8 dims); for the rotation it also reads the partner half's 8 values.
+template <int D>
+__global__ void __launch_bounds__(256) qkv_grad_pack_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
+                                                            const __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ g,
+                                                            const float* __restrict__ cos_tab,
+                                                            const float* __restrict__ sin_tab, int T, int B, int H, float q_scale) {
+  constexpr int VPH = D / 8;                         // vectors per head
+  const int E = H * D;
+  const int vecs_per_row = 3 * H * VPH;
+  const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t total = size_t(T) * B * vecs_per_row;
+  if (idx >= total) return;
+  const int vr = int(idx % vecs_per_row);
+  const size_t row = idx / vecs_per_row;             // t * B + b
+  const int t = int(row / B), b = int(row % B);
+  const int which = vr / (H * VPH), hv = vr % (H * VPH), h = hv / VPH, dv8 = hv % VPH;
+  const __nv_bfloat16* src = which == 0 ? dq : (which == 1 ? dk : dv);
+  const size_t base = ((size_t(b) * H + h) * T + t) * D;
+  float v[8];
+  unpack8(__ldg(reinterpret_cast<const uint4*>(src + base) + dv8), v);
+  if (cos_tab != nullptr && which < 2) {
+    // y = R x rotated forward: y_lo = x_lo c - x_hi s, y_hi = x_hi c + x_lo s; the gradient takes the transpose:
+    // dx_lo = dy_lo c + dy_hi s, dx_hi = dy_hi c - dy_lo s
+    constexpr int hd = D / 2;
+    const bool upper = dv8 * 8 >= hd;
+    const int pv = upper ? dv8 - VPH / 2 : dv8 + VPH / 2;
+    float o[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(src + base) + pv), o);
+    const int f0 = (upper ? dv8 * 8 - hd : dv8 * 8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float c = cos_tab[size_t(t) * hd + f0 + j], s = sin_tab[size_t(t) * hd + f0 + j];
+      v[j] = upper ? v[j] * c - o[j] * s : v[j] * c + o[j] * s;
+    }
+  }
+  if (which == 0 && q_scale != 1.f) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= q_scale;
+  }
+  const size_t col = size_t(which) * E + size_t(h) * D + dv8 * 8;
+  const uint4 packed = pack8(v);
+  *reinterpret_cast<uint4*>(g + row * 3 * E + col) = packed;
+}
+
+int fail(const char* what, cudaError_t e) {
+  set_error("%s: %s", what, cudaGetErrorString(e));
+  return MINTB_ECUDA;
+}
+
+int ln_maxv(int E) { return E <= 512 ? 2 : (E <= 1280 ? 5 : (E <= 2560 ? 10 : 0)); }
+
+int ln_grid(int rows) {
+  const int want = (rows + kLnWarps - 1) / kLnWarps;
+  return want < 148 * 8 ? want : 148 * 8;   // a few CTAs per SM; rows are walked with a grid stride
+}
+
+}  // namespace
+}  // namespace mintb
+
+extern "C" {
+
+using namespace mintb;
+
+int mintb_add_layernorm_fwd(const void* x, const void* r, float a, float b, const void* gamma, const void* beta, int param_dtype,
+                            void* s_out, void* y_out, float* stats, int rows, int E, float eps, void* stream) {
+  if (x == nullptr || rows <= 0 || E <= 0 || (E % 8) != 0 || ln_maxv(E) == 0) {
+    set_error("mintb_add_layernorm_fwd: x is required, rows > 0, E a multiple of 8 and at most 2560 (got rows %d, E %d)", rows, E);
+    return x == nullptr || rows <= 0 || E <= 0 ? MINTB_EINVAL : MINTB_EUNSUPPORTED;
+  }
+  if ((gamma != nullptr && y_out == nullptr) || (gamma == nullptr && s_out == nullptr) ||
+      (param_dtype != MINTB_F32 && param_dtype != MINTB_BF16)) {
+    set_error("mintb_add_layernorm_fwd: y_out is required with gamma, s_out without; parameters are f32 or bf16");
+    return MINTB_EINVAL;
+  }
+  LnParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.r = static_cast<const __nv_bfloat16*>(r);
+  p.a = a; p.b = b; p.gamma = gamma; p.beta = beta; p.param_dtype = param_dtype;
+  p.s_out = static_cast<__nv_bfloat16*>(s_out); p.y_out = static_cast<__nv_bfloat16*>(y_out);
+  p.stats = reinterpret_cast<float2*>(stats); p.rows = rows; p.E = E; p.eps = eps;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = (rows + kLnWarps - 1) / kLnWarps;
+  switch (ln_maxv(E)) {
+    case 2: add_layernorm_fwd_kernel<2><<<grid, kLnWarps * 32, 0, st>>>(p); break;
+    case 5: add_layernorm_fwd_kernel<5><<<grid, kLnWarps * 32, 0, st>>>(p); break;
+    default: add_layernorm_fwd_kernel<10><<<grid, kLnWarps * 32, 0, st>>>(p); break;
+  }
+  count_launches(1);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? MINTB_OK : fail("mintb_add_layernorm_fwd launch", e);
+}
+
+size_t mintb_add_layernorm_bwd_workspace_bytes(int rows, int E) {
+  if (rows <= 0 || E <= 0) return 0;
+  return align256(size_t(ln_grid(rows)) * 2 * E * sizeof(float));
+}
+
+int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const void* x, const void* r, float a, float b, const void* gamma,
+                            int param_dtype, const float* stats, void* dx, void* dr, float* dgamma, float* dbeta, void* workspace,
+                            size_t workspace_bytes, int rows, int E, void* stream) {
+  if (rows <= 0 || E <= 0 || (E % 8) != 0 || ln_maxv(E) == 0) {
+    set_error("mintb_add_layernorm_bwd: rows > 0, E a multiple of 8 and at most 2560 (got rows %d, E %d)", rows, E);
+    return rows <= 0 || E <= 0 ? MINTB_EINVAL : MINTB_EUNSUPPORTED;
+  }
+  const bool norm = gamma != nullptr;
+  if (dx == nullptr || (norm && (dy == nullptr || x == nullptr || stats == nullptr || dgamma == nullptr || dbeta == nullptr)) ||
+      (!norm && ds_in == nullptr)) {
+    set_error("mintb_add_layernorm_bwd: missing pointer (with gamma: dy, x, stats, dgamma, dbeta; without: ds_in; always dx)");
+    return MINTB_EINVAL;
+  }
+  if (norm && (workspace == nullptr || workspace_bytes < mintb_add_layernorm_bwd_workspace_bytes(rows, E))) {
+    set_error("mintb_add_layernorm_bwd: workspace of %zu bytes required", mintb_add_layernorm_bwd_workspace_bytes(rows, E));
+    return MINTB_EWORKSPACE;
+  }
+  LnParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.r = static_cast<const __nv_bfloat16*>(r);
+  p.a = a; p.b = b; p.gamma = gamma; p.param_dtype = param_dtype;
+  p.stats = const_cast<float2*>(reinterpret_cast<const float2*>(stats));
+  p.dy = static_cast<const __nv_bfloat16*>(dy); p.ds_in = static_cast<const __nv_bfloat16*>(ds_in);
+  p.dx = static_cast<__nv_bfloat16*>(dx); p.dr = static_cast<__nv_bfloat16*>(dr);
+  p.partial = static_cast<float*>(workspace); p.rows = rows; p.E = E;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = ln_grid(rows);
+  const size_t smem = norm ? size_t(kLnWarps) * 2 * E * sizeof(float) : 0;
+  cudaError_t e = cudaSuccess;
+#define MINTB_LN_BWD(V)                                                                                                   \
+  e = cudaFuncSetAttribute(add_layernorm_bwd_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));          \
+  if (e == cudaSuccess) add_layernorm_bwd_kernel<V><<<grid, kLnWarps * 32, smem, st>>>(p);
+  switch (ln_maxv(E)) {
+    case 2: MINTB_LN_BWD(2) break;
+    case 5: MINTB_LN_BWD(5) break;
+    default: MINTB_LN_BWD(10) break;
+  }
+#undef MINTB_LN_BWD
+  if (e != cudaSuccess) return fail("mintb_add_layernorm_bwd", e);
+  count_launches(1);
+  if (norm) {
+    ln_param_grad_kernel<<<(2 * E + 255) / 256, 256, 0, st>>>(p.partial, grid, E, dgamma, dbeta);
+    count_launches(1);
+  }
+  e = cudaGetLastError();
+  return e == cudaSuccess ? MINTB_OK : fail("mintb_add_layernorm_bwd launch", e);
+}
+
+int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, int M, int N, void* stream) {
+  if (dy == nullptr || M <= 0 || N <= 0 || (N % 8) != 0 || (z != nullptr && dz == nullptr) || (z == nullptr && db == nullptr)) {
+    set_error("mintb_gelu_bwd_colsum: dy required, N a multiple of 8, dz with z, db without z");
+    return MINTB_EINVAL;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (db != nullptr) {
+    cudaError_t e = cudaMemsetAsync(db, 0, size_t(N) * sizeof(float), st);
+    if (e != cudaSuccess) return fail("mintb_gelu_bwd_colsum memset", e);
+  }
+  dim3 grid((N / 8 + 127) / 128, (M + kColRows - 1) / kColRows);
+  gelu_bwd_colsum_kernel<<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(z),
+                                               static_cast<__nv_bfloat16*>(dz), db, M, N);
+  count_launches(1);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? MINTB_OK : fail("mintb_gelu_bwd_colsum launch", e);
+}
+
+int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g, const float* rope_cos, const float* rope_sin, int T,
+                        int B, int H, int D, float q_scale, void* stream) {
+  if (dq == nullptr || dk == nullptr || dv == nullptr || g == nullptr || T <= 0 || B <= 0 || H <= 0 ||
+      (rope_cos == nullptr) != (rope_sin == nullptr)) {
+    set_error("mintb_qkv_grad_pack: null pointer or non-positive size");
+    return MINTB_EINVAL;
+  }
+  if (D != 16 && D != 32 && D != 64) {
+    set_error("mintb_qkv_grad_pack: head_dim %d is not one of 16, 32, 64", D);
+    return MINTB_EUNSUPPORTED;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t total = size_t(T) * B * 3 * H * (D / 8);
+  const unsigned grid = unsigned((total + 255) / 256);
+  const __nv_bfloat16 *q = static_cast<const __nv_bfloat16*>(dq), *k = static_cast<const __nv_bfloat16*>(dk),
+                      *v = static_cast<const __nv_bfloat16*>(dv);
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g);
+  switch (D) {
+    case 16: qkv_grad_pack_kernel<16><<<grid, 256, 0, st>>>(q, k, v, o, rope_cos, rope_sin, T, B, H, q_scale); break;
+    case 32: qkv_grad_pack_kernel<32><<<grid, 256, 0, st>>>(q, k, v, o, rope_cos, rope_sin, T, B, H, q_scale); break;
+    default: qkv_grad_pack_kernel<64><<<grid, 256, 0, st>>>(q, k, v, o, rope_cos, rope_sin, T, B, H, q_scale); break;
+  }
+  count_launches(1);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? MINTB_OK : fail("mintb_qkv_grad_pack launch", e);
+}
+
+}  // extern "C"

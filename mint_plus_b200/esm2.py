@@ -118,7 +118,7 @@ class MINT(nn.Module):
         hidden_representations = {}
         if 0 in repr_layers:
             hidden_representations[0] = x
-        x = x.transpose(0, 1)                                          # (B,T,E) -> (T,B,E)
+        x = x.transpose(0, 1).contiguous()                             # (B,T,E) -> (T,B,E), laid out sequence-first
 
         use_ckpt = self.checkpoint_layers and self.training and torch.is_grad_enabled()
         if use_ckpt and not x.requires_grad:

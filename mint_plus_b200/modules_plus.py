@@ -147,6 +147,15 @@ class _PreLnLayer(_TwoPathwayLayer):
         self.final_layer_norm = norm()
 
     def forward(self, x, self_attn_mask=None, self_attn_padding_mask=None, chain_ids=None):
+        if x.is_cuda and x.dtype == torch.bfloat16 and isinstance(self.final_layer_norm, nn.LayerNorm):
+            # bf16 on the GPU: each residual add is fused with the LayerNorm that follows it (one pass over the activations)
+            _, h = ops.add_layernorm(x, None, 1.0, 0.0, self.self_attn_layer_norm, need_s=False)
+            if self.use_multimer:
+                h, attn = self._multimer_attention_plus(h, self_attn_mask, self_attn_padding_mask, chain_ids)
+            else:
+                h, attn = self._standard_attention(h, self_attn_mask, self_attn_padding_mask)
+            x, h = ops.add_layernorm(x, h, 1.0, 1.0, self.final_layer_norm, need_s=True)
+            return x + self.feed_forward(h), attn
         residual = x
         x = self.self_attn_layer_norm(x)
         if self.use_multimer:

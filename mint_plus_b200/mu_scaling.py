@@ -28,25 +28,17 @@ class _Fp8LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x2d, weight, bias, wq, w_scale, x_scale, gelu, out_scale):
         xq = ops.quantize_e4m3(x2d, x_scale)
-        ctx.save_for_backward(x2d, weight, bias)
-        ctx.gelu = gelu
-        ctx.scales = (wq, w_scale, x_scale, out_scale)
-        return ops.gemm_e4m3(xq, wq, x_scale * w_scale * out_scale, bias, gelu)
+        keep = gelu and any(ctx.needs_input_grad[:3])
+        res = ops.gemm_e4m3(xq, wq, x_scale * w_scale * out_scale, bias, gelu, save_preact=keep)
+        out, z = res if keep else (res, None)
+        ctx.save_for_backward(x2d, weight, bias, z)
+        ctx.out_scale = out_scale
+        return out
 
     @staticmethod
     def backward(ctx, dy):
-        x2d, weight, bias = ctx.saved_tensors
-        wb = weight if weight.dtype == torch.bfloat16 else weight.to(torch.bfloat16)
-        dz = dy
-        wq, w_scale, x_scale, out_scale = ctx.scales
-        if ctx.gelu:
-            z = ops.gemm_e4m3(ops.quantize_e4m3(x2d, x_scale), wq, x_scale * w_scale * out_scale, bias, False)
-            dz = (dy.float() * ops._gelu_erf_grad(z)).to(torch.bfloat16)
-        db = dz.float().sum(0).to(bias.dtype) if (bias is not None and ctx.needs_input_grad[2]) else None
-        if out_scale != 1.0:            # static output multiplier of the product (not of the bias)
-            dz = dz * out_scale
-        dx = dz @ wb if ctx.needs_input_grad[0] else None
-        dw = (dz.t() @ x2d).to(weight.dtype) if ctx.needs_input_grad[1] else None
+        x2d, weight, bias, z = ctx.saved_tensors
+        dx, dw, db = ops.linear_backward(dy, x2d, weight, bias, z, ctx.needs_input_grad, ctx.out_scale)
         return dx, dw, db, None, None, None, None, None
 
 
@@ -202,6 +194,11 @@ class TransformerLayer_MINT_mu(_TwoPathwayLayer):
             attn_out, _ = self._multimer_attention_plus(x, self_attn_mask, self_attn_padding_mask, chain_ids)
         else:
             attn_out, _ = self._standard_attention(x, self_attn_mask, self_attn_padding_mask)
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            # bf16 on the GPU: weighted residuals and the closing LayerNorm in two fused passes
+            x, _ = ops.add_layernorm(x, attn_out, keep, add, None)
+            _, y = ops.add_layernorm(x, self.feed_forward(x), keep, add, self.final_layer_norm, need_s=False)
+            return y, None
         x = keep * x + add * attn_out
         x = keep * x + add * self.feed_forward(x)
         return self.final_layer_norm(x), None

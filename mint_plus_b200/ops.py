@@ -282,18 +282,20 @@ def _bias_arg(bias):
     return bias.contiguous(), _BIAS_DT[bias.dtype]
 
 
-def gemm_bf16(x2d: torch.Tensor, w: torch.Tensor, bias=None, gelu: bool = False) -> torch.Tensor:
-    """act(x2d @ w.T + bias) on the tcgen05 GEMM: x2d [M,K] bf16, w [N,K] bf16 -> [M,N] bf16 (no autograd)."""
+def gemm_bf16(x2d: torch.Tensor, w: torch.Tensor, bias=None, gelu: bool = False, save_preact: bool = False):
+    """act(x2d @ w.T + bias) on the tcgen05 GEMM: x2d [M,K] bf16, w [N,K] bf16 -> [M,N] bf16 (no autograd).
+    With gelu and save_preact the pre-activation is returned as well: (out, z)."""
     _require_cuda(x2d, w, bias)
     M, K = x2d.shape
     N = w.shape[0]
     b, bdt = _bias_arg(bias)
     out = torch.empty(M, N, dtype=torch.bfloat16, device=x2d.device)
+    z = torch.empty(M, N, dtype=torch.bfloat16, device=x2d.device) if (gelu and save_preact) else None
     with torch.cuda.device(x2d.device):
-        rc = L.lib().mintb_linear_fwd(_ptr(x2d), _ptr(w), _ptr(b), _ptr(out), M, N, K, L.BF16, bdt, L.BF16, int(gelu), 1.0, 1.0,
-                                      _stream(), _ptr(_dev_status(x2d.device)))
+        rc = L.lib().mintb_linear_fwd(_ptr(x2d), _ptr(w), _ptr(b), _ptr(out), _ptr(z), M, N, K, L.BF16, bdt, L.BF16, int(gelu),
+                                      1.0, 1.0, _stream(), _ptr(_dev_status(x2d.device)))
     L.check(rc, "mintb_linear_fwd")
-    return out
+    return (out, z) if save_preact else out
 
 
 def quantize_e4m3(x: torch.Tensor, scale: float) -> torch.Tensor:
@@ -307,20 +309,37 @@ def quantize_e4m3(x: torch.Tensor, scale: float) -> torch.Tensor:
 
 
 def gemm_e4m3(xq: torch.Tensor, wq: torch.Tensor, alpha: float, bias=None, gelu: bool = False,
-              out_e4m3_scale: Optional[float] = None) -> torch.Tensor:
-    """act(alpha * xq @ wq.T + bias) with e4m3 operands; bf16 result, or e4m3 (result / out_e4m3_scale, saturated)."""
+              out_e4m3_scale: Optional[float] = None, save_preact: bool = False):
+    """act(alpha * xq @ wq.T + bias) with e4m3 operands; bf16 result, or e4m3 (result / out_e4m3_scale, saturated).
+    With gelu and save_preact the bf16 pre-activation is returned as well: (out, z)."""
     _require_cuda(xq, wq, bias)
     M, K = xq.shape
     N = wq.shape[0]
     b, bdt = _bias_arg(bias)
     to_f8 = out_e4m3_scale is not None
     out = torch.empty(M, N, dtype=torch.float8_e4m3fn if to_f8 else torch.bfloat16, device=xq.device)
+    z = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device) if (gelu and save_preact) else None
     with torch.cuda.device(xq.device):
-        rc = L.lib().mintb_linear_fwd(_ptr(xq), _ptr(wq), _ptr(b), _ptr(out), M, N, K, L.E4M3, bdt, L.E4M3 if to_f8 else L.BF16,
-                                      int(gelu), float(alpha), 1.0 / out_e4m3_scale if to_f8 else 1.0, _stream(),
-                                      _ptr(_dev_status(xq.device)))
+        rc = L.lib().mintb_linear_fwd(_ptr(xq), _ptr(wq), _ptr(b), _ptr(out), _ptr(z), M, N, K, L.E4M3, bdt,
+                                      L.E4M3 if to_f8 else L.BF16, int(gelu), float(alpha),
+                                      1.0 / out_e4m3_scale if to_f8 else 1.0, _stream(), _ptr(_dev_status(xq.device)))
     L.check(rc, "mintb_linear_fwd")
-    return out
+    return (out, z) if save_preact else out
+
+
+def gelu_bwd_colsum(dy: torch.Tensor, z: Optional[torch.Tensor], want_db: bool = True):
+    """(dz, db): dz = dy * gelu'(z) (bf16 [M,N]; dy itself when z is None) and db = column sums of dz (fp32 [N]) in one pass."""
+    _require_cuda(dy, z)
+    dy = dy.contiguous()
+    M, N = dy.shape
+    dz = torch.empty_like(dy) if z is not None else dy
+    db = torch.empty(N, dtype=torch.float32, device=dy.device) if want_db else None
+    if z is None and not want_db:
+        return dz, None
+    with torch.cuda.device(dy.device):
+        rc = L.lib().mintb_gelu_bwd_colsum(_ptr(dy), _ptr(z), _ptr(dz) if z is not None else None, _ptr(db), M, N, _stream())
+    L.check(rc, "mintb_gelu_bwd_colsum")
+    return dz, db
 
 
 def _gelu_erf_grad(z: torch.Tensor) -> torch.Tensor:
@@ -328,28 +347,40 @@ def _gelu_erf_grad(z: torch.Tensor) -> torch.Tensor:
     return 0.5 * (1.0 + torch.erf(zf * 0.7071067811865476)) + zf * torch.exp(-0.5 * zf * zf) * 0.3989422804014327
 
 
+def linear_backward(dy, x2d, w, bias, z, needs, out_scale: float = 1.0):
+    """Gradients of y = act(out_scale * x W^T + b): the GELU derivative and the bias gradient come from one fused pass;
+    dgrad and wgrad are plain library GEMMs on bf16 (the static output multiplier is folded into the small operand)."""
+    want_db = bias is not None and needs[2]
+    dz, db = gelu_bwd_colsum(dy, z, want_db)
+    wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+    dx = dw = None
+    if needs[0]:
+        dx = dz @ (wb * out_scale if out_scale != 1.0 else wb)
+    if needs[1]:
+        dw = dz.t() @ x2d
+        if out_scale != 1.0:
+            dw = dw * out_scale
+        dw = dw.to(w.dtype)
+    return dx, dw, (db.to(bias.dtype) if want_db else None)
+
+
 class _LinearFn(torch.autograd.Function):
-    """y = act(x W^T + b) with the forward on the tcgen05 GEMM.  The backward products (dgrad, wgrad) are plain library
-    GEMMs; with GELU the pre-activation is recomputed rather than stored."""
+    """y = act(x W^T + b) with the forward on the tcgen05 GEMM.  With GELU the pre-activation is written by the same GEMM
+    epilogue and kept for the backward pass."""
 
     @staticmethod
     def forward(ctx, x2d, w, bias, gelu):
-        wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
-        ctx.save_for_backward(x2d, w, bias)
-        ctx.gelu = gelu
-        return gemm_bf16(x2d, wb.contiguous(), bias, gelu)
+        wb = (w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)).contiguous()
+        keep = gelu and any(ctx.needs_input_grad[:3])
+        res = gemm_bf16(x2d, wb, bias, gelu, save_preact=keep)
+        out, z = res if keep else (res, None)
+        ctx.save_for_backward(x2d, w, bias, z)
+        return out
 
     @staticmethod
     def backward(ctx, dy):
-        x2d, w, bias = ctx.saved_tensors
-        wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
-        dz = dy
-        if ctx.gelu:
-            z = gemm_bf16(x2d, wb.contiguous(), bias, False)
-            dz = (dy.float() * _gelu_erf_grad(z)).to(torch.bfloat16)
-        dx = dz @ wb if ctx.needs_input_grad[0] else None
-        dw = (dz.t() @ x2d).to(w.dtype) if ctx.needs_input_grad[1] else None
-        db = dz.float().sum(0).to(bias.dtype) if (bias is not None and ctx.needs_input_grad[2]) else None
+        x2d, w, bias, z = ctx.saved_tensors
+        dx, dw, db = linear_backward(dy, x2d, w, bias, z, ctx.needs_input_grad)
         return dx, dw, db, None
 
 
@@ -360,6 +391,67 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, gelu: bool = False)
     x2d = x.reshape(-1, x.shape[-1]).contiguous()
     y = _LinearFn.apply(x2d, weight, bias, gelu)
     return y.view(*x.shape[:-1], weight.shape[0])
+
+
+# ----------------------------------------------------------------------------------------------- residual + LayerNorm
+class _AddLayerNormFn(torch.autograd.Function):
+    """(s, y) with s = a x + b r and y = LayerNorm(s) gamma + beta, in one pass over x and r; `need_s` False drops s,
+    gamma None drops the normalisation (then only s).  Replaces the residual add + LayerNorm pairs of the layers."""
+
+    @staticmethod
+    def forward(ctx, x, r, a, b, gamma, beta, eps, need_s):
+        E = x.shape[-1]
+        x2 = x.reshape(-1, E).contiguous()
+        r2 = r.reshape(-1, E).contiguous() if r is not None else None
+        rows = x2.shape[0]
+        norm = gamma is not None
+        s = torch.empty_like(x2) if (need_s or not norm) else None
+        y = torch.empty_like(x2) if norm else None
+        stats = torch.empty(rows, 2, dtype=torch.float32, device=x.device) if norm else None
+        pdt = _BIAS_DT[gamma.dtype] if norm else L.F32
+        with torch.cuda.device(x.device):
+            rc = L.lib().mintb_add_layernorm_fwd(_ptr(x2), _ptr(r2), float(a), float(b), _ptr(gamma), _ptr(beta), pdt, _ptr(s), _ptr(y),
+                                                 _ptr(stats), rows, E, float(eps), _stream())
+        L.check(rc, "mintb_add_layernorm_fwd")
+        ctx.save_for_backward(x2, r2, gamma, stats)
+        ctx.cfg = (float(a), float(b), x.shape, pdt, beta is not None)
+        outs = (s.view(x.shape) if s is not None else None, y.view(x.shape) if y is not None else None)
+        return outs
+
+    @staticmethod
+    def backward(ctx, ds_in, dy):
+        x2, r2, gamma, stats = ctx.saved_tensors
+        a, b, shape, pdt, has_beta = ctx.cfg
+        rows, E = x2.shape
+        norm = gamma is not None
+        if not norm and ds_in is None:
+            return (None,) * 8
+        dy2 = dy.reshape(rows, E).contiguous() if (norm and dy is not None) else None
+        if norm and dy2 is None:
+            dy2 = torch.zeros_like(x2)
+        ds2 = ds_in.reshape(rows, E).contiguous() if ds_in is not None else None
+        dx = torch.empty_like(x2)
+        dr = torch.empty_like(x2) if r2 is not None else None
+        dgamma = torch.empty(E, dtype=torch.float32, device=x2.device) if norm else None
+        dbeta = torch.empty(E, dtype=torch.float32, device=x2.device) if norm else None
+        lib = L.lib()
+        wsb = lib.mintb_add_layernorm_bwd_workspace_bytes(rows, E) if norm else 0
+        ws = torch.empty(wsb, dtype=torch.uint8, device=x2.device) if wsb else None
+        with torch.cuda.device(x2.device):
+            rc = lib.mintb_add_layernorm_bwd(_ptr(dy2), _ptr(ds2), _ptr(x2), _ptr(r2), a, b, _ptr(gamma), pdt, _ptr(stats), _ptr(dx),
+                                             _ptr(dr), _ptr(dgamma), _ptr(dbeta), _ptr(ws), wsb, rows, E, _stream())
+        L.check(rc, "mintb_add_layernorm_bwd")
+        return (dx.view(shape), dr.view(shape) if dr is not None else None, None, None,
+                dgamma.to(gamma.dtype) if norm else None, dbeta.to(gamma.dtype) if (norm and has_beta) else None, None, None)
+
+
+def add_layernorm(x, r, a: float, b: float, norm: Optional[torch.nn.LayerNorm], need_s: bool = True):
+    """(s, y): s = a x + b r (r may be None), y = norm(s).  bf16 CUDA tensors; `norm` None returns (s, None)."""
+    if x.dtype != torch.bfloat16 or not x.is_cuda:
+        raise TypeError("add_layernorm takes bfloat16 CUDA tensors")
+    if norm is None:
+        return _AddLayerNormFn.apply(x, r, a, b, None, None, 0.0, True)
+    return _AddLayerNormFn.apply(x, r, a, b, norm.weight, norm.bias, norm.eps, need_s)
 
 
 def _rope_rotate_torch(t, cos, sin, inverse=False):
@@ -397,19 +489,15 @@ class _QkvFn(torch.autograd.Function):
     def backward(ctx, dq, dk, dv):
         x2d, w, bias, cos, sin = ctx.saved_tensors
         T, B, H, D, q_scale, out_scale = ctx.dims
-        if cos is not None:
-            dq, dk = _rope_rotate_torch(dq, cos, sin, True), _rope_rotate_torch(dk, cos, sin, True)
-        if q_scale != 1.0:
-            dq = dq * q_scale
-        # (B,H,T,D) x3 -> [T*B, 3E]
-        g = torch.cat([t.permute(2, 0, 1, 3).reshape(T * B, H * D) for t in (dq, dk, dv)], dim=1).to(torch.bfloat16)
-        wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
-        db = g.float().sum(0).to(bias.dtype) if (bias is not None and ctx.needs_input_grad[2]) else None
-        if out_scale != 1.0:        # static output multiplier of the product (not of the bias)
-            g = g * out_scale
-        dx = (g @ wb).view(T, B, H * D) if ctx.needs_input_grad[0] else None
-        dw = (g.t() @ x2d).to(w.dtype) if ctx.needs_input_grad[1] else None
-        return dx, dw, db, None, None, None, None, None, None, None, None
+        E = H * D
+        # (B,H,T,D) x3 -> [T*B, 3E] with the rotation undone and the q scale applied, in one pass
+        g = torch.empty(T * B, 3 * E, dtype=torch.bfloat16, device=x2d.device)
+        with torch.cuda.device(x2d.device):
+            rc = L.lib().mintb_qkv_grad_pack(_ptr(dq.contiguous()), _ptr(dk.contiguous()), _ptr(dv.contiguous()), _ptr(g), _ptr(cos),
+                                             _ptr(sin), T, B, H, D, float(q_scale), _stream())
+        L.check(rc, "mintb_qkv_grad_pack")
+        dx, dw, db = linear_backward(g, x2d, w, bias, None, ctx.needs_input_grad, out_scale)
+        return (dx.view(T, B, E) if dx is not None else None), dw, db, None, None, None, None, None, None, None, None
 
 
 def qkv_project(x: torch.Tensor, weight: torch.Tensor, bias, num_heads: int, rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,

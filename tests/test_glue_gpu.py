@@ -1,0 +1,116 @@
+"""The HBM-bound glue kernels (fused residual + LayerNorm, GELU backward + bias gradient, QKV gradient pack) against plain
+PyTorch fp32 statements of the same arithmetic, through the C ABI."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from mint_plus_b200 import ops  # noqa: E402
+
+DEV = "cuda"
+
+
+def _bf(t):
+    return t.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("E", [320, 640, 1280, 2560, 72])
+@pytest.mark.parametrize("mode", ["ln_only", "add_ln", "add_ln_keep_s", "add_only"])
+def test_add_layernorm_forward_and_backward(E, mode):
+    torch.manual_seed(E)
+    rows_shape = (37, 3)                         # ragged number of rows: 111
+    x = _bf(torch.randn(*rows_shape, E, device=DEV)).requires_grad_(True)
+    r = _bf(torch.randn(*rows_shape, E, device=DEV)).requires_grad_(True) if mode != "ln_only" else None
+    a, b = (1.0, 0.0) if mode == "ln_only" else (math.sqrt(0.9), math.sqrt(0.1))
+    norm = None
+    if mode != "add_only":
+        norm = torch.nn.LayerNorm(E).to(DEV, torch.bfloat16)
+        with torch.no_grad():
+            norm.weight.copy_(1 + 0.1 * torch.randn(E))
+            norm.bias.copy_(0.1 * torch.randn(E))
+    need_s = mode in ("add_ln_keep_s", "add_only")
+    s, y = ops.add_layernorm(x, r, a, b, norm, need_s=need_s)
+
+    xf = x.detach().float().requires_grad_(True)
+    rf = r.detach().float().requires_grad_(True) if r is not None else None
+    sf = a * xf + (b * rf if rf is not None else 0.0)
+    gs = torch.randn_like(sf)
+    gy = torch.randn_like(sf)
+    loss_ref = 0.0
+    loss = 0.0
+    if need_s:
+        torch.testing.assert_close(s.float(), sf, rtol=1e-2, atol=1e-2)
+        loss = loss + (s.float() * gs).sum()
+        loss_ref = loss_ref + (sf * gs).sum()
+    else:
+        assert s is None
+    if norm is not None:
+        w32, b32 = norm.weight.detach().float().requires_grad_(True), norm.bias.detach().float().requires_grad_(True)
+        yf = torch.nn.functional.layer_norm(sf, (E,), w32, b32, norm.eps)
+        torch.testing.assert_close(y.float(), yf, rtol=2e-2, atol=2e-2)
+        loss = loss + (y.float() * gy).sum()
+        loss_ref = loss_ref + (yf * gy).sum()
+    loss.backward()
+    loss_ref.backward()
+    scale = xf.grad.abs().max().item()
+    assert (x.grad.float() - xf.grad).abs().max().item() <= 2e-2 * scale + 1e-3
+    if r is not None:
+        assert (r.grad.float() - rf.grad).abs().max().item() <= 2e-2 * rf.grad.abs().max().item() + 1e-3
+    if norm is not None:
+        assert (norm.weight.grad.float() - w32.grad).abs().max().item() <= 2e-2 * w32.grad.abs().max().item() + 1e-2
+        assert (norm.bias.grad.float() - b32.grad).abs().max().item() <= 2e-2 * b32.grad.abs().max().item() + 1e-2
+
+
+def test_add_layernorm_rejects_unsupported_width():
+    x = _bf(torch.randn(4, 4096, device=DEV))
+    with pytest.raises(NotImplementedError):
+        ops.add_layernorm(x, None, 1.0, 0.0, torch.nn.LayerNorm(4096).to(DEV, torch.bfloat16))
+    with pytest.raises((ValueError, NotImplementedError)):
+        ops.add_layernorm(_bf(torch.randn(4, 36, device=DEV)), None, 1.0, 0.0, None)
+
+
+@pytest.mark.parametrize("shape", [(300, 1280), (513, 72), (64, 5120)])
+@pytest.mark.parametrize("with_z", [True, False])
+def test_gelu_backward_and_bias_gradient(shape, with_z):
+    torch.manual_seed(1)
+    M, N = shape
+    dy = _bf(torch.randn(M, N, device=DEV))
+    z = _bf(2 * torch.randn(M, N, device=DEV)) if with_z else None
+    dz, db = ops.gelu_bwd_colsum(dy, z)
+    if with_z:
+        zf = z.float().requires_grad_(True)
+        torch.nn.functional.gelu(zf).backward(dy.float())
+        want = zf.grad
+        assert (dz.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item() + 1e-3
+    else:
+        assert dz is dy or torch.equal(dz, dy)
+    want_db = dz.float().sum(0)
+    assert (db - want_db).abs().max().item() <= 1e-3 * want_db.abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("D", [16, 32, 64])
+@pytest.mark.parametrize("rope", [True, False])
+def test_qkv_gradient_pack(D, rope):
+    torch.manual_seed(D)
+    T, B, H = 45, 3, 4
+    E = H * D
+    dq, dk, dv = (_bf(torch.randn(B, H, T, D, device=DEV)) for _ in range(3))
+    cos = sin = None
+    if rope:
+        cos, sin, _ = ops.rope_tables(T, D, torch.device(DEV))
+    q_scale = 0.25
+    g = torch.empty(T * B, 3 * E, dtype=torch.bfloat16, device=DEV)
+    from mint_plus_b200 import _lib as L
+    rc = L.lib().mintb_qkv_grad_pack(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), g.data_ptr(),
+                                     cos.data_ptr() if rope else None, sin.data_ptr() if rope else None, T, B, H, D, q_scale,
+                                     torch.cuda.current_stream().cuda_stream)
+    L.check(rc, "mintb_qkv_grad_pack")
+    torch.cuda.synchronize()
+    a, b = dq.float(), dk.float()
+    if rope:
+        a, b = ops._rope_rotate_torch(a, cos, sin, True).float(), ops._rope_rotate_torch(b, cos, sin, True).float()
+    a = a * q_scale
+    want = torch.cat([t.permute(2, 0, 1, 3).reshape(T * B, E) for t in (a, b, dv.float())], dim=1)
+    torch.testing.assert_close(g.float(), want, rtol=1e-2, atol=1e-2)
