@@ -237,37 +237,53 @@ __global__ void __launch_bounds__(256) ln_param_grad_kernel(const float* __restr
 
 // ------------------------------------------------------------------------------------------------ GELU backward + column sums
 constexpr int kColRows = 256;   // rows per CTA strip
+constexpr int kColLanes = 8;    // threads that share a column group, each taking every 8th row of the strip
 
 __device__ __forceinline__ float gelu_erf_grad(float z) {
   return 0.5f * (1.f + erff(z * 0.70710678118654752f)) + z * __expf(-0.5f * z * z) * 0.3989422804014327f;
 }
 
-// Thread = 8 consecutive columns; CTA = 128 column groups x a strip of kColRows rows.  db gets one atomicAdd per thread.
-__global__ void __launch_bounds__(128) gelu_bwd_colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ z,
+// CTA = 32 column groups (8 columns each: 256 columns) x 8 row lanes over a strip of kColRows rows; a warp reads 512
+// contiguous bytes of one row.  The 8 partial column sums meet in shared memory; db gets one atomicAdd per column and CTA.
+__global__ void __launch_bounds__(256) gelu_bwd_colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ z,
                                                               __nv_bfloat16* __restrict__ dz, float* __restrict__ db, int M, int N) {
-  const int cg = blockIdx.x * 128 + threadIdx.x;   // column group
-  if (cg * 8 >= N) return;
+  __shared__ float part[kColLanes][32][8];
+  const int cl = threadIdx.x % 32, rl = threadIdx.x / 32;
+  const int cg = blockIdx.x * 32 + cl;   // column group
+  const bool live = cg * 8 < N;
   const int m0 = blockIdx.y * kColRows, m1 = min(M, m0 + kColRows);
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int m = m0; m < m1; ++m) {
-    const size_t off = size_t(m) * N + size_t(cg) * 8;
-    float g[8];
-    unpack8(__ldg(reinterpret_cast<const uint4*>(dy + off)), g);
-    if (z != nullptr) {
-      float zv[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(z + off)), zv);
+  if (live) {
+#pragma unroll 4
+    for (int m = m0 + rl; m < m1; m += kColLanes) {
+      const size_t off = size_t(m) * N + size_t(cg) * 8;
+      float g[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(dy + off)), g);
+      if (z != nullptr) {
+        float zv[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(z + off)), zv);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) g[j] *= gelu_erf_grad(zv[j]);
-      const uint4 packed = pack8(g);
-      *reinterpret_cast<uint4*>(dz + off) = packed;
-      unpack8(packed, g);   // the bias gradient sums what the products will read
+        for (int j = 0; j < 8; ++j) g[j] *= gelu_erf_grad(zv[j]);
+        const uint4 packed = pack8(g);
+        *reinterpret_cast<uint4*>(dz + off) = packed;
+        unpack8(packed, g);   // the bias gradient sums what the products will read
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += g[j];
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] += g[j];
   }
-  if (db != nullptr) {
+  if (db == nullptr) return;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) atomicAdd(db + size_t(cg) * 8 + j, acc[j]);
+  for (int j = 0; j < 8; ++j) part[rl][cl][j] = acc[j];
+  __syncthreads();
+  // 256 threads <-> 256 columns of the CTA
+  const int c = threadIdx.x;
+  const int col = blockIdx.x * 256 + c;
+  if (col < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < kColLanes; ++r) t += part[r][c / 8][c % 8];
+    atomicAdd(db + col, t);
   }
 }
 
@@ -426,8 +442,8 @@ int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, in
     cudaError_t e = cudaMemsetAsync(db, 0, size_t(N) * sizeof(float), st);
     if (e != cudaSuccess) return fail("mintb_gelu_bwd_colsum memset", e);
   }
-  dim3 grid((N / 8 + 127) / 128, (M + kColRows - 1) / kColRows);
-  gelu_bwd_colsum_kernel<<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(z),
+  dim3 grid((N + 255) / 256, (M + kColRows - 1) / kColRows);
+  gelu_bwd_colsum_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(z),
                                                static_cast<__nv_bfloat16*>(dz), db, M, N);
   count_launches(1);
   cudaError_t e = cudaGetLastError();

@@ -1,0 +1,99 @@
+"""The N > 1 path on CPU: pairs shard across ranks with no data-path collective, trainable gradients are averaged with one
+flat all-reduce, timings reduce by max.  Two `gloo` ranks, spawned as child processes."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mint_plus_b200.distributed import (FlatGradAllReduce, balanced_shards, reduce_max, reduce_sum, shard_indices)
+from mint_plus_b200.lora import LoRALinear, apply_lora
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)                                   # same parameters on every rank
+        model = torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.Linear(8, 4))
+        model[0].weight.requires_grad_(False)                  # frozen parameters are not exchanged
+        data = torch.arange(6 * 8, dtype=torch.float32).view(6, 8) / 10.0
+        mine = shard_indices(6, rank, world)
+        model(data[mine]).square().sum().backward()
+        sync = FlatGradAllReduce(model.parameters())
+        assert sync.nbytes == 4 * (8 + 4 * 8 + 4)
+        sync()
+        tmax = reduce_max([float(rank + 1), 5.0 - rank], "cpu")
+        tsum = reduce_sum([float(len(mine))], "cpu")
+        torch.save({"grads": [p.grad.clone() for p in model.parameters() if p.requires_grad], "tmax": tmax, "tsum": tsum,
+                    "mine": mine}, os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_average_trainable_gradients_over_disjoint_shards(tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    r0, r1 = (torch.load(tmp_path / f"rank{r}.pt") for r in range(world))
+    assert sorted(r0["mine"] + r1["mine"]) == list(range(6)) and not set(r0["mine"]) & set(r1["mine"])
+    # both ranks end with the same gradients: the mean of the per-shard gradients
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.Linear(8, 4))
+    model[0].weight.requires_grad_(False)
+    data = torch.arange(6 * 8, dtype=torch.float32).view(6, 8) / 10.0
+    want = None
+    for r in range(world):
+        model.zero_grad()
+        model(data[shard_indices(6, r, world)]).square().sum().backward()
+        g = [p.grad.clone() for p in model.parameters() if p.requires_grad]
+        want = g if want is None else [a + b for a, b in zip(want, g)]
+    want = [w / world for w in want]
+    for got0, got1, w in zip(r0["grads"], r1["grads"], want):
+        torch.testing.assert_close(got0, w)
+        torch.testing.assert_close(got1, w)
+    assert r0["tmax"] == [2.0, 5.0] and r1["tmax"] == [2.0, 5.0]
+    assert r0["tsum"] == [6.0]
+
+
+def test_balanced_shards_even_out_skewed_costs():
+    lengths = [1900, 30, 1800, 40, 900, 950, 50, 60]
+    shards = balanced_shards([l * l for l in lengths], 2)
+    assert sorted(shards[0] + shards[1]) == list(range(8))
+    loads = [sum(lengths[i] ** 2 for i in s) for s in shards]
+    assert max(loads) / min(loads) < 1.35
+    assert balanced_shards([1, 1, 1], 4)[3] == []
+
+
+def test_lora_adapter_freezes_base_and_matches_the_formula():
+    torch.manual_seed(1)
+    lin = torch.nn.Linear(16, 12)
+    lora = LoRALinear(lin, r=4, alpha=8.0)
+    with torch.no_grad():
+        lora.lora_B.normal_(0, 0.1)
+    x = torch.randn(5, 16)
+    want = lin(x) + (x @ lora.lora_A.t()) @ lora.lora_B.t() * 2.0
+    torch.testing.assert_close(lora(x), want)
+    assert not lin.weight.requires_grad and lora.lora_A.requires_grad
+
+    class Layer(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            import mint_plus_b200 as M
+            self.self_attn = M.MultiHeadAttention(16, 2, use_rotary_embeddings=True)
+            self.multimer_attn = M.MultiHeadAttention(16, 2, no_proj=True)
+
+    class Model(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = torch.nn.ModuleList([Layer()])
+
+    m = apply_lora(Model())
+    names = [n for n, p in m.named_parameters() if p.requires_grad]
+    assert len(names) == 2 * 7 and all("lora_" in n for n in names)      # self q,k,v,out + cross q,k,v
