@@ -315,7 +315,8 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src):
                 "warmup": warmup, "ms_per_step": ms_total / steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
                 "config": {"workload": cfg["desc"] + " per GPU", "l2": "working set per step far exceeds L2 (no flush)",
-                           "launch": "eager", "checkpointing": "per layer" if cfg["train"] else "none",
+                           "launch": "eager", "checkpointing": ("per layer" if getattr(model, "last_forward_checkpointed", False) else
+                                             "off (activations of all layers fit in HBM)") if cfg["train"] else "none",
                            "grad_allreduce_bytes": sync_grads.nbytes if sync_grads is not None else 0},
                 "roofline": roof,
                 "e2e": {"value": pairs_total * e2e_steps / (e2e_ms * 1e-3), "unit": "pairs/s", "h2d_bytes_per_step": h2d,

@@ -34,9 +34,7 @@ __device__ unsigned long long g_trace_bwd[32 * 512];
 
 constexpr int kBwdTile = 128;       // keys per CTA and queries per step
 constexpr int kHalf = 64;           // queries per compute group
-constexpr int kBwdThreads = 640;   // 4 MMA-issuing warps (one also issues the TMA loads), 16 compute warps
 constexpr int kBwdMaxTiles = 256;   // T <= 32768
-constexpr uint32_t kTmemAll = 512;
 constexpr unsigned kBwdStaggerNs = 250;   // initial offset between the two pairs of compute groups
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -181,13 +179,23 @@ struct BwdCfg {
   static constexpr int kTileBytes = kBwdTile * kRowBytes;       // K, V, Q_i, dO_i tiles
   static constexpr int kDsBlock = kBwdTile * 128;               // one half (64 queries) of dS: [128 key rows][128 B]
   static constexpr int kDsBytes = 2 * kDsBlock;
-  // TMEM: dK, dV, two dQ tiles, then kNBuf buffers of {S^T half (64 columns), dP^T half (64 columns)}.
-  // Small heads leave room for a third buffer, which lets the products run two halves ahead of the compute warps.
-  static constexpr int kNBuf = D <= 32 ? 3 : 2;
-  static constexpr int kQStages = D <= 32 ? 3 : 2;              // stages of {Q_i, dO_i}
+  // Two shapes are provided.  The one in use: one CTA per SM, 16 compute warps, all 512 TMEM columns: dK, dV, two dQ tiles,
+  // then two (head_dim 64) or three (head_dim <= 32) buffers of {S^T half (64 columns), dP^T half (64 columns)}; the third
+  // buffer lets the products run two halves ahead of the compute warps.  The other (kTwoPerSm): two CTAs per SM, each with
+  // 8 compute warps and 256 columns (dK, dV, one dQ tile, one buffer); measured slower at B8 H20 T1024 D32 (0.37 ms against
+  // 0.31 ms): with a single buffer the products and the elementwise work of a CTA alternate and two CTAs do not fill the gaps.
+  static constexpr bool kTwoPerSm = false;
+  static constexpr int kCW = kTwoPerSm ? 8 : 16;                // compute warps
+  static constexpr int kThreads = 128 + 32 * kCW;
+  static constexpr int kMinBlocks = kTwoPerSm ? 2 : 1;
+  static constexpr int kNBuf = kTwoPerSm ? 1 : (D <= 32 ? 3 : 2);
+  static constexpr int kNDq = kTwoPerSm ? 1 : 2;                // dQ tiles in TMEM == dS tiles in shared memory
+  static constexpr int kQStages = (!kTwoPerSm && D <= 32) ? 3 : 2;   // stages of {Q_i, dO_i}
   static constexpr int kAcc = D <= 32 ? 32 : 64;                // columns reserved per accumulator
-  static constexpr int kColDK = 0, kColDV = kAcc, kColDQ = 2 * kAcc, kColBuf = 4 * kAcc;
-  static constexpr size_t kSmemBytes = 1024 + 2 * kTileBytes + size_t(kQStages) * 2 * kTileBytes + 2 * kDsBytes + 4096;
+  static constexpr int kColDK = 0, kColDV = kAcc, kColDQ = 2 * kAcc, kColBuf = (2 + kNDq) * kAcc;
+  static constexpr uint32_t kTmemCols = kTwoPerSm ? 256 : 512;
+  static constexpr int kVPG = 16 / kCW;                         // 16-column query groups per thread and half (1 or 2)
+  static constexpr size_t kSmemBytes = 1024 + 2 * kTileBytes + size_t(kQStages) * 2 * kTileBytes + size_t(kNDq) * kDsBytes + 4096;
 };
 
 struct BwdParams {
@@ -212,13 +220,14 @@ struct Ring {
 };
 
 template <int D, bool SQ>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(BwdCfg<D>::kThreads, BwdCfg<D>::kMinBlocks)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_constant__ CUtensorMap map_ks,
                    const __grid_constant__ CUtensorMap map_vs, const __grid_constant__ CUtensorMap map_qc,
                    const __grid_constant__ CUtensorMap map_kc, const __grid_constant__ CUtensorMap map_vc,
                    const __grid_constant__ CUtensorMap map_do, BwdParams p) {
   using Cfg = BwdCfg<D>;
-  constexpr int RB = Cfg::kRowBytes, kNBuf = Cfg::kNBuf, kQStages = Cfg::kQStages;
+  constexpr int RB = Cfg::kRowBytes, kNBuf = Cfg::kNBuf, kQStages = Cfg::kQStages, kNDq = Cfg::kNDq, kVPG = Cfg::kVPG;
+  constexpr int kBwdThreads = Cfg::kThreads, kComputeThreads = 32 * Cfg::kCW;
   constexpr int kColDK = Cfg::kColDK, kColDV = Cfg::kColDV, kColDQ = Cfg::kColDQ, kColBuf = Cfg::kColBuf, kAcc = Cfg::kAcc;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -226,7 +235,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   unsigned char* sV = sK + Cfg::kTileBytes;
   unsigned char* sQ = sV + Cfg::kTileBytes;                          // [stage][0: Q_i, 1: dO_i]
   unsigned char* sDS = sQ + size_t(kQStages) * 2 * Cfg::kTileBytes;  // [buf][half][128 rows x 128 B]
-  unsigned char* tail = sDS + 2 * Cfg::kDsBytes;
+  unsigned char* tail = sDS + size_t(kNDq) * Cfg::kDsBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
   uint64_t* kv_full = bars;            // 1
   uint64_t* acc_full = bars + 1;       // 1
@@ -264,13 +273,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     mbar_init(acc_full, 2);
     for (int s = 0; s < 3; ++s) {
       mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 2);      // released by the dV and the dK stream
-      mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 512);
+      mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], kComputeThreads);
       mbar_init(&buf_free[s], 2);                                // dV and dK of a half have read P^T, dS^T
     }
-    for (int s = 0; s < 2; ++s) { mbar_init(&dq_full[s], 1); mbar_init(&dq_empty[s], 512); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&dq_full[s], 1); mbar_init(&dq_empty[s], kComputeThreads); }
     fence_mbar_init();
   }
-  if (warp == 1) { tmem_alloc(tmem_slot, kTmemAll); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::kTmemCols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -396,15 +405,15 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         br.advance();
         if (ok) ok = mbar_wait(&pds_full[br.pos], br.phase, p.status, 0x523);
         br.advance();
-        if (ok) ok = mbar_wait(&dq_empty[it & 1], ((it / 2) & 1) ^ 1, p.status, 0x524);   // buffer drained two tiles ago
+        if (ok) ok = mbar_wait(&dq_empty[it % kNDq], ((it / kNDq) & 1) ^ 1, p.status, 0x524);   // buffer drained kNDq tiles ago
         if (!ok) break;
         MINTB_BTRACE_EV(30);
         tc_fence_after();
-        const uint32_t a_lo = ds_lo + uint32_t(it & 1) * kDsU;
+        const uint32_t a_lo = ds_lo + uint32_t(it % kNDq) * kDsU;
 #pragma unroll
         for (int k = 0; k < kBwdTile / 16; ++k)
-          umma_ss(tbase + kColDQ + (it & 1) * kAcc, make_desc(kHiA, a_lo + k * kAStep), make_desc(kHiB, kb_lo + k * kBStep), idesc_dq, k > 0);
-        umma_commit(&dq_full[it & 1]);
+          umma_ss(tbase + kColDQ + (it % kNDq) * kAcc, make_desc(kHiA, a_lo + k * kAStep), make_desc(kHiB, kb_lo + k * kBStep), idesc_dq, k > 0);
+        umma_commit(&dq_full[it % kNDq]);
         MINTB_BTRACE_EV(31);
         if (it + kQStages < n_active) {   // this tile's stage is released by its dV and dK streams
           ok = mbar_wait(&q_empty[er.pos], er.phase, p.status, 0x525);
@@ -419,14 +428,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     // products run up to kNBuf halves ahead, and groups 2,3 start a fraction of a half later than groups 0,1 so that the
     // exp2-heavy part of one pair of groups overlaps the TMEM traffic and barrier work of the other.
     // Everything here is elementwise: no exchange between threads.
-    const int cwp = warp - 4;                     // 0..15
-    const int grp = cwp / 4;
+    const int cwp = warp - 4;                     // 0..kCW-1
+    const int grp = cwp / 4;                      // physical group; it covers the 16-column groups vg = grp * kVPG + v
     const int quarter = warp % 4;
     const int r = quarter * 32 + lane;            // key row in the tile == TMEM lane
     const int kj = k0 + r;
     const int krow = kj < p.T ? kj : p.T - 1;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    const uint32_t tBuf = tbase + lane_base + kColBuf + 16 * grp;   // + 128 * buffer: S^T columns of this thread; dP^T 64 further
+    const uint32_t tBuf = tbase + lane_base + kColBuf;   // + 128 * buffer + 16 * vg: S^T columns of this thread; dP^T 64 further
     const bool key_valid = kj < p.T && !((p.kpad[size_t(b) * p.TW + krow / 32] >> (krow % 32)) & 1u);
     const uint32_t* mrow = p.bitsT + (size_t(b) * p.T + krow) * p.TW;
     const uint32_t flip = path == 0 ? 0xffffu : 0u;   // keep-bit = mask bit XOR flip
@@ -438,11 +447,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     Ring<kNBuf> br;
 
     auto drain_dq = [&](int jt, int qtile) -> bool {   // add dQ of active tile jt (query tile qtile) to HBM
-      if (!mbar_wait(&dq_full[jt & 1], (jt / 2) & 1, p.status, 0x601)) return false;
+      if (!mbar_wait(&dq_full[jt % kNDq], (jt / kNDq) & 1, p.status, 0x601)) return false;
       tc_fence_after();
-      constexpr int NC = D / 4;   // columns per group
+      constexpr int NC = D / 4 * kVPG;   // columns per thread
       uint32_t v[NC];
-      tmem_ld_n<NC>(tbase + lane_base + kColDQ + (jt & 1) * kAcc + grp * NC, v);
+      tmem_ld_n<NC>(tbase + lane_base + kColDQ + (jt % kNDq) * kAcc + grp * NC, v);
       tmem_ld_wait();
       const int qi = qtile * kBwdTile + r;
       if (qi < p.T) {
@@ -453,7 +462,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
                                                                     __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3])));
       }
       tc_fence_before();
-      mbar_arrive(&dq_empty[jt & 1]);
+      mbar_arrive(&dq_empty[jt % kNDq]);
       return true;
     };
 
@@ -461,62 +470,65 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     for (int i = 0; i < nqt && ok; ++i) {
       const uint8_t f = tq[i];
       if (f == 0) continue;
-      // the 32 mask bits that cover this thread's columns in both halves: half `sub` uses word 2 sub + grp / 2
-      uint32_t mw0 = 0, mw1 = 0;
-      if (f & 2) {
-        mw0 = mrow[4 * i + grp / 2];
-        mw1 = mrow[4 * i + 2 + grp / 2];
-      }
+      // mask bits of the tile for this key row: half `sub`, 16-column group vg -> word 2 sub + vg / 2, bits 16 (vg & 1)...
 #pragma unroll 1
       for (int sub = 0; sub < 2 && ok; ++sub) {
-        // statistics of this thread's 16 queries (L1/L2 hits, issued before the wait)
-        const float4* st = stats_bh + (i * kBwdTile + sub * kHalf + 16 * grp) / 2;
-        float4 sq[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) sq[j] = __ldg(st + j);
-        uint32_t keep = 0xffffu;
-        if (f & 2) keep = (((sub ? mw1 : mw0) >> (16 * (grp & 1))) & 0xffffu) ^ flip;
-        if (!key_valid) keep = 0u;
-        const bool all = keep == 0xffffu;
+        if (kNDq == 1 && sub == 0 && prev_tile >= 0) {   // the single dS tile in shared memory is about to be overwritten:
+          ok = drain_dq(it - 1, prev_tile);               // the dQ product that reads it must have completed
+          if (!ok) break;
+        }
         MINTB_BTRACE_EV(40);
         ok = mbar_wait(&sdp_full[br.pos], br.phase, p.status, 0x602);
         if (!ok) break;
         if (it == 0 && sub == 0 && grp >= 2) __nanosleep(kBwdStaggerNs);
         MINTB_BTRACE_EV(41);
         tc_fence_after();
-        const uint32_t tS = tBuf + br.pos * 128;
-        uint32_t sv[16], dpv[16];
-        tmem_ld16(tS, sv);
-        tmem_ld16(tS + 64, dpv);
-        tmem_ld_wait();
-        MINTB_BTRACE_EV(42);
-        uint32_t pp[8], dd[8];
+        unsigned char* ds_row = sDS + size_t(it % kNDq) * Cfg::kDsBytes + size_t(sub) * Cfg::kDsBlock;
 #pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-          const float4 q2 = sq[j / 2];   // (nl0, nd0, nl1, nd1)
-          float p0, p1;
-          unpack2(ffma2(pack2(__uint_as_float(sv[j]), __uint_as_float(sv[j + 1])), c22, pack2(q2.x, q2.z)), p0, p1);
-          p0 = bwd_ex2(p0);
-          p1 = bwd_ex2(p1);
-          if (!all) {
-            if (!((keep >> j) & 1u)) p0 = 0.f;
-            if (!((keep >> (j + 1)) & 1u)) p1 = 0.f;
+        for (int v = 0; v < kVPG; ++v) {
+          const int vg = grp * kVPG + v;
+          // statistics of this thread's 16 queries (L1/L2 hits)
+          const float4* st = stats_bh + (i * kBwdTile + sub * kHalf + 16 * vg) / 2;
+          float4 sq[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sq[j] = __ldg(st + j);
+          uint32_t keep = 0xffffu;
+          if (f & 2) keep = ((__ldg(mrow + 4 * i + 2 * sub + vg / 2) >> (16 * (vg & 1))) & 0xffffu) ^ flip;
+          if (!key_valid) keep = 0u;
+          const bool all = keep == 0xffffu;
+          const uint32_t tS = tBuf + br.pos * 128 + 16 * vg;
+          uint32_t sv[16], dpv[16];
+          tmem_ld16(tS, sv);
+          tmem_ld16(tS + 64, dpv);
+          tmem_ld_wait();
+          MINTB_BTRACE_EV(42);
+          uint32_t pp[8], dd[8];
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            const float4 q2 = sq[j / 2];   // (nl0, nd0, nl1, nd1)
+            float p0, p1;
+            unpack2(ffma2(pack2(__uint_as_float(sv[j]), __uint_as_float(sv[j + 1])), c22, pack2(q2.x, q2.z)), p0, p1);
+            p0 = bwd_ex2(p0);
+            p1 = bwd_ex2(p1);
+            if (!all) {
+              if (!((keep >> j) & 1u)) p0 = 0.f;
+              if (!((keep >> (j + 1)) & 1u)) p1 = 0.f;
+            }
+            float d0, d1;
+            const uint64_t p2 = pack2(p0, p1), dp2 = pack2(__uint_as_float(dpv[j]), __uint_as_float(dpv[j + 1])), nd2 = pack2(q2.y, q2.w);
+            if (SQ)   // r = sqrt(p) is what p0, p1 hold: dS = r (dP / 2 - r delta / 2), and r itself multiplies dO in dV
+              unpack2(fmul2(p2, ffma2(p2, nd2, fmul2(dp2, pack2(0.5f, 0.5f)))), d0, d1);
+            else      // dS = p (dP - delta)
+              unpack2(fmul2(p2, fadd2(dp2, nd2)), d0, d1);
+            pp[j / 2] = bwd_pack(p0, p1);
+            dd[j / 2] = bwd_pack(d0, d1);
           }
-          float d0, d1;
-          const uint64_t p2 = pack2(p0, p1), dp2 = pack2(__uint_as_float(dpv[j]), __uint_as_float(dpv[j + 1])), nd2 = pack2(q2.y, q2.w);
-          if (SQ)   // r = sqrt(p) is what p0, p1 hold: dS = r (dP / 2 - r delta / 2), and r itself multiplies dO in dV
-            unpack2(fmul2(p2, ffma2(p2, nd2, fmul2(dp2, pack2(0.5f, 0.5f)))), d0, d1);
-          else      // dS = p (dP - delta)
-            unpack2(fmul2(p2, fadd2(dp2, nd2)), d0, d1);
-          pp[j / 2] = bwd_pack(p0, p1);
-          dd[j / 2] = bwd_pack(d0, d1);
+          tmem_st8(tS, pp);         // P^T over the S^T columns this thread has read
+          tmem_st8(tS + 64, dd);    // dS^T likewise
+          // and dS into shared memory for the dQ product: 2 chunks of 8 queries in block `sub` of the dS tile
+          *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 2 * vg, 128)) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
+          *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 2 * vg + 1, 128)) = make_uint4(dd[4], dd[5], dd[6], dd[7]);
         }
-        tmem_st8(tS, pp);         // P^T over the S^T columns this thread has read
-        tmem_st8(tS + 64, dd);    // dS^T likewise
-        // and dS into shared memory for the dQ product: 2 chunks of 8 queries in block `sub` of buffer it & 1
-        unsigned char* ds_row = sDS + size_t(it & 1) * Cfg::kDsBytes + size_t(sub) * Cfg::kDsBlock;
-        *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 2 * grp, 128)) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
-        *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 2 * grp + 1, 128)) = make_uint4(dd[4], dd[5], dd[6], dd[7]);
         MINTB_BTRACE_EV(43);
         tmem_st_wait();
         fence_proxy_async_smem();
@@ -526,58 +538,68 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         br.advance();
       }
       if (!ok) break;
-      if (prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
+      if (kNDq > 1 && prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
       MINTB_BTRACE_EV(45);
       prev_tile = i;
       ++it;
     }
     if (ok && prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
 
-    // ---- epilogue: groups 0,1 write the two column halves of dK (scaled, un-rotated for the self pathway),
-    //      groups 2,3 those of dV
+    // ---- epilogue: 16-column groups vg 0,1 write the two column halves of dK (scaled, un-rotated for the self pathway),
+    //      vg 2,3 those of dV
     if (n_active > 0) {
       if (ok) ok = mbar_wait(acc_full, 0, p.status, 0x603);
       tc_fence_after();
     }
     if (ok) {
       constexpr int hD = D / 2;
-      const bool is_dk = grp < 2;
-      const int half_col = grp & 1;
-      float lo[hD], hi[hD];   // lower / upper half of the row (dK needs both for the rotation; dV only its own)
-      if (n_active > 0) {
-        const uint32_t src = tbase + lane_base + (is_dk ? kColDK : kColDV);
-        uint32_t t0[hD], t1[hD];
-        if (is_dk || half_col == 0) tmem_ld_n<hD>(src, t0);
-        if (is_dk || half_col == 1) tmem_ld_n<hD>(src + hD, t1);
-        tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < hD; ++j) { lo[j] = __uint_as_float(t0[j]); hi[j] = __uint_as_float(t1[j]); }
-      } else {
+      for (int v = 0; v < kVPG; ++v) {
+        const int vg = grp * kVPG + v;
+        const bool is_dk = vg < 2;
+        const int half_col = vg & 1;
+        float lo[hD], hi[hD];   // lower / upper half of the row (dK needs both for the rotation; dV only its own)
+        if (n_active > 0) {
+          const uint32_t src = tbase + lane_base + (is_dk ? kColDK : kColDV);
+          uint32_t t0[hD], t1[hD];
+          if (is_dk || half_col == 0) tmem_ld_n<hD>(src, t0);
+          if (is_dk || half_col == 1) tmem_ld_n<hD>(src + hD, t1);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < hD; ++j) lo[j] = hi[j] = 0.f;
-      }
-      if (kj < p.T) {
-        float outv[hD];
-        if (is_dk) {
-          const bool rot = path == 0 && p.cos_tab != nullptr;
-#pragma unroll
-          for (int d = 0; d < hD; ++d) {
-            float v = half_col == 0 ? lo[d] : hi[d];
-            if (rot) {   // R^T: dx_lo = dy_lo c + dy_hi s, dx_hi = dy_hi c - dy_lo s
-              const float cs = p.cos_tab[size_t(kj) * hD + d], sn = p.sin_tab[size_t(kj) * hD + d];
-              v = half_col == 0 ? lo[d] * cs + hi[d] * sn : hi[d] * cs - lo[d] * sn;
-            }
-            outv[d] = v * p.scale;
-          }
+          for (int j = 0; j < hD; ++j) { lo[j] = __uint_as_float(t0[j]); hi[j] = __uint_as_float(t1[j]); }
         } else {
 #pragma unroll
-          for (int d = 0; d < hD; ++d) outv[d] = half_col == 0 ? lo[d] : hi[d];
+          for (int j = 0; j < hD; ++j) lo[j] = hi[j] = 0.f;
         }
-        __nv_bfloat16* dst = (is_dk ? p.dk[path] : p.dv[path]) + (size_t(bh) * p.T + kj) * D + half_col * hD;
+        if (kj < p.T) {
+          float outv[hD];
+          if (is_dk) {
+            const bool rot = path == 0 && p.cos_tab != nullptr;
+            if (rot) {   // R^T: dx_lo = dy_lo c + dy_hi s, dx_hi = dy_hi c - dy_lo s; table rows read 16 bytes at a time
+              const float4* c4 = reinterpret_cast<const float4*>(p.cos_tab + size_t(kj) * hD);
+              const float4* s4 = reinterpret_cast<const float4*>(p.sin_tab + size_t(kj) * hD);
 #pragma unroll
-        for (int j = 0; j < hD; j += 8)
-          *reinterpret_cast<uint4*>(dst + j) = make_uint4(bwd_pack(outv[j], outv[j + 1]), bwd_pack(outv[j + 2], outv[j + 3]),
-                                                          bwd_pack(outv[j + 4], outv[j + 5]), bwd_pack(outv[j + 6], outv[j + 7]));
+              for (int d = 0; d < hD; d += 4) {
+                const float4 cs = __ldg(c4 + d / 4), sn = __ldg(s4 + d / 4);
+                const float cv[4] = {cs.x, cs.y, cs.z, cs.w}, sv4[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  outv[d + e] = (half_col == 0 ? lo[d + e] * cv[e] + hi[d + e] * sv4[e] : hi[d + e] * cv[e] - lo[d + e] * sv4[e]) * p.scale;
+              }
+            } else {
+#pragma unroll
+              for (int d = 0; d < hD; ++d) outv[d] = (half_col == 0 ? lo[d] : hi[d]) * p.scale;
+            }
+          } else {
+#pragma unroll
+            for (int d = 0; d < hD; ++d) outv[d] = half_col == 0 ? lo[d] : hi[d];
+          }
+          __nv_bfloat16* dst = (is_dk ? p.dk[path] : p.dv[path]) + (size_t(bh) * p.T + kj) * D + half_col * hD;
+#pragma unroll
+          for (int j = 0; j < hD; j += 8)
+            *reinterpret_cast<uint4*>(dst + j) = make_uint4(bwd_pack(outv[j], outv[j + 1]), bwd_pack(outv[j + 2], outv[j + 3]),
+                                                            bwd_pack(outv[j + 4], outv[j + 5]), bwd_pack(outv[j + 6], outv[j + 7]));
+        }
       }
     }
   }
@@ -587,7 +609,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc(tbase, kTmemAll);
+    tmem_dealloc(tbase, Cfg::kTmemCols);
   }
 }
 
@@ -637,7 +659,7 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const f
   p.scale_log2 = a.scale * kLog2e * (SQ ? 0.5f : 1.f);   // multiplies the logits inside exp2
   p.status = a.dev_status;
   dim3 grid((a.T + kBwdTile - 1) / kBwdTile, BH, 2);
-  attn_bwd_tc_kernel<D, SQ><<<grid, kBwdThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, p);
+  attn_bwd_tc_kernel<D, SQ><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, p);
   count_launches(1);
   e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("attention backward launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }

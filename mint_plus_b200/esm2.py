@@ -69,7 +69,9 @@ class MINT(nn.Module):
         self.use_multimer = use_multimer
         self.use_rmsnorm = use_rmsnorm
         self.use_erf_gelu = use_erf_gelu
-        self.checkpoint_layers = True
+        # True / False, or "auto": checkpoint per layer (as the reference always does, esm2.py:124-132) only when the
+        # activations of all layers would not fit in the free device memory — on a 180 GB part they usually do
+        self.checkpoint_layers = "auto"
         self._init_submodules(layer_factory)
 
     def _init_submodules(self, layer_factory=None):
@@ -120,7 +122,8 @@ class MINT(nn.Module):
             hidden_representations[0] = x
         x = x.transpose(0, 1).contiguous()                             # (B,T,E) -> (T,B,E), laid out sequence-first
 
-        use_ckpt = self.checkpoint_layers and self.training and torch.is_grad_enabled()
+        use_ckpt = self.training and torch.is_grad_enabled() and self._want_checkpoint(x)
+        self.last_forward_checkpointed = use_ckpt
         if use_ckpt and not x.requires_grad:
             x.requires_grad_(True)
         layer_idx = -1
@@ -139,6 +142,18 @@ class MINT(nn.Module):
             hidden_representations[layer_idx + 1] = x
         logits = self.lm_head(x)
         return {"logits": logits, "representations": hidden_representations}
+
+    def _want_checkpoint(self, x: torch.Tensor) -> bool:
+        if self.checkpoint_layers != "auto":
+            return bool(self.checkpoint_layers)
+        if not x.is_cuda:
+            return True
+        # what one layer keeps for its backward pass: about 11 tensors of the size of x (the layer input, both pathways'
+        # q, k, v, the attention output twice, the two residual sums) plus two 4E-wide FFN tensors; 22 x with some margin
+        per_layer = 22 * x.numel() * x.element_size()
+        free, _ = torch.cuda.mem_get_info(x.device)
+        free += torch.cuda.memory_reserved(x.device) - torch.cuda.memory_allocated(x.device)   # cached blocks are reusable
+        return per_layer * len(self.layers) > 0.7 * free
 
     @classmethod
     def from_config(cls, model_size: str, fp8: bool = False, use_erf_gelu: bool = False) -> "MINT":
