@@ -165,6 +165,9 @@ def main():
     ap.add_argument("--workload", default="attn",
                     help="attn (default: the isolated attention op) or a whole-model workload of bench_model.py: "
                          "mint650m_fp8, mint150m_lora, mint3b_infer, mint8m_fwd")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="whole-model workloads only: run this many layers instead of the configuration's (a smaller case for "
+                         "profiler captures; the line is then not a benchmark value and says so)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

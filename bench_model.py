@@ -183,7 +183,10 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src):
     from mint_plus_b200 import _lib as L, ops
     from mint_plus_b200.distributed import FlatGradAllReduce, reduce_max, reduce_sum
 
-    cfg = WORKLOADS[name]
+    cfg = dict(WORKLOADS[name])
+    if getattr(args, "layers", 0):
+        cfg["layers"] = args.layers
+        cfg["desc"] += f" [REDUCED to {args.layers} layers: profiling case, not a benchmark value]"
     dev = torch.device("cuda", local)
     steps, warmup = args.steps, max(args.warmup, 3)
     model = build_model(cfg, dev)
