@@ -4,7 +4,7 @@
 //   Persistent CTAs walk 128 x 256 output tiles (N fastest, so the CTAs running together share rows of x in L2).
 //   warp 0  TMA producer: 128-byte-wide K slabs of x (128 rows) and W (256 rows) into a 4-stage ring, 128B swizzle
 //   warp 1  MMA issuer: four tcgen05.mma (M128 N256) per slab into one of two 256-column TMEM accumulators
-//   warps 2-5  epilogue: one thread per output row; 32 columns at a time: alpha, bias, erf-GELU, cast, store —
+//   warps 2-9  epilogue: two threads per output row (one per half of the tile's columns); 32 columns at a time: alpha, bias, erf-GELU, cast, store —
 //              row-major, or scattered head-major into (B,H,T,D) q/k/v with optional scale and RoPE (the QKV projection),
 //              while the MMA warp already fills the other accumulator.
 // Every mbarrier wait is bounded (see ptx.cuh).
@@ -17,7 +17,8 @@ namespace mintb {
 
 using namespace ptx;
 
-constexpr int kGM = 128, kGN = 256, kGStages = 4, kGThreads = 192;
+constexpr int kGM = 128, kGN = 256, kGStages = 4;
+constexpr int kGEpiWarps = 8, kGEpiThreads = 32 * kGEpiWarps, kGThreads = 64 + kGEpiThreads;   // TMA warp, MMA warp, epilogue warps
 constexpr int kSlabBytes = 128;                       // bytes of K per stage and row (64 bf16 or 128 e4m3)
 constexpr int kABytes = kGM * kSlabBytes, kBBytes = kGN * kSlabBytes, kGStageBytes = kABytes + kBBytes;
 constexpr size_t kGemmSmem = 1024 + size_t(kGStages) * kGStageBytes + 256 + 2 * kGN * sizeof(float);
@@ -43,7 +44,22 @@ struct GemmParams {
   int* status;
 };
 
-__device__ __forceinline__ float gelu_erf_f(float x) { return x * 0.5f * (1.f + erff(x * 0.70710678118654752f)); }
+// erf-GELU x/2 (1 + erf(x / sqrt 2)) with erf from the rational-exponential form 1 - (a1 t + ... + a5 t^5) exp(-z^2),
+// t = 1 / (1 + p z) (absolute error below 1.5e-7, far inside the bf16 / e4m3 output precision): two special-function
+// operations and a short Horner chain per element keep the epilogue shorter than the products of a K = 1280 tile.
+__device__ __forceinline__ float gelu_erf_f(float x) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  float t;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.f)));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * z * z));
+  const float erf_abs = fmaf(-poly * t, e, 1.f);          // erf(|x| / sqrt 2)
+  return 0.5f * x + 0.5f * fabsf(x) * erf_abs;            // x/2 (1 + sign(x) erf(|x|/sqrt 2))
+}
 
 __device__ __forceinline__ float load_bias(const void* bias, int dtype, int n) {
   return dtype == MINTB_F32 ? static_cast<const float*>(bias)[n] : __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n]);
@@ -77,7 +93,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (tid == 0) {
     for (int s = 0; s < kGStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 128); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], kGEpiThreads); }
     fence_mbar_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
@@ -138,9 +154,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else {
+    // eight warps: warp w works on TMEM lanes 32 (w % 4) ... (the quarter it may access) and on column half (w - 2) / 4
     const int quarter = warp % 4;
+    const int chalf = (warp - 2) / 4;
     const int row = quarter * 32 + lane;
-    const int et = (warp - 2) * 32 + lane;   // thread index among the 128 epilogue threads
+    const int et = (warp - 2) * 32 + lane;   // thread index among the epilogue threads
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     uint32_t ab = 0, ab_phase = 0;
     bool ok = true;
@@ -148,8 +166,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int m0 = (t / tiles_n) * kGM, n0 = (t % tiles_n) * kGN;
       const int m = m0 + row;
       float* bias_t = s_bias + ab * kGN;
-      for (int j = et; j < kGN; j += 128) bias_t[j] = (p.bias != nullptr && n0 + j < p.N) ? load_bias(p.bias, p.bias_dtype, n0 + j) : 0.f;
-      named_bar_sync(1, 128);
+      for (int j = et; j < kGN; j += kGEpiThreads) bias_t[j] = (p.bias != nullptr && n0 + j < p.N) ? load_bias(p.bias, p.bias_dtype, n0 + j) : 0.f;
+      named_bar_sync(1, kGEpiThreads);
       ok = mbar_wait(&acc_full[ab], ab_phase, p.status, 0x704);
       if (!ok) break;
       tc_fence_after();
@@ -157,7 +175,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int hm_b = 0, hm_t = 0;   // head-major: decode the row once
       if constexpr (EPI == kEpiHeadMajor) { hm_t = m / p.B; hm_b = m % p.B; }
 #pragma unroll 1
-      for (int c0 = 0; c0 < kGN; c0 += 32) {
+      for (int c0 = chalf * (kGN / 2); c0 < (chalf + 1) * (kGN / 2); c0 += 32) {
         if (n0 + c0 >= p.N) break;   // uniform
         uint32_t r[32];
         tmem_ld32(tacc + c0, r);
@@ -180,13 +198,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             constexpr int hd = HD / 2;
             if (rot) {
 #pragma unroll
-              for (int h0 = 0; h0 < 32; h0 += HD) {
+              for (int j = 0; j < hd; j += 4) {   // table rows are read 16 bytes at a time
+                const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.rope_cos + size_t(hm_t) * hd + j));
+                const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.rope_sin + size_t(hm_t) * hd + j));
+                const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
-                for (int j = 0; j < hd; ++j) {
-                  const float cs = p.rope_cos[size_t(hm_t) * hd + j], sn = p.rope_sin[size_t(hm_t) * hd + j];
-                  const float a = v[h0 + j], bb = v[h0 + j + hd];
-                  v[h0 + j] = a * cs - bb * sn;
-                  v[h0 + j + hd] = bb * cs + a * sn;
+                for (int h0 = 0; h0 < 32; h0 += HD) {
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float a = v[h0 + j + e], bb = v[h0 + j + e + hd];
+                    v[h0 + j + e] = a * cs[e] - bb * sn[e];
+                    v[h0 + j + e + hd] = bb * cs[e] + a * sn[e];
+                  }
                 }
               }
             }
@@ -211,11 +234,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               tmem_ld32(tacc + c2, r2);
               tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                float x = fmaf(__uint_as_float(r2[j]), p.alpha, bias_t[c2 + j]);
-                if (which == 0) x *= p.q_scale;
-                const float cs = p.rope_cos[size_t(hm_t) * 32 + j], sn = p.rope_sin[size_t(hm_t) * 32 + j];
-                v[j] = upper ? v[j] * cs + x * sn : v[j] * cs - x * sn;
+              for (int j = 0; j < 32; j += 4) {
+                const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.rope_cos + size_t(hm_t) * 32 + j));
+                const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.rope_sin + size_t(hm_t) * 32 + j));
+                const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float x = fmaf(__uint_as_float(r2[j + e]), p.alpha, bias_t[c2 + j + e]);
+                  if (which == 0) x *= p.q_scale;
+                  v[j + e] = upper ? v[j + e] * cs[e] + x * sn[e] : v[j + e] * cs[e] - x * sn[e];
+                }
               }
             }
             if (m < p.M) {
