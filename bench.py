@@ -165,6 +165,8 @@ def main():
     ap.add_argument("--workload", default="attn",
                     help="attn (default: the isolated attention op) or a whole-model workload of bench_model.py: "
                          "mint650m_fp8, mint150m_lora, mint3b_infer, mint8m_fwd")
+    ap.add_argument("--no-model-metric", action="store_true",
+                    help="attn workload: skip the MINT-650M FP8 pairs/s measurement that is added to the line as `model_650m`")
     ap.add_argument("--layers", type=int, default=0,
                     help="whole-model workloads only: run this many layers instead of the configuration's (a smaller case for "
                          "profiler captures; the line is then not a benchmark value and says so)")
@@ -185,7 +187,9 @@ def main():
         if world > 1:
             dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         peaks, peak_src = load_peaks()
-        bench_model.run(args.workload, args, rank, world, local, ClockSampler, peaks, peak_src)
+        line = bench_model.run(args.workload, args, rank, world, local, ClockSampler, peaks, peak_src)
+        if line is not None:
+            print(json.dumps(line), flush=True)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
@@ -298,27 +302,59 @@ def main():
     h2d = sum(t.numel() * t.element_size() for t in host) + host_cid.numel() * 4 + host_pad.numel()
     d2h = sum(t.numel() * t.element_size() for t in out_host)
 
-    def step_e2e():
-        d = [t.to(dev, non_blocking=True).requires_grad_(True) for t in host[:6]]
-        g = host[6].to(dev, non_blocking=True)
-        o = M.multimer_attention(*d, chain_ids=host_cid.to(dev, non_blocking=True),
-                                 key_padding_mask=host_pad.to(dev, non_blocking=True))
-        grads = torch.autograd.grad(o, d, g)
-        for dst, src in zip(out_host, (o.detach(), *grads)):
-            dst.copy_(src, non_blocking=True)
+    # Three streams, so that the copy engines and the SMs work at the same time: step i's inputs are copied in while step
+    # i-1 computes and step i-2's results are copied out.  Every step still moves all of its inputs and results.
+    NBUF = 3
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    s_main = torch.cuda.current_stream()
+    in_bufs = [[torch.empty(B, H, T, D, dtype=torch.bfloat16, device=dev) for _ in range(7)] for _ in range(NBUF)]
+    id_bufs = [(torch.empty_like(host_cid, device=dev), torch.empty_like(host_pad, device=dev)) for _ in range(NBUF)]
+    res_bufs = [None] * NBUF
+    ev_in = [torch.cuda.Event() for _ in range(NBUF)]
+    ev_done = [torch.cuda.Event() for _ in range(NBUF)]
+    ev_out = [torch.cuda.Event() for _ in range(NBUF)]
+    out_hosts = [out_host] + [[torch.empty_like(t).pin_memory() for t in out_host] for _ in range(NBUF - 1)]
 
-    for _ in range(3):
-        step_e2e()
+    def step_e2e(i):
+        k = i % NBUF
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_done[k])                       # the step that last used these device buffers has computed
+            for dst, src in zip(in_bufs[k], host):
+                dst.copy_(src, non_blocking=True)
+            id_bufs[k][0].copy_(host_cid, non_blocking=True)
+            id_bufs[k][1].copy_(host_pad, non_blocking=True)
+            ev_in[k].record(s_in)
+        s_main.wait_event(ev_in[k])
+        s_main.wait_event(ev_out[k])                          # its previous results have left the device
+        d = [t.detach().requires_grad_(True) for t in in_bufs[k][:6]]
+        o = M.multimer_attention(*d, chain_ids=id_bufs[k][0], key_padding_mask=id_bufs[k][1])
+        grads = torch.autograd.grad(o, d, in_bufs[k][6])
+        res_bufs[k] = (o.detach(), *grads)
+        ev_done[k].record(s_main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_done[k])
+            for dst, src in zip(out_hosts[k], res_bufs[k]):
+                dst.copy_(src, non_blocking=True)
+            ev_out[k].record(s_out)
+
+    def drain_e2e():
+        s_main.wait_stream(s_in)
+        s_main.wait_stream(s_out)
+
+    for i in range(3):
+        step_e2e(i)
+    drain_e2e()
     barrier()
-    e2e_steps = min(steps, 20)
-    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(e2e_steps)]
-    for s, e in ev2:
-        flush.zero_()
-        s.record()
-        step_e2e()
-        e.record()
+    e2e_steps = min(steps, 30)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flush.zero_()
+    e0.record()
+    for i in range(e2e_steps):
+        step_e2e(i)
+    drain_e2e()
+    e1.record()
     barrier()
-    e2e_ms = sum(s.elapsed_time(e) for s, e in ev2)
+    e2e_ms = e0.elapsed_time(e1)
     clocks = sampler.finish()
     ops.check_device_status(dev)
 
@@ -331,6 +367,16 @@ def main():
     ms_total, e2e_ms = stats.tolist()
     total_flops_step = float(work.item())
 
+    # The second headline metric, PPI pairs/s of the MINT-650M FP8 forward+backward step, measured in the same run and
+    # attached to the line (a short run of the `mint650m_fp8` workload of bench_model.py; every rank takes part).
+    model_line = None
+    if not args.no_model_metric:
+        import bench_model
+        del dts, dgrad, in_bufs, res_bufs, flush
+        torch.cuda.empty_cache()
+        peaks_m, peak_src_m = load_peaks()
+        model_line = bench_model.run("mint650m_fp8", args, rank, world, local, ClockSampler, peaks_m, peak_src_m,
+                                     steps=max(2, min(steps, 4)), with_cpu_baseline=False)
     if rank == 0:
         peaks, peak_src = load_peaks()
         value = total_flops_step * steps / (ms_total * 1e-3) / 1e12
@@ -344,7 +390,9 @@ def main():
             "config": {"workload": "isolated combined-softmax multimer attention fwd+bwd, B=8 H=20 D=32 T=1024 per GPU",
                        "rope": "self pathway", "l2": "flushed between timed steps (256 MiB write)",
                        "launch": "CUDA graph replay of one step" if use_graph else "eager launches",
-                       "flops": "14*H*T*Tk*D per pair, Tk = unpadded keys"},
+                       "flops": "14*H*T*Tk*D per pair, Tk = unpadded keys",
+                       "e2e": "host->device copies, compute and device->host copies of consecutive steps overlap on three "
+                              "streams; every step moves all of its inputs and results"},
             "roofline": {"bound": "tensor", "kernel": dom[0], "achieved": achieved, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES,
                          "peak_source": peak_src, "fwd_ms": fwd_t, "bwd_ms": bwd_t,
@@ -354,6 +402,9 @@ def main():
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if model_line is not None:
+            line["model_650m"] = {k: model_line[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "dtype", "config",
+                                                             "roofline", "e2e", "gpu_launches")}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_baseline()
         print(json.dumps(line), flush=True)

@@ -178,7 +178,8 @@ def run_reference(name, args, rank):
     print(json.dumps(line), flush=True)
 
 
-def run(name, args, rank, world, local, ClockSampler, peaks, peak_src):
+def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=None, with_cpu_baseline=True):
+    """Runs the workload on this rank; returns the JSON line (a dict) on rank 0 and None elsewhere."""
     import torch.distributed as dist
     from mint_plus_b200 import _lib as L, ops
     from mint_plus_b200.distributed import FlatGradAllReduce, reduce_max, reduce_sum
@@ -188,7 +189,7 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src):
         cfg["layers"] = args.layers
         cfg["desc"] += f" [REDUCED to {args.layers} layers: profiling case, not a benchmark value]"
     dev = torch.device("cuda", local)
-    steps, warmup = args.steps, max(args.warmup, 3)
+    steps, warmup = (steps or args.steps), max(args.warmup, 3)
     model = build_model(cfg, dev)
     tokens, chain_ids = make_pairs(cfg, rank)
     labels = None
@@ -325,6 +326,7 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src):
                 "e2e": {"value": pairs_total * e2e_steps / (e2e_ms * 1e-3), "unit": "pairs/s", "h2d_bytes_per_step": h2d,
                         "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
                 "gpu_launches": int(launches_per_step * steps), "clocks": clocks}
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and with_cpu_baseline and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(cfg)
-        print(json.dumps(line), flush=True)
+        return line
+    return None
