@@ -134,9 +134,10 @@ def cpu_baseline(cfg, seconds_budget=25.0):
     mask = chain_ids.unsqueeze(-1) != chain_ids.unsqueeze(-2)
 
     def oracle_attention(q_s, k_s, v_s, q_c, k_c, v_c, *, chain_mask=None, key_padding_mask=None, rope=True, scale=None,
-                         sqrt_softmax=False, **kw):
-        return O.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, chain_mask, key_padding_mask, scale=scale, rope=rope,
-                                    sqrt_softmax=sqrt_softmax)
+                         sqrt_softmax=False, out_seq_first=False, **kw):
+        out = O.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, chain_mask, key_padding_mask, scale=scale, rope=rope,
+                                   sqrt_softmax=sqrt_softmax)
+        return out.permute(2, 0, 1, 3).contiguous() if out_seq_first else out   # the reference's own permute copy
 
     saved = ops.multimer_attention
     ops.multimer_attention = oracle_attention

@@ -25,16 +25,16 @@ __device__ __forceinline__ float group_sum(float v) {
 // y[d] = x[d] cos - x[d+h] sin (d < h), y[d] = x[d] cos + x[d-h] sin (d >= h)   (rotary_embedding.py:16-24).
 template <typename T, int D>
 __device__ __forceinline__ void stage_row(const T* __restrict__ x, int t, int Tlen, const float* cos_tab,
-                                          const float* sin_tab, float* dst, int lane, int nlanes) {
+                                          const float* sin_tab, float* dst, int lane, int nlanes, size_t row_stride = D) {
   constexpr int h = D / 2;
   for (int d = lane; d < D; d += nlanes) {
     float v = 0.f;
     if (t < Tlen) {
-      v = ld_f(x + size_t(t) * D + d);
+      v = ld_f(x + size_t(t) * row_stride + d);
       if (cos_tab != nullptr) {
         int f = d < h ? d : d - h;
         float c = cos_tab[size_t(t) * h + f], s = sin_tab[size_t(t) * h + f];
-        float partner = d < h ? -ld_f(x + size_t(t) * D + d + h) : ld_f(x + size_t(t) * D + d - h);
+        float partner = d < h ? -ld_f(x + size_t(t) * row_stride + d + h) : ld_f(x + size_t(t) * row_stride + d - h);
         v = v * c + partner * s;
       }
     }
@@ -53,6 +53,7 @@ struct SimtParams {
   float* delta;  // [B][H][T]
   int B, H, T, TW;
   float scale;
+  size_t o_row, o_bh;   // element strides of out and d_out: between queries, between (batch, head) pairs
   int sqrt_sm;  // square-root softmax: out = sum_j sqrt(p_j) v_j (mu_scaling/layer.py:162-163)
 };
 
@@ -141,7 +142,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_fwd_simt_kernel(SimtParams 
   if (i < p.T) {
     // A row whose keys are all padded gives 0/0 = NaN, as the softmax of an all -inf row does in PyTorch.
     const float inv = p.sqrt_sm ? rsqrtf(l) : 1.f / l;
-    T* o = static_cast<T*>(p.out) + head + size_t(i) * D + g * 8;
+    T* o = static_cast<T*>(p.out) + size_t(bh) * p.o_bh + size_t(i) * p.o_row + g * 8;
 #pragma unroll
     for (int d = 0; d < 8; ++d) st_f(o + d, acc[d] * inv);
     if (g == 0) p.lse[size_t(bh) * p.T + i] = (m + log2f(l)) * kLn2;
@@ -167,8 +168,8 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dq_simt_kernel(SimtPara
   const T* q_c = static_cast<const T*>(p.q_c) + head;
   const T* k_c = static_cast<const T*>(p.k_c) + head;
   const T* v_c = static_cast<const T*>(p.v_c) + head;
-  const T* o = static_cast<const T*>(p.out) + head;
-  const T* dO = static_cast<const T*>(p.d_out) + head;
+  const T* o = static_cast<const T*>(p.out) + size_t(bh) * p.o_bh;
+  const T* dO = static_cast<const T*>(p.d_out) + size_t(bh) * p.o_bh;
 
   stage_row<T, D>(q_s, i, p.T, p.cos_tab, p.sin_tab, sq_s[r], g, G);
   stage_row<T, D>(q_c, i, p.T, nullptr, nullptr, sq_c[r], g, G);
@@ -180,8 +181,8 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dq_simt_kernel(SimtPara
   for (int d = 0; d < 8; ++d) {
     qs[d] = sq_s[r][g * 8 + d];
     qc[d] = sq_c[r][g * 8 + d];
-    go[d] = ld_f(dO + size_t(irow) * D + g * 8 + d);
-    dpart = fmaf(go[d], ld_f(o + size_t(irow) * D + g * 8 + d), dpart);
+    go[d] = ld_f(dO + size_t(irow) * p.o_row + g * 8 + d);
+    dpart = fmaf(go[d], ld_f(o + size_t(irow) * p.o_row + g * 8 + d), dpart);
     dqs[d] = 0.f;
     dqc[d] = 0.f;
   }
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkv_simt_kernel(SimtPar
   const T* q_c = static_cast<const T*>(p.q_c) + head;
   const T* k_c = static_cast<const T*>(p.k_c) + head;
   const T* v_c = static_cast<const T*>(p.v_c) + head;
-  const T* dO = static_cast<const T*>(p.d_out) + head;
+  const T* dO = static_cast<const T*>(p.d_out) + size_t(bh) * p.o_bh;
 
   stage_row<T, D>(k_s, j, p.T, p.cos_tab, p.sin_tab, sk_s[r], g, G);
   stage_row<T, D>(k_c, j, p.T, nullptr, nullptr, sk_c[r], g, G);
@@ -302,7 +303,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkv_simt_kernel(SimtPar
       const int lane = threadIdx.x % 32;
       stage_row<T, D>(q_s, i0 + ii, p.T, p.cos_tab, p.sin_tab, sq_s[ii], lane, 32);
       stage_row<T, D>(q_c, i0 + ii, p.T, nullptr, nullptr, sq_c[ii], lane, 32);
-      stage_row<T, D>(dO, i0 + ii, p.T, nullptr, nullptr, sdo[ii], lane, 32);
+      stage_row<T, D>(dO, i0 + ii, p.T, nullptr, nullptr, sdo[ii], lane, 32, p.o_row);
     }
     if (threadIdx.x < QT) {
       const int i = i0 + threadIdx.x;
@@ -385,6 +386,8 @@ static SimtParams make_params(const AttnArgs& a) {
   p.B = a.B; p.H = a.H; p.T = a.T; p.TW = a.meta.TW;
   p.scale = a.scale;
   p.sqrt_sm = a.sqrt_softmax ? 1 : 0;
+  p.o_row = out_row_stride(a);
+  p.o_bh = out_bh_stride(a);
   return p;
 }
 

@@ -169,6 +169,7 @@ struct FwdParams {
   int H, T, TW, NT;
   float scale_log2;  // scale * log2(e)
   int* status;
+  size_t out_row_stride, out_bh_stride;   // elements between consecutive queries / (batch, head) pairs of `out`
 };
 
 // entry flags (low three bits are the class bits kHasIntra | kHasInter | kHasPad)
@@ -625,7 +626,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     tc_fence_after();
     if (ok) {
       constexpr int NC = D / 2;   // output columns written by this thread
-      __nv_bfloat16* orow = p.out + (size_t(bh) * p.T + qi) * D + ch * NC;
+      __nv_bfloat16* orow = p.out + size_t(bh) * p.out_bh_stride + size_t(qi) * p.out_row_stride + ch * NC;
       if (n_ent == 0) {
         if (qi < p.T) {   // no unpadded key at all: NaN, as the softmax of an all -inf row gives in the PyTorch path
           const uint32_t nan2 = 0x7FC07FC0u;
@@ -709,7 +710,7 @@ static int fwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s) {
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   }
   FwdParams p{a.meta.bits, a.meta.kpad, a.meta.cls, static_cast<__nv_bfloat16*>(a.out), a.lse, a.H, a.T, a.meta.TW, a.meta.NT,
-              a.scale * kLog2e, a.dev_status};
+              a.scale * kLog2e, a.dev_status, out_row_stride(a), out_bh_stride(a)};
   dim3 grid((a.T + kBM - 1) / kBM, BH);
   attn_fwd_tc_kernel<D, SQ><<<grid, kTcThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, p);
   count_launches(1);

@@ -51,12 +51,14 @@ static EncodeTiledFn bwd_encode_fn() {
   return fn;
 }
 
-static bool bwd_make_map(CUtensorMap* m, const void* ptr, int D, int T, int BH, int box_rows) {
+// (B,H,T,D) tensors: dimensions (D, T, BH), box (D, rows, 1).  Sequence-first (T,B,H,D) tensors: dimensions (D, BH, T),
+// box (D, 1, rows) — the same bytes land in shared memory, the two outer coordinates swap places.
+static bool bwd_make_map(CUtensorMap* m, const void* ptr, int D, int T, int BH, int box_rows, bool seq_first = false) {
   EncodeTiledFn fn = bwd_encode_fn();
   if (fn == nullptr) return false;
-  cuuint64_t dims[3] = {cuuint64_t(D), cuuint64_t(T), cuuint64_t(BH)};
-  cuuint64_t strides[2] = {cuuint64_t(D) * 2, cuuint64_t(T) * D * 2};
-  cuuint32_t box[3] = {cuuint32_t(D), cuuint32_t(box_rows), 1};
+  cuuint64_t dims[3] = {cuuint64_t(D), cuuint64_t(seq_first ? BH : T), cuuint64_t(seq_first ? T : BH)};
+  cuuint64_t strides[2] = {cuuint64_t(D) * 2, cuuint64_t(seq_first ? BH : T) * D * 2};
+  cuuint32_t box[3] = {cuuint32_t(D), cuuint32_t(seq_first ? 1 : box_rows), cuuint32_t(seq_first ? box_rows : 1)};
   cuuint32_t es[3] = {1, 1, 1};
   CUtensorMapSwizzle sw = D == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : D == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
   return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es,
@@ -105,7 +107,7 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
 // `factor` is 1, or 1/2 for the square-root softmax (whose kernel works with sqrt(p) = exp2((s c - lse) / 2) and delta / 2).
 __global__ void __launch_bounds__(256) bwd_stats_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                                         const float* __restrict__ lse, float2* __restrict__ stats, int BH, int T,
-                                                        int Tpad, int D, float factor) {
+                                                        int Tpad, int D, float factor, size_t row_stride, size_t bh_stride) {
   const int lpr = D / 8;  // lanes per row
   const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   const size_t prow = idx / lpr;          // row in the padded layout
@@ -115,9 +117,9 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const __nv_bfloat16* __r
   const bool live = bh < size_t(BH) && t < T;
   float acc = 0.f;
   if (live) {
-    const size_t row = bh * T + t;
-    const uint4 a = *reinterpret_cast<const uint4*>(o + row * D + c * 8);
-    const uint4 b = *reinterpret_cast<const uint4*>(d_o + row * D + c * 8);
+    const size_t off = bh * bh_stride + size_t(t) * row_stride + c * 8;   // same layout for O and dO
+    const uint4 a = *reinterpret_cast<const uint4*>(o + off);
+    const uint4 b = *reinterpret_cast<const uint4*>(d_o + off);
     const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
     const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
 #pragma unroll
@@ -208,6 +210,7 @@ struct BwdParams {
   int H, T, Tpad, TW, NT;
   float scale, scale_log2;
   int* status;
+  int do_seq_first;                // dO is laid out (T,B,H,D): its tensor map takes (0, bh, t) instead of (0, t, bh)
 };
 
 // ring counter with phase bit: position in [0, N), phase flips on wrap
@@ -392,7 +395,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         unsigned char* dst = sQ + size_t(lr.pos) * 2 * Cfg::kTileBytes;
         mbar_expect_tx(&q_full[lr.pos], 2 * Cfg::kTileBytes);
         tma_load_3d(dst, mq, &q_full[lr.pos], 0, next_q * kBwdTile, bh);
-        tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[lr.pos], 0, next_q * kBwdTile, bh);
+        if (p.do_seq_first) tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[lr.pos], 0, bh, next_q * kBwdTile);
+        else tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[lr.pos], 0, next_q * kBwdTile, bh);
         ++next_q;
         lr.advance();
       };
@@ -640,7 +644,7 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const f
   if (!bwd_make_map(&mqs, q_s, D, a.T, BH, kBwdTile) || !bwd_make_map(&mks, k_s, D, a.T, BH, kBwdTile) ||
       !bwd_make_map(&mvs, a.v_s, D, a.T, BH, kBwdTile) || !bwd_make_map(&mqc, a.q_c, D, a.T, BH, kBwdTile) ||
       !bwd_make_map(&mkc, a.k_c, D, a.T, BH, kBwdTile) || !bwd_make_map(&mvc, a.v_c, D, a.T, BH, kBwdTile) ||
-      !bwd_make_map(&mdo, a.d_out, D, a.T, BH, kBwdTile)) {
+      !bwd_make_map(&mdo, a.d_out, D, a.T, BH, kBwdTile, a.out_seq_first)) {
     set_error("mintb_attn_bwd: cuTensorMapEncodeTiled failed");
     return MINTB_ECUDA;
   }
@@ -658,6 +662,7 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const f
   p.scale = a.scale;
   p.scale_log2 = a.scale * kLog2e * (SQ ? 0.5f : 1.f);   // multiplies the logits inside exp2
   p.status = a.dev_status;
+  p.do_seq_first = a.out_seq_first ? 1 : 0;
   dim3 grid((a.T + kBwdTile - 1) / kBwdTile, BH, 2);
   attn_bwd_tc_kernel<D, SQ><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, p);
   count_launches(1);
@@ -691,7 +696,8 @@ int launch_attn_bwd_tc(const AttnArgs& a) {
     const size_t n = size_t(a.B) * a.H * tpad * (a.D / 8);
     bwd_stats_kernel<<<unsigned((n + 255) / 256), 256, 0, a.stream>>>(static_cast<const __nv_bfloat16*>(a.out),
                                                                      static_cast<const __nv_bfloat16*>(a.d_out), a.lse, stats,
-                                                                     a.B * a.H, a.T, tpad, a.D, a.sqrt_softmax ? 0.5f : 1.f);
+                                                                     a.B * a.H, a.T, tpad, a.D, a.sqrt_softmax ? 0.5f : 1.f, out_row_stride(a),
+                                                                     out_bh_stride(a));
     count_launches(1);
   }
   int rc = MINTB_EUNSUPPORTED;

@@ -73,10 +73,15 @@ struct AttnArgs {
   int dtype;
   bool rope;
   bool sqrt_softmax;
+  bool out_seq_first;                // out / d_out laid out (T,B,H,D) instead of (B,H,T,D)
   float scale;
   cudaStream_t stream;
   int* dev_status;
 };
+
+// element strides of out / d_out: row (query) stride and (batch, head) stride
+inline size_t out_row_stride(const AttnArgs& a) { return a.out_seq_first ? size_t(a.B) * a.H * a.D : size_t(a.D); }
+inline size_t out_bh_stride(const AttnArgs& a) { return a.out_seq_first ? size_t(a.D) : size_t(a.T) * a.D; }
 
 void set_error(const char* fmt, ...);
 void count_launches(int n);  // process-wide tally of kernels launched by this library

@@ -133,7 +133,16 @@ __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_bwd_kernel(LnPara
   const bool norm = p.gamma != nullptr;
   float* acc_g = ln_smem + size_t(warp) * 2 * p.E;   // sum dy * xhat
   float* acc_b = acc_g + p.E;                        // sum dy
-  if (norm) {
+  // Up to 1280 columns the parameter-gradient sums of a lane's own columns stay in registers over all the rows the warp
+  // walks; wider rows accumulate in the warp's slice of shared memory instead.
+  constexpr bool kRegAcc = MAXV <= 5;
+  float rg[kRegAcc ? MAXV : 1][8], rb[kRegAcc ? MAXV : 1][8];
+  if (kRegAcc) {
+#pragma unroll
+    for (int k = 0; k < (kRegAcc ? MAXV : 1); ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) rg[k][j] = rb[k][j] = 0.f;
+  } else if (norm) {
     for (int i = lane; i < 2 * p.E; i += 32) acc_g[i] = 0.f;
     __syncwarp();
   }
@@ -168,9 +177,14 @@ __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_bwd_kernel(LnPara
             ds[k][j] = g;
             c1 += g;
             c2 = fmaf(g, xhat, c2);
-            // this lane alone touches these entries; element e = 8 vi + j sits at j * nvec + vi (no bank conflicts)
-            acc_g[j * nvec + vi] = fmaf(dyv[j], xhat, acc_g[j * nvec + vi]);
-            acc_b[j * nvec + vi] += dyv[j];
+            if (kRegAcc) {
+              rg[kRegAcc ? k : 0][j] = fmaf(dyv[j], xhat, rg[kRegAcc ? k : 0][j]);
+              rb[kRegAcc ? k : 0][j] += dyv[j];
+            } else {
+              // this lane alone touches these entries; element e = 8 vi + j sits at j * nvec + vi (no bank conflicts)
+              acc_g[j * nvec + vi] = fmaf(dyv[j], xhat, acc_g[j * nvec + vi]);
+              acc_b[j * nvec + vi] += dyv[j];
+            }
           }
         }
       }
@@ -212,6 +226,19 @@ __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_bwd_kernel(LnPara
     }
   }
   if (norm) {
+    if (kRegAcc) {   // the register sums go through the same shared-memory slices for the reduction over the CTA's warps
+#pragma unroll
+      for (int k = 0; k < (kRegAcc ? MAXV : 1); ++k) {
+        const int vi = lane + 32 * k;
+        if (vi < nvec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            acc_g[j * nvec + vi] = rg[k][j];
+            acc_b[j * nvec + vi] = rb[k][j];
+          }
+        }
+      }
+    }
     __syncthreads();
     float* dst = p.partial + size_t(blockIdx.x) * 2 * p.E;
     for (int i = threadIdx.x; i < 2 * p.E; i += kLnWarps * 32) {
@@ -225,22 +252,45 @@ __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_bwd_kernel(LnPara
   }
 }
 
-// dgamma[e] = sum over CTAs of partial[c][0][e], dbeta likewise; fixed order.
+// dgamma[e] = sum over CTAs of partial[c][0][e], dbeta likewise; fixed order.  CTA = 32 columns x 8 row lanes: each lane
+// adds every 8th partial, the 8 sums meet in shared memory.
 __global__ void __launch_bounds__(256) ln_param_grad_kernel(const float* __restrict__ partial, int n_parts, int E, float* __restrict__ dgamma,
                                                             float* __restrict__ dbeta) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= 2 * E) return;
+  __shared__ float red[8][33];
+  const int cl = threadIdx.x % 32, rl = threadIdx.x / 32;
+  const int i = blockIdx.x * 32 + cl;
   float t = 0.f;
-  for (int c = 0; c < n_parts; ++c) t += partial[size_t(c) * 2 * E + i];
-  if (i < E) dgamma[i] = t; else dbeta[i - E] = t;
+  if (i < 2 * E)
+    for (int c = rl; c < n_parts; c += 8) t += partial[size_t(c) * 2 * E + i];
+  red[rl][cl] = t;
+  __syncthreads();
+  if (rl == 0 && i < 2 * E) {
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sum += red[k][cl];
+    if (i < E) dgamma[i] = sum; else dbeta[i - E] = sum;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ GELU backward + column sums
 constexpr int kColRows = 256;   // rows per CTA strip
 constexpr int kColLanes = 8;    // threads that share a column group, each taking every 8th row of the strip
 
+// d/dz [z/2 (1 + erf(z / sqrt 2))] = (1 + erf(z / sqrt 2)) / 2 + z exp(-z^2 / 2) / sqrt(2 pi).  erf comes from the
+// rational-exponential form 1 - (a1 t + ... + a5 t^5) exp(-u^2), t = 1 / (1 + p u), u = |z| / sqrt 2 (absolute error below
+// 1.5e-7), which needs the very exponential the second term needs: one exp2 and one reciprocal per element.
 __device__ __forceinline__ float gelu_erf_grad(float z) {
-  return 0.5f * (1.f + erff(z * 0.70710678118654752f)) + z * __expf(-0.5f * z * z) * 0.3989422804014327f;
+  const float u = fabsf(z) * 0.70710678118654752f;
+  float t, e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, u, 1.f)));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-0.72134752044448170f * z * z));   // exp(-z^2 / 2)
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float erf_abs = fmaf(-poly * t, e, 1.f);                   // erf(|z| / sqrt 2)
+  const float cdf = 0.5f + copysignf(0.5f * erf_abs, z);
+  return fmaf(z * 0.3989422804014327f, e, cdf);
 }
 
 // CTA = 32 column groups (8 columns each: 256 columns) x 8 row lanes over a strip of kColRows rows; a warp reads 512
@@ -254,7 +304,7 @@ __global__ void __launch_bounds__(256) gelu_bwd_colsum_kernel(const __nv_bfloat1
   const int m0 = blockIdx.y * kColRows, m1 = min(M, m0 + kColRows);
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (live) {
-#pragma unroll 4
+#pragma unroll 8
     for (int m = m0 + rl; m < m1; m += kColLanes) {
       const size_t off = size_t(m) * N + size_t(cg) * 8;
       float g[8];
@@ -342,7 +392,7 @@ int ln_maxv(int E) { return E <= 512 ? 2 : (E <= 1280 ? 5 : (E <= 2560 ? 10 : 0)
 
 int ln_grid(int rows) {
   const int want = (rows + kLnWarps - 1) / kLnWarps;
-  return want < 148 * 8 ? want : 148 * 8;   // a few CTAs per SM; rows are walked with a grid stride
+  return want < 148 * 4 ? want : 148 * 4;   // a few CTAs per SM; rows are walked with a grid stride
 }
 
 }  // namespace
@@ -369,7 +419,8 @@ int mintb_add_layernorm_fwd(const void* x, const void* r, float a, float b, cons
   p.s_out = static_cast<__nv_bfloat16*>(s_out); p.y_out = static_cast<__nv_bfloat16*>(y_out);
   p.stats = reinterpret_cast<float2*>(stats); p.rows = rows; p.E = E; p.eps = eps;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int grid = (rows + kLnWarps - 1) / kLnWarps;
+  const int want = (rows + kLnWarps - 1) / kLnWarps;
+  const int grid = want < 148 * 16 ? want : 148 * 16;   // rows are walked with a grid stride
   switch (ln_maxv(E)) {
     case 2: add_layernorm_fwd_kernel<2><<<grid, kLnWarps * 32, 0, st>>>(p); break;
     case 5: add_layernorm_fwd_kernel<5><<<grid, kLnWarps * 32, 0, st>>>(p); break;
@@ -425,7 +476,7 @@ int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const void* x, co
   if (e != cudaSuccess) return fail("mintb_add_layernorm_bwd", e);
   count_launches(1);
   if (norm) {
-    ln_param_grad_kernel<<<(2 * E + 255) / 256, 256, 0, st>>>(p.partial, grid, E, dgamma, dbeta);
+    ln_param_grad_kernel<<<(2 * E + 31) / 32, 256, 0, st>>>(p.partial, grid, E, dgamma, dbeta);
     count_launches(1);
   }
   e = cudaGetLastError();

@@ -111,14 +111,14 @@ class _TwoPathwayLayer(nn.Module):
             q_s, k_s, v_s = ops.qkv_project(x, ops_s[0], ops_s[1], sa.num_heads, rope=tabs, fp8=ops_s[2])
             q_c, k_c, v_c = ops.qkv_project(x, ops_c[0], ops_c[1], ma.num_heads, fp8=ops_c[2])
             attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=False, scale=sa.scaling,
-                                              sqrt_softmax=sqrt_sm, **mask_kw)
+                                              sqrt_softmax=sqrt_sm, out_seq_first=True, **mask_kw)
         else:
             q_s, k_s, v_s = sa.project_qkv_4d(x)
             q_c, k_c, v_c = ma.project_qkv_4d(x)
             attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=rope,
                                               inv_freq=sa.rot_emb.inv_freq if rope else None, scale=sa.scaling,
-                                              sqrt_softmax=sqrt_sm, **mask_kw)
-        attn_out = attn_out.permute(2, 0, 1, 3).reshape(T, B, E)
+                                              sqrt_softmax=sqrt_sm, out_seq_first=True, **mask_kw)
+        attn_out = attn_out.reshape(T, B, E)      # the kernels wrote (T,B,H,D): a view, no permute copy
         if x.is_cuda and x.dtype == torch.bfloat16:
             return _linear(sa.out_proj, attn_out), None
         return sa.out_proj(attn_out), None

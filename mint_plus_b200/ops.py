@@ -155,7 +155,8 @@ class _MultimerAttentionFn(torch.autograd.Function):
         B, H, T, D = q_s.shape
         dt = _DTYPES[q_s.dtype]
         lib = L.lib()
-        out = torch.empty_like(q_s)
+        # sequence-first result: (T,B,H,D), which the layer views as its (T,B,E) activations without a copy
+        out = torch.empty((T, B, H, D) if flags & L.FLAG_OUT_SEQ_FIRST else (B, H, T, D), dtype=q_s.dtype, device=q_s.device)
         lse = torch.empty(B, H, T, dtype=torch.float32, device=q_s.device)
         ws_bytes = lib.mintb_attn_fwd_workspace_bytes(B, H, T, D, dt, flags)
         ws = _workspace(ws_bytes, q_s.device)
@@ -190,8 +191,10 @@ class _MultimerAttentionFn(torch.autograd.Function):
 def multimer_attention(q_self, k_self, v_self, q_cross, k_cross, v_cross, *, meta: Optional[MaskMeta] = None,
                        chain_ids=None, chain_mask=None, key_padding_mask=None, rope: bool = True,
                        inv_freq: Optional[torch.Tensor] = None, scale: Optional[float] = None,
-                       sqrt_softmax: bool = False, force_simt: bool = False) -> torch.Tensor:
-    """Two-pathway combined-softmax attention on (B,H,T,D) projections; differentiable.
+                       sqrt_softmax: bool = False, force_simt: bool = False, out_seq_first: bool = False) -> torch.Tensor:
+    """Two-pathway combined-softmax attention on (B,H,T,D) projections; differentiable.  The result is (B,H,T,D), or
+    (T,B,H,D) with out_seq_first=True (the layout of the layer's (T,B,E) activations: no permute copy before out_proj).
+
 
     out = (P o ~M) V_self + (P o M) V_cross,  P = softmax_j where(M, s*Qc Kc^T, s*R(Qs) R(Ks)^T), padded keys -inf
     (modules.py:94-154 of the reference).  With rope=True the raw projections are passed and the kernels rotate
@@ -215,7 +218,8 @@ def multimer_attention(q_self, k_self, v_self, q_cross, k_cross, v_cross, *, met
         raise ValueError("meta already carries the chain and padding masks")
     if (meta.B, meta.T) != (B, T):
         raise ValueError(f"mask metadata is for (B, T) = ({meta.B}, {meta.T}), tensors have ({B}, {T})")
-    flags = (L.FLAG_ROPE if rope else 0) | (L.FLAG_SQRT_SOFTMAX if sqrt_softmax else 0) | (L.FLAG_FORCE_SIMT if force_simt else 0)
+    flags = ((L.FLAG_ROPE if rope else 0) | (L.FLAG_SQRT_SOFTMAX if sqrt_softmax else 0) | (L.FLAG_FORCE_SIMT if force_simt else 0)
+             | (L.FLAG_OUT_SEQ_FIRST if out_seq_first else 0))
     cos = sin = None
     if rope:
         cos, sin, _ = rope_tables(T, D, q_self.device, inv_freq)

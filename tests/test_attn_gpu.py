@@ -303,3 +303,27 @@ def test_layer_forward_backward_matches_oracle_composition():
     torch.testing.assert_close(xg.grad.cpu(), wgrad_x, rtol=1e-3, atol=1e-4)
     torch.testing.assert_close(glayer.multimer_attn.fused_qkv.weight.grad.cpu(), wgrad_w, rtol=1e-3, atol=1e-4)
     layer.to("cpu")
+
+
+@pytest.mark.parametrize("dtype,force_simt", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
+@pytest.mark.parametrize("shape", [(2, 3, 200, 64), (2, 4, 130, 32), (1, 2, 77, 16)])
+def test_sequence_first_output_layout(shape, dtype, force_simt):
+    """out_seq_first writes (T,B,H,D) and takes the upstream gradient in that layout: same numbers, no permute copies."""
+    B, H, T, D = shape
+    ts, cid, pad, grad = O.make_op_inputs(B, H, T, D, seed=5 + T, max_pad=T // 5)
+    kw = dict(chain_ids=cid.to(DEV), key_padding_mask=pad.to(DEV), force_simt=force_simt)
+    leaves = [t.to(DEV, dtype).requires_grad_(True) for t in ts]
+    out = M.multimer_attention(*leaves, **kw)
+    g = grad.to(DEV, dtype)
+    want = torch.autograd.grad(out, leaves, g)
+    leaves2 = [t.to(DEV, dtype).requires_grad_(True) for t in ts]
+    out2 = M.multimer_attention(*leaves2, out_seq_first=True, **kw)
+    assert tuple(out2.shape) == (T, B, H, D) and out2.is_contiguous()
+    torch.testing.assert_close(out2.permute(1, 2, 0, 3), out, rtol=0, atol=0)
+    got = torch.autograd.grad(out2, leaves2, g.permute(2, 0, 1, 3).contiguous())
+    ops.check_device_status()
+    for a, b in zip(got, want):
+        if dtype == torch.float32 or force_simt:
+            torch.testing.assert_close(a, b, rtol=0, atol=0)          # deterministic kernels: bit-equal
+        else:
+            assert (a.float() - b.float()).abs().max().item() <= 1e-2 * b.float().abs().max().item() + 1e-6   # dQ atomics reorder

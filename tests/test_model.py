@@ -43,12 +43,13 @@ def oracle_attention(monkeypatch):
         return chain_ids, padding_mask
 
     def fake_attention(q_s, k_s, v_s, q_c, k_c, v_c, *, meta=None, chain_mask=None, key_padding_mask=None, rope=True,
-                       inv_freq=None, scale=None, sqrt_softmax=False, **kw):
+                       inv_freq=None, scale=None, sqrt_softmax=False, out_seq_first=False, **kw):
         if meta is not None:
             ids, key_padding_mask = meta
             chain_mask = ids.unsqueeze(-1) != ids.unsqueeze(-2)
-        return O.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, chain_mask, key_padding_mask, scale=scale, rope=rope,
-                                    sqrt_softmax=sqrt_softmax)
+        out = O.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, chain_mask, key_padding_mask, scale=scale, rope=rope,
+                                   sqrt_softmax=sqrt_softmax)
+        return out.permute(2, 0, 1, 3).contiguous() if out_seq_first else out
 
     monkeypatch.setattr(modules_plus, "_cached_ids_meta", fake_meta)
     monkeypatch.setattr(ops, "multimer_attention", fake_attention)
