@@ -46,6 +46,7 @@ __device__ __forceinline__ float ld_param(const void* p, int dtype, int i) {
 }
 
 constexpr int kLnWarps = 4;
+constexpr int kLnMaxE = 2560;   // widest row the LayerNorm kernels take
 
 struct LnParams {
   const __nv_bfloat16 *x, *r;       // r may be null (then s = a x)
@@ -64,9 +65,17 @@ struct LnParams {
 // MAXV: 16-byte vectors per lane (E <= MAXV * 256)
 template <int MAXV>
 __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_fwd_kernel(LnParams p) {
+  __shared__ __align__(16) float s_gamma[kLnMaxE], s_beta[kLnMaxE];   // the parameters as fp32, read back 16 bytes at a time
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int nvec = p.E / 8;
   const float inv_e = 1.f / float(p.E);
+  if (p.gamma != nullptr) {
+    for (int i = threadIdx.x; i < p.E; i += kLnWarps * 32) {
+      s_gamma[i] = ld_param(p.gamma, p.param_dtype, i);
+      s_beta[i] = p.beta != nullptr ? ld_param(p.beta, p.param_dtype, i) : 0.f;
+    }
+    __syncthreads();
+  }
   for (int row = blockIdx.x * kLnWarps + warp; row < p.rows; row += gridDim.x * kLnWarps) {
     const uint4* xr = reinterpret_cast<const uint4*>(p.x + size_t(row) * p.E);
     const uint4* rr = p.r != nullptr ? reinterpret_cast<const uint4*>(p.r + size_t(row) * p.E) : nullptr;
@@ -111,11 +120,13 @@ __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_fwd_kernel(LnPara
     for (int k = 0; k < MAXV; ++k) {
       const int vi = lane + 32 * k;
       if (vi < nvec) {
-        float o[8];
+        float o[8], gm[8], bt[8];
+        *reinterpret_cast<float4*>(gm) = *reinterpret_cast<const float4*>(s_gamma + vi * 8);
+        *reinterpret_cast<float4*>(gm + 4) = *reinterpret_cast<const float4*>(s_gamma + vi * 8 + 4);
+        *reinterpret_cast<float4*>(bt) = *reinterpret_cast<const float4*>(s_beta + vi * 8);
+        *reinterpret_cast<float4*>(bt + 4) = *reinterpret_cast<const float4*>(s_beta + vi * 8 + 4);
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          o[j] = fmaf((v[k][j] - mean) * rstd, ld_param(p.gamma, p.param_dtype, vi * 8 + j),
-                      p.beta != nullptr ? ld_param(p.beta, p.param_dtype, vi * 8 + j) : 0.f);
+        for (int j = 0; j < 8; ++j) o[j] = fmaf((v[k][j] - mean) * rstd, gm[j], bt[j]);
         reinterpret_cast<uint4*>(p.y_out + size_t(row) * p.E)[vi] = pack8(o);
       }
     }
@@ -127,10 +138,15 @@ __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_fwd_kernel(LnPara
 template <int MAXV>
 __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_bwd_kernel(LnParams p) {
   extern __shared__ float ln_smem[];   // [kLnWarps][2][E] when normalising
+  __shared__ __align__(16) float s_gamma[kLnMaxE];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int nvec = p.E / 8;
   const float inv_e = 1.f / float(p.E);
   const bool norm = p.gamma != nullptr;
+  if (norm) {
+    for (int i = threadIdx.x; i < p.E; i += kLnWarps * 32) s_gamma[i] = ld_param(p.gamma, p.param_dtype, i);
+    __syncthreads();
+  }
   float* acc_g = ln_smem + size_t(warp) * 2 * p.E;   // sum dy * xhat
   float* acc_b = acc_g + p.E;                        // sum dy
   // Up to 1280 columns the parameter-gradient sums of a lane's own columns stay in registers over all the rows the warp
@@ -169,10 +185,13 @@ __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_bwd_kernel(LnPara
 #pragma unroll
             for (int j = 0; j < 8; ++j) xv[j] *= p.a;
           }
+          float gm[8];
+          *reinterpret_cast<float4*>(gm) = *reinterpret_cast<const float4*>(s_gamma + vi * 8);
+          *reinterpret_cast<float4*>(gm + 4) = *reinterpret_cast<const float4*>(s_gamma + vi * 8 + 4);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float xhat = (xv[j] - st.x) * st.y;
-            const float g = dyv[j] * ld_param(p.gamma, p.param_dtype, vi * 8 + j);
+            const float g = dyv[j] * gm[j];
             xh[k][j] = xhat;
             ds[k][j] = g;
             c1 += g;
