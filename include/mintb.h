@@ -51,6 +51,9 @@ extern "C" {
 #define MINTB_FLAG_ROPE 1u         /* rotate Q and K of the SELF pathway (rotary_embedding.py:47-55)                */
 #define MINTB_FLAG_SQRT_SOFTMAX 2u /* sqrt(softmax) coefficients (mu_scaling/layer.py:162-163)                       */
 #define MINTB_FLAG_FORCE_SIMT 4u   /* run the fp32 CUDA-core kernels even where the tcgen05 kernels apply (checking) */
+#define MINTB_FLAG_ROT_SAVED 16u    /* mintb_attn_bwd only, with MINTB_FLAG_ROPE: `workspace` is the very buffer mintb_attn_fwd was
+                                      given for the same inputs (sized for the backward pass), so the rotated copies of Q_self and
+                                      K_self at its start are reused instead of being computed again */
 #define MINTB_FLAG_OUT_SEQ_FIRST 8u /* `out` and `d_out` are laid out (T,B,H,D) — the layer's (T,B,E) — instead of (B,H,T,D):
                                       saves the permute copy before out_proj (modules.py:146-150) and the one of its gradient */
 

@@ -66,6 +66,20 @@ static bool bwd_make_map(CUtensorMap* m, const void* ptr, int D, int T, int BH, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// fp32 dQ accumulator [BH][T][D] as a reduction target: box = (D / 4 columns, 32 rows, 1), i.e. what one compute warp
+// drains from TMEM per query tile.
+static bool bwd_make_dq_map(CUtensorMap* m, const void* ptr, int D, int T, int BH) {
+  EncodeTiledFn fn = bwd_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[3] = {cuuint64_t(D), cuuint64_t(T), cuuint64_t(BH)};
+  cuuint64_t strides[2] = {cuuint64_t(D) * 4, cuuint64_t(T) * D * 4};
+  cuuint32_t box[3] = {cuuint32_t(D / 4), 32, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUtensorMapSwizzle sw = D == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : D == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 __device__ __forceinline__ float bwd_ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -197,7 +211,10 @@ struct BwdCfg {
   static constexpr int kColDK = 0, kColDV = kAcc, kColDQ = 2 * kAcc, kColBuf = (2 + kNDq) * kAcc;
   static constexpr uint32_t kTmemCols = kTwoPerSm ? 256 : 512;
   static constexpr int kVPG = 16 / kCW;                         // 16-column query groups per thread and half (1 or 2)
-  static constexpr size_t kSmemBytes = 1024 + 2 * kTileBytes + size_t(kQStages) * 2 * kTileBytes + size_t(kNDq) * kDsBytes + 4096;
+  static constexpr int kDqWarpBytes = 32 * (D / 4) * 4;          // staging of one warp's dQ slice: 32 queries x D/4 fp32 columns
+  static constexpr int kDqStageBytes = kCW * kDqWarpBytes;
+  static constexpr size_t kSmemBytes =
+      1024 + 2 * kTileBytes + size_t(kQStages) * 2 * kTileBytes + size_t(kNDq) * kDsBytes + kDqStageBytes + 4096;
 };
 
 struct BwdParams {
@@ -227,7 +244,8 @@ __global__ void __launch_bounds__(BwdCfg<D>::kThreads, BwdCfg<D>::kMinBlocks)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_constant__ CUtensorMap map_ks,
                    const __grid_constant__ CUtensorMap map_vs, const __grid_constant__ CUtensorMap map_qc,
                    const __grid_constant__ CUtensorMap map_kc, const __grid_constant__ CUtensorMap map_vc,
-                   const __grid_constant__ CUtensorMap map_do, BwdParams p) {
+                   const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_dq_s,
+                   const __grid_constant__ CUtensorMap map_dq_c, BwdParams p) {
   using Cfg = BwdCfg<D>;
   constexpr int RB = Cfg::kRowBytes, kNBuf = Cfg::kNBuf, kQStages = Cfg::kQStages, kNDq = Cfg::kNDq, kVPG = Cfg::kVPG;
   constexpr int kBwdThreads = Cfg::kThreads, kComputeThreads = 32 * Cfg::kCW;
@@ -238,7 +256,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   unsigned char* sV = sK + Cfg::kTileBytes;
   unsigned char* sQ = sV + Cfg::kTileBytes;                          // [stage][0: Q_i, 1: dO_i]
   unsigned char* sDS = sQ + size_t(kQStages) * 2 * Cfg::kTileBytes;  // [buf][half][128 rows x 128 B]
-  unsigned char* tail = sDS + size_t(kNDq) * Cfg::kDsBytes;
+  unsigned char* sDqStage = sDS + size_t(kNDq) * Cfg::kDsBytes;      // [compute warp][32 queries][D/4 fp32], swizzled
+  unsigned char* tail = sDqStage + Cfg::kDqStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
   uint64_t* kv_full = bars;            // 1
   uint64_t* acc_full = bars + 1;       // 1
@@ -445,28 +464,37 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     const uint32_t flip = path == 0 ? 0xffffu : 0u;   // keep-bit = mask bit XOR flip
     const uint64_t c22 = pack2(p.scale_log2, p.scale_log2);
     const float4* stats_bh = reinterpret_cast<const float4*>(p.stats + size_t(bh) * p.Tpad);   // two queries per float4
-    float* dq_bh = p.dq_acc[path] + size_t(bh) * p.T * D;
     bool ok = true;
     int it = 0;
     Ring<kNBuf> br;
 
+    // dQ of a tile leaves through shared memory: each compute warp stages its 32 queries x NC columns and one lane adds
+    // them to the fp32 accumulator in HBM with ONE bulk reduction (instead of a 16-byte atomic per thread and 4 columns).
+    const CUtensorMap* mdq = path == 0 ? &map_dq_s : &map_dq_c;
+    unsigned char* my_stage = sDqStage + size_t(cwp) * Cfg::kDqWarpBytes;
     auto drain_dq = [&](int jt, int qtile) -> bool {   // add dQ of active tile jt (query tile qtile) to HBM
       if (!mbar_wait(&dq_full[jt % kNDq], (jt / kNDq) & 1, p.status, 0x601)) return false;
       tc_fence_after();
       constexpr int NC = D / 4 * kVPG;   // columns per thread
+      constexpr int kRowB = NC * 4;      // bytes per staged row: 64, 32 or 16
       uint32_t v[NC];
       tmem_ld_n<NC>(tbase + lane_base + kColDQ + (jt % kNDq) * kAcc + grp * NC, v);
+      if (lane == 0) bulk_wait_read_all();   // the previous reduction of this warp has read the staging rows
+      __syncwarp();
       tmem_ld_wait();
-      const int qi = qtile * kBwdTile + r;
-      if (qi < p.T) {
-        float* dst = dq_bh + size_t(qi) * D + grp * NC;
-#pragma unroll
-        for (int e = 0; e < NC; e += 4)
-          atomicAdd(reinterpret_cast<float4*>(dst + e), make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
-                                                                    __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3])));
-      }
       tc_fence_before();
       mbar_arrive(&dq_empty[jt % kNDq]);
+#pragma unroll
+      for (int e = 0; e < NC; e += 4) {
+        const uint32_t off = kRowB == 16 ? uint32_t(lane) * 16u : swizzled_offset(lane, e / 4, kRowB);
+        *reinterpret_cast<uint4*>(my_stage + off) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && qtile * kBwdTile + quarter * 32 < p.T) {   // rows past T inside the box are dropped by the copy engine
+        tma_reduce_add_3d(mdq, my_stage, grp * NC, qtile * kBwdTile + quarter * 32, bh);
+        bulk_commit_group();
+      }
       return true;
     };
 
@@ -548,6 +576,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       ++it;
     }
     if (ok && prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
+    if (lane == 0) bulk_wait_all();   // the reductions must have landed before the kernel ends
 
     // ---- epilogue: 16-column groups vg 0,1 write the two column halves of dK (scaled, un-rotated for the self pathway),
     //      vg 2,3 those of dV
@@ -648,6 +677,11 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const f
     set_error("mintb_attn_bwd: cuTensorMapEncodeTiled failed");
     return MINTB_ECUDA;
   }
+  CUtensorMap mdq_s, mdq_c;
+  if (!bwd_make_dq_map(&mdq_s, acc_s, D, a.T, BH) || !bwd_make_dq_map(&mdq_c, acc_c, D, a.T, BH)) {
+    set_error("mintb_attn_bwd: cuTensorMapEncodeTiled failed for the dQ accumulators");
+    return MINTB_ECUDA;
+  }
   cudaError_t e = cudaFuncSetAttribute(attn_bwd_tc_kernel<D, SQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Cfg::kSmemBytes));
   if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   BwdParams p{};
@@ -664,7 +698,7 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const f
   p.status = a.dev_status;
   p.do_seq_first = a.out_seq_first ? 1 : 0;
   dim3 grid((a.T + kBwdTile - 1) / kBwdTile, BH, 2);
-  attn_bwd_tc_kernel<D, SQ><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, p);
+  attn_bwd_tc_kernel<D, SQ><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, mdq_s, mdq_c, p);
   count_launches(1);
   e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("attention backward launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
@@ -680,7 +714,7 @@ int launch_attn_bwd_tc(const AttnArgs& a) {
   if (a.rope) {
     __nv_bfloat16* qr = reinterpret_cast<__nv_bfloat16*>(ws);
     __nv_bfloat16* kr = reinterpret_cast<__nv_bfloat16*>(ws + bwd_rot_bytes(a.B, a.H, a.T, a.D));
-    launch_rope_rotate(a, qr, kr);
+    if (!a.rot_saved) launch_rope_rotate(a, qr, kr);
     q_s = qr;
     k_s = kr;
     ws += 2 * bwd_rot_bytes(a.B, a.H, a.T, a.D);

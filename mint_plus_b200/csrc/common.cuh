@@ -74,6 +74,7 @@ struct AttnArgs {
   bool rope;
   bool sqrt_softmax;
   bool out_seq_first;                // out / d_out laid out (T,B,H,D) instead of (B,H,T,D)
+  bool rot_saved;                    // backward: the workspace already starts with the rotated Q_self, K_self
   float scale;
   cudaStream_t stream;
   int* dev_status;

@@ -159,7 +159,15 @@ class _MultimerAttentionFn(torch.autograd.Function):
         out = torch.empty((T, B, H, D) if flags & L.FLAG_OUT_SEQ_FIRST else (B, H, T, D), dtype=q_s.dtype, device=q_s.device)
         lse = torch.empty(B, H, T, dtype=torch.float32, device=q_s.device)
         ws_bytes = lib.mintb_attn_fwd_workspace_bytes(B, H, T, D, dt, flags)
-        ws = _workspace(ws_bytes, q_s.device)
+        # With in-kernel RoPE the forward pass leaves rotated copies of Q_self and K_self at the start of its workspace.  When a
+        # backward pass will follow, the workspace is sized for it and kept, so that pass starts from those copies.
+        keep_ws = bool(flags & L.FLAG_ROPE) and ws_bytes > 0 and any(ctx.needs_input_grad[:6])
+        if keep_ws:
+            ws_bytes = max(ws_bytes, lib.mintb_attn_bwd_workspace_bytes(B, H, T, D, dt, flags))
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q_s.device)
+        else:
+            ws = _workspace(ws_bytes, q_s.device)
+        ctx.fwd_ws = ws if keep_ws else None
         with torch.cuda.device(q_s.device):
             rc = lib.mintb_attn_fwd(_ptr(q_s), _ptr(k_s), _ptr(v_s), _ptr(q_c), _ptr(k_c), _ptr(v_c), _ptr(meta.buf),
                                     _ptr(cos), _ptr(sin), _ptr(out), _ptr(lse), _ptr(ws), ws_bytes, B, H, T, D, dt,
@@ -178,11 +186,15 @@ class _MultimerAttentionFn(torch.autograd.Function):
         d_out = d_out.contiguous()
         grads = [torch.empty_like(q_s) for _ in range(6)]
         ws_bytes = lib.mintb_attn_bwd_workspace_bytes(B, H, T, D, dt, ctx.flags)
-        ws = _workspace(ws_bytes, q_s.device)
+        flags = ctx.flags
+        if ctx.fwd_ws is not None:
+            ws, ws_bytes, flags = ctx.fwd_ws, ctx.fwd_ws.numel(), flags | L.FLAG_ROT_SAVED
+        else:
+            ws = _workspace(ws_bytes, q_s.device)
         with torch.cuda.device(q_s.device):
             rc = lib.mintb_attn_bwd(_ptr(q_s), _ptr(k_s), _ptr(v_s), _ptr(q_c), _ptr(k_c), _ptr(v_c), _ptr(ctx.meta.buf),
                                     _ptr(cos), _ptr(sin), _ptr(out), _ptr(lse), _ptr(d_out), *[_ptr(g) for g in grads],
-                                    _ptr(ws), ws_bytes, B, H, T, D, dt, ctx.flags, ctx.scale, _stream(),
+                                    _ptr(ws), ws_bytes, B, H, T, D, dt, flags, ctx.scale, _stream(),
                                     _ptr(_dev_status(q_s.device)))
         L.check(rc, "mintb_attn_bwd")
         return (*grads, None, None, None, None, None)
