@@ -375,8 +375,14 @@ def main():
         del dts, dgrad, in_bufs, res_bufs, flush
         torch.cuda.empty_cache()
         peaks_m, peak_src_m = load_peaks()
-        model_line = bench_model.run("mint650m_fp8", args, rank, world, local, ClockSampler, peaks_m, peak_src_m,
-                                     steps=max(2, min(steps, 4)), with_cpu_baseline=False)
+        try:
+            model_line = bench_model.run("mint650m_fp8", args, rank, world, local, ClockSampler, peaks_m, peak_src_m,
+                                         steps=max(2, min(steps, 4)), with_cpu_baseline=False)
+        except Exception as exc:                       # the attention line must not be lost with it
+            if world > 1:
+                raise                                  # ranks would fall out of step: let the launcher see the failure
+            sys.stderr.write(f"bench: the MINT-650M measurement failed: {exc!r}\n")
+            model_line = {"error": repr(exc)}
     if rank == 0:
         peaks, peak_src = load_peaks()
         value = total_flops_step * steps / (ms_total * 1e-3) / 1e12
@@ -404,7 +410,7 @@ def main():
         }
         if model_line is not None:
             line["model_650m"] = {k: model_line[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "dtype", "config",
-                                                             "roofline", "e2e", "gpu_launches")}
+                                                             "roofline", "e2e", "gpu_launches", "error") if k in model_line}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_baseline()
         print(json.dumps(line), flush=True)
