@@ -116,7 +116,8 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
 }
 
 // ------------------------------------------------------------------------------------------------ pre / post passes
-// Per-query statistics for the backward pass: stats[bh][i] = (-lse * log2 e, -delta), delta = sum_d dO[i][d] * O[i][d].
+// Per-query statistics for the backward pass: nl = -lse * log2 e and nd = -delta, delta = sum_d dO[i][d] * O[i][d], stored
+// for each pair of queries (2p, 2p+1) of a (batch, head) as the 16 bytes (nl0, nl1, nd0, nd1).
 // Rows are padded to a multiple of 128 per (batch, head); the pad entries are (-inf, 0), which makes exp2 give 0 there.
 // `factor` is 1, or 1/2 for the square-root softmax (whose kernel works with sqrt(p) = exp2((s c - lse) / 2) and delta / 2).
 __global__ void __launch_bounds__(256) bwd_stats_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
@@ -144,8 +145,13 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const __nv_bfloat16* __r
     }
   }
   for (int off = lpr / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (bh < size_t(BH) && c == 0)
-    stats[prow] = live ? make_float2(-lse[bh * T + t] * kLog2e * factor, -acc * factor) : make_float2(-INFINITY, 0.f);
+  if (bh < size_t(BH) && c == 0) {
+    // two queries share 16 bytes as (nl0, nl1, nd0, nd1): the kernel then reads each pair of like values as one
+    // 64-bit register pair, ready for its packed fp32x2 arithmetic
+    float* dst = reinterpret_cast<float*>(stats) + (prow / 2) * 4 + (prow % 2);
+    dst[0] = live ? -lse[bh * T + t] * kLog2e * factor : -INFINITY;
+    dst[2] = live ? -acc * factor : 0.f;
+  }
 }
 
 // dq = scale * R^T(acc) for the self pathway (with tables), scale * acc for the cross pathway; fp32 -> bf16.
@@ -220,7 +226,7 @@ struct BwdCfg {
 struct BwdParams {
   const uint32_t *bitsT, *kpad;
   const uint8_t* cls;
-  const float2* stats;             // [B*H][Tpad] (-lse * log2 e, -delta), Tpad = T rounded up to 128
+  const float2* stats;             // [B*H][Tpad / 2] x (nl0, nl1, nd0, nd1): -lse * log2 e and -delta of two queries, Tpad = T rounded up to 128
   const float *cos_tab, *sin_tab;  // null without rope
   float* dq_acc[2];                // fp32 [B*H][T][D] per pathway
   __nv_bfloat16 *dk[2], *dv[2];
@@ -537,9 +543,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           uint32_t pp[8], dd[8];
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
-            const float4 q2 = sq[j / 2];   // (nl0, nd0, nl1, nd1)
+            const float4 q2 = sq[j / 2];   // (nl0, nl1, nd0, nd1)
             float p0, p1;
-            unpack2(ffma2(pack2(__uint_as_float(sv[j]), __uint_as_float(sv[j + 1])), c22, pack2(q2.x, q2.z)), p0, p1);
+            unpack2(ffma2(pack2(__uint_as_float(sv[j]), __uint_as_float(sv[j + 1])), c22, pack2(q2.x, q2.y)), p0, p1);
             p0 = bwd_ex2(p0);
             p1 = bwd_ex2(p1);
             if (!all) {
@@ -547,7 +553,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
               if (!((keep >> (j + 1)) & 1u)) p1 = 0.f;
             }
             float d0, d1;
-            const uint64_t p2 = pack2(p0, p1), dp2 = pack2(__uint_as_float(dpv[j]), __uint_as_float(dpv[j + 1])), nd2 = pack2(q2.y, q2.w);
+            const uint64_t p2 = pack2(p0, p1), dp2 = pack2(__uint_as_float(dpv[j]), __uint_as_float(dpv[j + 1])), nd2 = pack2(q2.z, q2.w);
             if (SQ)   // r = sqrt(p) is what p0, p1 hold: dS = r (dP / 2 - r delta / 2), and r itself multiplies dO in dV
               unpack2(fmul2(p2, ffma2(p2, nd2, fmul2(dp2, pack2(0.5f, 0.5f)))), d0, d1);
             else      // dS = p (dP - delta)
