@@ -589,6 +589,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     if (n_active > 0) {
       if (ok) ok = mbar_wait(acc_full, 0, p.status, 0x603);
       tc_fence_after();
+      MINTB_BTRACE_EV(46);
     }
     if (ok) {
       constexpr int hD = D / 2;

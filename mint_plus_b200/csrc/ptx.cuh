@@ -43,7 +43,10 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 }
 // The hint lets the hardware keep the thread suspended (no issue slots burnt on polling) until the phase completes or
 // the time runs out; completion wakes it at once.
-constexpr uint32_t kSuspendHintNs = 20000;
+#ifndef MINTB_SUSPEND_NS
+#define MINTB_SUSPEND_NS 20000
+#endif
+constexpr uint32_t kSuspendHintNs = MINTB_SUSPEND_NS;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
