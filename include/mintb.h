@@ -181,7 +181,8 @@ MINTB_API int mintb_quantize_e4m3(const void* x, void* out, size_t n, float inv_
  *   null); without z: db = column sums of dy (the bias gradient of a projection).  N a multiple of 8.
  * mintb_qkv_grad_pack: the gradients of head-major q, k, v (B,H,T,D) gathered into one [T*B][3E] matrix with columns
  *   [dQ | dK | dV], dq multiplied by q_scale and dq, dk un-rotated (transpose of the RoPE rotation) when tables are given:
- *   the inverse of mintb_qkv_fwd's epilogue, feeding the dgrad / wgrad products of the fused QKV projection.
+ *   the inverse of mintb_qkv_fwd's epilogue, feeding the dgrad / wgrad products of the fused QKV projection; a non-null
+ *   db (fp32 [3E]) receives the column sums of that matrix, the bias gradient, from the same pass.
  */
 MINTB_API int mintb_add_layernorm_fwd(const void* x, const void* r, float a, float b, const void* gamma, const void* beta,
                                       int param_dtype, void* s_out, void* y_out, float* stats, int rows, int E, float eps,
@@ -191,7 +192,7 @@ MINTB_API int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const v
                                       const void* gamma, int param_dtype, const float* stats, void* dx, void* dr, float* dgamma,
                                       float* dbeta, void* workspace, size_t workspace_bytes, int rows, int E, void* stream);
 MINTB_API int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, int M, int N, void* stream);
-MINTB_API int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g, const float* rope_cos,
+MINTB_API int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g, float* db, const float* rope_cos,
                                   const float* rope_sin, int T, int B, int H, int D, float q_scale, void* stream);
 
 #ifdef __cplusplus

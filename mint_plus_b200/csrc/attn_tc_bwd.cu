@@ -285,6 +285,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   const int nqt = (p.T + kBwdTile - 1) / kBwdTile;
   const uint8_t want = path == 0 ? kHasIntra : kHasInter;
 
+  int any_active = 0;
   for (int i = tid; i < nqt; i += kBwdThreads) {
     uint8_t c = 0;
 #pragma unroll
@@ -295,6 +296,20 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     uint8_t f = 0;
     if (c & want) f = 1 | (((c & 3) == 3) ? 2 : 0) | ((c & kHasPad) ? 4 : 0);
     tq[i] = f;
+    any_active |= f;
+  }
+  // A key tile without a single pair of this pathway (all its keys padded, or every query on the other side of the mask)
+  // has zero gradients: write them and leave before any barrier, TMEM or copy is set up.  Padded batches have many such tiles.
+  if (__syncthreads_or(any_active) == 0) {
+    for (int idx = tid; idx < kBwdTile * (D / 8); idx += kBwdThreads) {
+      const int row = idx / (D / 8), vec = idx % (D / 8);
+      if (k0 + row < p.T) {
+        const size_t off = (size_t(bh) * p.T + k0 + row) * D + vec * 8;
+        *reinterpret_cast<uint4*>(p.dk[path] + off) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(p.dv[path] + off) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    return;
   }
   if (tid == 0) {
     mbar_init(kv_full, 1);

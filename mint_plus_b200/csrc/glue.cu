@@ -357,49 +357,71 @@ __global__ void __launch_bounds__(256) gelu_bwd_colsum_kernel(const __nv_bfloat1
 }
 
 // ------------------------------------------------------------------------------------------------ QKV gradient pack
-// g[(t * B + b)][which * E + h * D + d] = f(dsrc[which][b][h][t][d]), f = q scale and the transposed rotation for dq, dk.
-// Thread = one (row, which, head, 8 dims); for the rotation it also reads the partner half's 8 values.
+// g[(t * B + b)][which * E + h * D + d] = f(dsrc[which][b][h][t][d]), f = q scale and the transposed rotation for dq, dk;
+// db[col] = sum over rows of g (the bias gradient of the fused projection) in the same pass.
+// CTA = 32 column groups (8 columns each: 256 columns of g) x 8 row lanes over a strip of kColRows rows; a thread's column
+// group — pathway third, head, 8 dimensions — is fixed, only (t, b) changes from row to row.
 template <int D>
 __global__ void __launch_bounds__(256) qkv_grad_pack_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
                                                             const __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ g,
-                                                            const float* __restrict__ cos_tab,
+                                                            float* __restrict__ db, const float* __restrict__ cos_tab,
                                                             const float* __restrict__ sin_tab, int T, int B, int H, float q_scale) {
-  constexpr int VPH = D / 8;                         // vectors per head
-  const int E = H * D;
-  const int vecs_per_row = 3 * H * VPH;
-  const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  const size_t total = size_t(T) * B * vecs_per_row;
-  if (idx >= total) return;
-  const int vr = int(idx % vecs_per_row);
-  const size_t row = idx / vecs_per_row;             // t * B + b
-  const int t = int(row / B), b = int(row % B);
-  const int which = vr / (H * VPH), hv = vr % (H * VPH), h = hv / VPH, dv8 = hv % VPH;
+  __shared__ float part[kColLanes][32][8];
+  constexpr int VPH = D / 8, hd = D / 2;             // vectors per head; rotation pairs dimension d with d + hd
+  const int E = H * D, N = 3 * E, M = T * B;
+  const int cl = threadIdx.x % 32, rl = threadIdx.x / 32;
+  const int cg = blockIdx.x * 32 + cl;               // column group
+  const bool live = cg * 8 < N;
+  const int col = live ? cg * 8 : 0;
+  const int which = col / E, e = col % E, h = e / D, dv8 = (e % D) / 8;
   const __nv_bfloat16* src = which == 0 ? dq : (which == 1 ? dk : dv);
-  const size_t base = ((size_t(b) * H + h) * T + t) * D;
-  float v[8];
-  unpack8(__ldg(reinterpret_cast<const uint4*>(src + base) + dv8), v);
-  if (cos_tab != nullptr && which < 2) {
-    // y = R x rotated forward: y_lo = x_lo c - x_hi s, y_hi = x_hi c + x_lo s; the gradient takes the transpose:
-    // dx_lo = dy_lo c + dy_hi s, dx_hi = dy_hi c - dy_lo s
-    constexpr int hd = D / 2;
-    const bool upper = dv8 * 8 >= hd;
-    const int pv = upper ? dv8 - VPH / 2 : dv8 + VPH / 2;
-    float o[8];
-    unpack8(__ldg(reinterpret_cast<const uint4*>(src + base) + pv), o);
-    const int f0 = (upper ? dv8 * 8 - hd : dv8 * 8);
+  const bool rot = cos_tab != nullptr && which < 2;
+  const bool upper = dv8 * 8 >= hd;
+  const int pv = upper ? dv8 - VPH / 2 : dv8 + VPH / 2;   // the vector holding the partner dimensions
+  const int f0 = upper ? dv8 * 8 - hd : dv8 * 8;
+  const float scale = which == 0 ? q_scale : 1.f;
+  const int m0 = blockIdx.y * kColRows, m1 = min(M, m0 + kColRows);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (live) {
+#pragma unroll 4
+    for (int m = m0 + rl; m < m1; m += kColLanes) {
+      const int t = m / B, b = m % B;
+      const uint4* row = reinterpret_cast<const uint4*>(src + ((size_t(b) * H + h) * T + t) * D);
+      float v[8];
+      unpack8(__ldg(row + dv8), v);
+      if (rot) {
+        // y = R x rotated forward: y_lo = x_lo c - x_hi s, y_hi = x_hi c + x_lo s; the gradient takes the transpose:
+        // dx_lo = dy_lo c + dy_hi s, dx_hi = dy_hi c - dy_lo s
+        float o[8], c[8], sn[8];
+        unpack8(__ldg(row + pv), o);
+        const float4* c4 = reinterpret_cast<const float4*>(cos_tab + size_t(t) * hd + f0);
+        const float4* s4 = reinterpret_cast<const float4*>(sin_tab + size_t(t) * hd + f0);
+        *reinterpret_cast<float4*>(c) = __ldg(c4); *reinterpret_cast<float4*>(c + 4) = __ldg(c4 + 1);
+        *reinterpret_cast<float4*>(sn) = __ldg(s4); *reinterpret_cast<float4*>(sn + 4) = __ldg(s4 + 1);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float c = cos_tab[size_t(t) * hd + f0 + j], s = sin_tab[size_t(t) * hd + f0 + j];
-      v[j] = upper ? v[j] * c - o[j] * s : v[j] * c + o[j] * s;
+        for (int j = 0; j < 8; ++j) v[j] = upper ? v[j] * c[j] - o[j] * sn[j] : v[j] * c[j] + o[j] * sn[j];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] *= scale;
+      const uint4 packed = pack8(v);
+      *reinterpret_cast<uint4*>(g + size_t(m) * N + col) = packed;
+      unpack8(packed, v);   // the bias gradient sums what the products will read
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
     }
   }
-  if (which == 0 && q_scale != 1.f) {
+  if (db == nullptr) return;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] *= q_scale;
+  for (int j = 0; j < 8; ++j) part[rl][cl][j] = acc[j];
+  __syncthreads();
+  const int c = threadIdx.x;
+  const int ocol = blockIdx.x * 256 + c;
+  if (ocol < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < kColLanes; ++r) t += part[r][c / 8][c % 8];
+    atomicAdd(db + ocol, t);
   }
-  const size_t col = size_t(which) * E + size_t(h) * D + dv8 * 8;
-  const uint4 packed = pack8(v);
-  *reinterpret_cast<uint4*>(g + row * 3 * E + col) = packed;
 }
 
 int fail(const char* what, cudaError_t e) {
@@ -520,8 +542,8 @@ int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, in
   return e == cudaSuccess ? MINTB_OK : fail("mintb_gelu_bwd_colsum launch", e);
 }
 
-int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g, const float* rope_cos, const float* rope_sin, int T,
-                        int B, int H, int D, float q_scale, void* stream) {
+int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g, float* db, const float* rope_cos,
+                        const float* rope_sin, int T, int B, int H, int D, float q_scale, void* stream) {
   if (dq == nullptr || dk == nullptr || dv == nullptr || g == nullptr || T <= 0 || B <= 0 || H <= 0 ||
       (rope_cos == nullptr) != (rope_sin == nullptr)) {
     set_error("mintb_qkv_grad_pack: null pointer or non-positive size");
@@ -532,15 +554,19 @@ int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g,
     return MINTB_EUNSUPPORTED;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t total = size_t(T) * B * 3 * H * (D / 8);
-  const unsigned grid = unsigned((total + 255) / 256);
+  const int N = 3 * H * D, M = T * B;
+  if (db != nullptr) {
+    cudaError_t e = cudaMemsetAsync(db, 0, size_t(N) * sizeof(float), st);
+    if (e != cudaSuccess) return fail("mintb_qkv_grad_pack memset", e);
+  }
+  dim3 grid((N + 255) / 256, (M + kColRows - 1) / kColRows);
   const __nv_bfloat16 *q = static_cast<const __nv_bfloat16*>(dq), *k = static_cast<const __nv_bfloat16*>(dk),
                       *v = static_cast<const __nv_bfloat16*>(dv);
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g);
   switch (D) {
-    case 16: qkv_grad_pack_kernel<16><<<grid, 256, 0, st>>>(q, k, v, o, rope_cos, rope_sin, T, B, H, q_scale); break;
-    case 32: qkv_grad_pack_kernel<32><<<grid, 256, 0, st>>>(q, k, v, o, rope_cos, rope_sin, T, B, H, q_scale); break;
-    default: qkv_grad_pack_kernel<64><<<grid, 256, 0, st>>>(q, k, v, o, rope_cos, rope_sin, T, B, H, q_scale); break;
+    case 16: qkv_grad_pack_kernel<16><<<grid, 256, 0, st>>>(q, k, v, o, db, rope_cos, rope_sin, T, B, H, q_scale); break;
+    case 32: qkv_grad_pack_kernel<32><<<grid, 256, 0, st>>>(q, k, v, o, db, rope_cos, rope_sin, T, B, H, q_scale); break;
+    default: qkv_grad_pack_kernel<64><<<grid, 256, 0, st>>>(q, k, v, o, db, rope_cos, rope_sin, T, B, H, q_scale); break;
   }
   count_launches(1);
   cudaError_t e = cudaGetLastError();

@@ -363,11 +363,15 @@ def _gelu_erf_grad(z: torch.Tensor) -> torch.Tensor:
     return 0.5 * (1.0 + torch.erf(zf * 0.7071067811865476)) + zf * torch.exp(-0.5 * zf * zf) * 0.3989422804014327
 
 
-def linear_backward(dy, x2d, w, bias, z, needs, out_scale: float = 1.0):
-    """Gradients of y = act(out_scale * x W^T + b): the GELU derivative and the bias gradient come from one fused pass;
-    dgrad and wgrad are plain library GEMMs on bf16 (the static output multiplier is folded into the small operand)."""
+def linear_backward(dy, x2d, w, bias, z, needs, out_scale: float = 1.0, db=None):
+    """Gradients of y = act(out_scale * x W^T + b): the GELU derivative and the bias gradient come from one fused pass
+    (or the bias gradient is handed in as `db` by the pass that produced dy); dgrad and wgrad are plain library GEMMs on
+    bf16 (the static output multiplier is folded into the small operand)."""
     want_db = bias is not None and needs[2]
-    dz, db = gelu_bwd_colsum(dy, z, want_db)
+    if db is not None:
+        dz = dy
+    else:
+        dz, db = gelu_bwd_colsum(dy, z, want_db)
     wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
     dx = dw = None
     if needs[0]:
@@ -508,11 +512,13 @@ class _QkvFn(torch.autograd.Function):
         E = H * D
         # (B,H,T,D) x3 -> [T*B, 3E] with the rotation undone and the q scale applied, in one pass
         g = torch.empty(T * B, 3 * E, dtype=torch.bfloat16, device=x2d.device)
+        want_db = bias is not None and ctx.needs_input_grad[2]
+        db = torch.empty(3 * E, dtype=torch.float32, device=x2d.device) if want_db else None
         with torch.cuda.device(x2d.device):
-            rc = L.lib().mintb_qkv_grad_pack(_ptr(dq.contiguous()), _ptr(dk.contiguous()), _ptr(dv.contiguous()), _ptr(g), _ptr(cos),
-                                             _ptr(sin), T, B, H, D, float(q_scale), _stream())
+            rc = L.lib().mintb_qkv_grad_pack(_ptr(dq.contiguous()), _ptr(dk.contiguous()), _ptr(dv.contiguous()), _ptr(g), _ptr(db),
+                                             _ptr(cos), _ptr(sin), T, B, H, D, float(q_scale), _stream())
         L.check(rc, "mintb_qkv_grad_pack")
-        dx, dw, db = linear_backward(g, x2d, w, bias, None, ctx.needs_input_grad, out_scale)
+        dx, dw, db = linear_backward(g, x2d, w, bias, None, ctx.needs_input_grad, out_scale, db=db)
         return (dx.view(T, B, E) if dx is not None else None), dw, db, None, None, None, None, None, None, None, None
 
 

@@ -103,7 +103,8 @@ def test_qkv_gradient_pack(D, rope):
     q_scale = 0.25
     g = torch.empty(T * B, 3 * E, dtype=torch.bfloat16, device=DEV)
     from mint_plus_b200 import _lib as L
-    rc = L.lib().mintb_qkv_grad_pack(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), g.data_ptr(),
+    db = torch.empty(3 * E, dtype=torch.float32, device=DEV)
+    rc = L.lib().mintb_qkv_grad_pack(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), g.data_ptr(), db.data_ptr(),
                                      cos.data_ptr() if rope else None, sin.data_ptr() if rope else None, T, B, H, D, q_scale,
                                      torch.cuda.current_stream().cuda_stream)
     L.check(rc, "mintb_qkv_grad_pack")
@@ -114,3 +115,4 @@ def test_qkv_gradient_pack(D, rope):
     a = a * q_scale
     want = torch.cat([t.permute(2, 0, 1, 3).reshape(T * B, E) for t in (a, b, dv.float())], dim=1)
     torch.testing.assert_close(g.float(), want, rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(db, g.float().sum(0), rtol=1e-3, atol=1e-3)
