@@ -52,22 +52,6 @@ def make_pairs(cfg, rank=0):
     return tokens, chain_ids
 
 
-def mlm_corrupt(tokens, seed, mask_idx=32):
-    """15 % of the non-special positions become targets; of those 80 % -> <mask>, 10 % -> random amino acid, 10 % kept
-    (training/wrapper.py:57-73 of the reference)."""
-    g = torch.Generator().manual_seed(seed)
-    special = (tokens < 4)
-    pick = (torch.rand(tokens.shape, generator=g) < 0.15) & ~special
-    labels = torch.where(pick, tokens, torch.full_like(tokens, -100))
-    r = torch.rand(tokens.shape, generator=g)
-    out = tokens.clone()
-    out[pick & (r < 0.8)] = mask_idx
-    rnd = torch.randint(4, 24, tokens.shape, generator=g)
-    swap = pick & (r >= 0.8) & (r < 0.9)
-    out[swap] = rnd[swap]
-    return out, labels
-
-
 def build_model(cfg, device):
     import mint_plus_b200 as M
     from mint_plus_b200.lora import apply_lora
@@ -184,6 +168,7 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
     import torch.distributed as dist
     from mint_plus_b200 import _lib as L, ops
     from mint_plus_b200.distributed import FlatGradAllReduce, reduce_max, reduce_sum
+    from mint_plus_b200.training import shared_step
 
     cfg = dict(WORKLOADS[name])
     if getattr(args, "layers", 0):
@@ -193,13 +178,8 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
     steps, warmup = (steps or args.steps), max(args.warmup, 3)
     model = build_model(cfg, dev)
     tokens, chain_ids = make_pairs(cfg, rank)
-    labels = None
-    if cfg["train"]:
-        tokens_in, labels = mlm_corrupt(tokens, cfg["seed"] + rank)
-    else:
-        tokens_in = tokens
-    h_tok, h_cid = tokens_in.pin_memory(), chain_ids.pin_memory()
-    h_lab = labels.pin_memory() if labels is not None else None
+    h_tok, h_cid = tokens.pin_memory(), chain_ids.pin_memory()
+    h_lab = None
     flops_step, flops_gemm, flops_attn = algorithmic_flops(cfg, tokens)
     trainable = [p for p in model.parameters() if p.requires_grad] if cfg["train"] else []
     sync_grads = FlatGradAllReduce(trainable, dtype=torch.float32 if cfg["kind"] == "lora" else torch.bfloat16) \
@@ -212,8 +192,8 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
         if cfg["train"]:
             for p in trainable:
                 p.grad = None
-            logits = model(tok, cid)["logits"]
-            loss = torch.nn.functional.cross_entropy(logits.float().view(-1, logits.shape[-1]), lab.view(-1), ignore_index=-100)
+            # the reference's training step: MLM corruption drawn on the device, forward, masked cross-entropy, backward
+            loss, _ = shared_step(model, (tok, cid))
             loss.backward()
             if sync_grads is not None:
                 sync_grads()

@@ -12,6 +12,7 @@ from .modules_plus import (TransformerLayer_MINT_plus, VanillaFeedForward, build
                            enable_fused_multi_pathway)
 from .modules import RobertaLMHead, TransformerLayer_MINT
 from .esm2 import MINT, MODEL_REGISTRY, Alphabet
+from .training import mlm_corrupt, shared_step
 from .rotary_embedding import RotaryEmbedding
 from .mu_scaling import (Fp8Linear, TransformerLayer_MINT_mu, apply_fp8_to_model, build_mint_mu, calibrate_fp8,
                          compute_tau, unit_variance_init_)
@@ -23,5 +24,5 @@ __all__ = [
     "MultiHeadAttention", "MultimerAttention", "TransformerLayer_MINT_plus", "VanillaFeedForward",
     "build_mint_plus", "enable_fused_multi_pathway", "RotaryEmbedding", "Fp8Linear", "apply_fp8_to_model", "calibrate_fp8",
     "unit_variance_init_", "TransformerLayer_MINT", "TransformerLayer_MINT_mu", "RobertaLMHead", "MINT", "MODEL_REGISTRY",
-    "Alphabet", "build_mint_mu", "compute_tau",
+    "Alphabet", "build_mint_mu", "compute_tau", "mlm_corrupt", "shared_step",
 ]

@@ -140,3 +140,20 @@ def test_model_bf16_training_step_gives_finite_gradients():
     assert torch.isfinite(loss)
     for n, p in model.named_parameters():
         assert p.grad is not None and torch.isfinite(p.grad).all(), n
+
+
+def test_shared_step_masks_only_residues_and_gives_a_finite_loss(oracle_attention):
+    """The MLM step of the reference wrapper (training/wrapper.py:48-86): targets are non-special positions only."""
+    torch.manual_seed(3)
+    model = M.MINT(num_layers=1, embed_dim=64, attention_heads=4, use_multimer=True).train()
+    tokens, chain_ids = c1_batch(21, 3, 80, 10, 30)
+    g = torch.Generator().manual_seed(5)
+    inp, target = M.mlm_corrupt(tokens, 0, model.eos_idx, model.padding_idx, model.mask_idx, g)
+    special = (tokens == 0) | (tokens == model.eos_idx) | (tokens == model.padding_idx)
+    assert not (target & special).any() and target.any()
+    assert torch.equal(inp[~target], tokens[~target])                      # untouched outside the targets
+    changed = inp[target] != tokens[target]
+    assert ((inp[target] == model.mask_idx) | ~changed | ((inp[target] >= 4) & (inp[target] < 24))).all()
+    loss, ppl = M.shared_step(model, (tokens, chain_ids), generator=torch.Generator().manual_seed(6))
+    loss.backward()
+    assert torch.isfinite(loss) and torch.isfinite(ppl) and abs(float(ppl) - float(torch.exp(loss))) < 1e-4
