@@ -17,19 +17,19 @@ import time
 import torch
 
 WORKLOADS = {
-    # BASELINE configuration 4
+    # the reference's 650M FP8 training configuration
     "mint650m_fp8": dict(layers=33, embed=1280, heads=20, pairs=16, T=2048, lo=100, hi=900, seed=4004, train=True,
                          kind="mu_fp8", dtype="e4m3 GEMMs / bf16 attention",
                          desc="MINT-650M muS Res-Post-LN, e4m3 projections, bf16 attention, fwd+bwd, 16 pairs padded to 2048"),
-    # BASELINE configuration 3
+    # the reference's 150M LoRA training configuration
     "mint150m_lora": dict(layers=30, embed=640, heads=20, pairs=32, T=1024, lo=50, hi=500, seed=3003, train=True,
                           kind="lora", dtype="bf16",
                           desc="MINT-150M frozen base + LoRA r=8 on q/k/v/out, bf16, training step, 32 pairs padded to 1024"),
-    # BASELINE configuration 5
+    # the reference's large inference (embedding extraction) configuration
     "mint3b_infer": dict(layers=36, embed=2560, heads=40, pairs=64, T=2048, lo=30, hi=80, lo2=800, hi2=1900, seed=5005,
                          train=False, kind="plus", dtype="bf16",
                          desc="MINT 36x2560 (40 heads) inference forward, bf16, 64 pairs with skewed chain lengths padded to 2048"),
-    # BASELINE configuration 1 (a latency line; its parity is a test)
+    # the reference's CPU-runnable 8M forward configuration (a latency line; its parity is a test)
     "mint8m_fwd": dict(layers=6, embed=320, heads=20, pairs=4, T=512, lo=64, hi=200, seed=1001, train=False,
                        kind="base_fp32", dtype="f32",
                        desc="MINT-8M forward, fp32, 4 pairs padded to 512"),

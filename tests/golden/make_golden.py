@@ -187,7 +187,7 @@ def run_model_case(name, kind, seed, batch_seed, B, T, lo, hi, sqrt_softmax=Fals
 
 MODEL_CASES = [
     # name                kind    weight seed  batch seed  B  T    lo  hi   sqrt
-    ("mint8m_c1",          "base", 1234,        1001,       4, 512, 64, 200, False),   # BASELINE config 1
+    ("mint8m_c1",          "base", 1234,        1001,       4, 512, 64, 200, False),   # the reference's CPU-runnable 8M configuration
     ("mint8m_small",       "base", 1235,        1002,       2, 96,  10, 40,  False),
     ("mint8m_mu",          "mu",   1236,        1003,       2, 160, 20, 70,  False),
     ("mint8m_mu_sqrt",     "mu",   1237,        1004,       2, 160, 20, 70,  True),
