@@ -54,6 +54,9 @@ extern "C" {
 #define MINTB_FLAG_ROT_SAVED 16u    /* mintb_attn_bwd only, with MINTB_FLAG_ROPE: `workspace` is the very buffer mintb_attn_fwd was
                                       given for the same inputs (sized for the backward pass), so the rotated copies of Q_self and
                                       K_self at its start are reused instead of being computed again */
+#define MINTB_FLAG_SKIP_PAD_QUERIES 32u /* query tiles of 128 rows that hold only padded positions are not computed: their rows of
+                                      `out` / `lse` stay unwritten and contribute nothing to the gradients (their d_out rows are
+                                      ignored).  For callers that drop padded tokens from the token-wise work */
 #define MINTB_FLAG_OUT_SEQ_FIRST 8u /* `out` and `d_out` are laid out (T,B,H,D) — the layer's (T,B,E) — instead of (B,H,T,D):
                                       saves the permute copy before out_proj (modules.py:146-150) and the one of its gradient */
 
@@ -155,7 +158,9 @@ MINTB_API int mintb_combine_bwd(const void* intra_logits, const void* inter_logi
  *
  * mintb_qkv_fwd: the fused QKV projection of one pathway (attention.py:97-117, 304-323): x is (T,B,E) flattened to
  * [T*B][E], w [3E][E] with rows ordered [Q;K;V]; q, k, v are written head-major (B,H,T,D) directly (no permute copy),
- * the q third multiplied by q_scale, and the q and k thirds rotated by RoPE when the tables are given.
+ * the q third multiplied by q_scale, and the q and k thirds rotated by RoPE when the tables are given.  With padding
+ * dropped from the token-wise work (variable-length packing) x holds only the n_rows unpadded tokens and row_map[m] = t * B + b
+ * names the token of row m; positions that no row maps to are left untouched in q, k, v (row_map null: all T * B rows).
  *
  * mintb_quantize_e4m3: out[i] = saturate(x[i] * inv_scale) from bf16 (the per-tensor scaled cast of the FP8 path).
  */
@@ -164,7 +169,7 @@ MINTB_API int mintb_linear_fwd(const void* x, const void* w, const void* bias, v
                                int* dev_status);
 MINTB_API int mintb_qkv_fwd(const void* x, const void* w, const void* bias, void* q, void* k, void* v, int T, int B, int H,
                             int D, int in_dtype, int bias_dtype, float alpha, float q_scale, const float* rope_cos,
-                            const float* rope_sin, void* stream, int* dev_status);
+                            const float* rope_sin, const int32_t* row_map, int n_rows, void* stream, int* dev_status);
 MINTB_API int mintb_quantize_e4m3(const void* x, void* out, size_t n, float inv_scale, void* stream);
 
 /* ---------------------------------------------------------------------------------------------------
@@ -193,7 +198,8 @@ MINTB_API int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const v
                                       float* dbeta, void* workspace, size_t workspace_bytes, int rows, int E, void* stream);
 MINTB_API int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, int M, int N, void* stream);
 MINTB_API int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g, float* db, const float* rope_cos,
-                                  const float* rope_sin, int T, int B, int H, int D, float q_scale, void* stream);
+                                  const float* rope_sin, const int32_t* row_map, int n_rows, int T, int B, int H, int D,
+                                  float q_scale, void* stream);
 
 #ifdef __cplusplus
 }

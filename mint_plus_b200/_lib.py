@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libmintb.so")
 
 OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA = 0, -1, -2, -3, -4
 F32, BF16, E4M3 = 0, 1, 2
-FLAG_ROPE, FLAG_SQRT_SOFTMAX, FLAG_FORCE_SIMT, FLAG_OUT_SEQ_FIRST, FLAG_ROT_SAVED = 1, 2, 4, 8, 16
+FLAG_ROPE, FLAG_SQRT_SOFTMAX, FLAG_FORCE_SIMT, FLAG_OUT_SEQ_FIRST, FLAG_ROT_SAVED, FLAG_SKIP_PAD_QUERIES = 1, 2, 4, 8, 16, 32
 STATIC_SCRATCH_BYTES = 32 << 20
 
 _P = c_void_p
@@ -35,14 +35,15 @@ PROTOTYPES = {
     "mintb_attn_bwd": (c_int, [_P] * 6 + [_P, _P, _P, _P, _P, _P] + [_P] * 6 + [_P, c_size_t, c_int, c_int, c_int, c_int,
                                c_int, c_uint, c_float, _P, _P]),
     "mintb_linear_fwd": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P, _P]),
-    "mintb_qkv_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P, _P, _P, _P]),
+    "mintb_qkv_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P, _P, _P, c_int,
+                              _P, _P]),
     "mintb_quantize_e4m3": (c_int, [_P, _P, c_size_t, c_float, _P]),
     "mintb_add_layernorm_fwd": (c_int, [_P, _P, c_float, c_float, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_float, _P]),
     "mintb_add_layernorm_bwd_workspace_bytes": (c_size_t, [c_int, c_int]),
     "mintb_add_layernorm_bwd": (c_int, [_P, _P, _P, _P, c_float, c_float, _P, c_int, _P, _P, _P, _P, _P, _P, c_size_t, c_int,
                                         c_int, _P]),
     "mintb_gelu_bwd_colsum": (c_int, [_P, _P, _P, _P, c_int, c_int, _P]),
-    "mintb_qkv_grad_pack": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P]),
+    "mintb_qkv_grad_pack": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P]),
     "mintb_combine_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "mintb_combine_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "mintb_combine_bwd": (c_int, [_P] * 10 + [_P, c_size_t, c_int, c_int, c_int, c_int, c_int, _P]),

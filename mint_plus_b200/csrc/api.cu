@@ -114,7 +114,8 @@ static int fill_common(AttnArgs& a, const char* who, const void* q_s, const void
                        int T, int D, int dtype, unsigned flags, float scale, void* stream, int* dev_status) {
   int rc = check_shape(B, H, T, D, dtype, who);
   if (rc != MINTB_OK) return rc;
-  if (flags & ~(MINTB_FLAG_ROPE | MINTB_FLAG_SQRT_SOFTMAX | MINTB_FLAG_FORCE_SIMT | MINTB_FLAG_OUT_SEQ_FIRST | MINTB_FLAG_ROT_SAVED)) {
+  if (flags & ~(MINTB_FLAG_ROPE | MINTB_FLAG_SQRT_SOFTMAX | MINTB_FLAG_FORCE_SIMT | MINTB_FLAG_OUT_SEQ_FIRST | MINTB_FLAG_ROT_SAVED |
+                MINTB_FLAG_SKIP_PAD_QUERIES)) {
     set_error("%s: unknown flag bits 0x%x", who, flags);
     return MINTB_EINVAL;
   }
@@ -150,6 +151,7 @@ static int fill_common(AttnArgs& a, const char* who, const void* q_s, const void
   a.sqrt_softmax = (flags & MINTB_FLAG_SQRT_SOFTMAX) != 0;
   a.out_seq_first = (flags & MINTB_FLAG_OUT_SEQ_FIRST) != 0;
   a.rot_saved = (flags & MINTB_FLAG_ROT_SAVED) != 0;
+  a.skip_pad_queries = (flags & MINTB_FLAG_SKIP_PAD_QUERIES) != 0;
   a.scale = scale;
   a.stream = static_cast<cudaStream_t>(stream);
   a.dev_status = dev_status;

@@ -170,6 +170,7 @@ struct FwdParams {
   float scale_log2;  // scale * log2(e)
   int* status;
   size_t out_row_stride, out_bh_stride;   // elements between consecutive queries / (batch, head) pairs of `out`
+  int skip_pad_queries;                   // leave out query tiles that hold only padded positions
 };
 
 // entry flags (low three bits are the class bits kHasIntra | kHasInter | kHasPad)
@@ -265,6 +266,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   MINTB_TRACE_DECL
   MINTB_TRACE_EV(1);
 
+  if (p.skip_pad_queries) {   // the padding bits describe positions, so they cover the query rows of this tile as well
+    const uint32_t* w = p.kpad + size_t(b) * p.TW + 4 * qt;
+    if ((w[0] & w[1] & w[2] & w[3]) == 0xffffffffu) return;   // uniform over the CTA; nothing has been set up yet
+  }
   // tile classes of this query tile: OR of its two 64-row halves
   for (int kt = tid; kt < nkt; kt += kTcThreads) {
     const uint8_t* row0 = p.cls + (size_t(b) * p.NT + 2 * qt) * p.NT;
@@ -710,7 +715,7 @@ static int fwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s) {
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   }
   FwdParams p{a.meta.bits, a.meta.kpad, a.meta.cls, static_cast<__nv_bfloat16*>(a.out), a.lse, a.H, a.T, a.meta.TW, a.meta.NT,
-              a.scale * kLog2e, a.dev_status, out_row_stride(a), out_bh_stride(a)};
+              a.scale * kLog2e, a.dev_status, out_row_stride(a), out_bh_stride(a), a.skip_pad_queries ? 1 : 0};
   dim3 grid((a.T + kBM - 1) / kBM, BH);
   attn_fwd_tc_kernel<D, SQ><<<grid, kTcThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, p);
   count_launches(1);

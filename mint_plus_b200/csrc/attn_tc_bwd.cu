@@ -234,6 +234,7 @@ struct BwdParams {
   float scale, scale_log2;
   int* status;
   int do_seq_first;                // dO is laid out (T,B,H,D): its tensor map takes (0, bh, t) instead of (0, t, bh)
+  int skip_pad_queries;            // query tiles that hold only padded positions are left out
 };
 
 // ring counter with phase bit: position in [0, N), phase flips on wrap
@@ -295,6 +296,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         if (2 * i + a < p.NT && 2 * kt + e < p.NT) c |= p.cls[(size_t(b) * p.NT + 2 * i + a) * p.NT + 2 * kt + e];
     uint8_t f = 0;
     if (c & want) f = 1 | (((c & 3) == 3) ? 2 : 0) | ((c & kHasPad) ? 4 : 0);
+    if (p.skip_pad_queries) {   // the padding bits describe positions: words 4 i .. 4 i + 3 cover the queries of tile i
+      const uint32_t* w = p.kpad + size_t(b) * p.TW + 4 * i;
+      if ((w[0] & w[1] & w[2] & w[3]) == 0xffffffffu) f = 0;
+    }
     tq[i] = f;
     any_active |= f;
   }
@@ -719,6 +724,7 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const f
   p.scale_log2 = a.scale * kLog2e * (SQ ? 0.5f : 1.f);   // multiplies the logits inside exp2
   p.status = a.dev_status;
   p.do_seq_first = a.out_seq_first ? 1 : 0;
+  p.skip_pad_queries = a.skip_pad_queries ? 1 : 0;
   dim3 grid((a.T + kBwdTile - 1) / kBwdTile, BH, 2);
   attn_bwd_tc_kernel<D, SQ><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, mdq_s, mdq_c, p);
   count_launches(1);

@@ -75,6 +75,7 @@ struct AttnArgs {
   bool sqrt_softmax;
   bool out_seq_first;                // out / d_out laid out (T,B,H,D) instead of (B,H,T,D)
   bool rot_saved;                    // backward: the workspace already starts with the rotated Q_self, K_self
+  bool skip_pad_queries;             // query tiles holding only padded positions are left out
   float scale;
   cudaStream_t stream;
   int* dev_status;

@@ -41,6 +41,7 @@ struct GemmParams {
   int B, T, H, D;
   float q_scale;               // multiplies the q third (1 to leave the scaling to the attention kernel)
   const float *rope_cos, *rope_sin;   // [T][D/2]; rotate the q and k thirds when non-null
+  const int32_t* row_map;             // packed input rows: row m of x is token row_map[m] = t * B + b (null: m itself)
   int* status;
 };
 
@@ -173,7 +174,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_after();
       const uint32_t tacc = tbase + lane_base + ab * kGN;
       int hm_b = 0, hm_t = 0;   // head-major: decode the row once
-      if constexpr (EPI == kEpiHeadMajor) { hm_t = m / p.B; hm_b = m % p.B; }
+      if constexpr (EPI == kEpiHeadMajor) {
+        // rows past M (the ragged last tile) compute on token 0 and are not stored: their table reads stay in range
+        const int mo = m < p.M ? (p.row_map != nullptr ? p.row_map[m] : m) : 0;
+        hm_t = mo / p.B;
+        hm_b = mo % p.B;
+      }
 #pragma unroll 1
       for (int c0 = chalf * (kGN / 2); c0 < (chalf + 1) * (kGN / 2); c0 += 32) {
         if (n0 + c0 >= p.N) break;   // uniform
@@ -450,9 +456,10 @@ extern "C" int mintb_linear_fwd(const void* x, const void* w, const void* bias, 
 
 extern "C" int mintb_qkv_fwd(const void* x, const void* w, const void* bias, void* q, void* k, void* v, int T, int B, int H, int D,
                              int in_dtype, int bias_dtype, float alpha, float q_scale, const float* rope_cos,
-                             const float* rope_sin, void* stream, int* dev_status) {
+                             const float* rope_sin, const int32_t* row_map, int n_rows, void* stream, int* dev_status) {
   const int E = H * D;
-  int rc = check_gemm("mintb_qkv_fwd", x, w, T * B, 3 * E, E, in_dtype);
+  const int M = row_map != nullptr ? n_rows : T * B;
+  int rc = check_gemm("mintb_qkv_fwd", x, w, M, 3 * E, E, in_dtype);
   if (rc != MINTB_OK) return rc;
   if (q == nullptr || k == nullptr || v == nullptr || (D != 16 && D != 32 && D != 64) || T <= 0 || B <= 0 || H <= 0 ||
       E % (D == 64 ? 64 : 32) != 0) {
@@ -464,8 +471,9 @@ extern "C" int mintb_qkv_fwd(const void* x, const void* w, const void* bias, voi
     return MINTB_EINVAL;
   }
   GemmParams p{};
-  p.M = T * B; p.N = 3 * E; p.K = E; p.in_dtype = in_dtype; p.out_dtype = MINTB_BF16; p.bias_dtype = bias_dtype;
+  p.M = M; p.N = 3 * E; p.K = E; p.in_dtype = in_dtype; p.out_dtype = MINTB_BF16; p.bias_dtype = bias_dtype;
   p.epilogue = kEpiHeadMajor;
+  p.row_map = row_map;
   p.alpha = alpha; p.out_scale = 1.f; p.bias = bias; p.out = nullptr;
   p.qkv[0] = static_cast<__nv_bfloat16*>(q); p.qkv[1] = static_cast<__nv_bfloat16*>(k); p.qkv[2] = static_cast<__nv_bfloat16*>(v);
   p.B = B; p.T = T; p.H = H; p.D = D; p.q_scale = q_scale; p.rope_cos = rope_cos; p.rope_sin = rope_sin;

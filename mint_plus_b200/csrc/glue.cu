@@ -365,10 +365,11 @@ template <int D>
 __global__ void __launch_bounds__(256) qkv_grad_pack_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
                                                             const __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ g,
                                                             float* __restrict__ db, const float* __restrict__ cos_tab,
-                                                            const float* __restrict__ sin_tab, int T, int B, int H, float q_scale) {
+                                                            const float* __restrict__ sin_tab, const int32_t* __restrict__ row_map,
+                                                            int M, int T, int B, int H, float q_scale) {
   __shared__ float part[kColLanes][32][8];
   constexpr int VPH = D / 8, hd = D / 2;             // vectors per head; rotation pairs dimension d with d + hd
-  const int E = H * D, N = 3 * E, M = T * B;
+  const int E = H * D, N = 3 * E;
   const int cl = threadIdx.x % 32, rl = threadIdx.x / 32;
   const int cg = blockIdx.x * 32 + cl;               // column group
   const bool live = cg * 8 < N;
@@ -385,7 +386,8 @@ __global__ void __launch_bounds__(256) qkv_grad_pack_kernel(const __nv_bfloat16*
   if (live) {
 #pragma unroll 4
     for (int m = m0 + rl; m < m1; m += kColLanes) {
-      const int t = m / B, b = m % B;
+      const int mo = row_map != nullptr ? row_map[m] : m;   // packed rows: output row m is token mo = t * B + b
+      const int t = mo / B, b = mo % B;
       const uint4* row = reinterpret_cast<const uint4*>(src + ((size_t(b) * H + h) * T + t) * D);
       float v[8];
       unpack8(__ldg(row + dv8), v);
@@ -543,7 +545,8 @@ int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, in
 }
 
 int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g, float* db, const float* rope_cos,
-                        const float* rope_sin, int T, int B, int H, int D, float q_scale, void* stream) {
+                        const float* rope_sin, const int32_t* row_map, int n_rows, int T, int B, int H, int D, float q_scale,
+                        void* stream) {
   if (dq == nullptr || dk == nullptr || dv == nullptr || g == nullptr || T <= 0 || B <= 0 || H <= 0 ||
       (rope_cos == nullptr) != (rope_sin == nullptr)) {
     set_error("mintb_qkv_grad_pack: null pointer or non-positive size");
@@ -554,7 +557,11 @@ int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g,
     return MINTB_EUNSUPPORTED;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int N = 3 * H * D, M = T * B;
+  const int N = 3 * H * D, M = row_map != nullptr ? n_rows : T * B;
+  if (M <= 0) {
+    set_error("mintb_qkv_grad_pack: no rows");
+    return MINTB_EINVAL;
+  }
   if (db != nullptr) {
     cudaError_t e = cudaMemsetAsync(db, 0, size_t(N) * sizeof(float), st);
     if (e != cudaSuccess) return fail("mintb_qkv_grad_pack memset", e);
@@ -564,9 +571,9 @@ int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g,
                       *v = static_cast<const __nv_bfloat16*>(dv);
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g);
   switch (D) {
-    case 16: qkv_grad_pack_kernel<16><<<grid, 256, 0, st>>>(q, k, v, o, db, rope_cos, rope_sin, T, B, H, q_scale); break;
-    case 32: qkv_grad_pack_kernel<32><<<grid, 256, 0, st>>>(q, k, v, o, db, rope_cos, rope_sin, T, B, H, q_scale); break;
-    default: qkv_grad_pack_kernel<64><<<grid, 256, 0, st>>>(q, k, v, o, db, rope_cos, rope_sin, T, B, H, q_scale); break;
+    case 16: qkv_grad_pack_kernel<16><<<grid, 256, 0, st>>>(q, k, v, o, db, rope_cos, rope_sin, row_map, M, T, B, H, q_scale); break;
+    case 32: qkv_grad_pack_kernel<32><<<grid, 256, 0, st>>>(q, k, v, o, db, rope_cos, rope_sin, row_map, M, T, B, H, q_scale); break;
+    default: qkv_grad_pack_kernel<64><<<grid, 256, 0, st>>>(q, k, v, o, db, rope_cos, rope_sin, row_map, M, T, B, H, q_scale); break;
   }
   count_launches(1);
   cudaError_t e = cudaGetLastError();

@@ -72,6 +72,10 @@ class MINT(nn.Module):
         # True / False, or "auto": checkpoint per layer (as the reference always does, esm2.py:124-132) only when the
         # activations of all layers would not fit in the free device memory — on a 180 GB part they usually do
         self.checkpoint_layers = "auto"
+        # Variable-length packing: padded positions are dropped from the token-wise work (projections, norms, FFN) and
+        # query tiles that hold only padding are left out of the attention.  Non-padded positions get the same values; padded
+        # positions of the outputs are zero instead of the values the reference computes there.  bfloat16 on the GPU only.
+        self.pack_padding = False
         self._init_submodules(layer_factory)
 
     def _init_submodules(self, layer_factory=None):
@@ -121,6 +125,20 @@ class MINT(nn.Module):
         if 0 in repr_layers:
             hidden_representations[0] = x
         x = x.transpose(0, 1).contiguous()                             # (B,T,E) -> (T,B,E), laid out sequence-first
+        pack = None
+        if self.pack_padding:
+            if self_attn_mask is not None or not (x.is_cuda and x.dtype == torch.bfloat16):
+                raise NotImplementedError("pack_padding needs bfloat16 CUDA activations and the fused two-pathway layers")
+            from .ops import PackInfo
+            pack = PackInfo(padding_mask)
+            T_, B_, E_ = x.shape
+            x = x.view(T_ * B_, E_).index_select(0, pack.rows64).unsqueeze(1)      # (N,1,E): the unpadded tokens
+
+        def unpack(t):                                                 # (N,1,E) -> (T,B,E), zeros at padded positions
+            if pack is None:
+                return t
+            full = t.new_zeros(pack.T * pack.B, t.shape[-1])
+            return full.index_copy(0, pack.rows64, t.squeeze(1)).view(pack.T, pack.B, t.shape[-1])
 
         use_ckpt = self.training and torch.is_grad_enabled() and self._want_checkpoint(x)
         self.last_forward_checkpointed = use_ckpt
@@ -128,15 +146,17 @@ class MINT(nn.Module):
             x.requires_grad_(True)
         layer_idx = -1
         for layer_idx, layer in enumerate(self.layers):
+            kw = dict(self_attn_padding_mask=padding_mask, self_attn_mask=self_attn_mask, chain_ids=chain_ids)
+            if pack is not None:
+                kw["pack"] = pack
             if use_ckpt:
-                x, _ = checkpoint(layer, x, self_attn_padding_mask=padding_mask, self_attn_mask=self_attn_mask,
-                                  chain_ids=chain_ids, use_reentrant=False)
+                x, _ = checkpoint(layer, x, use_reentrant=False, **kw)
             else:
-                x, _ = layer(x, self_attn_padding_mask=padding_mask, self_attn_mask=self_attn_mask, chain_ids=chain_ids)
+                x, _ = layer(x, **kw)
             if (layer_idx + 1) in repr_layers:
-                hidden_representations[layer_idx + 1] = x.transpose(0, 1)
+                hidden_representations[layer_idx + 1] = unpack(x).transpose(0, 1)
 
-        x = self.emb_layer_norm_after(x)
+        x = unpack(self.emb_layer_norm_after(x))
         x = x.transpose(0, 1)                                          # (T,B,E) -> (B,T,E)
         if (layer_idx + 1) in repr_layers:
             hidden_representations[layer_idx + 1] = x

@@ -75,9 +75,11 @@ class _TwoPathwayLayer(nn.Module):
     def _standard_attention(self, x, attn_mask, padding_mask):
         return self.self_attn(x=x, key_padding_mask=padding_mask, attn_mask=attn_mask)
 
-    def _multimer_attention_plus(self, x, chain_mask, padding_mask, chain_ids=None):
+    def _multimer_attention_plus(self, x, chain_mask, padding_mask, chain_ids=None, pack=None):
         if self._use_fused_multi_pathway:
-            return self._multimer_attention_superfused(x, chain_mask, padding_mask, chain_ids)
+            return self._multimer_attention_superfused(x, chain_mask, padding_mask, chain_ids, pack)
+        if pack is not None:
+            raise NotImplementedError("packed tokens need the fused attention (enable_fused_multi_pathway)")
         if self._use_sqrt_softmax:
             raise NotImplementedError("square-root softmax needs the fused attention (enable_fused_multi_pathway)")
         T, B, E = x.shape
@@ -91,9 +93,14 @@ class _TwoPathwayLayer(nn.Module):
         attn_out = attn_out.permute(2, 0, 1, 3).reshape(T, B, E)
         return sa.out_proj(attn_out), None
 
-    def _multimer_attention_superfused(self, x, chain_mask, padding_mask, chain_ids=None):
-        """x (T,B,E) -> (T,B,E): both QKV projections, fused two-pathway attention, output projection."""
-        T, B, E = x.shape
+    def _multimer_attention_superfused(self, x, chain_mask, padding_mask, chain_ids=None, pack=None):
+        """x (T,B,E) -> (T,B,E): both QKV projections, fused two-pathway attention, output projection.  With `pack`
+        (ops.PackInfo) x is (N,1,E), the N unpadded tokens only: the projections run on those rows, the attention on the
+        padded grid with fully padded query tiles left out, and its result is gathered back to the N rows."""
+        if pack is None:
+            T, B, E = x.shape
+        else:
+            (T, B), E = (pack.T, pack.B), x.shape[-1]
         sa, ma = self.self_attn, self.multimer_attn
         if chain_ids is not None and chain_mask is None:
             mask_kw = dict(meta=_cached_ids_meta(chain_ids, padding_mask))
@@ -108,10 +115,13 @@ class _TwoPathwayLayer(nn.Module):
             # bf16 activations on the GPU: the QKV GEMMs (bf16 or e4m3 operands) write q, k, v head-major and rotate the self
             # pathway in their epilogue, so the attention kernel gets ready-made operands (no permute copies, no rotation pass)
             tabs = ops.rope_tables(T, sa.head_dim, x.device, sa.rot_emb.inv_freq)[:2] if rope else None
-            q_s, k_s, v_s = ops.qkv_project(x, ops_s[0], ops_s[1], sa.num_heads, rope=tabs, fp8=ops_s[2])
-            q_c, k_c, v_c = ops.qkv_project(x, ops_c[0], ops_c[1], ma.num_heads, fp8=ops_c[2])
+            q_s, k_s, v_s = ops.qkv_project(x, ops_s[0], ops_s[1], sa.num_heads, rope=tabs, fp8=ops_s[2], pack=pack)
+            q_c, k_c, v_c = ops.qkv_project(x, ops_c[0], ops_c[1], ma.num_heads, fp8=ops_c[2], pack=pack)
             attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=False, scale=sa.scaling,
-                                              sqrt_softmax=sqrt_sm, out_seq_first=True, **mask_kw)
+                                              sqrt_softmax=sqrt_sm, out_seq_first=True, skip_pad_queries=pack is not None,
+                                              **mask_kw)
+        elif pack is not None:
+            raise NotImplementedError("packed tokens need bfloat16 CUDA activations and nn.Linear / Fp8Linear projections")
         else:
             q_s, k_s, v_s = sa.project_qkv_4d(x)
             q_c, k_c, v_c = ma.project_qkv_4d(x)
@@ -119,6 +129,8 @@ class _TwoPathwayLayer(nn.Module):
                                               inv_freq=sa.rot_emb.inv_freq if rope else None, scale=sa.scaling,
                                               sqrt_softmax=sqrt_sm, out_seq_first=True, **mask_kw)
         attn_out = attn_out.reshape(T, B, E)      # the kernels wrote (T,B,H,D): a view, no permute copy
+        if pack is not None:
+            attn_out = attn_out.view(T * B, E).index_select(0, pack.rows64).unsqueeze(1)
         if x.is_cuda and x.dtype == torch.bfloat16:
             return _linear(sa.out_proj, attn_out), None
         return sa.out_proj(attn_out), None
@@ -146,16 +158,18 @@ class _PreLnLayer(_TwoPathwayLayer):
         self.self_attn_layer_norm = norm()
         self.final_layer_norm = norm()
 
-    def forward(self, x, self_attn_mask=None, self_attn_padding_mask=None, chain_ids=None):
+    def forward(self, x, self_attn_mask=None, self_attn_padding_mask=None, chain_ids=None, pack=None):
         if x.is_cuda and x.dtype == torch.bfloat16 and isinstance(self.final_layer_norm, nn.LayerNorm):
             # bf16 on the GPU: each residual add is fused with the LayerNorm that follows it (one pass over the activations)
             _, h = ops.add_layernorm(x, None, 1.0, 0.0, self.self_attn_layer_norm, need_s=False)
             if self.use_multimer:
-                h, attn = self._multimer_attention_plus(h, self_attn_mask, self_attn_padding_mask, chain_ids)
+                h, attn = self._multimer_attention_plus(h, self_attn_mask, self_attn_padding_mask, chain_ids, pack)
             else:
                 h, attn = self._standard_attention(h, self_attn_mask, self_attn_padding_mask)
             x, h = ops.add_layernorm(x, h, 1.0, 1.0, self.final_layer_norm, need_s=True)
             return x + self.feed_forward(h), attn
+        if pack is not None:
+            raise NotImplementedError("packed tokens need bfloat16 CUDA activations")
         residual = x
         x = self.self_attn_layer_norm(x)
         if self.use_multimer:

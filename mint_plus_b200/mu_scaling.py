@@ -187,11 +187,13 @@ class TransformerLayer_MINT_mu(_TwoPathwayLayer):
         self.register_buffer("_tau", torch.tensor(tau, dtype=torch.float32))
         self._tau_f = float(tau)
 
-    def forward(self, x, self_attn_mask=None, self_attn_padding_mask=None, chain_ids=None):
+    def forward(self, x, self_attn_mask=None, self_attn_padding_mask=None, chain_ids=None, pack=None):
         tau = self._tau_f                       # host copy of the buffer: no device read-back per call
         keep, add = math.sqrt(1.0 - tau), math.sqrt(tau)
         if self.use_multimer:
-            attn_out, _ = self._multimer_attention_plus(x, self_attn_mask, self_attn_padding_mask, chain_ids)
+            attn_out, _ = self._multimer_attention_plus(x, self_attn_mask, self_attn_padding_mask, chain_ids, pack)
+        elif pack is not None:
+            raise NotImplementedError("packed tokens need the two-pathway attention")
         else:
             attn_out, _ = self._standard_attention(x, self_attn_mask, self_attn_padding_mask)
         if x.is_cuda and x.dtype == torch.bfloat16:

@@ -203,9 +203,11 @@ class _MultimerAttentionFn(torch.autograd.Function):
 def multimer_attention(q_self, k_self, v_self, q_cross, k_cross, v_cross, *, meta: Optional[MaskMeta] = None,
                        chain_ids=None, chain_mask=None, key_padding_mask=None, rope: bool = True,
                        inv_freq: Optional[torch.Tensor] = None, scale: Optional[float] = None,
-                       sqrt_softmax: bool = False, force_simt: bool = False, out_seq_first: bool = False) -> torch.Tensor:
+                       sqrt_softmax: bool = False, force_simt: bool = False, out_seq_first: bool = False,
+                       skip_pad_queries: bool = False) -> torch.Tensor:
     """Two-pathway combined-softmax attention on (B,H,T,D) projections; differentiable.  The result is (B,H,T,D), or
     (T,B,H,D) with out_seq_first=True (the layout of the layer's (T,B,E) activations: no permute copy before out_proj).
+    skip_pad_queries=True leaves out 128-row query tiles that hold only padded positions: their output rows stay unwritten.
 
 
     out = (P o ~M) V_self + (P o M) V_cross,  P = softmax_j where(M, s*Qc Kc^T, s*R(Qs) R(Ks)^T), padded keys -inf
@@ -231,7 +233,7 @@ def multimer_attention(q_self, k_self, v_self, q_cross, k_cross, v_cross, *, met
     if (meta.B, meta.T) != (B, T):
         raise ValueError(f"mask metadata is for (B, T) = ({meta.B}, {meta.T}), tensors have ({B}, {T})")
     flags = ((L.FLAG_ROPE if rope else 0) | (L.FLAG_SQRT_SOFTMAX if sqrt_softmax else 0) | (L.FLAG_FORCE_SIMT if force_simt else 0)
-             | (L.FLAG_OUT_SEQ_FIRST if out_seq_first else 0))
+             | (L.FLAG_OUT_SEQ_FIRST if out_seq_first else 0) | (L.FLAG_SKIP_PAD_QUERIES if skip_pad_queries else 0))
     cos = sin = None
     if rope:
         cos, sin, _ = rope_tables(T, D, q_self.device, inv_freq)
@@ -413,6 +415,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, gelu: bool = False)
     return y.view(*x.shape[:-1], weight.shape[0])
 
 
+# ----------------------------------------------------------------------------------------------- variable-length packing
+class PackInfo:
+    """Which rows of the (T*B) token grid hold a token: `rows64` / `rows32` list them (row = t * B + b) in increasing order.
+    Token-wise work (projections, norms, FFN) then runs on those rows only; the attention keeps the padded (B,H,T,D) grid."""
+
+    def __init__(self, padding_mask: torch.Tensor):
+        B, T = padding_mask.shape
+        keep = ~padding_mask.t().reshape(-1)               # (T, B) order, like the layer's activations
+        self.rows64 = torch.nonzero(keep, as_tuple=False).squeeze(1)
+        self.rows32 = self.rows64.to(torch.int32)
+        self.T, self.B, self.n = T, B, int(self.rows64.numel())
+
+
 # ----------------------------------------------------------------------------------------------- residual + LayerNorm
 class _AddLayerNormFn(torch.autograd.Function):
     """(s, y) with s = a x + b r and y = LayerNorm(s) gamma + beta, in one pass over x and r; `need_s` False drops s,
@@ -486,22 +501,32 @@ class _QkvFn(torch.autograd.Function):
     """Fused QKV projection of one pathway with head-major outputs (and RoPE on q, k when tables are given)."""
 
     @staticmethod
-    def forward(ctx, x, w, bias, H, cos, sin, q_scale, wq=None, w_scale=1.0, x_scale=1.0, out_scale=1.0):
-        T, B, E = x.shape
+    def forward(ctx, x, w, bias, H, cos, sin, q_scale, wq=None, w_scale=1.0, x_scale=1.0, out_scale=1.0, pack=None):
+        if pack is None:
+            T, B, E = x.shape
+            x2d = x.reshape(T * B, E).contiguous()
+        else:                       # x holds the unpadded tokens only; pack.rows names the (t, b) position of each
+            (T, B), E = (pack.T, pack.B), x.shape[-1]
+            x2d = x.reshape(-1, E).contiguous()
         D = E // H
         b, bdt = _bias_arg(bias)
-        x2d = x.reshape(T * B, E).contiguous()
         if wq is None:      # bf16 operands
             a_op, b_op, in_dt, alpha = x2d, (w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)).contiguous(), L.BF16, 1.0
         else:               # e4m3 operands, one scale per tensor; the product of the scales is folded into alpha
             a_op, b_op, in_dt, alpha = quantize_e4m3(x2d, x_scale), wq, L.E4M3, float(x_scale) * float(w_scale) * float(out_scale)
-        q, k, v = (torch.empty(B, H, T, D, dtype=torch.bfloat16, device=x.device) for _ in range(3))
+        # packed: positions without a token are never written, and keys there are masked but still multiplied by a zero
+        # probability, so they must hold finite numbers
+        alloc = torch.zeros if pack is not None else torch.empty
+        q, k, v = (alloc(B, H, T, D, dtype=torch.bfloat16, device=x.device) for _ in range(3))
         with torch.cuda.device(x.device):
             rc = L.lib().mintb_qkv_fwd(_ptr(a_op), _ptr(b_op), _ptr(b), _ptr(q), _ptr(k), _ptr(v), T, B, H, D, in_dt, bdt,
-                                       float(alpha), float(q_scale), _ptr(cos), _ptr(sin), _stream(),
+                                       float(alpha), float(q_scale), _ptr(cos), _ptr(sin),
+                                       _ptr(pack.rows32) if pack is not None else None, x2d.shape[0], _stream(),
                                        _ptr(_dev_status(x.device)))
         L.check(rc, "mintb_qkv_fwd")
         ctx.save_for_backward(x2d, w, bias, cos, sin)
+        ctx.pack = pack
+        ctx.x_shape = tuple(x.shape)
         ctx.dims = (T, B, H, D, q_scale, float(out_scale))
         return q, k, v
 
@@ -511,25 +536,28 @@ class _QkvFn(torch.autograd.Function):
         T, B, H, D, q_scale, out_scale = ctx.dims
         E = H * D
         # (B,H,T,D) x3 -> [T*B, 3E] with the rotation undone and the q scale applied, in one pass
-        g = torch.empty(T * B, 3 * E, dtype=torch.bfloat16, device=x2d.device)
+        pack = ctx.pack
+        n_rows = x2d.shape[0]
+        g = torch.empty(n_rows, 3 * E, dtype=torch.bfloat16, device=x2d.device)
         want_db = bias is not None and ctx.needs_input_grad[2]
         db = torch.empty(3 * E, dtype=torch.float32, device=x2d.device) if want_db else None
         with torch.cuda.device(x2d.device):
             rc = L.lib().mintb_qkv_grad_pack(_ptr(dq.contiguous()), _ptr(dk.contiguous()), _ptr(dv.contiguous()), _ptr(g), _ptr(db),
-                                             _ptr(cos), _ptr(sin), T, B, H, D, float(q_scale), _stream())
+                                             _ptr(cos), _ptr(sin), _ptr(pack.rows32) if pack is not None else None, n_rows,
+                                             T, B, H, D, float(q_scale), _stream())
         L.check(rc, "mintb_qkv_grad_pack")
         dx, dw, db = linear_backward(g, x2d, w, bias, None, ctx.needs_input_grad, out_scale, db=db)
-        return (dx.view(T, B, E) if dx is not None else None), dw, db, None, None, None, None, None, None, None, None
+        return (dx.view(ctx.x_shape) if dx is not None else None), dw, db, None, None, None, None, None, None, None, None, None
 
 
 def qkv_project(x: torch.Tensor, weight: torch.Tensor, bias, num_heads: int, rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-                q_scale: float = 1.0, fp8: Optional[Tuple[torch.Tensor, float, float, float]] = None):
+                q_scale: float = 1.0, fp8: Optional[Tuple[torch.Tensor, float, float, float]] = None, pack=None):
     """x (T,B,E) bf16, weight (3E,E) with rows [Q;K;V] -> q, k, v (B,H,T,D) bf16, written head-major by the GEMM epilogue
     (attention.py:97-117, 304-323 of the reference without the three permute copies).  `rope` = (cos, sin) tables rotates q, k.
     `fp8` = (e4m3 weight, weight scale, activation scale, static output multiplier) runs the product on e4m3 operands; `weight` stays the master copy
     that receives the gradient."""
-    if x.dtype != torch.bfloat16 or x.dim() != 3:
-        raise TypeError("qkv_project takes a (T, B, E) bfloat16 tensor")
+    if x.dtype != torch.bfloat16 or (pack is None and x.dim() != 3):
+        raise TypeError("qkv_project takes a (T, B, E) bfloat16 tensor (or the packed rows of one, with `pack`)")
     cos, sin = rope if rope is not None else (None, None)
     wq, w_scale, x_scale, out_scale = fp8 if fp8 is not None else (None, 1.0, 1.0, 1.0)
-    return _QkvFn.apply(x, weight, bias, num_heads, cos, sin, q_scale, wq, w_scale, x_scale, out_scale)
+    return _QkvFn.apply(x, weight, bias, num_heads, cos, sin, q_scale, wq, w_scale, x_scale, out_scale, pack)

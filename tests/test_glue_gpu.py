@@ -105,8 +105,8 @@ def test_qkv_gradient_pack(D, rope):
     from mint_plus_b200 import _lib as L
     db = torch.empty(3 * E, dtype=torch.float32, device=DEV)
     rc = L.lib().mintb_qkv_grad_pack(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), g.data_ptr(), db.data_ptr(),
-                                     cos.data_ptr() if rope else None, sin.data_ptr() if rope else None, T, B, H, D, q_scale,
-                                     torch.cuda.current_stream().cuda_stream)
+                                     cos.data_ptr() if rope else None, sin.data_ptr() if rope else None, None, 0, T, B, H, D,
+                                     q_scale, torch.cuda.current_stream().cuda_stream)
     L.check(rc, "mintb_qkv_grad_pack")
     torch.cuda.synchronize()
     a, b = dq.float(), dk.float()
@@ -116,3 +116,13 @@ def test_qkv_gradient_pack(D, rope):
     want = torch.cat([t.permute(2, 0, 1, 3).reshape(T * B, E) for t in (a, b, dv.float())], dim=1)
     torch.testing.assert_close(g.float(), want, rtol=1e-2, atol=1e-2)
     torch.testing.assert_close(db, g.float().sum(0), rtol=1e-3, atol=1e-3)
+    # packed rows: only the listed (t, b) positions, in the listed order
+    rows = torch.tensor([5, 0, 7, 44, T * B - 1, 17, 18, 19, 60], dtype=torch.int32, device=DEV)
+    gp = torch.empty(rows.numel(), 3 * E, dtype=torch.bfloat16, device=DEV)
+    rc = L.lib().mintb_qkv_grad_pack(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), gp.data_ptr(), db.data_ptr(),
+                                     cos.data_ptr() if rope else None, sin.data_ptr() if rope else None, rows.data_ptr(),
+                                     rows.numel(), T, B, H, D, q_scale, torch.cuda.current_stream().cuda_stream)
+    L.check(rc, "mintb_qkv_grad_pack")
+    torch.cuda.synchronize()
+    assert torch.equal(gp, g[rows.long()])
+    torch.testing.assert_close(db, gp.float().sum(0), rtol=1e-3, atol=1e-3)

@@ -157,3 +157,40 @@ def test_shared_step_masks_only_residues_and_gives_a_finite_loss(oracle_attentio
     loss, ppl = M.shared_step(model, (tokens, chain_ids), generator=torch.Generator().manual_seed(6))
     loss.backward()
     assert torch.isfinite(loss) and torch.isfinite(ppl) and abs(float(ppl) - float(torch.exp(loss))) < 1e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["base", "mu_fp8"])
+def test_packed_tokens_give_the_same_values_at_unpadded_positions(kind):
+    """pack_padding drops padded positions from the token-wise work and padded query tiles from the attention: logits
+    at real positions and all parameter gradients must agree with the unpacked run (same kernels, same row arithmetic)."""
+    torch.manual_seed(0)
+    if kind == "base":
+        model = M.MINT(num_layers=2, embed_dim=128, attention_heads=4, use_multimer=True)
+    else:
+        model = M.build_mint_mu("8M", num_layers=2, embed_dim=128, attention_heads=4, use_fp8=True, use_sqrt_softmax=True)
+    fill_state_dict_(model, 3)
+    model = model.cuda().to(torch.bfloat16).train()
+    model.token_dropout = False
+    for layer in model.layers:
+        layer.self_attn.rot_emb.inv_freq = layer.self_attn.rot_emb.inv_freq.float()
+    tokens, chain_ids = c1_batch(31, 3, 384, 20, 60)          # 384 positions, at most 124 real: whole query tiles are padding
+    tokens, chain_ids = tokens.cuda(), chain_ids.cuda()
+    valid = tokens != 1
+
+    def run(pack):
+        model.pack_padding = pack
+        model.zero_grad()
+        logits = model(tokens, chain_ids)["logits"].float()
+        (logits[valid].square().mean()).backward()
+        ops.check_device_status()
+        return logits.detach(), {n: p.grad.detach().float().clone() for n, p in model.named_parameters() if p.grad is not None}
+
+    want, wgrads = run(False)
+    got, ggrads = run(True)
+    assert torch.equal(got[valid], want[valid])                # identical arithmetic row by row
+    assert (got[~valid] == model.lm_head(torch.zeros(1, 128, device="cuda", dtype=torch.bfloat16)).float()).all()
+    assert ggrads.keys() == wgrads.keys()
+    for n in wgrads:
+        scale = wgrads[n].abs().max().item()
+        assert (ggrads[n] - wgrads[n]).abs().max().item() <= 2e-2 * scale + 1e-6, n
