@@ -164,7 +164,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="attn",
                     help="attn (default: the isolated attention op) or a whole-model workload of bench_model.py: "
-                         "mint650m_fp8, mint150m_lora, mint3b_infer, mint8m_fwd")
+                         "mint650m_fp8, mint150m_lora, mint3b_infer, mint8m_fwd, mint650m_fp8_packed, mint3b_infer_packed")
     ap.add_argument("--no-model-metric", action="store_true",
                     help="attn workload: skip the MINT-650M FP8 pairs/s measurement that is added to the line as `model_650m`")
     ap.add_argument("--layers", type=int, default=0,

@@ -29,6 +29,14 @@ WORKLOADS = {
     "mint3b_infer": dict(layers=36, embed=2560, heads=40, pairs=64, T=2048, lo=30, hi=80, lo2=800, hi2=1900, seed=5005,
                          train=False, kind="plus", dtype="bf16",
                          desc="MINT 36x2560 (40 heads) inference forward, bf16, 64 pairs with skewed chain lengths padded to 2048"),
+    # the same two with padded positions dropped from the token-wise work and from the attention's query tiles
+    # (MINT.pack_padding): same values at real positions, zeros at padded ones; FLOPs are counted on real tokens only
+    "mint650m_fp8_packed": dict(layers=33, embed=1280, heads=20, pairs=16, T=2048, lo=100, hi=900, seed=4004, train=True,
+                                kind="mu_fp8", dtype="e4m3 GEMMs / bf16 attention", pack=True,
+                                desc="MINT-650M muS FP8 fwd+bwd, 16 pairs padded to 2048, padding dropped (variable-length packing)"),
+    "mint3b_infer_packed": dict(layers=36, embed=2560, heads=40, pairs=64, T=2048, lo=30, hi=80, lo2=800, hi2=1900, seed=5005,
+                                train=False, kind="plus", dtype="bf16", pack=True,
+                                desc="MINT 36x2560 inference forward, 64 skewed pairs padded to 2048, padding dropped (variable-length packing)"),
     # the reference's CPU-runnable 8M forward configuration (a latency line; its parity is a test)
     "mint8m_fwd": dict(layers=6, embed=320, heads=20, pairs=4, T=512, lo=64, hi=200, seed=1001, train=False,
                        kind="base_fp32", dtype="f32",
@@ -82,6 +90,7 @@ def build_model(cfg, device):
                 if n.endswith("lora_B"):
                     p.normal_(0.0, 0.02)
     model.train(cfg["train"])
+    model.pack_padding = bool(cfg.get("pack", False))
     return model
 
 
@@ -93,8 +102,12 @@ def algorithmic_flops(cfg, tokens):
     D = E_ // H_
     B, T = tokens.shape
     tk = (tokens != 1).sum(1).double()
-    gemm_fwd = 30.0 * E_ * E_ * B * T * L_
-    attn_fwd = float((4.0 * H_ * T * tk * D).sum()) * L_
+    if cfg.get("pack"):       # padding dropped: only real tokens go through the projections, only real queries through attention
+        gemm_fwd = 30.0 * E_ * E_ * float(tk.sum()) * L_
+        attn_fwd = float((4.0 * H_ * tk * tk * D).sum()) * L_
+    else:
+        gemm_fwd = 30.0 * E_ * E_ * B * T * L_
+        attn_fwd = float((4.0 * H_ * T * tk * D).sum()) * L_
     if not cfg["train"]:
         return gemm_fwd + attn_fwd, gemm_fwd, attn_fwd
     gemm = gemm_fwd * (2.0 if cfg["kind"] == "lora" else 3.0)

@@ -102,3 +102,20 @@ def test_cpu_tensors_are_refused():
         M.multimer_attention(t, t, t, t, t, t, chain_ids=torch.zeros(1, 8, dtype=torch.int32))
     with pytest.raises(NotImplementedError):
         M.fused_multi_pathway_attention(t, t, t, t, t, t, torch.zeros(1, 8, 8, dtype=torch.bool), dropout_p=0.1)
+
+
+def test_pack_info_lists_unpadded_rows_in_sequence_first_order():
+    from mint_plus_b200.ops import PackInfo
+    pad = torch.tensor([[False, False, True, True], [False, True, True, True], [False, False, False, True]])   # (B=3, T=4)
+    pk = PackInfo(pad)
+    # row = t * B + b over the (T, B) grid of the layer's activations
+    assert pk.rows64.tolist() == [0, 1, 2, 3, 5, 8] and pk.rows32.dtype == torch.int32
+    assert (pk.T, pk.B, pk.n) == (4, 3, 6)
+
+
+def test_pack_padding_refuses_cpu_tensors():
+    model = M.MINT(num_layers=1, embed_dim=32, attention_heads=2, use_multimer=True).eval()
+    model.pack_padding = True
+    tokens = torch.tensor([[0, 5, 6, 2, 1, 1]])
+    with pytest.raises(NotImplementedError):
+        model(tokens, torch.zeros_like(tokens))
