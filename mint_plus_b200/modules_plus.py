@@ -23,6 +23,9 @@ def _linear(mod, x, gelu=False):
     from .mu_scaling import Fp8Linear
     if isinstance(mod, Fp8Linear):
         return mod(x, gelu=gelu)
+    if type(mod) is not nn.Linear:          # a wrapped projection (e.g. LoRA adapters): its own forward decides
+        y = mod(x)
+        return gelu_erf(y) if gelu else y
     return ops.linear(x, mod.weight, mod.bias, gelu=gelu)
 
 
@@ -47,11 +50,19 @@ class VanillaFeedForward(nn.Module):
 
 
 def _qkv_operands(attn):
-    """(weight [3E,E], bias, fp8 triple or None) of one pathway's Q/K/V projections, whether the module holds one fused
-    Linear or three separate ones (rows ordered [Q;K;V] either way), or None when the modules are of mixed kinds."""
+    """(weight [3E,E], bias, fp8 tuple or None, lora tuple or None) of one pathway's Q/K/V projections, whether the module
+    holds one fused Linear or three separate ones (rows ordered [Q;K;V] either way), or None when the modules are of mixed kinds."""
+    from .lora import LoRALinear
     from .mu_scaling import Fp8Linear, fused_fp8_weight
     fused = getattr(attn, "fused_qkv", None)
     mods = [fused] if fused is not None else [attn.q_proj, attn.k_proj, attn.v_proj]
+    if len(mods) == 3 and all(isinstance(m, LoRALinear) and type(m.base) is nn.Linear and not isinstance(m.dropout, nn.Dropout)
+                              for m in mods) and len({(m.r, m.scaling) for m in mods}) == 1:
+        # frozen base + LoRA adapters on q, k, v: one fused product on the merged weight
+        w = torch.cat([m.base.weight for m in mods], dim=0)
+        b = torch.cat([m.base.bias for m in mods], dim=0) if mods[0].base.bias is not None else None
+        lora = (torch.stack([m.lora_A for m in mods]), torch.stack([m.lora_B for m in mods]), mods[0].scaling)
+        return w, b, None, lora
     if all(isinstance(m, Fp8Linear) for m in mods):
         kind = "fp8"
     elif all(type(m) is nn.Linear for m in mods):
@@ -63,7 +74,7 @@ def _qkv_operands(attn):
     else:
         w = torch.cat([m.weight for m in mods], dim=0)
         b = torch.cat([m.bias for m in mods], dim=0) if mods[0].bias is not None else None
-    return w, b, (fused_fp8_weight(attn, mods) if kind == "fp8" else None)
+    return w, b, (fused_fp8_weight(attn, mods) if kind == "fp8" else None), None
 
 
 class _TwoPathwayLayer(nn.Module):
@@ -115,8 +126,8 @@ class _TwoPathwayLayer(nn.Module):
             # bf16 activations on the GPU: the QKV GEMMs (bf16 or e4m3 operands) write q, k, v head-major and rotate the self
             # pathway in their epilogue, so the attention kernel gets ready-made operands (no permute copies, no rotation pass)
             tabs = ops.rope_tables(T, sa.head_dim, x.device, sa.rot_emb.inv_freq)[:2] if rope else None
-            q_s, k_s, v_s = ops.qkv_project(x, ops_s[0], ops_s[1], sa.num_heads, rope=tabs, fp8=ops_s[2], pack=pack)
-            q_c, k_c, v_c = ops.qkv_project(x, ops_c[0], ops_c[1], ma.num_heads, fp8=ops_c[2], pack=pack)
+            q_s, k_s, v_s = ops.qkv_project(x, ops_s[0], ops_s[1], sa.num_heads, rope=tabs, fp8=ops_s[2], pack=pack, lora=ops_s[3])
+            q_c, k_c, v_c = ops.qkv_project(x, ops_c[0], ops_c[1], ma.num_heads, fp8=ops_c[2], pack=pack, lora=ops_c[3])
             attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=False, scale=sa.scaling,
                                               sqrt_softmax=sqrt_sm, out_seq_first=True, skip_pad_queries=pack is not None,
                                               **mask_kw)

@@ -497,11 +497,21 @@ def _rope_rotate_torch(t, cos, sin, inverse=False):
     return torch.cat((lo * cos - hi * s, hi * cos + lo * s), dim=-1).to(t.dtype)
 
 
+def _lora_merged(w, lora_a, lora_b, scaling):
+    """W + s [B_q A_q; B_k A_k; B_v A_v] for a [3E, E] weight with adapters A (3, r, E), B (3, E, r); W itself without."""
+    if lora_a is None:
+        return w
+    with torch.no_grad():
+        delta = torch.bmm(lora_b.to(w.dtype), lora_a.to(w.dtype)).reshape(w.shape)
+        return w + scaling * delta
+
+
 class _QkvFn(torch.autograd.Function):
     """Fused QKV projection of one pathway with head-major outputs (and RoPE on q, k when tables are given)."""
 
     @staticmethod
-    def forward(ctx, x, w, bias, H, cos, sin, q_scale, wq=None, w_scale=1.0, x_scale=1.0, out_scale=1.0, pack=None):
+    def forward(ctx, x, w, bias, H, cos, sin, q_scale, wq=None, w_scale=1.0, x_scale=1.0, out_scale=1.0, pack=None,
+                lora_a=None, lora_b=None, lora_scaling=1.0):
         if pack is None:
             T, B, E = x.shape
             x2d = x.reshape(T * B, E).contiguous()
@@ -511,7 +521,8 @@ class _QkvFn(torch.autograd.Function):
         D = E // H
         b, bdt = _bias_arg(bias)
         if wq is None:      # bf16 operands
-            a_op, b_op, in_dt, alpha = x2d, (w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)).contiguous(), L.BF16, 1.0
+            w_used = _lora_merged(w, lora_a, lora_b, lora_scaling)
+            a_op, b_op, in_dt, alpha = x2d, (w_used if w_used.dtype == torch.bfloat16 else w_used.to(torch.bfloat16)).contiguous(), L.BF16, 1.0
         else:               # e4m3 operands, one scale per tensor; the product of the scales is folded into alpha
             a_op, b_op, in_dt, alpha = quantize_e4m3(x2d, x_scale), wq, L.E4M3, float(x_scale) * float(w_scale) * float(out_scale)
         # packed: positions without a token are never written, and keys there are masked but still multiplied by a zero
@@ -524,7 +535,8 @@ class _QkvFn(torch.autograd.Function):
                                        _ptr(pack.rows32) if pack is not None else None, x2d.shape[0], _stream(),
                                        _ptr(_dev_status(x.device)))
         L.check(rc, "mintb_qkv_fwd")
-        ctx.save_for_backward(x2d, w, bias, cos, sin)
+        ctx.save_for_backward(x2d, w, bias, cos, sin, lora_a, lora_b)
+        ctx.lora_scaling = float(lora_scaling)
         ctx.pack = pack
         ctx.x_shape = tuple(x.shape)
         ctx.dims = (T, B, H, D, q_scale, float(out_scale))
@@ -532,7 +544,7 @@ class _QkvFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dq, dk, dv):
-        x2d, w, bias, cos, sin = ctx.saved_tensors
+        x2d, w, bias, cos, sin, lora_a, lora_b = ctx.saved_tensors
         T, B, H, D, q_scale, out_scale = ctx.dims
         E = H * D
         # (B,H,T,D) x3 -> [T*B, 3E] with the rotation undone and the q scale applied, in one pass
@@ -546,18 +558,35 @@ class _QkvFn(torch.autograd.Function):
                                              _ptr(cos), _ptr(sin), _ptr(pack.rows32) if pack is not None else None, n_rows,
                                              T, B, H, D, float(q_scale), _stream())
         L.check(rc, "mintb_qkv_grad_pack")
-        dx, dw, db = linear_backward(g, x2d, w, bias, None, ctx.needs_input_grad, out_scale, db=db)
-        return (dx.view(ctx.x_shape) if dx is not None else None), dw, db, None, None, None, None, None, None, None, None, None
+        w_used = _lora_merged(w, lora_a, lora_b, ctx.lora_scaling)
+        dx, dw, db = linear_backward(g, x2d, w_used, bias, None, ctx.needs_input_grad, out_scale, db=db)
+        d_a = d_b = None
+        if lora_a is not None and (ctx.needs_input_grad[12] or ctx.needs_input_grad[13]):
+            # the adapters' gradients through thin products only (no E x E weight gradient): for each of q, k, v
+            # dB = s g^T (x A^T), dA = s (g B)^T x
+            s_ = ctx.lora_scaling
+            g3 = g.view(-1, 3, E)
+            d_a, d_b = torch.empty_like(lora_a), torch.empty_like(lora_b)
+            for i in range(3):
+                gi = g3[:, i]
+                d_b[i] = ((gi.t() @ (x2d @ lora_a[i].to(x2d.dtype).t())) * s_).to(lora_b.dtype)
+                d_a[i] = (((gi @ lora_b[i].to(x2d.dtype)).t() @ x2d) * s_).to(lora_a.dtype)
+        return ((dx.view(ctx.x_shape) if dx is not None else None), dw, db, None, None, None, None, None, None, None, None, None,
+                d_a, d_b, None)
 
 
 def qkv_project(x: torch.Tensor, weight: torch.Tensor, bias, num_heads: int, rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-                q_scale: float = 1.0, fp8: Optional[Tuple[torch.Tensor, float, float, float]] = None, pack=None):
+                q_scale: float = 1.0, fp8: Optional[Tuple[torch.Tensor, float, float, float]] = None, pack=None,
+                lora: Optional[Tuple[torch.Tensor, torch.Tensor, float]] = None):
     """x (T,B,E) bf16, weight (3E,E) with rows [Q;K;V] -> q, k, v (B,H,T,D) bf16, written head-major by the GEMM epilogue
     (attention.py:97-117, 304-323 of the reference without the three permute copies).  `rope` = (cos, sin) tables rotates q, k.
+    `lora` = (A (3,r,E), B (3,E,r), alpha / r) adds frozen-base LoRA adapters of q, k, v: the product runs on the merged
+    weight, the adapters get their gradients through thin products.
     `fp8` = (e4m3 weight, weight scale, activation scale, static output multiplier) runs the product on e4m3 operands; `weight` stays the master copy
     that receives the gradient."""
     if x.dtype != torch.bfloat16 or (pack is None and x.dim() != 3):
         raise TypeError("qkv_project takes a (T, B, E) bfloat16 tensor (or the packed rows of one, with `pack`)")
     cos, sin = rope if rope is not None else (None, None)
     wq, w_scale, x_scale, out_scale = fp8 if fp8 is not None else (None, 1.0, 1.0, 1.0)
-    return _QkvFn.apply(x, weight, bias, num_heads, cos, sin, q_scale, wq, w_scale, x_scale, out_scale, pack)
+    la, lb, ls = lora if lora is not None else (None, None, 1.0)
+    return _QkvFn.apply(x, weight, bias, num_heads, cos, sin, q_scale, wq, w_scale, x_scale, out_scale, pack, la, lb, ls)

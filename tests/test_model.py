@@ -156,7 +156,7 @@ def test_shared_step_masks_only_residues_and_gives_a_finite_loss(oracle_attentio
     assert ((inp[target] == model.mask_idx) | ~changed | ((inp[target] >= 4) & (inp[target] < 24))).all()
     loss, ppl = M.shared_step(model, (tokens, chain_ids), generator=torch.Generator().manual_seed(6))
     loss.backward()
-    assert torch.isfinite(loss) and torch.isfinite(ppl) and abs(float(ppl) - float(torch.exp(loss))) < 1e-4
+    assert torch.isfinite(loss.detach()) and torch.isfinite(ppl) and abs(float(ppl) - float(torch.exp(loss.detach()))) < 1e-4
 
 
 @pytest.mark.gpu
@@ -194,3 +194,41 @@ def test_packed_tokens_give_the_same_values_at_unpadded_positions(kind):
     for n in wgrads:
         scale = wgrads[n].abs().max().item()
         assert (ggrads[n] - wgrads[n]).abs().max().item() <= 2e-2 * scale + 1e-6, n
+
+
+@pytest.mark.gpu
+def test_lora_adapters_on_the_fused_projection_match_the_module_by_module_path(monkeypatch):
+    """Frozen base + LoRA on q/k/v/out: the fused QKV product on the merged weight (adapter gradients through thin
+    products) against the plain LoRALinear modules called one by one."""
+    from mint_plus_b200.lora import apply_lora
+    torch.manual_seed(0)
+    model = fill_state_dict_(M.MINT(num_layers=2, embed_dim=128, attention_heads=4, use_multimer=True), 9)
+    model = model.cuda().to(torch.bfloat16)
+    for layer in model.layers:
+        layer.self_attn.rot_emb.inv_freq = layer.self_attn.rot_emb.inv_freq.float()
+    apply_lora(model, r=8, alpha=16.0)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if n.endswith("lora_B"):
+                p.normal_(0.0, 0.05)
+    model.train()
+    model.token_dropout = False
+    tokens, chain_ids = c1_batch(41, 2, 160, 20, 60)
+    tokens, chain_ids = tokens.cuda(), chain_ids.cuda()
+
+    def run():
+        model.zero_grad()
+        logits = model(tokens, chain_ids)["logits"].float()
+        logits.square().mean().backward()
+        ops.check_device_status()
+        return logits.detach(), {n: p.grad.float().clone() for n, p in model.named_parameters() if p.requires_grad}
+
+    fast, fgrads = run()
+    monkeypatch.setattr(modules_plus, "_qkv_operands", lambda attn: None)       # module-by-module projections
+    slow, sgrads = run()
+    # the merged weight is rounded to bf16 once, the module path rounds base and adapter outputs separately
+    assert (fast - slow).abs().max().item() < 0.15 and (fast - slow).abs().mean().item() < 0.03
+    assert fgrads.keys() == sgrads.keys() and len(fgrads) == 2 * 2 * 7
+    for n in sgrads:
+        scale = sgrads[n].abs().max().item()
+        assert (fgrads[n] - sgrads[n]).abs().max().item() <= 0.08 * scale + 1e-5, n
