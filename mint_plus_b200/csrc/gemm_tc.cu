@@ -21,7 +21,8 @@ constexpr int kGM = 128, kGN = 256, kGStages = 4;
 constexpr int kGEpiWarps = 8, kGEpiThreads = 32 * kGEpiWarps, kGThreads = 64 + kGEpiThreads;   // TMA warp, MMA warp, epilogue warps
 constexpr int kSlabBytes = 128;                       // bytes of K per stage and row (64 bf16 or 128 e4m3)
 constexpr int kABytes = kGM * kSlabBytes, kBBytes = kGN * kSlabBytes, kGStageBytes = kABytes + kBBytes;
-constexpr size_t kGemmSmem = 1024 + size_t(kGStages) * kGStageBytes + 256 + 2 * kGN * sizeof(float);
+constexpr int kGStageOutBytes = 32 * 64;   // one epilogue warp's staging of 32 rows x 32 bf16 columns for a bulk store
+constexpr size_t kGemmSmem = 1024 + size_t(kGStages) * kGStageBytes + kGEpiWarps * kGStageOutBytes + 256 + 2 * kGN * sizeof(float);
 
 enum GemmEpilogue : int { kEpiBias = 0, kEpiBiasGelu = 1, kEpiHeadMajor = 2 };
 
@@ -42,6 +43,7 @@ struct GemmParams {
   float q_scale;               // multiplies the q third (1 to leave the scaling to the attention kernel)
   const float *rope_cos, *rope_sin;   // [T][D/2]; rotate the q and k thirds when non-null
   const int32_t* row_map;             // packed input rows: row m of x is token row_map[m] = t * B + b (null: m itself)
+  int use_bulk_store;          // bf16 row-major outputs leave through shared memory and bulk tensor stores
   int* status;
 };
 
@@ -75,10 +77,12 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // EPI: epilogue kind; HD: head_dim of the head-major epilogue (0 otherwise)
 template <int EPI, int HD>
 __global__ void __launch_bounds__(kGThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_pre, GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* tail = smem + size_t(kGStages) * kGStageBytes;
+  unsigned char* s_out = smem + size_t(kGStages) * kGStageBytes;   // [epilogue warp][32 rows][64 B], 64B swizzle
+  unsigned char* tail = s_out + kGEpiWarps * kGStageOutBytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(tail);   // [kGStages]
   uint64_t* empty = full + kGStages;                     // [kGStages]
   uint64_t* acc_full = empty + kGStages;                 // [2]
@@ -160,6 +164,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int chalf = (warp - 2) / 4;
     const int row = quarter * 32 + lane;
     const int et = (warp - 2) * 32 + lane;   // thread index among the epilogue threads
+    unsigned char* my_out = s_out + size_t(warp - 2) * kGStageOutBytes;
+    // 32 columns of this warp's 32 rows as bf16 -> shared memory (row = lane) -> one bulk tensor store: whole 64-byte row
+    // pieces reach L2 instead of one 16-byte piece per lane and instruction; rows / columns past the matrix are dropped.
+    auto bulk_store32 = [&](const CUtensorMap* map, const float (&val)[32], int n, int row0) {
+      if (lane == 0) bulk_wait_read_all();   // the previous store of this warp has read the staging rows
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 32; j += 8)
+        *reinterpret_cast<uint4*>(my_out + swizzled_offset(lane, j / 8, 64)) =
+            make_uint4(pack_bf16x2(val[j], val[j + 1]), pack_bf16x2(val[j + 2], val[j + 3]), pack_bf16x2(val[j + 4], val[j + 5]),
+                       pack_bf16x2(val[j + 6], val[j + 7]));
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(map, my_out, n, row0);
+        bulk_commit_group();
+      }
+    };
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     uint32_t ab = 0, ab_phase = 0;
     bool ok = true;
@@ -263,7 +285,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         } else {
           const int n = n0 + c0;
           if constexpr (EPI == kEpiBiasGelu) {
-            if (p.preact != nullptr && m < p.M) {   // the backward pass reads the pre-activation instead of recomputing it
+            if (p.preact != nullptr && p.use_bulk_store) {
+              bulk_store32(&map_pre, v, n, m0 + quarter * 32);
+            } else if (p.preact != nullptr && m < p.M) {   // the backward pass reads the pre-activation instead of recomputing it
               __nv_bfloat16* dst = p.preact + size_t(m) * p.N + n;
               if (n + 32 <= p.N) {
 #pragma unroll
@@ -279,7 +303,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = gelu_erf_f(v[j]);
           }
-          if (m < p.M) {
+          if (p.use_bulk_store && p.out_dtype == MINTB_BF16) {
+            bulk_store32(&map_out, v, n, m0 + quarter * 32);
+          } else if (m < p.M) {
             if (p.out_dtype == MINTB_BF16) {
               __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + size_t(m) * p.N + n;
               if (n + 32 <= p.N) {
@@ -316,6 +342,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_arrive(&acc_empty[ab]);
       if (++ab == 2) { ab = 0; ab_phase ^= 1; }
     }
+    if (lane == 0) bulk_wait_all();   // outstanding bulk stores must have landed before the kernel ends
   }
   tc_fence_before();
   __syncthreads();
@@ -377,13 +404,36 @@ static bool gemm_map(CUtensorMap* m, const void* ptr, int rows, int K, int dtype
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int launch_gemm(const GemmParams& p, const void* x, const void* w, cudaStream_t stream) {
+// bf16 [rows][N] output, box = (32 columns, 32 rows) with 64B swizzle: the unit one epilogue warp stores at a time
+static bool gemm_out_map(CUtensorMap* m, const void* ptr, int rows, int N) {
+  EncodeTiledFn fn = gemm_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {cuuint64_t(N), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(N) * 2};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t es[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_gemm(const GemmParams& p_in, const void* x, const void* w, cudaStream_t stream) {
+  GemmParams p = p_in;
   CUtensorMap ma, mb;
   if (!gemm_map(&ma, x, p.M, p.K, p.in_dtype, kGM) || !gemm_map(&mb, w, p.N, p.K, p.in_dtype, kGN)) {
     set_error("mintb gemm: cuTensorMapEncodeTiled failed");
     return MINTB_ECUDA;
   }
-  void (*kern)(CUtensorMap, CUtensorMap, GemmParams) = nullptr;
+  // row-major bf16 outputs (and the pre-activation copy) go out as bulk tensor stores when their rows are 16-byte multiples
+  CUtensorMap mo = ma, mp = ma;   // placeholders when unused
+  p.use_bulk_store = 0;
+  if (p.epilogue != kEpiHeadMajor && p.out_dtype == MINTB_BF16 && p.N % 8 == 0) {
+    if (!gemm_out_map(&mo, p.out, p.M, p.N) || (p.preact != nullptr && !gemm_out_map(&mp, p.preact, p.M, p.N))) {
+      set_error("mintb gemm: cuTensorMapEncodeTiled failed for the output");
+      return MINTB_ECUDA;
+    }
+    p.use_bulk_store = 1;
+  }
+  void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, GemmParams) = nullptr;
   if (p.epilogue == kEpiBias) kern = gemm_tc_kernel<kEpiBias, 0>;
   else if (p.epilogue == kEpiBiasGelu) kern = gemm_tc_kernel<kEpiBiasGelu, 0>;
   else if (p.D == 16) kern = gemm_tc_kernel<kEpiHeadMajor, 16>;
@@ -396,7 +446,7 @@ int launch_gemm(const GemmParams& p, const void* x, const void* w, cudaStream_t 
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = ((p.M + kGM - 1) / kGM) * ((p.N + kGN - 1) / kGN);
   const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, kGThreads, kGemmSmem, stream>>>(ma, mb, p);
+  kern<<<grid, kGThreads, kGemmSmem, stream>>>(ma, mb, mo, mp, p);
   count_launches(1);
   e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("gemm launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
