@@ -57,6 +57,12 @@ extern "C" {
 #define MINTB_FLAG_SKIP_PAD_QUERIES 32u /* query tiles of 128 rows that hold only padded positions are not computed: their rows of
                                       `out` / `lse` stay unwritten and contribute nothing to the gradients (their d_out rows are
                                       ignored).  For callers that drop padded tokens from the token-wise work */
+#define MINTB_FLAG_QK_PREROTATED 64u /* with MINTB_FLAG_ROPE: q_self and k_self are given already rotated (the fused QKV product rotates
+                                      them in its epilogue); they are used as they are, and the gradients come back with respect to
+                                      the un-rotated projections (the transposed rotation is applied to dq_self, dk_self) */
+#define MINTB_FLAG_GRAD_ROWMAJOR 128u /* mintb_attn_bwd: the six gradients are written straight into the [T*B][3E] row-major input
+                                      gradient of a fused QKV projection: element (t,b,h,d) of a gradient goes to
+                                      ptr[(t*B + b)*3E + h*D + d]; the caller passes dq = G, dk = G + E, dv = G + 2E per pathway */
 #define MINTB_FLAG_OUT_SEQ_FIRST 8u /* `out` and `d_out` are laid out (T,B,H,D) — the layer's (T,B,E) — instead of (B,H,T,D):
                                       saves the permute copy before out_proj (modules.py:146-150) and the one of its gradient */
 

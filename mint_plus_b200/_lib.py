@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libmintb.so")
 OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA = 0, -1, -2, -3, -4
 F32, BF16, E4M3 = 0, 1, 2
 FLAG_ROPE, FLAG_SQRT_SOFTMAX, FLAG_FORCE_SIMT, FLAG_OUT_SEQ_FIRST, FLAG_ROT_SAVED, FLAG_SKIP_PAD_QUERIES = 1, 2, 4, 8, 16, 32
+FLAG_QK_PREROTATED, FLAG_GRAD_ROWMAJOR = 64, 128
 STATIC_SCRATCH_BYTES = 32 << 20
 
 _P = c_void_p

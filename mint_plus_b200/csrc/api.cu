@@ -98,13 +98,15 @@ int mintb_rope_tables(const float* inv_freq, float* cos_tab, float* sin_tab, int
 
 size_t mintb_attn_fwd_workspace_bytes(int B, int H, int T, int D, int dtype, unsigned flags) {
   if (check_shape(B, H, T, D, dtype, "mintb_attn_fwd_workspace_bytes") != MINTB_OK) return 0;
-  if (use_tc(D, dtype, flags)) return tc_fwd_workspace_bytes(B, H, T, D, (flags & MINTB_FLAG_ROPE) != 0);
+  if (use_tc(D, dtype, flags))
+    return tc_fwd_workspace_bytes(B, H, T, D, (flags & MINTB_FLAG_ROPE) != 0 && !(flags & MINTB_FLAG_QK_PREROTATED));
   return 0;
 }
 
 size_t mintb_attn_bwd_workspace_bytes(int B, int H, int T, int D, int dtype, unsigned flags) {
   if (check_shape(B, H, T, D, dtype, "mintb_attn_bwd_workspace_bytes") != MINTB_OK) return 0;
-  if (use_tc(D, dtype, flags)) return tc_bwd_workspace_bytes(B, H, T, D, (flags & MINTB_FLAG_ROPE) != 0);
+  if (use_tc(D, dtype, flags))
+    return tc_bwd_workspace_bytes(B, H, T, D, (flags & MINTB_FLAG_ROPE) != 0 && !(flags & MINTB_FLAG_QK_PREROTATED));
   return simt_bwd_workspace_bytes(B, H, T, D);
 }
 
@@ -115,7 +117,7 @@ static int fill_common(AttnArgs& a, const char* who, const void* q_s, const void
   int rc = check_shape(B, H, T, D, dtype, who);
   if (rc != MINTB_OK) return rc;
   if (flags & ~(MINTB_FLAG_ROPE | MINTB_FLAG_SQRT_SOFTMAX | MINTB_FLAG_FORCE_SIMT | MINTB_FLAG_OUT_SEQ_FIRST | MINTB_FLAG_ROT_SAVED |
-                MINTB_FLAG_SKIP_PAD_QUERIES)) {
+                MINTB_FLAG_SKIP_PAD_QUERIES | MINTB_FLAG_QK_PREROTATED | MINTB_FLAG_GRAD_ROWMAJOR)) {
     set_error("%s: unknown flag bits 0x%x", who, flags);
     return MINTB_EINVAL;
   }
@@ -152,6 +154,16 @@ static int fill_common(AttnArgs& a, const char* who, const void* q_s, const void
   a.out_seq_first = (flags & MINTB_FLAG_OUT_SEQ_FIRST) != 0;
   a.rot_saved = (flags & MINTB_FLAG_ROT_SAVED) != 0;
   a.skip_pad_queries = (flags & MINTB_FLAG_SKIP_PAD_QUERIES) != 0;
+  a.qk_prerotated = (flags & MINTB_FLAG_QK_PREROTATED) != 0;
+  a.grad_rowmajor = (flags & MINTB_FLAG_GRAD_ROWMAJOR) != 0;
+  if ((a.qk_prerotated || a.grad_rowmajor) && !use_tc(D, dtype, flags)) {
+    set_error("%s: pre-rotated inputs / row-major gradients are served by the bf16 tensor-core kernels only", who);
+    return MINTB_EUNSUPPORTED;
+  }
+  if (a.qk_prerotated && !a.rope) {
+    set_error("%s: MINTB_FLAG_QK_PREROTATED goes with MINTB_FLAG_ROPE and the tables", who);
+    return MINTB_EINVAL;
+  }
   a.scale = scale;
   a.stream = static_cast<cudaStream_t>(stream);
   a.dev_status = dev_status;

@@ -737,7 +737,7 @@ int launch_attn_fwd_tc(const AttnArgs& a) {
   if (2 * a.meta.NT > kMaxKeyTiles) { set_error("mintb_attn_fwd: T = %d exceeds %d", a.T, kMaxKeyTiles * 32); return MINTB_EUNSUPPORTED; }
   const void* q_s = a.q_s;
   const void* k_s = a.k_s;
-  if (a.rope) {
+  if (a.rope && !a.qk_prerotated) {
     char* ws = static_cast<char*>(a.workspace);
     __nv_bfloat16* qr = reinterpret_cast<__nv_bfloat16*>(ws);
     __nv_bfloat16* kr = reinterpret_cast<__nv_bfloat16*>(ws + rot_bytes(a.B, a.H, a.T, a.D));
@@ -805,7 +805,7 @@ extern "C" int mintb_attn_fwd_static(const void* q_self, const void* k_self, con
     set_error("mintb_attn_fwd_static: out (16-byte aligned) and lse are required");
     return MINTB_EINVAL;
   }
-  const size_t need = tc_fwd_workspace_bytes(B, H, T, D, a.rope);
+  const size_t need = tc_fwd_workspace_bytes(B, H, T, D, a.rope && !a.qk_prerotated);
   if (need > size_t(MINTB_STATIC_SCRATCH_BYTES)) {
     set_error("mintb_attn_fwd_static: B*H*T*D = %zu needs %zu bytes of scratch, the built-in array holds %zu; "
               "use mintb_attn_fwd with a caller-provided workspace",

@@ -158,7 +158,8 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const __nv_bfloat16* __r
 __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __restrict__ acc_s, const float* __restrict__ acc_c,
                                                              __nv_bfloat16* __restrict__ dq_s, __nv_bfloat16* __restrict__ dq_c,
                                                              const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
-                                                             size_t rows, int T, int D, float scale) {
+                                                             size_t rows, int T, int D, float scale, int H, size_t g_row,
+                                                             size_t g_b, size_t g_h) {
   const int h = D / 2, cpr = h / 8;
   const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= rows * cpr) return;
@@ -169,7 +170,9 @@ __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __rest
 #pragma unroll
   for (int which = 0; which < 2; ++which) {
     const float* src = (which == 0 ? acc_s : acc_c) + row * D + c * 8;
-    __nv_bfloat16* dst = (which == 0 ? dq_s : dq_c) + row * D + c * 8;
+    // accumulators are [b][h][t][D]; the result goes to ptr + t * g_row + b * g_b + h * g_h (+ column)
+    const size_t bh_ = row / T;
+    __nv_bfloat16* dst = (which == 0 ? dq_s : dq_c) + size_t(t) * g_row + (bh_ / H) * g_b + (bh_ % H) * g_h + c * 8;
     *reinterpret_cast<float4*>(lo) = *reinterpret_cast<const float4*>(src);
     *reinterpret_cast<float4*>(lo + 4) = *reinterpret_cast<const float4*>(src + 4);
     *reinterpret_cast<float4*>(hi) = *reinterpret_cast<const float4*>(src + h);
@@ -235,6 +238,7 @@ struct BwdParams {
   int* status;
   int do_seq_first;                // dO is laid out (T,B,H,D): its tensor map takes (0, bh, t) instead of (0, t, bh)
   int skip_pad_queries;            // query tiles that hold only padded positions are left out
+  size_t g_row, g_b, g_h;          // element strides of dk / dv: between keys, batch entries, heads
 };
 
 // ring counter with phase bit: position in [0, N), phase flips on wrap
@@ -309,7 +313,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     for (int idx = tid; idx < kBwdTile * (D / 8); idx += kBwdThreads) {
       const int row = idx / (D / 8), vec = idx % (D / 8);
       if (k0 + row < p.T) {
-        const size_t off = (size_t(bh) * p.T + k0 + row) * D + vec * 8;
+        const size_t off = size_t(k0 + row) * p.g_row + size_t(b) * p.g_b + size_t(bh % p.H) * p.g_h + vec * 8;
         *reinterpret_cast<uint4*>(p.dk[path] + off) = make_uint4(0u, 0u, 0u, 0u);
         *reinterpret_cast<uint4*>(p.dv[path] + off) = make_uint4(0u, 0u, 0u, 0u);
       }
@@ -654,7 +658,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
 #pragma unroll
             for (int d = 0; d < hD; ++d) outv[d] = half_col == 0 ? lo[d] : hi[d];
           }
-          __nv_bfloat16* dst = (is_dk ? p.dk[path] : p.dv[path]) + (size_t(bh) * p.T + kj) * D + half_col * hD;
+          __nv_bfloat16* dst = (is_dk ? p.dk[path] : p.dv[path]) + size_t(kj) * p.g_row + size_t(b) * p.g_b +
+                               size_t(bh % p.H) * p.g_h + half_col * hD;
 #pragma unroll
           for (int j = 0; j < hD; j += 8)
             *reinterpret_cast<uint4*>(dst + j) = make_uint4(bwd_pack(outv[j], outv[j + 1]), bwd_pack(outv[j + 2], outv[j + 3]),
@@ -725,6 +730,7 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const f
   p.status = a.dev_status;
   p.do_seq_first = a.out_seq_first ? 1 : 0;
   p.skip_pad_queries = a.skip_pad_queries ? 1 : 0;
+  p.g_row = grad_row_stride(a); p.g_b = grad_b_stride(a); p.g_h = grad_h_stride(a);
   dim3 grid((a.T + kBwdTile - 1) / kBwdTile, BH, 2);
   attn_bwd_tc_kernel<D, SQ><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, mdq_s, mdq_c, p);
   count_launches(1);
@@ -739,7 +745,7 @@ int launch_attn_bwd_tc(const AttnArgs& a) {
   const void* q_s = a.q_s;
   const void* k_s = a.k_s;
   const size_t rows = size_t(a.B) * a.H * a.T;
-  if (a.rope) {
+  if (a.rope && !a.qk_prerotated) {
     __nv_bfloat16* qr = reinterpret_cast<__nv_bfloat16*>(ws);
     __nv_bfloat16* kr = reinterpret_cast<__nv_bfloat16*>(ws + bwd_rot_bytes(a.B, a.H, a.T, a.D));
     if (!a.rot_saved) launch_rope_rotate(a, qr, kr);
@@ -779,7 +785,8 @@ int launch_attn_bwd_tc(const AttnArgs& a) {
     const size_t n = rows * (a.D / 16);
     bwd_dq_convert_kernel<<<unsigned((n + 255) / 256), 256, 0, a.stream>>>(
         acc_s, acc_c, static_cast<__nv_bfloat16*>(a.dq_s), static_cast<__nv_bfloat16*>(a.dq_c),
-        a.rope ? a.rope_cos : nullptr, a.rope ? a.rope_sin : nullptr, rows, a.T, a.D, a.scale);
+        a.rope ? a.rope_cos : nullptr, a.rope ? a.rope_sin : nullptr, rows, a.T, a.D, a.scale, a.H, grad_row_stride(a),
+        grad_b_stride(a), grad_h_stride(a));
     count_launches(1);
   }
   e = cudaGetLastError();

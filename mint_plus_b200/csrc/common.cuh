@@ -76,6 +76,8 @@ struct AttnArgs {
   bool out_seq_first;                // out / d_out laid out (T,B,H,D) instead of (B,H,T,D)
   bool rot_saved;                    // backward: the workspace already starts with the rotated Q_self, K_self
   bool skip_pad_queries;             // query tiles holding only padded positions are left out
+  bool qk_prerotated;                // q_self / k_self arrive rotated; only the gradients are (un-)rotated
+  bool grad_rowmajor;                // gradients go into [T*B][3E] row-major matrices
   float scale;
   cudaStream_t stream;
   int* dev_status;
@@ -84,6 +86,11 @@ struct AttnArgs {
 // element strides of out / d_out: row (query) stride and (batch, head) stride
 inline size_t out_row_stride(const AttnArgs& a) { return a.out_seq_first ? size_t(a.B) * a.H * a.D : size_t(a.D); }
 inline size_t out_bh_stride(const AttnArgs& a) { return a.out_seq_first ? size_t(a.D) : size_t(a.T) * a.D; }
+
+// element strides of the six gradient tensors: between rows (t), batch entries and heads
+inline size_t grad_row_stride(const AttnArgs& a) { return a.grad_rowmajor ? size_t(a.B) * 3 * a.H * a.D : size_t(a.D); }
+inline size_t grad_b_stride(const AttnArgs& a) { return a.grad_rowmajor ? size_t(3) * a.H * a.D : size_t(a.H) * a.T * a.D; }
+inline size_t grad_h_stride(const AttnArgs& a) { return a.grad_rowmajor ? size_t(a.D) : size_t(a.T) * a.D; }
 
 void set_error(const char* fmt, ...);
 void count_launches(int n);  // process-wide tally of kernels launched by this library

@@ -128,8 +128,10 @@ class _TwoPathwayLayer(nn.Module):
             tabs = ops.rope_tables(T, sa.head_dim, x.device, sa.rot_emb.inv_freq)[:2] if rope else None
             q_s, k_s, v_s = ops.qkv_project(x, ops_s[0], ops_s[1], sa.num_heads, rope=tabs, fp8=ops_s[2], pack=pack, lora=ops_s[3])
             q_c, k_c, v_c = ops.qkv_project(x, ops_c[0], ops_c[1], ma.num_heads, fp8=ops_c[2], pack=pack, lora=ops_c[3])
+            # (without packing the backward pass writes the gradients row-major for the projections' backward passes)
             attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=False, scale=sa.scaling,
                                               sqrt_softmax=sqrt_sm, out_seq_first=True, skip_pad_queries=pack is not None,
+                                              grad_rowmajor_tabs=(tabs if tabs is not None else (None, None)) if pack is None else None,
                                               **mask_kw)
         elif pack is not None:
             raise NotImplementedError("packed tokens need bfloat16 CUDA activations and nn.Linear / Fp8Linear projections")

@@ -151,7 +151,7 @@ def rope_tables(T: int, D: int, device, inv_freq: Optional[torch.Tensor] = None)
 # ----------------------------------------------------------------------------------------------- attention
 class _MultimerAttentionFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q_s, k_s, v_s, q_c, k_c, v_c, meta: MaskMeta, cos, sin, scale: float, flags: int):
+    def forward(ctx, q_s, k_s, v_s, q_c, k_c, v_c, meta: MaskMeta, cos, sin, scale: float, flags: int, grad_tabs=None):
         B, H, T, D = q_s.shape
         dt = _DTYPES[q_s.dtype]
         lib = L.lib()
@@ -175,6 +175,7 @@ class _MultimerAttentionFn(torch.autograd.Function):
         L.check(rc, "mintb_attn_fwd")
         ctx.save_for_backward(q_s, k_s, v_s, q_c, k_c, v_c, out, lse, cos, sin)
         ctx.meta, ctx.scale, ctx.flags = meta, scale, flags
+        ctx.grad_tabs = grad_tabs
         return out
 
     @staticmethod
@@ -184,9 +185,21 @@ class _MultimerAttentionFn(torch.autograd.Function):
         dt = _DTYPES[q_s.dtype]
         lib = L.lib()
         d_out = d_out.contiguous()
-        grads = [torch.empty_like(q_s) for _ in range(6)]
-        ws_bytes = lib.mintb_attn_bwd_workspace_bytes(B, H, T, D, dt, ctx.flags)
         flags = ctx.flags
+        rowmajor = ctx.grad_tabs is not None
+        if rowmajor:
+            # The inputs came from the fused QKV products (q, k of the self pathway already rotated there): the gradients are
+            # written straight into the [T*B][3E] matrices those products' backward passes consume — un-rotated, no gather pass.
+            E = H * D
+            g_s, g_c = (torch.empty(T * B, 3 * E, dtype=q_s.dtype, device=q_s.device) for _ in range(2))
+            grads = [g_s[:, :E], g_s[:, E:2 * E], g_s[:, 2 * E:], g_c[:, :E], g_c[:, E:2 * E], g_c[:, 2 * E:]]
+            if ctx.grad_tabs[0] is not None:
+                cos, sin = ctx.grad_tabs
+                flags |= L.FLAG_ROPE | L.FLAG_QK_PREROTATED
+            flags |= L.FLAG_GRAD_ROWMAJOR
+        else:
+            grads = [torch.empty_like(q_s) for _ in range(6)]
+        ws_bytes = lib.mintb_attn_bwd_workspace_bytes(B, H, T, D, dt, flags)
         if ctx.fwd_ws is not None:
             ws, ws_bytes, flags = ctx.fwd_ws, ctx.fwd_ws.numel(), flags | L.FLAG_ROT_SAVED
         else:
@@ -197,17 +210,22 @@ class _MultimerAttentionFn(torch.autograd.Function):
                                     _ptr(ws), ws_bytes, B, H, T, D, dt, flags, ctx.scale, _stream(),
                                     _ptr(_dev_status(q_s.device)))
         L.check(rc, "mintb_attn_bwd")
-        return (*grads, None, None, None, None, None)
+        if rowmajor:   # hand each gradient back as the (B,H,T,D) view of its third of the row-major matrix
+            grads = [g.view(T, B, H, D).permute(1, 2, 0, 3) for g in grads]
+        return (*grads, None, None, None, None, None, None)
 
 
 def multimer_attention(q_self, k_self, v_self, q_cross, k_cross, v_cross, *, meta: Optional[MaskMeta] = None,
                        chain_ids=None, chain_mask=None, key_padding_mask=None, rope: bool = True,
                        inv_freq: Optional[torch.Tensor] = None, scale: Optional[float] = None,
                        sqrt_softmax: bool = False, force_simt: bool = False, out_seq_first: bool = False,
-                       skip_pad_queries: bool = False) -> torch.Tensor:
+                       skip_pad_queries: bool = False, grad_rowmajor_tabs=None) -> torch.Tensor:
     """Two-pathway combined-softmax attention on (B,H,T,D) projections; differentiable.  The result is (B,H,T,D), or
     (T,B,H,D) with out_seq_first=True (the layout of the layer's (T,B,E) activations: no permute copy before out_proj).
     skip_pad_queries=True leaves out 128-row query tiles that hold only padded positions: their output rows stay unwritten.
+    grad_rowmajor_tabs = (cos, sin) or (None, None): for inputs that came from `qkv_project` (q, k of the self pathway rotated
+    there with these tables, rope=False here): the backward pass writes the gradients straight into the [T*B][3E] matrices
+    the projections' backward passes consume, un-rotating dq_self / dk_self on the way (bf16 tensor-core path only).
 
 
     out = (P o ~M) V_self + (P o M) V_cross,  P = softmax_j where(M, s*Qc Kc^T, s*R(Qs) R(Ks)^T), padded keys -inf
@@ -240,7 +258,9 @@ def multimer_attention(q_self, k_self, v_self, q_cross, k_cross, v_cross, *, met
     if scale is None:
         scale = D ** -0.5
     ts = tuple(t.contiguous() for t in ts)
-    return _MultimerAttentionFn.apply(*ts, meta, cos, sin, float(scale), int(flags))
+    if grad_rowmajor_tabs is not None and (rope or force_simt or q_self.dtype != torch.bfloat16 or D not in (16, 32, 64)):
+        grad_rowmajor_tabs = None      # served by the bf16 tensor-core kernels on pre-rotated inputs only
+    return _MultimerAttentionFn.apply(*ts, meta, cos, sin, float(scale), int(flags), grad_rowmajor_tabs)
 
 
 # ----------------------------------------------------------------------------------------------- combine from logits
@@ -506,6 +526,37 @@ def _lora_merged(w, lora_a, lora_b, scaling):
         return w + scaling * delta
 
 
+def _lora_grads(g, x2d, lora_a, lora_b, scaling, E, wanted):
+    """The adapters' gradients through thin products only (no E x E weight gradient): for each of q, k, v
+    dB = s g^T (x A^T), dA = s (g B)^T x."""
+    if lora_a is None or not wanted:
+        return None, None
+    g3 = g.view(-1, 3, E)
+    d_a, d_b = torch.empty_like(lora_a), torch.empty_like(lora_b)
+    for i in range(3):
+        gi = g3[:, i]
+        d_b[i] = ((gi.t() @ (x2d @ lora_a[i].to(x2d.dtype).t())) * scaling).to(lora_b.dtype)
+        d_a[i] = (((gi @ lora_b[i].to(x2d.dtype)).t() @ x2d) * scaling).to(lora_a.dtype)
+    return d_a, d_b
+
+
+def _rowmajor_base(dq, dk, dv, T, B, H, D):
+    """If dq, dk, dv are the (B,H,T,D) views of the three thirds of ONE contiguous [T*B][3E] matrix (what the attention
+    backward pass hands back when it writes row-major), return that matrix, else None."""
+    E = H * D
+    want_stride = (3 * E, D, B * 3 * E, 1)
+    ts = (dq, dk, dv)
+    if any(t.dtype != torch.bfloat16 or tuple(t.shape) != (B, H, T, D) or tuple(t.stride()) != want_stride for t in ts):
+        return None
+    st = dq.untyped_storage()
+    if any(t.untyped_storage().data_ptr() != st.data_ptr() for t in ts):
+        return None
+    o = dq.storage_offset()
+    if dk.storage_offset() != o + E or dv.storage_offset() != o + 2 * E:
+        return None
+    return torch.as_strided(dq, (T * B, 3 * E), (3 * E, 1), o)
+
+
 class _QkvFn(torch.autograd.Function):
     """Fused QKV projection of one pathway with head-major outputs (and RoPE on q, k when tables are given)."""
 
@@ -550,8 +601,16 @@ class _QkvFn(torch.autograd.Function):
         # (B,H,T,D) x3 -> [T*B, 3E] with the rotation undone and the q scale applied, in one pass
         pack = ctx.pack
         n_rows = x2d.shape[0]
-        g = torch.empty(n_rows, 3 * E, dtype=torch.bfloat16, device=x2d.device)
         want_db = bias is not None and ctx.needs_input_grad[2]
+        g = _rowmajor_base(dq, dk, dv, T, B, H, D) if (pack is None and q_scale == 1.0) else None
+        if g is not None:
+            # the attention backward pass has already written [dQ | dK | dV] row-major (and un-rotated): no gather pass
+            w_used = _lora_merged(w, lora_a, lora_b, ctx.lora_scaling)
+            dx, dw, db = linear_backward(g, x2d, w_used, bias, None, ctx.needs_input_grad, out_scale)
+            d_a, d_b = _lora_grads(g, x2d, lora_a, lora_b, ctx.lora_scaling, E, ctx.needs_input_grad[12] or ctx.needs_input_grad[13])
+            return ((dx.view(ctx.x_shape) if dx is not None else None), dw, db, None, None, None, None, None, None, None, None, None,
+                    d_a, d_b, None)
+        g = torch.empty(n_rows, 3 * E, dtype=torch.bfloat16, device=x2d.device)
         db = torch.empty(3 * E, dtype=torch.float32, device=x2d.device) if want_db else None
         with torch.cuda.device(x2d.device):
             rc = L.lib().mintb_qkv_grad_pack(_ptr(dq.contiguous()), _ptr(dk.contiguous()), _ptr(dv.contiguous()), _ptr(g), _ptr(db),
@@ -560,17 +619,7 @@ class _QkvFn(torch.autograd.Function):
         L.check(rc, "mintb_qkv_grad_pack")
         w_used = _lora_merged(w, lora_a, lora_b, ctx.lora_scaling)
         dx, dw, db = linear_backward(g, x2d, w_used, bias, None, ctx.needs_input_grad, out_scale, db=db)
-        d_a = d_b = None
-        if lora_a is not None and (ctx.needs_input_grad[12] or ctx.needs_input_grad[13]):
-            # the adapters' gradients through thin products only (no E x E weight gradient): for each of q, k, v
-            # dB = s g^T (x A^T), dA = s (g B)^T x
-            s_ = ctx.lora_scaling
-            g3 = g.view(-1, 3, E)
-            d_a, d_b = torch.empty_like(lora_a), torch.empty_like(lora_b)
-            for i in range(3):
-                gi = g3[:, i]
-                d_b[i] = ((gi.t() @ (x2d @ lora_a[i].to(x2d.dtype).t())) * s_).to(lora_b.dtype)
-                d_a[i] = (((gi @ lora_b[i].to(x2d.dtype)).t() @ x2d) * s_).to(lora_a.dtype)
+        d_a, d_b = _lora_grads(g, x2d, lora_a, lora_b, ctx.lora_scaling, E, ctx.needs_input_grad[12] or ctx.needs_input_grad[13])
         return ((dx.view(ctx.x_shape) if dx is not None else None), dw, db, None, None, None, None, None, None, None, None, None,
                 d_a, d_b, None)
 
