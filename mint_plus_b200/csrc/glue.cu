@@ -79,26 +79,35 @@ __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_fwd_kernel(LnPara
   for (int row = blockIdx.x * kLnWarps + warp; row < p.rows; row += gridDim.x * kLnWarps) {
     const uint4* xr = reinterpret_cast<const uint4*>(p.x + size_t(row) * p.E);
     const uint4* rr = p.r != nullptr ? reinterpret_cast<const uint4*>(p.r + size_t(row) * p.E) : nullptr;
+    // every load of the row is issued before the first use (a store between two loads would order them)
+    uint4 xq[MAXV], rq[MAXV];
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int vi = lane + 32 * k;
+      xq[k] = rq[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (vi < nvec) {
+        xq[k] = __ldg(xr + vi);
+        if (rr != nullptr) rq[k] = __ldg(rr + vi);
+      }
+    }
     float v[MAXV][8];
     float sum = 0.f;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
-      const int vi = lane + 32 * k;
-      if (vi < nvec) {
-        float xv[8];
-        unpack8(__ldg(xr + vi), xv);
-        if (rr != nullptr) {
-          float rv[8];
-          unpack8(__ldg(rr + vi), rv);
+      float xv[8], rv[8];
+      unpack8(xq[k], xv);
+      unpack8(rq[k], rv);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[k][j] = fmaf(p.a, xv[j], p.b * rv[j]);
-        } else {
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = rr != nullptr ? fmaf(p.a, xv[j], p.b * rv[j]) : p.a * xv[j];
+        sum += v[k][j];
+      }
+    }
+    if (p.s_out != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[k][j] = p.a * xv[j];
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) sum += v[k][j];
-        if (p.s_out != nullptr) reinterpret_cast<uint4*>(p.s_out + size_t(row) * p.E)[vi] = pack8(v[k]);
+      for (int k = 0; k < MAXV; ++k) {
+        const int vi = lane + 32 * k;
+        if (vi < nvec) reinterpret_cast<uint4*>(p.s_out + size_t(row) * p.E)[vi] = pack8(v[k]);
       }
     }
     if (p.gamma == nullptr) continue;
@@ -135,139 +144,143 @@ __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_fwd_kernel(LnPara
 
 // ds = LayerNorm'(dy) + ds_in;  dx = a ds;  dr = b ds;  per-CTA partial sums for dgamma / dbeta.
 // LayerNorm backward per row: g = dy gamma, xhat = (s - mean) rstd, ds = rstd (g - mean(g) - xhat mean(g xhat)).
-template <int MAXV>
-__global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_bwd_kernel(LnParams p) {
-  extern __shared__ float ln_smem[];   // [kLnWarps][2][E] when normalising
-  __shared__ __align__(16) float s_gamma[kLnMaxE];
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+//
+// A CTA spans one row: thread i owns the 8 columns of 16-byte vector i for every row the CTA walks, so its share of
+// dgamma / dbeta stays in 16 registers and no thread ever adds into another thread's columns.  kLnBwdRows rows are in
+// flight at a time (up to 16 loads of 16 bytes per thread before the first use); their 2 x kLnBwdRows row sums are reduced
+// by warp shuffles, then across the warps through a double-buffered shared-memory slot with ONE barrier per batch of rows.
+#ifndef MINTB_LN_BWD_ROWS
+#define MINTB_LN_BWD_ROWS 4
+#endif
+#ifndef MINTB_LN_BWD_PER_SM
+#define MINTB_LN_BWD_PER_SM 3
+#endif
+constexpr int kLnBwdRows = MINTB_LN_BWD_ROWS;
+static_assert(kLnBwdRows % 2 == 0, "row sums travel as float4");
+constexpr int kLnBwdMaxWarps = kLnMaxE / 8 / 32;   // 10
+
+// NW: warps per CTA (E <= NW * 256); MINB: CTAs per SM the register budget is cut for.
+template <int NW, int MINB>
+__global__ void __launch_bounds__(NW * 32, MINB) add_layernorm_bwd_kernel(LnParams p) {
+  __shared__ __align__(16) float red[2][NW][2 * kLnBwdRows];
+  const int vi = threadIdx.x, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int nvec = p.E / 8;
-  const float inv_e = 1.f / float(p.E);
+  constexpr int nwarps = NW;
+  const bool live = vi < nvec;
   const bool norm = p.gamma != nullptr;
-  if (norm) {
-    for (int i = threadIdx.x; i < p.E; i += kLnWarps * 32) s_gamma[i] = ld_param(p.gamma, p.param_dtype, i);
-    __syncthreads();
-  }
-  float* acc_g = ln_smem + size_t(warp) * 2 * p.E;   // sum dy * xhat
-  float* acc_b = acc_g + p.E;                        // sum dy
-  // Up to 1280 columns the parameter-gradient sums of a lane's own columns stay in registers over all the rows the warp
-  // walks; wider rows accumulate in the warp's slice of shared memory instead.
-  constexpr bool kRegAcc = MAXV <= 5;
-  float rg[kRegAcc ? MAXV : 1][8], rb[kRegAcc ? MAXV : 1][8];
-  if (kRegAcc) {
+  const float inv_e = 1.f / float(p.E);
+  float gm[8], rg[8], rb[8];
 #pragma unroll
-    for (int k = 0; k < (kRegAcc ? MAXV : 1); ++k)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) rg[k][j] = rb[k][j] = 0.f;
-  } else if (norm) {
-    for (int i = lane; i < 2 * p.E; i += 32) acc_g[i] = 0.f;
-    __syncwarp();
+  for (int j = 0; j < 8; ++j) {
+    gm[j] = (norm && live) ? ld_param(p.gamma, p.param_dtype, vi * 8 + j) : 0.f;
+    rg[j] = rb[j] = 0.f;
   }
-  for (int row = blockIdx.x * kLnWarps + warp; row < p.rows; row += gridDim.x * kLnWarps) {
-    const size_t off = size_t(row) * p.E;
-    float ds[MAXV][8];
+  int parity = 0;
+  for (int row0 = blockIdx.x * kLnBwdRows; row0 < p.rows; row0 += gridDim.x * kLnBwdRows, parity ^= 1) {
+    uint4 xq[kLnBwdRows], dq[kLnBwdRows], rq[kLnBwdRows];
+    float2 st[kLnBwdRows];
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int r = 0; r < kLnBwdRows; ++r) {
+      const int row = row0 + r;
+      const bool ok = live && row < p.rows;
+      const size_t off = size_t(row) * p.E;
+      xq[r] = dq[r] = rq[r] = zero4;
+      st[r] = make_float2(0.f, 0.f);
+      if (ok && norm) {
+        xq[r] = __ldg(reinterpret_cast<const uint4*>(p.x + off) + vi);
+        dq[r] = __ldg(reinterpret_cast<const uint4*>(p.dy + off) + vi);
+        if (p.r != nullptr) rq[r] = __ldg(reinterpret_cast<const uint4*>(p.r + off) + vi);
+        st[r] = __ldg(p.stats + row);
+      }
+    }
+    float c[2 * kLnBwdRows];
     if (norm) {
-      const float2 st = p.stats[row];
-      float xh[MAXV][8];
-      float c1 = 0.f, c2 = 0.f;
 #pragma unroll
-      for (int k = 0; k < MAXV; ++k) {
-        const int vi = lane + 32 * k;
-        if (vi < nvec) {
-          float xv[8], dyv[8];
-          unpack8(__ldg(reinterpret_cast<const uint4*>(p.x + off) + vi), xv);
-          unpack8(__ldg(reinterpret_cast<const uint4*>(p.dy + off) + vi), dyv);
-          if (p.r != nullptr) {
-            float rv[8];
-            unpack8(__ldg(reinterpret_cast<const uint4*>(p.r + off) + vi), rv);
+      for (int r = 0; r < kLnBwdRows; ++r) {
+        float xv[8], dyv[8], rv[8];
+        unpack8(xq[r], xv);
+        unpack8(dq[r], dyv);
+        unpack8(rq[r], rv);
+        float c1 = 0.f, c2 = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) xv[j] = fmaf(p.a, xv[j], p.b * rv[j]);
-          } else {
+        for (int j = 0; j < 8; ++j) {
+          const float xhat = (fmaf(p.a, xv[j], p.b * rv[j]) - st[r].x) * st[r].y;   // rows past the end: all zeros
+          const float g = dyv[j] * gm[j];
+          c1 += g;
+          c2 = fmaf(g, xhat, c2);
+          rg[j] = fmaf(dyv[j], xhat, rg[j]);
+          rb[j] += dyv[j];
+        }
+        c[2 * r] = warp_sum_f(c1);
+        c[2 * r + 1] = warp_sum_f(c2);
+      }
+      if (lane == 0) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) xv[j] *= p.a;
-          }
-          float gm[8];
-          *reinterpret_cast<float4*>(gm) = *reinterpret_cast<const float4*>(s_gamma + vi * 8);
-          *reinterpret_cast<float4*>(gm + 4) = *reinterpret_cast<const float4*>(s_gamma + vi * 8 + 4);
+        for (int i = 0; i < 2 * kLnBwdRows; i += 4)
+          *reinterpret_cast<float4*>(&red[parity][warp][i]) = make_float4(c[i], c[i + 1], c[i + 2], c[i + 3]);
+      }
+      __syncthreads();   // the slot of the other parity is free again once every thread is past this barrier
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float xhat = (xv[j] - st.x) * st.y;
-            const float g = dyv[j] * gm[j];
-            xh[k][j] = xhat;
-            ds[k][j] = g;
-            c1 += g;
-            c2 = fmaf(g, xhat, c2);
-            if (kRegAcc) {
-              rg[kRegAcc ? k : 0][j] = fmaf(dyv[j], xhat, rg[kRegAcc ? k : 0][j]);
-              rb[kRegAcc ? k : 0][j] += dyv[j];
-            } else {
-              // this lane alone touches these entries; element e = 8 vi + j sits at j * nvec + vi (no bank conflicts)
-              acc_g[j * nvec + vi] = fmaf(dyv[j], xhat, acc_g[j * nvec + vi]);
-              acc_b[j * nvec + vi] += dyv[j];
-            }
-          }
+      for (int i = 0; i < 2 * kLnBwdRows; ++i) c[i] = 0.f;
+#pragma unroll
+      for (int w = 0; w < nwarps; ++w) {   // same order in every thread: all of them hold identical sums
+#pragma unroll
+        for (int i = 0; i < 2 * kLnBwdRows; i += 4) {
+          const float4 t = *reinterpret_cast<const float4*>(&red[parity][w][i]);
+          c[i] += t.x; c[i + 1] += t.y; c[i + 2] += t.z; c[i + 3] += t.w;
         }
       }
-      c1 = warp_sum_f(c1) * inv_e;
-      c2 = warp_sum_f(c2) * inv_e;
-#pragma unroll
-      for (int k = 0; k < MAXV; ++k) {
-        if (lane + 32 * k < nvec) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) ds[k][j] = st.y * (ds[k][j] - c1 - xh[k][j] * c2);
-        }
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < MAXV; ++k)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ds[k][j] = 0.f;
     }
+    // The second pass unpacks the rows again instead of keeping 2 x 8 x kLnBwdRows fp32 values alive across the barrier;
+    // the empty statements stop the compiler from undoing that.
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
-      const int vi = lane + 32 * k;
-      if (vi < nvec) {
-        if (p.ds_in != nullptr) {
-          float e[8];
-          unpack8(__ldg(reinterpret_cast<const uint4*>(p.ds_in + off) + vi), e);
+    for (int r = 0; r < kLnBwdRows; ++r) {
+      asm volatile("" : "+r"(xq[r].x), "+r"(xq[r].y), "+r"(xq[r].z), "+r"(xq[r].w));
+      asm volatile("" : "+r"(dq[r].x), "+r"(dq[r].y), "+r"(dq[r].z), "+r"(dq[r].w));
+      asm volatile("" : "+r"(rq[r].x), "+r"(rq[r].y), "+r"(rq[r].z), "+r"(rq[r].w));
+    }
+    uint4 eq[kLnBwdRows];   // the gradient that reaches s directly (the residual branch of a Pre-LN layer), or zeros
 #pragma unroll
-          for (int j = 0; j < 8; ++j) ds[k][j] += e[j];
+    for (int r = 0; r < kLnBwdRows; ++r)
+      eq[r] = (p.ds_in != nullptr && live && row0 + r < p.rows)
+                  ? __ldg(reinterpret_cast<const uint4*>(p.ds_in + size_t(row0 + r) * p.E) + vi) : zero4;
+#pragma unroll
+    for (int r = 0; r < kLnBwdRows; ++r) {
+      const int row = row0 + r;
+      if (!(live && row < p.rows)) continue;
+      const size_t off = size_t(row) * p.E;
+      float ds[8];
+      unpack8(eq[r], ds);
+      if (norm) {
+        float xv[8], dyv[8], rv[8];
+        unpack8(xq[r], xv);
+        unpack8(dq[r], dyv);
+        unpack8(rq[r], rv);
+        const float c1 = c[2 * r] * inv_e, c2 = c[2 * r + 1] * inv_e;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xhat = (fmaf(p.a, xv[j], p.b * rv[j]) - st[r].x) * st[r].y;
+          ds[j] += st[r].y * (dyv[j] * gm[j] - c1 - xhat * c2);
         }
-        float o[8];
+      }
+      float o[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = p.a * ds[k][j];
-        reinterpret_cast<uint4*>(p.dx + off)[vi] = pack8(o);
-        if (p.dr != nullptr) {
+      for (int j = 0; j < 8; ++j) o[j] = p.a * ds[j];
+      reinterpret_cast<uint4*>(p.dx + off)[vi] = pack8(o);
+      if (p.dr != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = p.b * ds[k][j];
-          reinterpret_cast<uint4*>(p.dr + off)[vi] = pack8(o);
-        }
+        for (int j = 0; j < 8; ++j) o[j] = p.b * ds[j];
+        reinterpret_cast<uint4*>(p.dr + off)[vi] = pack8(o);
       }
     }
   }
-  if (norm) {
-    if (kRegAcc) {   // the register sums go through the same shared-memory slices for the reduction over the CTA's warps
-#pragma unroll
-      for (int k = 0; k < (kRegAcc ? MAXV : 1); ++k) {
-        const int vi = lane + 32 * k;
-        if (vi < nvec) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            acc_g[j * nvec + vi] = rg[k][j];
-            acc_b[j * nvec + vi] = rb[k][j];
-          }
-        }
-      }
-    }
-    __syncthreads();
-    float* dst = p.partial + size_t(blockIdx.x) * 2 * p.E;
-    for (int i = threadIdx.x; i < 2 * p.E; i += kLnWarps * 32) {
-      const int which = i / p.E, e = i % p.E;
-      const int src = which * p.E + (e % 8) * nvec + e / 8;
-      float t = 0.f;
-#pragma unroll
-      for (int w = 0; w < kLnWarps; ++w) t += ln_smem[size_t(w) * 2 * p.E + src];
-      dst[i] = t;
-    }
+  if (norm && live) {
+    float* dst = p.partial + size_t(blockIdx.x) * 2 * p.E + vi * 8;
+    *reinterpret_cast<float4*>(dst) = make_float4(rg[0], rg[1], rg[2], rg[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(rg[4], rg[5], rg[6], rg[7]);
+    *reinterpret_cast<float4*>(dst + p.E) = make_float4(rb[0], rb[1], rb[2], rb[3]);
+    *reinterpret_cast<float4*>(dst + p.E + 4) = make_float4(rb[4], rb[5], rb[6], rb[7]);
   }
 }
 
@@ -292,7 +305,9 @@ __global__ void __launch_bounds__(256) ln_param_grad_kernel(const float* __restr
 }
 
 // ------------------------------------------------------------------------------------------------ GELU backward + column sums
-constexpr int kColRows = 256;   // rows per CTA strip
+constexpr int kColRows = 256;   // rows per CTA strip of the gradient pack
+constexpr int kSumRows = 64;    // rows per CTA strip of the column sums: every thread has its 8 rows in flight at once, and
+                                // the grid is many waves deep (a 256-row strip left 1.6 to 2.2 waves at 32768 rows)
 constexpr int kColLanes = 8;    // threads that share a column group, each taking every 8th row of the strip
 
 // d/dz [z/2 (1 + erf(z / sqrt 2))] = (1 + erf(z / sqrt 2)) / 2 + z exp(-z^2 / 2) / sqrt(2 pi).  erf comes from the
@@ -312,33 +327,53 @@ __device__ __forceinline__ float gelu_erf_grad(float z) {
   return fmaf(z * 0.3989422804014327f, e, cdf);
 }
 
-// CTA = 32 column groups (8 columns each: 256 columns) x 8 row lanes over a strip of kColRows rows; a warp reads 512
-// contiguous bytes of one row.  The 8 partial column sums meet in shared memory; db gets one atomicAdd per column and CTA.
+// CTA = 32 column groups (8 columns each: 256 columns) x 8 row lanes over a strip of kSumRows rows; a warp reads 512
+// contiguous bytes of one row.  A thread issues the loads of all its rows of the strip (in two halves when z is read as
+// well) before it touches the first value.  The 8 partial column sums meet in shared memory; db gets one atomicAdd per
+// column and CTA.
+template <bool HAS_Z>
 __global__ void __launch_bounds__(256) gelu_bwd_colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ z,
                                                               __nv_bfloat16* __restrict__ dz, float* __restrict__ db, int M, int N) {
   __shared__ float part[kColLanes][32][8];
   const int cl = threadIdx.x % 32, rl = threadIdx.x / 32;
   const int cg = blockIdx.x * 32 + cl;   // column group
   const bool live = cg * 8 < N;
-  const int m0 = blockIdx.y * kColRows, m1 = min(M, m0 + kColRows);
+  const int m0 = blockIdx.y * kSumRows;
+  constexpr int kPerThread = kSumRows / kColLanes;        // 8 rows of the strip per thread
+  constexpr int kBatch = HAS_Z ? kPerThread / 2 : kPerThread;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (live) {
-#pragma unroll 8
-    for (int m = m0 + rl; m < m1; m += kColLanes) {
-      const size_t off = size_t(m) * N + size_t(cg) * 8;
-      float g[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(dy + off)), g);
-      if (z != nullptr) {
-        float zv[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(z + off)), zv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) g[j] *= gelu_erf_grad(zv[j]);
-        const uint4 packed = pack8(g);
-        *reinterpret_cast<uint4*>(dz + off) = packed;
-        unpack8(packed, g);   // the bias gradient sums what the products will read
+    for (int h = 0; h < kPerThread / kBatch; ++h) {
+      uint4 gq[kBatch], zq[HAS_Z ? kBatch : 1];
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        const int m = m0 + rl + (h * kBatch + i) * kColLanes;
+        const size_t off = size_t(m) * N + size_t(cg) * 8;
+        gq[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (HAS_Z) zq[i] = gq[i];
+        if (m < M) {
+          gq[i] = __ldg(reinterpret_cast<const uint4*>(dy + off));
+          if (HAS_Z) zq[i] = __ldg(reinterpret_cast<const uint4*>(z + off));
+        }
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] += g[j];
+      for (int i = 0; i < kBatch; ++i) {
+        const int m = m0 + rl + (h * kBatch + i) * kColLanes;
+        float g[8];
+        unpack8(gq[i], g);
+        if (HAS_Z) {
+          float zv[8];
+          unpack8(zq[i], zv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] *= gelu_erf_grad(zv[j]);
+          const uint4 packed = pack8(g);
+          if (m < M) *reinterpret_cast<uint4*>(dz + size_t(m) * N + size_t(cg) * 8) = packed;
+          unpack8(packed, g);   // the bias gradient sums what the products will read
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += g[j];   // rows past the end hold zeros
+      }
     }
   }
   if (db == nullptr) return;
@@ -433,9 +468,10 @@ int fail(const char* what, cudaError_t e) {
 
 int ln_maxv(int E) { return E <= 512 ? 2 : (E <= 1280 ? 5 : (E <= 2560 ? 10 : 0)); }
 
-int ln_grid(int rows) {
-  const int want = (rows + kLnWarps - 1) / kLnWarps;
-  return want < 148 * 4 ? want : 148 * 4;   // a few CTAs per SM; rows are walked with a grid stride
+// Upper bound of the backward grid (sizes the partial-sum workspace); the launch takes min(this, 148 x resident CTAs per SM).
+int ln_bwd_grid_max(int rows) {
+  const int want = (rows + kLnBwdRows - 1) / kLnBwdRows;
+  return want < 148 * 8 ? want : 148 * 8;
 }
 
 }  // namespace
@@ -476,7 +512,7 @@ int mintb_add_layernorm_fwd(const void* x, const void* r, float a, float b, cons
 
 size_t mintb_add_layernorm_bwd_workspace_bytes(int rows, int E) {
   if (rows <= 0 || E <= 0) return 0;
-  return align256(size_t(ln_grid(rows)) * 2 * E * sizeof(float));
+  return align256(size_t(ln_bwd_grid_max(rows)) * 2 * E * sizeof(float));
 }
 
 int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const void* x, const void* r, float a, float b, const void* gamma,
@@ -504,18 +540,17 @@ int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const void* x, co
   p.dx = static_cast<__nv_bfloat16*>(dx); p.dr = static_cast<__nv_bfloat16*>(dr);
   p.partial = static_cast<float*>(workspace); p.rows = rows; p.E = E;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int grid = ln_grid(rows);
-  const size_t smem = norm ? size_t(kLnWarps) * 2 * E * sizeof(float) : 0;
-  cudaError_t e = cudaSuccess;
-#define MINTB_LN_BWD(V)                                                                                                   \
-  e = cudaFuncSetAttribute(add_layernorm_bwd_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));          \
-  if (e == cudaSuccess) add_layernorm_bwd_kernel<V><<<grid, kLnWarps * 32, smem, st>>>(p);
-  switch (ln_maxv(E)) {
-    case 2: MINTB_LN_BWD(2) break;
-    case 5: MINTB_LN_BWD(5) break;
-    default: MINTB_LN_BWD(10) break;
+  // one 16-byte vector of the row per thread; ONE wave of CTAs, each walking its share of the rows
+  const int nw = ln_maxv(E);   // 2, 5 or 10 warps
+  const int per_sm = nw == 2 ? 8 : (nw == 5 ? MINTB_LN_BWD_PER_SM : 1);
+  const int grid_max = ln_bwd_grid_max(rows);
+  const int grid = grid_max < 148 * per_sm ? grid_max : 148 * per_sm;
+  switch (nw) {
+    case 2: add_layernorm_bwd_kernel<2, 8><<<grid, 64, 0, st>>>(p); break;
+    case 5: add_layernorm_bwd_kernel<5, MINTB_LN_BWD_PER_SM><<<grid, 160, 0, st>>>(p); break;
+    default: add_layernorm_bwd_kernel<10, 1><<<grid, 320, 0, st>>>(p); break;
   }
-#undef MINTB_LN_BWD
+  cudaError_t e = cudaSuccess;
   if (e != cudaSuccess) return fail("mintb_add_layernorm_bwd", e);
   count_launches(1);
   if (norm) {
@@ -536,9 +571,12 @@ int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, in
     cudaError_t e = cudaMemsetAsync(db, 0, size_t(N) * sizeof(float), st);
     if (e != cudaSuccess) return fail("mintb_gelu_bwd_colsum memset", e);
   }
-  dim3 grid((N + 255) / 256, (M + kColRows - 1) / kColRows);
-  gelu_bwd_colsum_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(z),
-                                               static_cast<__nv_bfloat16*>(dz), db, M, N);
+  dim3 grid((N + 255) / 256, (M + kSumRows - 1) / kSumRows);
+  if (z != nullptr)
+    gelu_bwd_colsum_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(z),
+                                                       static_cast<__nv_bfloat16*>(dz), db, M, N);
+  else
+    gelu_bwd_colsum_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), nullptr, nullptr, db, M, N);
   count_launches(1);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? MINTB_OK : fail("mintb_gelu_bwd_colsum launch", e);

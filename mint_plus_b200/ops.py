@@ -346,6 +346,23 @@ def quantize_e4m3(x: torch.Tensor, scale: float) -> torch.Tensor:
     return out
 
 
+_shared_q = None   # (x, key, e4m3 copy) of the last activation quantised for a fused QKV projection
+
+
+def _quantize_shared(x2d: torch.Tensor, scale: float) -> torch.Tensor:
+    """quantize_e4m3 with a one-entry memo: the self and the cross pathway of a layer project the SAME activation, and
+    with equal activation scales (what `calibrate_fp8` measures on one tensor) the second projection reuses the first's
+    e4m3 copy.  The entry keeps its source tensor alive, so a matching address, version counter and stream mean the same
+    values."""
+    global _shared_q
+    key = (x2d.data_ptr(), x2d._version, tuple(x2d.shape), float(scale), _stream())
+    if _shared_q is not None and _shared_q[1] == key:
+        return _shared_q[2]
+    out = quantize_e4m3(x2d, scale)
+    _shared_q = (x2d, key, out)
+    return out
+
+
 def gemm_e4m3(xq: torch.Tensor, wq: torch.Tensor, alpha: float, bias=None, gelu: bool = False,
               out_e4m3_scale: Optional[float] = None, save_preact: bool = False):
     """act(alpha * xq @ wq.T + bias) with e4m3 operands; bf16 result, or e4m3 (result / out_e4m3_scale, saturated).
@@ -575,7 +592,7 @@ class _QkvFn(torch.autograd.Function):
             w_used = _lora_merged(w, lora_a, lora_b, lora_scaling)
             a_op, b_op, in_dt, alpha = x2d, (w_used if w_used.dtype == torch.bfloat16 else w_used.to(torch.bfloat16)).contiguous(), L.BF16, 1.0
         else:               # e4m3 operands, one scale per tensor; the product of the scales is folded into alpha
-            a_op, b_op, in_dt, alpha = quantize_e4m3(x2d, x_scale), wq, L.E4M3, float(x_scale) * float(w_scale) * float(out_scale)
+            a_op, b_op, in_dt, alpha = _quantize_shared(x2d, x_scale), wq, L.E4M3, float(x_scale) * float(w_scale) * float(out_scale)
         # packed: positions without a token are never written, and keys there are masked but still multiplied by a zero
         # probability, so they must hold finite numbers
         alloc = torch.zeros if pack is not None else torch.empty

@@ -63,6 +63,39 @@ def test_add_layernorm_forward_and_backward(E, mode):
         assert (norm.bias.grad.float() - b32.grad).abs().max().item() <= 2e-2 * b32.grad.abs().max().item() + 1e-2
 
 
+@pytest.mark.parametrize("E", [320, 1280, 2560])
+def test_add_layernorm_backward_walks_many_rows(E):
+    """More rows than one sweep of the backward grid holds (a CTA takes several batches of rows, the last one ragged)."""
+    torch.manual_seed(7)
+    rows = 10007
+    x = _bf(torch.randn(rows, E, device=DEV)).requires_grad_(True)
+    r = _bf(torch.randn(rows, E, device=DEV)).requires_grad_(True)
+    a, b = math.sqrt(0.7), math.sqrt(0.3)
+    norm = torch.nn.LayerNorm(E).to(DEV, torch.bfloat16)
+    with torch.no_grad():
+        norm.weight.copy_(1 + 0.1 * torch.randn(E))
+    s, y = ops.add_layernorm(x, r, a, b, norm, need_s=True)
+    gs, gy = torch.randn(rows, E, device=DEV), torch.randn(rows, E, device=DEV)
+    ((s.float() * gs).sum() + (y.float() * gy).sum()).backward()
+    xf, rf = x.detach().float().requires_grad_(True), r.detach().float().requires_grad_(True)
+    w32, b32 = norm.weight.detach().float().requires_grad_(True), norm.bias.detach().float().requires_grad_(True)
+    sf = a * xf + b * rf
+    yf = torch.nn.functional.layer_norm(sf, (E,), w32, b32, norm.eps)
+    # the kernel receives the upstream gradients rounded to bf16
+    ((sf * _bf(gs).float()).sum() + (yf * _bf(gy).float()).sum()).backward()
+    for got, want in ((x.grad, xf.grad), (r.grad, rf.grad)):
+        assert (got.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-3
+    for got, want in ((norm.weight.grad, w32.grad), (norm.bias.grad, b32.grad)):
+        assert (got.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 5e-2
+    # fixed order of every sum: a second run gives the same bits
+    x2, r2 = x.detach().clone().requires_grad_(True), r.detach().clone().requires_grad_(True)
+    norm.weight.grad = None
+    norm.bias.grad = None
+    s2, y2 = ops.add_layernorm(x2, r2, a, b, norm, need_s=True)
+    ((s2.float() * gs).sum() + (y2.float() * gy).sum()).backward()
+    assert torch.equal(x2.grad, x.grad) and torch.equal(r2.grad, r.grad)
+
+
 def test_add_layernorm_rejects_unsupported_width():
     x = _bf(torch.randn(4, 4096, device=DEV))
     with pytest.raises(NotImplementedError):
