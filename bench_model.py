@@ -44,12 +44,18 @@ WORKLOADS = {
 }
 
 
-def make_pairs(cfg, rank=0):
-    g = torch.Generator().manual_seed(cfg["seed"] + 7919 * rank)
+def make_pairs(cfg, rank=0, world=1):
+    """Seeded synthetic pairs of the workload's length distribution.  One global list of world x pairs pairs comes from one
+    seed (the first `pairs` of it are the single-GPU batch); with several ranks the list is dealt so that every rank holds
+    `pairs` of them with about the same attention cost (squared unpadded length, `distributed.snake_shards`)."""
+    from mint_plus_b200.distributed import snake_shards
+    g = torch.Generator().manual_seed(cfg["seed"])
     B, T = cfg["pairs"], cfg["T"]
-    tokens = torch.full((B, T), 1, dtype=torch.int64)
-    chain_ids = torch.zeros(B, T, dtype=torch.int64)
-    for b in range(B):
+    n = B * world
+    tokens = torch.full((n, T), 1, dtype=torch.int64)
+    chain_ids = torch.zeros(n, T, dtype=torch.int64)
+    cost = []
+    for b in range(n):
         la = int(torch.randint(cfg["lo"], cfg["hi"] + 1, (1,), generator=g))
         lb = int(torch.randint(cfg.get("lo2", cfg["lo"]), cfg.get("hi2", cfg["hi"]) + 1, (1,), generator=g))
         a = torch.randint(4, 24, (la,), generator=g)
@@ -57,7 +63,11 @@ def make_pairs(cfg, rank=0):
         row = torch.cat([torch.tensor([0]), a, torch.tensor([2, 0]), c, torch.tensor([2])])
         tokens[b, :row.numel()] = row
         chain_ids[b, la + 2:] = 1
-    return tokens, chain_ids
+        cost.append(float(row.numel()) ** 2)
+    if world == 1:
+        return tokens, chain_ids
+    mine = torch.tensor(snake_shards(cost, world)[rank])
+    return tokens[mine].contiguous(), chain_ids[mine].contiguous()
 
 
 def build_model(cfg, device):
@@ -190,11 +200,12 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
     dev = torch.device("cuda", local)
     steps, warmup = (steps or args.steps), max(args.warmup, 3)
     model = build_model(cfg, dev)
-    tokens, chain_ids = make_pairs(cfg, rank)
+    tokens, chain_ids = make_pairs(cfg, rank, world)
     h_tok, h_cid = tokens.pin_memory(), chain_ids.pin_memory()
     h_lab = None
     flops_step, flops_gemm, flops_attn = algorithmic_flops(cfg, tokens)
     trainable = [p for p in model.parameters() if p.requires_grad] if cfg["train"] else []
+    # one all-reduce (average) of the trainable gradients after the backward pass, on a flat buffer filled by one multi-tensor copy
     sync_grads = FlatGradAllReduce(trainable, dtype=torch.float32 if cfg["kind"] == "lora" else torch.bfloat16) \
         if (cfg["train"] and world > 1) else None
     lib = L.lib()
@@ -315,7 +326,9 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
                 "config": {"workload": cfg["desc"] + " per GPU", "l2": "working set per step far exceeds L2 (no flush)",
                            "launch": "eager", "checkpointing": ("per layer" if getattr(model, "last_forward_checkpointed", False) else
                                              "off (activations of all layers fit in HBM)") if cfg["train"] else "none",
-                           "grad_allreduce_bytes": sync_grads.nbytes if sync_grads is not None else 0},
+                           "grad_allreduce_bytes": sync_grads.nbytes if sync_grads is not None else 0,
+                           "dealing": "one seeded list of n_gpus x pairs, dealt to ranks in equal counts by squared length (snake order)"
+                           if world > 1 else "single batch"},
                 "roofline": roof,
                 "e2e": {"value": pairs_total * e2e_steps / (e2e_ms * 1e-3), "unit": "pairs/s", "h2d_bytes_per_step": h2d,
                         "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},

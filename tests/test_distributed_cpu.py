@@ -3,11 +3,14 @@ flat all-reduce, timings reduce by max.  Two `gloo` ranks, spawned as child proc
 import os
 import socket
 
+import pytest
+
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from mint_plus_b200.distributed import (FlatGradAllReduce, balanced_shards, reduce_max, reduce_sum, shard_indices)
+from mint_plus_b200.distributed import (FlatGradAllReduce, BucketedGradAllReduce, balanced_shards, reduce_max, reduce_sum,
+                                        shard_indices, snake_shards)
 from mint_plus_b200.lora import LoRALinear, apply_lora
 
 
@@ -62,6 +65,61 @@ def test_two_ranks_average_trainable_gradients_over_disjoint_shards(tmp_path):
     assert r0["tsum"] == [6.0]
 
 
+def _overlap_worker(rank, world, port, out_dir, with_unused, overlap):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.Tanh(), torch.nn.Linear(8, 8), torch.nn.Linear(8, 4))
+        unused = torch.nn.Parameter(torch.ones(3))             # never reached by the loss: counts as a zero gradient
+        params = list(model.parameters()) + ([unused] if with_unused else [])
+        # small buckets, filled in reverse registration order: `unused` shares the first one, which therefore only goes out in finish()
+        sync = BucketedGradAllReduce(params, bucket_bytes=140, overlap=overlap)
+        data = torch.arange(6 * 8, dtype=torch.float32).view(6, 8) / 10.0
+        mine = shard_indices(6, rank, world)
+        results = []
+        launched_in_backward = []
+        for step in range(2):                                  # the second step checks that the state resets
+            for p in params:
+                p.grad = None
+            model(data[mine] * (step + 1)).square().sum().backward()
+            launched_in_backward.append(sum(b.launched for b in sync.buckets))
+            sync.finish()
+            results.append([p.grad.clone() for p in params])
+        views = all(p.grad.data_ptr() == sync._where[p][1].data_ptr() for p in params)
+        torch.save({"grads": results, "views": views, "n_buckets": len(sync.buckets), "nbytes": sync.nbytes,
+                    "launched_in_backward": launched_in_backward},
+                   os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("with_unused,overlap", [(False, True), (True, True), (False, False)])
+def test_two_ranks_bucketed_gradient_average(tmp_path, with_unused, overlap):
+    world = 2
+    mp.spawn(_overlap_worker, args=(world, _free_port(), str(tmp_path), with_unused, overlap), nprocs=world, join=True)
+    r0, r1 = (torch.load(tmp_path / f"rank{r}.pt") for r in range(world))
+    assert r0["n_buckets"] >= 3 and r0["views"] and r1["views"]
+    assert r0["nbytes"] == 4 * ((3 if with_unused else 0) + 2 * (64 + 8) + 32 + 4)
+    # with every gradient arriving, all buckets are on the wire before backward() returns; a parameter without a gradient
+    # holds its bucket (and, to keep one order on all ranks, the later ones) back until finish()
+    assert r0["launched_in_backward"] == ([0, 0] if (with_unused or not overlap) else [r0["n_buckets"]] * 2)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.Tanh(), torch.nn.Linear(8, 8), torch.nn.Linear(8, 4))
+    data = torch.arange(6 * 8, dtype=torch.float32).view(6, 8) / 10.0
+    for step in range(2):
+        want = None
+        for r in range(world):
+            model.zero_grad()
+            model(data[shard_indices(6, r, world)] * (step + 1)).square().sum().backward()
+            g = [p.grad.clone() for p in model.parameters()]
+            want = g if want is None else [a + b for a, b in zip(want, g)]
+        want = [w / world for w in want] + ([torch.zeros(3)] if with_unused else [])
+        for got0, got1, w in zip(r0["grads"][step], r1["grads"][step], want):
+            torch.testing.assert_close(got0, w)
+            torch.testing.assert_close(got1, w)
+
+
 def test_balanced_shards_even_out_skewed_costs():
     lengths = [1900, 30, 1800, 40, 900, 950, 50, 60]
     shards = balanced_shards([l * l for l in lengths], 2)
@@ -69,6 +127,18 @@ def test_balanced_shards_even_out_skewed_costs():
     loads = [sum(lengths[i] ** 2 for i in s) for s in shards]
     assert max(loads) / min(loads) < 1.35
     assert balanced_shards([1, 1, 1], 4)[3] == []
+
+
+def test_snake_shards_give_equal_counts_and_even_costs():
+    g = torch.Generator().manual_seed(3)
+    lengths = torch.randint(200, 1800, (128,), generator=g).tolist()
+    costs = [float(l) ** 2 for l in lengths]
+    shards = snake_shards(costs, 8)
+    assert sorted(i for s in shards for i in s) == list(range(128)) and all(len(s) == 16 for s in shards)
+    loads = [sum(costs[i] for i in s) for s in shards]
+    naive = [sum(costs[i] for i in shard_indices(128, r, 8)) for r in range(8)]
+    assert max(loads) / min(loads) < 1.05 < max(naive) / min(naive)
+    assert snake_shards([3.0, 1.0, 2.0], 1) == [[0, 1, 2]]
 
 
 def test_lora_adapter_freezes_base_and_matches_the_formula():
