@@ -136,6 +136,16 @@ MINTB_API int mintb_attn_bwd(const void* q_self, const void* k_self, const void*
                    void* dk_self, void* dv_self, void* dq_cross, void* dk_cross, void* dv_cross, void* workspace,
                    size_t workspace_bytes, int B, int H, int T, int D, int dtype, unsigned flags, float scale,
                    void* stream, int* dev_status);
+/* mintb_attn_bwd for callers whose token-wise tensors hold only the unpadded tokens (the reference pads every batch to
+ * its longest pair, data/data.py:63-129, and has no such mode).  With MINTB_FLAG_GRAD_ROWMAJOR the two gradient matrices
+ * then have one row per kept token, [n_rows][3E]: token_row[t*B + b] (int32, device) is the row of token (t, b), negative
+ * for a token without a row, whose gradients are dropped.  token_row == NULL is mintb_attn_bwd. */
+MINTB_API int mintb_attn_bwd_rows(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
+                   const void* k_cross, const void* v_cross, const void* meta, const float* rope_cos,
+                   const float* rope_sin, const void* out, const float* lse, const void* d_out, void* dq_self,
+                   void* dk_self, void* dv_self, void* dq_cross, void* dk_cross, void* dv_cross, void* workspace,
+                   size_t workspace_bytes, int B, int H, int T, int D, int dtype, unsigned flags, float scale,
+                   void* stream, int* dev_status, const int32_t* token_row);
 
 /* ---------------------------------------------------------------------------------------------------
  * Combine from materialised logits.  Replaces fused_multimer_combine / fused_multimer_combine_bwd

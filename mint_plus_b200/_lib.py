@@ -35,6 +35,8 @@ PROTOTYPES = {
     "mintb_attn_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_uint]),
     "mintb_attn_bwd": (c_int, [_P] * 6 + [_P, _P, _P, _P, _P, _P] + [_P] * 6 + [_P, c_size_t, c_int, c_int, c_int, c_int,
                                c_int, c_uint, c_float, _P, _P]),
+    "mintb_attn_bwd_rows": (c_int, [_P] * 6 + [_P, _P, _P, _P, _P, _P] + [_P] * 6 + [_P, c_size_t, c_int, c_int, c_int, c_int,
+                                    c_int, c_uint, c_float, _P, _P, _P]),
     "mintb_linear_fwd": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P, _P]),
     "mintb_qkv_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P, _P, _P, c_int,
                               _P, _P]),

@@ -205,12 +205,12 @@ int mintb_attn_fwd(const void* q_self, const void* k_self, const void* v_self, c
   return e == cudaSuccess ? MINTB_OK : cuda_fail(e, "attention forward launch");
 }
 
-int mintb_attn_bwd(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
-                   const void* k_cross, const void* v_cross, const void* meta, const float* rope_cos,
-                   const float* rope_sin, const void* out, const float* lse, const void* d_out, void* dq_self,
-                   void* dk_self, void* dv_self, void* dq_cross, void* dk_cross, void* dv_cross, void* workspace,
-                   size_t workspace_bytes, int B, int H, int T, int D, int dtype, unsigned flags, float scale,
-                   void* stream, int* dev_status) {
+int mintb_attn_bwd_rows(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
+                        const void* k_cross, const void* v_cross, const void* meta, const float* rope_cos,
+                        const float* rope_sin, const void* out, const float* lse, const void* d_out, void* dq_self,
+                        void* dk_self, void* dv_self, void* dq_cross, void* dk_cross, void* dv_cross, void* workspace,
+                        size_t workspace_bytes, int B, int H, int T, int D, int dtype, unsigned flags, float scale,
+                        void* stream, int* dev_status, const int32_t* token_row) {
   AttnArgs a{};
   size_t need = mintb_attn_bwd_workspace_bytes(B, H, T, D, dtype, flags);
   int rc = fill_common(a, "mintb_attn_bwd", q_self, k_self, v_self, q_cross, k_cross, v_cross, meta, rope_cos,
@@ -223,6 +223,11 @@ int mintb_attn_bwd(const void* q_self, const void* k_self, const void* v_self, c
       return MINTB_EINVAL;
     }
   }
+  if (token_row != nullptr && !a.grad_rowmajor) {
+    set_error("mintb_attn_bwd_rows: a token-row map needs MINTB_FLAG_GRAD_ROWMAJOR");
+    return MINTB_EINVAL;
+  }
+  a.token_row = token_row;
   a.out = const_cast<void*>(out);
   a.lse = const_cast<float*>(lse);
   a.d_out = d_out;
@@ -230,6 +235,17 @@ int mintb_attn_bwd(const void* q_self, const void* k_self, const void* v_self, c
   if (use_tc(D, dtype, flags)) return launch_attn_bwd_tc(a);
   cudaError_t e = launch_attn_bwd_simt(a);
   return e == cudaSuccess ? MINTB_OK : cuda_fail(e, "attention backward launch");
+}
+
+int mintb_attn_bwd(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
+                   const void* k_cross, const void* v_cross, const void* meta, const float* rope_cos,
+                   const float* rope_sin, const void* out, const float* lse, const void* d_out, void* dq_self,
+                   void* dk_self, void* dv_self, void* dq_cross, void* dk_cross, void* dv_cross, void* workspace,
+                   size_t workspace_bytes, int B, int H, int T, int D, int dtype, unsigned flags, float scale,
+                   void* stream, int* dev_status) {
+  return mintb_attn_bwd_rows(q_self, k_self, v_self, q_cross, k_cross, v_cross, meta, rope_cos, rope_sin, out, lse, d_out,
+                             dq_self, dk_self, dv_self, dq_cross, dk_cross, dv_cross, workspace, workspace_bytes, B, H, T,
+                             D, dtype, flags, scale, stream, dev_status, nullptr);
 }
 
 int mintb_combine_fwd(const void* intra_logits, const void* inter_logits, const uint8_t* chain_mask,

@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __rest
                                                              __nv_bfloat16* __restrict__ dq_s, __nv_bfloat16* __restrict__ dq_c,
                                                              const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
                                                              size_t rows, int T, int D, float scale, int H, size_t g_row,
-                                                             size_t g_b, size_t g_h) {
+                                                             size_t g_b, size_t g_h, const int32_t* __restrict__ token_row, int B) {
   const int h = D / 2, cpr = h / 8;
   const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= rows * cpr) return;
@@ -170,9 +170,16 @@ __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __rest
 #pragma unroll
   for (int which = 0; which < 2; ++which) {
     const float* src = (which == 0 ? acc_s : acc_c) + row * D + c * 8;
-    // accumulators are [b][h][t][D]; the result goes to ptr + t * g_row + b * g_b + h * g_h (+ column)
+    // accumulators are [b][h][t][D]; the result goes to ptr + t * g_row + b * g_b + h * g_h (+ column), or, with a token
+    // map, to row token_row[t * B + b] of the row-major matrix (g_b is its row length); tokens without a row are dropped
     const size_t bh_ = row / T;
-    __nv_bfloat16* dst = (which == 0 ? dq_s : dq_c) + size_t(t) * g_row + (bh_ / H) * g_b + (bh_ % H) * g_h + c * 8;
+    size_t base = size_t(t) * g_row + (bh_ / H) * g_b;
+    if (token_row != nullptr) {
+      const int tr = __ldg(token_row + size_t(t) * B + bh_ / H);
+      if (tr < 0) return;
+      base = size_t(tr) * g_b;
+    }
+    __nv_bfloat16* dst = (which == 0 ? dq_s : dq_c) + base + (bh_ % H) * g_h + c * 8;
     *reinterpret_cast<float4*>(lo) = *reinterpret_cast<const float4*>(src);
     *reinterpret_cast<float4*>(lo + 4) = *reinterpret_cast<const float4*>(src + 4);
     *reinterpret_cast<float4*>(hi) = *reinterpret_cast<const float4*>(src + h);
@@ -239,6 +246,8 @@ struct BwdParams {
   int do_seq_first;                // dO is laid out (T,B,H,D): its tensor map takes (0, bh, t) instead of (0, t, bh)
   int skip_pad_queries;            // query tiles that hold only padded positions are left out
   size_t g_row, g_b, g_h;          // element strides of dk / dv: between keys, batch entries, heads
+  const int32_t* token_row;        // row of the row-major gradient matrices per token t * B + b (negative: none), or null
+  int B;
 };
 
 // ring counter with phase bit: position in [0, N), phase flips on wrap
@@ -313,7 +322,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     for (int idx = tid; idx < kBwdTile * (D / 8); idx += kBwdThreads) {
       const int row = idx / (D / 8), vec = idx % (D / 8);
       if (k0 + row < p.T) {
-        const size_t off = size_t(k0 + row) * p.g_row + size_t(b) * p.g_b + size_t(bh % p.H) * p.g_h + vec * 8;
+        size_t base = size_t(k0 + row) * p.g_row + size_t(b) * p.g_b;
+        if (p.token_row != nullptr) {
+          const int tr = __ldg(p.token_row + size_t(k0 + row) * p.B + b);
+          if (tr < 0) continue;
+          base = size_t(tr) * p.g_b;
+        }
+        const size_t off = base + size_t(bh % p.H) * p.g_h + vec * 8;
         *reinterpret_cast<uint4*>(p.dk[path] + off) = make_uint4(0u, 0u, 0u, 0u);
         *reinterpret_cast<uint4*>(p.dv[path] + off) = make_uint4(0u, 0u, 0u, 0u);
       }
@@ -635,7 +650,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
 #pragma unroll
           for (int j = 0; j < hD; ++j) lo[j] = hi[j] = 0.f;
         }
-        if (kj < p.T) {
+        bool has_row = kj < p.T;
+        size_t g_base = size_t(kj) * p.g_row + size_t(b) * p.g_b;
+        if (has_row && p.token_row != nullptr) {
+          const int tr = __ldg(p.token_row + size_t(kj) * p.B + b);
+          has_row = tr >= 0;
+          g_base = size_t(tr < 0 ? 0 : tr) * p.g_b;
+        }
+        if (has_row) {
           float outv[hD];
           if (is_dk) {
             const bool rot = path == 0 && p.cos_tab != nullptr;
@@ -658,8 +680,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
 #pragma unroll
             for (int d = 0; d < hD; ++d) outv[d] = half_col == 0 ? lo[d] : hi[d];
           }
-          __nv_bfloat16* dst = (is_dk ? p.dk[path] : p.dv[path]) + size_t(kj) * p.g_row + size_t(b) * p.g_b +
-                               size_t(bh % p.H) * p.g_h + half_col * hD;
+          __nv_bfloat16* dst = (is_dk ? p.dk[path] : p.dv[path]) + g_base + size_t(bh % p.H) * p.g_h + half_col * hD;
 #pragma unroll
           for (int j = 0; j < hD; j += 8)
             *reinterpret_cast<uint4*>(dst + j) = make_uint4(bwd_pack(outv[j], outv[j + 1]), bwd_pack(outv[j + 2], outv[j + 3]),
@@ -731,6 +752,7 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const f
   p.do_seq_first = a.out_seq_first ? 1 : 0;
   p.skip_pad_queries = a.skip_pad_queries ? 1 : 0;
   p.g_row = grad_row_stride(a); p.g_b = grad_b_stride(a); p.g_h = grad_h_stride(a);
+  p.token_row = a.token_row; p.B = a.B;
   dim3 grid((a.T + kBwdTile - 1) / kBwdTile, BH, 2);
   attn_bwd_tc_kernel<D, SQ><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, mdq_s, mdq_c, p);
   count_launches(1);
@@ -786,7 +808,7 @@ int launch_attn_bwd_tc(const AttnArgs& a) {
     bwd_dq_convert_kernel<<<unsigned((n + 255) / 256), 256, 0, a.stream>>>(
         acc_s, acc_c, static_cast<__nv_bfloat16*>(a.dq_s), static_cast<__nv_bfloat16*>(a.dq_c),
         a.rope ? a.rope_cos : nullptr, a.rope ? a.rope_sin : nullptr, rows, a.T, a.D, a.scale, a.H, grad_row_stride(a),
-        grad_b_stride(a), grad_h_stride(a));
+        grad_b_stride(a), grad_h_stride(a), a.token_row, a.B);
     count_launches(1);
   }
   e = cudaGetLastError();

@@ -78,6 +78,8 @@ struct AttnArgs {
   bool skip_pad_queries;             // query tiles holding only padded positions are left out
   bool qk_prerotated;                // q_self / k_self arrive rotated; only the gradients are (un-)rotated
   bool grad_rowmajor;                // gradients go into [T*B][3E] row-major matrices
+  const int32_t* token_row;          // with grad_rowmajor: row of those matrices that belongs to token t*B + b, negative = none
+                                     // (the matrices then hold only the listed rows); null = row t*B + b
   float scale;
   cudaStream_t stream;
   int* dev_status;

@@ -180,39 +180,54 @@ class _MultimerAttentionFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, d_out):
-        q_s, k_s, v_s, q_c, k_c, v_c, out, lse, cos, sin = ctx.saved_tensors
-        B, H, T, D = q_s.shape
-        dt = _DTYPES[q_s.dtype]
-        lib = L.lib()
-        d_out = d_out.contiguous()
-        flags = ctx.flags
-        rowmajor = ctx.grad_tabs is not None
-        if rowmajor:
-            # The inputs came from the fused QKV products (q, k of the self pathway already rotated there): the gradients are
-            # written straight into the [T*B][3E] matrices those products' backward passes consume — un-rotated, no gather pass.
-            E = H * D
-            g_s, g_c = (torch.empty(T * B, 3 * E, dtype=q_s.dtype, device=q_s.device) for _ in range(2))
-            grads = [g_s[:, :E], g_s[:, E:2 * E], g_s[:, 2 * E:], g_c[:, :E], g_c[:, E:2 * E], g_c[:, 2 * E:]]
-            if ctx.grad_tabs[0] is not None:
-                cos, sin = ctx.grad_tabs
-                flags |= L.FLAG_ROPE | L.FLAG_QK_PREROTATED
-            flags |= L.FLAG_GRAD_ROWMAJOR
-        else:
-            grads = [torch.empty_like(q_s) for _ in range(6)]
-        ws_bytes = lib.mintb_attn_bwd_workspace_bytes(B, H, T, D, dt, flags)
-        if ctx.fwd_ws is not None:
-            ws, ws_bytes, flags = ctx.fwd_ws, ctx.fwd_ws.numel(), flags | L.FLAG_ROT_SAVED
-        else:
-            ws = _workspace(ws_bytes, q_s.device)
-        with torch.cuda.device(q_s.device):
-            rc = lib.mintb_attn_bwd(_ptr(q_s), _ptr(k_s), _ptr(v_s), _ptr(q_c), _ptr(k_c), _ptr(v_c), _ptr(ctx.meta.buf),
-                                    _ptr(cos), _ptr(sin), _ptr(out), _ptr(lse), _ptr(d_out), *[_ptr(g) for g in grads],
-                                    _ptr(ws), ws_bytes, B, H, T, D, dt, flags, ctx.scale, _stream(),
-                                    _ptr(_dev_status(q_s.device)))
-        L.check(rc, "mintb_attn_bwd")
-        if rowmajor:   # hand each gradient back as the (B,H,T,D) view of its third of the row-major matrix
-            grads = [g.view(T, B, H, D).permute(1, 2, 0, 3) for g in grads]
+        grads, _, _ = _attention_backward(ctx, d_out)
         return (*grads, None, None, None, None, None, None)
+
+
+def _attention_backward(ctx, d_out, pack=None):
+    """Backward pass of `_MultimerAttentionFn` for a context `ctx` of its forward pass.  Returns (the six gradients as
+    (B,H,T,D) tensors or views, g_self, g_cross); the last two are the row-major [rows][3E] matrices [dQ | dK | dV] when the
+    context asked for them (`grad_tabs`), else None.  With `pack` those matrices hold only the unpadded tokens' rows (the
+    kernels drop the others), and the six per-tensor gradients are not formed (None)."""
+    q_s, k_s, v_s, q_c, k_c, v_c, out, lse, cos, sin = ctx.saved_tensors
+    B, H, T, D = q_s.shape
+    dt = _DTYPES[q_s.dtype]
+    lib = L.lib()
+    d_out = d_out.contiguous()
+    flags = ctx.flags
+    rowmajor = ctx.grad_tabs is not None
+    g_s = g_c = None
+    if rowmajor:
+        # The inputs came from the fused QKV products (q, k of the self pathway already rotated there): the gradients are
+        # written straight into the [rows][3E] matrices those products' backward passes consume — un-rotated, no gather pass.
+        E = H * D
+        n_rows = pack.n if pack is not None else T * B
+        g_s, g_c = (torch.empty(n_rows, 3 * E, dtype=q_s.dtype, device=q_s.device) for _ in range(2))
+        grads = [g_s[:, :E], g_s[:, E:2 * E], g_s[:, 2 * E:], g_c[:, :E], g_c[:, E:2 * E], g_c[:, 2 * E:]]
+        if ctx.grad_tabs[0] is not None:
+            cos, sin = ctx.grad_tabs
+            flags |= L.FLAG_ROPE | L.FLAG_QK_PREROTATED
+        flags |= L.FLAG_GRAD_ROWMAJOR
+    else:
+        if pack is not None:
+            raise ValueError("packed gradient rows need the row-major gradient layout")
+        grads = [torch.empty_like(q_s) for _ in range(6)]
+    ws_bytes = lib.mintb_attn_bwd_workspace_bytes(B, H, T, D, dt, flags)
+    if ctx.fwd_ws is not None:
+        ws, ws_bytes, flags = ctx.fwd_ws, ctx.fwd_ws.numel(), flags | L.FLAG_ROT_SAVED
+    else:
+        ws = _workspace(ws_bytes, q_s.device)
+    with torch.cuda.device(q_s.device):
+        rc = lib.mintb_attn_bwd_rows(_ptr(q_s), _ptr(k_s), _ptr(v_s), _ptr(q_c), _ptr(k_c), _ptr(v_c), _ptr(ctx.meta.buf),
+                                     _ptr(cos), _ptr(sin), _ptr(out), _ptr(lse), _ptr(d_out), *[_ptr(g) for g in grads],
+                                     _ptr(ws), ws_bytes, B, H, T, D, dt, flags, ctx.scale, _stream(),
+                                     _ptr(_dev_status(q_s.device)), _ptr(pack.inv32) if pack is not None else None)
+    L.check(rc, "mintb_attn_bwd")
+    if pack is not None:
+        grads = [None] * 6
+    elif rowmajor:   # hand each gradient back as the (B,H,T,D) view of its third of the row-major matrix
+        grads = [g.view(T, B, H, D).permute(1, 2, 0, 3) for g in grads]
+    return grads, g_s, g_c
 
 
 def multimer_attention(q_self, k_self, v_self, q_cross, k_cross, v_cross, *, meta: Optional[MaskMeta] = None,
@@ -402,10 +417,11 @@ def _gelu_erf_grad(z: torch.Tensor) -> torch.Tensor:
     return 0.5 * (1.0 + torch.erf(zf * 0.7071067811865476)) + zf * torch.exp(-0.5 * zf * zf) * 0.3989422804014327
 
 
-def linear_backward(dy, x2d, w, bias, z, needs, out_scale: float = 1.0, db=None):
+def linear_backward(dy, x2d, w, bias, z, needs, out_scale: float = 1.0, db=None, dx_accum=None):
     """Gradients of y = act(out_scale * x W^T + b): the GELU derivative and the bias gradient come from one fused pass
     (or the bias gradient is handed in as `db` by the pass that produced dy); dgrad and wgrad are plain library GEMMs on
-    bf16 (the static output multiplier is folded into the small operand)."""
+    bf16 (the static output multiplier is folded into the small operand).  `dx_accum`: a tensor of dx's shape that the input
+    gradient is ADDED to in place by the dgrad product itself (two projections of one activation: no separate add pass)."""
     want_db = bias is not None and needs[2]
     if db is not None:
         dz = dy
@@ -414,7 +430,8 @@ def linear_backward(dy, x2d, w, bias, z, needs, out_scale: float = 1.0, db=None)
     wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
     dx = dw = None
     if needs[0]:
-        dx = dz @ (wb * out_scale if out_scale != 1.0 else wb)
+        w_eff = wb * out_scale if out_scale != 1.0 else wb
+        dx = dz @ w_eff if dx_accum is None else dx_accum.addmm_(dz, w_eff)
     if needs[1]:
         dw = dz.t() @ x2d
         if out_scale != 1.0:
@@ -463,6 +480,9 @@ class PackInfo:
         self.rows64 = torch.nonzero(keep, as_tuple=False).squeeze(1)
         self.rows32 = self.rows64.to(torch.int32)
         self.T, self.B, self.n = T, B, int(self.rows64.numel())
+        # the inverse: packed row of token t * B + b, -1 where the position holds no token
+        self.inv32 = torch.full((T * B,), -1, dtype=torch.int32, device=padding_mask.device)
+        self.inv32[self.rows64] = torch.arange(self.n, dtype=torch.int32, device=padding_mask.device)
 
 
 # ----------------------------------------------------------------------------------------------- residual + LayerNorm
@@ -615,30 +635,113 @@ class _QkvFn(torch.autograd.Function):
         x2d, w, bias, cos, sin, lora_a, lora_b = ctx.saved_tensors
         T, B, H, D, q_scale, out_scale = ctx.dims
         E = H * D
-        # (B,H,T,D) x3 -> [T*B, 3E] with the rotation undone and the q scale applied, in one pass
         pack = ctx.pack
         n_rows = x2d.shape[0]
         want_db = bias is not None and ctx.needs_input_grad[2]
         g = _rowmajor_base(dq, dk, dv, T, B, H, D) if (pack is None and q_scale == 1.0) else None
-        if g is not None:
-            # the attention backward pass has already written [dQ | dK | dV] row-major (and un-rotated): no gather pass
-            w_used = _lora_merged(w, lora_a, lora_b, ctx.lora_scaling)
-            dx, dw, db = linear_backward(g, x2d, w_used, bias, None, ctx.needs_input_grad, out_scale)
-            d_a, d_b = _lora_grads(g, x2d, lora_a, lora_b, ctx.lora_scaling, E, ctx.needs_input_grad[12] or ctx.needs_input_grad[13])
-            return ((dx.view(ctx.x_shape) if dx is not None else None), dw, db, None, None, None, None, None, None, None, None, None,
-                    d_a, d_b, None)
-        g = torch.empty(n_rows, 3 * E, dtype=torch.bfloat16, device=x2d.device)
-        db = torch.empty(3 * E, dtype=torch.float32, device=x2d.device) if want_db else None
-        with torch.cuda.device(x2d.device):
-            rc = L.lib().mintb_qkv_grad_pack(_ptr(dq.contiguous()), _ptr(dk.contiguous()), _ptr(dv.contiguous()), _ptr(g), _ptr(db),
-                                             _ptr(cos), _ptr(sin), _ptr(pack.rows32) if pack is not None else None, n_rows,
-                                             T, B, H, D, float(q_scale), _stream())
-        L.check(rc, "mintb_qkv_grad_pack")
-        w_used = _lora_merged(w, lora_a, lora_b, ctx.lora_scaling)
-        dx, dw, db = linear_backward(g, x2d, w_used, bias, None, ctx.needs_input_grad, out_scale, db=db)
-        d_a, d_b = _lora_grads(g, x2d, lora_a, lora_b, ctx.lora_scaling, E, ctx.needs_input_grad[12] or ctx.needs_input_grad[13])
-        return ((dx.view(ctx.x_shape) if dx is not None else None), dw, db, None, None, None, None, None, None, None, None, None,
-                d_a, d_b, None)
+        db = None
+        if g is None:
+            # (B,H,T,D) x3 -> [rows, 3E] with the rotation undone and the q scale applied, in one pass
+            g = torch.empty(n_rows, 3 * E, dtype=torch.bfloat16, device=x2d.device)
+            db = torch.empty(3 * E, dtype=torch.float32, device=x2d.device) if want_db else None
+            with torch.cuda.device(x2d.device):
+                rc = L.lib().mintb_qkv_grad_pack(_ptr(dq.contiguous()), _ptr(dk.contiguous()), _ptr(dv.contiguous()), _ptr(g), _ptr(db),
+                                                 _ptr(cos), _ptr(sin), _ptr(pack.rows32) if pack is not None else None, n_rows,
+                                                 T, B, H, D, float(q_scale), _stream())
+            L.check(rc, "mintb_qkv_grad_pack")
+        # else: the attention backward pass has already written [dQ | dK | dV] row-major (and un-rotated): no gather pass
+        dx, dw, db, d_a, d_b = _qkv_backward_from_g(ctx, g, db)
+        return (dx, dw, db, None, None, None, None, None, None, None, None, None, d_a, d_b, None)
+
+
+def _qkv_backward_from_g(ctx, g, db=None, dx_accum=None):
+    """Gradients of one fused QKV projection (context `ctx` of `_QkvFn.forward`) from the row-major gradient matrix
+    g = [dQ | dK | dV] of its output: (dx shaped like the input, dW, dbias, dA, dB of the LoRA adapters)."""
+    x2d, w, bias, _, _, lora_a, lora_b = ctx.saved_tensors
+    T, B, H, D, q_scale, out_scale = ctx.dims
+    needs = ctx.needs_input_grad
+    w_used = _lora_merged(w, lora_a, lora_b, ctx.lora_scaling)
+    dx, dw, db = linear_backward(g, x2d, w_used, bias, None, needs, out_scale, db=db,
+                                 dx_accum=dx_accum.view(x2d.shape) if dx_accum is not None else None)
+    d_a, d_b = _lora_grads(g, x2d, lora_a, lora_b, ctx.lora_scaling, H * D, needs[12] or needs[13])
+    return (dx.view(ctx.x_shape) if dx is not None else None), dw, db, d_a, d_b
+
+
+class _SubCtx:
+    """Stand-in for an autograd context when one Function runs the forward and backward code of another as plain calls."""
+
+    def __init__(self, needs_input_grad):
+        self.needs_input_grad = tuple(needs_input_grad)
+        self.saved_tensors = ()
+
+    def save_for_backward(self, *tensors):
+        self.saved_tensors = tensors
+
+
+class _QkvAttentionFn(torch.autograd.Function):
+    """Both fused QKV projections of a layer and its two-pathway attention as ONE differentiable step: x -> attention output.
+
+    Between the three products nothing but the kernels' own layouts exists: q, k, v head-major from the GEMM epilogues, and
+    on the way back the attention kernels write [dQ | dK | dV] of each pathway row-major (only the unpadded tokens' rows when
+    packed), which the dgrad / wgrad products read as they are; the second pathway's input gradient is accumulated into the
+    first's by its own product."""
+
+    @staticmethod
+    def forward(ctx, x, w_s, b_s, la_s, lb_s, w_c, b_c, la_c, lb_c, H, cos, sin, q_scale, fp8_s, fp8_c, ls_s, ls_c, pack,
+                meta, scale, flags):
+        n = ctx.needs_input_grad
+        f = (False,) * 9
+        cs = _SubCtx((n[0], n[1], n[2]) + f + (n[3], n[4], False))
+        cc = _SubCtx((n[0], n[5], n[6]) + f + (n[7], n[8], False))
+        ca = _SubCtx((any(n[:9]),) * 6 + (False,) * 6)
+        q_s, k_s, v_s = _QkvFn.forward(cs, x, w_s, b_s, H, cos, sin, q_scale, *fp8_s, pack, la_s, lb_s, ls_s)
+        q_c, k_c, v_c = _QkvFn.forward(cc, x, w_c, b_c, H, None, None, q_scale, *fp8_c, pack, la_c, lb_c, ls_c)
+        out = _MultimerAttentionFn.forward(ca, q_s, k_s, v_s, q_c, k_c, v_c, meta, None, None, scale, flags, (cos, sin))
+        ctx.subs = (cs, cc, ca)
+        ctx.counts = tuple(len(c.saved_tensors) for c in ctx.subs)
+        ctx.save_for_backward(*cs.saved_tensors, *cc.saved_tensors, *ca.saved_tensors)
+        for c in ctx.subs:
+            c.saved_tensors = ()
+        ctx.pack = pack
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        cs, cc, ca = ctx.subs
+        saved, off = ctx.saved_tensors, 0
+        for c, k in zip(ctx.subs, ctx.counts):
+            c.saved_tensors = saved[off:off + k]
+            off += k
+        _, g_s, g_c = _attention_backward(ca, d_out, ctx.pack)
+        dx, dw_s, db_s, da_s, dlb_s = _qkv_backward_from_g(cs, g_s)
+        dx2, dw_c, db_c, da_c, dlb_c = _qkv_backward_from_g(cc, g_c, dx_accum=dx)
+        for c in ctx.subs:
+            c.saved_tensors = ()
+        return (dx if dx is not None else dx2, dw_s, db_s, da_s, dlb_s, dw_c, db_c, da_c, dlb_c) + (None,) * 12
+
+
+def qkv_attention(x: torch.Tensor, proj_self, proj_cross, num_heads: int, meta: "MaskMeta", rope=None, scale: float = 1.0,
+                  sqrt_softmax: bool = False, pack=None, skip_pad_queries: bool = False) -> torch.Tensor:
+    """Attention output (T,B,H,D) of a layer from its input x (T,B,E) (or the packed rows of one, with `pack`): both fused
+    QKV projections (`qkv_project`'s arithmetic; `proj_*` = (weight (3E,E), bias, fp8 operands or None, lora or None)) and
+    `multimer_attention` on their head-major results, differentiable as one step (attention.py:87-117,188-323 and
+    modules.py:94-154 of the reference).  `rope` = (cos, sin) rotates q, k of the self pathway in the GEMM epilogue;
+    `scale` multiplies the logits of both pathways inside the attention kernels.  Head sizes 16, 32, 64."""
+    if x.dtype != torch.bfloat16 or not x.is_cuda or (pack is None and x.dim() != 3):
+        raise TypeError("qkv_attention takes a (T, B, E) bfloat16 CUDA tensor (or the packed rows of one, with `pack`)")
+    cos, sin = rope if rope is not None else (None, None)
+
+    def unpack(proj):
+        w, b, fp8, lora = proj
+        la, lb, ls = lora if lora is not None else (None, None, 1.0)
+        return w, b, la, lb, (fp8 if fp8 is not None else (None, 1.0, 1.0, 1.0)), ls
+
+    w_s, b_s, la_s, lb_s, f_s, ls_s = unpack(proj_self)
+    w_c, b_c, la_c, lb_c, f_c, ls_c = unpack(proj_cross)
+    flags = (L.FLAG_OUT_SEQ_FIRST | (L.FLAG_SQRT_SOFTMAX if sqrt_softmax else 0)
+             | (L.FLAG_SKIP_PAD_QUERIES if skip_pad_queries else 0))
+    return _QkvAttentionFn.apply(x, w_s, b_s, la_s, lb_s, w_c, b_c, la_c, lb_c, num_heads, cos, sin, 1.0, f_s, f_c, ls_s, ls_c,
+                                 pack, meta, float(scale), int(flags))
 
 
 def qkv_project(x: torch.Tensor, weight: torch.Tensor, bias, num_heads: int, rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,

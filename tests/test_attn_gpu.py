@@ -327,3 +327,55 @@ def test_sequence_first_output_layout(shape, dtype, force_simt):
             torch.testing.assert_close(a, b, rtol=0, atol=0)          # deterministic kernels: bit-equal
         else:
             assert (a.float() - b.float()).abs().max().item() <= 1e-2 * b.float().abs().max().item() + 1e-6   # dQ atomics reorder
+
+
+@pytest.mark.parametrize("sqrt_sm", [False, True])
+@pytest.mark.parametrize("shape", [(2, 3, 300, 64), (3, 2, 200, 32), (2, 2, 130, 16)])
+def test_backward_writes_row_major_gradients_and_packed_rows(shape, sqrt_sm):
+    """MINTB_FLAG_QK_PREROTATED + MINTB_FLAG_GRAD_ROWMAJOR: for q, k of the self pathway rotated by the caller, the backward
+    pass writes [dQ | dK | dV] of each pathway straight into a [T*B][3E] matrix, un-rotating dq_self / dk_self, and the
+    values equal those of the ordinary call on the un-rotated tensors.  With a token-row map (mintb_attn_bwd_rows) only the
+    unpadded tokens' rows exist, and they hold the same numbers."""
+    B, H, T, D = shape
+    E = H * D
+    ts, cid, pad, grad = O.make_op_inputs(B, H, T, D, seed=11 + T, max_pad=T // 3)
+    kw = dict(chain_ids=cid.to(DEV), key_padding_mask=pad.to(DEV), sqrt_softmax=sqrt_sm)
+    dt = torch.bfloat16
+    leaves = [t.to(DEV, dt).requires_grad_(True) for t in ts]
+    out = M.multimer_attention(*leaves, **kw)                                  # rotates inside, scale D^-0.5
+    g = grad.to(DEV, dt)
+    want = torch.autograd.grad(out, leaves, g)
+
+    cos, sin, _ = ops.rope_tables(T, D, torch.device(DEV))
+    def rot(x):                                                                # rotary_embedding.py:16-24 on fp32 tables
+        xf = x.float()
+        x1, x2 = xf[..., : D // 2], xf[..., D // 2:]
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(dt)
+    pre = [rot(leaves[0].detach()), rot(leaves[1].detach())] + [t.detach() for t in leaves[2:]]
+    pre = [t.contiguous().requires_grad_(True) for t in pre]
+    out2 = M.multimer_attention(*pre, rope=False, scale=D ** -0.5, out_seq_first=True, grad_rowmajor_tabs=(cos, sin), **kw)
+    assert (out2.permute(1, 2, 0, 3).float() - out.float()).abs().max().item() <= 2e-2 * max(1.0, out.float().abs().max().item())
+    got = torch.autograd.grad(out2, pre, g.permute(2, 0, 1, 3).contiguous())
+    ops.check_device_status()
+    g_s = ops._rowmajor_base(got[0], got[1], got[2], T, B, H, D)
+    g_c = ops._rowmajor_base(got[3], got[4], got[5], T, B, H, D)
+    assert g_s is not None and g_c is not None and tuple(g_s.shape) == (T * B, 3 * E)
+    for a, b, n in zip(got, want, ("dq_s", "dk_s", "dv_s", "dq_c", "dk_c", "dv_c")):
+        err, scale = (a.float() - b.float()).abs().max().item(), b.float().abs().max().item()
+        assert err <= 3e-2 * scale + 1e-5, f"{n}: {err:.4g} vs scale {scale:.4g}"
+
+    # the same backward pass with a token-row map: rows of the unpadded tokens only
+    pack = ops.PackInfo(pad.to(DEV))
+    meta = ops.mask_meta_from_chain_ids(cid.to(DEV), pad.to(DEV))
+    flags = ops.L.FLAG_OUT_SEQ_FIRST | (ops.L.FLAG_SQRT_SOFTMAX if sqrt_sm else 0)
+    ctx = ops._SubCtx((True,) * 6 + (False,) * 6)
+    with torch.no_grad():
+        out3 = ops._MultimerAttentionFn.forward(ctx, *[t.detach() for t in pre], meta, None, None, D ** -0.5, flags, (cos, sin))
+        _, p_s, p_c = ops._attention_backward(ctx, g.permute(2, 0, 1, 3).contiguous(), pack)
+    ops.check_device_status()
+    torch.testing.assert_close(out3, out2, rtol=0, atol=0)
+    assert tuple(p_s.shape) == (pack.n, 3 * E) and pack.n < T * B
+    for packed, full in ((p_s, g_s), (p_c, g_c)):
+        ref = full.index_select(0, pack.rows64)
+        torch.testing.assert_close(packed[:, E:], ref[:, E:], rtol=0, atol=0)            # dK, dV: fixed-order sums
+        assert (packed[:, :E].float() - ref[:, :E].float()).abs().max().item() <= 1e-2 * ref[:, :E].float().abs().max().item() + 1e-6
