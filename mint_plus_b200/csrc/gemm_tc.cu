@@ -182,6 +182,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bulk_commit_group();
       }
     };
+    // Head-major outputs: the 32 columns (64 bytes) of a row go to one place of q / k / v, rows lie far apart.  Staged like
+    // above and read back so that four neighbouring lanes write the four 16-byte pieces of one row: every store instruction
+    // covers whole 64-byte runs (eight rows) instead of one 16-byte piece of each of 32 rows.  `row_off` is this lane's row
+    // offset in elements (negative: row not stored), `col_off` what the chunk adds; HD = 16 splits the chunk over two heads
+    // (`head_step` elements apart).
+    auto scatter_store32 = [&](__nv_bfloat16* base, const float (&val)[32], long long row_off, size_t col_off, size_t head_step) {
+      // (the head-major kernels issue no bulk stores, so nothing else reads the staging rows)
+#pragma unroll
+      for (int j = 0; j < 32; j += 8)
+        *reinterpret_cast<uint4*>(my_out + swizzled_offset(lane, j / 8, 64)) =
+            make_uint4(pack_bf16x2(val[j], val[j + 1]), pack_bf16x2(val[j + 2], val[j + 3]), pack_bf16x2(val[j + 4], val[j + 5]),
+                       pack_bf16x2(val[j + 6], val[j + 7]));
+      __syncwarp();
+      const int piece = lane % 4;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = i * 8 + lane / 4;
+        const long long ro = __shfl_sync(0xffffffffu, row_off, r);
+        const uint4 q = *reinterpret_cast<const uint4*>(my_out + swizzled_offset(r, piece, 64));
+        if (ro >= 0) {
+          const size_t within = HD == 16 ? size_t(piece / 2) * head_step + size_t(piece % 2) * 8 : size_t(piece) * 8;
+          *reinterpret_cast<uint4*>(base + size_t(ro) + col_off + within) = q;
+        }
+      }
+      __syncwarp();
+    };
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     uint32_t ab = 0, ab_phase = 0;
     bool ok = true;
@@ -196,11 +222,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_after();
       const uint32_t tacc = tbase + lane_base + ab * kGN;
       int hm_b = 0, hm_t = 0;   // head-major: decode the row once
+      long long hm_row = -1;    // element offset of (b, head 0, t, 0) in q / k / v, negative for rows past M
       if constexpr (EPI == kEpiHeadMajor) {
         // rows past M (the ragged last tile) compute on token 0 and are not stored: their table reads stay in range
         const int mo = m < p.M ? (p.row_map != nullptr ? p.row_map[m] : m) : 0;
         hm_t = mo / p.B;
         hm_b = mo % p.B;
+        if (m < p.M) hm_row = (static_cast<long long>(hm_b) * p.H * p.T + hm_t) * HD;
       }
 #pragma unroll 1
       for (int c0 = chalf * (kGN / 2); c0 < (chalf + 1) * (kGN / 2); c0 += 32) {
@@ -241,17 +269,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
               }
             }
-            if (m < p.M) {
-#pragma unroll
-              for (int h0 = 0; h0 < 32; h0 += HD) {
-                __nv_bfloat16* dst = p.qkv[which] + ((size_t(hm_b) * p.H + (e + h0) / HD) * p.T + hm_t) * HD;
-#pragma unroll
-                for (int j = 0; j < HD; j += 8)
-                  *reinterpret_cast<uint4*>(dst + j) =
-                      make_uint4(pack_bf16x2(v[h0 + j], v[h0 + j + 1]), pack_bf16x2(v[h0 + j + 2], v[h0 + j + 3]),
-                                 pack_bf16x2(v[h0 + j + 4], v[h0 + j + 5]), pack_bf16x2(v[h0 + j + 6], v[h0 + j + 7]));
-              }
-            }
+            // the chunk starts at head e / HD (HD = 16: and covers the next one too), heads are T * HD elements apart
+            scatter_store32(p.qkv[which], v, hm_row, size_t(e / HD) * p.T * HD, size_t(p.T) * HD);
           } else {
             // HD = 64: this chunk is the lower or the upper half of one head; the rotation needs the partner half,
             // which is read from TMEM as well (same tile: pairs of chunks are 64-column aligned)
@@ -274,13 +293,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
               }
             }
-            if (m < p.M) {
-              __nv_bfloat16* dst = p.qkv[which] + ((size_t(hm_b) * p.H + e / 64) * p.T + hm_t) * 64 + (upper ? 32 : 0);
-#pragma unroll
-              for (int j = 0; j < 32; j += 8)
-                *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
-                                                                pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
-            }
+            scatter_store32(p.qkv[which], v, hm_row, size_t(e / 64) * p.T * 64 + (upper ? 32 : 0), 0);
           }
         } else {
           const int n = n0 + c0;
