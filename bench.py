@@ -146,7 +146,7 @@ def run_reference(args, rank, world):
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
             "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "isolated combined-softmax multimer attention fwd+bwd, B=8 H=20 D=32 T=1024",
+            "config": {"workload": "isolated combined-softmax multimer attention fwd+bwd, B=8 H=20 D=32 T=1024 per GPU",
                        "device": "cpu"},
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                              "sample": sample},

@@ -180,7 +180,7 @@ def run_reference(name, args, rank):
     line = {"impl": "reference", "metric": "ppi_pairs_per_sec", "value": base["value"], "unit": "pairs/s",
             "n_gpus": args.gpus, "steps": 1, "warmup": 1, "ms_per_step": 1e3 * cfg["pairs"] / base["value"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": cfg["desc"], "device": "cpu"}, "cpu_baseline": base,
+            "config": {"workload": cfg["desc"] + " per GPU", "device": "cpu"}, "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "pairs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
