@@ -420,7 +420,8 @@ def _gelu_erf_grad(z: torch.Tensor) -> torch.Tensor:
 def linear_backward(dy, x2d, w, bias, z, needs, out_scale: float = 1.0, db=None, dx_accum=None):
     """Gradients of y = act(out_scale * x W^T + b): the GELU derivative and the bias gradient come from one fused pass
     (or the bias gradient is handed in as `db` by the pass that produced dy); dgrad and wgrad are plain library GEMMs on
-    bf16 (the static output multiplier is folded into the small operand).  `dx_accum`: a tensor of dx's shape that the input
+    bf16 (the static output multiplier is folded into the small operand; as the alpha of an addmm with a broadcast first
+    argument it cost an extra pass over the result).  `dx_accum`: a tensor of dx's shape that the input
     gradient is ADDED to in place by the dgrad product itself (two projections of one activation: no separate add pass)."""
     want_db = bias is not None and needs[2]
     if db is not None:
