@@ -630,8 +630,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       tc_fence_after();
       MINTB_BTRACE_EV(46);
     }
+    ok = __all_sync(0xffffffffu, ok);   // the stores below exchange rows between the lanes of the warp
     if (ok) {
       constexpr int hD = D / 2;
+      constexpr int kPieces = hD / 8;   // 16-byte pieces of a thread's half row: 4, 2 or 1
+      if (kPieces > 1) {                // the staging rows of the dQ reductions are reused below
+        if (lane == 0) bulk_wait_read_all();
+        __syncwarp();
+      }
 #pragma unroll
       for (int v = 0; v < kVPG; ++v) {
         const int vg = grp * kVPG + v;
@@ -650,41 +656,62 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
 #pragma unroll
           for (int j = 0; j < hD; ++j) lo[j] = hi[j] = 0.f;
         }
-        bool has_row = kj < p.T;
-        size_t g_base = size_t(kj) * p.g_row + size_t(b) * p.g_b;
-        if (has_row && p.token_row != nullptr) {
-          const int tr = __ldg(p.token_row + size_t(kj) * p.B + b);
-          has_row = tr >= 0;
-          g_base = size_t(tr < 0 ? 0 : tr) * p.g_b;
+        // element offset of this thread's half row in dk / dv, negative when the key has no row (past T, or dropped token)
+        long long row_off = -1;
+        if (kj < p.T) {
+          row_off = static_cast<long long>(size_t(kj) * p.g_row + size_t(b) * p.g_b);
+          if (p.token_row != nullptr) {
+            const int tr = __ldg(p.token_row + size_t(kj) * p.B + b);
+            row_off = tr < 0 ? -1 : static_cast<long long>(size_t(tr) * p.g_b);
+          }
+          if (row_off >= 0) row_off += static_cast<long long>(size_t(bh % p.H) * p.g_h + half_col * hD);
         }
-        if (has_row) {
-          float outv[hD];
-          if (is_dk) {
-            const bool rot = path == 0 && p.cos_tab != nullptr;
-            if (rot) {   // R^T: dx_lo = dy_lo c + dy_hi s, dx_hi = dy_hi c - dy_lo s; table rows read 16 bytes at a time
-              const float4* c4 = reinterpret_cast<const float4*>(p.cos_tab + size_t(kj) * hD);
-              const float4* s4 = reinterpret_cast<const float4*>(p.sin_tab + size_t(kj) * hD);
+        float outv[hD];
+        if (is_dk) {
+          const bool rot = path == 0 && p.cos_tab != nullptr;
+          if (rot) {   // R^T: dx_lo = dy_lo c + dy_hi s, dx_hi = dy_hi c - dy_lo s; table rows read 16 bytes at a time
+            const float4* c4 = reinterpret_cast<const float4*>(p.cos_tab + size_t(krow) * hD);
+            const float4* s4 = reinterpret_cast<const float4*>(p.sin_tab + size_t(krow) * hD);
 #pragma unroll
-              for (int d = 0; d < hD; d += 4) {
-                const float4 cs = __ldg(c4 + d / 4), sn = __ldg(s4 + d / 4);
-                const float cv[4] = {cs.x, cs.y, cs.z, cs.w}, sv4[4] = {sn.x, sn.y, sn.z, sn.w};
+            for (int d = 0; d < hD; d += 4) {
+              const float4 cs = __ldg(c4 + d / 4), sn = __ldg(s4 + d / 4);
+              const float cv[4] = {cs.x, cs.y, cs.z, cs.w}, sv4[4] = {sn.x, sn.y, sn.z, sn.w};
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  outv[d + e] = (half_col == 0 ? lo[d + e] * cv[e] + hi[d + e] * sv4[e] : hi[d + e] * cv[e] - lo[d + e] * sv4[e]) * p.scale;
-              }
-            } else {
-#pragma unroll
-              for (int d = 0; d < hD; ++d) outv[d] = (half_col == 0 ? lo[d] : hi[d]) * p.scale;
+              for (int e = 0; e < 4; ++e)
+                outv[d + e] = (half_col == 0 ? lo[d + e] * cv[e] + hi[d + e] * sv4[e] : hi[d + e] * cv[e] - lo[d + e] * sv4[e]) * p.scale;
             }
           } else {
 #pragma unroll
-            for (int d = 0; d < hD; ++d) outv[d] = half_col == 0 ? lo[d] : hi[d];
+            for (int d = 0; d < hD; ++d) outv[d] = (half_col == 0 ? lo[d] : hi[d]) * p.scale;
           }
-          __nv_bfloat16* dst = (is_dk ? p.dk[path] : p.dv[path]) + g_base + size_t(bh % p.H) * p.g_h + half_col * hD;
+        } else {
+#pragma unroll
+          for (int d = 0; d < hD; ++d) outv[d] = half_col == 0 ? lo[d] : hi[d];
+        }
+        __nv_bfloat16* base = is_dk ? p.dk[path] : p.dv[path];
+        if constexpr (kPieces == 1) {
+          if (row_off >= 0)
+            *reinterpret_cast<uint4*>(base + row_off) = make_uint4(bwd_pack(outv[0], outv[1]), bwd_pack(outv[2], outv[3]),
+                                                                   bwd_pack(outv[4], outv[5]), bwd_pack(outv[6], outv[7]));
+        } else {
+          // Rows of different keys lie far apart (row-major gradients) or 2 hD elements apart: staged per warp and read back
+          // so that kPieces neighbouring lanes write one row's contiguous 16 hD bytes, a store instruction covers whole runs.
+          constexpr int kRowB = hD * 2;   // 64 or 32 bytes
 #pragma unroll
           for (int j = 0; j < hD; j += 8)
-            *reinterpret_cast<uint4*>(dst + j) = make_uint4(bwd_pack(outv[j], outv[j + 1]), bwd_pack(outv[j + 2], outv[j + 3]),
-                                                            bwd_pack(outv[j + 4], outv[j + 5]), bwd_pack(outv[j + 6], outv[j + 7]));
+            *reinterpret_cast<uint4*>(my_stage + swizzled_offset(lane, j / 8, kRowB)) =
+                make_uint4(bwd_pack(outv[j], outv[j + 1]), bwd_pack(outv[j + 2], outv[j + 3]), bwd_pack(outv[j + 4], outv[j + 5]),
+                           bwd_pack(outv[j + 6], outv[j + 7]));
+          __syncwarp();
+          const int piece = lane % kPieces;
+#pragma unroll
+          for (int i = 0; i < kPieces; ++i) {
+            const int r = i * (32 / kPieces) + lane / kPieces;
+            const long long ro = __shfl_sync(0xffffffffu, row_off, r);
+            const uint4 q = *reinterpret_cast<const uint4*>(my_stage + swizzled_offset(r, piece, kRowB));
+            if (ro >= 0) *reinterpret_cast<uint4*>(base + ro + piece * 8) = q;
+          }
+          __syncwarp();
         }
       }
     }
