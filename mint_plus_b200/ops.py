@@ -29,6 +29,23 @@ def _require_cuda(*tensors):
             raise RuntimeError("mint_plus_b200 operators run on CUDA tensors only (no CPU fallback)")
 
 
+class _NoCtx:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_CTX = _NoCtx()
+
+
+def _on(device):
+    """Context that makes `device` the current CUDA device for a library call; free when it already is (the usual case:
+    switching costs several microseconds of host time per call, and a training step makes thousands of calls)."""
+    return _NO_CTX if torch.cuda.current_device() == device.index else torch.cuda.device(device)
+
+
 def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
     # torch's caching allocator hands out 512-byte aligned blocks
     return torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
@@ -77,7 +94,7 @@ def mask_meta_from_chain_ids(chain_ids: torch.Tensor, key_padding_mask: Optional
     cid = chain_ids.to(torch.int32).contiguous()
     pad = _key_pad_u8(key_padding_mask, B, T)
     buf = torch.empty(L.lib().mintb_mask_meta_bytes(B, T), dtype=torch.uint8, device=cid.device)
-    with torch.cuda.device(cid.device):
+    with _on(cid.device):
         L.check(L.lib().mintb_mask_meta_from_chain_ids(_ptr(cid), _ptr(pad), _ptr(buf), B, T, _stream()),
                 "mask_meta_from_chain_ids")
     return MaskMeta(buf, B, T)
@@ -92,7 +109,7 @@ def mask_meta_from_mask(chain_mask: torch.Tensor, key_padding_mask: Optional[tor
     m = chain_mask.to(torch.uint8).contiguous() if chain_mask.dtype != torch.bool else chain_mask.contiguous().view(torch.uint8)
     pad = _key_pad_u8(key_padding_mask, B, T)
     buf = torch.empty(L.lib().mintb_mask_meta_bytes(B, T), dtype=torch.uint8, device=m.device)
-    with torch.cuda.device(m.device):
+    with _on(m.device):
         L.check(L.lib().mintb_mask_meta_from_mask(_ptr(m), _ptr(pad), _ptr(buf), B, T, _stream()), "mask_meta_from_mask")
     return MaskMeta(buf, B, T)
 
@@ -140,7 +157,7 @@ def rope_tables(T: int, D: int, device, inv_freq: Optional[torch.Tensor] = None)
         raise ValueError(f"inv_freq must have D/2 = {D // 2} entries")
     cos = torch.empty(T, D // 2, dtype=torch.float32, device=device)
     sin = torch.empty_like(cos)
-    with torch.cuda.device(device):
+    with _on(device):
         L.check(L.lib().mintb_rope_tables(_ptr(inv), _ptr(cos), _ptr(sin), T, D, _stream()), "rope_tables")
     if len(_rope_cache) > 16:
         _rope_cache.clear()
@@ -168,7 +185,7 @@ class _MultimerAttentionFn(torch.autograd.Function):
         else:
             ws = _workspace(ws_bytes, q_s.device)
         ctx.fwd_ws = ws if keep_ws else None
-        with torch.cuda.device(q_s.device):
+        with _on(q_s.device):
             rc = lib.mintb_attn_fwd(_ptr(q_s), _ptr(k_s), _ptr(v_s), _ptr(q_c), _ptr(k_c), _ptr(v_c), _ptr(meta.buf),
                                     _ptr(cos), _ptr(sin), _ptr(out), _ptr(lse), _ptr(ws), ws_bytes, B, H, T, D, dt,
                                     flags, scale, _stream(), _ptr(_dev_status(q_s.device)))
@@ -217,7 +234,7 @@ def _attention_backward(ctx, d_out, pack=None):
         ws, ws_bytes, flags = ctx.fwd_ws, ctx.fwd_ws.numel(), flags | L.FLAG_ROT_SAVED
     else:
         ws = _workspace(ws_bytes, q_s.device)
-    with torch.cuda.device(q_s.device):
+    with _on(q_s.device):
         rc = lib.mintb_attn_bwd_rows(_ptr(q_s), _ptr(k_s), _ptr(v_s), _ptr(q_c), _ptr(k_c), _ptr(v_c), _ptr(ctx.meta.buf),
                                      _ptr(cos), _ptr(sin), _ptr(out), _ptr(lse), _ptr(d_out), *[_ptr(g) for g in grads],
                                      _ptr(ws), ws_bytes, B, H, T, D, dt, flags, ctx.scale, _stream(),
@@ -284,7 +301,7 @@ class _CombineFn(torch.autograd.Function):
     def forward(ctx, il, el, mask_u8, iv, ev):
         B, H, T, D = iv.shape
         out = torch.empty_like(iv)
-        with torch.cuda.device(iv.device):
+        with _on(iv.device):
             rc = L.lib().mintb_combine_fwd(_ptr(il), _ptr(el), _ptr(mask_u8), _ptr(iv), _ptr(ev), _ptr(out), B, H, T, D,
                                           _DTYPES[iv.dtype], _stream())
         L.check(rc, "mintb_combine_fwd")
@@ -300,7 +317,7 @@ class _CombineFn(torch.autograd.Function):
         lib = L.lib()
         ws_bytes = lib.mintb_combine_bwd_workspace_bytes(B, H, T)
         ws = _workspace(ws_bytes, iv.device)
-        with torch.cuda.device(iv.device):
+        with _on(iv.device):
             rc = lib.mintb_combine_bwd(_ptr(il), _ptr(el), _ptr(mask_u8), _ptr(iv), _ptr(ev), _ptr(d_out), _ptr(d_il),
                                        _ptr(d_el), _ptr(d_iv), _ptr(d_ev), _ptr(ws), ws_bytes, B, H, T, D,
                                        _DTYPES[iv.dtype], _stream())
@@ -344,7 +361,7 @@ def gemm_bf16(x2d: torch.Tensor, w: torch.Tensor, bias=None, gelu: bool = False,
     b, bdt = _bias_arg(bias)
     out = torch.empty(M, N, dtype=torch.bfloat16, device=x2d.device)
     z = torch.empty(M, N, dtype=torch.bfloat16, device=x2d.device) if (gelu and save_preact) else None
-    with torch.cuda.device(x2d.device):
+    with _on(x2d.device):
         rc = L.lib().mintb_linear_fwd(_ptr(x2d), _ptr(w), _ptr(b), _ptr(out), _ptr(z), M, N, K, L.BF16, bdt, L.BF16, int(gelu),
                                       1.0, 1.0, _stream(), _ptr(_dev_status(x2d.device)))
     L.check(rc, "mintb_linear_fwd")
@@ -356,7 +373,7 @@ def quantize_e4m3(x: torch.Tensor, scale: float) -> torch.Tensor:
     _require_cuda(x)
     x = x.contiguous()
     out = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         L.check(L.lib().mintb_quantize_e4m3(_ptr(x), _ptr(out), x.numel(), 1.0 / scale, _stream()), "mintb_quantize_e4m3")
     return out
 
@@ -389,7 +406,7 @@ def gemm_e4m3(xq: torch.Tensor, wq: torch.Tensor, alpha: float, bias=None, gelu:
     to_f8 = out_e4m3_scale is not None
     out = torch.empty(M, N, dtype=torch.float8_e4m3fn if to_f8 else torch.bfloat16, device=xq.device)
     z = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device) if (gelu and save_preact) else None
-    with torch.cuda.device(xq.device):
+    with _on(xq.device):
         rc = L.lib().mintb_linear_fwd(_ptr(xq), _ptr(wq), _ptr(b), _ptr(out), _ptr(z), M, N, K, L.E4M3, bdt,
                                       L.E4M3 if to_f8 else L.BF16, int(gelu), float(alpha),
                                       1.0 / out_e4m3_scale if to_f8 else 1.0, _stream(), _ptr(_dev_status(xq.device)))
@@ -406,7 +423,7 @@ def gelu_bwd_colsum(dy: torch.Tensor, z: Optional[torch.Tensor], want_db: bool =
     db = torch.empty(N, dtype=torch.float32, device=dy.device) if want_db else None
     if z is None and not want_db:
         return dz, None
-    with torch.cuda.device(dy.device):
+    with _on(dy.device):
         rc = L.lib().mintb_gelu_bwd_colsum(_ptr(dy), _ptr(z), _ptr(dz) if z is not None else None, _ptr(db), M, N, _stream())
     L.check(rc, "mintb_gelu_bwd_colsum")
     return dz, db
@@ -502,7 +519,7 @@ class _AddLayerNormFn(torch.autograd.Function):
         y = torch.empty_like(x2) if norm else None
         stats = torch.empty(rows, 2, dtype=torch.float32, device=x.device) if norm else None
         pdt = _BIAS_DT[gamma.dtype] if norm else L.F32
-        with torch.cuda.device(x.device):
+        with _on(x.device):
             rc = L.lib().mintb_add_layernorm_fwd(_ptr(x2), _ptr(r2), float(a), float(b), _ptr(gamma), _ptr(beta), pdt, _ptr(s), _ptr(y),
                                                  _ptr(stats), rows, E, float(eps), _stream())
         L.check(rc, "mintb_add_layernorm_fwd")
@@ -530,7 +547,7 @@ class _AddLayerNormFn(torch.autograd.Function):
         lib = L.lib()
         wsb = lib.mintb_add_layernorm_bwd_workspace_bytes(rows, E) if norm else 0
         ws = torch.empty(wsb, dtype=torch.uint8, device=x2.device) if wsb else None
-        with torch.cuda.device(x2.device):
+        with _on(x2.device):
             rc = lib.mintb_add_layernorm_bwd(_ptr(dy2), _ptr(ds2), _ptr(x2), _ptr(r2), a, b, _ptr(gamma), pdt, _ptr(stats), _ptr(dx),
                                              _ptr(dr), _ptr(dgamma), _ptr(dbeta), _ptr(ws), wsb, rows, E, _stream())
         L.check(rc, "mintb_add_layernorm_bwd")
@@ -618,7 +635,7 @@ class _QkvFn(torch.autograd.Function):
         # probability, so they must hold finite numbers
         alloc = torch.zeros if pack is not None else torch.empty
         q, k, v = (alloc(B, H, T, D, dtype=torch.bfloat16, device=x.device) for _ in range(3))
-        with torch.cuda.device(x.device):
+        with _on(x.device):
             rc = L.lib().mintb_qkv_fwd(_ptr(a_op), _ptr(b_op), _ptr(b), _ptr(q), _ptr(k), _ptr(v), T, B, H, D, in_dt, bdt,
                                        float(alpha), float(q_scale), _ptr(cos), _ptr(sin),
                                        _ptr(pack.rows32) if pack is not None else None, x2d.shape[0], _stream(),
@@ -645,7 +662,7 @@ class _QkvFn(torch.autograd.Function):
             # (B,H,T,D) x3 -> [rows, 3E] with the rotation undone and the q scale applied, in one pass
             g = torch.empty(n_rows, 3 * E, dtype=torch.bfloat16, device=x2d.device)
             db = torch.empty(3 * E, dtype=torch.float32, device=x2d.device) if want_db else None
-            with torch.cuda.device(x2d.device):
+            with _on(x2d.device):
                 rc = L.lib().mintb_qkv_grad_pack(_ptr(dq.contiguous()), _ptr(dk.contiguous()), _ptr(dv.contiguous()), _ptr(g), _ptr(db),
                                                  _ptr(cos), _ptr(sin), _ptr(pack.rows32) if pack is not None else None, n_rows,
                                                  T, B, H, D, float(q_scale), _stream())
