@@ -142,6 +142,31 @@ def test_model_bf16_training_step_gives_finite_gradients():
         assert p.grad is not None and torch.isfinite(p.grad).all(), n
 
 
+@pytest.mark.gpu
+def test_checkpointed_layers_give_the_same_gradients():
+    """Per-layer activation checkpointing (esm2.py:117-127 of the reference always checkpoints) recomputes the fused
+    projection + attention step in the backward pass: same loss, and gradients equal up to the order of the dQ reductions."""
+    torch.manual_seed(0)
+    model = M.MINT(num_layers=2, embed_dim=320, attention_heads=20, use_multimer=True).cuda().to(torch.bfloat16).train()
+    tokens, chain_ids = c1_batch(13, 2, 256, 30, 100)
+    tokens, chain_ids = tokens.cuda(), chain_ids.cuda()
+    results = []
+    for ckpt in (False, True):
+        model.checkpoint_layers = ckpt
+        model.zero_grad(set_to_none=True)
+        out = model(tokens, chain_ids)["logits"]
+        loss = torch.nn.functional.cross_entropy(out.float().view(-1, 33), tokens.view(-1), ignore_index=1)
+        loss.backward()
+        assert model.last_forward_checkpointed == ckpt
+        results.append((loss.detach().clone(), {n: p.grad.detach().float().clone() for n, p in model.named_parameters()}))
+    ops.check_device_status()
+    (l0, g0), (l1, g1) = results
+    assert torch.equal(l0, l1)
+    for n in g0:
+        scale = g0[n].abs().max().item()
+        assert (g0[n] - g1[n]).abs().max().item() <= 2e-2 * scale + 1e-6, n
+
+
 def test_shared_step_masks_only_residues_and_gives_a_finite_loss(oracle_attention):
     """The MLM step of the reference wrapper (training/wrapper.py:48-86): targets are non-special positions only."""
     torch.manual_seed(3)
