@@ -586,13 +586,16 @@ def _lora_grads(g, x2d, lora_a, lora_b, scaling, E, wanted):
     dB = s g^T (x A^T), dA = s (g B)^T x."""
     if lora_a is None or not wanted:
         return None, None
-    g3 = g.view(-1, 3, E)
-    d_a, d_b = torch.empty_like(lora_a), torch.empty_like(lora_b)
-    for i in range(3):
-        gi = g3[:, i]
-        d_b[i] = ((gi.t() @ (x2d @ lora_a[i].to(x2d.dtype).t())) * scaling).to(lora_b.dtype)
-        d_a[i] = (((gi @ lora_b[i].to(x2d.dtype)).t() @ x2d) * scaling).to(lora_a.dtype)
-    return d_a, d_b
+    # four launches for the three adapters together: x A^T for all of them in one product, the two per-adapter products
+    # as batched ones on strided views of g (no copies of g), and (g B)^T x again as one product
+    M_, r = g.shape[0], lora_a.shape[1]
+    dt = x2d.dtype
+    g3 = g.view(M_, 3, E)
+    xa = (x2d @ lora_a.to(dt).reshape(3 * r, -1).t()).view(M_, 3, r)                 # [M, 3, r]
+    d_b = torch.bmm(g3.permute(1, 2, 0), xa.permute(1, 0, 2))                         # (3, E, M) x (3, M, r) -> (3, E, r)
+    gb = torch.bmm(g3.permute(1, 0, 2), lora_b.to(dt))                                # (3, M, E) x (3, E, r) -> (3, M, r)
+    d_a = (gb.permute(1, 0, 2).reshape(M_, 3 * r).t() @ x2d).view(3, r, -1)            # (3r, M) x (M, E) -> (3, r, E)
+    return (d_a * scaling).to(lora_a.dtype), (d_b * scaling).to(lora_b.dtype)
 
 
 def _rowmajor_base(dq, dk, dv, T, B, H, D):
