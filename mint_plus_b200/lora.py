@@ -36,6 +36,9 @@ class LoRALinear(nn.Module):
     def forward(self, x):
         from . import ops
         if x.is_cuda and x.dtype == torch.bfloat16 and type(self.base) is nn.Linear:
+            if isinstance(self.dropout, nn.Identity) or not self.training:
+                # one product on the merged weight (tcgen05 GEMM); the adapters' gradients come from thin products
+                return ops.lora_linear(x, self.base.weight, self.base.bias, self.lora_A, self.lora_B, self.scaling)
             y = ops.linear(x, self.base.weight, self.base.bias)       # frozen product on the tcgen05 GEMM
         else:
             y = self.base(x)

@@ -478,6 +478,47 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db, None
 
 
+class _LoraLinearFn(torch.autograd.Function):
+    """y = x (W + s B A)^T + b on ONE product with the merged weight; the adapters get their gradients through thin
+    products (dA = s (dy B)^T x, dB = s dy^T (x A^T)), the frozen W none unless it asks for one."""
+
+    @staticmethod
+    def forward(ctx, x2d, w, bias, lora_a, lora_b, scaling):
+        with torch.no_grad():
+            w_used = (w + scaling * (lora_b.to(w.dtype) @ lora_a.to(w.dtype))).to(torch.bfloat16).contiguous()
+        out = gemm_bf16(x2d, w_used, bias, False)
+        ctx.save_for_backward(x2d, w, bias, lora_a, lora_b)
+        ctx.scaling = float(scaling)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2d, w, bias, lora_a, lora_b = ctx.saved_tensors
+        s, needs, dt = ctx.scaling, ctx.needs_input_grad, x2d.dtype
+        dy = dy.contiguous()
+        dx = dw = db = d_a = d_b = None
+        if needs[0]:
+            dx = dy @ (w + s * (lora_b.to(w.dtype) @ lora_a.to(w.dtype))).to(dt)
+        if needs[1]:
+            dw = (dy.t() @ x2d).to(w.dtype)
+        if bias is not None and needs[2]:
+            db = gelu_bwd_colsum(dy, None, True)[1].to(bias.dtype)
+        if needs[3]:
+            d_a = (((dy @ lora_b.to(dt)).t() @ x2d) * s).to(lora_a.dtype)
+        if needs[4]:
+            d_b = ((dy.t() @ (x2d @ lora_a.to(dt).t())) * s).to(lora_b.dtype)
+        return dx, dw, db, d_a, d_b, None
+
+
+def lora_linear(x: torch.Tensor, weight: torch.Tensor, bias, lora_a: torch.Tensor, lora_b: torch.Tensor, scaling: float) -> torch.Tensor:
+    """A Linear with LoRA adapters A (r, in), B (out, r) for bf16 CUDA activations: x (W + scaling B A)^T + b; differentiable."""
+    if x.dtype != torch.bfloat16:
+        raise TypeError("ops.lora_linear takes bfloat16 activations")
+    x2d = x.reshape(-1, x.shape[-1]).contiguous()
+    y = _LoraLinearFn.apply(x2d, weight, bias, lora_a, lora_b, float(scaling))
+    return y.view(*x.shape[:-1], weight.shape[0])
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, gelu: bool = False) -> torch.Tensor:
     """nn.Linear forward (optionally followed by erf-GELU) for bf16 CUDA activations; differentiable."""
     if x.dtype != torch.bfloat16:

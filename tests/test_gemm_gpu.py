@@ -163,3 +163,24 @@ def test_bf16_layer_forward_backward_against_oracle_composition(fp8):
     assert (out.float().cpu() - want.detach()).abs().max().item() <= tol * scale
     assert (xg.grad.float().cpu() - wgx).abs().max().item() <= tol * wgx.abs().max().item() + 0.05
     layer.to("cpu").float()
+
+
+def test_lora_linear_on_the_merged_weight_matches_the_formula():
+    """y = x W^T + b + s (x A^T) B^T (lora.py / peft's LoRA) as one product on W + s B A, adapter gradients through thin
+    products: values and gradients against the fp32 formula."""
+    torch.manual_seed(4)
+    M_, K, N, r, s = 300, 320, 192, 8, 2.0
+    x = torch.randn(M_, K, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    b = (0.1 * torch.randn(N, device="cuda")).to(torch.bfloat16)
+    A = (torch.randn(r, K, device="cuda") / K ** 0.5).to(torch.bfloat16).requires_grad_(True)
+    B = (0.3 * torch.randn(N, r, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    y = ops.lora_linear(x, w, b, A, B, s)
+    gy = torch.randn(M_, N, device="cuda").to(torch.bfloat16)
+    gx, gA, gB = torch.autograd.grad(y, (x, A, B), gy)
+    xf, Af, Bf = (t.detach().float().requires_grad_(True) for t in (x, A, B))
+    yf = xf @ w.float().t() + b.float() + (xf @ Af.t()) @ Bf.t() * s
+    wx, wA, wB = torch.autograd.grad(yf, (xf, Af, Bf), gy.float())
+    assert (y.float() - yf).abs().max().item() <= 2e-2 * yf.abs().max().item()
+    for got, want in ((gx, wx), (gA, wA), (gB, wB)):
+        assert (got.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-3
