@@ -229,8 +229,9 @@ struct BwdCfg {
   static constexpr int kVPG = 16 / kCW;                         // 16-column query groups per thread and half (1 or 2)
   static constexpr int kDqWarpBytes = 32 * (D / 4) * 4;          // staging of one warp's dQ slice: 32 queries x D/4 fp32 columns
   static constexpr int kDqStageBytes = kCW * kDqWarpBytes;
+  static constexpr int kStatBytes = 128 * 8;                     // softmax statistics of one query tile: 128 x (-lse log2 e, -delta)
   static constexpr size_t kSmemBytes =
-      1024 + 2 * kTileBytes + size_t(kQStages) * 2 * kTileBytes + size_t(kNDq) * kDsBytes + kDqStageBytes + 4096;
+      1024 + 2 * kTileBytes + size_t(kQStages) * 2 * kTileBytes + size_t(kNDq) * kDsBytes + kDqStageBytes + kQStages * kStatBytes + 4096;
 };
 
 struct BwdParams {
@@ -277,7 +278,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   unsigned char* sQ = sV + Cfg::kTileBytes;                          // [stage][0: Q_i, 1: dO_i]
   unsigned char* sDS = sQ + size_t(kQStages) * 2 * Cfg::kTileBytes;  // [buf][half][128 rows x 128 B]
   unsigned char* sDqStage = sDS + size_t(kNDq) * Cfg::kDsBytes;      // [compute warp][32 queries][D/4 fp32], swizzled
-  unsigned char* tail = sDqStage + Cfg::kDqStageBytes;
+  unsigned char* sStats = sDqStage + Cfg::kDqStageBytes;             // [stage][64] x (nl0, nl1, nd0, nd1), loaded with the query tile
+  unsigned char* tail = sStats + size_t(kQStages) * Cfg::kStatBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
   uint64_t* kv_full = bars;            // 1
   uint64_t* acc_full = bars + 1;       // 1
@@ -457,7 +459,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         while (next_q < nqt && tq[next_q] == 0) ++next_q;
         if (next_q >= nqt) return;
         unsigned char* dst = sQ + size_t(lr.pos) * 2 * Cfg::kTileBytes;
-        mbar_expect_tx(&q_full[lr.pos], 2 * Cfg::kTileBytes);
+        mbar_expect_tx(&q_full[lr.pos], 2 * Cfg::kTileBytes + Cfg::kStatBytes);
+        bulk_load_1d(sStats + size_t(lr.pos) * Cfg::kStatBytes, p.stats + size_t(bh) * p.Tpad + size_t(next_q) * kBwdTile,
+                     Cfg::kStatBytes, &q_full[lr.pos]);
         tma_load_3d(dst, mq, &q_full[lr.pos], 0, next_q * kBwdTile, bh);
         if (p.do_seq_first) tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[lr.pos], 0, bh, next_q * kBwdTile);
         else tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[lr.pos], 0, next_q * kBwdTile, bh);
@@ -508,10 +512,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     const uint32_t* mrow = p.bitsT + (size_t(b) * p.T + krow) * p.TW;
     const uint32_t flip = path == 0 ? 0xffffu : 0u;   // keep-bit = mask bit XOR flip
     const uint64_t c22 = pack2(p.scale_log2, p.scale_log2);
-    const float4* stats_bh = reinterpret_cast<const float4*>(p.stats + size_t(bh) * p.Tpad);   // two queries per float4
     bool ok = true;
     int it = 0;
     Ring<kNBuf> br;
+    Ring<kQStages> sr;     // stage that holds the current tile's statistics
 
     // dQ of a tile leaves through shared memory: each compute warp stages its 32 queries x NC columns and one lane adds
     // them to the fp32 accumulator in HBM with ONE bulk reduction (instead of a 16-byte atomic per thread and 4 columns).
@@ -557,6 +561,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         MINTB_BTRACE_EV(40);
         ok = mbar_wait(&sdp_full[br.pos], br.phase, p.status, 0x602);
         if (!ok) break;
+        if (sub == 0) {   // the tile's loads have landed long ago (its products are done): this only orders the reads below
+          ok = mbar_wait(&q_full[sr.pos], sr.phase, p.status, 0x604);
+          if (!ok) break;
+        }
         if (it == 0 && sub == 0 && grp >= 2) __nanosleep(kBwdStaggerNs);
         MINTB_BTRACE_EV(41);
         tc_fence_after();
@@ -564,11 +572,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
 #pragma unroll
         for (int v = 0; v < kVPG; ++v) {
           const int vg = grp * kVPG + v;
-          // statistics of this thread's 16 queries (L1/L2 hits)
-          const float4* st = stats_bh + (i * kBwdTile + sub * kHalf + 16 * vg) / 2;
+          // statistics of this thread's 16 queries, from the copy that arrived in shared memory with the query tile
+          const float4* st = reinterpret_cast<const float4*>(sStats + size_t(sr.pos) * Cfg::kStatBytes) + (sub * kHalf + 16 * vg) / 2;
           float4 sq[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) sq[j] = __ldg(st + j);
+          for (int j = 0; j < 8; ++j) sq[j] = st[j];
           uint32_t keep = 0xffffu;
           if (f & 2) keep = ((__ldg(mrow + 4 * i + 2 * sub + vg / 2) >> (16 * (vg & 1))) & 0xffffu) ^ flip;
           if (!key_valid) keep = 0u;
@@ -618,6 +626,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       if (kNDq > 1 && prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
       MINTB_BTRACE_EV(45);
       prev_tile = i;
+      sr.advance();
       ++it;
     }
     if (ok && prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
