@@ -190,7 +190,7 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
     """Runs the workload on this rank; returns the JSON line (a dict) on rank 0 and None elsewhere."""
     import torch.distributed as dist
     from mint_plus_b200 import _lib as L, ops
-    from mint_plus_b200.distributed import FlatGradAllReduce, reduce_max, reduce_sum
+    from mint_plus_b200.distributed import ChunkedGradAllReduce, FlatGradAllReduce, reduce_max, reduce_sum
     from mint_plus_b200.training import shared_step
 
     cfg = dict(WORKLOADS[name])
@@ -206,8 +206,13 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
     flops_step, flops_gemm, flops_attn = algorithmic_flops(cfg, tokens)
     trainable = [p for p in model.parameters() if p.requires_grad] if cfg["train"] else []
     # one all-reduce (average) of the trainable gradients after the backward pass, on a flat buffer filled by one multi-tensor copy
-    sync_grads = FlatGradAllReduce(trainable, dtype=torch.float32 if cfg["kind"] == "lora" else torch.bfloat16) \
-        if (cfg["train"] and world > 1) else None
+    sync_grads = None
+    if cfg["train"] and world > 1:
+        gdt = torch.float32 if cfg["kind"] == "lora" else torch.bfloat16
+        if os.environ.get("MINTB_GRAD_CHUNKS", "0") != "0":   # a few large chunks, each sent as the backward pass leaves its layers
+            sync_grads = ChunkedGradAllReduce(model, n_chunks=int(os.environ["MINTB_GRAD_CHUNKS"]), dtype=gdt)
+        else:
+            sync_grads = FlatGradAllReduce(trainable, dtype=gdt)
     lib = L.lib()
     loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
     out_host = None
@@ -220,7 +225,7 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
             loss, _ = shared_step(model, (tok, cid))
             loss.backward()
             if sync_grads is not None:
-                sync_grads()
+                sync_grads.finish() if isinstance(sync_grads, ChunkedGradAllReduce) else sync_grads()
             return loss.detach()
         with torch.no_grad():
             res = model(tok, cid, repr_layers=[cfg["layers"]])

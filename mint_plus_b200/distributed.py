@@ -204,6 +204,117 @@ class BucketedGradAllReduce:
         self._handles = []
 
 
+class ChunkedGradAllReduce:
+    """Averages the trainable gradients of a model with a `layers` ModuleList in a few large chunks, each sent as soon as
+    the backward pass has left its layers: the layers are cut into `n_chunks` consecutive groups; a backward pre-hook on the
+    LAST layer before a group (it fires when the gradient with respect to that layer's output exists, i.e. when every later
+    layer has finished) gathers the group's gradients into its slice of one flat buffer with one multi-tensor copy and
+    issues the slice's all-reduce asynchronously (NCCL: on the communicator's stream, ordered after the copy).  Three or
+    four hook calls per step instead of one per parameter keep the host cost of the overlap negligible.  Parameters used
+    after the layers (final norm, LM head) ride with the first group, everything else (embeddings, tied weights) with the
+    last one, which `finish()` sends after `backward()` before it waits for all of them, divides, and leaves every `.grad`
+    a view of the buffer.  Not for activation checkpointing (the hooks would fire during recomputation)."""
+
+    def __init__(self, model: torch.nn.Module, n_chunks: int = 4, group=None, dtype: torch.dtype = torch.float32,
+                 after_layers: Sequence[str] = ("lm_head", "emb_layer_norm_after", "contact_head")):
+        layers = list(model.layers)
+        n_chunks = max(1, min(n_chunks, len(layers)))
+        self.group = group
+        # chunk c (in backward order) holds layers [bounds[c+1], bounds[c])
+        bounds = [len(layers) - (len(layers) * c) // n_chunks for c in range(n_chunks + 1)]
+        chunk_of_layer = {}
+        for c in range(n_chunks):
+            for li in range(bounds[c + 1], bounds[c]):
+                chunk_of_layer[li] = c
+        members: List[List[torch.nn.Parameter]] = [[] for _ in range(n_chunks)]
+        for name, p in model.named_parameters():
+            if not p.requires_grad:
+                continue
+            parts = name.split(".")
+            if parts[0] == "layers" and parts[1].isdigit():
+                members[chunk_of_layer[int(parts[1])]].append(p)
+            elif parts[0] in after_layers:
+                members[0].append(p)
+            else:
+                members[-1].append(p)
+        self.params = [p for m in members for p in m]
+        n = sum(p.numel() for p in self.params)
+        dev = self.params[0].device if self.params else torch.device("cpu")
+        self.flat = torch.zeros(n, dtype=dtype, device=dev)
+        self.chunks = []          # (params, views, flat slice)
+        off = 0
+        for m in members:
+            start, views = off, []
+            for p in m:
+                views.append(self.flat[off:off + p.numel()].view_as(p))
+                off += p.numel()
+            self.chunks.append((m, views, self.flat[start:off]))
+        self._sent = [False] * n_chunks
+        self._work = []
+        self._handles = []
+        for c in range(n_chunks - 1):          # chunk c is complete when the backward pass arrives at layer bounds[c+1] - 1
+            self._handles.append(layers[bounds[c + 1] - 1].register_full_backward_pre_hook(self._make_hook(c)))
+
+    @property
+    def nbytes(self) -> int:
+        return self.flat.numel() * self.flat.element_size()
+
+    def _world(self) -> int:
+        return dist.get_world_size(self.group) if dist.is_initialized() else 1
+
+    def _make_hook(self, c: int):
+        def hook(module, grad_output):
+            self._send(c, only_if_complete=True)
+            return None
+        return hook
+
+    @torch.no_grad()
+    def _send(self, c: int, only_if_complete: bool) -> None:
+        if self._sent[c] or (c > 0 and not self._sent[c - 1]):   # chunks leave in one order on every rank
+            return
+        params, views, piece = self.chunks[c]
+        if only_if_complete and any(p.grad is None for p in params):
+            return
+        have = [(p, v) for p, v in zip(params, views) if p.grad is not None and p.grad.data_ptr() != v.data_ptr()]
+        for p, v in zip(params, views):
+            if p.grad is None:
+                v.zero_()
+        if have:
+            torch._foreach_copy_([v for _, v in have], [p.grad for p, _ in have])
+        self._sent[c] = True
+        if self._world() > 1 and piece.numel():
+            self._work.append(dist.all_reduce(piece, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    @torch.no_grad()
+    def finish(self) -> int:
+        """After backward(): sends what has not left yet, waits, divides; every `.grad` becomes a view of the flat buffer
+        (a copy back only where the buffer's dtype differs).  Returns how many chunks had left during the backward pass."""
+        early = sum(self._sent)
+        for c in range(len(self.chunks)):
+            self._send(c, only_if_complete=False)
+        for w in self._work:
+            w.wait()
+        self._work = []
+        world = self._world()
+        if world > 1:
+            self.flat.div_(world)
+        for params, views, _ in self.chunks:
+            for p, v in zip(params, views):
+                if v.dtype == p.dtype:
+                    p.grad = v
+                elif p.grad is None:
+                    p.grad = v.to(p.dtype)
+                else:
+                    p.grad.copy_(v)
+        self._sent = [False] * len(self.chunks)
+        return early
+
+    def remove(self):
+        for h in self._handles:
+            h.remove()
+        self._handles = []
+
+
 def reduce_max(values: Sequence[float], device, group=None) -> List[float]:
     """Max over ranks of a few host scalars (timings)."""
     t = torch.tensor(list(values), dtype=torch.float64, device=device)

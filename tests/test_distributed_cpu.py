@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from mint_plus_b200.distributed import (FlatGradAllReduce, BucketedGradAllReduce, balanced_shards, reduce_max, reduce_sum,
+from mint_plus_b200.distributed import (FlatGradAllReduce, BucketedGradAllReduce, ChunkedGradAllReduce, balanced_shards, reduce_max, reduce_sum,
                                         shard_indices, snake_shards)
 from mint_plus_b200.lora import LoRALinear, apply_lora
 
@@ -127,6 +127,66 @@ def test_balanced_shards_even_out_skewed_costs():
     loads = [sum(lengths[i] ** 2 for i in s) for s in shards]
     assert max(loads) / min(loads) < 1.35
     assert balanced_shards([1, 1, 1], 4)[3] == []
+
+
+class _Stack(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.embed = torch.nn.Linear(8, 8)
+        self.layers = torch.nn.ModuleList([torch.nn.Linear(8, 8) for _ in range(5)])
+        self.lm_head = torch.nn.Linear(8, 4)
+        self.lm_head.weight = torch.nn.Parameter(self.lm_head.weight.detach().clone())
+
+    def forward(self, x):
+        x = self.embed(x)
+        for layer in self.layers:
+            x = torch.tanh(layer(x))
+        return self.lm_head(x)
+
+
+def _chunk_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        model = _Stack()
+        model.layers[1].bias.requires_grad_(False)
+        sync = ChunkedGradAllReduce(model, n_chunks=3)
+        data = torch.arange(6 * 8, dtype=torch.float32).view(6, 8) / 10.0
+        mine = shard_indices(6, rank, world)
+        results, early = [], []
+        for step in range(2):
+            for p in model.parameters():
+                p.grad = None
+            model(data[mine] * (step + 1)).square().sum().backward()
+            early.append(sync.finish())
+            results.append({n: p.grad.clone() for n, p in model.named_parameters() if p.requires_grad})
+        views = all(p.grad.untyped_storage().data_ptr() == sync.flat.untyped_storage().data_ptr()
+                    for p in model.parameters() if p.requires_grad)
+        torch.save({"grads": results, "early": early, "views": views}, os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_chunked_gradient_average_leaves_during_backward(tmp_path):
+    world = 2
+    mp.spawn(_chunk_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    r0, r1 = (torch.load(tmp_path / f"rank{r}.pt") for r in range(world))
+    assert r0["early"] == [2, 2] and r1["early"] == [2, 2] and r0["views"]      # two of three chunks left before finish()
+    torch.manual_seed(0)
+    model = _Stack()
+    data = torch.arange(6 * 8, dtype=torch.float32).view(6, 8) / 10.0
+    for step in range(2):
+        want = None
+        for r in range(world):
+            model.zero_grad()
+            model(data[shard_indices(6, r, world)] * (step + 1)).square().sum().backward()
+            g = {n: p.grad.clone() for n, p in model.named_parameters()}
+            want = g if want is None else {n: want[n] + g[n] for n in g}
+        for n, got in r0["grads"][step].items():
+            torch.testing.assert_close(got, want[n] / world)
+            torch.testing.assert_close(r1["grads"][step][n], want[n] / world)
+        assert "layers.1.bias" not in r0["grads"][step]
 
 
 def test_snake_shards_give_equal_counts_and_even_costs():
