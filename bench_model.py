@@ -129,7 +129,7 @@ def cpu_baseline(cfg, seconds_budget=25.0):
     oracle, fp32.  One layer on one pair is timed (forward, plus backward for training workloads) and scaled by layers x
     pairs — an extrapolation, stated as such."""
     import mint_plus_b200 as M
-    from mint_plus_b200 import modules_plus, ops
+    from mint_plus_b200 import ops
     from oracle import multimer_attention as O
     torch.set_num_threads(os.cpu_count() or 1)
     E_, H_, T = cfg["embed"], cfg["heads"], cfg["T"]

@@ -4,7 +4,6 @@ every computation runs in the CUDA library (there is no eager fallback).
 """
 from __future__ import annotations
 
-import math
 import weakref
 from typing import Optional, Tuple
 
