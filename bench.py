@@ -29,8 +29,8 @@ METRIC = "fused_multimer_attention_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # DRAM bytes (read + write) per launch of the dominant kernel (attn_bwd_tc_kernel<32> on this workload) from the ncu
-# capture summarised in profiles/attn_tc_kernels_B8_H20_T1024_D32.md: 121.5 MB read + 40.6 MB written.
-NCU_TRAFFIC_BYTES = 162.1e6
+# capture summarised in profiles/attn_tc_kernels_B8_H20_T1024_D32.md: 124.1 MB read + 45.5 MB written.
+NCU_TRAFFIC_BYTES = 169.5e6
 
 
 def algorithmic_flops(H, T, D, key_pad, fwd=True, bwd=True):
