@@ -200,6 +200,8 @@ MINTB_API int mintb_quantize_e4m3(const void* x, void* out, size_t n, float inv_
  *   dgamma / dbeta (fp32 [E]) summed in a fixed order through the workspace.
  * mintb_gelu_bwd_colsum: with z: dz = dy * gelu'(z) (erf form, modules.py:16-23) and db[N] = column sums of dz (db may be
  *   null); without z: db = column sums of dy (the bias gradient of a projection).  N a multiple of 8.
+ *   mintb_gelu_bwd_colsum_act also writes act = gelu(z) (bf16 [M][N], may be null) in the same pass: the forward pass of an
+ *   FFN whose fc1 hands its result to fc2 as e4m3 keeps only z, and fc2's weight gradient reads this copy.
  * mintb_qkv_grad_pack: the gradients of head-major q, k, v (B,H,T,D) gathered into one [T*B][3E] matrix with columns
  *   [dQ | dK | dV], dq multiplied by q_scale and dq, dk un-rotated (transpose of the RoPE rotation) when tables are given:
  *   the inverse of mintb_qkv_fwd's epilogue, feeding the dgrad / wgrad products of the fused QKV projection; a non-null
@@ -213,6 +215,8 @@ MINTB_API int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const v
                                       const void* gamma, int param_dtype, const float* stats, void* dx, void* dr, float* dgamma,
                                       float* dbeta, void* workspace, size_t workspace_bytes, int rows, int E, void* stream);
 MINTB_API int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, int M, int N, void* stream);
+MINTB_API int mintb_gelu_bwd_colsum_act(const void* dy, const void* z, void* dz, void* act, float* db, int M, int N,
+                                        void* stream);
 MINTB_API int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g, float* db, const float* rope_cos,
                                   const float* rope_sin, const int32_t* row_map, int n_rows, int T, int B, int H, int D,
                                   float q_scale, void* stream);

@@ -46,6 +46,7 @@ PROTOTYPES = {
     "mintb_add_layernorm_bwd": (c_int, [_P, _P, _P, _P, c_float, c_float, _P, c_int, _P, _P, _P, _P, _P, _P, c_size_t, c_int,
                                         c_int, _P]),
     "mintb_gelu_bwd_colsum": (c_int, [_P, _P, _P, _P, c_int, c_int, _P]),
+    "mintb_gelu_bwd_colsum_act": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, _P]),
     "mintb_qkv_grad_pack": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P]),
     "mintb_combine_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "mintb_combine_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),

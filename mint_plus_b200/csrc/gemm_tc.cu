@@ -44,6 +44,7 @@ struct GemmParams {
   const float *rope_cos, *rope_sin;   // [T][D/2]; rotate the q and k thirds when non-null
   const int32_t* row_map;             // packed input rows: row m of x is token row_map[m] = t * B + b (null: m itself)
   int use_bulk_store;          // bf16 row-major outputs leave through shared memory and bulk tensor stores
+  int use_bulk_f8;        // the e4m3 result leaves as bulk tensor stores too (32 x 32-byte boxes)
   int* status;
 };
 
@@ -175,6 +176,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         *reinterpret_cast<uint4*>(my_out + swizzled_offset(lane, j / 8, 64)) =
             make_uint4(pack_bf16x2(val[j], val[j + 1]), pack_bf16x2(val[j + 2], val[j + 3]), pack_bf16x2(val[j + 4], val[j + 5]),
                        pack_bf16x2(val[j + 6], val[j + 7]));
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(map, my_out, n, row0);
+        bulk_commit_group();
+      }
+    };
+    // the same for an e4m3 result: 32 rows x 32 bytes, rows unswizzled
+    auto bulk_store32_f8 = [&](const CUtensorMap* map, const float (&val)[32], int n, int row0) {
+      if (lane == 0) bulk_wait_read_all();
+      __syncwarp();
+      uint4 o[2];
+      __nv_fp8x2_storage_t* op = reinterpret_cast<__nv_fp8x2_storage_t*>(o);
+#pragma unroll
+      for (int j = 0; j < 32; j += 2)   // the conversion itself saturates at +-448
+        op[j / 2] = __nv_cvt_float2_to_fp8x2(make_float2(val[j] * p.out_scale, val[j + 1] * p.out_scale), __NV_SATFINITE, __NV_E4M3);
+      *reinterpret_cast<uint4*>(my_out + lane * 32) = o[0];
+      *reinterpret_cast<uint4*>(my_out + lane * 32 + 16) = o[1];
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
@@ -318,6 +337,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           if (p.use_bulk_store && p.out_dtype == MINTB_BF16) {
             bulk_store32(&map_out, v, n, m0 + quarter * 32);
+          } else if (p.use_bulk_f8) {
+            bulk_store32_f8(&map_out, v, n, m0 + quarter * 32);
           } else if (m < p.M) {
             if (p.out_dtype == MINTB_BF16) {
               __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + size_t(m) * p.N + n;
@@ -429,6 +450,18 @@ static bool gemm_out_map(CUtensorMap* m, const void* ptr, int rows, int N) {
             CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// e4m3 [rows][N] output, box = (32 bytes, 32 rows), no swizzle
+static bool gemm_out_map_f8(CUtensorMap* m, const void* ptr, int rows, int N) {
+  EncodeTiledFn fn = gemm_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {cuuint64_t(N), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(N)};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t es[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int launch_gemm(const GemmParams& p_in, const void* x, const void* w, cudaStream_t stream) {
   GemmParams p = p_in;
   CUtensorMap ma, mb;
@@ -439,12 +472,22 @@ int launch_gemm(const GemmParams& p_in, const void* x, const void* w, cudaStream
   // row-major bf16 outputs (and the pre-activation copy) go out as bulk tensor stores when their rows are 16-byte multiples
   CUtensorMap mo = ma, mp = ma;   // placeholders when unused
   p.use_bulk_store = 0;
-  if (p.epilogue != kEpiHeadMajor && p.out_dtype == MINTB_BF16 && p.N % 8 == 0) {
-    if (!gemm_out_map(&mo, p.out, p.M, p.N) || (p.preact != nullptr && !gemm_out_map(&mp, p.preact, p.M, p.N))) {
+  // (with an e4m3 result only the bf16 pre-activation copy takes this route)
+  if (p.epilogue != kEpiHeadMajor && p.N % 8 == 0 && (p.out_dtype == MINTB_BF16 || p.preact != nullptr)) {
+    if ((p.out_dtype == MINTB_BF16 && !gemm_out_map(&mo, p.out, p.M, p.N)) ||
+        (p.preact != nullptr && !gemm_out_map(&mp, p.preact, p.M, p.N))) {
       set_error("mintb gemm: cuTensorMapEncodeTiled failed for the output");
       return MINTB_ECUDA;
     }
     p.use_bulk_store = 1;
+  }
+  p.use_bulk_f8 = 0;
+  if (p.epilogue != kEpiHeadMajor && p.out_dtype == MINTB_E4M3 && p.N % 16 == 0) {
+    if (!gemm_out_map_f8(&mo, p.out, p.M, p.N)) {
+      set_error("mintb gemm: cuTensorMapEncodeTiled failed for the e4m3 output");
+      return MINTB_ECUDA;
+    }
+    p.use_bulk_f8 = 1;
   }
   void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, GemmParams) = nullptr;
   if (p.epilogue == kEpiBias) kern = gemm_tc_kernel<kEpiBias, 0>;

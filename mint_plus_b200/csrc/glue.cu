@@ -327,13 +327,30 @@ __device__ __forceinline__ float gelu_erf_grad(float z) {
   return fmaf(z * 0.3989422804014327f, e, cdf);
 }
 
+// the same with gelu(z) = z cdf(z) as a second result
+__device__ __forceinline__ float gelu_erf_grad_val(float z, float& val) {
+  const float u = fabsf(z) * 0.70710678118654752f;
+  float t, e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, u, 1.f)));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-0.72134752044448170f * z * z));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float erf_abs = fmaf(-poly * t, e, 1.f);
+  const float cdf = 0.5f + copysignf(0.5f * erf_abs, z);
+  val = z * cdf;
+  return fmaf(z * 0.3989422804014327f, e, cdf);
+}
+
 // CTA = 32 column groups (8 columns each: 256 columns) x 8 row lanes over a strip of kSumRows rows; a warp reads 512
 // contiguous bytes of one row.  A thread issues the loads of all its rows of the strip (in two halves when z is read as
 // well) before it touches the first value.  The 8 partial column sums meet in shared memory; db gets one atomicAdd per
 // column and CTA.
 template <bool HAS_Z>
 __global__ void __launch_bounds__(256) gelu_bwd_colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ z,
-                                                              __nv_bfloat16* __restrict__ dz, float* __restrict__ db, int M, int N) {
+                                                              __nv_bfloat16* __restrict__ dz, float* __restrict__ db, int M, int N,
+                                                              __nv_bfloat16* __restrict__ act) {
   __shared__ float part[kColLanes][32][8];
   const int cl = threadIdx.x % 32, rl = threadIdx.x / 32;
   const int cg = blockIdx.x * 32 + cl;   // column group
@@ -365,8 +382,15 @@ __global__ void __launch_bounds__(256) gelu_bwd_colsum_kernel(const __nv_bfloat1
         if (HAS_Z) {
           float zv[8];
           unpack8(zq[i], zv);
+          if (act != nullptr) {   // gelu(z) itself as well: the activation the next product's weight gradient needs
+            float a[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) g[j] *= gelu_erf_grad(zv[j]);
+            for (int j = 0; j < 8; ++j) g[j] *= gelu_erf_grad_val(zv[j], a[j]);
+            if (m < M) *reinterpret_cast<uint4*>(act + size_t(m) * N + size_t(cg) * 8) = pack8(a);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] *= gelu_erf_grad(zv[j]);
+          }
           const uint4 packed = pack8(g);
           if (m < M) *reinterpret_cast<uint4*>(dz + size_t(m) * N + size_t(cg) * 8) = packed;
           unpack8(packed, g);   // the bias gradient sums what the products will read
@@ -561,9 +585,10 @@ int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const void* x, co
   return e == cudaSuccess ? MINTB_OK : fail("mintb_add_layernorm_bwd launch", e);
 }
 
-int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, int M, int N, void* stream) {
-  if (dy == nullptr || M <= 0 || N <= 0 || (N % 8) != 0 || (z != nullptr && dz == nullptr) || (z == nullptr && db == nullptr)) {
-    set_error("mintb_gelu_bwd_colsum: dy required, N a multiple of 8, dz with z, db without z");
+int mintb_gelu_bwd_colsum_act(const void* dy, const void* z, void* dz, void* act, float* db, int M, int N, void* stream) {
+  if (dy == nullptr || M <= 0 || N <= 0 || (N % 8) != 0 || (z != nullptr && dz == nullptr) || (z == nullptr && db == nullptr) ||
+      (z == nullptr && act != nullptr)) {
+    set_error("mintb_gelu_bwd_colsum: dy required, N a multiple of 8, dz with z, db without z, act only with z");
     return MINTB_EINVAL;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -574,12 +599,16 @@ int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, in
   dim3 grid((N + 255) / 256, (M + kSumRows - 1) / kSumRows);
   if (z != nullptr)
     gelu_bwd_colsum_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(z),
-                                                       static_cast<__nv_bfloat16*>(dz), db, M, N);
+                                                       static_cast<__nv_bfloat16*>(dz), db, M, N, static_cast<__nv_bfloat16*>(act));
   else
-    gelu_bwd_colsum_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), nullptr, nullptr, db, M, N);
+    gelu_bwd_colsum_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), nullptr, nullptr, db, M, N, nullptr);
   count_launches(1);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? MINTB_OK : fail("mintb_gelu_bwd_colsum launch", e);
+}
+
+int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, int M, int N, void* stream) {
+  return mintb_gelu_bwd_colsum_act(dy, z, dz, nullptr, db, M, N, stream);
 }
 
 int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g, float* db, const float* rope_cos,

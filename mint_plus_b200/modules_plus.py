@@ -44,6 +44,9 @@ class VanillaFeedForward(nn.Module):
         # bf16 on the GPU: both projections run on the tcgen05 GEMM, bias and erf-GELU in its epilogue
         # (F.gelu's default is the exact erf form too, so both flags give the same function)
         if x.is_cuda and x.dtype == torch.bfloat16:
+            from .mu_scaling import Fp8Linear, fp8_ffn
+            if isinstance(self.fc1, Fp8Linear) and isinstance(self.fc2, Fp8Linear):
+                return fp8_ffn(self.fc1, self.fc2, x)    # fc1 hands gelu(.) to fc2 as e4m3: no bf16 copy, no cast pass
             return _linear(self.fc2, _linear(self.fc1, x, gelu=True))
         x = gelu_erf(self.fc1(x)) if self.use_erf_gelu else F.gelu(self.fc1(x))
         return self.fc2(x)

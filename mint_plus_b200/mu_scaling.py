@@ -42,6 +42,40 @@ class _Fp8LinearFn(torch.autograd.Function):
         return dx, dw, db, None, None, None, None, None
 
 
+class _Fp8FfnFn(torch.autograd.Function):
+    """fc2(gelu(fc1(x))) on two e4m3 products as ONE differentiable step: fc1's epilogue writes gelu(.) directly as the e4m3
+    operand of fc2 (with fc2's activation scale) beside the bf16 pre-activation z, so neither a bf16 copy of the 4E-wide
+    activation nor a cast pass over it exists; the backward pass rebuilds gelu(z) in the pass that computes gelu'(z) dy,
+    for fc2's weight gradient (mu_scaling/layer.py:236-241 and modules.py:323-335 of the reference; te.Linear there)."""
+
+    @staticmethod
+    def forward(ctx, x2d, w1, b1, w2, b2, wq1, ws1, xs1, os1, wq2, ws2, xs2, os2):
+        xq = ops.quantize_e4m3(x2d, xs1)
+        a8, z = ops.gemm_e4m3(xq, wq1, xs1 * ws1 * os1, b1, True, out_e4m3_scale=xs2, save_preact=True)
+        y = ops.gemm_e4m3(a8, wq2, xs2 * ws2 * os2, b2, False)
+        ctx.save_for_backward(x2d, w1, b1, w2, b2, z)
+        ctx.scales = (float(os1), float(os2))
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2d, w1, b1, w2, b2, z = ctx.saved_tensors
+        os1, os2 = ctx.scales
+        n = ctx.needs_input_grad
+        dy = dy.contiguous()
+        # fc2: bias gradient, then the gradient of its input; its weight gradient waits for gelu(z)
+        db2 = ops.gelu_bwd_colsum(dy, None, True)[1].to(b2.dtype) if (b2 is not None and n[4]) else None
+        w2b = w2 if w2.dtype == torch.bfloat16 else w2.to(torch.bfloat16)
+        da = dy @ (w2b * os2 if os2 != 1.0 else w2b)
+        dz, db1, act = ops.gelu_bwd_colsum(da, z, b1 is not None and n[2], want_act=n[3])
+        dw2 = None
+        if n[3]:
+            dw2 = dy.t() @ act
+            dw2 = (dw2 * os2 if os2 != 1.0 else dw2).to(w2.dtype)
+        dx, dw1, db1 = ops.linear_backward(dz, x2d, w1, b1, None, (n[0], n[1], n[2]), os1, db=db1 if db1 is not None else False)
+        return (dx, dw1, db1, dw2, db2) + (None,) * 8
+
+
 class Fp8Linear(nn.Module):
     """Drop-in for nn.Linear (same `weight`, `bias`, `in_features`, `out_features`) computing in e4m3 on the GPU."""
 
@@ -86,6 +120,16 @@ class Fp8Linear(nn.Module):
 
     def extra_repr(self):
         return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, x_scale={self.x_scale}"
+
+
+def fp8_ffn(fc1: "Fp8Linear", fc2: "Fp8Linear", x: torch.Tensor) -> torch.Tensor:
+    """fc2(gelu_erf(fc1(x))) for two Fp8Linear modules on bf16 CUDA activations, as one differentiable step (`_Fp8FfnFn`)."""
+    wq1, ws1 = fc1._quantized_weight()
+    wq2, ws2 = fc2._quantized_weight()
+    x2d = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+    y = _Fp8FfnFn.apply(x2d, fc1.weight, fc1.bias, fc2.weight, fc2.bias, wq1, ws1, fc1.x_scale, fc1.out_scale,
+                        wq2, ws2, fc2.x_scale, fc2.out_scale)
+    return y.view(*x.shape[:-1], fc2.out_features)
 
 
 def fused_fp8_weight(owner: nn.Module, mods):

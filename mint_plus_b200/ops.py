@@ -413,19 +413,22 @@ def gemm_e4m3(xq: torch.Tensor, wq: torch.Tensor, alpha: float, bias=None, gelu:
     return (out, z) if save_preact else out
 
 
-def gelu_bwd_colsum(dy: torch.Tensor, z: Optional[torch.Tensor], want_db: bool = True):
-    """(dz, db): dz = dy * gelu'(z) (bf16 [M,N]; dy itself when z is None) and db = column sums of dz (fp32 [N]) in one pass."""
+def gelu_bwd_colsum(dy: torch.Tensor, z: Optional[torch.Tensor], want_db: bool = True, want_act: bool = False):
+    """(dz, db): dz = dy * gelu'(z) (bf16 [M,N]; dy itself when z is None) and db = column sums of dz (fp32 [N]) in one pass.
+    With want_act the same pass also writes gelu(z) in bf16 and the result is (dz, db, act)."""
     _require_cuda(dy, z)
     dy = dy.contiguous()
     M, N = dy.shape
     dz = torch.empty_like(dy) if z is not None else dy
     db = torch.empty(N, dtype=torch.float32, device=dy.device) if want_db else None
+    act = torch.empty_like(dy) if (want_act and z is not None) else None
     if z is None and not want_db:
-        return dz, None
+        return (dz, None, None) if want_act else (dz, None)
     with _on(dy.device):
-        rc = L.lib().mintb_gelu_bwd_colsum(_ptr(dy), _ptr(z), _ptr(dz) if z is not None else None, _ptr(db), M, N, _stream())
+        rc = L.lib().mintb_gelu_bwd_colsum_act(_ptr(dy), _ptr(z), _ptr(dz) if z is not None else None, _ptr(act), _ptr(db), M, N,
+                                               _stream())
     L.check(rc, "mintb_gelu_bwd_colsum")
-    return dz, db
+    return (dz, db, act) if want_act else (dz, db)
 
 
 def _gelu_erf_grad(z: torch.Tensor) -> torch.Tensor:

@@ -184,3 +184,30 @@ def test_lora_linear_on_the_merged_weight_matches_the_formula():
     assert (y.float() - yf).abs().max().item() <= 2e-2 * yf.abs().max().item()
     for got, want in ((gx, wx), (gA, wA), (gB, wB)):
         assert (got.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-3
+
+
+def test_fp8_ffn_as_one_step_matches_the_two_projection_path():
+    """fc1 handing gelu(.) to fc2 as e4m3 (no bf16 copy, gelu(z) rebuilt in the backward pass) against the two separate
+    Fp8Linear calls: same arithmetic up to the rounding of the activation before its e4m3 cast."""
+    from mint_plus_b200.mu_scaling import Fp8Linear, fp8_ffn
+    torch.manual_seed(6)
+    E, F_, M_ = 256, 1024, 300
+    fc1, fc2 = Fp8Linear(E, F_).cuda().to(torch.bfloat16), Fp8Linear(F_, E).cuda().to(torch.bfloat16)
+    with torch.no_grad():
+        fc1.weight.normal_(0, 1); fc2.weight.normal_(0, 1)
+        fc1.bias.normal_(0, 0.1); fc2.bias.normal_(0, 0.1)
+    fc1.out_scale, fc2.out_scale = E ** -0.5, F_ ** -0.5
+    x = torch.randn(M_, 1, E, device="cuda").to(torch.bfloat16)
+    gy = torch.randn(M_, 1, E, device="cuda").to(torch.bfloat16)
+    res = []
+    for fused in (False, True):
+        xi = x.clone().requires_grad_(True)
+        for p in list(fc1.parameters()) + list(fc2.parameters()):
+            p.grad = None
+        y = fp8_ffn(fc1, fc2, xi) if fused else fc2(fc1(xi, gelu=True))
+        y.backward(gy)
+        res.append([y.detach().float(), xi.grad.float()] + [p.grad.float() for p in (fc1.weight, fc1.bias, fc2.weight, fc2.bias)])
+    ops.check_device_status()
+    for a, b, n in zip(res[1], res[0], ("y", "dx", "dW1", "db1", "dW2", "db2")):
+        err, scale = (a - b).abs().max().item(), b.abs().max().item()
+        assert err <= 3e-2 * scale + 1e-3, f"{n}: {err:.4g} vs scale {scale:.4g}"
