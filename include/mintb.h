@@ -210,6 +210,11 @@ MINTB_API int mintb_quantize_e4m3(const void* x, void* out, size_t n, float inv_
 MINTB_API int mintb_add_layernorm_fwd(const void* x, const void* r, float a, float b, const void* gamma, const void* beta,
                                       int param_dtype, void* s_out, void* y_out, float* stats, int rows, int E, float eps,
                                       void* stream);
+/* the same, also writing an e4m3 copy q_out[rows][E] = sat(result * q_inv_scale) of the main result (y with gamma, else s):
+ * the operand of the next e4m3 projection without a separate cast pass */
+MINTB_API int mintb_add_layernorm_fwd_q(const void* x, const void* r, float a, float b, const void* gamma, const void* beta,
+                                        int param_dtype, void* s_out, void* y_out, float* stats, int rows, int E, float eps,
+                                        void* q_out, float q_inv_scale, void* stream);
 MINTB_API size_t mintb_add_layernorm_bwd_workspace_bytes(int rows, int E);
 MINTB_API int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const void* x, const void* r, float a, float b,
                                       const void* gamma, int param_dtype, const float* stats, void* dx, void* dr, float* dgamma,

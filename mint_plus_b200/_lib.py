@@ -42,6 +42,7 @@ PROTOTYPES = {
                               _P, _P]),
     "mintb_quantize_e4m3": (c_int, [_P, _P, c_size_t, c_float, _P]),
     "mintb_add_layernorm_fwd": (c_int, [_P, _P, c_float, c_float, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_float, _P]),
+    "mintb_add_layernorm_fwd_q": (c_int, [_P, _P, c_float, c_float, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_float, _P, c_float, _P]),
     "mintb_add_layernorm_bwd_workspace_bytes": (c_size_t, [c_int, c_int]),
     "mintb_add_layernorm_bwd": (c_int, [_P, _P, _P, _P, c_float, c_float, _P, c_int, _P, _P, _P, _P, _P, _P, c_size_t, c_int,
                                         c_int, _P]),

@@ -41,6 +41,14 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return u;
 }
 
+__device__ __forceinline__ uint2 pack8_e4m3(const float (&f)[8], float inv) {
+  uint2 u;
+  __nv_fp8x2_storage_t* h = reinterpret_cast<__nv_fp8x2_storage_t*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __nv_cvt_float2_to_fp8x2(make_float2(f[2 * i] * inv, f[2 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+  return u;
+}
+
 __device__ __forceinline__ float ld_param(const void* p, int dtype, int i) {
   return dtype == MINTB_F32 ? static_cast<const float*>(p)[i] : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
 }
@@ -54,6 +62,8 @@ struct LnParams {
   const void *gamma, *beta;         // null: no normalisation, only s
   int param_dtype;                  // MINTB_F32 or MINTB_BF16
   __nv_bfloat16 *s_out, *y_out;     // either may be null
+  __nv_fp8_storage_t* q_out;        // e4m3 copy of the main result (y with gamma, else s), sat(value * q_inv); may be null
+  float q_inv;
   float2* stats;                    // [rows] (mean, rstd); written by forward, read by backward
   const __nv_bfloat16 *dy, *ds_in;  // backward inputs (either may be null)
   __nv_bfloat16 *dx, *dr;           // backward outputs (dr may be null)
@@ -107,7 +117,15 @@ __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_fwd_kernel(LnPara
 #pragma unroll
       for (int k = 0; k < MAXV; ++k) {
         const int vi = lane + 32 * k;
-        if (vi < nvec) reinterpret_cast<uint4*>(p.s_out + size_t(row) * p.E)[vi] = pack8(v[k]);
+        if (vi < nvec) {
+          const uint4 packed = pack8(v[k]);
+          reinterpret_cast<uint4*>(p.s_out + size_t(row) * p.E)[vi] = packed;
+          if (p.q_out != nullptr && p.gamma == nullptr) {   // the e4m3 copy is taken from the rounded bf16 values
+            float rb[8];
+            unpack8(packed, rb);
+            reinterpret_cast<uint2*>(p.q_out + size_t(row) * p.E)[vi] = pack8_e4m3(rb, p.q_inv);
+          }
+        }
       }
     }
     if (p.gamma == nullptr) continue;
@@ -136,7 +154,13 @@ __global__ void __launch_bounds__(kLnWarps * 32) add_layernorm_fwd_kernel(LnPara
         *reinterpret_cast<float4*>(bt + 4) = *reinterpret_cast<const float4*>(s_beta + vi * 8 + 4);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = fmaf((v[k][j] - mean) * rstd, gm[j], bt[j]);
-        reinterpret_cast<uint4*>(p.y_out + size_t(row) * p.E)[vi] = pack8(o);
+        const uint4 packed = pack8(o);
+        reinterpret_cast<uint4*>(p.y_out + size_t(row) * p.E)[vi] = packed;
+        if (p.q_out != nullptr) {
+          float rb[8];
+          unpack8(packed, rb);
+          reinterpret_cast<uint2*>(p.q_out + size_t(row) * p.E)[vi] = pack8_e4m3(rb, p.q_inv);
+        }
       }
     }
   }
@@ -505,8 +529,9 @@ extern "C" {
 
 using namespace mintb;
 
-int mintb_add_layernorm_fwd(const void* x, const void* r, float a, float b, const void* gamma, const void* beta, int param_dtype,
-                            void* s_out, void* y_out, float* stats, int rows, int E, float eps, void* stream) {
+int mintb_add_layernorm_fwd_q(const void* x, const void* r, float a, float b, const void* gamma, const void* beta, int param_dtype,
+                              void* s_out, void* y_out, float* stats, int rows, int E, float eps, void* q_out, float q_inv_scale,
+                              void* stream) {
   if (x == nullptr || rows <= 0 || E <= 0 || (E % 8) != 0 || ln_maxv(E) == 0) {
     set_error("mintb_add_layernorm_fwd: x is required, rows > 0, E a multiple of 8 and at most 2560 (got rows %d, E %d)", rows, E);
     return x == nullptr || rows <= 0 || E <= 0 ? MINTB_EINVAL : MINTB_EUNSUPPORTED;
@@ -521,6 +546,7 @@ int mintb_add_layernorm_fwd(const void* x, const void* r, float a, float b, cons
   p.a = a; p.b = b; p.gamma = gamma; p.beta = beta; p.param_dtype = param_dtype;
   p.s_out = static_cast<__nv_bfloat16*>(s_out); p.y_out = static_cast<__nv_bfloat16*>(y_out);
   p.stats = reinterpret_cast<float2*>(stats); p.rows = rows; p.E = E; p.eps = eps;
+  p.q_out = static_cast<__nv_fp8_storage_t*>(q_out); p.q_inv = q_inv_scale;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int want = (rows + kLnWarps - 1) / kLnWarps;
   const int grid = want < 148 * 16 ? want : 148 * 16;   // rows are walked with a grid stride
@@ -532,6 +558,11 @@ int mintb_add_layernorm_fwd(const void* x, const void* r, float a, float b, cons
   count_launches(1);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? MINTB_OK : fail("mintb_add_layernorm_fwd launch", e);
+}
+
+int mintb_add_layernorm_fwd(const void* x, const void* r, float a, float b, const void* gamma, const void* beta, int param_dtype,
+                            void* s_out, void* y_out, float* stats, int rows, int E, float eps, void* stream) {
+  return mintb_add_layernorm_fwd_q(x, r, a, b, gamma, beta, param_dtype, s_out, y_out, stats, rows, E, eps, nullptr, 1.f, stream);
 }
 
 size_t mintb_add_layernorm_bwd_workspace_bytes(int rows, int E) {

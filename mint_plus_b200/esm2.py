@@ -146,6 +146,9 @@ class MINT(nn.Module):
             x.requires_grad_(True)
         layer_idx = -1
         for layer_idx, layer in enumerate(self.layers):
+            if hasattr(layer, "_next_x_scale"):   # lets the layer's last pass write the next layer's e4m3 QKV operand
+                from .mu_scaling import qkv_activation_scale
+                layer._next_x_scale = qkv_activation_scale(self.layers[layer_idx + 1]) if layer_idx + 1 < len(self.layers) else None
             kw = dict(self_attn_padding_mask=padding_mask, self_attn_mask=self_attn_mask, chain_ids=chain_ids)
             if pack is not None:
                 kw["pack"] = pack

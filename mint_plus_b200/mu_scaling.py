@@ -50,7 +50,7 @@ class _Fp8FfnFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x2d, w1, b1, w2, b2, wq1, ws1, xs1, os1, wq2, ws2, xs2, os2):
-        xq = ops.quantize_e4m3(x2d, xs1)
+        xq = ops._quantize_shared(x2d, xs1)      # the pass that produced x may have left the e4m3 copy already
         a8, z = ops.gemm_e4m3(xq, wq1, xs1 * ws1 * os1, b1, True, out_e4m3_scale=xs2, save_preact=True)
         y = ops.gemm_e4m3(a8, wq2, xs2 * ws2 * os2, b2, False)
         ctx.save_for_backward(x2d, w1, b1, w2, b2, z)
@@ -198,6 +198,19 @@ def calibrate_fp8(model: nn.Module, *forward_args, margin: float = 1.0, **forwar
     return model
 
 
+def qkv_activation_scale(layer) -> Optional[float]:
+    """The activation scale with which the layer's fused QKV products cast their input to e4m3, or None when they are
+    not FP8 projections (the scale `fused_fp8_weight` hands to the GEMM)."""
+    sa = getattr(layer, "self_attn", None)
+    if sa is None:
+        return None
+    fused = getattr(sa, "fused_qkv", None)
+    mods = [fused] if fused is not None else [getattr(sa, n, None) for n in ("q_proj", "k_proj", "v_proj")]
+    if all(isinstance(m, Fp8Linear) for m in mods):
+        return max(m.x_scale for m in mods)
+    return None
+
+
 def compute_tau(num_layers: int) -> float:
     """Residual coefficient for a depth: 0.5 / sqrt(L) (mu_scaling/optim.py:20-41)."""
     return 0.5 / math.sqrt(max(1, num_layers))
@@ -231,6 +244,8 @@ class TransformerLayer_MINT_mu(_TwoPathwayLayer):
         self.register_buffer("_tau", torch.tensor(tau, dtype=torch.float32))
         self._tau_f = float(tau)
 
+    _next_x_scale = None   # set by MINT.forward: the activation scale of the NEXT layer's FP8 QKV products, if any
+
     def forward(self, x, self_attn_mask=None, self_attn_padding_mask=None, chain_ids=None, pack=None):
         tau = self._tau_f                       # host copy of the buffer: no device read-back per call
         keep, add = math.sqrt(1.0 - tau), math.sqrt(tau)
@@ -242,8 +257,11 @@ class TransformerLayer_MINT_mu(_TwoPathwayLayer):
             attn_out, _ = self._standard_attention(x, self_attn_mask, self_attn_padding_mask)
         if x.is_cuda and x.dtype == torch.bfloat16:
             # bf16 on the GPU: weighted residuals and the closing LayerNorm in two fused passes
-            x, _ = ops.add_layernorm(x, attn_out, keep, add, None)
-            _, y = ops.add_layernorm(x, self.feed_forward(x), keep, add, self.final_layer_norm, need_s=False)
+            # (each pass also writes the e4m3 operand of the FP8 projection that reads its result next)
+            fc1 = self.feed_forward.fc1
+            x, _ = ops.add_layernorm(x, attn_out, keep, add, None, quant_scale=fc1.x_scale if isinstance(fc1, Fp8Linear) else None)
+            _, y = ops.add_layernorm(x, self.feed_forward(x), keep, add, self.final_layer_norm, need_s=False,
+                                     quant_scale=self._next_x_scale)
             return y, None
         x = keep * x + add * attn_out
         x = keep * x + add * self.feed_forward(x)

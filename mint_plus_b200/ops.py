@@ -552,7 +552,8 @@ class _AddLayerNormFn(torch.autograd.Function):
     gamma None drops the normalisation (then only s).  Replaces the residual add + LayerNorm pairs of the layers."""
 
     @staticmethod
-    def forward(ctx, x, r, a, b, gamma, beta, eps, need_s):
+    def forward(ctx, x, r, a, b, gamma, beta, eps, need_s, quant_scale=None):
+        global _shared_q
         E = x.shape[-1]
         x2 = x.reshape(-1, E).contiguous()
         r2 = r.reshape(-1, E).contiguous() if r is not None else None
@@ -562,10 +563,16 @@ class _AddLayerNormFn(torch.autograd.Function):
         y = torch.empty_like(x2) if norm else None
         stats = torch.empty(rows, 2, dtype=torch.float32, device=x.device) if norm else None
         pdt = _BIAS_DT[gamma.dtype] if norm else L.F32
+        # the e4m3 copy of the main result for the e4m3 projection that consumes it next (same values as quantize_e4m3)
+        q8 = torch.empty(rows, E, dtype=torch.float8_e4m3fn, device=x.device) if quant_scale else None
         with _on(x.device):
-            rc = L.lib().mintb_add_layernorm_fwd(_ptr(x2), _ptr(r2), float(a), float(b), _ptr(gamma), _ptr(beta), pdt, _ptr(s), _ptr(y),
-                                                 _ptr(stats), rows, E, float(eps), _stream())
+            rc = L.lib().mintb_add_layernorm_fwd_q(_ptr(x2), _ptr(r2), float(a), float(b), _ptr(gamma), _ptr(beta), pdt, _ptr(s), _ptr(y),
+                                                   _ptr(stats), rows, E, float(eps), _ptr(q8),
+                                                   1.0 / quant_scale if quant_scale else 1.0, _stream())
         L.check(rc, "mintb_add_layernorm_fwd")
+        if q8 is not None:   # hand it to the consumer through the one-entry memo of _quantize_shared
+            main = y if norm else s
+            _shared_q = (main, (main.data_ptr(), main._version, tuple(main.shape), float(quant_scale), _stream()), q8)
         ctx.save_for_backward(x2, r2, gamma, stats)
         ctx.cfg = (float(a), float(b), x.shape, pdt, beta is not None)
         outs = (s.view(x.shape) if s is not None else None, y.view(x.shape) if y is not None else None)
@@ -578,7 +585,7 @@ class _AddLayerNormFn(torch.autograd.Function):
         rows, E = x2.shape
         norm = gamma is not None
         if not norm and ds_in is None:
-            return (None,) * 8
+            return (None,) * 9
         dy2 = dy.reshape(rows, E).contiguous() if (norm and dy is not None) else None
         if norm and dy2 is None:
             dy2 = torch.zeros_like(x2)
@@ -595,16 +602,19 @@ class _AddLayerNormFn(torch.autograd.Function):
                                              _ptr(dr), _ptr(dgamma), _ptr(dbeta), _ptr(ws), wsb, rows, E, _stream())
         L.check(rc, "mintb_add_layernorm_bwd")
         return (dx.view(shape), dr.view(shape) if dr is not None else None, None, None,
-                dgamma.to(gamma.dtype) if norm else None, dbeta.to(gamma.dtype) if (norm and has_beta) else None, None, None)
+                dgamma.to(gamma.dtype) if norm else None, dbeta.to(gamma.dtype) if (norm and has_beta) else None, None, None, None)
 
 
-def add_layernorm(x, r, a: float, b: float, norm: Optional[torch.nn.LayerNorm], need_s: bool = True):
-    """(s, y): s = a x + b r (r may be None), y = norm(s).  bf16 CUDA tensors; `norm` None returns (s, None)."""
+def add_layernorm(x, r, a: float, b: float, norm: Optional[torch.nn.LayerNorm], need_s: bool = True,
+                  quant_scale: Optional[float] = None):
+    """(s, y): s = a x + b r (r may be None), y = norm(s).  bf16 CUDA tensors; `norm` None returns (s, None).
+    `quant_scale`: the activation scale of the e4m3 projection that reads the main result (y, or s without `norm`) next:
+    the kernel then writes that projection's e4m3 operand in the same pass and the projection finds it instead of casting."""
     if x.dtype != torch.bfloat16 or not x.is_cuda:
         raise TypeError("add_layernorm takes bfloat16 CUDA tensors")
     if norm is None:
-        return _AddLayerNormFn.apply(x, r, a, b, None, None, 0.0, True)
-    return _AddLayerNormFn.apply(x, r, a, b, norm.weight, norm.bias, norm.eps, need_s)
+        return _AddLayerNormFn.apply(x, r, a, b, None, None, 0.0, True, quant_scale)
+    return _AddLayerNormFn.apply(x, r, a, b, norm.weight, norm.bias, norm.eps, need_s, quant_scale)
 
 
 def _rope_rotate_torch(t, cos, sin, inverse=False):

@@ -159,3 +159,20 @@ def test_qkv_gradient_pack(D, rope):
     torch.cuda.synchronize()
     assert torch.equal(gp, g[rows.long()])
     torch.testing.assert_close(db, gp.float().sum(0), rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_add_layernorm_writes_the_e4m3_operand_of_the_next_projection(with_norm):
+    """quant_scale: the pass also leaves sat(result / scale) in e4m3 — the very bytes quantize_e4m3 gives — where the next
+    FP8 projection looks for it."""
+    torch.manual_seed(2)
+    x, r = _bf(3 * torch.randn(70, 2, 640, device=DEV)), _bf(3 * torch.randn(70, 2, 640, device=DEV))
+    norm = torch.nn.LayerNorm(640).to(DEV, torch.bfloat16) if with_norm else None
+    scale = 0.004                                     # small enough that some values saturate at 448
+    s, y = ops.add_layernorm(x, r, 0.8, 0.6, norm, need_s=not with_norm, quant_scale=scale)
+    main = (y if with_norm else s).reshape(-1, 640)
+    got = ops._quantize_shared(main, scale)            # served from the memo the pass has filled
+    assert ops._shared_q[2] is got
+    want = ops.quantize_e4m3(main.contiguous(), scale)
+    assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+    assert (want.float().abs() == 448).any()
