@@ -197,7 +197,8 @@ MINTB_API int mintb_quantize_e4m3(const void* x, void* out, size_t n, float inv_
  *   no normalisation, only s_out is written.  Otherwise y_out is written, s_out if non-null, and stats[rows] = (mean, rstd)
  *   (2 floats per row) if non-null.  E must be a multiple of 8, at most 2560; gamma / beta are f32 or bf16 (param_dtype).
  * mintb_add_layernorm_bwd: ds = dLayerNorm(dy) + ds_in (either part may be absent), dx = a ds, dr = b ds (dr may be null),
- *   dgamma / dbeta (fp32 [E]) summed in a fixed order through the workspace.
+ *   dgamma / dbeta (fp32 [E]) summed in a fixed order through the workspace; both null (frozen parameters) skips them and
+ *   needs no workspace.
  * mintb_gelu_bwd_colsum: with z: dz = dy * gelu'(z) (erf form, modules.py:16-23) and db[N] = column sums of dz (db may be
  *   null); without z: db = column sums of dy (the bias gradient of a projection).  N a multiple of 8.
  *   mintb_gelu_bwd_colsum_act also writes act = gelu(z) (bf16 [M][N], may be null) in the same pass: the forward pass of an

@@ -299,7 +299,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) add_layernorm_bwd_kernel(LnPara
       }
     }
   }
-  if (norm && live) {
+  if (norm && live && p.partial != nullptr) {
     float* dst = p.partial + size_t(blockIdx.x) * 2 * p.E + vi * 8;
     *reinterpret_cast<float4*>(dst) = make_float4(rg[0], rg[1], rg[2], rg[3]);
     *reinterpret_cast<float4*>(dst + 4) = make_float4(rg[4], rg[5], rg[6], rg[7]);
@@ -578,12 +578,13 @@ int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const void* x, co
     return rows <= 0 || E <= 0 ? MINTB_EINVAL : MINTB_EUNSUPPORTED;
   }
   const bool norm = gamma != nullptr;
-  if (dx == nullptr || (norm && (dy == nullptr || x == nullptr || stats == nullptr || dgamma == nullptr || dbeta == nullptr)) ||
+  if (dx == nullptr || (norm && (dy == nullptr || x == nullptr || stats == nullptr || (dgamma == nullptr) != (dbeta == nullptr))) ||
       (!norm && ds_in == nullptr)) {
-    set_error("mintb_add_layernorm_bwd: missing pointer (with gamma: dy, x, stats, dgamma, dbeta; without: ds_in; always dx)");
+    set_error("mintb_add_layernorm_bwd: missing pointer (with gamma: dy, x, stats, dgamma and dbeta or neither; without: ds_in; always dx)");
     return MINTB_EINVAL;
   }
-  if (norm && (workspace == nullptr || workspace_bytes < mintb_add_layernorm_bwd_workspace_bytes(rows, E))) {
+  const bool param_grads = norm && dgamma != nullptr;   // frozen parameters: no partial sums, no second pass
+  if (param_grads && (workspace == nullptr || workspace_bytes < mintb_add_layernorm_bwd_workspace_bytes(rows, E))) {
     set_error("mintb_add_layernorm_bwd: workspace of %zu bytes required", mintb_add_layernorm_bwd_workspace_bytes(rows, E));
     return MINTB_EWORKSPACE;
   }
@@ -593,7 +594,7 @@ int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const void* x, co
   p.stats = const_cast<float2*>(reinterpret_cast<const float2*>(stats));
   p.dy = static_cast<const __nv_bfloat16*>(dy); p.ds_in = static_cast<const __nv_bfloat16*>(ds_in);
   p.dx = static_cast<__nv_bfloat16*>(dx); p.dr = static_cast<__nv_bfloat16*>(dr);
-  p.partial = static_cast<float*>(workspace); p.rows = rows; p.E = E;
+  p.partial = param_grads ? static_cast<float*>(workspace) : nullptr; p.rows = rows; p.E = E;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // one 16-byte vector of the row per thread; ONE wave of CTAs, each walking its share of the rows
   const int nw = ln_maxv(E);   // 2, 5 or 10 warps
@@ -608,7 +609,7 @@ int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const void* x, co
   cudaError_t e = cudaSuccess;
   if (e != cudaSuccess) return fail("mintb_add_layernorm_bwd", e);
   count_launches(1);
-  if (norm) {
+  if (param_grads) {
     ln_param_grad_kernel<<<(2 * E + 31) / 32, 256, 0, st>>>(p.partial, grid, E, dgamma, dbeta);
     count_launches(1);
   }

@@ -592,17 +592,18 @@ class _AddLayerNormFn(torch.autograd.Function):
         ds2 = ds_in.reshape(rows, E).contiguous() if ds_in is not None else None
         dx = torch.empty_like(x2)
         dr = torch.empty_like(x2) if r2 is not None else None
-        dgamma = torch.empty(E, dtype=torch.float32, device=x2.device) if norm else None
-        dbeta = torch.empty(E, dtype=torch.float32, device=x2.device) if norm else None
+        want_pg = norm and (ctx.needs_input_grad[4] or ctx.needs_input_grad[5])   # frozen norm parameters: no sums at all
+        dgamma = torch.empty(E, dtype=torch.float32, device=x2.device) if want_pg else None
+        dbeta = torch.empty(E, dtype=torch.float32, device=x2.device) if want_pg else None
         lib = L.lib()
-        wsb = lib.mintb_add_layernorm_bwd_workspace_bytes(rows, E) if norm else 0
+        wsb = lib.mintb_add_layernorm_bwd_workspace_bytes(rows, E) if want_pg else 0
         ws = torch.empty(wsb, dtype=torch.uint8, device=x2.device) if wsb else None
         with _on(x2.device):
             rc = lib.mintb_add_layernorm_bwd(_ptr(dy2), _ptr(ds2), _ptr(x2), _ptr(r2), a, b, _ptr(gamma), pdt, _ptr(stats), _ptr(dx),
                                              _ptr(dr), _ptr(dgamma), _ptr(dbeta), _ptr(ws), wsb, rows, E, _stream())
         L.check(rc, "mintb_add_layernorm_bwd")
         return (dx.view(shape), dr.view(shape) if dr is not None else None, None, None,
-                dgamma.to(gamma.dtype) if norm else None, dbeta.to(gamma.dtype) if (norm and has_beta) else None, None, None, None)
+                dgamma.to(gamma.dtype) if want_pg else None, dbeta.to(gamma.dtype) if (want_pg and has_beta) else None, None, None, None)
 
 
 def add_layernorm(x, r, a: float, b: float, norm: Optional[torch.nn.LayerNorm], need_s: bool = True,

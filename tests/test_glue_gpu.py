@@ -176,3 +176,23 @@ def test_add_layernorm_writes_the_e4m3_operand_of_the_next_projection(with_norm)
     want = ops.quantize_e4m3(main.contiguous(), scale)
     assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
     assert (want.float().abs() == 448).any()
+
+
+def test_add_layernorm_backward_with_frozen_norm_parameters():
+    """Frozen gamma / beta (LoRA fine-tuning): the parameter-gradient sums and their second pass are skipped, the input
+    gradients are the same bits."""
+    torch.manual_seed(3)
+    x0, r0 = _bf(torch.randn(500, 640, device=DEV)), _bf(torch.randn(500, 640, device=DEV))
+    gy = _bf(torch.randn(500, 640, device=DEV))
+    norm = torch.nn.LayerNorm(640).to(DEV, torch.bfloat16)
+    grads = []
+    for frozen in (False, True):
+        for p in norm.parameters():
+            p.requires_grad_(not frozen)
+            p.grad = None
+        x, r = x0.clone().requires_grad_(True), r0.clone().requires_grad_(True)
+        _, y = ops.add_layernorm(x, r, 0.9, 0.4, norm, need_s=False)
+        y.backward(gy)
+        grads.append((x.grad, r.grad))
+        assert (norm.weight.grad is None) == frozen
+    assert torch.equal(grads[0][0], grads[1][0]) and torch.equal(grads[0][1], grads[1][1])
