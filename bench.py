@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -28,8 +29,10 @@ WORKLOAD = dict(B=8, H=20, T=1024, D=32)
 METRIC = "fused_multimer_attention_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-# DRAM bytes (read + write) per launch of the dominant kernel (attn_bwd_tc_kernel<32> on this workload) from the ncu
-# capture summarised in profiles/attn_tc_kernels_B8_H20_T1024_D32.md: 124.1 MB read + 45.5 MB written.
+MIN_TIMED_SECONDS = 0.5      # the K-step sweep is repeated until at least this much device time has been measured
+# DRAM bytes (read + write) of ONE launch of the backward kernel on this workload, from an ncu capture of that kernel
+# (dram__bytes_read.sum + dram__bytes_write.sum = 124.1 MB + 45.5 MB).  A constant of the kernel, not of the run: it is
+# reported beside the bytes computed from the tensor sizes and has to be refreshed when the kernel's data movement changes.
 NCU_TRAFFIC_BYTES = 169.5e6
 
 
@@ -41,8 +44,32 @@ def algorithmic_flops(H, T, D, key_pad, fwd=True, bwd=True):
     return float((per * H * T * tk * D).sum())
 
 
+def algorithmic_bytes(B, H, T, D):
+    """HBM bytes the backward call has to move at least once (bf16 tensors): the six inputs, O and dO in, six gradients
+    out, the log-sum-exp in, and the fp32 dQ accumulators of both pathways written and read back once."""
+    elems = B * H * T * D
+    return 14 * elems * 2 + B * H * T * 4 + 2 * 2 * elems * 4
+
+
+def make_op_inputs(B, H, T, D, seed, max_pad=64):
+    """Seeded inputs of the isolated-op configuration: six N(0,1)/sqrt(D) tensors, a chain split point per sample uniform
+    in [200, 824] (scaled with T), 0..max_pad trailing padded positions, N(0,1) upstream gradient.  Draws the same numbers
+    as the generator of the parity tests (a test compares the two)."""
+    g = torch.Generator().manual_seed(seed)
+    ts = [torch.randn(B, H, T, D, generator=g) / math.sqrt(D) for _ in range(6)]
+    split = torch.randint(T * 200 // 1024, T * 824 // 1024 + 1, (B,), generator=g)
+    pad = torch.randint(0, min(max_pad, max(T - int(split.max()) - 1, 0)) + 1, (B,), generator=g)
+    chain_ids = torch.zeros(B, T, dtype=torch.int32)
+    key_pad = torch.zeros(B, T, dtype=torch.bool)
+    for b in range(B):
+        chain_ids[b, int(split[b]):] = 1
+        if int(pad[b]) > 0:
+            key_pad[b, T - int(pad[b]):] = True
+    grad = torch.randn(B, H, T, D, generator=g)
+    return ts, chain_ids, key_pad, grad
+
+
 def make_inputs(seed):
-    from oracle.multimer_attention import make_op_inputs   # seeded generator shared with the parity tests
     return make_op_inputs(WORKLOAD["B"], WORKLOAD["H"], WORKLOAD["T"], WORKLOAD["D"], seed=seed)
 
 
@@ -86,6 +113,49 @@ class ClockSampler(threading.Thread):
                 continue
         return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx or None,
                 "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def time_shape(M, dev, flush, B, H, T, D, seed, iters):
+    """Forward and forward+backward time of the attention op at another shape: chains of 100..900 positions per pair padded
+    to T, inputs resident in HBM (larger than L2, which is flushed between iterations as well)."""
+    g = torch.Generator().manual_seed(seed)
+    ts = [(torch.randn(B, H, T, D, generator=g) / math.sqrt(D)).bfloat16().to(dev) for _ in range(6)]
+    la = torch.randint(100, 901, (B,), generator=g)
+    lb = torch.randint(100, 901, (B,), generator=g)
+    cid = torch.zeros(B, T, dtype=torch.int32)
+    pad = torch.zeros(B, T, dtype=torch.bool)
+    for b in range(B):
+        cid[b, int(la[b]):] = 1
+        pad[b, int(la[b]) + int(lb[b]):] = True
+    grad = torch.randn(B, H, T, D, generator=g).bfloat16().to(dev)
+    meta = M.mask_meta_from_chain_ids(cid.to(dev), pad.to(dev))
+
+    def fwd():
+        with torch.no_grad():
+            return M.multimer_attention(*ts, meta=meta)
+
+    def step():
+        leaves = [t.requires_grad_(True) for t in ts]
+        return torch.autograd.grad(M.multimer_attention(*leaves, meta=meta), leaves, grad)
+
+    res = {}
+    for name, fn in (("fwd", fwd), ("step", step)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        evs = []
+        for _ in range(iters):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        res[name] = statistics.median(a.elapsed_time(b) for a, b in evs)
+    f_fwd = algorithmic_flops(H, T, D, pad, bwd=False)
+    f_all = algorithmic_flops(H, T, D, pad)
+    return {"shape": {"B": B, "H": H, "T": T, "D": D, "chains": "100..900 residues each, padded to T"},
+            "fwd_ms": res["fwd"], "fwd_bwd_ms": res["step"], "fwd_tflops": f_fwd / (res["fwd"] * 1e-3) / 1e12,
+            "fwd_bwd_tflops": f_all / (res["step"] * 1e-3) / 1e12, "launch": "eager", "iters": iters}
 
 
 def cpu_baseline(seconds_budget=20.0):
@@ -165,7 +235,8 @@ def main():
                     help="attn (default: the isolated attention op) or a whole-model workload of bench_model.py: "
                          "mint650m_fp8, mint150m_lora, mint3b_infer, mint8m_fwd, mint650m_fp8_packed, mint3b_infer_packed")
     ap.add_argument("--no-model-metric", action="store_true",
-                    help="attn workload: skip the MINT-650M FP8 pairs/s measurement that is added to the line as `model_650m`")
+                    help="attn workload: skip the model-level measurements that are added to the line as `model_650m`, "
+                         "`model_150m_lora` and `model_3b_infer`")
     ap.add_argument("--layers", type=int, default=0,
                     help="whole-model workloads only: run this many layers instead of the configuration's (a smaller case for "
                          "profiler captures; the line is then not a benchmark value and says so)")
@@ -272,21 +343,33 @@ def main():
     barrier()
     sampler = ClockSampler(local)
     sampler.start()
-    # ---- device-resident inputs: K steps, each bracketed by its own events, L2 flushed between steps
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    # ---- device-resident inputs: sweeps of K steps, each step bracketed by its own events, L2 flushed between steps.
+    # One sweep of this workload lasts a few milliseconds, so the sweep is repeated until MIN_TIMED_SECONDS of device time
+    # have been measured; the line reports the MEDIAN sweep (exactly K steps).
+    sweep_ms = []
     barrier()
-    for s, e in ev:
-        flush.zero_()
-        s.record()
-        run_step()
-        e.record()
+    while True:
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for s, e in ev:
+            flush.zero_()
+            s.record()
+            run_step()
+            e.record()
+        torch.cuda.synchronize()
+        sweep_ms.append(sum(s.elapsed_time(e) for s, e in ev))
+        more = torch.tensor([1.0 if sum(sweep_ms) < MIN_TIMED_SECONDS * 1e3 and len(sweep_ms) < 2000 else 0.0], device=dev)
+        if world > 1:
+            dist.all_reduce(more, op=dist.ReduceOp.MAX)        # every rank runs the same number of sweeps
+        if more.item() == 0.0:
+            break
     barrier()
+    n_sweeps = len(sweep_ms)
     launches = launches_per_step * steps
-    ms_total = sum(s.elapsed_time(e) for s, e in ev)
+    ms_total = statistics.median(sweep_ms)
 
     # ---- the forward call alone (same method); the backward call is the difference
     fwd_ms = []
-    for _ in range(min(steps, 20)):
+    for _ in range(100):
         flush.zero_()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
@@ -344,18 +427,31 @@ def main():
         step_e2e(i)
     drain_e2e()
     barrier()
-    e2e_steps = min(steps, 30)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    flush.zero_()
-    e0.record()
-    for i in range(e2e_steps):
-        step_e2e(i)
-    drain_e2e()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    def time_e2e(n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        flush.zero_()
+        e0.record()
+        for i in range(n):
+            step_e2e(i)
+        drain_e2e()
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1)
+
+    # a short run sizes the timed one so that it lasts at least MIN_TIMED_SECONDS (the same count on every rank)
+    est = torch.tensor([time_e2e(10) / 10], device=dev)
+    if world > 1:
+        dist.all_reduce(est, op=dist.ReduceOp.MIN)
+    e2e_steps = int(min(4000, max(steps, MIN_TIMED_SECONDS * 1e3 / max(est.item(), 1e-3) + 1)))
+    e2e_ms = time_e2e(e2e_steps)
     clocks = sampler.finish()
     ops.check_device_status(dev)
+
+    # ---- the attention shape of the MINT-650M workload (H=20, D=64, T=2048; 8 pairs with chains of 100..900 residues),
+    # timed the same way on rank 0's GPU (eager launches: its kernels last a millisecond), for a second roofline entry
+    d64 = None
+    if rank == 0:
+        d64 = time_shape(M, dev, flush, B=8, H=20, T=2048, D=64, seed=4004, iters=30)
 
     # max over ranks of the timed totals; whole-job work = every rank's flops
     stats = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device=dev)
@@ -366,22 +462,27 @@ def main():
     ms_total, e2e_ms = stats.tolist()
     total_flops_step = float(work.item())
 
-    # The second headline metric, PPI pairs/s of the MINT-650M FP8 forward+backward step, measured in the same run and
-    # attached to the line (a short run of the `mint650m_fp8` workload of bench_model.py; every rank takes part).
-    model_line = None
+    # The model-level metrics, measured in the same run and attached to the line: PPI pairs/s of the MINT-650M FP8
+    # forward+backward step (the second headline metric), of the MINT-150M LoRA training step and of the 36 x 2560
+    # inference forward (short runs of those workloads of bench_model.py; every rank takes part).
+    model_lines = {}
     if not args.no_model_metric:
         import bench_model
         del dts, dgrad, in_bufs, res_bufs, flush
         torch.cuda.empty_cache()
         peaks_m, peak_src_m = load_peaks()
-        try:
-            model_line = bench_model.run("mint650m_fp8", args, rank, world, local, ClockSampler, peaks_m, peak_src_m,
-                                         steps=max(2, min(steps, 4)), with_cpu_baseline=False)
-        except Exception as exc:                       # the attention line must not be lost with it
-            if world > 1:
-                raise                                  # ranks would fall out of step: let the launcher see the failure
-            sys.stderr.write(f"bench: the MINT-650M measurement failed: {exc!r}\n")
-            model_line = {"error": repr(exc)}
+        for key, workload, k_steps in (("model_650m", "mint650m_fp8", max(2, min(steps, 4))),
+                                       ("model_150m_lora", "mint150m_lora", max(2, min(steps, 4))),
+                                       ("model_3b_infer", "mint3b_infer", 2)):
+            try:
+                model_lines[key] = bench_model.run(workload, args, rank, world, local, ClockSampler, peaks_m, peak_src_m,
+                                                   steps=k_steps, with_cpu_baseline=False)
+            except Exception as exc:                   # the attention line must not be lost with it
+                if world > 1:
+                    raise                              # ranks would fall out of step: let the launcher see the failure
+                sys.stderr.write(f"bench: the {workload} measurement failed: {exc!r}\n")
+                model_lines[key] = {"error": repr(exc)}
+            torch.cuda.empty_cache()
     if rank == 0:
         peaks, peak_src = load_peaks()
         value = total_flops_step * steps / (ms_total * 1e-3) / 1e12
@@ -396,20 +497,29 @@ def main():
                        "rope": "self pathway", "l2": "flushed between timed steps (256 MiB write)",
                        "launch": "CUDA graph replay of one step" if use_graph else "eager launches",
                        "flops": "14*H*T*Tk*D per pair, Tk = unpadded keys",
+                       "sweeps": f"{n_sweeps} sweeps of {steps} steps timed ({sum(sweep_ms) * 1e-3:.2f} s of device time); "
+                                 "value and ms_per_step are the median sweep",
                        "e2e": "host->device copies, compute and device->host copies of consecutive steps overlap on three "
                               "streams; every step moves all of its inputs and results"},
             "roofline": {"bound": "tensor", "kernel": dom[0], "achieved": achieved, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES,
+                         "traffic_source": "ncu capture of one launch of the backward kernel at this workload (constant)",
+                         "algorithmic_bytes": algorithmic_bytes(B, H, T, D),
                          "peak_source": peak_src, "fwd_ms": fwd_t, "bwd_ms": bwd_t,
                          "fwd_tflops": flops_fwd / (fwd_t * 1e-3) / 1e12, "bwd_tflops": flops_bwd / (bwd_t * 1e-3) / 1e12},
+            "roofline_d64_t2048": None if d64 is None else {
+                "bound": "tensor", "kernel": "attention forward + backward calls", "achieved": d64["fwd_bwd_tflops"],
+                "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": d64["fwd_bwd_tflops"] / peaks["bf16_tflops"],
+                "traffic": None, "peak_source": peak_src, **d64},
             "e2e": {"value": total_flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
-        if model_line is not None:
-            line["model_650m"] = {k: model_line[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "dtype", "config",
-                                                             "roofline", "e2e", "gpu_launches", "error") if k in model_line}
+        for key, ml in model_lines.items():
+            if ml is not None:
+                line[key] = {k: ml[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "dtype", "config",
+                                                "roofline", "e2e", "gpu_launches", "error") if k in ml}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_baseline()
         print(json.dumps(line), flush=True)

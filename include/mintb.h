@@ -72,6 +72,12 @@ MINTB_API const char* mintb_last_error(void);
  * has no counterpart). */
 MINTB_API unsigned long long mintb_kernel_launches(void);
 
+/* Self-test of the bounded waits (no counterpart in the reference).  Launches a one-CTA kernel with the set-up of the
+ * tensor-core kernels whose consumer waits on a barrier that is never completed; after limit_ns (at most 1e9) the wait
+ * gives up, *dev_status receives 0x901 (if it was 0), TMEM is released and the kernel returns - nothing traps, nothing
+ * spins on.  trail (device int[2], may be NULL) receives {2, 1}: the wait gave up, and TMEM was released after it. */
+MINTB_API int mintb_selftest_wait(unsigned long long limit_ns, int* dev_status, int* trail, void* stream);
+
 /* ---------------------------------------------------------------------------------------------------
  * Mask metadata.  Replaces the (B,T,T) bool tensor the reference builds every step (esm2.py:89) and
  * re-reads per head (modules.py:129-141; multi_pathway_attention.py:101-128): one bit per (query,key)
@@ -128,7 +134,11 @@ MINTB_API int mintb_attn_fwd_static(const void* q_self, const void* k_self, cons
 /* Attention backward.  Replaces fused_multi_pathway_attention_bwd (kernels/multi_pathway_attention_bwd.py:15-59)
  * with what torch.autograd computes through modules.py:129-144: probabilities are recomputed from lse;
  * dq/dk of the self pathway are un-rotated and dq is multiplied by scale, so the six results are the
- * gradients w.r.t. the tensors that were passed to mintb_attn_fwd. */
+ * gradients w.r.t. the tensors that were passed to mintb_attn_fwd.
+ * Reproducibility: dk and dv are reduced in a fixed order and are bit-identical from run to run; on the bf16 tensor-core
+ * path dq is summed over key tiles in fp32 in the order the CTAs happen to arrive (one rounding to bf16 at the end), so
+ * its last bf16 bit may differ between two runs on the same inputs.  The fp32 path (and MINTB_FLAG_FORCE_SIMT) is
+ * bit-reproducible for all six. */
 MINTB_API size_t mintb_attn_bwd_workspace_bytes(int B, int H, int T, int D, int dtype, unsigned flags);
 MINTB_API int mintb_attn_bwd(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
                    const void* k_cross, const void* v_cross, const void* meta, const float* rope_cos,

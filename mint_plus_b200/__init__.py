@@ -10,12 +10,12 @@ from .ops import (MaskMeta, check_device_status, mask_meta_from_chain_ids, mask_
 from .attention import MultiHeadAttention, MultimerAttention
 from .modules_plus import (TransformerLayer_MINT_plus, VanillaFeedForward, build_mint_plus,
                            enable_fused_multi_pathway)
-from .modules import RobertaLMHead, TransformerLayer_MINT
-from .esm2 import MINT, MODEL_REGISTRY, Alphabet
+from .modules import CheckpointedBlock, RobertaLMHead, TransformerLayer_MINT, build_checkpointed_model
+from .esm2 import MINT, MODEL_REGISTRY, SUPPORTED_HEAD_DIMS, Alphabet
 from .training import mlm_corrupt, shared_step
 from .rotary_embedding import RotaryEmbedding
-from .mu_scaling import (Fp8Linear, TransformerLayer_MINT_mu, apply_fp8_to_model, build_mint_mu, calibrate_fp8,
-                         compute_tau, unit_variance_init_)
+from .mu_scaling import (Fp8Linear, TransformerLayer_MINT_mu, apply_fp8_to_model, build_mint_fp8, build_mint_mu,
+                         calibrate_fp8, compute_tau, set_unit_output_scales, unit_variance_init_)
 
 __all__ = [
     "fused_multi_pathway_attention", "differentiable_multi_pathway_attention", "fused_multimer_combine",
@@ -24,5 +24,6 @@ __all__ = [
     "MultiHeadAttention", "MultimerAttention", "TransformerLayer_MINT_plus", "VanillaFeedForward",
     "build_mint_plus", "enable_fused_multi_pathway", "RotaryEmbedding", "Fp8Linear", "apply_fp8_to_model", "calibrate_fp8",
     "unit_variance_init_", "TransformerLayer_MINT", "TransformerLayer_MINT_mu", "RobertaLMHead", "MINT", "MODEL_REGISTRY",
-    "Alphabet", "build_mint_mu", "compute_tau", "mlm_corrupt", "shared_step",
+    "Alphabet", "build_mint_mu", "build_mint_fp8", "compute_tau", "mlm_corrupt", "shared_step", "CheckpointedBlock",
+    "build_checkpointed_model", "set_unit_output_scales", "SUPPORTED_HEAD_DIMS",
 ]

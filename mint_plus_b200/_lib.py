@@ -23,6 +23,7 @@ PROTOTYPES = {
     "mintb_version": (c_int, []),
     "mintb_last_error": (c_char_p, []),
     "mintb_kernel_launches": (c_ulonglong, []),
+    "mintb_selftest_wait": (c_int, [c_ulonglong, _P, _P, _P]),
     "mintb_mask_meta_bytes": (c_size_t, [c_int, c_int]),
     "mintb_mask_meta_from_chain_ids": (c_int, [_P, _P, _P, c_int, c_int, _P]),
     "mintb_mask_meta_from_mask": (c_int, [_P, _P, _P, c_int, c_int, _P]),

@@ -20,18 +20,6 @@ namespace mintb {
 
 using namespace ptx;
 
-// Optional per-warp timeline of one CTA (debug builds with -DMINTB_TRACE only; compiled out otherwise).
-#ifdef MINTB_TRACE
-__device__ unsigned long long g_trace[32 * 512];
-#define MINTB_TRACE_DECL int tr_n = 0; const bool tr_on = (blockIdx.x == 3 && blockIdx.y == 7 && (threadIdx.x % 32) == 0);
-#define MINTB_TRACE_EV(code) do { if (tr_on && tr_n < 510) g_trace[(threadIdx.x / 32) * 512 + (++tr_n)] = ((unsigned long long)clock64() << 8) | (unsigned)(code); } while (0)
-#define MINTB_TRACE_END do { if (tr_on) g_trace[(threadIdx.x / 32) * 512] = tr_n; } while (0)
-#else
-#define MINTB_TRACE_DECL
-#define MINTB_TRACE_EV(code)
-#define MINTB_TRACE_END
-#endif
-
 constexpr int kBM = 128;          // query rows per CTA
 constexpr int kTcThreads = 320;   // producer warp, MMA warp, 8 softmax warps
 constexpr int kTmemCols = 256;
@@ -263,8 +251,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   const int qt = blockIdx.x, bh = blockIdx.y, b = bh / p.H;
   const int q0 = qt * kBM;
   const int nkt = p.NT;  // key tiles of 64 == class-table columns
-  MINTB_TRACE_DECL
-  MINTB_TRACE_EV(1);
 
   if (p.skip_pad_queries) {   // the padding bits describe positions, so they cover the query rows of this tile as well
     const uint32_t* w = p.kpad + size_t(b) * p.TW + 4 * qt;
@@ -334,7 +320,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   tc_fence_after();
   const uint32_t tbase = *tmem_slot;
   const int n_ent = *n_entries_s;
-  MINTB_TRACE_EV(2);
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -344,7 +329,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       for (int it = 0; it < n_ent; ++it) {
         const int stage = it % kStages;
         if (!mbar_wait(&kv_empty[stage], ((it / kStages) & 1) ^ 1, p.status, 0x101)) break;
-        MINTB_TRACE_EV(10);
         const uint8_t c = ent_c[it];
         const int k0 = int(ent_k[it]) * 32;
         unsigned char* kslot = sKV + size_t(stage) * Cfg::kStageBytes;
@@ -389,7 +373,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       auto issue_qk = [&](int it) -> bool {
         const uint32_t stage = uint32_t(it % kStages);
         if (!mbar_wait(&kv_full[stage], (it / kStages) & 1, p.status, 0x202)) return false;
-        MINTB_TRACE_EV(20);
         tc_fence_after();
         const uint8_t c = ent_c[it];
         const uint32_t slot = lo_kv + stage * kStageUnits + kLboK;
@@ -421,7 +404,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         }
         ok = mbar_wait(p_full, it & 1, p.status, 0x203);
         if (!ok) break;
-        MINTB_TRACE_EV(21);
         tc_fence_after();
         const uint8_t c = ent_c[it];
         const uint32_t v_lo = lo_kv + uint32_t(it % kStages) * kStageUnits + kSlot + kLboV;
@@ -452,7 +434,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         }
         umma_commit(o_ready);
         umma_commit(&kv_empty[it % kStages]);
-        MINTB_TRACE_EV(22);
       }
     }
   } else {
@@ -498,7 +479,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       ok = mbar_wait(s_full, it & 1, p.status, 0x301);
       if (!ok) break;
       if (it == 0 && ch == 1) __nanosleep(kStaggerNs);   // the two key halves run out of phase (see kStaggerNs)
-      MINTB_TRACE_EV(30);
       tc_fence_after();
       // Every phase of o_ready is observed, entry by entry (a parity wait cannot tell phases two apart): before O is
       // rescaled or, at the latest, before P (single-buffered) is overwritten.
@@ -533,7 +513,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           tmem_ld_wait();
           tc_fence_before();
           mbar_arrive(s_free);                       // both chunks are in registers: S may be overwritten
-          MINTB_TRACE_EV(31);
 #pragma unroll
           for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(r[j]);
           softmax_chunk<32, SQ>(s, has_pad ? prow[kw + 2 * ch + 1] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk2);
@@ -549,7 +528,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
             }
           }
         }
-        MINTB_TRACE_EV(32);
         ok = see_o();
         if (!ok) break;
         tmem_st16(tP + 32 * ch, pk);
@@ -566,13 +544,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           tmem_ld_wait();
           tc_fence_before();
           mbar_arrive(s_free);
-          MINTB_TRACE_EV(31);
 #pragma unroll
           for (int j = 0; j < W; ++j) s[j] = __uint_as_float(r[j]);
           softmax_chunk<W, SQ>(s, has_pad ? prow[kw + ch] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
         }
         if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
-        MINTB_TRACE_EV(32);
         ok = see_o();
         if (!ok) break;
         tmem_st16(tP + (W / 2) * ch, pk);
@@ -593,7 +569,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           tmem_ld_wait();
           tc_fence_before();
           mbar_arrive(s_free);
-          MINTB_TRACE_EV(31);
 #pragma unroll
           for (int j = 0; j < W; ++j) s[j] = __uint_as_float(((cw >> j) & 1u) ? rc[j] : rs[j]);
           softmax_chunk<W, SQ>(s, pw, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
@@ -608,17 +583,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           pe[j] = pk[j] & keep_e;
           pi[j] = pk[j] & ~keep_e;
         }
-        MINTB_TRACE_EV(32);
         ok = see_o();
         if (!ok) break;
         tmem_st_n<W / 2>(tP + (W / 2) * ch, pi);
         tmem_st_n<W / 2>(tP + kBox / 2 + (W / 2) * ch, pe);
       }
       tmem_st_wait();
-      MINTB_TRACE_EV(33);
       tc_fence_before();
       mbar_arrive(p_full);
-      MINTB_TRACE_EV(36);
     }
     // ---- epilogue: merge the two softmax states of each row, O / l -> bf16, lse
     float* hm = hstat;          // [2][128] running maxima
@@ -676,8 +648,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       }
     }
   }
-  MINTB_TRACE_EV(3);
-  MINTB_TRACE_END;
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -685,12 +655,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     tmem_dealloc(tbase, kTmemCols);
   }
 }
-
-#ifdef MINTB_TRACE
-extern "C" __attribute__((visibility("default"))) int mintb_trace_read(unsigned long long* dst) {
-  return int(cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace)));
-}
-#endif
 
 // ------------------------------------------------------------------------------------------------ host side
 bool tc_supported(int D, int dtype) { return dtype == MINTB_BF16 && (D == 16 || D == 32 || D == 64); }

@@ -20,18 +20,6 @@ namespace mintb {
 
 using namespace ptx;
 
-// Optional per-warp timeline of one CTA (debug builds with -DMINTB_TRACE only; compiled out otherwise).
-#ifdef MINTB_TRACE
-__device__ unsigned long long g_trace_bwd[32 * 512];
-#define MINTB_BTRACE_DECL int tr_n = 0; const bool tr_on = (blockIdx.x == 2 && blockIdx.y == 7 && blockIdx.z == 0 && (threadIdx.x % 32) == 0);
-#define MINTB_BTRACE_EV(code) do { if (tr_on && tr_n < 510) g_trace_bwd[(threadIdx.x / 32) * 512 + (++tr_n)] = ((unsigned long long)clock64() << 8) | (unsigned)(code); } while (0)
-#define MINTB_BTRACE_END do { if (tr_on) g_trace_bwd[(threadIdx.x / 32) * 512] = tr_n; } while (0)
-#else
-#define MINTB_BTRACE_DECL
-#define MINTB_BTRACE_EV(code)
-#define MINTB_BTRACE_END
-#endif
-
 constexpr int kBwdTile = 128;       // keys per CTA and queries per step
 constexpr int kHalf = 64;           // queries per compute group
 constexpr int kBwdMaxTiles = 256;   // T <= 32768
@@ -211,22 +199,18 @@ struct BwdCfg {
   static constexpr int kTileBytes = kBwdTile * kRowBytes;       // K, V, Q_i, dO_i tiles
   static constexpr int kDsBlock = kBwdTile * 128;               // one half (64 queries) of dS: [128 key rows][128 B]
   static constexpr int kDsBytes = 2 * kDsBlock;
-  // Two shapes are provided.  The one in use: one CTA per SM, 16 compute warps, all 512 TMEM columns: dK, dV, two dQ tiles,
-  // then two (head_dim 64) or three (head_dim <= 32) buffers of {S^T half (64 columns), dP^T half (64 columns)}; the third
-  // buffer lets the products run two halves ahead of the compute warps.  The other (kTwoPerSm): two CTAs per SM, each with
-  // 8 compute warps and 256 columns (dK, dV, one dQ tile, one buffer); measured slower at B8 H20 T1024 D32 (0.37 ms against
-  // 0.31 ms): with a single buffer the products and the elementwise work of a CTA alternate and two CTAs do not fill the gaps.
-  static constexpr bool kTwoPerSm = false;
-  static constexpr int kCW = kTwoPerSm ? 8 : 16;                // compute warps
+  // One CTA per SM, 16 compute warps, all 512 TMEM columns: dK, dV, two dQ tiles, then two (head_dim 64) or three
+  // (head_dim <= 32) buffers of {S^T half (64 columns), dP^T half (64 columns)}; the third buffer lets the products run
+  // two halves ahead of the compute warps.
+  static constexpr int kCW = 16;                                // compute warps
   static constexpr int kThreads = 128 + 32 * kCW;
-  static constexpr int kMinBlocks = kTwoPerSm ? 2 : 1;
-  static constexpr int kNBuf = kTwoPerSm ? 1 : (D <= 32 ? 3 : 2);
-  static constexpr int kNDq = kTwoPerSm ? 1 : 2;                // dQ tiles in TMEM == dS tiles in shared memory
-  static constexpr int kQStages = (!kTwoPerSm && D <= 32) ? 3 : 2;   // stages of {Q_i, dO_i}
+  static constexpr int kNBuf = D <= 32 ? 3 : 2;
+  static constexpr int kNDq = 2;                                // dQ tiles in TMEM == dS tiles in shared memory
+  static constexpr int kQStages = D <= 32 ? 3 : 2;              // stages of {Q_i, dO_i}
   static constexpr int kAcc = D <= 32 ? 32 : 64;                // columns reserved per accumulator
   static constexpr int kColDK = 0, kColDV = kAcc, kColDQ = 2 * kAcc, kColBuf = (2 + kNDq) * kAcc;
-  static constexpr uint32_t kTmemCols = kTwoPerSm ? 256 : 512;
-  static constexpr int kVPG = 16 / kCW;                         // 16-column query groups per thread and half (1 or 2)
+  static constexpr uint32_t kTmemCols = 512;
+  static constexpr int kVPG = 16 / kCW;                         // 16-column query groups per thread and half
   static constexpr int kDqWarpBytes = 32 * (D / 4) * 4;          // staging of one warp's dQ slice: 32 queries x D/4 fp32 columns
   static constexpr int kDqStageBytes = kCW * kDqWarpBytes;
   static constexpr int kStatBytes = 128 * 8;                     // softmax statistics of one query tile: 128 x (-lse log2 e, -delta)
@@ -261,7 +245,7 @@ struct Ring {
 };
 
 template <int D, bool SQ>
-__global__ void __launch_bounds__(BwdCfg<D>::kThreads, BwdCfg<D>::kMinBlocks)
+__global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_constant__ CUtensorMap map_ks,
                    const __grid_constant__ CUtensorMap map_vs, const __grid_constant__ CUtensorMap map_qc,
                    const __grid_constant__ CUtensorMap map_kc, const __grid_constant__ CUtensorMap map_vc,
@@ -295,8 +279,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int kt = blockIdx.x, bh = blockIdx.y, path = blockIdx.z, b = bh / p.H;
-  MINTB_BTRACE_DECL
-  MINTB_BTRACE_EV(1);
   const int k0 = kt * kBwdTile;
   const int nqt = (p.T + kBwdTile - 1) / kBwdTile;
   const uint8_t want = path == 0 ? kHasIntra : kHasInter;
@@ -353,7 +335,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = *tmem_slot;
-  MINTB_BTRACE_EV(2);
   int n_active = 0;
   for (int i = 0; i < nqt; ++i) n_active += tq[i] != 0;
   const int n_sub = 2 * n_active;   // 64-query halves, numbered u = 2 * tile + half; half u lives in buffer u % kNBuf
@@ -398,10 +379,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       for (int u = 0; issued < n_sub && ok; ++u, ++issued) {
         ok = mbar_wait(&buf_free[wb.pos], wb.phase, p.status, 0x505);   // dV and dK of half u have consumed P^T, dS^T
         if (!ok) break;
-        MINTB_BTRACE_EV(10);
         wb.advance();
         ok = issue_sdp(issued);
-        MINTB_BTRACE_EV(11);
       }
     }
   } else if (warp == 2 || warp == 3) {
@@ -424,14 +403,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         for (int h = 0; h < 2 && ok; ++h) {
           ok = mbar_wait(&pds_full[br.pos], br.phase, p.status, 0x512);
           if (!ok) break;
-          MINTB_BTRACE_EV(20);
           tc_fence_after();
           const uint32_t rows = b_lo + qr.pos * 2 * kTileU + h * kHalfU;
 #pragma unroll
           for (int k = 0; k < kHalf / 16; ++k)
             umma_ts(d_col, a_col + br.pos * 128 + k * 16, make_desc(kHi, rows + k * kStep), idesc_acc, it > 0 || h > 0 || k > 0);
           umma_commit(&buf_free[br.pos]);
-          MINTB_BTRACE_EV(21);
           br.advance();
         }
         if (ok) umma_commit(&q_empty[qr.pos]);
@@ -479,14 +456,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         br.advance();
         if (ok) ok = mbar_wait(&dq_empty[it % kNDq], ((it / kNDq) & 1) ^ 1, p.status, 0x524);   // buffer drained kNDq tiles ago
         if (!ok) break;
-        MINTB_BTRACE_EV(30);
         tc_fence_after();
         const uint32_t a_lo = ds_lo + uint32_t(it % kNDq) * kDsU;
 #pragma unroll
         for (int k = 0; k < kBwdTile / 16; ++k)
           umma_ss(tbase + kColDQ + (it % kNDq) * kAcc, make_desc(kHiA, a_lo + k * kAStep), make_desc(kHiB, kb_lo + k * kBStep), idesc_dq, k > 0);
         umma_commit(&dq_full[it % kNDq]);
-        MINTB_BTRACE_EV(31);
         if (it + kQStages < n_active) {   // this tile's stage is released by its dV and dK streams
           ok = mbar_wait(&q_empty[er.pos], er.phase, p.status, 0x525);
           if (ok) load_next();
@@ -554,11 +529,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       // mask bits of the tile for this key row: half `sub`, 16-column group vg -> word 2 sub + vg / 2, bits 16 (vg & 1)...
 #pragma unroll 1
       for (int sub = 0; sub < 2 && ok; ++sub) {
-        if (kNDq == 1 && sub == 0 && prev_tile >= 0) {   // the single dS tile in shared memory is about to be overwritten:
-          ok = drain_dq(it - 1, prev_tile);               // the dQ product that reads it must have completed
-          if (!ok) break;
-        }
-        MINTB_BTRACE_EV(40);
         ok = mbar_wait(&sdp_full[br.pos], br.phase, p.status, 0x602);
         if (!ok) break;
         if (sub == 0) {   // the tile's loads have landed long ago (its products are done): this only orders the reads below
@@ -566,7 +536,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           if (!ok) break;
         }
         if (it == 0 && sub == 0 && grp >= 2) __nanosleep(kBwdStaggerNs);
-        MINTB_BTRACE_EV(41);
         tc_fence_after();
         unsigned char* ds_row = sDS + size_t(it % kNDq) * Cfg::kDsBytes + size_t(sub) * Cfg::kDsBlock;
 #pragma unroll
@@ -586,7 +555,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           tmem_ld16(tS, sv);
           tmem_ld16(tS + 64, dpv);
           tmem_ld_wait();
-          MINTB_BTRACE_EV(42);
           uint32_t pp[8], dd[8];
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
@@ -614,17 +582,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
           *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 2 * vg, 128)) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
           *reinterpret_cast<uint4*>(ds_row + swizzled_offset(r, 2 * vg + 1, 128)) = make_uint4(dd[4], dd[5], dd[6], dd[7]);
         }
-        MINTB_BTRACE_EV(43);
         tmem_st_wait();
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(&pds_full[br.pos]);
-        MINTB_BTRACE_EV(44);
         br.advance();
       }
       if (!ok) break;
-      if (kNDq > 1 && prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
-      MINTB_BTRACE_EV(45);
+      if (prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
       prev_tile = i;
       sr.advance();
       ++it;
@@ -637,7 +602,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     if (n_active > 0) {
       if (ok) ok = mbar_wait(acc_full, 0, p.status, 0x603);
       tc_fence_after();
-      MINTB_BTRACE_EV(46);
     }
     ok = __all_sync(0xffffffffu, ok);   // the stores below exchange rows between the lanes of the warp
     if (ok) {
@@ -725,8 +689,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       }
     }
   }
-  MINTB_BTRACE_EV(3);
-  MINTB_BTRACE_END;
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -734,12 +696,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     tmem_dealloc(tbase, Cfg::kTmemCols);
   }
 }
-
-#ifdef MINTB_TRACE
-extern "C" __attribute__((visibility("default"))) int mintb_trace_read_bwd(unsigned long long* dst) {
-  return int(cudaMemcpyFromSymbol(dst, g_trace_bwd, sizeof(g_trace_bwd)));
-}
-#endif
 
 // ------------------------------------------------------------------------------------------------ host side
 static size_t bwd_rot_bytes(int B, int H, int T, int D) { return align256(size_t(B) * H * T * D * 2); }

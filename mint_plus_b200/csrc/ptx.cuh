@@ -62,11 +62,11 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// Bounded wait: gives up once `kWaitLimitNs` of wall time have passed (checked every 1024 polls), records `code` in
+// Bounded wait: gives up once `limit_ns` (kWaitLimitNs for every wait of the library's kernels) of wall time have passed (checked every 1024 polls), records `code` in
 // *status (if non-null) and returns false.  Callers unwind (skip the rest of their work, still release TMEM)
 // instead of spinning forever.  The common case - the phase has already completed - costs one test.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, int* status, int code, uint64_t limit_ns) {
   if (mbar_test_wait(bar, parity)) return true;
 #pragma unroll 1
   for (int it = 0; it < 1024; ++it)   // ordinary waits end here; the timer (slow to read) is not touched
@@ -76,10 +76,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
 #pragma unroll 1
     for (int it = 0; it < 1024; ++it)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    if (global_timer_ns() - t0 > limit_ns) break;
   }
   if (status != nullptr) atomicCAS(status, 0, code);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  return mbar_wait_limit(bar, parity, status, code, kWaitLimitNs);
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

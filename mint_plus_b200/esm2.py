@@ -25,6 +25,21 @@ MODEL_REGISTRY = {
     "15B": dict(name="esm2_t48_15B_UR50D", num_layers=48, embed_dim=5120, attention_heads=20, intermediate_size=20480),
 }
 
+# Head sizes the CUDA attention kernels take, and the widest rows the fused residual + LayerNorm kernels take.  The
+# registry's "35M" (head size 24), "3B" (head size 112) and "15B" (head size 256, rows of 5120) entries are kept for their names and shapes
+# (state dicts can be inspected on the CPU); running them on the GPU raises NotImplementedError.
+SUPPORTED_HEAD_DIMS = (16, 32, 64)
+MAX_EMBED_DIM = 2560
+
+
+def check_supported_shape(embed_dim: int, attention_heads: int) -> None:
+    """Raise NotImplementedError for a model shape the CUDA path cannot run (there is no eager fallback)."""
+    head_dim = embed_dim // attention_heads
+    if head_dim not in SUPPORTED_HEAD_DIMS or embed_dim > MAX_EMBED_DIM:
+        raise NotImplementedError(
+            f"embed_dim={embed_dim}, attention_heads={attention_heads} (head size {head_dim}) is outside what the CUDA kernels "
+            f"of this package run: head sizes {SUPPORTED_HEAD_DIMS}, embed_dim <= {MAX_EMBED_DIM}")
+
 
 class Alphabet:
     """The ESM-1b token table: 33 entries, <cls>=0, <pad>=1, <eos>=2, <unk>=3, amino acids from 4, <mask>=32."""
@@ -183,6 +198,7 @@ class MINT(nn.Module):
         if model_size not in MODEL_REGISTRY:
             raise ValueError(f"Unknown model size: {model_size}. Available: {list(MODEL_REGISTRY)}")
         cfg = MODEL_REGISTRY[model_size]
+        check_supported_shape(cfg["embed_dim"], cfg["attention_heads"])
         return cls(num_layers=cfg["num_layers"], embed_dim=cfg["embed_dim"], attention_heads=cfg["attention_heads"],
                    fp8=fp8, use_erf_gelu=use_erf_gelu)
 

@@ -7,6 +7,8 @@ same fused CUDA operator as the `_plus` layer; the three weights of a pathway ar
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 import torch.nn.functional as F
 from torch import nn
@@ -40,3 +42,39 @@ class RobertaLMHead(nn.Module):
     def forward(self, features):
         x = self.layer_norm(F.gelu(self.dense(features)))
         return F.linear(x, self.weight) + self.bias
+
+
+class CheckpointedBlock(nn.Module):
+    """A run of consecutive layers that `MINT.forward` treats (and checkpoints) as one layer: same call signature and
+    `(x, None)` result as a single layer (modules.py:420-457 of the reference)."""
+
+    def __init__(self, layers: nn.ModuleList):
+        super().__init__()
+        self.layers = layers
+
+    def forward(self, x, self_attn_padding_mask: Optional[torch.Tensor] = None, self_attn_mask: Optional[torch.Tensor] = None,
+                chain_ids: Optional[torch.Tensor] = None, pack=None):
+        kw = dict(self_attn_padding_mask=self_attn_padding_mask, self_attn_mask=self_attn_mask, chain_ids=chain_ids)
+        if pack is not None:
+            kw["pack"] = pack
+        for layer in self.layers:
+            x, _ = layer(x, **kw)
+        return x, None
+
+    def __len__(self):
+        return len(self.layers)
+
+    def __getitem__(self, idx):
+        return self.layers[idx]
+
+
+def build_checkpointed_model(model: nn.Module, block_size: int = 3) -> nn.Module:
+    """Group `model.layers` into CheckpointedBlocks of `block_size` layers, in place; `block_size` must divide the number
+    of layers (modules.py:460-510 of the reference)."""
+    layers = list(model.layers)
+    if block_size <= 0 or len(layers) % block_size != 0:
+        raise ValueError(f"block_size={block_size} does not evenly divide {len(layers)} layers. Try a different block_size.")
+    model.layers = nn.ModuleList(CheckpointedBlock(nn.ModuleList(layers[i:i + block_size]))
+                                 for i in range(0, len(layers), block_size))
+    model._checkpoint_block_size = block_size
+    return model

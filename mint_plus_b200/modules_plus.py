@@ -116,6 +116,9 @@ class _TwoPathwayLayer(nn.Module):
         else:
             (T, B), E = (pack.T, pack.B), x.shape[-1]
         sa, ma = self.self_attn, self.multimer_attn
+        if sa.head_dim not in (16, 32, 64):
+            raise NotImplementedError(f"head size {sa.head_dim}: the CUDA attention kernels take head sizes 16, 32 and 64 "
+                                      "(there is no eager fallback)")
         if chain_ids is not None and chain_mask is None:
             mask_kw = dict(meta=_cached_ids_meta(chain_ids, padding_mask))
         else:
@@ -129,18 +132,11 @@ class _TwoPathwayLayer(nn.Module):
             # bf16 activations on the GPU: the QKV GEMMs (bf16 or e4m3 operands) write q, k, v head-major and rotate the self
             # pathway in their epilogue, so the attention kernel gets ready-made operands (no permute copies, no rotation pass)
             tabs = ops.rope_tables(T, sa.head_dim, x.device, sa.rot_emb.inv_freq)[:2] if rope else None
-            if sa.head_dim in (16, 32, 64):
-                # projections and attention as one differentiable step: on the way back the attention kernels write
-                # [dQ | dK | dV] row-major (only the unpadded tokens' rows when packed) for the projections' products
-                meta = mask_kw["meta"] if "meta" in mask_kw else ops.cached_mask_meta(chain_mask, padding_mask)
-                attn_out = ops.qkv_attention(x, ops_s, ops_c, sa.num_heads, meta, rope=tabs, scale=sa.scaling,
-                                             sqrt_softmax=sqrt_sm, pack=pack, skip_pad_queries=pack is not None)
-            else:   # head sizes the tensor-core attention does not take: fp32-arithmetic kernels, gradients gathered by a pass
-                q_s, k_s, v_s = ops.qkv_project(x, ops_s[0], ops_s[1], sa.num_heads, rope=tabs, fp8=ops_s[2], pack=pack, lora=ops_s[3])
-                q_c, k_c, v_c = ops.qkv_project(x, ops_c[0], ops_c[1], ma.num_heads, fp8=ops_c[2], pack=pack, lora=ops_c[3])
-                attn_out = ops.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, rope=False, scale=sa.scaling,
-                                                  sqrt_softmax=sqrt_sm, out_seq_first=True, skip_pad_queries=pack is not None,
-                                                  **mask_kw)
+            # projections and attention as one differentiable step: on the way back the attention kernels write
+            # [dQ | dK | dV] row-major (only the unpadded tokens' rows when packed) for the projections' products
+            meta = mask_kw["meta"] if "meta" in mask_kw else ops.cached_mask_meta(chain_mask, padding_mask)
+            attn_out = ops.qkv_attention(x, ops_s, ops_c, sa.num_heads, meta, rope=tabs, scale=sa.scaling,
+                                         sqrt_softmax=sqrt_sm, pack=pack, skip_pad_queries=pack is not None)
         elif pack is not None:
             raise NotImplementedError("packed tokens need bfloat16 CUDA activations and nn.Linear / Fp8Linear projections")
         else:

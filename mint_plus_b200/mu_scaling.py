@@ -283,10 +283,12 @@ def build_mint_mu(model_size: str = "150M", use_multimer: bool = True, tau: Opti
     `num_layers`/`embed_dim`/`attention_heads` override the registry entry (for shapes the registry does not hold).
     `unit_scaled=True` applies `unit_variance_init_` and gives every projection the static 1/sqrt(fan_in) output
     multiplier that keeps unit-variance activations (mu_scaling/init.py:59-72 describes it; the reference builder leaves
-    it switched off).  Warm start from ESM-2 files and block checkpointing are outside this package."""
+    it switched off).  `checkpoint_block_size` > 0 groups the layers into CheckpointedBlocks.  Warm start from ESM-2
+    files is outside this package."""
     from .esm2 import MINT, MODEL_REGISTRY
-    if warm_start_esm2 or checkpoint_block_size:
-        raise NotImplementedError("warm_start_esm2 / checkpoint_block_size are not part of this package")
+    from .modules import build_checkpointed_model
+    if warm_start_esm2:
+        raise NotImplementedError("warm_start_esm2 is not part of this package (load a state dict instead)")
     cfg = MODEL_REGISTRY[model_size]
     L_ = num_layers or cfg["num_layers"]
     E_ = embed_dim or cfg["embed_dim"]
@@ -301,12 +303,31 @@ def build_mint_mu(model_size: str = "150M", use_multimer: bool = True, tau: Opti
         layer._use_fused_multi_pathway = use_fused_multi_pathway
     if unit_scaled:
         unit_variance_init_(model)
+    if checkpoint_block_size > 0:
+        build_checkpointed_model(model, block_size=checkpoint_block_size)
     if use_fp8:
         apply_fp8_to_model(model, static_scale=fp8_static_scale)
     if unit_scaled:
         set_unit_output_scales(model)
     model._mu_config = {"tau": tau, "use_sqrt_softmax": use_sqrt_softmax, "use_fp8": use_fp8, "unit_scaled": unit_scaled}
     return model
+
+
+def build_mint_fp8(model_size: str = "150M", use_multimer: bool = True, static_scale: bool = True,
+                   checkpoint_block_size: int = 3, use_fused_multi_pathway: bool = True):
+    """The Pre-LN MINT of a registry size with every hidden projection swapped for Fp8Linear
+    (mu_scaling/__init__.py:269-312): standard architecture and state-dict names, so pre-trained weights load unchanged;
+    layers grouped into CheckpointedBlocks of `checkpoint_block_size` (0: none).  Returned on the CPU."""
+    from .esm2 import MINT, MODEL_REGISTRY
+    from .modules import build_checkpointed_model
+    from .modules_plus import enable_fused_multi_pathway
+    cfg = MODEL_REGISTRY[model_size]
+    model = MINT(num_layers=cfg["num_layers"], embed_dim=cfg["embed_dim"], attention_heads=cfg["attention_heads"],
+                 use_multimer=use_multimer)
+    enable_fused_multi_pathway(model, enabled=use_fused_multi_pathway)
+    if checkpoint_block_size > 0:
+        build_checkpointed_model(model, block_size=checkpoint_block_size)
+    return apply_fp8_to_model(model, static_scale=static_scale)
 
 
 def set_unit_output_scales(model: nn.Module) -> nn.Module:

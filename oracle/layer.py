@@ -1,0 +1,155 @@
+"""CPU restatement of one MINT layer with the rounding points of the bf16 / e4m3 GPU path.
+
+TEST INFRASTRUCTURE ONLY.  Tests import it as the checker of the layer-level GPU path; the product package
+never does.  It composes, on the CPU in fp32,
+
+  * the projections          nn.Linear arithmetic, or the per-tensor-scaled e4m3 arithmetic of
+                             mint_plus/models/alt/munit_scaling.py:22-34 (`fp8_e4m3_linear` of this package) with the
+                             straight-through gradients of lines 36-55 taken on the un-quantised operands,
+  * the attention            `oracle.multimer_attention` (mint_plus/models/modules.py:129-144, mu_scaling/layer.py:159-165),
+  * the layer glue           Pre-LN (mint_plus/models/modules.py:179-195) or muS Res-Post-LN
+                             (mint_plus/models/mu_scaling/layer.py:259-280),
+
+and rounds every tensor that the GPU path stores as bf16 to bf16 (straight-through for autograd), so that a GPU layer
+can be compared at a tolerance of a few bf16 steps instead of the accumulated quantisation error of the number format.
+FP8 parity is unpinned: transformer_engine 2.16.0, which holds the production FP8 arithmetic, is neither vendored in the
+reference nor installed here; the e4m3 branch checks the restated formula only.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import multimer_attention as O
+
+E4M3_MAX = 448.0
+
+
+class _RoundBf16(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        return x.bfloat16().float()
+
+    @staticmethod
+    def backward(ctx, g):
+        return g
+
+
+def bf16r(x: torch.Tensor) -> torch.Tensor:
+    """Round to bf16 (kept as fp32); the gradient passes straight through."""
+    return _RoundBf16.apply(x)
+
+
+def weight_scale(*weights: torch.Tensor) -> float:
+    """Per-tensor e4m3 scale amax / 448 of one weight, or of several that share a scale (fused Q/K/V)."""
+    return max(max(float(w.detach().abs().amax()) for w in weights), 1e-12) / E4M3_MAX
+
+
+def quant_e4m3(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """saturate(x * (1 / scale)) rounded to e4m3, returned as fp32 (still divided by the scale)."""
+    inv = torch.tensor(1.0 / scale, dtype=torch.float32)
+    return (x.float() * inv).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).float()
+
+
+class _QuantLinear(torch.autograd.Function):
+    """y = (x_scale w_scale out_scale) q(x) q(w)^T + b; gradients as for y = out_scale x w^T + b (straight-through)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, x_scale, w_scale, out_scale):
+        alpha = torch.tensor(float(x_scale) * float(w_scale) * float(out_scale), dtype=torch.float32)
+        y = (quant_e4m3(x, x_scale) @ quant_e4m3(w, w_scale).t()) * alpha
+        if b is not None:
+            y = y + b.float()
+        ctx.save_for_backward(x, w)
+        ctx.out_scale = float(out_scale)
+        ctx.has_bias = b is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dx = (dy @ w) * ctx.out_scale
+        dw = (dy.t() @ x) * ctx.out_scale
+        return dx, dw, (dy.sum(0) if ctx.has_bias else None), None, None, None
+
+
+def linear(x2d, w, b, fp8: Optional[dict] = None, w_scale: Optional[float] = None, x_is_e4m3: bool = False):
+    """fp32 result of one projection on rows x2d [M,K] (not yet rounded to bf16).  `fp8` = {"x_scale", "out_scale"} selects the
+    e4m3 arithmetic; `w_scale` overrides amax(w)/448 (fused Q/K/V weights share one scale)."""
+    if fp8 is None:
+        return F.linear(x2d, w, b)
+    ws = weight_scale(w) if w_scale is None else w_scale
+    return _QuantLinear.apply(x2d, w, b, fp8.get("x_scale", 1.0), ws, fp8.get("out_scale", 1.0))
+
+
+def _heads(t2d, T, B, H, D):
+    return t2d.reshape(T, B, H, D).permute(1, 2, 0, 3)
+
+
+def _qkv(attn, x2d, T, B, H, D, rope: bool, fp8):
+    """q, k, v (B,H,T,D) of one pathway as the fused QKV GEMM leaves them: bias added, q and k rotated in fp32, then bf16."""
+    if getattr(attn, "fused_qkv", None) is not None:
+        w, b = attn.fused_qkv.weight, attn.fused_qkv.bias
+    else:
+        w = torch.cat([attn.q_proj.weight, attn.k_proj.weight, attn.v_proj.weight], dim=0)
+        b = torch.cat([attn.q_proj.bias, attn.k_proj.bias, attn.v_proj.bias], dim=0) if attn.q_proj.bias is not None else None
+    qkv = linear(x2d, w, b, fp8)
+    q, k, v = (_heads(t, T, B, H, D) for t in qkv.chunk(3, dim=-1))
+    if rope:
+        q, k = O.apply_rope(q), O.apply_rope(k)
+    return bf16r(q), bf16r(k), bf16r(v)
+
+
+def attention_block(layer, x, chain_mask, key_pad, fp8=None, sqrt_softmax=False):
+    """x (T,B,E) -> out_proj(attention) (T,B,E), every stored tensor rounded to bf16."""
+    T, B, E = x.shape
+    sa, ma = layer.self_attn, layer.multimer_attn
+    H = sa.num_heads
+    D = E // H
+    x2d = x.reshape(T * B, E)
+    q_s, k_s, v_s = _qkv(sa, x2d, T, B, H, D, sa.rot_emb is not None, fp8)
+    q_c, k_c, v_c = _qkv(ma, x2d, T, B, H, D, False, fp8)
+    a = O.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, chain_mask, key_pad, scale=D ** -0.5, rope=False,
+                             sqrt_softmax=sqrt_softmax)
+    a = bf16r(a.permute(2, 0, 1, 3).reshape(T * B, E))
+    return bf16r(linear(a, sa.out_proj.weight, sa.out_proj.bias, fp8)).reshape(T, B, E)
+
+
+def feed_forward(layer, x, fp8=None):
+    """fc2(gelu_erf(fc1(x))).  bf16 path: gelu(.) is stored as bf16 between the products; e4m3 path: fc1's epilogue casts
+    gelu(.) straight to fc2's e4m3 operand from the fp32 value (fc2's activation scale), no bf16 copy in between."""
+    T, B, E = x.shape
+    ff = layer.feed_forward
+    z = linear(x.reshape(T * B, E), ff.fc1.weight, ff.fc1.bias, fp8)
+    g = O.gelu_erf(z)
+    if fp8 is None:
+        g = bf16r(g)
+    return bf16r(linear(g, ff.fc2.weight, ff.fc2.bias, fp8)).reshape(T, B, E)
+
+
+def mu_layer(layer, x, chain_mask, key_pad, tau: float, fp8=None, sqrt_softmax=False):
+    """muS Res-Post-LN layer (mu_scaling/layer.py:259-280): x = sqrt(1-tau) x + sqrt(tau) attn(x);
+    x = sqrt(1-tau) x + sqrt(tau) ffn(x); LayerNorm.  The first residual sum is stored (bf16), the second feeds the
+    LayerNorm in fp32, as the fused residual + LayerNorm pass computes it."""
+    keep, add = math.sqrt(1.0 - tau), math.sqrt(tau)
+    a = attention_block(layer, x, chain_mask, key_pad, fp8, sqrt_softmax)
+    s1 = bf16r(keep * x + add * a)
+    s2 = keep * s1 + add * feed_forward(layer, s1, fp8)
+    ln = layer.final_layer_norm
+    return bf16r(F.layer_norm(s2, (s2.shape[-1],), ln.weight, ln.bias, ln.eps))
+
+
+def pre_ln_layer(layer, x, chain_mask, key_pad, fp8=None):
+    """Pre-LN layer (modules.py:179-195): x + attn(LN(x)), then + ffn(LN(.)); LayerNorm results and the residual sums
+    are stored as bf16."""
+    E = x.shape[-1]
+    n1, n2 = layer.self_attn_layer_norm, layer.final_layer_norm
+    h = bf16r(F.layer_norm(x, (E,), n1.weight, n1.bias, n1.eps))
+    a = attention_block(layer, h, chain_mask, key_pad, fp8)
+    s = x + a
+    y = bf16r(s)
+    h2 = bf16r(F.layer_norm(s, (E,), n2.weight, n2.bias, n2.eps))
+    return bf16r(y + feed_forward(layer, h2, fp8))

@@ -119,3 +119,13 @@ def test_pack_padding_refuses_cpu_tensors():
     tokens = torch.tensor([[0, 5, 6, 2, 1, 1]])
     with pytest.raises(NotImplementedError):
         model(tokens, torch.zeros_like(tokens))
+
+
+def test_benchmark_input_generator_draws_the_oracle_generators_numbers():
+    """bench.py carries its own copy of the seeded input generator (its measured arm imports nothing from oracle/)."""
+    import bench
+    a = bench.make_op_inputs(2, 3, 256, 32, seed=2002)
+    b = O.make_op_inputs(2, 3, 256, 32, seed=2002)
+    for x, y in zip(a[0], b[0]):
+        assert torch.equal(x, y)
+    assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])

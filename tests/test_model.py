@@ -14,6 +14,9 @@ from mint_plus_b200 import modules_plus, ops
 from oracle import multimer_attention as O
 from oracle.seeded_weights import c1_batch, fill_state_dict_
 
+# Six layers of fp32 arithmetic whose sums run in another order than the reference's CPU kernels (tiled attention with an
+# online softmax, warp-shuffle LayerNorm sums, split-K-free but differently blocked matrix products).
+FP32_MODEL_RTOL = 4e-5
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 CASES = ["mint8m_small", "mint8m_mu", "mint8m_mu_sqrt", "mint8m_c1"]
 
@@ -108,7 +111,9 @@ def test_model_fp32_matches_reference_logits(name):
     ops.check_device_status()
     got, want = res["logits"].cpu().numpy(), z["logits"]
     # fp32 tolerance: 1e-5 relative to the logits' scale (values are O(1..5))
-    assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max()) * 4, np.abs(got - want).max()
+    rel = np.abs(got - want).max() / max(1.0, np.abs(want).max())
+    print(f"{name}: fp32 logits max err / scale = {rel:.3g}")
+    assert rel <= FP32_MODEL_RTOL, rel
     np.testing.assert_allclose(res["representations"][6][:, ::8].cpu().numpy(), z["repr6"], rtol=1e-4, atol=4e-5)
 
 
