@@ -23,8 +23,21 @@ def apply_rotary_pos_emb(x, cos, sin):
 class RotaryEmbedding(torch.nn.Module):
     def __init__(self, dim: int, *_, **__):
         super().__init__()
-        inv_freq = 1.0 / (10000 ** (torch.arange(0, dim, 2).float() / dim))
-        self.register_buffer("inv_freq", inv_freq)
+        self.dim = dim
+        self.register_buffer("inv_freq", self._frequencies(dim))
+
+    @staticmethod
+    def _frequencies(dim: int, device=None) -> torch.Tensor:
+        return 1.0 / (10000 ** (torch.arange(0, dim, 2, device=device).float() / dim))
+
+    def _apply(self, fn, *args, **kwargs):
+        # A cast of the whole model (model.to(torch.bfloat16)) would round the frequencies to 8 bits, and a later .float()
+        # does not bring them back: at position 2000 the angles are then off by radians.  The buffer therefore stays fp32:
+        # after a cast it is rebuilt from `dim` on the device it has moved to.
+        super()._apply(fn, *args, **kwargs)
+        if self.inv_freq.dtype != torch.float32:
+            self.inv_freq = self._frequencies(self.dim, self.inv_freq.device)
+        return self
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         seq_len = x.shape[-2]

@@ -129,3 +129,14 @@ def test_benchmark_input_generator_draws_the_oracle_generators_numbers():
     for x, y in zip(a[0], b[0]):
         assert torch.equal(x, y)
     assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])
+
+
+def test_rotary_frequencies_stay_fp32_through_a_model_cast():
+    rot = M.RotaryEmbedding(64)
+    want = rot.inv_freq.clone()
+    rot = rot.to(torch.bfloat16)
+    assert rot.inv_freq.dtype == torch.float32 and torch.equal(rot.inv_freq, want)
+    layer = M.TransformerLayer_MINT_plus(128, 512, 2, use_multimer=True).to(torch.bfloat16)
+    assert layer.self_attn.rot_emb.inv_freq.dtype == torch.float32
+    assert layer.self_attn.out_proj.weight.dtype == torch.bfloat16
+    assert "self_attn.rot_emb.inv_freq" in layer.state_dict()
