@@ -46,6 +46,7 @@ extern "C" {
 #define MINTB_F32 0
 #define MINTB_BF16 1
 #define MINTB_E4M3 2 /* operands / outputs of the projection GEMMs only */
+#define MINTB_E5M2 3 /* gradient operand of the backward projection GEMMs only */
 
 /* flags */
 #define MINTB_FLAG_ROPE 1u         /* rotate Q and K of the SELF pathway (rotary_embedding.py:47-55)                */
@@ -197,6 +198,25 @@ MINTB_API int mintb_qkv_fwd(const void* x, const void* w, const void* bias, void
                             int D, int in_dtype, int bias_dtype, float alpha, float q_scale, const float* rope_cos,
                             const float* rope_sin, const int32_t* row_map, int n_rows, void* stream, int* dev_status);
 MINTB_API int mintb_quantize_e4m3(const void* x, void* out, size_t n, float inv_scale, void* stream);
+
+/* Backward of the projections: the two products torch.autograd forms for y = x w^T (attention.py:68, modules.py:326-334;
+ * te.Linear's backward under mu_scaling/__init__.py:83-124; alt/munit_scaling.py:36-55 states the 8-bit variant: gradient
+ * in e5m2 against e4m3 weights / activations).  All matrices are row-major as the forward pass left them - none is
+ * transposed in memory.  Operands are both bf16, or both 8-bit floats (MINTB_E4M3 / MINTB_E5M2 per operand); fp32 accumulate.
+ *
+ * mintb_linear_dgrad: dx[M][K] = alpha * (dz[M][N] w[N][K] + dz2[M][N2] w2[N2][K]), stored as bf16.  The second pair is
+ *   optional (dz2 = w2 = NULL, N2 = 0): two projections of one activation (the self and cross QKV products) add their input
+ *   gradients in one accumulator instead of a separate pass.  For 8-bit operands alpha carries the dequantisation scales.
+ * mintb_linear_wgrad: dw[N][K] = alpha * dz^T x with dz[M][N], x[M][K]; dw is fp32 or bf16.  The reduction over the M
+ *   tokens is cut into aligned splits that add fp32 partial tiles into one fp32 matrix: dw itself when it is fp32, else
+ *   `workspace` (mintb_linear_wgrad_workspace_bytes), which a final pass converts to bf16.  The order of those additions is
+ *   not fixed, so the last bits of dw may differ from run to run when more than one split is used.
+ */
+MINTB_API int mintb_linear_dgrad(const void* dz, const void* w, const void* dz2, const void* w2, void* dx, int M, int N, int K,
+                                 int N2, int dz_dtype, int w_dtype, float alpha, void* stream, int* dev_status);
+MINTB_API size_t mintb_linear_wgrad_workspace_bytes(int N, int K, int out_dtype);
+MINTB_API int mintb_linear_wgrad(const void* dz, const void* x, void* dw, void* workspace, size_t workspace_bytes, int M, int N,
+                                 int K, int dz_dtype, int x_dtype, int out_dtype, float alpha, void* stream, int* dev_status);
 
 /* ---------------------------------------------------------------------------------------------------
  * HBM-bound glue of the layer around the GEMMs and the attention (bf16 tensors [rows][E] / [M][N], fp32 arithmetic).

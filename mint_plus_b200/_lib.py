@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libmintb.so")
 
 OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA = 0, -1, -2, -3, -4
-F32, BF16, E4M3 = 0, 1, 2
+F32, BF16, E4M3, E5M2 = 0, 1, 2, 3
 FLAG_ROPE, FLAG_SQRT_SOFTMAX, FLAG_FORCE_SIMT, FLAG_OUT_SEQ_FIRST, FLAG_ROT_SAVED, FLAG_SKIP_PAD_QUERIES = 1, 2, 4, 8, 16, 32
 FLAG_QK_PREROTATED, FLAG_GRAD_ROWMAJOR = 64, 128
 STATIC_SCRATCH_BYTES = 32 << 20
@@ -42,6 +42,9 @@ PROTOTYPES = {
     "mintb_qkv_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P, _P, _P, c_int,
                               _P, _P]),
     "mintb_quantize_e4m3": (c_int, [_P, _P, c_size_t, c_float, _P]),
+    "mintb_linear_dgrad": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P]),
+    "mintb_linear_wgrad_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "mintb_linear_wgrad": (c_int, [_P, _P, _P, _P, c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P]),
     "mintb_add_layernorm_fwd": (c_int, [_P, _P, c_float, c_float, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_float, _P]),
     "mintb_add_layernorm_fwd_q": (c_int, [_P, _P, c_float, c_float, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_float, _P, c_float, _P]),
     "mintb_add_layernorm_bwd_workspace_bytes": (c_size_t, [c_int, c_int]),

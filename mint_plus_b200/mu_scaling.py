@@ -6,8 +6,8 @@ tcgen05 e4m3 GEMM of libmintb: x and W are cast to e4m3 with one scale per tenso
 mint_plus/models/alt/munit_scaling.py:22-34 states the arithmetic), accumulated in fp32, multiplied by the product of the
 two scales, and bias / erf-GELU are applied in the GEMM epilogue.  The weight scale is amax(W)/448, refreshed when the weight
 changes; the activation scale is static (1.0 by default, which suits unit-variance muS activations; `calibrate_fp8`
-measures it on a sample batch otherwise).  Gradients are computed in bf16 from the master weights (straight-through for
-the casts).
+measures it on a sample batch otherwise).  Gradients are computed by the library's dgrad / wgrad GEMMs in bf16 from the
+master weights (straight-through for the casts).
 """
 from __future__ import annotations
 
@@ -38,7 +38,7 @@ class _Fp8LinearFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x2d, weight, bias, z = ctx.saved_tensors
-        dx, dw, db = ops.linear_backward(dy, x2d, weight, bias, z, ctx.needs_input_grad, ctx.out_scale)
+        dx, dw, db, _ = ops.linear_backward(dy, x2d, weight, bias, z, ctx.needs_input_grad, ctx.out_scale)
         return dx, dw, db, None, None, None, None, None
 
 
@@ -65,14 +65,14 @@ class _Fp8FfnFn(torch.autograd.Function):
         dy = dy.contiguous()
         # fc2: bias gradient, then the gradient of its input; its weight gradient waits for gelu(z)
         db2 = ops.gelu_bwd_colsum(dy, None, True)[1].to(b2.dtype) if (b2 is not None and n[4]) else None
-        w2b = w2 if w2.dtype == torch.bfloat16 else w2.to(torch.bfloat16)
-        da = dy @ (w2b * os2 if os2 != 1.0 else w2b)
+        da = ops.gemm_dgrad(dy, ops._as_bf16(w2), alpha=os2)
         dz, db1, act = ops.gelu_bwd_colsum(da, z, b1 is not None and n[2], want_act=n[3])
         dw2 = None
         if n[3]:
-            dw2 = dy.t() @ act
-            dw2 = (dw2 * os2 if os2 != 1.0 else dw2).to(w2.dtype)
-        dx, dw1, db1 = ops.linear_backward(dz, x2d, w1, b1, None, (n[0], n[1], n[2]), os1, db=db1 if db1 is not None else False)
+            dw2 = ops.gemm_wgrad(dy, act, alpha=os2, out_dtype=torch.float32 if w2.dtype == torch.float32 else torch.bfloat16)
+            if dw2.dtype != w2.dtype:
+                dw2 = dw2.to(w2.dtype)
+        dx, dw1, db1, _ = ops.linear_backward(dz, x2d, w1, b1, None, (n[0], n[1], n[2]), os1, db=db1 if db1 is not None else False)
         return (dx, dw1, db1, dw2, db2) + (None,) * 8
 
 

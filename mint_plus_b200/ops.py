@@ -413,6 +413,59 @@ def gemm_e4m3(xq: torch.Tensor, wq: torch.Tensor, alpha: float, bias=None, gelu:
     return (out, z) if save_preact else out
 
 
+_GEMM_DT = {torch.bfloat16: L.BF16, torch.float8_e4m3fn: L.E4M3, torch.float8_e5m2: L.E5M2}
+
+
+def gemm_dgrad(dz: torch.Tensor, w: torch.Tensor, dz2: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = None,
+               alpha: float = 1.0) -> torch.Tensor:
+    """dx = alpha (dz @ w + dz2 @ w2) on the tcgen05 GEMM: dz [M,N], w [N,K] (the nn.Linear weight as stored) -> bf16 [M,K].
+    Operands are all bf16, or all 8-bit floats (e5m2 gradients, e4m3 weights; alpha then carries the scales).  The optional
+    second pair adds another projection's input gradient in the same accumulator (no autograd)."""
+    _require_cuda(dz, w, dz2, w2)
+    M, N = dz.shape
+    K = w.shape[1]
+    if w.shape[0] != N or (dz2 is None) != (w2 is None):
+        raise ValueError("gemm_dgrad: dz [M,N] needs w [N,K]; dz2 and w2 come together")
+    N2 = 0 if dz2 is None else dz2.shape[1]
+    if dz2 is not None and (dz2.shape[0] != M or tuple(w2.shape) != (N2, K) or dz2.dtype != dz.dtype or w2.dtype != w.dtype):
+        raise ValueError("gemm_dgrad: the second operand pair must match the first in rows, K and dtypes")
+    if dz.dtype not in _GEMM_DT or w.dtype not in _GEMM_DT:
+        raise TypeError("gemm_dgrad takes bfloat16 or float8 operands")
+    dz, w = dz.contiguous(), w.contiguous()
+    dz2, w2 = (None, None) if dz2 is None else (dz2.contiguous(), w2.contiguous())
+    dx = torch.empty(M, K, dtype=torch.bfloat16, device=dz.device)
+    with _on(dz.device):
+        rc = L.lib().mintb_linear_dgrad(_ptr(dz), _ptr(w), _ptr(dz2), _ptr(w2), _ptr(dx), M, N, K, N2, _GEMM_DT[dz.dtype],
+                                        _GEMM_DT[w.dtype], float(alpha), _stream(), _ptr(_dev_status(dz.device)))
+    L.check(rc, "mintb_linear_dgrad")
+    return dx
+
+
+def gemm_wgrad(dz: torch.Tensor, x: torch.Tensor, alpha: float = 1.0, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """dw = alpha dz^T @ x on the tcgen05 GEMM: dz [M,N], x [M,K] -> [N,K] in bf16 or fp32 (fp32 accumulation over the M rows
+    either way).  Operands are both bf16, or both 8-bit floats (no autograd)."""
+    _require_cuda(dz, x)
+    M, N = dz.shape
+    if x.shape[0] != M:
+        raise ValueError("gemm_wgrad: dz [M,N] and x [M,K] must have the same number of rows")
+    K = x.shape[1]
+    if dz.dtype not in _GEMM_DT or x.dtype not in _GEMM_DT:
+        raise TypeError("gemm_wgrad takes bfloat16 or float8 operands")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("gemm_wgrad writes bfloat16 or float32")
+    dz, x = dz.contiguous(), x.contiguous()
+    odt = L.F32 if out_dtype == torch.float32 else L.BF16
+    dw = torch.empty(N, K, dtype=out_dtype, device=dz.device)
+    lib = L.lib()
+    wsb = lib.mintb_linear_wgrad_workspace_bytes(N, K, odt)
+    ws = _workspace(wsb, dz.device)
+    with _on(dz.device):
+        rc = lib.mintb_linear_wgrad(_ptr(dz), _ptr(x), _ptr(dw), _ptr(ws), wsb, M, N, K, _GEMM_DT[dz.dtype], _GEMM_DT[x.dtype], odt,
+                                    float(alpha), _stream(), _ptr(_dev_status(dz.device)))
+    L.check(rc, "mintb_linear_wgrad")
+    return dw
+
+
 def gelu_bwd_colsum(dy: torch.Tensor, z: Optional[torch.Tensor], want_db: bool = True, want_act: bool = False):
     """(dz, db): dz = dy * gelu'(z) (bf16 [M,N]; dy itself when z is None) and db = column sums of dz (fp32 [N]) in one pass.
     With want_act the same pass also writes gelu(z) in bf16 and the result is (dz, db, act)."""
@@ -436,28 +489,29 @@ def _gelu_erf_grad(z: torch.Tensor) -> torch.Tensor:
     return 0.5 * (1.0 + torch.erf(zf * 0.7071067811865476)) + zf * torch.exp(-0.5 * zf * zf) * 0.3989422804014327
 
 
-def linear_backward(dy, x2d, w, bias, z, needs, out_scale: float = 1.0, db=None, dx_accum=None):
+def linear_backward(dy, x2d, w, bias, z, needs, out_scale: float = 1.0, db=None, want_dx=True):
     """Gradients of y = act(out_scale * x W^T + b): the GELU derivative and the bias gradient come from one fused pass
-    (or the bias gradient is handed in as `db` by the pass that produced dy); dgrad and wgrad are plain library GEMMs on
-    bf16 (the static output multiplier is folded into the small operand; as the alpha of an addmm with a broadcast first
-    argument it cost an extra pass over the result).  `dx_accum`: a tensor of dx's shape that the input
-    gradient is ADDED to in place by the dgrad product itself (two projections of one activation: no separate add pass)."""
+    (or the bias gradient is handed in as `db` by the pass that produced dy); dgrad (dz W) and wgrad (dz^T x) run on the
+    tcgen05 GEMMs of the library from the row-major matrices as they are, bf16 operands, with the static output multiplier
+    as their alpha.  Returns (dx, dW, dbias, dz); `want_dx` False leaves dx to the caller (who adds several projections'
+    input gradients in one product, `gemm_dgrad` with two operand pairs)."""
     want_db = bias is not None and needs[2]
     if db is not None:
         dz = dy
     else:
         dz, db = gelu_bwd_colsum(dy, z, want_db)
-    wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
     dx = dw = None
-    if needs[0]:
-        w_eff = wb * out_scale if out_scale != 1.0 else wb
-        dx = dz @ w_eff if dx_accum is None else dx_accum.addmm_(dz, w_eff)
+    if needs[0] and want_dx:
+        dx = gemm_dgrad(dz, _as_bf16(w), alpha=out_scale)
     if needs[1]:
-        dw = dz.t() @ x2d
-        if out_scale != 1.0:
-            dw = dw * out_scale
-        dw = dw.to(w.dtype)
-    return dx, dw, (db.to(bias.dtype) if want_db else None)
+        dw = gemm_wgrad(dz, x2d, alpha=out_scale, out_dtype=torch.float32 if w.dtype == torch.float32 else torch.bfloat16)
+        if dw.dtype != w.dtype:
+            dw = dw.to(w.dtype)
+    return dx, dw, (db.to(bias.dtype) if want_db else None), dz
+
+
+def _as_bf16(w: torch.Tensor) -> torch.Tensor:
+    return (w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)).contiguous()
 
 
 class _LinearFn(torch.autograd.Function):
@@ -476,7 +530,7 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x2d, w, bias, z = ctx.saved_tensors
-        dx, dw, db = linear_backward(dy, x2d, w, bias, z, ctx.needs_input_grad)
+        dx, dw, db, _ = linear_backward(dy, x2d, w, bias, z, ctx.needs_input_grad)
         return dx, dw, db, None
 
 
@@ -500,9 +554,9 @@ class _LoraLinearFn(torch.autograd.Function):
         dy = dy.contiguous()
         dx = dw = db = d_a = d_b = None
         if needs[0]:
-            dx = dy @ (w + s * (lora_b.to(w.dtype) @ lora_a.to(w.dtype))).to(dt)
+            dx = gemm_dgrad(dy, _as_bf16(w + s * (lora_b.to(w.dtype) @ lora_a.to(w.dtype))))
         if needs[1]:
-            dw = (dy.t() @ x2d).to(w.dtype)
+            dw = gemm_wgrad(dy, x2d).to(w.dtype)
         if bias is not None and needs[2]:
             db = gelu_bwd_colsum(dy, None, True)[1].to(bias.dtype)
         if needs[3]:
@@ -725,21 +779,21 @@ class _QkvFn(torch.autograd.Function):
                                                  T, B, H, D, float(q_scale), _stream())
             L.check(rc, "mintb_qkv_grad_pack")
         # else: the attention backward pass has already written [dQ | dK | dV] row-major (and un-rotated): no gather pass
-        dx, dw, db, d_a, d_b = _qkv_backward_from_g(ctx, g, db)
+        dx, dw, db, d_a, d_b, _ = _qkv_backward_from_g(ctx, g, db)
         return (dx, dw, db, None, None, None, None, None, None, None, None, None, d_a, d_b, None)
 
 
-def _qkv_backward_from_g(ctx, g, db=None, dx_accum=None):
+def _qkv_backward_from_g(ctx, g, db=None, want_dx=True):
     """Gradients of one fused QKV projection (context `ctx` of `_QkvFn.forward`) from the row-major gradient matrix
-    g = [dQ | dK | dV] of its output: (dx shaped like the input, dW, dbias, dA, dB of the LoRA adapters)."""
+    g = [dQ | dK | dV] of its output: (dx shaped like the input or None, dW, dbias, dA, dB of the LoRA adapters, the bf16
+    weight and the multiplier its dgrad product takes)."""
     x2d, w, bias, _, _, lora_a, lora_b = ctx.saved_tensors
     T, B, H, D, q_scale, out_scale = ctx.dims
     needs = ctx.needs_input_grad
     w_used = _lora_merged(w, lora_a, lora_b, ctx.lora_scaling)
-    dx, dw, db = linear_backward(g, x2d, w_used, bias, None, needs, out_scale, db=db,
-                                 dx_accum=dx_accum.view(x2d.shape) if dx_accum is not None else None)
+    dx, dw, db, _ = linear_backward(g, x2d, w_used, bias, None, needs, out_scale, db=db, want_dx=want_dx)
     d_a, d_b = _lora_grads(g, x2d, lora_a, lora_b, ctx.lora_scaling, H * D, needs[12] or needs[13])
-    return (dx.view(ctx.x_shape) if dx is not None else None), dw, db, d_a, d_b
+    return (dx.view(ctx.x_shape) if dx is not None else None), dw, db, d_a, d_b, (_as_bf16(w_used), out_scale)
 
 
 class _SubCtx:
@@ -788,11 +842,19 @@ class _QkvAttentionFn(torch.autograd.Function):
             c.saved_tensors = saved[off:off + k]
             off += k
         _, g_s, g_c = _attention_backward(ca, d_out, ctx.pack)
-        dx, dw_s, db_s, da_s, dlb_s = _qkv_backward_from_g(cs, g_s)
-        dx2, dw_c, db_c, da_c, dlb_c = _qkv_backward_from_g(cc, g_c, dx_accum=dx)
+        _, dw_s, db_s, da_s, dlb_s, (wb_s, os_s) = _qkv_backward_from_g(cs, g_s, want_dx=False)
+        _, dw_c, db_c, da_c, dlb_c, (wb_c, os_c) = _qkv_backward_from_g(cc, g_c, want_dx=False)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            # both projections read the same x: their input gradients are ONE product over the concatenated reduction
+            if os_s == os_c:
+                dx = gemm_dgrad(g_s, wb_s, g_c, wb_c, alpha=os_s)
+            else:
+                dx = gemm_dgrad(g_s, wb_s, alpha=os_s) + gemm_dgrad(g_c, wb_c, alpha=os_c)
+            dx = dx.view(cs.x_shape)
         for c in ctx.subs:
             c.saved_tensors = ()
-        return (dx if dx is not None else dx2, dw_s, db_s, da_s, dlb_s, dw_c, db_c, da_c, dlb_c) + (None,) * 12
+        return (dx, dw_s, db_s, da_s, dlb_s, dw_c, db_c, da_c, dlb_c) + (None,) * 12
 
 
 def qkv_attention(x: torch.Tensor, proj_self, proj_cross, num_heads: int, meta: "MaskMeta", rope=None, scale: float = 1.0,
