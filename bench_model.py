@@ -323,13 +323,13 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
                 "flops_per_step": flops_step, "gemm_flops": flops_gemm, "attention_flops": flops_attn}
         roof["frac"] = roof["achieved"] / roof["peak"]
         if cfg["kind"] == "mu_fp8":
-            # the forward projections run on e4m3 operands (twice the bf16 rate); their dgrad / wgrad and the attention on
-            # bf16: the time the step needs at those peaks is the blended bound
-            f8 = flops_gemm / 3.0
+            # every projection product (forward, dgrad, wgrad) runs on 8-bit operands (twice the bf16 rate), the attention
+            # on bf16: the time the step needs at those peaks is the blended bound
+            f8 = flops_gemm
             t_min = (f8 / 2.0 + (flops_step - f8)) / (roof["peak"] * 1e12)
             roof["blended_peak"] = flops_step / t_min / 1e12
             roof["frac_blended"] = roof["achieved"] / roof["blended_peak"]
-            roof["blended_note"] = "forward GEMM FLOPs at 2 x the sustained bf16 peak (e4m3), all other FLOPs at 1 x"
+            roof["blended_note"] = "projection GEMM FLOPs (forward e4m3 x e4m3, backward e5m2 x e4m3) at 2 x the sustained bf16 peak, attention FLOPs at 1 x"
         if gemm is not None:
             roof["largest_gemm"] = {"shape": [Mtok, 4 * E_, E_], "epilogue": "bias + erf-GELU", **gemm,
                                     "frac": gemm["tflops"] / gemm["peak"]}

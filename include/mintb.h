@@ -253,6 +253,12 @@ MINTB_API int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const v
 MINTB_API int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, int M, int N, void* stream);
 MINTB_API int mintb_gelu_bwd_colsum_act(const void* dy, const void* z, void* dz, void* act, float* db, int M, int N,
                                         void* stream);
+/* mintb_gelu_bwd_colsum_act with an 8-bit copy of the result for the 8-bit dgrad / wgrad products: dz_e5m2[M][N] =
+ * saturate_e5m2(dz / e5m2_scale) (alt/munit_scaling.py:41-45 of the reference: the gradient is scaled, clamped to +-57344
+ * and cast to e5m2), written by the same pass; dz (bf16) may then be NULL.  db then sums the e5m2 numbers times e5m2_scale,
+ * the very values the products read (alt/munit_scaling.py:55). */
+MINTB_API int mintb_gelu_bwd_colsum_f8(const void* dy, const void* z, void* dz, void* act, float* db, void* dz_e5m2,
+                                       float e5m2_scale, int M, int N, void* stream);
 MINTB_API int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv, void* g, float* db, const float* rope_cos,
                                   const float* rope_sin, const int32_t* row_map, int n_rows, int T, int B, int H, int D,
                                   float q_scale, void* stream);

@@ -52,6 +52,7 @@ PROTOTYPES = {
                                         c_int, _P]),
     "mintb_gelu_bwd_colsum": (c_int, [_P, _P, _P, _P, c_int, c_int, _P]),
     "mintb_gelu_bwd_colsum_act": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, _P]),
+    "mintb_gelu_bwd_colsum_f8": (c_int, [_P, _P, _P, _P, _P, _P, c_float, c_int, c_int, _P]),
     "mintb_qkv_grad_pack": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P]),
     "mintb_combine_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "mintb_combine_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),

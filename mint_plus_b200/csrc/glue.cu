@@ -49,6 +49,21 @@ __device__ __forceinline__ uint2 pack8_e4m3(const float (&f)[8], float inv) {
   return u;
 }
 
+// eight values -> e5m2 (saturating at +-57344) after multiplication by inv; `f` is overwritten with the values the
+// 8-bit numbers stand for, times `scale` (an e5m2 number is the upper byte of the fp16 number with the same value)
+__device__ __forceinline__ uint2 pack8_e5m2_roundtrip(float (&f)[8], float inv, float scale) {
+  uint2 u;
+  __nv_fp8x2_storage_t* h = reinterpret_cast<__nv_fp8x2_storage_t*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    h[i] = __nv_cvt_float2_to_fp8x2(make_float2(f[2 * i] * inv, f[2 * i + 1] * inv), __NV_SATFINITE, __NV_E5M2);
+    const unsigned short lo = static_cast<unsigned short>((h[i] & 0xffu) << 8), hi = static_cast<unsigned short>(h[i] & 0xff00u);
+    f[2 * i] = __half2float(__ushort_as_half(lo)) * scale;
+    f[2 * i + 1] = __half2float(__ushort_as_half(hi)) * scale;
+  }
+  return u;
+}
+
 __device__ __forceinline__ float ld_param(const void* p, int dtype, int i) {
   return dtype == MINTB_F32 ? static_cast<const float*>(p)[i] : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
 }
@@ -374,7 +389,8 @@ __device__ __forceinline__ float gelu_erf_grad_val(float z, float& val) {
 template <bool HAS_Z>
 __global__ void __launch_bounds__(256) gelu_bwd_colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ z,
                                                               __nv_bfloat16* __restrict__ dz, float* __restrict__ db, int M, int N,
-                                                              __nv_bfloat16* __restrict__ act) {
+                                                              __nv_bfloat16* __restrict__ act, __nv_fp8_storage_t* __restrict__ q8,
+                                                              float q_inv, float q_scale) {
   __shared__ float part[kColLanes][32][8];
   const int cl = threadIdx.x % 32, rl = threadIdx.x / 32;
   const int cg = blockIdx.x * 32 + cl;   // column group
@@ -415,9 +431,15 @@ __global__ void __launch_bounds__(256) gelu_bwd_colsum_kernel(const __nv_bfloat1
 #pragma unroll
             for (int j = 0; j < 8; ++j) g[j] *= gelu_erf_grad(zv[j]);
           }
-          const uint4 packed = pack8(g);
-          if (m < M) *reinterpret_cast<uint4*>(dz + size_t(m) * N + size_t(cg) * 8) = packed;
-          unpack8(packed, g);   // the bias gradient sums what the products will read
+          if (dz != nullptr) {
+            const uint4 packed = pack8(g);
+            if (m < M) *reinterpret_cast<uint4*>(dz + size_t(m) * N + size_t(cg) * 8) = packed;
+            if (q8 == nullptr) unpack8(packed, g);   // the bias gradient sums what the products will read
+          }
+        }
+        if (q8 != nullptr) {   // the e5m2 operand of the 8-bit dgrad / wgrad products; the bias gradient sums these very numbers
+          const uint2 pk = pack8_e5m2_roundtrip(g, q_inv, q_scale);
+          if (m < M) *reinterpret_cast<uint2*>(q8 + size_t(m) * N + size_t(cg) * 8) = pk;
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] += g[j];   // rows past the end hold zeros
@@ -617,10 +639,12 @@ int mintb_add_layernorm_bwd(const void* dy, const void* ds_in, const void* x, co
   return e == cudaSuccess ? MINTB_OK : fail("mintb_add_layernorm_bwd launch", e);
 }
 
-int mintb_gelu_bwd_colsum_act(const void* dy, const void* z, void* dz, void* act, float* db, int M, int N, void* stream) {
-  if (dy == nullptr || M <= 0 || N <= 0 || (N % 8) != 0 || (z != nullptr && dz == nullptr) || (z == nullptr && db == nullptr) ||
-      (z == nullptr && act != nullptr)) {
-    set_error("mintb_gelu_bwd_colsum: dy required, N a multiple of 8, dz with z, db without z, act only with z");
+int mintb_gelu_bwd_colsum_f8(const void* dy, const void* z, void* dz, void* act, float* db, void* dz_e5m2, float e5m2_scale, int M,
+                             int N, void* stream) {
+  if (dy == nullptr || M <= 0 || N <= 0 || (N % 8) != 0 || (z != nullptr && dz == nullptr && dz_e5m2 == nullptr) ||
+      (z == nullptr && db == nullptr && dz_e5m2 == nullptr) || (z == nullptr && act != nullptr) || (dz_e5m2 != nullptr && !(e5m2_scale > 0.f))) {
+    set_error("mintb_gelu_bwd_colsum: dy required, N a multiple of 8, a result to write (dz / dz_e5m2 with z, db / dz_e5m2 without), "
+              "act only with z, a positive e5m2_scale with dz_e5m2");
     return MINTB_EINVAL;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -629,14 +653,26 @@ int mintb_gelu_bwd_colsum_act(const void* dy, const void* z, void* dz, void* act
     if (e != cudaSuccess) return fail("mintb_gelu_bwd_colsum memset", e);
   }
   dim3 grid((N + 255) / 256, (M + kSumRows - 1) / kSumRows);
+  __nv_fp8_storage_t* q8 = static_cast<__nv_fp8_storage_t*>(dz_e5m2);
+  const float q_inv = q8 != nullptr ? 1.f / e5m2_scale : 1.f, q_scale = q8 != nullptr ? e5m2_scale : 1.f;
   if (z != nullptr)
     gelu_bwd_colsum_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(z),
-                                                       static_cast<__nv_bfloat16*>(dz), db, M, N, static_cast<__nv_bfloat16*>(act));
+                                                       static_cast<__nv_bfloat16*>(dz), db, M, N, static_cast<__nv_bfloat16*>(act), q8,
+                                                       q_inv, q_scale);
   else
-    gelu_bwd_colsum_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), nullptr, nullptr, db, M, N, nullptr);
+    gelu_bwd_colsum_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), nullptr, nullptr, db, M, N, nullptr, q8,
+                                                        q_inv, q_scale);
   count_launches(1);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? MINTB_OK : fail("mintb_gelu_bwd_colsum launch", e);
+}
+
+int mintb_gelu_bwd_colsum_act(const void* dy, const void* z, void* dz, void* act, float* db, int M, int N, void* stream) {
+  if ((z != nullptr && dz == nullptr) || (z == nullptr && db == nullptr)) {
+    set_error("mintb_gelu_bwd_colsum: dy required, N a multiple of 8, dz with z, db without z, act only with z");
+    return MINTB_EINVAL;
+  }
+  return mintb_gelu_bwd_colsum_f8(dy, z, dz, act, db, nullptr, 1.f, M, N, stream);
 }
 
 int mintb_gelu_bwd_colsum(const void* dy, const void* z, void* dz, float* db, int M, int N, void* stream) {

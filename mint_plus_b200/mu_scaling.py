@@ -6,8 +6,9 @@ tcgen05 e4m3 GEMM of libmintb: x and W are cast to e4m3 with one scale per tenso
 mint_plus/models/alt/munit_scaling.py:22-34 states the arithmetic), accumulated in fp32, multiplied by the product of the
 two scales, and bias / erf-GELU are applied in the GEMM epilogue.  The weight scale is amax(W)/448, refreshed when the weight
 changes; the activation scale is static (1.0 by default, which suits unit-variance muS activations; `calibrate_fp8`
-measures it on a sample batch otherwise).  Gradients are computed by the library's dgrad / wgrad GEMMs in bf16 from the
-master weights (straight-through for the casts).
+measures it on a sample batch otherwise).  The backward products run on the library's dgrad / wgrad GEMMs: in 8 bits by
+default (e5m2 gradient with a static scale against the e4m3 operands, alt/munit_scaling.py:36-55), or in bf16 on the
+master weights with `fp8_grads=False`.
 """
 from __future__ import annotations
 
@@ -24,56 +25,87 @@ from .modules_plus import VanillaFeedForward, _TwoPathwayLayer
 E4M3_MAX = 448.0
 
 
+def _w_grad(g8, xq, alpha, like):
+    dw = ops.gemm_wgrad(g8, xq, alpha=alpha, out_dtype=torch.float32 if like.dtype == torch.float32 else torch.bfloat16)
+    return dw if dw.dtype == like.dtype else dw.to(like.dtype)
+
+
 class _Fp8LinearFn(torch.autograd.Function):
+    """y = act(out_scale x W^T + b) on e4m3 operands.  Backward: with a GradScale `gs` both products run in 8 bits — the
+    gradient cast to e5m2 with the static scale, against the e4m3 weight (dgrad) and the e4m3 activation kept from the
+    forward pass (wgrad), as mint_plus/models/alt/munit_scaling.py:36-55 states them; without one, in bf16 on the master
+    weight and the bf16 activation."""
+
     @staticmethod
-    def forward(ctx, x2d, weight, bias, wq, w_scale, x_scale, gelu, out_scale):
+    def forward(ctx, x2d, weight, bias, wq, w_scale, x_scale, gelu, out_scale, gs):
         xq = ops.quantize_e4m3(x2d, x_scale)
         keep = gelu and any(ctx.needs_input_grad[:3])
         res = ops.gemm_e4m3(xq, wq, x_scale * w_scale * out_scale, bias, gelu, save_preact=keep)
         out, z = res if keep else (res, None)
-        ctx.save_for_backward(x2d, weight, bias, z)
-        ctx.out_scale = out_scale
+        ctx.save_for_backward(xq if gs is not None else x2d, weight, bias, z, wq)
+        ctx.cfg = (float(out_scale), float(w_scale), float(x_scale), gs)
         return out
 
     @staticmethod
     def backward(ctx, dy):
-        x2d, weight, bias, z = ctx.saved_tensors
-        dx, dw, db, _ = ops.linear_backward(dy, x2d, weight, bias, z, ctx.needs_input_grad, ctx.out_scale)
-        return dx, dw, db, None, None, None, None, None
+        x_saved, weight, bias, z, wq = ctx.saved_tensors
+        out_scale, w_scale, x_scale, gs = ctx.cfg
+        n = ctx.needs_input_grad
+        if gs is None:
+            dx, dw, db, _ = ops.linear_backward(dy, x_saved, weight, bias, z, n, out_scale)
+            return dx, dw, db, None, None, None, None, None, None
+        want_db = bias is not None and n[2]
+        g8, db, s = ops.f8_output_grad(dy.contiguous(), z, want_db, gs)
+        dx = ops.gemm_dgrad(g8, wq, alpha=s * w_scale * out_scale) if n[0] else None
+        dw = _w_grad(g8, x_saved, s * x_scale * out_scale, weight) if n[1] else None
+        return dx, dw, (db.to(bias.dtype) if want_db else None), None, None, None, None, None, None
 
 
 class _Fp8FfnFn(torch.autograd.Function):
     """fc2(gelu(fc1(x))) on two e4m3 products as ONE differentiable step: fc1's epilogue writes gelu(.) directly as the e4m3
     operand of fc2 (with fc2's activation scale) beside the bf16 pre-activation z, so neither a bf16 copy of the 4E-wide
-    activation nor a cast pass over it exists; the backward pass rebuilds gelu(z) in the pass that computes gelu'(z) dy,
-    for fc2's weight gradient (mu_scaling/layer.py:236-241 and modules.py:323-335 of the reference; te.Linear there)."""
+    activation nor a cast pass over it exists (mu_scaling/layer.py:236-241 and modules.py:323-335 of the reference; te.Linear
+    there).  Backward with GradScales: four 8-bit products (e5m2 gradients; the e4m3 operands of the forward pass are the
+    other sides, fc2's being that very gelu(.) copy); the gradient casts ride on the passes that form the bias gradients and
+    gelu'(z) dy.  Without: bf16 products, gelu(z) rebuilt for fc2's weight gradient."""
 
     @staticmethod
-    def forward(ctx, x2d, w1, b1, w2, b2, wq1, ws1, xs1, os1, wq2, ws2, xs2, os2):
+    def forward(ctx, x2d, w1, b1, w2, b2, wq1, ws1, xs1, os1, wq2, ws2, xs2, os2, gs1, gs2):
         xq = ops._quantize_shared(x2d, xs1)      # the pass that produced x may have left the e4m3 copy already
         a8, z = ops.gemm_e4m3(xq, wq1, xs1 * ws1 * os1, b1, True, out_e4m3_scale=xs2, save_preact=True)
         y = ops.gemm_e4m3(a8, wq2, xs2 * ws2 * os2, b2, False)
-        ctx.save_for_backward(x2d, w1, b1, w2, b2, z)
-        ctx.scales = (float(os1), float(os2))
+        f8 = gs1 is not None and gs2 is not None
+        ctx.save_for_backward(xq if f8 else x2d, w1, b1, w2, b2, z, *((a8, wq1, wq2) if f8 else ()))
+        ctx.cfg = (float(os1), float(os2), float(ws1), float(xs1), float(ws2), float(xs2), gs1 if f8 else None, gs2 if f8 else None)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x2d, w1, b1, w2, b2, z = ctx.saved_tensors
-        os1, os2 = ctx.scales
+        os1, os2, ws1, xs1, ws2, xs2, gs1, gs2 = ctx.cfg
         n = ctx.needs_input_grad
         dy = dy.contiguous()
-        # fc2: bias gradient, then the gradient of its input; its weight gradient waits for gelu(z)
-        db2 = ops.gelu_bwd_colsum(dy, None, True)[1].to(b2.dtype) if (b2 is not None and n[4]) else None
-        da = ops.gemm_dgrad(dy, ops._as_bf16(w2), alpha=os2)
-        dz, db1, act = ops.gelu_bwd_colsum(da, z, b1 is not None and n[2], want_act=n[3])
-        dw2 = None
-        if n[3]:
-            dw2 = ops.gemm_wgrad(dy, act, alpha=os2, out_dtype=torch.float32 if w2.dtype == torch.float32 else torch.bfloat16)
-            if dw2.dtype != w2.dtype:
-                dw2 = dw2.to(w2.dtype)
-        dx, dw1, db1, _ = ops.linear_backward(dz, x2d, w1, b1, None, (n[0], n[1], n[2]), os1, db=db1 if db1 is not None else False)
-        return (dx, dw1, db1, dw2, db2) + (None,) * 8
+        tail = (None,) * 10
+        if gs1 is None:
+            x2d, w1, b1, w2, b2, z = ctx.saved_tensors
+            # fc2: bias gradient, then the gradient of its input; its weight gradient waits for gelu(z)
+            db2 = ops.gelu_bwd_colsum(dy, None, True)[1].to(b2.dtype) if (b2 is not None and n[4]) else None
+            da = ops.gemm_dgrad(dy, ops._as_bf16(w2), alpha=os2)
+            dz, db1, act = ops.gelu_bwd_colsum(da, z, b1 is not None and n[2], want_act=n[3])
+            dw2 = None
+            if n[3]:
+                dw2 = ops.gemm_wgrad(dy, act, alpha=os2, out_dtype=torch.float32 if w2.dtype == torch.float32 else torch.bfloat16)
+                if dw2.dtype != w2.dtype:
+                    dw2 = dw2.to(w2.dtype)
+            dx, dw1, db1, _ = ops.linear_backward(dz, x2d, w1, b1, None, (n[0], n[1], n[2]), os1, db=db1 if db1 is not None else False)
+            return (dx, dw1, db1, dw2, db2) + tail
+        xq, w1, b1, w2, b2, z, a8, wq1, wq2 = ctx.saved_tensors
+        g2, db2, s2 = ops.f8_output_grad(dy, None, b2 is not None and n[4], gs2)
+        da = ops.gemm_dgrad(g2, wq2, alpha=s2 * ws2 * os2)
+        dw2 = _w_grad(g2, a8, s2 * xs2 * os2, w2) if n[3] else None
+        g1, db1, s1 = ops.f8_output_grad(da, z, b1 is not None and n[2], gs1)
+        dx = ops.gemm_dgrad(g1, wq1, alpha=s1 * ws1 * os1) if n[0] else None
+        dw1 = _w_grad(g1, xq, s1 * xs1 * os1, w1) if n[1] else None
+        return (dx, dw1, db1.to(b1.dtype) if db1 is not None else None, dw2, db2.to(b2.dtype) if db2 is not None else None) + tail
 
 
 class Fp8Linear(nn.Module):
@@ -86,6 +118,8 @@ class Fp8Linear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
         self.x_scale = float(x_scale)
         self.out_scale = 1.0        # static multiplier of x W^T (muS: 1/sqrt(fan_in)); 1.0 = plain linear
+        self.fp8_grads = True       # backward products in 8 bits (e5m2 gradient); False: bf16 on the master weight
+        self.grad_scale = ops.GradScale()   # static scale of the e5m2 cast, measured on the first backward pass
         self._wq: Optional[torch.Tensor] = None
         self._wq_key = None
         self._w_scale = 1.0
@@ -115,7 +149,8 @@ class Fp8Linear(nn.Module):
             raise RuntimeError("Fp8Linear runs on CUDA tensors only (no CPU fallback)")
         wq, w_scale = self._quantized_weight()
         x2d = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
-        y = _Fp8LinearFn.apply(x2d, self.weight, self.bias, wq, w_scale, self.x_scale, gelu, self.out_scale)
+        y = _Fp8LinearFn.apply(x2d, self.weight, self.bias, wq, w_scale, self.x_scale, gelu, self.out_scale,
+                               self.grad_scale if self.fp8_grads else None)
         return y.view(*x.shape[:-1], self.out_features)
 
     def extra_repr(self):
@@ -127,18 +162,22 @@ def fp8_ffn(fc1: "Fp8Linear", fc2: "Fp8Linear", x: torch.Tensor) -> torch.Tensor
     wq1, ws1 = fc1._quantized_weight()
     wq2, ws2 = fc2._quantized_weight()
     x2d = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+    f8 = fc1.fp8_grads and fc2.fp8_grads
     y = _Fp8FfnFn.apply(x2d, fc1.weight, fc1.bias, fc2.weight, fc2.bias, wq1, ws1, fc1.x_scale, fc1.out_scale,
-                        wq2, ws2, fc2.x_scale, fc2.out_scale)
+                        wq2, ws2, fc2.x_scale, fc2.out_scale, fc1.grad_scale if f8 else None, fc2.grad_scale if f8 else None)
     return y.view(*x.shape[:-1], fc2.out_features)
 
 
 def fused_fp8_weight(owner: nn.Module, mods):
-    """(e4m3 [3E][E] weight, its scale, activation scale) of the Q/K/V projections `mods` (one fused Fp8Linear or three
+    """(e4m3 [3E][E] weight, its scale, activation scale, output multiplier, GradScale or None) of the Q/K/V projections `mods` (one fused Fp8Linear or three
     separate ones) for the head-major QKV GEMM.  Three separate weights share one scale (the largest amax of the three);
     the quantised concatenation is cached on `owner` until one of the weights changes."""
+    f8_grads = all(m.fp8_grads for m in mods)
     if len(mods) == 1:
         wq, w_scale = mods[0]._quantized_weight()
-        return wq, w_scale, mods[0].x_scale, mods[0].out_scale
+        return wq, w_scale, mods[0].x_scale, mods[0].out_scale, (mods[0].grad_scale if f8_grads else None)
+    if getattr(owner, "_fp8_qkv_grad_scale", None) is None:
+        owner._fp8_qkv_grad_scale = ops.GradScale()       # the three projections share one gradient matrix, hence one scale
     key = tuple((m.weight.data_ptr(), m.weight._version) for m in mods)
     cached = getattr(owner, "_fp8_qkv_cache", None)
     if cached is None or cached[0] != key:
@@ -146,7 +185,7 @@ def fused_fp8_weight(owner: nn.Module, mods):
         w_scale = max(float(w.abs().amax()), 1e-12) / E4M3_MAX
         cached = (key, ops.quantize_e4m3(w.to(torch.bfloat16).contiguous(), w_scale), w_scale)
         owner._fp8_qkv_cache = cached
-    return cached[1], cached[2], max(m.x_scale for m in mods), mods[0].out_scale
+    return cached[1], cached[2], max(m.x_scale for m in mods), mods[0].out_scale, (owner._fp8_qkv_grad_scale if f8_grads else None)
 
 
 def _sublayers(model):
@@ -155,14 +194,18 @@ def _sublayers(model):
 
 
 def apply_fp8_to_model(model: nn.Module, static_scale: bool = True, keep_embed_in_bf16: bool = True,
-                       keep_lm_head_in_bf16: bool = True) -> nn.Module:
+                       keep_lm_head_in_bf16: bool = True, fp8_grads: bool = True) -> nn.Module:
     """Swap the hidden projections of every layer for Fp8Linear, in place: self_attn q/k/v/out_proj (or its fused_qkv),
     multimer_attn.fused_qkv (or q/k/v), feed_forward fc1/fc2.  Embedding and LM head are left alone, as in the reference.
-    `static_scale` is recorded (activation scales here are always static)."""
+    `static_scale` is recorded (activation scales here are always static).  `fp8_grads`: the backward products run in 8 bits
+    too, the gradient cast to e5m2 with a static scale that each projection measures on its first backward pass (the
+    reference's te.Linear does the same under its HYBRID recipe); False keeps them in bf16 on the master weights."""
     def swap(mod, name):
         lin = getattr(mod, name, None)
         if isinstance(lin, nn.Linear):
-            setattr(mod, name, Fp8Linear.from_linear(lin))
+            new = Fp8Linear.from_linear(lin)
+            new.fp8_grads = fp8_grads
+            setattr(mod, name, new)
 
     for sub in _sublayers(model):
         for attn_name in ("self_attn", "multimer_attn"):

@@ -484,6 +484,50 @@ def gelu_bwd_colsum(dy: torch.Tensor, z: Optional[torch.Tensor], want_db: bool =
     return (dz, db, act) if want_act else (dz, db)
 
 
+E5M2_MAX = 57344.0
+GRAD_HEADROOM = 16.0     # the largest gradient seen at calibration lands this far below the e5m2 maximum
+
+
+class GradScale:
+    """Static scale of the e5m2 cast of one projection's output gradient: g8 = saturate_e5m2(dz / scale)
+    (mint_plus/models/alt/munit_scaling.py:41-45 states the cast with a fixed multiplier).  `scale` None means "not
+    measured yet": the first backward pass that meets it measures amax(dz) once (one host read) and fixes
+    scale = amax * GRAD_HEADROOM / 57344, so that gradients GRAD_HEADROOM times larger still fit and e5m2's 2^-30 range
+    below that covers the small ones.  Set `scale` by hand, or back to None to measure again."""
+
+    def __init__(self, scale: Optional[float] = None):
+        self.scale = scale
+
+    def fix(self, amax: float) -> float:
+        self.scale = max(float(amax), 1e-30) * GRAD_HEADROOM / E5M2_MAX
+        return self.scale
+
+
+def grad_colsum_f8(dy: torch.Tensor, z: Optional[torch.Tensor], want_db: bool, scale: float, want_dz: bool = False):
+    """(dz8, db, dz): dz = dy * gelu'(z) (dy itself without z) as e5m2 numbers dz8 = saturate(dz / scale) [M,N], the bias
+    gradient db (fp32 [N], the column sums of the e5m2 numbers times scale) and, with want_dz, dz in bf16 — one pass."""
+    _require_cuda(dy, z)
+    dy = dy.contiguous()
+    M, N = dy.shape
+    dz8 = torch.empty(M, N, dtype=torch.float8_e5m2, device=dy.device)
+    db = torch.empty(N, dtype=torch.float32, device=dy.device) if want_db else None
+    dz = torch.empty_like(dy) if (want_dz and z is not None) else None
+    with _on(dy.device):
+        rc = L.lib().mintb_gelu_bwd_colsum_f8(_ptr(dy), _ptr(z), _ptr(dz), None, _ptr(db), _ptr(dz8), float(scale), M, N, _stream())
+    L.check(rc, "mintb_gelu_bwd_colsum_f8")
+    return dz8, db, (dz if z is not None else (dy if want_dz else None))
+
+
+def f8_output_grad(dy: torch.Tensor, z: Optional[torch.Tensor], want_db: bool, holder: "GradScale"):
+    """The e5m2 operand of a projection's 8-bit backward products from its upstream gradient: (dz8, db, scale).  Measures
+    the holder's scale on first use."""
+    if holder.scale is None:
+        dz = gelu_bwd_colsum(dy, z, False)[0] if z is not None else dy
+        holder.fix(float(dz.detach().abs().amax()))
+    dz8, db, _ = grad_colsum_f8(dy, z, want_db, holder.scale)
+    return dz8, db, holder.scale
+
+
 def _gelu_erf_grad(z: torch.Tensor) -> torch.Tensor:
     zf = z.float()
     return 0.5 * (1.0 + torch.erf(zf * 0.7071067811865476)) + zf * torch.exp(-0.5 * zf * zf) * 0.3989422804014327
@@ -727,7 +771,7 @@ class _QkvFn(torch.autograd.Function):
     """Fused QKV projection of one pathway with head-major outputs (and RoPE on q, k when tables are given)."""
 
     @staticmethod
-    def forward(ctx, x, w, bias, H, cos, sin, q_scale, wq=None, w_scale=1.0, x_scale=1.0, out_scale=1.0, pack=None,
+    def forward(ctx, x, w, bias, H, cos, sin, q_scale, wq=None, w_scale=1.0, x_scale=1.0, out_scale=1.0, gs=None, pack=None,
                 lora_a=None, lora_b=None, lora_scaling=1.0):
         if pack is None:
             T, B, E = x.shape
@@ -753,6 +797,8 @@ class _QkvFn(torch.autograd.Function):
                                        _ptr(_dev_status(x.device)))
         L.check(rc, "mintb_qkv_fwd")
         ctx.save_for_backward(x2d, w, bias, cos, sin, lora_a, lora_b)
+        # 8-bit backward products (e5m2 gradient against these e4m3 operands): (xq, wq, weight scale, activation scale, GradScale)
+        ctx.f8 = (a_op, b_op, float(w_scale), float(x_scale), gs) if (wq is not None and gs is not None) else None
         ctx.lora_scaling = float(lora_scaling)
         ctx.pack = pack
         ctx.x_shape = tuple(x.shape)
@@ -780,20 +826,40 @@ class _QkvFn(torch.autograd.Function):
             L.check(rc, "mintb_qkv_grad_pack")
         # else: the attention backward pass has already written [dQ | dK | dV] row-major (and un-rotated): no gather pass
         dx, dw, db, d_a, d_b, _ = _qkv_backward_from_g(ctx, g, db)
-        return (dx, dw, db, None, None, None, None, None, None, None, None, None, d_a, d_b, None)
+        return (dx, dw, db, None, None, None, None, None, None, None, None, None, None, d_a, d_b, None)
 
 
-def _qkv_backward_from_g(ctx, g, db=None, want_dx=True):
+def _qkv_backward_from_g(ctx, g, db=None, want_dx=True, f8_scale=None):
     """Gradients of one fused QKV projection (context `ctx` of `_QkvFn.forward`) from the row-major gradient matrix
-    g = [dQ | dK | dV] of its output: (dx shaped like the input or None, dW, dbias, dA, dB of the LoRA adapters, the bf16
-    weight and the multiplier its dgrad product takes)."""
+    g = [dQ | dK | dV] of its output: (dx shaped like the input or None, dW, dbias, dA, dB of the LoRA adapters, and the
+    (gradient operand, weight operand, multiplier) its dgrad product takes).  A projection that ran on e4m3 operands with
+    8-bit gradients enabled casts g to e5m2 (scale `f8_scale`, else its own GradScale) and runs both products in 8 bits."""
     x2d, w, bias, _, _, lora_a, lora_b = ctx.saved_tensors
     T, B, H, D, q_scale, out_scale = ctx.dims
     needs = ctx.needs_input_grad
+    if getattr(ctx, "f8", None) is not None:
+        xq, wq, w_scale, x_scale, gs = ctx.f8
+        want_db = bias is not None and needs[2] and db is None
+        if f8_scale is None:
+            g8, db8, f8_scale = f8_output_grad(g, None, want_db, gs)
+        else:
+            g8, db8, _ = grad_colsum_f8(g, None, want_db, f8_scale)
+        if want_db:
+            db = db8
+        dx = dw = None
+        if needs[0] and want_dx:
+            dx = gemm_dgrad(g8, wq, alpha=f8_scale * w_scale * out_scale).view(ctx.x_shape)
+        if needs[1]:
+            dw = gemm_wgrad(g8, xq, alpha=f8_scale * x_scale * out_scale,
+                            out_dtype=torch.float32 if w.dtype == torch.float32 else torch.bfloat16)
+            if dw.dtype != w.dtype:
+                dw = dw.to(w.dtype)
+        db_out = db.to(bias.dtype) if (bias is not None and needs[2] and db is not None) else None
+        return dx, dw, db_out, None, None, (g8, wq, f8_scale * w_scale * out_scale)
     w_used = _lora_merged(w, lora_a, lora_b, ctx.lora_scaling)
     dx, dw, db, _ = linear_backward(g, x2d, w_used, bias, None, needs, out_scale, db=db, want_dx=want_dx)
-    d_a, d_b = _lora_grads(g, x2d, lora_a, lora_b, ctx.lora_scaling, H * D, needs[12] or needs[13])
-    return (dx.view(ctx.x_shape) if dx is not None else None), dw, db, d_a, d_b, (_as_bf16(w_used), out_scale)
+    d_a, d_b = _lora_grads(g, x2d, lora_a, lora_b, ctx.lora_scaling, H * D, needs[13] or needs[14])
+    return (dx.view(ctx.x_shape) if dx is not None else None), dw, db, d_a, d_b, (g, _as_bf16(w_used), out_scale)
 
 
 class _SubCtx:
@@ -819,7 +885,7 @@ class _QkvAttentionFn(torch.autograd.Function):
     def forward(ctx, x, w_s, b_s, la_s, lb_s, w_c, b_c, la_c, lb_c, H, cos, sin, q_scale, fp8_s, fp8_c, ls_s, ls_c, pack,
                 meta, scale, flags):
         n = ctx.needs_input_grad
-        f = (False,) * 9
+        f = (False,) * 10
         cs = _SubCtx((n[0], n[1], n[2]) + f + (n[3], n[4], False))
         cc = _SubCtx((n[0], n[5], n[6]) + f + (n[7], n[8], False))
         ca = _SubCtx((any(n[:9]),) * 6 + (False,) * 6)
@@ -842,15 +908,24 @@ class _QkvAttentionFn(torch.autograd.Function):
             c.saved_tensors = saved[off:off + k]
             off += k
         _, g_s, g_c = _attention_backward(ca, d_out, ctx.pack)
-        _, dw_s, db_s, da_s, dlb_s, (wb_s, os_s) = _qkv_backward_from_g(cs, g_s, want_dx=False)
-        _, dw_c, db_c, da_c, dlb_c, (wb_c, os_c) = _qkv_backward_from_g(cc, g_c, want_dx=False)
+        scale_c = None
+        if getattr(cs, "f8", None) is not None and getattr(cc, "f8", None) is not None:
+            # 8-bit products for both pathways.  Their input gradients share ONE accumulator, hence one multiplier: the cross
+            # pathway's e5m2 cast takes the scale that makes its multiplier equal the self pathway's.
+            (_, _, ws_s, _, gs_s), (_, _, ws_c, _, _) = cs.f8, cc.f8
+            ratio = (ws_s * cs.dims[5]) / (ws_c * cc.dims[5])
+            if gs_s.scale is None:
+                gs_s.fix(max(float(g_s.abs().amax()), float(g_c.abs().amax()) / ratio))
+            scale_c = gs_s.scale * ratio
+        _, dw_s, db_s, da_s, dlb_s, (ga_s, wb_s, al_s) = _qkv_backward_from_g(cs, g_s, want_dx=False)
+        _, dw_c, db_c, da_c, dlb_c, (ga_c, wb_c, al_c) = _qkv_backward_from_g(cc, g_c, want_dx=False, f8_scale=scale_c)
         dx = None
         if ctx.needs_input_grad[0]:
             # both projections read the same x: their input gradients are ONE product over the concatenated reduction
-            if os_s == os_c:
-                dx = gemm_dgrad(g_s, wb_s, g_c, wb_c, alpha=os_s)
+            if ga_s.dtype == ga_c.dtype and abs(al_s - al_c) <= 1e-6 * abs(al_s):
+                dx = gemm_dgrad(ga_s, wb_s, ga_c, wb_c, alpha=al_s)
             else:
-                dx = gemm_dgrad(g_s, wb_s, alpha=os_s) + gemm_dgrad(g_c, wb_c, alpha=os_c)
+                dx = gemm_dgrad(ga_s, wb_s, alpha=al_s) + gemm_dgrad(ga_c, wb_c, alpha=al_c)
             dx = dx.view(cs.x_shape)
         for c in ctx.subs:
             c.saved_tensors = ()
@@ -871,7 +946,7 @@ def qkv_attention(x: torch.Tensor, proj_self, proj_cross, num_heads: int, meta: 
     def unpack(proj):
         w, b, fp8, lora = proj
         la, lb, ls = lora if lora is not None else (None, None, 1.0)
-        return w, b, la, lb, (fp8 if fp8 is not None else (None, 1.0, 1.0, 1.0)), ls
+        return w, b, la, lb, (tuple(fp8) + (None,) * (5 - len(fp8)) if fp8 is not None else (None, 1.0, 1.0, 1.0, None)), ls
 
     w_s, b_s, la_s, lb_s, f_s, ls_s = unpack(proj_self)
     w_c, b_c, la_c, lb_c, f_c, ls_c = unpack(proj_cross)
@@ -888,11 +963,12 @@ def qkv_project(x: torch.Tensor, weight: torch.Tensor, bias, num_heads: int, rop
     (attention.py:97-117, 304-323 of the reference without the three permute copies).  `rope` = (cos, sin) tables rotates q, k.
     `lora` = (A (3,r,E), B (3,E,r), alpha / r) adds frozen-base LoRA adapters of q, k, v: the product runs on the merged
     weight, the adapters get their gradients through thin products.
-    `fp8` = (e4m3 weight, weight scale, activation scale, static output multiplier) runs the product on e4m3 operands; `weight` stays the master copy
-    that receives the gradient."""
+    `fp8` = (e4m3 weight, weight scale, activation scale, static output multiplier[, GradScale]) runs the product on e4m3
+    operands; `weight` stays the master copy that receives the gradient.  With a GradScale the backward products run in 8 bits
+    as well (e5m2 gradient against the e4m3 operands), else in bf16 on the master weight."""
     if x.dtype != torch.bfloat16 or (pack is None and x.dim() != 3):
         raise TypeError("qkv_project takes a (T, B, E) bfloat16 tensor (or the packed rows of one, with `pack`)")
     cos, sin = rope if rope is not None else (None, None)
-    wq, w_scale, x_scale, out_scale = fp8 if fp8 is not None else (None, 1.0, 1.0, 1.0)
+    wq, w_scale, x_scale, out_scale, gs = (tuple(fp8) + (None,) * (5 - len(fp8))) if fp8 is not None else (None, 1.0, 1.0, 1.0, None)
     la, lb, ls = lora if lora is not None else (None, None, 1.0)
-    return _QkvFn.apply(x, weight, bias, num_heads, cos, sin, q_scale, wq, w_scale, x_scale, out_scale, pack, la, lb, ls)
+    return _QkvFn.apply(x, weight, bias, num_heads, cos, sin, q_scale, wq, w_scale, x_scale, out_scale, gs, pack, la, lb, ls)

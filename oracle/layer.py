@@ -26,6 +26,7 @@ import torch.nn.functional as F
 from . import multimer_attention as O
 
 E4M3_MAX = 448.0
+E5M2_MAX = 57344.0
 
 
 class _RoundBf16(torch.autograd.Function):
@@ -54,49 +55,84 @@ def quant_e4m3(x: torch.Tensor, scale: float) -> torch.Tensor:
     return (x.float() * inv).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).float()
 
 
+def quant_e5m2(g: torch.Tensor, scale: float) -> torch.Tensor:
+    """saturate(g * (1 / scale)) rounded to e5m2, returned as fp32 (still divided by the scale)."""
+    inv = torch.tensor(1.0 / scale, dtype=torch.float32)
+    return (g.float() * inv).clamp(-E5M2_MAX, E5M2_MAX).to(torch.float8_e5m2).float()
+
+
 class _QuantLinear(torch.autograd.Function):
-    """y = (x_scale w_scale out_scale) q(x) q(w)^T + b; gradients as for y = out_scale x w^T + b (straight-through)."""
+    """y = (x_scale w_scale out_scale) q(x) q(w)^T + b.  Backward, g_scale None: as for y = out_scale x w^T + b on the
+    un-quantised operands (straight-through).  With g_scale (alt/munit_scaling.py:36-55): the gradient is cast to e5m2,
+    g8 = q5(dy / g_scale), and dx = g8 q(w), dw = g8^T q(x), db = sum g8, each times its scales."""
 
     @staticmethod
-    def forward(ctx, x, w, b, x_scale, w_scale, out_scale):
+    def forward(ctx, x, w, b, x_scale, w_scale, out_scale, g_scale):
         alpha = torch.tensor(float(x_scale) * float(w_scale) * float(out_scale), dtype=torch.float32)
         y = (quant_e4m3(x, x_scale) @ quant_e4m3(w, w_scale).t()) * alpha
         if b is not None:
             y = y + b.float()
         ctx.save_for_backward(x, w)
-        ctx.out_scale = float(out_scale)
+        ctx.cfg = (float(x_scale), float(w_scale), float(out_scale), g_scale)
         ctx.has_bias = b is not None
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
-        dx = (dy @ w) * ctx.out_scale
-        dw = (dy.t() @ x) * ctx.out_scale
-        return dx, dw, (dy.sum(0) if ctx.has_bias else None), None, None, None
+        x_scale, w_scale, out_scale, g_scale = ctx.cfg
+        if g_scale is None:
+            dx = (dy @ w) * out_scale
+            dw = (dy.t() @ x) * out_scale
+            db = dy.sum(0) if ctx.has_bias else None
+        else:
+            g8 = quant_e5m2(dy, g_scale)
+            # (the product leaves the GPU as bf16, and the next projection's e5m2 cast sees that rounding)
+            dx = ((g8 @ quant_e4m3(w, w_scale)) * torch.tensor(g_scale * w_scale * out_scale, dtype=torch.float32)).bfloat16().float()
+            dw = (g8.t() @ quant_e4m3(x, x_scale)) * torch.tensor(g_scale * x_scale * out_scale, dtype=torch.float32)
+            db = g8.sum(0) * g_scale if ctx.has_bias else None
+        return dx, dw, db, None, None, None, None
 
 
-def linear(x2d, w, b, fp8: Optional[dict] = None, w_scale: Optional[float] = None, x_is_e4m3: bool = False):
-    """fp32 result of one projection on rows x2d [M,K] (not yet rounded to bf16).  `fp8` = {"x_scale", "out_scale"} selects the
-    e4m3 arithmetic; `w_scale` overrides amax(w)/448 (fused Q/K/V weights share one scale)."""
+class _GeluKeepsBf16Preactivation(torch.autograd.Function):
+    """gelu_erf(z) computed from the fp32 pre-activation (the GEMM epilogue), differentiated at the bf16 copy of z that the
+    forward pass keeps for the backward pass."""
+
+    @staticmethod
+    def forward(ctx, z):
+        ctx.save_for_backward(z.bfloat16().float())
+        return O.gelu_erf(z)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (zb,) = ctx.saved_tensors
+        return dy * (0.5 * (1.0 + torch.erf(zb * 0.7071067811865476)) + zb * torch.exp(-0.5 * zb * zb) * 0.3989422804014327)
+
+
+def linear(x2d, w, b, fp8: Optional[dict] = None, w_scale: Optional[float] = None, name: Optional[str] = None):
+    """fp32 result of one projection on rows x2d [M,K] (not yet rounded to bf16).  `fp8` = {"x_scale", "out_scale", "g_scale"}
+    selects the e4m3 arithmetic (g_scale: the 8-bit backward as well); an entry fp8["per"][name] overrides those fields for
+    the projection `name` ("sa_qkv", "ma_qkv", "out", "fc1", "fc2").  `w_scale` overrides amax(w)/448."""
     if fp8 is None:
         return F.linear(x2d, w, b)
+    cfg = dict(fp8)
+    cfg.update(fp8.get("per", {}).get(name, {}))
     ws = weight_scale(w) if w_scale is None else w_scale
-    return _QuantLinear.apply(x2d, w, b, fp8.get("x_scale", 1.0), ws, fp8.get("out_scale", 1.0))
+    return _QuantLinear.apply(x2d, w, b, cfg.get("x_scale", 1.0), ws, cfg.get("out_scale", 1.0), cfg.get("g_scale"))
 
 
 def _heads(t2d, T, B, H, D):
     return t2d.reshape(T, B, H, D).permute(1, 2, 0, 3)
 
 
-def _qkv(attn, x2d, T, B, H, D, rope: bool, fp8):
+def _qkv(attn, x2d, T, B, H, D, rope: bool, fp8, name):
     """q, k, v (B,H,T,D) of one pathway as the fused QKV GEMM leaves them: bias added, q and k rotated in fp32, then bf16."""
     if getattr(attn, "fused_qkv", None) is not None:
         w, b = attn.fused_qkv.weight, attn.fused_qkv.bias
     else:
         w = torch.cat([attn.q_proj.weight, attn.k_proj.weight, attn.v_proj.weight], dim=0)
         b = torch.cat([attn.q_proj.bias, attn.k_proj.bias, attn.v_proj.bias], dim=0) if attn.q_proj.bias is not None else None
-    qkv = linear(x2d, w, b, fp8)
+    qkv = linear(x2d, w, b, fp8, name=name)
     q, k, v = (_heads(t, T, B, H, D) for t in qkv.chunk(3, dim=-1))
     if rope:
         q, k = O.apply_rope(q), O.apply_rope(k)
@@ -110,12 +146,12 @@ def attention_block(layer, x, chain_mask, key_pad, fp8=None, sqrt_softmax=False)
     H = sa.num_heads
     D = E // H
     x2d = x.reshape(T * B, E)
-    q_s, k_s, v_s = _qkv(sa, x2d, T, B, H, D, sa.rot_emb is not None, fp8)
-    q_c, k_c, v_c = _qkv(ma, x2d, T, B, H, D, False, fp8)
+    q_s, k_s, v_s = _qkv(sa, x2d, T, B, H, D, sa.rot_emb is not None, fp8, "sa_qkv")
+    q_c, k_c, v_c = _qkv(ma, x2d, T, B, H, D, False, fp8, "ma_qkv")
     a = O.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, chain_mask, key_pad, scale=D ** -0.5, rope=False,
                              sqrt_softmax=sqrt_softmax)
     a = bf16r(a.permute(2, 0, 1, 3).reshape(T * B, E))
-    return bf16r(linear(a, sa.out_proj.weight, sa.out_proj.bias, fp8)).reshape(T, B, E)
+    return bf16r(linear(a, sa.out_proj.weight, sa.out_proj.bias, fp8, name="out")).reshape(T, B, E)
 
 
 def feed_forward(layer, x, fp8=None):
@@ -123,11 +159,11 @@ def feed_forward(layer, x, fp8=None):
     gelu(.) straight to fc2's e4m3 operand from the fp32 value (fc2's activation scale), no bf16 copy in between."""
     T, B, E = x.shape
     ff = layer.feed_forward
-    z = linear(x.reshape(T * B, E), ff.fc1.weight, ff.fc1.bias, fp8)
-    g = O.gelu_erf(z)
+    z = linear(x.reshape(T * B, E), ff.fc1.weight, ff.fc1.bias, fp8, name="fc1")
+    g = _GeluKeepsBf16Preactivation.apply(z)
     if fp8 is None:
         g = bf16r(g)
-    return bf16r(linear(g, ff.fc2.weight, ff.fc2.bias, fp8)).reshape(T, B, E)
+    return bf16r(linear(g, ff.fc2.weight, ff.fc2.bias, fp8, name="fc2")).reshape(T, B, E)
 
 
 def mu_layer(layer, x, chain_mask, key_pad, tau: float, fp8=None, sqrt_softmax=False):

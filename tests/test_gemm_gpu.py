@@ -120,34 +120,30 @@ def test_linear_and_qkv_gradients_match_autograd():
 
 
 @pytest.mark.parametrize("fp8", [False, True])
-def test_bf16_layer_forward_backward_against_oracle_composition(fp8):
-    """TransformerLayer_MINT_plus in bf16 on the GPU (GEMM epilogues + fused attention; e4m3 projections when `fp8`)
-    against the same layer evaluated in fp32 with the oracle attention on the CPU."""
+def test_bf16_layer_forward_backward_against_restated_layer(fp8):
+    """TransformerLayer_MINT_plus in bf16 on the GPU (GEMM epilogues + fused attention; e4m3 projections with 8-bit backward
+    products when `fp8`) against the CPU restatement of the same layer with the same rounding and quantisation points
+    (oracle/layer.py), at a tolerance of a few bf16 steps.  The e4m3 / e5m2 arithmetic is parity-unpinned (transformer_engine,
+    which the reference calls for it, is not available): the check is against the formulas restated from
+    mint_plus/models/alt/munit_scaling.py:22-55."""
+    import copy
+    from oracle import layer as OL
     torch.manual_seed(11)
     E, H, T, B = 128, 4, 150, 2
     layer = M.TransformerLayer_MINT_plus(E, 4 * E, H, use_multimer=True, use_erf_gelu=True).float()
+    with torch.no_grad():
+        for name, p in layer.named_parameters():
+            if name.endswith("bias"):
+                p.normal_(0, 0.05)
     for p in layer.parameters():                      # bf16-representable weights so both sides see the same numbers
         p.data = p.data.bfloat16().float()
     x = torch.randn(T, B, E).bfloat16().float()
+    gy = torch.randn(T, B, E).bfloat16().float()
     cid = torch.zeros(B, T, dtype=torch.int32); cid[:, 70:] = 1
     pad = torch.zeros(B, T, dtype=torch.bool); pad[1, -13:] = True
     mask = O.chain_mask_from_ids(cid)
 
-    def cpu_forward(xx):
-        h = layer.self_attn_layer_norm(xx)
-        qs, ks, vs = layer.self_attn.project_qkv_4d(h)
-        qc, kc, vc = layer.multimer_attn.project_qkv_4d(h)
-        a = O.multimer_attention(qs, ks, vs, qc, kc, vc, mask, pad)
-        a = layer.self_attn.out_proj(a.permute(2, 0, 1, 3).reshape(T, B, E))
-        y = xx + a
-        return y + layer.feed_forward(layer.final_layer_norm(y))
-
-    xc = x.clone().requires_grad_(True)
-    want = cpu_forward(xc)
-    want.sum().backward()
-    wgx = xc.grad.clone()
-    layer.zero_grad()
-    glayer = layer.to(DEV).to(torch.bfloat16)
+    glayer = copy.deepcopy(layer).to(DEV).to(torch.bfloat16)
     if fp8:
         holder = torch.nn.Module()
         holder.layers = torch.nn.ModuleList([glayer])
@@ -156,13 +152,31 @@ def test_bf16_layer_forward_backward_against_oracle_composition(fp8):
         assert holder._fp8_config == {"enabled": True, "static_scale": True}
     xg = x.to(DEV, torch.bfloat16).requires_grad_(True)
     out, _ = glayer(xg, self_attn_mask=mask.to(DEV), self_attn_padding_mask=pad.to(DEV))
-    out.sum().backward()
+    out.backward(gy.to(DEV, torch.bfloat16))
     ops.check_device_status()
-    tol = 0.25 if fp8 else 0.06          # e4m3 has 3 mantissa bits; bf16 8
-    scale = want.abs().max().item()
-    assert (out.float().cpu() - want.detach()).abs().max().item() <= tol * scale
-    assert (xg.grad.float().cpu() - wgx).abs().max().item() <= tol * wgx.abs().max().item() + 0.05
-    layer.to("cpu").float()
+
+    cfg = None
+    if fp8:      # the static e5m2 gradient scales the GPU layer measured on this (its first) backward pass
+        sa, ma, ff = glayer.self_attn, glayer.multimer_attn, glayer.feed_forward
+        gs = sa.fused_qkv.grad_scale.scale
+        ratio = OL.weight_scale(layer.self_attn.fused_qkv.weight) / OL.weight_scale(layer.multimer_attn.fused_qkv.weight)
+        cfg = {"x_scale": 1.0, "out_scale": 1.0, "per": {
+            "sa_qkv": {"g_scale": gs}, "ma_qkv": {"g_scale": gs * ratio}, "out": {"g_scale": sa.out_proj.grad_scale.scale},
+            "fc1": {"g_scale": ff.fc1.grad_scale.scale}, "fc2": {"g_scale": ff.fc2.grad_scale.scale}}}
+    xc = x.clone().requires_grad_(True)
+    want = OL.pre_ln_layer(layer, xc, mask, pad, fp8=cfg)
+    want.backward(gy)
+
+    def rel(got, ref):
+        return (got.float().cpu() - ref).abs().max().item() / ref.abs().max().item()
+
+    errs = {"out": rel(out.detach(), want.detach()), "dx": rel(xg.grad, xc.grad),
+            "dW_fc2": rel(glayer.feed_forward.fc2.weight.grad, layer.feed_forward.fc2.weight.grad),
+            "dW_qkv_cross": rel(glayer.multimer_attn.fused_qkv.weight.grad, layer.multimer_attn.fused_qkv.weight.grad),
+            "db_out": rel(glayer.self_attn.out_proj.bias.grad, layer.self_attn.out_proj.bias.grad)}
+    print(f"pre-LN layer fp8={fp8}: " + ", ".join(f"{k} {v:.3g}" for k, v in errs.items()))
+    assert errs["out"] <= 3e-2, errs
+    assert max(errs["dx"], errs["dW_fc2"], errs["dW_qkv_cross"], errs["db_out"]) <= 5e-2, errs
 
 
 def test_lora_linear_on_the_merged_weight_matches_the_formula():

@@ -7,6 +7,7 @@ Tolerances: attention outputs <= 2e-2 max-abs against the fp32 oracle on the sam
 their scale (as tests/test_attn_gpu.py); layer outputs and gradients within a few bf16 steps of the restated layer.  The
 e4m3 arithmetic itself is parity-unpinned: transformer_engine 2.16.0, which the reference calls for it, is not available;
 the check is against the formula restated from mint_plus/models/alt/munit_scaling.py:22-55."""
+import copy
 import math
 
 import pytest
@@ -110,23 +111,8 @@ def test_mus_layer_1280_wide_against_restated_layer(mode):
     pad = torch.zeros(B, T, dtype=torch.bool); pad[:, la + lb:] = True
     mask = O.chain_mask_from_ids(cid)
 
-    fp8 = None
-    if mode != "bf16":
-        fp8 = {"x_scale": 1.0, "out_scale": 1.0}
-    # CPU restatement (fp32 arithmetic on bf16-representable values)
-    xc = x.clone().requires_grad_(True)
-    if mode == "fp8_unit_sqrt":
-        want = _mu_layer_unit(layer, xc, mask, pad, tau)
-    else:
-        want = OL.mu_layer(layer, xc, mask, pad, tau, fp8=fp8, sqrt_softmax=sqrt_sm)
-    want.backward(gy)
-    wgx = xc.grad.clone()
-    wg_fc1 = layer.feed_forward.fc1.weight.grad.clone()
-    wg_q = layer.self_attn.q_proj.weight.grad.clone()
-    layer.zero_grad()
-
-    glayer = layer.to(DEV).to(torch.bfloat16)
-    glayer.self_attn.rot_emb.inv_freq = glayer.self_attn.rot_emb.inv_freq.float()
+    # GPU layer first: its 8-bit backward measures the static e5m2 gradient scales that the restatement then takes over
+    glayer = copy.deepcopy(layer).to(DEV).to(torch.bfloat16)
     if mode != "bf16":
         holder = torch.nn.Module()
         holder.layers = torch.nn.ModuleList([glayer])
@@ -138,28 +124,44 @@ def test_mus_layer_1280_wide_against_restated_layer(mode):
     out.backward(gy.to(DEV, torch.bfloat16))
     ops.check_device_status()
 
+    fp8 = None
+    if mode != "bf16":
+        sa, ma, ff = glayer.self_attn, glayer.multimer_attn, glayer.feed_forward
+        os_e, os_4e = (E ** -0.5, (4 * E) ** -0.5) if mode == "fp8_unit_sqrt" else (1.0, 1.0)
+        ws_s = OL.weight_scale(layer.self_attn.q_proj.weight, layer.self_attn.k_proj.weight, layer.self_attn.v_proj.weight)
+        ws_c = OL.weight_scale(layer.multimer_attn.q_proj.weight, layer.multimer_attn.k_proj.weight, layer.multimer_attn.v_proj.weight)
+        gs_s = sa._fp8_qkv_grad_scale.scale
+        assert gs_s is not None and sa.out_proj.grad_scale.scale is not None and ff.fc1.grad_scale.scale is not None
+        fp8 = {"x_scale": 1.0, "out_scale": os_e, "per": {
+            "sa_qkv": {"g_scale": gs_s}, "ma_qkv": {"g_scale": gs_s * ws_s / ws_c},     # one multiplier for both dgrad pairs
+            "out": {"g_scale": sa.out_proj.grad_scale.scale}, "fc1": {"g_scale": ff.fc1.grad_scale.scale},
+            "fc2": {"g_scale": ff.fc2.grad_scale.scale, "out_scale": os_4e}}}
+    # CPU restatement (fp32 arithmetic on bf16-representable values)
+    xc = x.clone().requires_grad_(True)
+    want = OL.mu_layer(layer, xc, mask, pad, tau, fp8=fp8, sqrt_softmax=sqrt_sm)
+    want.backward(gy)
+    wgx = xc.grad.clone()
+    wg_fc1 = layer.feed_forward.fc1.weight.grad.clone()
+    wg_q = layer.self_attn.q_proj.weight.grad.clone()
+    layer.zero_grad()
+
     def rel(got, ref):
         return (got.float().cpu() - ref).abs().max().item() / ref.abs().max().item()
 
-    errs = {"out": rel(out.detach(), want.detach()), "dx": rel(xg.grad, wgx),
-            "dW_fc1": rel(glayer.feed_forward.fc1.weight.grad, wg_fc1), "dW_q": rel(glayer.self_attn.q_proj.weight.grad, wg_q)}
-    print(f"mus layer {mode}: " + ", ".join(f"{k} {v:.3g}" for k, v in errs.items()))
+    def fro(got, ref):
+        return ((got.float().cpu() - ref).norm() / ref.norm()).item()
+
+    pairs = {"out": (out.detach(), want.detach()), "dx": (xg.grad, wgx), "dW_fc1": (glayer.feed_forward.fc1.weight.grad, wg_fc1),
+             "dW_q": (glayer.self_attn.q_proj.weight.grad, wg_q)}
+    errs = {k: rel(*v) for k, v in pairs.items()}
+    frob = {k: fro(*v) for k, v in pairs.items()}
+    print(f"mus layer {mode}: max/scale " + ", ".join(f"{k} {v:.3g}" for k, v in errs.items())
+          + " | frobenius " + ", ".join(f"{k} {v:.3g}" for k, v in frob.items()))
     # the layer's output is a LayerNorm result (values of a few units): a bf16 step there is 1.6e-2 relative to the largest
     assert errs["out"] <= 3e-2, errs
-    assert errs["dx"] <= 4e-2 and errs["dW_fc1"] <= 4e-2 and errs["dW_q"] <= 4e-2, errs
-
-
-def _mu_layer_unit(layer, x, mask, pad, tau):
-    """OL.mu_layer with the static 1/sqrt(fan_in) output multiplier on every projection (alt/munit_scaling.py:22-34)."""
-    keep, add = math.sqrt(1.0 - tau), math.sqrt(tau)
-    E = x.shape[-1]
-    f_e, f_4e = {"x_scale": 1.0, "out_scale": E ** -0.5}, {"x_scale": 1.0, "out_scale": (4 * E) ** -0.5}
-    a = OL.attention_block(layer, x, mask, pad, f_e, sqrt_softmax=True)
-    s1 = OL.bf16r(keep * x + add * a)
-    T, B, _ = s1.shape
-    ff = layer.feed_forward
-    z = OL.linear(s1.reshape(T * B, E), ff.fc1.weight, ff.fc1.bias, f_e)
-    y2 = OL.bf16r(OL.linear(O.gelu_erf(z), ff.fc2.weight, ff.fc2.bias, f_4e)).reshape(T, B, E)
-    s2 = keep * s1 + add * y2
-    ln = layer.final_layer_norm
-    return OL.bf16r(torch.nn.functional.layer_norm(s2, (E,), ln.weight, ln.bias, ln.eps))
+    # Gradients.  bf16 products: a few bf16 steps.  8-bit products: an e5m2 number has two mantissa bits, and a gradient
+    # element that differs by one bf16 step between the two sides can round to e5m2 neighbours 12.5 - 25 % apart, so single
+    # elements of a weight gradient move by more than the bulk does; the bulk is held by the relative Frobenius error.
+    grad_tol = 4e-2 if mode == "bf16" else 1e-1
+    assert max(errs["dx"], errs["dW_fc1"], errs["dW_q"]) <= grad_tol, errs
+    assert max(frob.values()) <= (2e-2 if mode == "bf16" else 8e-2), frob
