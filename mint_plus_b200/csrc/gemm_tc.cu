@@ -359,14 +359,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 __nv_fp8_storage_t* op = reinterpret_cast<__nv_fp8_storage_t*>(o);
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
-                  op[j] = __nv_cvt_float_to_fp8(fminf(fmaxf(v[j] * p.out_scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+                  op[j] = __nv_cvt_float_to_fp8(v[j] * p.out_scale, __NV_SATFINITE, __NV_E4M3);
                 *reinterpret_cast<uint4*>(dst) = o[0];
                 *reinterpret_cast<uint4*>(dst + 16) = o[1];
               } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
                   if (n + j < p.N)
-                    dst[j] = __nv_cvt_float_to_fp8(fminf(fmaxf(v[j] * p.out_scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+                    dst[j] = __nv_cvt_float_to_fp8(v[j] * p.out_scale, __NV_SATFINITE, __NV_E4M3);
               }
             }
           }
@@ -386,7 +386,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
-// x (bf16) -> e4m3 with a per-tensor scale: q = sat(x * inv_scale); 16 elements per thread.
+// x (bf16) -> e4m3 with a per-tensor scale: q = sat(x * inv_scale); 16 elements per thread.  The conversion saturates
+// finite values at +-448 and keeps a NaN a NaN (an explicit clamp would turn it into -448 and hide a diverged run).
 __global__ void __launch_bounds__(256) quantize_e4m3_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_storage_t* __restrict__ out,
                                                             size_t n, float inv_scale) {
   const size_t i = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) * 16;
@@ -399,13 +400,13 @@ __global__ void __launch_bounds__(256) quantize_e4m3_kernel(const __nv_bfloat16*
     __nv_fp8_storage_t* op = reinterpret_cast<__nv_fp8_storage_t*>(&o);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      op[j] = __nv_cvt_float_to_fp8(fminf(fmaxf(__bfloat162float(ap[j]) * inv_scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
-      op[8 + j] = __nv_cvt_float_to_fp8(fminf(fmaxf(__bfloat162float(bp[j]) * inv_scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+      op[j] = __nv_cvt_float_to_fp8(__bfloat162float(ap[j]) * inv_scale, __NV_SATFINITE, __NV_E4M3);
+      op[8 + j] = __nv_cvt_float_to_fp8(__bfloat162float(bp[j]) * inv_scale, __NV_SATFINITE, __NV_E4M3);
     }
     *reinterpret_cast<uint4*>(out + i) = o;
   } else {
     for (size_t j = i; j < n; ++j)
-      out[j] = __nv_cvt_float_to_fp8(fminf(fmaxf(__bfloat162float(x[j]) * inv_scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+      out[j] = __nv_cvt_float_to_fp8(__bfloat162float(x[j]) * inv_scale, __NV_SATFINITE, __NV_E4M3);
   }
 }
 

@@ -70,8 +70,7 @@ class _Fp8FfnFn(torch.autograd.Function):
     gelu'(z) dy.  Without: bf16 products, gelu(z) rebuilt for fc2's weight gradient."""
 
     @staticmethod
-    def forward(ctx, x2d, w1, b1, w2, b2, wq1, ws1, xs1, os1, wq2, ws2, xs2, os2, gs1, gs2):
-        xq = ops._quantize_shared(x2d, xs1)      # the pass that produced x may have left the e4m3 copy already
+    def forward(ctx, x2d, w1, b1, w2, b2, wq1, ws1, xs1, os1, wq2, ws2, xs2, os2, gs1, gs2, xq):
         a8, z = ops.gemm_e4m3(xq, wq1, xs1 * ws1 * os1, b1, True, out_e4m3_scale=xs2, save_preact=True)
         y = ops.gemm_e4m3(a8, wq2, xs2 * ws2 * os2, b2, False)
         f8 = gs1 is not None and gs2 is not None
@@ -84,7 +83,7 @@ class _Fp8FfnFn(torch.autograd.Function):
         os1, os2, ws1, xs1, ws2, xs2, gs1, gs2 = ctx.cfg
         n = ctx.needs_input_grad
         dy = dy.contiguous()
-        tail = (None,) * 10
+        tail = (None,) * 11
         if gs1 is None:
             x2d, w1, b1, w2, b2, z = ctx.saved_tensors
             # fc2: bias gradient, then the gradient of its input; its weight gradient waits for gelu(z)
@@ -162,9 +161,10 @@ def fp8_ffn(fc1: "Fp8Linear", fc2: "Fp8Linear", x: torch.Tensor) -> torch.Tensor
     wq1, ws1 = fc1._quantized_weight()
     wq2, ws2 = fc2._quantized_weight()
     x2d = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+    xq = ops.e4m3_of(x, fc1.x_scale) if x.dtype == torch.bfloat16 else ops.quantize_e4m3(x2d, fc1.x_scale)   # the pass that produced x may have left the copy
     f8 = fc1.fp8_grads and fc2.fp8_grads
     y = _Fp8FfnFn.apply(x2d, fc1.weight, fc1.bias, fc2.weight, fc2.bias, wq1, ws1, fc1.x_scale, fc1.out_scale,
-                        wq2, ws2, fc2.x_scale, fc2.out_scale, fc1.grad_scale if f8 else None, fc2.grad_scale if f8 else None)
+                        wq2, ws2, fc2.x_scale, fc2.out_scale, fc1.grad_scale if f8 else None, fc2.grad_scale if f8 else None, xq)
     return y.view(*x.shape[:-1], fc2.out_features)
 
 
@@ -186,6 +186,19 @@ def fused_fp8_weight(owner: nn.Module, mods):
         cached = (key, ops.quantize_e4m3(w.to(torch.bfloat16).contiguous(), w_scale), w_scale)
         owner._fp8_qkv_cache = cached
     return cached[1], cached[2], max(m.x_scale for m in mods), mods[0].out_scale, (owner._fp8_qkv_grad_scale if f8_grads else None)
+
+
+def refresh_fp8_weights(model: nn.Module) -> nn.Module:
+    """Drop every cached e4m3 weight copy of `model`, so that the next forward pass casts the master weights again.
+    The caches notice in-place updates of a Parameter (optimizer steps, `weight.copy_`), which bump its version counter;
+    writes through `weight.data` (sharded or apex-style optimizers, broadcasts into `.data`) do not - call this after such
+    a write, or the forward pass keeps multiplying by the old e4m3 weights."""
+    for m in model.modules():
+        if isinstance(m, Fp8Linear):
+            m._wq, m._wq_key = None, None
+        if getattr(m, "_fp8_qkv_cache", None) is not None:
+            m._fp8_qkv_cache = None
+    return model
 
 
 def _sublayers(model):

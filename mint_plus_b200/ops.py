@@ -377,21 +377,19 @@ def quantize_e4m3(x: torch.Tensor, scale: float) -> torch.Tensor:
     return out
 
 
-_shared_q = None   # (x, key, e4m3 copy) of the last activation quantised for a fused QKV projection
+def attach_e4m3(t: torch.Tensor, q8: torch.Tensor, scale: float) -> None:
+    """Hand the e4m3 copy of `t` (cast with `scale`) to whoever receives `t` next: the copy rides on the tensor object itself.
+    The pass that produced `t` (a fused residual + LayerNorm) wrote it for the e4m3 projections that read `t` next."""
+    t._mintb_e4m3 = (q8, float(scale), t._version)
 
 
-def _quantize_shared(x2d: torch.Tensor, scale: float) -> torch.Tensor:
-    """quantize_e4m3 with a one-entry memo: the self and the cross pathway of a layer project the SAME activation, and
-    with equal activation scales (what `calibrate_fp8` measures on one tensor) the second projection reuses the first's
-    e4m3 copy.  The entry keeps its source tensor alive, so a matching address, version counter and stream mean the same
-    values."""
-    global _shared_q
-    key = (x2d.data_ptr(), x2d._version, tuple(x2d.shape), float(scale), _stream())
-    if _shared_q is not None and _shared_q[1] == key:
-        return _shared_q[2]
-    out = quantize_e4m3(x2d, scale)
-    _shared_q = (x2d, key, out)
-    return out
+def e4m3_of(t: torch.Tensor, scale: float) -> torch.Tensor:
+    """The e4m3 operand of a projection that reads the (rows, E) view of `t`: the copy attached by the pass that produced `t`
+    when there is one with this scale and `t` has not been written since, else a cast pass."""
+    hit = getattr(t, "_mintb_e4m3", None)
+    if hit is not None and hit[1] == float(scale) and hit[2] == t._version and hit[0].numel() == t.numel():
+        return hit[0].view(-1, t.shape[-1])
+    return quantize_e4m3(t.reshape(-1, t.shape[-1]), scale)
 
 
 def gemm_e4m3(xq: torch.Tensor, wq: torch.Tensor, alpha: float, bias=None, gelu: bool = False,
@@ -651,7 +649,6 @@ class _AddLayerNormFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, r, a, b, gamma, beta, eps, need_s, quant_scale=None):
-        global _shared_q
         E = x.shape[-1]
         x2 = x.reshape(-1, E).contiguous()
         r2 = r.reshape(-1, E).contiguous() if r is not None else None
@@ -668,16 +665,13 @@ class _AddLayerNormFn(torch.autograd.Function):
                                                    _ptr(stats), rows, E, float(eps), _ptr(q8),
                                                    1.0 / quant_scale if quant_scale else 1.0, _stream())
         L.check(rc, "mintb_add_layernorm_fwd")
-        if q8 is not None:   # hand it to the consumer through the one-entry memo of _quantize_shared
-            main = y if norm else s
-            _shared_q = (main, (main.data_ptr(), main._version, tuple(main.shape), float(quant_scale), _stream()), q8)
         ctx.save_for_backward(x2, r2, gamma, stats)
         ctx.cfg = (float(a), float(b), x.shape, pdt, beta is not None)
-        outs = (s.view(x.shape) if s is not None else None, y.view(x.shape) if y is not None else None)
-        return outs
+        ctx.mark_non_differentiable(*([q8] if q8 is not None else []))
+        return s.view(x.shape) if s is not None else None, y.view(x.shape) if y is not None else None, q8
 
     @staticmethod
-    def backward(ctx, ds_in, dy):
+    def backward(ctx, ds_in, dy, _dq8=None):
         x2, r2, gamma, stats = ctx.saved_tensors
         a, b, shape, pdt, has_beta = ctx.cfg
         rows, E = x2.shape
@@ -708,12 +702,17 @@ def add_layernorm(x, r, a: float, b: float, norm: Optional[torch.nn.LayerNorm], 
                   quant_scale: Optional[float] = None):
     """(s, y): s = a x + b r (r may be None), y = norm(s).  bf16 CUDA tensors; `norm` None returns (s, None).
     `quant_scale`: the activation scale of the e4m3 projection that reads the main result (y, or s without `norm`) next:
-    the kernel then writes that projection's e4m3 operand in the same pass and the projection finds it instead of casting."""
+    the kernel then writes that projection's e4m3 operand in the same pass; the copy rides on the returned tensor
+    (`attach_e4m3`) and the projection takes it from there (`e4m3_of`) instead of casting."""
     if x.dtype != torch.bfloat16 or not x.is_cuda:
         raise TypeError("add_layernorm takes bfloat16 CUDA tensors")
     if norm is None:
-        return _AddLayerNormFn.apply(x, r, a, b, None, None, 0.0, True, quant_scale)
-    return _AddLayerNormFn.apply(x, r, a, b, norm.weight, norm.bias, norm.eps, need_s, quant_scale)
+        s, y, q8 = _AddLayerNormFn.apply(x, r, a, b, None, None, 0.0, True, quant_scale)
+    else:
+        s, y, q8 = _AddLayerNormFn.apply(x, r, a, b, norm.weight, norm.bias, norm.eps, need_s, quant_scale)
+    if q8 is not None:
+        attach_e4m3(y if y is not None else s, q8, quant_scale)
+    return s, y
 
 
 def _rope_rotate_torch(t, cos, sin, inverse=False):
@@ -785,7 +784,7 @@ class _QkvFn(torch.autograd.Function):
             w_used = _lora_merged(w, lora_a, lora_b, lora_scaling)
             a_op, b_op, in_dt, alpha = x2d, (w_used if w_used.dtype == torch.bfloat16 else w_used.to(torch.bfloat16)).contiguous(), L.BF16, 1.0
         else:               # e4m3 operands, one scale per tensor; the product of the scales is folded into alpha
-            a_op, b_op, in_dt, alpha = _quantize_shared(x2d, x_scale), wq, L.E4M3, float(x_scale) * float(w_scale) * float(out_scale)
+            a_op, b_op, in_dt, alpha = e4m3_of(x, x_scale), wq, L.E4M3, float(x_scale) * float(w_scale) * float(out_scale)
         # packed: positions without a token are never written, and keys there are masked but still multiplied by a zero
         # probability, so they must hold finite numbers
         alloc = torch.zeros if pack is not None else torch.empty

@@ -225,3 +225,37 @@ def test_fp8_ffn_as_one_step_matches_the_two_projection_path():
     for a, b, n in zip(res[1], res[0], ("y", "dx", "dW1", "db1", "dW2", "db2")):
         err, scale = (a - b).abs().max().item(), b.abs().max().item()
         assert err <= 3e-2 * scale + 1e-3, f"{n}: {err:.4g} vs scale {scale:.4g}"
+
+
+def test_e4m3_cast_saturates_finite_values_and_keeps_nan():
+    """A diverged run must stay visible: NaN activations stay NaN through the e4m3 cast (a clamp would turn them into -448)."""
+    x = torch.tensor([0.5, -3.0, 1e6, -1e6, float("nan"), float("inf"), 448.0, 20.0] * 4, dtype=torch.bfloat16, device=DEV)
+    q = ops.quantize_e4m3(x, 1.0).float().cpu()
+    want = torch.tensor([0.5, -3.0, 448.0, -448.0, float("nan"), 448.0, 448.0, 20.0] * 4)
+    assert torch.equal(torch.isnan(q), torch.isnan(want))
+    assert torch.equal(q[~torch.isnan(q)], want[~torch.isnan(want)])
+    # and through a projection: one NaN in x poisons its output row, the other rows stay finite
+    xm = torch.randn(64, 128, device=DEV).to(torch.bfloat16)
+    xm[3, 5] = float("nan")
+    w = ops.quantize_e4m3(torch.randn(64, 128, device=DEV).to(torch.bfloat16), 1.0)
+    y = ops.gemm_e4m3(ops.quantize_e4m3(xm, 1.0), w, 1.0).float()
+    assert torch.isnan(y[3]).all() and torch.isfinite(y[:3]).all() and torch.isfinite(y[4:]).all()
+
+
+def test_fp8_weight_cache_follows_in_place_updates_and_refresh():
+    from mint_plus_b200.mu_scaling import Fp8Linear, refresh_fp8_weights
+    torch.manual_seed(2)
+    lin = Fp8Linear(128, 64).cuda().to(torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.normal_(0, 1)
+    x = torch.randn(32, 128, device=DEV).to(torch.bfloat16)
+    y0 = lin(x).float()
+    with torch.no_grad():
+        lin.weight.mul_(2.0)                        # in place on the Parameter: the version counter moves, the cache follows
+    y1 = lin(x).float()
+    assert (y1 - 2 * y0).abs().max().item() <= 2e-2 * y1.abs().max().item()
+    lin.weight.data.mul_(0.5)                       # an in-place write through .data is invisible to the cache ...
+    assert torch.equal(lin(x).float(), y1)
+    refresh_fp8_weights(lin)                        # ... until it is dropped
+    y2 = lin(x).float()
+    assert (y2 - y0).abs().max().item() <= 2e-2 * y0.abs().max().item()

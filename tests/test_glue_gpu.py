@@ -123,6 +123,35 @@ def test_gelu_backward_and_bias_gradient(shape, with_z):
     assert (db - want_db).abs().max().item() <= 1e-3 * want_db.abs().max().item() + 1e-3
 
 
+@pytest.mark.parametrize("shape", [(300, 1280), (513, 72)])
+@pytest.mark.parametrize("with_z", [True, False])
+def test_e5m2_gradient_copy_and_its_bias_gradient(shape, with_z):
+    """mintb_gelu_bwd_colsum_f8: dz = dy gelu'(z) (dy without z) leaves the pass as e5m2 numbers saturate(dz / scale) - the
+    operand of the 8-bit dgrad / wgrad products - and db sums those very numbers times the scale
+    (mint_plus/models/alt/munit_scaling.py:41-55 of the reference)."""
+    torch.manual_seed(4)
+    M, N = shape
+    dy = _bf(torch.randn(M, N, device=DEV))
+    dy[0, :8] = _bf(torch.tensor([1e4, -1e4, 3e-7, 0.0, 1.0, -1.0, 2.5, 1e-3], device=DEV))
+    z = _bf(2 * torch.randn(M, N, device=DEV)) if with_z else None
+    scale = 0.01                                          # 1e4 / 0.01 = 1e6 saturates at 57344
+    dz8, db, dz = ops.grad_colsum_f8(dy, z, True, scale, want_dz=True)
+    want = dy.float()
+    if with_z:
+        zf = z.float().requires_grad_(True)
+        torch.nn.functional.gelu(zf).backward(dy.float())
+        want = zf.grad
+        assert (dz.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item() + 1e-3
+    deq = dz8.float() * scale
+    ref = (want / scale).clamp(-57344.0, 57344.0).to(torch.float8_e5m2).float() * scale
+    # e5m2 has two mantissa bits: the kernel's fp32 value and the reference's may round to neighbours (one step = 25 %)
+    close = (deq - ref).abs() <= 0.26 * ref.abs() + 1e-7
+    assert close.all() and (deq == ref).float().mean().item() > 0.98
+    assert deq.abs().max().item() == 57344.0 * scale     # saturated, finite
+    want_db = deq.sum(0)
+    assert (db - want_db).abs().max().item() <= 1e-3 * want_db.abs().max().item() + 1e-4
+
+
 @pytest.mark.parametrize("D", [16, 32, 64])
 @pytest.mark.parametrize("rope", [True, False])
 def test_qkv_gradient_pack(D, rope):
@@ -164,16 +193,17 @@ def test_qkv_gradient_pack(D, rope):
 @pytest.mark.parametrize("with_norm", [True, False])
 def test_add_layernorm_writes_the_e4m3_operand_of_the_next_projection(with_norm):
     """quant_scale: the pass also leaves sat(result / scale) in e4m3 — the very bytes quantize_e4m3 gives — where the next
-    FP8 projection looks for it."""
+    FP8 projection looks for it (attached to the returned tensor)."""
     torch.manual_seed(2)
     x, r = _bf(3 * torch.randn(70, 2, 640, device=DEV)), _bf(3 * torch.randn(70, 2, 640, device=DEV))
     norm = torch.nn.LayerNorm(640).to(DEV, torch.bfloat16) if with_norm else None
     scale = 0.004                                     # small enough that some values saturate at 448
     s, y = ops.add_layernorm(x, r, 0.8, 0.6, norm, need_s=not with_norm, quant_scale=scale)
-    main = (y if with_norm else s).reshape(-1, 640)
-    got = ops._quantize_shared(main, scale)            # served from the memo the pass has filled
-    assert ops._shared_q[2] is got
-    want = ops.quantize_e4m3(main.contiguous(), scale)
+    main = y if with_norm else s
+    assert main._mintb_e4m3[1] == scale                # the copy rides on the tensor the pass returned
+    got = ops.e4m3_of(main, scale)
+    assert got.data_ptr() == main._mintb_e4m3[0].data_ptr() and tuple(got.shape) == (140, 640)
+    want = ops.quantize_e4m3(main.reshape(-1, 640).contiguous(), scale)
     assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
     assert (want.float().abs() == 448).any()
 

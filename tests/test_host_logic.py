@@ -140,3 +140,16 @@ def test_rotary_frequencies_stay_fp32_through_a_model_cast():
     assert layer.self_attn.rot_emb.inv_freq.dtype == torch.float32
     assert layer.self_attn.out_proj.weight.dtype == torch.bfloat16
     assert "self_attn.rot_emb.inv_freq" in layer.state_dict()
+
+
+def test_e4m3_copy_rides_on_the_tensor_and_expires_when_it_is_written():
+    from mint_plus_b200 import ops
+    t = torch.zeros(6, 2, 8)
+    q8 = torch.zeros(12, 8, dtype=torch.uint8)
+    ops.attach_e4m3(t, q8, 0.5)
+    assert ops.e4m3_of(t, 0.5).data_ptr() == q8.data_ptr() and tuple(ops.e4m3_of(t, 0.5).shape) == (12, 8)
+    with pytest.raises(RuntimeError):           # another scale: a cast pass is needed, and that runs on CUDA tensors only
+        ops.e4m3_of(t, 1.0)
+    t.add_(1.0)                                 # written since: the copy no longer describes it
+    with pytest.raises(RuntimeError):
+        ops.e4m3_of(t, 0.5)
