@@ -263,6 +263,30 @@ MINTB_API int mintb_qkv_grad_pack(const void* dq, const void* dk, const void* dv
                                   const float* rope_sin, const int32_t* row_map, int n_rows, int T, int B, int H, int D,
                                   float q_scale, void* stream);
 
+/* ---------------------------------------------------------------------------------------------------
+ * The two ends of the model around the layer stack (HBM-bound, one pass each).
+ *
+ * mintb_embed_fwd: the prologue of MINT.forward (esm2.py:91-104): out[t][b][:] = weight[tokens[b][t]][:] * f(b, t), written
+ *   sequence-first (T,B,E); f = 0 for <pad>, 0 for <mask> when token_dropout, else the row's rescale
+ *   (1 - mask_ratio_train) / (1 - masked_b / unpadded_b) when token_dropout, else 1.  tokens int64 [B][T]; weight and out
+ *   f32 or bf16 (dtype); row_scales[B] (may be NULL) receives the rescale of each row for the backward pass.
+ * mintb_embed_bwd: d_weight[V][E] (fp32, overwritten) = sum over tokens of f(b, t) * d_out[t][b][:] into row tokens[b][t]
+ *   (private sums per CTA, then fp32 atomics: the order of the additions is not fixed).  V <= 64.
+ * mintb_masked_ce_fwd: the loss of the masked-language-model step (training/wrapper.py:77-80): sums[0] = sum over rows with
+ *   mask != 0 of (logsumexp(logits[i][:V]) - logits[i][targets[i]]), sums[1] = number of such rows, lse[i] for the backward
+ *   pass; logits bf16 [N][ld] (ld >= V: row stride in elements), fp32 arithmetic.  The mean is sums[0] / sums[1].
+ * mintb_masked_ce_bwd: d_logits[N][ld] (bf16) = (softmax(logits[i]) - onehot(targets[i])) * grad_loss[0] / sums[1] at the
+ *   masked rows, 0 elsewhere and in the columns past V.
+ */
+MINTB_API int mintb_embed_fwd(const long long* tokens, const void* weight, void* out, float* row_scales, int B, int T, int E, int V,
+                              int dtype, int pad_idx, int mask_idx, int token_dropout, float mask_ratio_train, void* stream);
+MINTB_API int mintb_embed_bwd(const long long* tokens, const void* d_out, const float* row_scales, float* d_weight, int B, int T,
+                              int E, int V, int dtype, int pad_idx, int mask_idx, int token_dropout, void* stream);
+MINTB_API int mintb_masked_ce_fwd(const void* logits, const long long* targets, const unsigned char* mask, float* lse, float* sums,
+                                  int N, int ld, int V, void* stream);
+MINTB_API int mintb_masked_ce_bwd(const void* logits, const long long* targets, const unsigned char* mask, const float* lse,
+                                  const float* sums, const float* grad_loss, void* d_logits, int N, int ld, int V, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

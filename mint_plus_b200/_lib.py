@@ -54,6 +54,10 @@ PROTOTYPES = {
     "mintb_gelu_bwd_colsum_act": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, _P]),
     "mintb_gelu_bwd_colsum_f8": (c_int, [_P, _P, _P, _P, _P, _P, c_float, c_int, c_int, _P]),
     "mintb_qkv_grad_pack": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P]),
+    "mintb_embed_fwd": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P]),
+    "mintb_embed_bwd": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
+    "mintb_masked_ce_fwd": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P]),
+    "mintb_masked_ce_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P]),
     "mintb_combine_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "mintb_combine_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "mintb_combine_bwd": (c_int, [_P] * 10 + [_P, c_size_t, c_int, c_int, c_int, c_int, c_int, _P]),

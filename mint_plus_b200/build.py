@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmintb.so")
-SOURCES = ["api.cu", "prep.cu", "attn_simt.cu", "attn_tc.cu", "attn_tc_bwd.cu", "gemm_tc.cu", "gemm_bwd.cu", "combine.cu", "glue.cu", "selftest.cu"]
+SOURCES = ["api.cu", "prep.cu", "attn_simt.cu", "attn_tc.cu", "attn_tc_bwd.cu", "gemm_tc.cu", "gemm_bwd.cu", "combine.cu", "glue.cu", "embed_loss.cu", "selftest.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

@@ -126,20 +126,27 @@ class MINT(nn.Module):
             if not self.use_multimer:
                 self_attn_mask = None                                 # a single-pathway model attends everywhere
 
-        x = self.embed_tokens(tokens)
-        if self.token_dropout and self.training:
-            x = x.masked_fill((tokens == self.mask_idx).unsqueeze(-1), 0.0)
-            mask_ratio_train = 0.15 * 0.8
-            src_lengths = (~padding_mask).sum(-1)
-            mask_ratio_observed = (tokens == self.mask_idx).sum(-1).to(x.dtype) / src_lengths
-            x = x * (1 - mask_ratio_train) / (1 - mask_ratio_observed)[:, None, None]
-        x = x * (1 - padding_mask.unsqueeze(-1).type_as(x))
-
         repr_layers = set(repr_layers)
         hidden_representations = {}
-        if 0 in repr_layers:
-            hidden_representations[0] = x
-        x = x.transpose(0, 1).contiguous()                             # (B,T,E) -> (T,B,E), laid out sequence-first
+        w_emb = self.embed_tokens.weight
+        if tokens.is_cuda and w_emb.dtype in (torch.float32, torch.bfloat16) and (self.embed_dim * w_emb.element_size()) % 16 == 0:
+            # on the GPU: lookup, token-dropout rescale, <mask> / <pad> zeroing and the (B,T,E) -> (T,B,E) layout change in one pass
+            from . import ops
+            x = ops.embed_tokens(tokens, w_emb, self.padding_idx, self.mask_idx, bool(self.token_dropout and self.training), 0.15 * 0.8)
+            if 0 in repr_layers:
+                hidden_representations[0] = x.transpose(0, 1)
+        else:
+            x = self.embed_tokens(tokens)
+            if self.token_dropout and self.training:
+                x = x.masked_fill((tokens == self.mask_idx).unsqueeze(-1), 0.0)
+                mask_ratio_train = 0.15 * 0.8
+                src_lengths = (~padding_mask).sum(-1)
+                mask_ratio_observed = (tokens == self.mask_idx).sum(-1).to(x.dtype) / src_lengths
+                x = x * (1 - mask_ratio_train) / (1 - mask_ratio_observed)[:, None, None]
+            x = x * (1 - padding_mask.unsqueeze(-1).type_as(x))
+            if 0 in repr_layers:
+                hidden_representations[0] = x
+            x = x.transpose(0, 1).contiguous()                         # (B,T,E) -> (T,B,E), laid out sequence-first
         pack = None
         if self.pack_padding:
             if self_attn_mask is not None or not (x.is_cuda and x.dtype == torch.bfloat16):
@@ -174,11 +181,17 @@ class MINT(nn.Module):
             if (layer_idx + 1) in repr_layers:
                 hidden_representations[layer_idx + 1] = unpack(x).transpose(0, 1)
 
-        x = unpack(self.emb_layer_norm_after(x))
-        x = x.transpose(0, 1)                                          # (T,B,E) -> (B,T,E)
+        if x.is_cuda and x.dtype == torch.bfloat16 and isinstance(self.emb_layer_norm_after, nn.LayerNorm):
+            from . import ops
+            _, x = ops.add_layernorm(x, None, 1.0, 0.0, self.emb_layer_norm_after, need_s=False)
+            x = unpack(x)
+        else:
+            x = unpack(self.emb_layer_norm_after(x))
         if (layer_idx + 1) in repr_layers:
-            hidden_representations[layer_idx + 1] = x
-        logits = self.lm_head(x)
+            hidden_representations[layer_idx + 1] = x.transpose(0, 1)
+        # the head runs on the sequence-first rows as they are; (T,B,V) -> (B,T,V) is a copy of the small logits tensor only
+        # (contiguous, as the reference returns them: callers reshape them with .view)
+        logits = self.lm_head(x).transpose(0, 1).contiguous()
         return {"logits": logits, "representations": hidden_representations}
 
     def _want_checkpoint(self, x: torch.Tensor) -> bool:

@@ -40,6 +40,17 @@ class RobertaLMHead(nn.Module):
         self.bias = nn.Parameter(torch.zeros(output_dim))
 
     def forward(self, features):
+        if features.is_cuda and features.dtype == torch.bfloat16 and type(self.dense) is nn.Linear and self.weight.dtype == torch.bfloat16:
+            # bf16 on the GPU: dense + erf-GELU in one tcgen05 GEMM, the LayerNorm kernel, and the tied projection as a GEMM on
+            # the vocabulary padded to a multiple of 8 rows (the extra logits are sliced off again)
+            from . import ops
+            h = ops.linear(features, self.dense.weight, self.dense.bias, gelu=True)
+            _, h = ops.add_layernorm(h, None, 1.0, 0.0, self.layer_norm, need_s=False)
+            V = self.weight.shape[0]
+            extra = (-V) % 8
+            w = F.pad(self.weight, (0, 0, 0, extra)) if extra else self.weight
+            b = F.pad(self.bias, (0, extra)) if extra else self.bias
+            return ops.linear(h, w, b)[..., :V]
         x = self.layer_norm(F.gelu(self.dense(features)))
         return F.linear(x, self.weight) + self.bias
 

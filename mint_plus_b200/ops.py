@@ -971,3 +971,93 @@ def qkv_project(x: torch.Tensor, weight: torch.Tensor, bias, num_heads: int, rop
     wq, w_scale, x_scale, out_scale, gs = (tuple(fp8) + (None,) * (5 - len(fp8))) if fp8 is not None else (None, 1.0, 1.0, 1.0, None)
     la, lb, ls = lora if lora is not None else (None, None, 1.0)
     return _QkvFn.apply(x, weight, bias, num_heads, cos, sin, q_scale, wq, w_scale, x_scale, out_scale, gs, pack, la, lb, ls)
+
+
+# ----------------------------------------------------------------------------------------------- model prologue / epilogue
+class _EmbedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tokens, weight, pad_idx, mask_idx, token_dropout, mask_ratio_train):
+        B, T = tokens.shape
+        V, E = weight.shape
+        out = torch.empty(T, B, E, dtype=weight.dtype, device=weight.device)
+        scales = torch.empty(B, dtype=torch.float32, device=weight.device)
+        w = weight.contiguous()
+        with _on(weight.device):
+            rc = L.lib().mintb_embed_fwd(_ptr(tokens), _ptr(w), _ptr(out), _ptr(scales), B, T, E, V, _DTYPES[weight.dtype], int(pad_idx),
+                                         int(mask_idx), int(bool(token_dropout)), float(mask_ratio_train), _stream())
+        L.check(rc, "mintb_embed_fwd")
+        ctx.save_for_backward(tokens, scales)
+        ctx.cfg = (V, E, weight.dtype, int(pad_idx), int(mask_idx), int(bool(token_dropout)))
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        tokens, scales = ctx.saved_tensors
+        V, E, dt, pad_idx, mask_idx, td = ctx.cfg
+        B, T = tokens.shape
+        d_out = d_out.contiguous()
+        dw = torch.empty(V, E, dtype=torch.float32, device=d_out.device)
+        with _on(d_out.device):
+            rc = L.lib().mintb_embed_bwd(_ptr(tokens), _ptr(d_out), _ptr(scales), _ptr(dw), B, T, E, V, _DTYPES[dt], pad_idx, mask_idx, td,
+                                         _stream())
+        L.check(rc, "mintb_embed_bwd")
+        return None, dw.to(dt), None, None, None, None
+
+
+def embed_tokens(tokens: torch.Tensor, weight: torch.Tensor, pad_idx: int, mask_idx: int, token_dropout: bool,
+                 mask_ratio_train: float = 0.12) -> torch.Tensor:
+    """The model's prologue in one pass (esm2.py:91-104 of the reference): x = W[tokens]; under token dropout <mask> rows are
+    zeroed and every row of sample b is multiplied by (1 - mask_ratio_train) / (1 - masked_b / unpadded_b); <pad> rows are
+    zeroed; the result is written sequence-first, (T, B, E), the layout of the layer stack.  tokens (B, T) int64 on the
+    device; weight (V, E) fp32 or bf16; differentiable with respect to the weight."""
+    _require_cuda(tokens, weight)
+    if tokens.dtype != torch.int64 or tokens.dim() != 2 or weight.dtype not in _DTYPES:
+        raise TypeError("embed_tokens takes int64 tokens (B, T) and an fp32 or bf16 weight (V, E)")
+    return _EmbedFn.apply(tokens.contiguous(), weight, pad_idx, mask_idx, token_dropout, mask_ratio_train)
+
+
+class _MaskedCeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, rows, targets, mask_u8, V):
+        N, ld = rows.shape[0], rows.stride(0)
+        lse = torch.empty(N, dtype=torch.float32, device=rows.device)
+        sums = torch.empty(2, dtype=torch.float32, device=rows.device)
+        with _on(rows.device):
+            rc = L.lib().mintb_masked_ce_fwd(_ptr(rows), _ptr(targets), _ptr(mask_u8), _ptr(lse), _ptr(sums), N, ld, V, _stream())
+        L.check(rc, "mintb_masked_ce_fwd")
+        ctx.save_for_backward(rows, targets, mask_u8, lse, sums)
+        ctx.V = V
+        return sums[0] / sums[1]
+
+    @staticmethod
+    def backward(ctx, g):
+        rows, targets, mask_u8, lse, sums = ctx.saved_tensors
+        N, ld = rows.shape[0], rows.stride(0)
+        d_pad = torch.empty(N, ld, dtype=torch.bfloat16, device=rows.device)
+        g32 = g.detach().to(torch.float32).reshape(1).contiguous()
+        with _on(rows.device):
+            rc = L.lib().mintb_masked_ce_bwd(_ptr(rows), _ptr(targets), _ptr(mask_u8), _ptr(lse), _ptr(sums), _ptr(g32), _ptr(d_pad), N, ld,
+                                             ctx.V, _stream())
+        L.check(rc, "mintb_masked_ce_bwd")
+        return d_pad[:, :rows.shape[1]], None, None, None
+
+
+def masked_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, target_mask: torch.Tensor) -> torch.Tensor:
+    """mean over the target positions of cross_entropy(logits, targets) (training/wrapper.py:77-80 of the reference) in one
+    pass over the logits, fp32 arithmetic: logits (B, T, V) bf16 on the device — a (T, B)-ordered or (B, T)-ordered view of
+    rows with 16-byte aligned stride is read in place — targets (B, T) int64, target_mask (B, T) bool.  Differentiable with
+    respect to the logits."""
+    _require_cuda(logits, targets, target_mask)
+    if logits.dtype != torch.bfloat16 or logits.dim() != 3 or logits.stride(-1) != 1:
+        raise TypeError("masked_cross_entropy takes bfloat16 logits (B, T, V) with a contiguous last dimension")
+    B, T, V = logits.shape
+    if logits.stride(0) == T * logits.stride(1):                         # rows in (B, T) order
+        rows = torch.as_strided(logits, (B * T, V), (logits.stride(1), 1), logits.storage_offset())
+        tg, mk = targets, target_mask
+    elif logits.stride(1) == B * logits.stride(0):                       # rows in (T, B) order: a transposed view
+        rows = torch.as_strided(logits, (T * B, V), (logits.stride(0), 1), logits.storage_offset())
+        tg, mk = targets.t(), target_mask.t()
+    else:
+        c = logits.contiguous()
+        rows, tg, mk = c.view(B * T, V), targets, target_mask
+    return _MaskedCeFn.apply(rows, tg.contiguous().view(-1), mk.contiguous().view(-1).to(torch.uint8), V)

@@ -28,6 +28,10 @@ def shared_step(model, batch, generator: Optional[torch.Generator] = None) -> Tu
     tokens, chain_ids = batch
     inp, target = mlm_corrupt(tokens, 0, model.eos_idx, model.padding_idx, model.mask_idx, generator)
     out = model(inp, chain_ids=chain_ids)["logits"]
-    loss = F.cross_entropy(out.float().transpose(1, 2), tokens, reduction="none")
-    loss = (loss * target).sum() / target.sum()
+    if out.is_cuda and out.dtype == torch.bfloat16:
+        from . import ops
+        loss = ops.masked_cross_entropy(out, tokens, target)      # one pass over the logits, fp32 arithmetic
+    else:
+        loss = F.cross_entropy(out.float().transpose(1, 2), tokens, reduction="none")
+        loss = (loss * target).sum() / target.sum()
     return loss, torch.exp(loss.detach())

@@ -145,9 +145,9 @@ def test_e5m2_gradient_copy_and_its_bias_gradient(shape, with_z):
     deq = dz8.float() * scale
     ref = (want / scale).clamp(-57344.0, 57344.0).to(torch.float8_e5m2).float() * scale
     # e5m2 has two mantissa bits: the kernel's fp32 value and the reference's may round to neighbours (one step = 25 %)
-    close = (deq - ref).abs() <= 0.26 * ref.abs() + 1e-7
+    close = (deq - ref).abs() <= 0.26 * ref.abs() + 1.01 * 2.0 ** -16 * scale       # (or by one subnormal step near zero)
     assert close.all() and (deq == ref).float().mean().item() > 0.98
-    assert deq.abs().max().item() == 57344.0 * scale     # saturated, finite
+    assert deq.abs().max().item() == pytest.approx(57344.0 * scale, rel=1e-6)     # saturated, finite
     want_db = deq.sum(0)
     assert (db - want_db).abs().max().item() <= 1e-3 * want_db.abs().max().item() + 1e-4
 
