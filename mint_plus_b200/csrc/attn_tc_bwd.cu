@@ -283,6 +283,53 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   const int nqt = (p.T + kBwdTile - 1) / kBwdTile;
   const uint8_t want = path == 0 ? kHasIntra : kHasInter;
 
+  const CUtensorMap* mq = path == 0 ? &map_qs : &map_qc;
+  const CUtensorMap* mk = path == 0 ? &map_ks : &map_kc;
+  const CUtensorMap* mv = path == 0 ? &map_vs : &map_vc;
+
+  // the gradients of a key tile without a single pair of this pathway are zero
+  auto write_zero_gradients = [&]() {
+    for (int idx = tid; idx < kBwdTile * (D / 8); idx += kBwdThreads) {
+      const int row = idx / (D / 8), vec = idx % (D / 8);
+      if (k0 + row < p.T) {
+        size_t base = size_t(k0 + row) * p.g_row + size_t(b) * p.g_b;
+        if (p.token_row != nullptr) {
+          const int tr = __ldg(p.token_row + size_t(k0 + row) * p.B + b);
+          if (tr < 0) continue;
+          base = size_t(tr) * p.g_b;
+        }
+        const size_t off = base + size_t(bh % p.H) * p.g_h + vec * 8;
+        *reinterpret_cast<uint4*>(p.dk[path] + off) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(p.dv[path] + off) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+  // Every key of the tile padded (padded batches have many such tiles): leave before any barrier, TMEM or copy is set up.
+  {
+    const uint32_t* w = p.kpad + size_t(b) * p.TW + 4 * kt;
+    if ((w[0] & w[1] & w[2] & w[3]) == 0xffffffffu) {   // uniform over the CTA
+      write_zero_gradients();
+      return;
+    }
+  }
+  if (tid == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(acc_full, 2);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 2);      // released by the dV and the dK stream
+      mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], kComputeThreads);
+      mbar_init(&buf_free[s], 2);                                // dV and dK of a half have read P^T, dS^T
+    }
+    for (int s = 0; s < 2; ++s) { mbar_init(&dq_full[s], 1); mbar_init(&dq_empty[s], kComputeThreads); }
+    fence_mbar_init();
+    // K and V of the tile do not depend on the query-tile scan below: their copies run while it does
+    prefetch_tensormap(mk); prefetch_tensormap(mv);
+    mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
+    tma_load_3d(sK, mk, kv_full, 0, k0, bh);
+    tma_load_3d(sV, mv, kv_full, 0, k0, bh);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::kTmemCols); tmem_relinquish(); }
+
   int any_active = 0;
   for (int i = tid; i < nqt; i += kBwdThreads) {
     uint8_t c = 0;
@@ -300,48 +347,25 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     tq[i] = f;
     any_active |= f;
   }
-  // A key tile without a single pair of this pathway (all its keys padded, or every query on the other side of the mask)
-  // has zero gradients: write them and leave before any barrier, TMEM or copy is set up.  Padded batches have many such tiles.
-  if (__syncthreads_or(any_active) == 0) {
-    for (int idx = tid; idx < kBwdTile * (D / 8); idx += kBwdThreads) {
-      const int row = idx / (D / 8), vec = idx % (D / 8);
-      if (k0 + row < p.T) {
-        size_t base = size_t(k0 + row) * p.g_row + size_t(b) * p.g_b;
-        if (p.token_row != nullptr) {
-          const int tr = __ldg(p.token_row + size_t(k0 + row) * p.B + b);
-          if (tr < 0) continue;
-          base = size_t(tr) * p.g_b;
-        }
-        const size_t off = base + size_t(bh % p.H) * p.g_h + vec * 8;
-        *reinterpret_cast<uint4*>(p.dk[path] + off) = make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(p.dv[path] + off) = make_uint4(0u, 0u, 0u, 0u);
-      }
+  tc_fence_before();
+  any_active = __syncthreads_or(any_active);
+  tc_fence_after();
+  const uint32_t tbase = *tmem_slot;
+  if (any_active == 0) {
+    // no query tile holds a pair of this pathway (every query on the other side of the mask): zero gradients; the copies of
+    // K and V must have landed and TMEM must be given back before the CTA leaves
+    write_zero_gradients();
+    if (tid == 0) mbar_wait(kv_full, 0, p.status, 0x500);
+    __syncthreads();
+    if (warp == 1) {
+      __syncwarp();
+      tmem_dealloc(tbase, Cfg::kTmemCols);
     }
     return;
   }
-  if (tid == 0) {
-    mbar_init(kv_full, 1);
-    mbar_init(acc_full, 2);
-    for (int s = 0; s < 3; ++s) {
-      mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 2);      // released by the dV and the dK stream
-      mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], kComputeThreads);
-      mbar_init(&buf_free[s], 2);                                // dV and dK of a half have read P^T, dS^T
-    }
-    for (int s = 0; s < 2; ++s) { mbar_init(&dq_full[s], 1); mbar_init(&dq_empty[s], kComputeThreads); }
-    fence_mbar_init();
-  }
-  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::kTmemCols); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tbase = *tmem_slot;
   int n_active = 0;
   for (int i = 0; i < nqt; ++i) n_active += tq[i] != 0;
   const int n_sub = 2 * n_active;   // 64-query halves, numbered u = 2 * tile + half; half u lives in buffer u % kNBuf
-
-  const CUtensorMap* mq = path == 0 ? &map_qs : &map_qc;
-  const CUtensorMap* mk = path == 0 ? &map_ks : &map_kc;
-  const CUtensorMap* mv = path == 0 ? &map_vs : &map_vc;
 
   if (warp == 1) {
     // ---------------------------------------------------------------- MMA stream A: S^T = K Q^T and dP^T = V dO^T
@@ -426,10 +450,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       const uint32_t ds_lo = desc_addr32(smem_u32(sDS)) + desc_lbo32(Cfg::kDsBlock);
       const uint32_t kb_lo = desc_addr32(smem_u32(sK)) + desc_lbo32(8 * RB);
       constexpr uint32_t kDsU = Cfg::kDsBytes >> 4, kAStep = (16 * 128) >> 4, kBStep = (16 * RB) >> 4;
-      prefetch_tensormap(mq); prefetch_tensormap(mk); prefetch_tensormap(mv); prefetch_tensormap(&map_do);
-      mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
-      tma_load_3d(sK, mk, kv_full, 0, k0, bh);
-      tma_load_3d(sV, mv, kv_full, 0, k0, bh);
+      prefetch_tensormap(mq); prefetch_tensormap(&map_do);      // (K and V were requested before the query-tile scan)
       int next_q = 0;        // next query tile index to look at
       Ring<kQStages> lr;     // stage the next load goes to
       auto load_next = [&]() {   // issue the loads of the next active query tile
@@ -595,7 +616,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       ++it;
     }
     if (ok && prev_tile >= 0) ok = drain_dq(it - 1, prev_tile);
-    if (lane == 0) bulk_wait_all();   // the reductions must have landed before the kernel ends
+    if (lane == 0) bulk_wait_read_all();   // the reductions have read their staging rows (their additions may still be under way)
 
     // ---- epilogue: 16-column groups vg 0,1 write the two column halves of dK (scaled, un-rotated for the self pathway),
     //      vg 2,3 those of dV

@@ -229,7 +229,7 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
       mbar_arrive(&acc_empty[ab]);
       if (++ab == 2) { ab = 0; ab_phase ^= 1; }
     }
-    if (lane == 0) bulk_wait_all();   // outstanding bulk operations must have landed before the kernel ends
+    if (lane == 0) bulk_wait_read_all();   // the bulk operations have read their staging rows (the kernel boundary orders their writes)
   }
   tc_fence_before();
   __syncthreads();
