@@ -198,6 +198,23 @@ MINTB_API int mintb_qkv_fwd(const void* x, const void* w, const void* bias, void
                             int D, int in_dtype, int bias_dtype, float alpha, float q_scale, const float* rope_cos,
                             const float* rope_sin, const int32_t* row_map, int n_rows, void* stream, int* dev_status);
 MINTB_API int mintb_quantize_e4m3(const void* x, void* out, size_t n, float inv_scale, void* stream);
+/* mintb_linear_res_fwd: mintb_linear_fwd without activation and with the layer's residual sum formed in the epilogue:
+ * out[M][N] = res_a * resid[M][N] + res_b * (alpha * x w^T + bias) - x + out_proj(attention) of the Pre-LN layer
+ * (modules.py:183-186: res_a = res_b = 1) and sqrt(1 - tau) x + sqrt(tau) out_proj(attention) of the muS layer
+ * (mu_scaling/layer.py:262-266).  resid bf16 (NULL: no residual).  With an e4m3 `out` (the operand of the projection that
+ * reads the sum next) bf16_copy_out, when non-null, receives the sum in bf16 and the e4m3 numbers are cast from those bf16
+ * values.
+ * mintb_qkv2_fwd: mintb_qkv_fwd for BOTH pathways of a layer in one product: w is [6E][E] with rows [Q1;K1;V1;Q2;K2;V2],
+ * bias [6E]; the first pathway's q and k are rotated when the tables are given, the second pathway's never; alpha1 / alpha2
+ * multiply the two pathways' columns (their weights carry separate e4m3 scales); q_scale multiplies both q thirds.  The
+ * activation is read once instead of twice (modules.py:179-195 computes the two projections as separate Linears). */
+MINTB_API int mintb_linear_res_fwd(const void* x, const void* w, const void* bias, const void* resid, float res_a, float res_b,
+                                   void* out, void* bf16_copy_out, int M, int N, int K, int in_dtype, int bias_dtype,
+                                   int out_dtype, float alpha, float out_scale, void* stream, int* dev_status);
+MINTB_API int mintb_qkv2_fwd(const void* x, const void* w, const void* bias, void* q1, void* k1, void* v1, void* q2, void* k2,
+                             void* v2, int T, int B, int H, int D, int in_dtype, int bias_dtype, float alpha1, float alpha2,
+                             float q_scale, const float* rope_cos, const float* rope_sin, const int32_t* row_map, int n_rows,
+                             void* stream, int* dev_status);
 
 /* Backward of the projections: the two products torch.autograd forms for y = x w^T (attention.py:68, modules.py:326-334;
  * te.Linear's backward under mu_scaling/__init__.py:83-124; alt/munit_scaling.py:36-55 states the 8-bit variant: gradient

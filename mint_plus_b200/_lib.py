@@ -42,6 +42,9 @@ PROTOTYPES = {
     "mintb_qkv_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P, _P, _P, c_int,
                               _P, _P]),
     "mintb_quantize_e4m3": (c_int, [_P, _P, c_size_t, c_float, _P]),
+    "mintb_linear_res_fwd": (c_int, [_P, _P, _P, _P, c_float, c_float, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                     _P, _P]),
+    "mintb_qkv2_fwd": (c_int, [_P] * 9 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, _P, _P, _P, c_int, _P, _P]),
     "mintb_linear_dgrad": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P]),
     "mintb_linear_wgrad_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "mintb_linear_wgrad": (c_int, [_P, _P, _P, _P, c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P]),

@@ -33,12 +33,15 @@ struct GemmParams {
   int bias_dtype;              // MINTB_F32 or MINTB_BF16
   int epilogue;
   float alpha;                 // multiplies the accumulator (product of the operands' dequantisation scales)
+  float alpha2;                // head-major epilogue with two pathways: the multiplier of the second pathway's columns (n >= 3E)
+  const __nv_bfloat16* resid;  // row-major epilogues: when non-null the result is res_a * resid[m][n] + res_b * (alpha x w^T + bias)
+  float res_a, res_b;
   float out_scale;             // multiplies the result before the cast to e4m3
   const void* bias;            // [N] or null
   void* out;                   // row-major [M][N]
-  __nv_bfloat16* preact;       // GELU epilogue: when non-null, alpha * x w^T + bias is also stored here (bf16 [M][N])
+  __nv_bfloat16* preact;       // when non-null, the value before the activation / the e4m3 cast is also stored here (bf16 [M][N])
   // head-major scatter: row m = t * B + b, column n = which * E + h * D + d  ->  dst[which][((b * H + h) * T + t) * D + d]
-  __nv_bfloat16* qkv[3];
+  __nv_bfloat16* qkv[6];       // q, k, v of the first pathway, then (two-pathway projection) of the second
   int B, T, H, D;
   float q_scale;               // multiplies the q third (1 to leave the scaling to the attention kernel)
   const float *rope_cos, *rope_sin;   // [T][D/2]; rotate the q and k thirds when non-null
@@ -257,15 +260,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tmem_ld_wait();
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = fmaf(__uint_as_float(r[j]), p.alpha, bias_t[c0 + j]);
+        // (two-pathway QKV projection: the columns of the second pathway carry their own multiplier)
+        const float al = (EPI == kEpiHeadMajor && n0 + c0 >= 3 * p.H * HD) ? p.alpha2 : p.alpha;
+        for (int j = 0; j < 32; ++j) v[j] = fmaf(__uint_as_float(r[j]), al, bias_t[c0 + j]);
         if constexpr (EPI == kEpiHeadMajor) {
-          // column n = which * E + h * HD + d.  E is a multiple of 32 (of 64 when HD = 64), so a 32-column chunk lies in one
-          // third and covers whole heads (HD = 16: two, HD = 32: one) or one half of a head (HD = 64).
+          // column n = which * E + h * HD + d, which = 0..2 (q, k, v of the first pathway) or 3..5 (of the second, never
+          // rotated).  E is a multiple of 32 (of 64 when HD = 64), so a 32-column chunk lies in one third and covers whole
+          // heads (HD = 16: two, HD = 32: one) or one half of a head (HD = 64).
           const int E = p.H * HD;
           const int n = n0 + c0;
           const int which = n / E, e = n % E;
           const bool rot = p.rope_cos != nullptr && which < 2;
-          if (which == 0) {
+          if (which == 0 || which == 3) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= p.q_scale;
           }
@@ -306,7 +312,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                  float x = fmaf(__uint_as_float(r2[j + e]), p.alpha, bias_t[c2 + j + e]);
+                  float x = fmaf(__uint_as_float(r2[j + e]), al, bias_t[c2 + j + e]);
                   if (which == 0) x *= p.q_scale;
                   v[j + e] = upper ? v[j + e] * cs[e] + x * sn[e] : v[j + e] * cs[e] - x * sn[e];
                 }
@@ -316,6 +322,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         } else {
           const int n = n0 + c0;
+          if (p.resid != nullptr) {   // res_a * resid + res_b * (projection): the residual sum of the layer, formed here
+            if (m < p.M) {
+              const __nv_bfloat16* rr = p.resid + size_t(m) * p.N + n;
+              if (n + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  const uint4 q = __ldg(reinterpret_cast<const uint4*>(rr + j));
+                  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(h2[e]);
+                    v[j + 2 * e] = fmaf(p.res_a, f.x, p.res_b * v[j + 2 * e]);
+                    v[j + 2 * e + 1] = fmaf(p.res_a, f.y, p.res_b * v[j + 2 * e + 1]);
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (n + j < p.N) v[j] = fmaf(p.res_a, __bfloat162float(rr[j]), p.res_b * v[j]);
+              }
+            }
+          }
+          if constexpr (EPI == kEpiBias) {
+            // the value itself in bf16 beside an e4m3 result (the bf16 copy the layer keeps, the e4m3 copy the next projection reads)
+            if (p.preact != nullptr) {
+              if (p.use_bulk_store) {
+                bulk_store32(&map_pre, v, n, m0 + quarter * 32);
+              } else if (m < p.M) {
+                __nv_bfloat16* dst = p.preact + size_t(m) * p.N + n;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (n + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+              }
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));   // the e4m3 copy is taken from the bf16 values
+            }
+          }
           if constexpr (EPI == kEpiBiasGelu) {
             if (p.preact != nullptr && p.use_bulk_store) {
               bulk_store32(&map_pre, v, n, m0 + quarter * 32);
@@ -581,8 +624,58 @@ extern "C" int mintb_qkv_fwd(const void* x, const void* w, const void* bias, voi
   p.M = M; p.N = 3 * E; p.K = E; p.in_dtype = in_dtype; p.out_dtype = MINTB_BF16; p.bias_dtype = bias_dtype;
   p.epilogue = kEpiHeadMajor;
   p.row_map = row_map;
-  p.alpha = alpha; p.out_scale = 1.f; p.bias = bias; p.out = nullptr;
+  p.alpha = alpha; p.alpha2 = alpha; p.out_scale = 1.f; p.bias = bias; p.out = nullptr;
   p.qkv[0] = static_cast<__nv_bfloat16*>(q); p.qkv[1] = static_cast<__nv_bfloat16*>(k); p.qkv[2] = static_cast<__nv_bfloat16*>(v);
+  p.B = B; p.T = T; p.H = H; p.D = D; p.q_scale = q_scale; p.rope_cos = rope_cos; p.rope_sin = rope_sin;
+  p.status = dev_status;
+  return launch_gemm(p, x, w, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mintb_linear_res_fwd(const void* x, const void* w, const void* bias, const void* resid, float res_a, float res_b, void* out,
+                                    void* bf16_copy_out, int M, int N, int K, int in_dtype, int bias_dtype, int out_dtype, float alpha,
+                                    float out_scale, void* stream, int* dev_status) {
+  int rc = check_gemm("mintb_linear_res_fwd", x, w, M, N, K, in_dtype);
+  if (rc != MINTB_OK) return rc;
+  if (out == nullptr || (out_dtype != MINTB_BF16 && out_dtype != MINTB_E4M3) || (reinterpret_cast<uintptr_t>(out) & 15) || N % 8 != 0 ||
+      (reinterpret_cast<uintptr_t>(resid) & 15) || (reinterpret_cast<uintptr_t>(bf16_copy_out) & 15) ||
+      (bf16_copy_out != nullptr && out_dtype != MINTB_E4M3)) {
+    set_error("mintb_linear_res_fwd: out must be a 16-byte aligned bf16 or e4m3 buffer, N a multiple of 8, resid and bf16_copy_out "
+              "16-byte aligned, and bf16_copy_out goes with an e4m3 out");
+    return MINTB_EINVAL;
+  }
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.in_dtype = in_dtype; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype;
+  p.epilogue = kEpiBias;
+  p.alpha = alpha; p.out_scale = out_scale; p.bias = bias; p.out = out; p.status = dev_status;
+  p.preact = static_cast<__nv_bfloat16*>(bf16_copy_out);
+  p.resid = static_cast<const __nv_bfloat16*>(resid); p.res_a = res_a; p.res_b = res_b;
+  return launch_gemm(p, x, w, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mintb_qkv2_fwd(const void* x, const void* w, const void* bias, void* q1, void* k1, void* v1, void* q2, void* k2, void* v2,
+                              int T, int B, int H, int D, int in_dtype, int bias_dtype, float alpha1, float alpha2, float q_scale,
+                              const float* rope_cos, const float* rope_sin, const int32_t* row_map, int n_rows, void* stream,
+                              int* dev_status) {
+  const int E = H * D;
+  const int M = row_map != nullptr ? n_rows : T * B;
+  int rc = check_gemm("mintb_qkv2_fwd", x, w, M, 6 * E, E, in_dtype);
+  if (rc != MINTB_OK) return rc;
+  if (q1 == nullptr || k1 == nullptr || v1 == nullptr || q2 == nullptr || k2 == nullptr || v2 == nullptr ||
+      (D != 16 && D != 32 && D != 64) || T <= 0 || B <= 0 || H <= 0 || E % (D == 64 ? 64 : 32) != 0) {
+    set_error("mintb_qkv2_fwd: six outputs, head_dim 16, 32 or 64 and H * D a multiple of 32 (64 at head_dim 64) are required");
+    return MINTB_EINVAL;
+  }
+  if ((rope_cos == nullptr) != (rope_sin == nullptr)) {
+    set_error("mintb_qkv2_fwd: give both RoPE tables or neither");
+    return MINTB_EINVAL;
+  }
+  GemmParams p{};
+  p.M = M; p.N = 6 * E; p.K = E; p.in_dtype = in_dtype; p.out_dtype = MINTB_BF16; p.bias_dtype = bias_dtype;
+  p.epilogue = kEpiHeadMajor;
+  p.row_map = row_map;
+  p.alpha = alpha1; p.alpha2 = alpha2; p.out_scale = 1.f; p.bias = bias; p.out = nullptr;
+  void* outs[6] = {q1, k1, v1, q2, k2, v2};
+  for (int i = 0; i < 6; ++i) p.qkv[i] = static_cast<__nv_bfloat16*>(outs[i]);
   p.B = B; p.T = T; p.H = H; p.D = D; p.q_scale = q_scale; p.rope_cos = rope_cos; p.rope_sin = rope_sin;
   p.status = dev_status;
   return launch_gemm(p, x, w, static_cast<cudaStream_t>(stream));

@@ -29,6 +29,25 @@ def _linear(mod, x, gelu=False):
     return ops.linear(x, mod.weight, mod.bias, gelu=gelu)
 
 
+import os as _os
+# the two whole-layer fusions (module-level switches; both on by default)
+FUSE_QKV6 = _os.environ.get("MINTB_FUSE_QKV6", "1") != "0"              # both pathways' QKV projections as one product
+_QKV6_MAX_BYTES = 40 << 20
+FUSE_OUT_RESIDUAL = _os.environ.get("MINTB_FUSE_OUT_RESIDUAL", "1") != "0"   # residual sum in the output projection's epilogue
+
+
+def _linear_res(mod, x, resid, a, b, quant_scale=None):
+    """a * resid + b * mod(x) for bf16 CUDA tensors: in the projection's GEMM epilogue for nn.Linear / Fp8Linear, as a
+    separate fused pass for wrapped projections (e.g. LoRA adapters)."""
+    from .mu_scaling import Fp8Linear
+    if isinstance(mod, Fp8Linear):
+        return mod.forward_res(x, resid, a, b, quant_scale)
+    if type(mod) is nn.Linear:
+        return ops.linear_res(x, mod.weight, mod.bias, resid, a, b, quant_scale)
+    s, _ = ops.add_layernorm(resid, mod(x), a, b, None, quant_scale=quant_scale)
+    return s
+
+
 def gelu_erf(x):
     return x * 0.5 * (1.0 + torch.erf(x / math.sqrt(2.0)))
 
@@ -80,6 +99,38 @@ def _qkv_operands(attn):
     return w, b, (fused_fp8_weight(attn, mods) if kind == "fp8" else None), None
 
 
+def _qkv_params(attn):
+    fused = getattr(attn, "fused_qkv", None)
+    mods = [fused] if fused is not None else [attn.q_proj, attn.k_proj, attn.v_proj]
+    mods = [getattr(m, "base", m) for m in mods]
+    return [p for m in mods for p in (m.weight, m.bias) if p is not None]
+
+
+def _fused6_operands(layer, ops_s, ops_c):
+    """The [6E][E] weight operand (bf16, or e4m3 for FP8 projections) and [6E] bias of BOTH pathways' QKV projections for
+    the one-product QKV GEMM, cached on the layer until one of the underlying parameters changes; None when the two
+    pathways cannot share a product (adapters, mixed kinds)."""
+    (w_s, b_s, f8_s, lora_s), (w_c, b_c, f8_c, lora_c) = ops_s, ops_c
+    if lora_s is not None or lora_c is not None or (f8_s is None) != (f8_c is None) or (b_s is None) != (b_c is None):
+        return None
+    if f8_s is not None and f8_s[2] != f8_c[2]:
+        return None
+    if 6 * w_s.shape[1] * w_s.shape[1] * (1 if f8_s is not None else 2) > _QKV6_MAX_BYTES:
+        return None       # a [6E][E] operand this large pushes the activation rows out of L2 between column tiles (measured slower)
+    key = tuple((p.data_ptr(), p._version) for p in _qkv_params(layer.self_attn) + _qkv_params(layer.multimer_attn)) + (f8_s is not None,)
+    cached = getattr(layer, "_qkv6_cache", None)
+    if cached is not None and cached[0] == key:
+        return cached[1], cached[2]
+    with torch.no_grad():
+        if f8_s is not None:
+            w6 = torch.cat([f8_s[0].view(torch.uint8), f8_c[0].view(torch.uint8)], dim=0).view(torch.float8_e4m3fn)
+        else:
+            w6 = torch.cat([w_s.detach().to(torch.bfloat16), w_c.detach().to(torch.bfloat16)], dim=0)
+        b6 = torch.cat([b_s.detach().float(), b_c.detach().float()], dim=0) if b_s is not None else None
+    layer._qkv6_cache = (key, w6, b6)
+    return w6, b6
+
+
 class _TwoPathwayLayer(nn.Module):
     """The attention half shared by the Pre-LN layers and the muS layer: both QKV projections, the fused two-pathway
     attention (or the materialised-logits combine when `_use_fused_multi_pathway` is False), the output projection."""
@@ -107,10 +158,12 @@ class _TwoPathwayLayer(nn.Module):
         attn_out = attn_out.permute(2, 0, 1, 3).reshape(T, B, E)
         return sa.out_proj(attn_out), None
 
-    def _multimer_attention_superfused(self, x, chain_mask, padding_mask, chain_ids=None, pack=None):
+    def _multimer_attention_superfused(self, x, chain_mask, padding_mask, chain_ids=None, pack=None, residual=None, quant_scale=None):
         """x (T,B,E) -> (T,B,E): both QKV projections, fused two-pathway attention, output projection.  With `pack`
         (ops.PackInfo) x is (N,1,E), the N unpadded tokens only: the projections run on those rows, the attention on the
-        padded grid with fully padded query tiles left out, and its result is gathered back to the N rows."""
+        padded grid with fully padded query tiles left out, and its result is gathered back to the N rows.
+        `residual` = (r, a, b) (bf16 on the GPU only): the result is a r + b out_proj(attention), the sum formed in the output
+        projection's GEMM epilogue; `quant_scale` then also attaches the e4m3 copy of that sum for the next e4m3 projection."""
         if pack is None:
             T, B, E = x.shape
         else:
@@ -136,7 +189,8 @@ class _TwoPathwayLayer(nn.Module):
             # [dQ | dK | dV] row-major (only the unpadded tokens' rows when packed) for the projections' products
             meta = mask_kw["meta"] if "meta" in mask_kw else ops.cached_mask_meta(chain_mask, padding_mask)
             attn_out = ops.qkv_attention(x, ops_s, ops_c, sa.num_heads, meta, rope=tabs, scale=sa.scaling,
-                                         sqrt_softmax=sqrt_sm, pack=pack, skip_pad_queries=pack is not None)
+                                         sqrt_softmax=sqrt_sm, pack=pack, skip_pad_queries=pack is not None,
+                                         fused6=_fused6_operands(self, ops_s, ops_c) if FUSE_QKV6 else None)
         elif pack is not None:
             raise NotImplementedError("packed tokens need bfloat16 CUDA activations and nn.Linear / Fp8Linear projections")
         else:
@@ -149,7 +203,11 @@ class _TwoPathwayLayer(nn.Module):
         if pack is not None:
             attn_out = attn_out.view(T * B, E).index_select(0, pack.rows64).unsqueeze(1)
         if x.is_cuda and x.dtype == torch.bfloat16:
+            if residual is not None:
+                return _linear_res(sa.out_proj, attn_out, residual[0], residual[1], residual[2], quant_scale), None
             return _linear(sa.out_proj, attn_out), None
+        if residual is not None:
+            raise NotImplementedError("the residual epilogue needs bfloat16 CUDA activations")
         return sa.out_proj(attn_out), None
 
     # the PyTorch-named entry of the reference resolves to the same fused path
@@ -179,6 +237,12 @@ class _PreLnLayer(_TwoPathwayLayer):
         if x.is_cuda and x.dtype == torch.bfloat16 and isinstance(self.final_layer_norm, nn.LayerNorm):
             # bf16 on the GPU: each residual add is fused with the LayerNorm that follows it (one pass over the activations)
             _, h = ops.add_layernorm(x, None, 1.0, 0.0, self.self_attn_layer_norm, need_s=False)
+            if self.use_multimer and self._use_fused_multi_pathway and FUSE_OUT_RESIDUAL:
+                # x + out_proj(attention): the residual add rides in the output projection's GEMM epilogue
+                x, attn = self._multimer_attention_superfused(h, self_attn_mask, self_attn_padding_mask, chain_ids, pack,
+                                                              residual=(x, 1.0, 1.0))
+                _, h = ops.add_layernorm(x, None, 1.0, 0.0, self.final_layer_norm, need_s=False)
+                return x + self.feed_forward(h), attn
             if self.use_multimer:
                 h, attn = self._multimer_attention_plus(h, self_attn_mask, self_attn_padding_mask, chain_ids, pack)
             else:

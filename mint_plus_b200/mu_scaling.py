@@ -61,6 +61,42 @@ class _Fp8LinearFn(torch.autograd.Function):
         return dx, dw, (db.to(bias.dtype) if want_db else None), None, None, None, None, None, None
 
 
+class _Fp8LinearResFn(torch.autograd.Function):
+    """s = a r + b (out_scale x W^T + bias) on e4m3 operands with the residual sum formed in the GEMM epilogue; optionally the
+    e4m3 copy of s for the next projection (second output).  Backward as `_Fp8LinearFn`, the factor b folded into the
+    products' multipliers; the residual receives a dy."""
+
+    @staticmethod
+    def forward(ctx, x2d, weight, bias, resid2d, a, b, wq, w_scale, x_scale, out_scale, gs, quant_scale, xq):
+        if xq is None:
+            xq = ops.quantize_e4m3(x2d, x_scale)
+        out, q8 = ops.gemm_res(xq, wq, x_scale * w_scale * out_scale, bias, resid2d, a, b, quant_scale)
+        ctx.save_for_backward(xq if gs is not None else x2d, weight, bias, wq)
+        ctx.cfg = (float(a), float(b), float(out_scale), float(w_scale), float(x_scale), gs)
+        if q8 is not None:
+            ctx.mark_non_differentiable(q8)
+        return out, q8
+
+    @staticmethod
+    def backward(ctx, dy, _dq8=None):
+        x_saved, weight, bias, wq = ctx.saved_tensors
+        a, b, out_scale, w_scale, x_scale, gs = ctx.cfg
+        n = ctx.needs_input_grad
+        dy = dy.contiguous()
+        tail = (None,) * 9
+        d_res = (dy if a == 1.0 else dy * a) if n[3] else None
+        if gs is None:
+            dx, dw, db, _ = ops.linear_backward(dy, x_saved, weight, bias, None, n, out_scale * b)
+            if db is not None and b != 1.0:
+                db = db * b
+            return (dx, dw, db, d_res) + tail
+        want_db = bias is not None and n[2]
+        g8, db, s = ops.f8_output_grad(dy, None, want_db, gs)
+        dx = ops.gemm_dgrad(g8, wq, alpha=s * w_scale * out_scale * b) if n[0] else None
+        dw = _w_grad(g8, x_saved, s * x_scale * out_scale * b, weight) if n[1] else None
+        return (dx, dw, (db * b).to(bias.dtype) if want_db else None, d_res) + tail
+
+
 class _Fp8FfnFn(torch.autograd.Function):
     """fc2(gelu(fc1(x))) on two e4m3 products as ONE differentiable step: fc1's epilogue writes gelu(.) directly as the e4m3
     operand of fc2 (with fc2's activation scale) beside the bf16 pre-activation z, so neither a bf16 copy of the 4E-wide
@@ -151,6 +187,19 @@ class Fp8Linear(nn.Module):
         y = _Fp8LinearFn.apply(x2d, self.weight, self.bias, wq, w_scale, self.x_scale, gelu, self.out_scale,
                                self.grad_scale if self.fp8_grads else None)
         return y.view(*x.shape[:-1], self.out_features)
+
+    def forward_res(self, x: torch.Tensor, resid: torch.Tensor, a: float, b: float, quant_scale: Optional[float] = None) -> torch.Tensor:
+        """a * resid + b * self(x), the residual sum formed in the GEMM epilogue; with quant_scale the e4m3 copy of the sum is
+        attached to it for the e4m3 projection that reads it next."""
+        wq, w_scale = self._quantized_weight()
+        x2d = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+        xq = ops.e4m3_of(x, self.x_scale) if x.dtype == torch.bfloat16 else None
+        out, q8 = _Fp8LinearResFn.apply(x2d, self.weight, self.bias, resid.reshape(-1, self.out_features), float(a), float(b), wq, w_scale,
+                                        self.x_scale, self.out_scale, self.grad_scale if self.fp8_grads else None, quant_scale, xq)
+        out = out.view(*x.shape[:-1], self.out_features)
+        if q8 is not None:
+            ops.attach_e4m3(out, q8, quant_scale)
+        return out
 
     def extra_repr(self):
         return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, x_scale={self.x_scale}"
@@ -305,17 +354,29 @@ class TransformerLayer_MINT_mu(_TwoPathwayLayer):
     def forward(self, x, self_attn_mask=None, self_attn_padding_mask=None, chain_ids=None, pack=None):
         tau = self._tau_f                       # host copy of the buffer: no device read-back per call
         keep, add = math.sqrt(1.0 - tau), math.sqrt(tau)
+        gpu_bf16 = x.is_cuda and x.dtype == torch.bfloat16
+        fc1 = self.feed_forward.fc1
+        fc1_scale = fc1.x_scale if isinstance(fc1, Fp8Linear) else None
+        from . import modules_plus as _mp
+        if self.use_multimer and gpu_bf16 and self._use_fused_multi_pathway and _mp.FUSE_OUT_RESIDUAL:
+            # the first weighted residual sum is formed in the epilogue of the output projection (which also writes the e4m3
+            # operand of fc1), the second one together with the closing LayerNorm in one fused pass (which writes the e4m3
+            # operand of the next layer's QKV products)
+            x, _ = self._multimer_attention_superfused(x, self_attn_mask, self_attn_padding_mask, chain_ids, pack,
+                                                       residual=(x, keep, add), quant_scale=fc1_scale)
+            _, y = ops.add_layernorm(x, self.feed_forward(x), keep, add, self.final_layer_norm, need_s=False,
+                                     quant_scale=self._next_x_scale)
+            return y, None
         if self.use_multimer:
             attn_out, _ = self._multimer_attention_plus(x, self_attn_mask, self_attn_padding_mask, chain_ids, pack)
         elif pack is not None:
             raise NotImplementedError("packed tokens need the two-pathway attention")
         else:
             attn_out, _ = self._standard_attention(x, self_attn_mask, self_attn_padding_mask)
-        if x.is_cuda and x.dtype == torch.bfloat16:
+        if gpu_bf16:
             # bf16 on the GPU: weighted residuals and the closing LayerNorm in two fused passes
             # (each pass also writes the e4m3 operand of the FP8 projection that reads its result next)
-            fc1 = self.feed_forward.fc1
-            x, _ = ops.add_layernorm(x, attn_out, keep, add, None, quant_scale=fc1.x_scale if isinstance(fc1, Fp8Linear) else None)
+            x, _ = ops.add_layernorm(x, attn_out, keep, add, None, quant_scale=fc1_scale)
             _, y = ops.add_layernorm(x, self.feed_forward(x), keep, add, self.final_layer_norm, need_s=False,
                                      quant_scale=self._next_x_scale)
             return y, None

@@ -411,6 +411,28 @@ def gemm_e4m3(xq: torch.Tensor, wq: torch.Tensor, alpha: float, bias=None, gelu:
     return (out, z) if save_preact else out
 
 
+def gemm_res(x_op: torch.Tensor, w_op: torch.Tensor, alpha: float, bias, resid: torch.Tensor, a: float, b: float,
+             quant_scale: Optional[float] = None):
+    """a * resid + b * (alpha * x_op @ w_op.T + bias) on the tcgen05 GEMM, the residual sum formed in its epilogue: operands
+    bf16 or e4m3 (both alike), resid bf16 [M,N] -> bf16 [M,N].  With quant_scale the pass also leaves the e4m3 copy
+    saturate(result / quant_scale) for the projection that reads the sum next: returns (sum, copy), else (sum, None)."""
+    _require_cuda(x_op, w_op, bias, resid)
+    M, K = x_op.shape
+    N = w_op.shape[0]
+    bt, bdt = _bias_arg(bias)
+    in_dt = L.E4M3 if x_op.dtype == torch.float8_e4m3fn else L.BF16
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x_op.device)
+    q8 = torch.empty(M, N, dtype=torch.float8_e4m3fn, device=x_op.device) if quant_scale else None
+    resid = resid.contiguous()
+    with _on(x_op.device):
+        rc = L.lib().mintb_linear_res_fwd(_ptr(x_op), _ptr(w_op), _ptr(bt), _ptr(resid), float(a), float(b),
+                                          _ptr(q8) if q8 is not None else _ptr(out), _ptr(out) if q8 is not None else None, M, N, K,
+                                          in_dt, bdt, L.E4M3 if q8 is not None else L.BF16, float(alpha),
+                                          1.0 / quant_scale if quant_scale else 1.0, _stream(), _ptr(_dev_status(x_op.device)))
+    L.check(rc, "mintb_linear_res_fwd")
+    return out, q8
+
+
 _GEMM_DT = {torch.bfloat16: L.BF16, torch.float8_e4m3fn: L.E4M3, torch.float8_e5m2: L.E5M2}
 
 
@@ -574,6 +596,46 @@ class _LinearFn(torch.autograd.Function):
         x2d, w, bias, z = ctx.saved_tensors
         dx, dw, db, _ = linear_backward(dy, x2d, w, bias, z, ctx.needs_input_grad)
         return dx, dw, db, None
+
+
+class _LinearResFn(torch.autograd.Function):
+    """s = a r + b (x W^T + bias) with the residual sum formed in the GEMM epilogue (bf16 operands); optionally also the e4m3
+    copy of s for the projection that reads it next (second output, not differentiable)."""
+
+    @staticmethod
+    def forward(ctx, x2d, w, bias, resid2d, a, b, quant_scale):
+        out, q8 = gemm_res(x2d, _as_bf16(w), 1.0, bias, resid2d, a, b, quant_scale)
+        ctx.save_for_backward(x2d, w, bias)
+        ctx.ab = (float(a), float(b))
+        if q8 is not None:
+            ctx.mark_non_differentiable(q8)
+        return out, q8
+
+    @staticmethod
+    def backward(ctx, dy, _dq8=None):
+        x2d, w, bias = ctx.saved_tensors
+        a, b = ctx.ab
+        n = ctx.needs_input_grad
+        dy = dy.contiguous()
+        dx, dw, db, _ = linear_backward(dy, x2d, w, bias, None, n, out_scale=b)
+        if db is not None and b != 1.0:
+            db = db * b
+        d_res = (dy if a == 1.0 else dy * a) if n[3] else None
+        return dx, dw, db, d_res, None, None, None
+
+
+def linear_res(x: torch.Tensor, weight: torch.Tensor, bias, resid: torch.Tensor, a: float, b: float,
+               quant_scale: Optional[float] = None) -> torch.Tensor:
+    """a * resid + b * nn.Linear(x) for bf16 CUDA activations, one pass (the residual add rides in the GEMM epilogue);
+    differentiable.  With quant_scale the e4m3 copy of the result is attached to it for the next e4m3 projection."""
+    if x.dtype != torch.bfloat16 or resid.dtype != torch.bfloat16:
+        raise TypeError("ops.linear_res takes bfloat16 activations")
+    x2d = x.reshape(-1, x.shape[-1]).contiguous()
+    out, q8 = _LinearResFn.apply(x2d, weight, bias, resid.reshape(-1, weight.shape[0]), float(a), float(b), quant_scale)
+    out = out.view(*x.shape[:-1], weight.shape[0])
+    if q8 is not None:
+        attach_e4m3(out, q8, quant_scale)
+    return out
 
 
 class _LoraLinearFn(torch.autograd.Function):
@@ -872,6 +934,41 @@ class _SubCtx:
         self.saved_tensors = tensors
 
 
+def _qkv2_forward(cs, cc, x, w_s, b_s, w_c, b_c, H, cos, sin, q_scale, fp8_s, fp8_c, pack, w6, b6):
+    """Both pathways' fused QKV projections as ONE product on the [6E][E] operand `w6` (rows [Q;K;V] of the self pathway, then
+    of the cross pathway): x is read once, the epilogue writes the six head-major tensors and rotates q, k of the self pathway.
+    Fills the two sub-contexts exactly as two `_QkvFn.forward` calls would."""
+    if pack is None:
+        T, B, E = x.shape
+        x2d = x.reshape(T * B, E).contiguous()
+    else:
+        (T, B), E = (pack.T, pack.B), x.shape[-1]
+        x2d = x.reshape(-1, E).contiguous()
+    D = E // H
+    b6t, bdt = _bias_arg(b6)
+    wq_s, ws_s, xs_s, os_s, gs_s = fp8_s
+    wq_c, ws_c, xs_c, os_c, gs_c = fp8_c
+    if wq_s is None:
+        a_op, in_dt, al1, al2 = x2d, L.BF16, 1.0, 1.0
+    else:
+        a_op, in_dt = e4m3_of(x, xs_s), L.E4M3
+        al1, al2 = float(xs_s) * float(ws_s) * float(os_s), float(xs_c) * float(ws_c) * float(os_c)
+    alloc = torch.zeros if pack is not None else torch.empty     # packed: positions without a token must hold finite numbers
+    outs = [alloc(B, H, T, D, dtype=torch.bfloat16, device=x.device) for _ in range(6)]
+    with _on(x.device):
+        rc = L.lib().mintb_qkv2_fwd(_ptr(a_op), _ptr(w6), _ptr(b6t), *[_ptr(t) for t in outs], T, B, H, D, in_dt, bdt, al1, al2,
+                                    float(q_scale), _ptr(cos), _ptr(sin), _ptr(pack.rows32) if pack is not None else None,
+                                    x2d.shape[0], _stream(), _ptr(_dev_status(x.device)))
+    L.check(rc, "mintb_qkv2_fwd")
+    for c, w, b, tabs, wq, ws, xs, os_, gs in ((cs, w_s, b_s, (cos, sin), wq_s, ws_s, xs_s, os_s, gs_s),
+                                                (cc, w_c, b_c, (None, None), wq_c, ws_c, xs_c, os_c, gs_c)):
+        c.save_for_backward(x2d, w, b, tabs[0], tabs[1], None, None)
+        c.f8 = (a_op, wq, float(ws), float(xs), gs) if (wq is not None and gs is not None) else None
+        c.lora_scaling, c.pack, c.x_shape = 1.0, pack, tuple(x.shape)
+        c.dims = (T, B, H, D, q_scale, float(os_))
+    return outs
+
+
 class _QkvAttentionFn(torch.autograd.Function):
     """Both fused QKV projections of a layer and its two-pathway attention as ONE differentiable step: x -> attention output.
 
@@ -882,14 +979,19 @@ class _QkvAttentionFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w_s, b_s, la_s, lb_s, w_c, b_c, la_c, lb_c, H, cos, sin, q_scale, fp8_s, fp8_c, ls_s, ls_c, pack,
-                meta, scale, flags):
+                meta, scale, flags, fused6=None):
         n = ctx.needs_input_grad
         f = (False,) * 10
         cs = _SubCtx((n[0], n[1], n[2]) + f + (n[3], n[4], False))
         cc = _SubCtx((n[0], n[5], n[6]) + f + (n[7], n[8], False))
         ca = _SubCtx((any(n[:9]),) * 6 + (False,) * 6)
-        q_s, k_s, v_s = _QkvFn.forward(cs, x, w_s, b_s, H, cos, sin, q_scale, *fp8_s, pack, la_s, lb_s, ls_s)
-        q_c, k_c, v_c = _QkvFn.forward(cc, x, w_c, b_c, H, None, None, q_scale, *fp8_c, pack, la_c, lb_c, ls_c)
+        one_product = (fused6 is not None and la_s is None and la_c is None and (fp8_s[0] is None) == (fp8_c[0] is None)
+                       and (fp8_s[0] is None or fp8_s[2] == fp8_c[2]) and (b_s is None) == (b_c is None))
+        if one_product:
+            q_s, k_s, v_s, q_c, k_c, v_c = _qkv2_forward(cs, cc, x, w_s, b_s, w_c, b_c, H, cos, sin, q_scale, fp8_s, fp8_c, pack, *fused6)
+        else:
+            q_s, k_s, v_s = _QkvFn.forward(cs, x, w_s, b_s, H, cos, sin, q_scale, *fp8_s, pack, la_s, lb_s, ls_s)
+            q_c, k_c, v_c = _QkvFn.forward(cc, x, w_c, b_c, H, None, None, q_scale, *fp8_c, pack, la_c, lb_c, ls_c)
         out = _MultimerAttentionFn.forward(ca, q_s, k_s, v_s, q_c, k_c, v_c, meta, None, None, scale, flags, (cos, sin))
         ctx.subs = (cs, cc, ca)
         ctx.counts = tuple(len(c.saved_tensors) for c in ctx.subs)
@@ -928,16 +1030,18 @@ class _QkvAttentionFn(torch.autograd.Function):
             dx = dx.view(cs.x_shape)
         for c in ctx.subs:
             c.saved_tensors = ()
-        return (dx, dw_s, db_s, da_s, dlb_s, dw_c, db_c, da_c, dlb_c) + (None,) * 12
+        return (dx, dw_s, db_s, da_s, dlb_s, dw_c, db_c, da_c, dlb_c) + (None,) * 13
 
 
 def qkv_attention(x: torch.Tensor, proj_self, proj_cross, num_heads: int, meta: "MaskMeta", rope=None, scale: float = 1.0,
-                  sqrt_softmax: bool = False, pack=None, skip_pad_queries: bool = False) -> torch.Tensor:
+                  sqrt_softmax: bool = False, pack=None, skip_pad_queries: bool = False, fused6=None) -> torch.Tensor:
     """Attention output (T,B,H,D) of a layer from its input x (T,B,E) (or the packed rows of one, with `pack`): both fused
     QKV projections (`qkv_project`'s arithmetic; `proj_*` = (weight (3E,E), bias, fp8 operands or None, lora or None)) and
     `multimer_attention` on their head-major results, differentiable as one step (attention.py:87-117,188-323 and
     modules.py:94-154 of the reference).  `rope` = (cos, sin) rotates q, k of the self pathway in the GEMM epilogue;
-    `scale` multiplies the logits of both pathways inside the attention kernels.  Head sizes 16, 32, 64."""
+    `scale` multiplies the logits of both pathways inside the attention kernels.  Head sizes 16, 32, 64.
+    `fused6` = (the [6E][E] operand holding both pathways' weights — bf16, or e4m3 when the projections are FP8 — and the
+    [6E] bias): both projections then run as ONE product that reads x once."""
     if x.dtype != torch.bfloat16 or not x.is_cuda or (pack is None and x.dim() != 3):
         raise TypeError("qkv_attention takes a (T, B, E) bfloat16 CUDA tensor (or the packed rows of one, with `pack`)")
     cos, sin = rope if rope is not None else (None, None)
@@ -952,7 +1056,7 @@ def qkv_attention(x: torch.Tensor, proj_self, proj_cross, num_heads: int, meta: 
     flags = (L.FLAG_OUT_SEQ_FIRST | (L.FLAG_SQRT_SOFTMAX if sqrt_softmax else 0)
              | (L.FLAG_SKIP_PAD_QUERIES if skip_pad_queries else 0))
     return _QkvAttentionFn.apply(x, w_s, b_s, la_s, lb_s, w_c, b_c, la_c, lb_c, num_heads, cos, sin, 1.0, f_s, f_c, ls_s, ls_c,
-                                 pack, meta, float(scale), int(flags))
+                                 pack, meta, float(scale), int(flags), fused6)
 
 
 def qkv_project(x: torch.Tensor, weight: torch.Tensor, bias, num_heads: int, rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,

@@ -62,36 +62,40 @@ def quant_e5m2(g: torch.Tensor, scale: float) -> torch.Tensor:
 
 
 class _QuantLinear(torch.autograd.Function):
-    """y = (x_scale w_scale out_scale) q(x) q(w)^T + b.  Backward, g_scale None: as for y = out_scale x w^T + b on the
-    un-quantised operands (straight-through).  With g_scale (alt/munit_scaling.py:36-55): the gradient is cast to e5m2,
-    g8 = q5(dy / g_scale), and dx = g8 q(w), dw = g8^T q(x), db = sum g8, each times its scales."""
+    """y = (x_scale w_scale out_scale) q(x) q(w)^T + b, or with a residual ra r + rb y (the sum the GEMM epilogue forms).
+    Backward, g_scale None: as for y = out_scale x w^T + b on the un-quantised operands (straight-through).  With g_scale
+    (alt/munit_scaling.py:36-55): the gradient of the result (of the SUM when there is a residual) is cast to e5m2,
+    g8 = q5(dy / g_scale), and dx = g8 q(w), dw = g8^T q(x), db = sum g8, each times its scales (and rb); the residual
+    receives ra dy."""
 
     @staticmethod
-    def forward(ctx, x, w, b, x_scale, w_scale, out_scale, g_scale):
+    def forward(ctx, x, w, b, x_scale, w_scale, out_scale, g_scale, resid=None, ra=1.0, rb=1.0):
         alpha = torch.tensor(float(x_scale) * float(w_scale) * float(out_scale), dtype=torch.float32)
         y = (quant_e4m3(x, x_scale) @ quant_e4m3(w, w_scale).t()) * alpha
         if b is not None:
             y = y + b.float()
+        if resid is not None:
+            y = ra * resid + rb * y
         ctx.save_for_backward(x, w)
-        ctx.cfg = (float(x_scale), float(w_scale), float(out_scale), g_scale)
-        ctx.has_bias = b is not None
+        ctx.cfg = (float(x_scale), float(w_scale), float(out_scale), g_scale, float(ra), float(rb) if resid is not None else 1.0)
+        ctx.has_bias, ctx.has_res = b is not None, resid is not None
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
-        x_scale, w_scale, out_scale, g_scale = ctx.cfg
+        x_scale, w_scale, out_scale, g_scale, ra, rb = ctx.cfg
         if g_scale is None:
-            dx = (dy @ w) * out_scale
-            dw = (dy.t() @ x) * out_scale
-            db = dy.sum(0) if ctx.has_bias else None
+            dx = (dy @ w) * (out_scale * rb)
+            dw = (dy.t() @ x) * (out_scale * rb)
+            db = dy.sum(0) * rb if ctx.has_bias else None
         else:
             g8 = quant_e5m2(dy, g_scale)
             # (the product leaves the GPU as bf16, and the next projection's e5m2 cast sees that rounding)
-            dx = ((g8 @ quant_e4m3(w, w_scale)) * torch.tensor(g_scale * w_scale * out_scale, dtype=torch.float32)).bfloat16().float()
-            dw = (g8.t() @ quant_e4m3(x, x_scale)) * torch.tensor(g_scale * x_scale * out_scale, dtype=torch.float32)
-            db = g8.sum(0) * g_scale if ctx.has_bias else None
-        return dx, dw, db, None, None, None, None
+            dx = ((g8 @ quant_e4m3(w, w_scale)) * torch.tensor(g_scale * w_scale * out_scale * rb, dtype=torch.float32)).bfloat16().float()
+            dw = (g8.t() @ quant_e4m3(x, x_scale)) * torch.tensor(g_scale * x_scale * out_scale * rb, dtype=torch.float32)
+            db = g8.sum(0) * (g_scale * rb) if ctx.has_bias else None
+        return dx, dw, db, None, None, None, None, (ra * dy if ctx.has_res else None), None, None
 
 
 class _GeluKeepsBf16Preactivation(torch.autograd.Function):
@@ -109,16 +113,18 @@ class _GeluKeepsBf16Preactivation(torch.autograd.Function):
         return dy * (0.5 * (1.0 + torch.erf(zb * 0.7071067811865476)) + zb * torch.exp(-0.5 * zb * zb) * 0.3989422804014327)
 
 
-def linear(x2d, w, b, fp8: Optional[dict] = None, w_scale: Optional[float] = None, name: Optional[str] = None):
+def linear(x2d, w, b, fp8: Optional[dict] = None, w_scale: Optional[float] = None, name: Optional[str] = None, residual=None):
     """fp32 result of one projection on rows x2d [M,K] (not yet rounded to bf16).  `fp8` = {"x_scale", "out_scale", "g_scale"}
     selects the e4m3 arithmetic (g_scale: the 8-bit backward as well); an entry fp8["per"][name] overrides those fields for
     the projection `name` ("sa_qkv", "ma_qkv", "out", "fc1", "fc2").  `w_scale` overrides amax(w)/448."""
     if fp8 is None:
-        return F.linear(x2d, w, b)
+        y = F.linear(x2d, w, b)
+        return y if residual is None else residual[1] * residual[0] + residual[2] * y
     cfg = dict(fp8)
     cfg.update(fp8.get("per", {}).get(name, {}))
     ws = weight_scale(w) if w_scale is None else w_scale
-    return _QuantLinear.apply(x2d, w, b, cfg.get("x_scale", 1.0), ws, cfg.get("out_scale", 1.0), cfg.get("g_scale"))
+    res = (None, 1.0, 1.0) if residual is None else residual
+    return _QuantLinear.apply(x2d, w, b, cfg.get("x_scale", 1.0), ws, cfg.get("out_scale", 1.0), cfg.get("g_scale"), *res)
 
 
 def _heads(t2d, T, B, H, D):
@@ -139,8 +145,10 @@ def _qkv(attn, x2d, T, B, H, D, rope: bool, fp8, name):
     return bf16r(q), bf16r(k), bf16r(v)
 
 
-def attention_block(layer, x, chain_mask, key_pad, fp8=None, sqrt_softmax=False):
-    """x (T,B,E) -> out_proj(attention) (T,B,E), every stored tensor rounded to bf16."""
+def attention_block(layer, x, chain_mask, key_pad, fp8=None, sqrt_softmax=False, residual=None):
+    """x (T,B,E) -> out_proj(attention) (T,B,E), every stored tensor rounded to bf16.  `residual` = (r, a, b): the result is
+    a r + b out_proj(attention), formed in fp32 from the unrounded projection (the GEMM epilogue adds the residual) and
+    rounded once."""
     T, B, E = x.shape
     sa, ma = layer.self_attn, layer.multimer_attn
     H = sa.num_heads
@@ -151,7 +159,8 @@ def attention_block(layer, x, chain_mask, key_pad, fp8=None, sqrt_softmax=False)
     a = O.multimer_attention(q_s, k_s, v_s, q_c, k_c, v_c, chain_mask, key_pad, scale=D ** -0.5, rope=False,
                              sqrt_softmax=sqrt_softmax)
     a = bf16r(a.permute(2, 0, 1, 3).reshape(T * B, E))
-    return bf16r(linear(a, sa.out_proj.weight, sa.out_proj.bias, fp8, name="out")).reshape(T, B, E)
+    res = None if residual is None else (residual[0].reshape(T * B, E), residual[1], residual[2])
+    return bf16r(linear(a, sa.out_proj.weight, sa.out_proj.bias, fp8, name="out", residual=res)).reshape(T, B, E)
 
 
 def feed_forward(layer, x, fp8=None):
@@ -168,11 +177,10 @@ def feed_forward(layer, x, fp8=None):
 
 def mu_layer(layer, x, chain_mask, key_pad, tau: float, fp8=None, sqrt_softmax=False):
     """muS Res-Post-LN layer (mu_scaling/layer.py:259-280): x = sqrt(1-tau) x + sqrt(tau) attn(x);
-    x = sqrt(1-tau) x + sqrt(tau) ffn(x); LayerNorm.  The first residual sum is stored (bf16), the second feeds the
-    LayerNorm in fp32, as the fused residual + LayerNorm pass computes it."""
+    x = sqrt(1-tau) x + sqrt(tau) ffn(x); LayerNorm.  The first residual sum leaves the output projection's epilogue as bf16,
+    the second feeds the LayerNorm in fp32, as the fused residual + LayerNorm pass computes it."""
     keep, add = math.sqrt(1.0 - tau), math.sqrt(tau)
-    a = attention_block(layer, x, chain_mask, key_pad, fp8, sqrt_softmax)
-    s1 = bf16r(keep * x + add * a)
+    s1 = attention_block(layer, x, chain_mask, key_pad, fp8, sqrt_softmax, residual=(x, keep, add))
     s2 = keep * s1 + add * feed_forward(layer, s1, fp8)
     ln = layer.final_layer_norm
     return bf16r(F.layer_norm(s2, (s2.shape[-1],), ln.weight, ln.bias, ln.eps))
@@ -180,12 +188,10 @@ def mu_layer(layer, x, chain_mask, key_pad, tau: float, fp8=None, sqrt_softmax=F
 
 def pre_ln_layer(layer, x, chain_mask, key_pad, fp8=None):
     """Pre-LN layer (modules.py:179-195): x + attn(LN(x)), then + ffn(LN(.)); LayerNorm results and the residual sums
-    are stored as bf16."""
+    are stored as bf16 (the second LayerNorm reads the stored first sum)."""
     E = x.shape[-1]
     n1, n2 = layer.self_attn_layer_norm, layer.final_layer_norm
     h = bf16r(F.layer_norm(x, (E,), n1.weight, n1.bias, n1.eps))
-    a = attention_block(layer, h, chain_mask, key_pad, fp8)
-    s = x + a
-    y = bf16r(s)
-    h2 = bf16r(F.layer_norm(s, (E,), n2.weight, n2.bias, n2.eps))
+    y = attention_block(layer, h, chain_mask, key_pad, fp8, residual=(x, 1.0, 1.0))
+    h2 = bf16r(F.layer_norm(y, (E,), n2.weight, n2.bias, n2.eps))
     return bf16r(y + feed_forward(layer, h2, fp8))

@@ -85,6 +85,69 @@ def test_qkv_projection_head_major_with_rope(dims, rope):
         torch.testing.assert_close(got.float().cpu(), want, rtol=1e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("dims", [(70, 3, 4, 32), (130, 2, 5, 64), (40, 2, 6, 16)])
+@pytest.mark.parametrize("fp8", [False, True])
+def test_two_pathway_qkv_product_equals_the_two_single_products(dims, fp8):
+    """mintb_qkv2_fwd: both pathways' projections as one product on the [6E][E] operand give the very bits of the two
+    3E-wide products (same tiles, same accumulation order): six head-major tensors, RoPE on the first pathway only,
+    separate multipliers for the two pathways' e4m3 weights."""
+    from mint_plus_b200 import _lib as L
+    T, B, H, D = dims
+    E = H * D
+    g = torch.Generator().manual_seed(T * 7 + D)
+    x = torch.randn(T, B, E, generator=g).bfloat16().to(DEV)
+    w1, w2 = ((torch.randn(3 * E, E, generator=g) * s).bfloat16().to(DEV) for s in (E ** -0.5, 2 * E ** -0.5))
+    b1, b2 = ((0.1 * torch.randn(3 * E, generator=g)).to(DEV) for _ in range(2))
+    tabs = ops.rope_tables(T, D, torch.device(DEV))[:2]
+    if fp8:
+        s1, s2 = float(w1.float().abs().max()) / 448, float(w2.float().abs().max()) / 448
+        f1, f2 = (ops.quantize_e4m3(w1, s1), s1, 1.0, 1.0), (ops.quantize_e4m3(w2, s2), s2, 1.0, 1.0)
+        w6 = torch.cat([f1[0].view(torch.uint8), f2[0].view(torch.uint8)]).view(torch.float8_e4m3fn)
+        xin, in_dt, al = ops.quantize_e4m3(x.reshape(-1, E), 1.0), L.E4M3, (s1, s2)
+    else:
+        f1 = f2 = None
+        w6, xin, in_dt, al = torch.cat([w1, w2]), x.reshape(-1, E), L.BF16, (1.0, 1.0)
+    want = list(ops.qkv_project(x, w1, b1, H, rope=tabs, fp8=f1)) + list(ops.qkv_project(x, w2, b2, H, fp8=f2))
+    b6 = torch.cat([b1, b2])
+    outs = [torch.empty(B, H, T, D, dtype=torch.bfloat16, device=DEV) for _ in range(6)]
+    rc = L.lib().mintb_qkv2_fwd(xin.data_ptr(), w6.data_ptr(), b6.data_ptr(), *[t.data_ptr() for t in outs], T, B, H, D, in_dt, L.F32,
+                                al[0], al[1], 1.0, tabs[0].data_ptr(), tabs[1].data_ptr(), None, T * B,
+                                torch.cuda.current_stream().cuda_stream, ops._dev_status(torch.device(DEV, 0)).data_ptr())
+    L.check(rc, "mintb_qkv2_fwd")
+    ops.check_device_status()
+    for got, ref in zip(outs, want):
+        assert torch.equal(got, ref)
+
+
+@pytest.mark.parametrize("shape", [(300, 256, 128), (77, 136, 64), (2048, 1280, 1280)])
+@pytest.mark.parametrize("quant", [False, True])
+def test_residual_sum_in_the_projection_epilogue(shape, quant):
+    """mintb_linear_res_fwd: a r + b (x W^T + bias) in one pass, and with an e4m3 result the bf16 copy beside it, the e4m3
+    numbers cast from the bf16 values."""
+    M_, N, K = shape
+    g = torch.Generator().manual_seed(N)
+    x = torch.randn(M_, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16()
+    bias = 0.1 * torch.randn(N, generator=g)
+    r = torch.randn(M_, N, generator=g).bfloat16()
+    a, b = 0.9, 0.4
+    want = a * r.float() + b * (x.float() @ w.float().t() + bias)
+    out, q8 = ops.gemm_res(x.to(DEV), w.to(DEV), 1.0, bias.to(DEV), r.to(DEV), a, b, quant_scale=0.02 if quant else None)
+    ops.check_device_status()
+    assert (out.float().cpu() - want).abs().max().item() <= 1e-2 * want.abs().max().item() + 1e-3
+    if quant:
+        ref8 = ops.quantize_e4m3(out, 0.02)
+        assert torch.equal(q8.view(torch.uint8), ref8.view(torch.uint8))
+    # and differentiable: gradients of x, W, bias and the residual
+    xd, wd, bd, rd = (t.to(DEV).requires_grad_(True) for t in (x, w, bias, r))
+    gy = torch.randn(M_, N, generator=g).bfloat16()
+    ops.linear_res(xd, wd, bd, rd, a, b).backward(gy.to(DEV))
+    xr, wr, br, rr = (t.float().requires_grad_(True) for t in (x, w, bias, r))
+    (a * rr + b * (xr @ wr.t() + br)).backward(gy.float())
+    for got, ref in ((xd.grad, xr.grad), (wd.grad, wr.grad), (bd.grad, br.grad), (rd.grad, rr.grad)):
+        assert (got.float().cpu() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3
+
+
 def test_linear_and_qkv_gradients_match_autograd():
     g = torch.Generator().manual_seed(3)
     T, B, H, D = 40, 2, 4, 32
@@ -176,7 +239,8 @@ def test_bf16_layer_forward_backward_against_restated_layer(fp8):
             "db_out": rel(glayer.self_attn.out_proj.bias.grad, layer.self_attn.out_proj.bias.grad)}
     print(f"pre-LN layer fp8={fp8}: " + ", ".join(f"{k} {v:.3g}" for k, v in errs.items()))
     assert errs["out"] <= 3e-2, errs
-    assert max(errs["dx"], errs["dW_fc2"], errs["dW_qkv_cross"], errs["db_out"]) <= 5e-2, errs
+    # (e5m2 gradients: elements that differ by one bf16 step between the two sides can round to e5m2 neighbours 12.5 - 25 % apart)
+    assert max(errs["dx"], errs["dW_fc2"], errs["dW_qkv_cross"], errs["db_out"]) <= (8e-2 if fp8 else 3e-2), errs
 
 
 def test_lora_linear_on_the_merged_weight_matches_the_formula():
