@@ -105,6 +105,9 @@ MINTB_API int mintb_rope_tables(const float* inv_freq, float* cos_tab, float* si
  * projections and scale = D^-0.5; without it the caller has already scaled and rotated
  * (multi_pathway_attention.py:199-202) — pass scale = 1.
  * lse [B][H][T] receives log(sum_j exp(logit_ij)) for the backward pass.
+ * The workspace is never empty on the bf16 tensor-core path: the persistent kernel draws its (query tile, batch, head)
+ * work items from a counter at the end of it, which each call clears in stream order; with MINTB_FLAG_ROPE the rotated
+ * copies of q_self and k_self come first.  Calls that overlap on the GPU need separate workspaces.
  */
 MINTB_API size_t mintb_attn_fwd_workspace_bytes(int B, int H, int T, int D, int dtype, unsigned flags);
 MINTB_API int mintb_attn_fwd(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
@@ -116,8 +119,8 @@ MINTB_API int mintb_attn_fwd(const void* q_self, const void* k_self, const void*
  * memory at the point where they call it: code that runs while a CUDA graph is being captured, real-time or
  * fixed-memory-budget hosts that forbid cudaMalloc after start-up, and host languages whose bindings hand over
  * pre-pinned buffers only.  For them this variant of mintb_attn_fwd (bf16 tensor-core path) keeps the scratch it needs
- * with MINTB_FLAG_ROPE - the rotated copies of q_self and k_self - in an array of MINTB_STATIC_SCRATCH_BYTES inside the
- * library image, so the caller passes inputs and outputs only and nothing is allocated or freed, here or in any
+ - the work counter and, with MINTB_FLAG_ROPE, the rotated copies of q_self and k_self - in an array of
+ * MINTB_STATIC_SCRATCH_BYTES (plus the counter) inside the library image, so the caller passes inputs and outputs only and nothing is allocated or freed, here or in any
  * library routine it calls.  Limits and rules:
  *   - 2 * B*H*T*D * 2 bytes must fit the array (B*H*T*D <= 8 Mi elements with rope); larger calls return
  *     MINTB_EWORKSPACE with a message and launch nothing.  Every GPU that loads the library holds the array until exit.

@@ -146,7 +146,7 @@ struct FwdCfg {
   static constexpr int kColS = 0, kColP = kN;                // S: kN fp32 columns; P: kN/2 columns of packed bf16
   static constexpr int kColO = D == 64 ? 128 : 192;          // O of key-half 0, then O of key-half 1
   static constexpr int kOStride = D == 64 ? 64 : 32;
-  static constexpr size_t kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + size_t(kStages) * kStageBytes + 6144 /*tail*/;
+  static constexpr size_t kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + size_t(kStages) * kStageBytes + 8192 /*tail: barriers, items, statistics, two entry lists*/;
 };
 
 struct FwdParams {
@@ -159,6 +159,8 @@ struct FwdParams {
   int* status;
   size_t out_row_stride, out_bh_stride;   // elements between consecutive queries / (batch, head) pairs of `out`
   int skip_pad_queries;                   // leave out query tiles that hold only padded positions
+  int* sched;                             // work counter in global memory, zero when the kernel starts
+  int NQ, n_items;                        // query tiles per (batch, head); items = NQ * B * H, item = bh * NQ + qt
 };
 
 // entry flags (low three bits are the class bits kHasIntra | kHasInter | kHasPad)
@@ -220,6 +222,17 @@ __device__ __forceinline__ void softmax_chunk(float (&s)[W], uint32_t pad_bits, 
   l += l0 + l1;
 }
 
+// A work item of the persistent forward kernel as the producer warp hands it to the other roles.
+struct FwdItem {
+  int qt, bh;
+  int n_ent;    // entries of the item; kItemEnd: no more work; kItemSkip: a query tile that is left out (nothing to write)
+};
+constexpr int kItemEnd = -1, kItemSkip = -2;
+
+// Persistent CTAs (two per SM) take (query tile, batch * head) items from a counter in global memory.  The producer warp
+// runs one item ahead: while the other roles work on item i it fetches item i + 1, builds its entry list (double buffered)
+// and, as soon as the last Q K^T of item i has read the Q tiles, loads the next Q tiles and the first K/V stages, so that
+// the set-up of an item hides behind the tail of its predecessor, and a CTA that drew a cheap item simply draws the next.
 template <int D, bool SQ>
 __global__ void __launch_bounds__(kTcThreads, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_constant__ CUtensorMap map_ks,
@@ -233,130 +246,176 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   unsigned char* sQc = smem + Cfg::kQBytes;
   unsigned char* sKV = smem + 2 * Cfg::kQBytes;  // [stage][K slot | V slot]
   unsigned char* tail = sKV + size_t(kStages) * Cfg::kStageBytes;
-  uint64_t* bar_q = reinterpret_cast<uint64_t*>(tail);
-  uint64_t* kv_full = bar_q + 1;          // [kStages]
+  uint64_t* bar_q = reinterpret_cast<uint64_t*>(tail);   // producer -> MMA: the Q tiles of the item have landed
+  uint64_t* q_free = bar_q + 1;           // MMA -> producer: the item's last Q K^T has completed, the Q tiles may be overwritten
+  uint64_t* kv_full = q_free + 1;         // [kStages]
   uint64_t* kv_empty = kv_full + kStages; // [kStages]
   uint64_t* s_full = kv_empty + kStages;  // MMA -> softmax: logits of the entry are in TMEM
   uint64_t* s_free = s_full + 1;          // softmax -> MMA: every thread has read its logits (256 arrivals)
   uint64_t* p_full = s_free + 1;          // softmax -> MMA: probabilities are in TMEM (256 arrivals)
   uint64_t* o_ready = p_full + 1;         // MMA -> softmax: P V of the entry has completed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
-  int* n_entries_s = reinterpret_cast<int*>(tmem_slot + 1);
-  float* hstat = reinterpret_cast<float*>(tmem_slot + 2);          // [2][128] running maxima, [2][128] row sums
-  uint16_t* ent_k = reinterpret_cast<uint16_t*>(hstat + 512);      // first key of the entry / 32
-  uint8_t* ent_c = reinterpret_cast<uint8_t*>(ent_k + kMaxKeyTiles);
-  uint8_t* tcls = ent_c + kMaxKeyTiles;                            // class per 64-key tile, 0 = skip
+  uint64_t* item_full = o_ready + 1;      // [2] producer -> MMA, softmax: the item and its entry list are in shared memory
+  uint64_t* item_free = item_full + 2;    // [2] MMA, softmax -> producer: the slot may be overwritten (257 arrivals)
+  uint64_t* h_full = item_free + 2;       // softmax -> softmax: both halves' statistics of the item are written (256 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(h_full + 1);
+  FwdItem* items = reinterpret_cast<FwdItem*>(tmem_slot + 2);     // [2]
+  float* hstat = reinterpret_cast<float*>(items + 2);              // per item slot: [2][128] running maxima, [2][128] row sums
+  uint16_t* ent_k = reinterpret_cast<uint16_t*>(hstat + 2 * 512);  // [2][kMaxKeyTiles] first key of the entry / 32
+  uint8_t* ent_c = reinterpret_cast<uint8_t*>(ent_k + 2 * kMaxKeyTiles);   // [2][kMaxKeyTiles]
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int qt = blockIdx.x, bh = blockIdx.y, b = bh / p.H;
-  const int q0 = qt * kBM;
   const int nkt = p.NT;  // key tiles of 64 == class-table columns
 
-  if (p.skip_pad_queries) {   // the padding bits describe positions, so they cover the query rows of this tile as well
-    const uint32_t* w = p.kpad + size_t(b) * p.TW + 4 * qt;
-    if ((w[0] & w[1] & w[2] & w[3]) == 0xffffffffu) return;   // uniform over the CTA; nothing has been set up yet
-  }
-  // tile classes of this query tile: OR of its two 64-row halves
-  for (int kt = tid; kt < nkt; kt += kTcThreads) {
-    const uint8_t* row0 = p.cls + (size_t(b) * p.NT + 2 * qt) * p.NT;
-    uint8_t c = row0[kt];
-    if (2 * qt + 1 < p.NT) c |= row0[p.NT + kt];
-    tcls[kt] = (c & (kHasIntra | kHasInter)) ? c : 0;
-  }
   if (tid == 0) {
     mbar_init(bar_q, 1);
+    mbar_init(q_free, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(s_full, 1);
     mbar_init(s_free, 256);
     mbar_init(p_full, 256);
     mbar_init(o_ready, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&item_full[s], 1); mbar_init(&item_free[s], 257); }
+    mbar_init(h_full, 256);
     fence_mbar_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
-  __syncthreads();
-  if (warp == 0 && lane == 0) {   // the Q tiles do not depend on the entry list: start them now
-    prefetch_tensormap(&map_qs); prefetch_tensormap(&map_qc);
-    mbar_expect_tx(bar_q, 2 * Cfg::kQBytes);
-    tma_load_3d(sQs, &map_qs, bar_q, 0, q0, bh);
-    tma_load_3d(sQc, &map_qc, bar_q, 0, q0, bh);
-  }
-  if (warp == 2) {   // one warp turns the class row into the entry list, 32 tiles per pass
-    int n = 0;
-    for (int base = 0; base < nkt; base += 32) {
-      const int kt = base + lane;
-      const uint8_t c = kt < nkt ? tcls[kt] : uint8_t(0);
-      const uint8_t cn = (kt + 1 < nkt && lane < 31) ? tcls[kt + 1] : uint8_t(0);   // a pass boundary also ends a run
-      const bool mixed = (c & 3) == 3, pure = c != 0 && !mixed;
-      const uint8_t cp = lane > 0 ? tcls[kt - 1] : uint8_t(0);
-      // runs of pure tiles of one pathway: a tile starts a run unless its predecessor is a pure tile of the same pathway
-      const bool run_start = pure && !(cp != 0 && (cp & 3) == (c & 3));
-      const unsigned starts = __ballot_sync(0xffffffffu, run_start);
-      const unsigned below = starts & (0xffffffffu >> (31 - lane));               // run starts at or before this lane
-      const int off = pure ? lane - (31 - __clz(below)) : 0;                      // position inside the run
-      const bool can_pair = kN == 128 && pure && cn != 0 && (cn & 3) == (c & 3);
-      int cnt = 0;
-      uint8_t flags = c;
-      if (mixed) cnt = kN == 128 ? 1 : 2;
-      else if (pure) {
-        if constexpr (kN == 128) {
-          if ((off & 1) == 0) { cnt = 1; if (can_pair) flags = uint8_t(c | cn | kEntryFull); }
-        } else {
-          cnt = 1;
-          flags = uint8_t(c | kEntryFull);
-        }
-      }
-      // exclusive prefix sum of cnt over the lanes (cnt is 0, 1 or 2)
-      const unsigned b1 = __ballot_sync(0xffffffffu, cnt & 1), b2 = __ballot_sync(0xffffffffu, cnt & 2);
-      const unsigned lt = (1u << lane) - 1u;
-      const int pos = n + __popc(b1 & lt) + 2 * __popc(b2 & lt);
-      if (cnt >= 1) { ent_k[pos] = uint16_t(2 * kt); ent_c[pos] = flags; }
-      if (cnt == 2) { ent_k[pos + 1] = uint16_t(2 * kt + 1); ent_c[pos + 1] = flags; }
-      n += __popc(b1) + 2 * __popc(b2);
-    }
-    if (lane == 0) *n_entries_s = n;
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = *tmem_slot;
-  const int n_ent = *n_entries_s;
 
   if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer
+    // ---------------------------------------------------------------- producer: scheduler, entry lists, TMA
     if (lane == 0) {
+      prefetch_tensormap(&map_qs); prefetch_tensormap(&map_qc);
       prefetch_tensormap(&map_ks); prefetch_tensormap(&map_vs);
       prefetch_tensormap(&map_kc); prefetch_tensormap(&map_vc);
-      for (int it = 0; it < n_ent; ++it) {
-        const int stage = it % kStages;
-        if (!mbar_wait(&kv_empty[stage], ((it / kStages) & 1) ^ 1, p.status, 0x101)) break;
-        const uint8_t c = ent_c[it];
-        const int k0 = int(ent_k[it]) * 32;
-        unsigned char* kslot = sKV + size_t(stage) * Cfg::kStageBytes;
-        unsigned char* vslot = kslot + Cfg::kSlotBytes;
-        if ((c & 3) == 3) {   // mixed: one box of each of the four tensors
-          mbar_expect_tx(&kv_full[stage], 4 * Cfg::kBoxBytes);
-          tma_load_3d(kslot, &map_ks, &kv_full[stage], 0, k0, bh);
-          tma_load_3d(kslot + Cfg::kBoxBytes, &map_kc, &kv_full[stage], 0, k0, bh);
-          tma_load_3d(vslot, &map_vs, &kv_full[stage], 0, k0, bh);
-          tma_load_3d(vslot + Cfg::kBoxBytes, &map_vc, &kv_full[stage], 0, k0, bh);
+    }
+    uint32_t item_no = 0, q_no = 0, g_it = 0;   // items drawn, Q loads issued, entries loaded (over all items of this CTA)
+    bool ok = true;
+    for (;;) {
+      const int slot = item_no & 1;
+      int item = 0;
+      if (lane == 0) item = atomicAdd(p.sched, 1);
+      item = __shfl_sync(0xffffffffu, item, 0);
+      const bool have = item < p.n_items;
+      if (item_no >= 2) {   // the slot was last used by item item_no - 2: the other roles must have left it
+        ok = __all_sync(0xffffffffu, mbar_wait(&item_free[slot], ((item_no >> 1) - 1) & 1, p.status, 0x102));
+        if (!ok) break;
+      }
+      const int qt = have ? item % p.NQ : 0, bh = have ? item / p.NQ : 0, b = bh / p.H;
+      int n = kItemEnd;
+      if (have) {
+        bool skip = false;
+        if (p.skip_pad_queries) {   // the padding bits describe positions, so they cover the query rows of this tile as well
+          const uint32_t* w = p.kpad + size_t(b) * p.TW + 4 * qt;
+          skip = (w[0] & w[1] & w[2] & w[3]) == 0xffffffffu;
+        }
+        if (skip) {
+          n = kItemSkip;
         } else {
-          const CUtensorMap* mk = (c & kHasIntra) ? &map_ks : &map_kc;
-          const CUtensorMap* mv = (c & kHasIntra) ? &map_vs : &map_vc;
-          const int boxes = (c & kEntryFull) ? 2 : 1;
-          mbar_expect_tx(&kv_full[stage], 2 * boxes * Cfg::kBoxBytes);
-          for (int bx = 0; bx < boxes; ++bx) {
-            tma_load_3d(kslot + bx * Cfg::kBoxBytes, mk, &kv_full[stage], 0, k0 + bx * kBox, bh);
-            tma_load_3d(vslot + bx * Cfg::kBoxBytes, mv, &kv_full[stage], 0, k0 + bx * kBox, bh);
+          // tile classes of this query tile (OR of its two 64-row halves) turned into the entry list, 32 key tiles per pass
+          uint16_t* ek = ent_k + slot * kMaxKeyTiles;
+          uint8_t* ec = ent_c + slot * kMaxKeyTiles;
+          const uint8_t* row0 = p.cls + (size_t(b) * p.NT + 2 * qt) * p.NT;
+          const bool two_rows = 2 * qt + 1 < p.NT;
+          n = 0;
+          for (int base = 0; base < nkt; base += 32) {
+            const int kt = base + lane;
+            uint8_t c = 0;
+            if (kt < nkt) {
+              c = row0[kt];
+              if (two_rows) c |= row0[p.NT + kt];
+              if (!(c & (kHasIntra | kHasInter))) c = 0;
+            }
+            uint8_t cn = uint8_t(__shfl_down_sync(0xffffffffu, unsigned(c), 1));   // a pass boundary also ends a run
+            uint8_t cp = uint8_t(__shfl_up_sync(0xffffffffu, unsigned(c), 1));
+            if (lane == 31) cn = 0;
+            if (lane == 0) cp = 0;
+            const bool mixed = (c & 3) == 3, pure = c != 0 && !mixed;
+            // runs of pure tiles of one pathway: a tile starts a run unless its predecessor is a pure tile of the same pathway
+            const bool run_start = pure && !(cp != 0 && (cp & 3) == (c & 3));
+            const unsigned starts = __ballot_sync(0xffffffffu, run_start);
+            const unsigned below = starts & (0xffffffffu >> (31 - lane));               // run starts at or before this lane
+            const int off = pure ? lane - (31 - __clz(below)) : 0;                      // position inside the run
+            const bool can_pair = kN == 128 && pure && cn != 0 && (cn & 3) == (c & 3);
+            int cnt = 0;
+            uint8_t flags = c;
+            if (mixed) cnt = kN == 128 ? 1 : 2;
+            else if (pure) {
+              if constexpr (kN == 128) {
+                if ((off & 1) == 0) { cnt = 1; if (can_pair) flags = uint8_t(c | cn | kEntryFull); }
+              } else {
+                cnt = 1;
+                flags = uint8_t(c | kEntryFull);
+              }
+            }
+            // exclusive prefix sum of cnt over the lanes (cnt is 0, 1 or 2)
+            const unsigned b1 = __ballot_sync(0xffffffffu, cnt & 1), b2 = __ballot_sync(0xffffffffu, cnt & 2);
+            const unsigned lt = (1u << lane) - 1u;
+            const int pos = n + __popc(b1 & lt) + 2 * __popc(b2 & lt);
+            if (cnt >= 1) { ek[pos] = uint16_t(2 * kt); ec[pos] = flags; }
+            if (cnt == 2) { ek[pos + 1] = uint16_t(2 * kt + 1); ec[pos + 1] = flags; }
+            n += __popc(b1) + 2 * __popc(b2);
           }
         }
       }
+      if (lane == 0) items[slot] = FwdItem{qt, bh, n};
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&item_full[slot]);
+      if (!have) break;
+      if (n > 0) {
+        if (lane == 0) {
+          if (q_no > 0) ok = mbar_wait(q_free, (q_no - 1) & 1, p.status, 0x103);   // the previous item's Q tiles are no longer read
+          if (ok) {
+            mbar_expect_tx(bar_q, 2 * Cfg::kQBytes);
+            tma_load_3d(sQs, &map_qs, bar_q, 0, qt * kBM, bh);
+            tma_load_3d(sQc, &map_qc, bar_q, 0, qt * kBM, bh);
+            const uint16_t* ek = ent_k + slot * kMaxKeyTiles;
+            const uint8_t* ec = ent_c + slot * kMaxKeyTiles;
+            for (int it = 0; it < n; ++it, ++g_it) {
+              const int stage = g_it % kStages;
+              if (!mbar_wait(&kv_empty[stage], ((g_it / kStages) & 1) ^ 1, p.status, 0x101)) { ok = false; break; }
+              const uint8_t c = ec[it];
+              const int k0 = int(ek[it]) * 32;
+              unsigned char* kslot = sKV + size_t(stage) * Cfg::kStageBytes;
+              unsigned char* vslot = kslot + Cfg::kSlotBytes;
+              if ((c & 3) == 3) {   // mixed: one box of each of the four tensors
+                mbar_expect_tx(&kv_full[stage], 4 * Cfg::kBoxBytes);
+                tma_load_3d(kslot, &map_ks, &kv_full[stage], 0, k0, bh);
+                tma_load_3d(kslot + Cfg::kBoxBytes, &map_kc, &kv_full[stage], 0, k0, bh);
+                tma_load_3d(vslot, &map_vs, &kv_full[stage], 0, k0, bh);
+                tma_load_3d(vslot + Cfg::kBoxBytes, &map_vc, &kv_full[stage], 0, k0, bh);
+              } else {
+                const CUtensorMap* mk = (c & kHasIntra) ? &map_ks : &map_kc;
+                const CUtensorMap* mv = (c & kHasIntra) ? &map_vs : &map_vc;
+                const int boxes = (c & kEntryFull) ? 2 : 1;
+                mbar_expect_tx(&kv_full[stage], 2 * boxes * Cfg::kBoxBytes);
+                for (int bx = 0; bx < boxes; ++bx) {
+                  tma_load_3d(kslot + bx * Cfg::kBoxBytes, mk, &kv_full[stage], 0, k0 + bx * kBox, bh);
+                  tma_load_3d(vslot + bx * Cfg::kBoxBytes, mv, &kv_full[stage], 0, k0 + bx * kBox, bh);
+                }
+              }
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+        g_it = __shfl_sync(0xffffffffu, g_it, 0);
+        ++q_no;
+        if (!ok) break;
+      }
+      ++item_no;
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    // One thread issues everything and its instruction count per entry is on the critical path: descriptors are kept as
-    // (constant high word, running low word).  Order per entry: as soon as the softmax threads have READ S(it) the next
-    // Q K^T is issued into the same columns (P lives elsewhere), then P V (it) once the probabilities have arrived.
-    if (lane == 0 && n_ent > 0) {
+    // The whole warp runs this loop and one elected lane issues: with warp-uniform control flow and operands the compiler
+    // keeps the descriptors in uniform registers, which is what the MMA instruction reads; issued from a divergent
+    // single-lane region every instruction first moves its operands there, and that, not the tensor pipe, set the pace.
+    // Values read from shared memory are made provably uniform with a lane-0 shuffle.  Order per entry: as soon as the
+    // softmax threads have READ S of the entry before, the next Q K^T is issued into the same columns (P lives
+    // elsewhere) - also across items -, then P V of this entry once its probabilities have arrived.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_qk_full = idesc_bf16(kBM, kN, false, false);
       constexpr uint32_t idesc_qk_half = idesc_bf16(kBM, kBox, false, false);
       constexpr uint32_t idesc_pv = idesc_bf16(kBM, D, false, true);
@@ -364,98 +423,129 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       constexpr uint32_t kLboK = desc_lbo32(16), kLboV = desc_lbo32(8 * RB);
       constexpr uint32_t kSlot = Cfg::kSlotBytes >> 4, kBoxU = Cfg::kBoxBytes >> 4, kStageUnits = Cfg::kStageBytes >> 4;
       constexpr uint32_t kVStep = (16 * RB) >> 4;
-      const uint32_t lo_qs = desc_addr32(smem_u32(sQs)) + kLboK, lo_qc = desc_addr32(smem_u32(sQc)) + kLboK;
-      const uint32_t lo_kv = desc_addr32(smem_u32(sKV));
-      const uint32_t col_s = tbase + Cfg::kColS, col_p = tbase + Cfg::kColP, col_o = tbase + Cfg::kColO;
-      bool ok = mbar_wait(bar_q, 0, p.status, 0x201);
-      tc_fence_after();
+      const uint32_t smem_base = __shfl_sync(0xffffffffu, smem_u32(smem), 0);
+      const uint32_t tb = __shfl_sync(0xffffffffu, tbase, 0);
+      const uint32_t lo_qs = desc_addr32(smem_base) + kLboK, lo_qc = desc_addr32(smem_base + Cfg::kQBytes) + kLboK;
+      const uint32_t lo_kv = desc_addr32(smem_base + 2 * Cfg::kQBytes);
+      const uint32_t col_s = tb + Cfg::kColS, col_p = tb + Cfg::kColP, col_o = tb + Cfg::kColO;
+      uint32_t item_no = 0, q_no = 0, g_it = 0;   // g_it: entries whose P V has been issued (over all items)
+      bool ok = true;
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, p.status, code));
+      };
 
-      auto issue_qk = [&](int it) -> bool {
-        const uint32_t stage = uint32_t(it % kStages);
-        if (!mbar_wait(&kv_full[stage], (it / kStages) & 1, p.status, 0x202)) return false;
+      // Q K^T of entry number g (over all items), class byte c; S must have been read by the softmax threads of entry g - 1
+      auto issue_qk = [&](uint32_t g, uint32_t c) -> bool {
+        if (g > 0 && !wait_all(s_free, (g - 1) & 1, 0x205)) return false;
+        const uint32_t stage = g % kStages;
+        if (!wait_all(&kv_full[stage], (g / kStages) & 1, 0x202)) return false;
         tc_fence_after();
-        const uint8_t c = ent_c[it];
         const uint32_t slot = lo_kv + stage * kStageUnits + kLboK;
         if ((c & 3) == 3) {   // mixed: self logits in columns [0, kBox), cross logits in [kBox, 2 kBox)
+          if (leader) {
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k)
-            umma_ss(col_s, make_desc(kHi, lo_qs + 2 * k), make_desc(kHi, slot + 2 * k), idesc_qk_half, k > 0);
+            for (int k = 0; k < D / 16; ++k)
+              umma_ss(col_s, make_desc(kHi, lo_qs + 2 * k), make_desc(kHi, slot + 2 * k), idesc_qk_half, k > 0);
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k)
-            umma_ss(col_s + kBox, make_desc(kHi, lo_qc + 2 * k), make_desc(kHi, slot + kBoxU + 2 * k), idesc_qk_half, k > 0);
+            for (int k = 0; k < D / 16; ++k)
+              umma_ss(col_s + kBox, make_desc(kHi, lo_qc + 2 * k), make_desc(kHi, slot + kBoxU + 2 * k), idesc_qk_half, k > 0);
+          }
         } else {
           const uint32_t a_lo = (c & kHasIntra) ? lo_qs : lo_qc;
           const uint32_t idesc = (c & kEntryFull) ? idesc_qk_full : idesc_qk_half;
+          if (leader) {
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) umma_ss(col_s, make_desc(kHi, a_lo + 2 * k), make_desc(kHi, slot + 2 * k), idesc, k > 0);
+            for (int k = 0; k < D / 16; ++k) umma_ss(col_s, make_desc(kHi, a_lo + 2 * k), make_desc(kHi, slot + 2 * k), idesc, k > 0);
+          }
         }
-        umma_commit(s_full);
+        if (leader) umma_commit(s_full);
+        __syncwarp();
         return true;
       };
 
-      if (ok) ok = issue_qk(0);
-      for (int it = 0; it < n_ent && ok; ++it) {
-        if (it + 1 < n_ent) {
-          ok = mbar_wait(s_free, it & 1, p.status, 0x205);   // S(it) has been read: its columns may be overwritten
+      for (;;) {
+        const int slot = item_no & 1;
+        ok = wait_all(&item_full[slot], (item_no >> 1) & 1, 0x206);
+        if (!ok) break;
+        const int n_ent = __shfl_sync(0xffffffffu, items[slot].n_ent, 0);
+        if (n_ent == kItemEnd) break;
+        if (n_ent > 0) {
+          const uint8_t* ec = ent_c + slot * kMaxKeyTiles;
+          ok = wait_all(bar_q, q_no & 1, 0x201);
           if (!ok) break;
           tc_fence_after();
-          ok = issue_qk(it + 1);
-          if (!ok) break;
-        }
-        ok = mbar_wait(p_full, it & 1, p.status, 0x203);
-        if (!ok) break;
-        tc_fence_after();
-        const uint8_t c = ent_c[it];
-        const uint32_t v_lo = lo_kv + uint32_t(it % kStages) * kStageUnits + kSlot + kLboV;
-        const bool acc = it > 0;
-        if ((c & 3) == 3) {
-          // keys [0, kBox/2) of the entry belong to softmax half 0 (O half 0), the rest to half 1
+          uint32_t c_next = __shfl_sync(0xffffffffu, uint32_t(ec[0]), 0);
+          ok = issue_qk(g_it, c_next);
+          if (ok && n_ent == 1 && leader) umma_commit(q_free);
+          for (int it = 0; it < n_ent && ok; ++it, ++g_it) {
+            const uint32_t c = c_next;
+            if (it + 1 < n_ent) {
+              c_next = __shfl_sync(0xffffffffu, uint32_t(ec[it + 1]), 0);
+              ok = issue_qk(g_it + 1, c_next);
+              if (!ok) break;
+              if (it + 2 == n_ent && leader) umma_commit(q_free);   // that was the item's last Q K^T
+            }
+            ok = wait_all(p_full, g_it & 1, 0x203);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t v_lo = lo_kv + uint32_t(g_it % kStages) * kStageUnits + kSlot + kLboV;
+            const bool acc = it > 0;
+            if ((c & 3) == 3) {
+              // keys [0, kBox/2) of the entry belong to softmax half 0 (O half 0), the rest to half 1
+              if (leader) {
 #pragma unroll
-          for (int k = 0; k < kBox / 16; ++k)
-            umma_ts(col_o + (k >= kBox / 32 ? Cfg::kOStride : 0), col_p + k * 8, make_desc(kHi, v_lo + k * kVStep), idesc_pv,
-                    acc || (k % (kBox / 32)) != 0);
+                for (int k = 0; k < kBox / 16; ++k)
+                  umma_ts(col_o + (k >= kBox / 32 ? Cfg::kOStride : 0), col_p + k * 8, make_desc(kHi, v_lo + k * kVStep), idesc_pv,
+                          acc || (k % (kBox / 32)) != 0);
 #pragma unroll
-          for (int k = 0; k < kBox / 16; ++k)
-            umma_ts(col_o + (k >= kBox / 32 ? Cfg::kOStride : 0), col_p + kBox / 2 + k * 8,
-                    make_desc(kHi, v_lo + kBoxU + k * kVStep), idesc_pv, true);
-        } else {
-          const uint32_t vv = v_lo;
-          if (c & kEntryFull) {
+                for (int k = 0; k < kBox / 16; ++k)
+                  umma_ts(col_o + (k >= kBox / 32 ? Cfg::kOStride : 0), col_p + kBox / 2 + k * 8,
+                          make_desc(kHi, v_lo + kBoxU + k * kVStep), idesc_pv, true);
+              }
+            } else if (c & kEntryFull) {
+              if (leader) {
 #pragma unroll
-            for (int k = 0; k < kN / 16; ++k)
-              umma_ts(col_o + (k >= kN / 32 ? Cfg::kOStride : 0), col_p + k * 8, make_desc(kHi, vv + k * kVStep), idesc_pv,
-                      acc || (k % (kN / 32)) != 0);
-          } else {
+                for (int k = 0; k < kN / 16; ++k)
+                  umma_ts(col_o + (k >= kN / 32 ? Cfg::kOStride : 0), col_p + k * 8, make_desc(kHi, v_lo + k * kVStep), idesc_pv,
+                          acc || (k % (kN / 32)) != 0);
+              }
+            } else {
+              if (leader) {
 #pragma unroll
-            for (int k = 0; k < kBox / 16; ++k)
-              umma_ts(col_o + (k >= kBox / 32 ? Cfg::kOStride : 0), col_p + k * 8, make_desc(kHi, vv + k * kVStep), idesc_pv,
-                      acc || (k % (kBox / 32)) != 0);
+                for (int k = 0; k < kBox / 16; ++k)
+                  umma_ts(col_o + (k >= kBox / 32 ? Cfg::kOStride : 0), col_p + k * 8, make_desc(kHi, v_lo + k * kVStep), idesc_pv,
+                          acc || (k % (kBox / 32)) != 0);
+              }
+            }
+            if (leader) {
+              umma_commit(o_ready);
+              umma_commit(&kv_empty[g_it % kStages]);
+            }
+            __syncwarp();
           }
+          if (!ok) break;
+          ++q_no;
         }
-        umma_commit(o_ready);
-        umma_commit(&kv_empty[it % kStages]);
+        if (leader) mbar_arrive(&item_free[slot]);
+        ++item_no;
       }
     }
   } else {
     // ---------------------------------------------------------------- softmax warps: two threads per query row
     // Thread (row, ch) owns half ch of the keys of every entry of its row, with its OWN running maximum, row sum and O
     // accumulator (the P V product of key-half ch lands in O half ch), so the two threads of a row never synchronise inside
-    // the loop; the two partial softmax states are merged once, in the epilogue.
+    // the loop; the two partial softmax states are merged once per item, in its epilogue.
     const int sw = warp - 2;                      // 0..7
     const int quarter = warp % 4;                 // TMEM lane quarter this warp may access
     const int ch = sw / 4;                        // key half
     const int row = quarter * 32 + lane;          // row within the query tile == TMEM lane
-    const int qi = q0 + row;
-    const int qrow = qi < p.T ? qi : p.T - 1;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const uint32_t tO = tbase + lane_base + Cfg::kColO + Cfg::kOStride * ch;
     const uint32_t tS = tbase + lane_base + Cfg::kColS;
     const uint32_t tP = tbase + lane_base + Cfg::kColP;
-    const uint32_t* mrow = p.bits + (size_t(b) * p.T + qrow) * p.TW;
-    const uint32_t* prow = p.kpad + size_t(b) * p.TW;
     const float c2 = p.scale_log2;
     const uint64_t c22 = SQ ? pack2(0.5f * c2, 0.5f * c2) : pack2(c2, c2);   // multiplies the logits inside exp2
-    float m_ref = -INFINITY, l = 0.f;
+    uint32_t item_no = 0, g_it = 0, h_no = 0;   // items seen, entries done, items whose statistics were merged
     bool ok = true;
 
     // rescale this thread's O accumulator by alpha (rare: the running maximum grew by more than the threshold)
@@ -471,181 +561,210 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       }
     };
 
-    for (int it = 0; it < n_ent && ok; ++it) {
-      const uint8_t c = ent_c[it];
-      const int kw = int(ent_k[it]);              // first key of the entry / 32
-      const bool mixed = (c & 3) == 3;
-      const bool has_pad = (c & kHasPad) != 0;
-      ok = mbar_wait(s_full, it & 1, p.status, 0x301);
+    for (;;) {
+      const int slot = item_no & 1;
+      ok = mbar_wait(&item_full[slot], (item_no >> 1) & 1, p.status, 0x306);
       if (!ok) break;
-      if (it == 0 && ch == 1) __nanosleep(kStaggerNs);   // the two key halves run out of phase (see kStaggerNs)
-      tc_fence_after();
-      // Every phase of o_ready is observed, entry by entry (a parity wait cannot tell phases two apart): before O is
-      // rescaled or, at the latest, before P (single-buffered) is overwritten.
-      bool o_seen = it == 0;
-      auto see_o = [&]() -> bool {
-        if (o_seen) return true;
-        o_seen = true;
-        if (!mbar_wait(o_ready, (it - 1) & 1, p.status, 0x304)) return false;
-        tc_fence_after();
-        return true;
-      };
+      const FwdItem item = items[slot];
+      if (item.n_ent == kItemEnd) break;
+      const int n_ent = item.n_ent, bh = item.bh, b = bh / p.H;
+      const int qi = item.qt * kBM + row;
+      const int qrow = qi < p.T ? qi : p.T - 1;
+      if (n_ent != kItemSkip) {
+      const uint16_t* ent_k_i = ent_k + slot * kMaxKeyTiles;
+      const uint8_t* ent_c_i = ent_c + slot * kMaxKeyTiles;
+      const uint32_t* mrow = p.bits + (size_t(b) * p.T + qrow) * p.TW;
+      const uint32_t* prow = p.kpad + size_t(b) * p.TW;
+      float m_ref = -INFINITY, l = 0.f;
 
-      if (!mixed && (c & kEntryFull) && kN == 128) {
-        // 128 keys: this thread's 64 logits in two chunks of 32
-        float alpha; bool resc;
-        uint32_t pk[16];
-        {
-          float s[32];
-          uint32_t r[32];
-          tmem_ld32(tS + 64 * ch, r);
-          tmem_ld_wait();
+      for (int it = 0; it < n_ent && ok; ++it, ++g_it) {
+        const uint8_t c = ent_c_i[it];
+        const int kw = int(ent_k_i[it]);              // first key of the entry / 32
+        const bool mixed = (c & 3) == 3;
+        const bool has_pad = (c & kHasPad) != 0;
+        ok = mbar_wait(s_full, g_it & 1, p.status, 0x301);
+        if (!ok) break;
+        if (it == 0 && ch == 1) __nanosleep(kStaggerNs);   // the two key halves run out of phase (see kStaggerNs)
+        tc_fence_after();
+        // Every phase of o_ready is observed, entry by entry (a parity wait cannot tell phases two apart): before O is
+        // rescaled or, at the latest, before P (single-buffered) is overwritten.
+        bool o_seen = it == 0;
+        auto see_o = [&]() -> bool {
+          if (o_seen) return true;
+          o_seen = true;
+          if (!mbar_wait(o_ready, (g_it - 1) & 1, p.status, 0x304)) return false;
+          tc_fence_after();
+          return true;
+        };
+
+        if (!mixed && (c & kEntryFull) && kN == 128) {
+          // 128 keys: this thread's 64 logits in two chunks of 32
+          float alpha; bool resc;
+          uint32_t pk[16];
+          {
+            float s[32];
+            uint32_t r[32];
+            tmem_ld32(tS + 64 * ch, r);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(r[j]);
-          softmax_chunk<32, SQ>(s, has_pad ? prow[kw + 2 * ch] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
-        }
-        if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
-        uint32_t pk2[16];
-        {
-          float s[32];
-          uint32_t r[32];
-          tmem_ld32(tS + 64 * ch + 32, r);
-          tmem_ld_wait();
-          tc_fence_before();
-          mbar_arrive(s_free);                       // both chunks are in registers: S may be overwritten
+            for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(r[j]);
+            softmax_chunk<32, SQ>(s, has_pad ? prow[kw + 2 * ch] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
+          }
+          if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
+          uint32_t pk2[16];
+          {
+            float s[32];
+            uint32_t r[32];
+            tmem_ld32(tS + 64 * ch + 32, r);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(s_free);                       // both chunks are in registers: S may be overwritten
 #pragma unroll
-          for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(r[j]);
-          softmax_chunk<32, SQ>(s, has_pad ? prow[kw + 2 * ch + 1] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk2);
-        }
-        // a rescale decided by the second chunk also applies to what the first chunk contributes: fold it into pk
-        if (__any_sync(0xffffffffu, resc)) {
-          if (it > 0) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
-          if (resc) {
+            for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(r[j]);
+            softmax_chunk<32, SQ>(s, has_pad ? prow[kw + 2 * ch + 1] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk2);
+          }
+          // a rescale decided by the second chunk also applies to what the first chunk contributes: fold it into pk
+          if (__any_sync(0xffffffffu, resc)) {
+            if (it > 0) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
+            if (resc) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float a0 = __uint_as_float(pk[j] << 16) * alpha, a1 = __uint_as_float(pk[j] & 0xffff0000u) * alpha;
-              pk[j] = pack_bf16(a0, a1);
+              for (int j = 0; j < 16; ++j) {
+                const float a0 = __uint_as_float(pk[j] << 16) * alpha, a1 = __uint_as_float(pk[j] & 0xffff0000u) * alpha;
+                pk[j] = pack_bf16(a0, a1);
+              }
             }
           }
-        }
-        ok = see_o();
-        if (!ok) break;
-        tmem_st16(tP + 32 * ch, pk);
-        tmem_st16(tP + 32 * ch + 16, pk2);
-      } else if (!mixed) {
-        // kBox (D <= 32: 64) or kN (D = 64: 64) keys: 32 logits per thread;  D = 64 half entries do not occur for pure tiles
-        constexpr int W = 32;
-        float alpha; bool resc;
-        uint32_t pk[W / 2];
-        {
-          float s[W];
-          uint32_t r[W];
-          tmem_ld32(tS + W * ch, r);
-          tmem_ld_wait();
-          tc_fence_before();
-          mbar_arrive(s_free);
+          ok = see_o();
+          if (!ok) break;
+          tmem_st16(tP + 32 * ch, pk);
+          tmem_st16(tP + 32 * ch + 16, pk2);
+        } else if (!mixed) {
+          // kBox (D <= 32: 64) or kN (D = 64: 64) keys: 32 logits per thread;  D = 64 half entries do not occur for pure tiles
+          constexpr int W = 32;
+          float alpha; bool resc;
+          uint32_t pk[W / 2];
+          {
+            float s[W];
+            uint32_t r[W];
+            tmem_ld32(tS + W * ch, r);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(s_free);
 #pragma unroll
-          for (int j = 0; j < W; ++j) s[j] = __uint_as_float(r[j]);
-          softmax_chunk<W, SQ>(s, has_pad ? prow[kw + ch] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
-        }
-        if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
-        ok = see_o();
-        if (!ok) break;
-        tmem_st16(tP + (W / 2) * ch, pk);
-      } else {
-        // mixed entry of kBox keys: W = kBox / 2 logits per thread, selected between the self and cross logits
-        constexpr int W = kBox / 2;   // 32 (D <= 32) or 16 (D = 64)
-        float alpha; bool resc;
-        uint32_t pk[W / 2];
-        // mask and padding bits of this thread's W keys: key index of bit 0 is 32 kw + W ch
-        const int bit0 = W * ch;                       // offset inside the entry (entry starts on a 32-key boundary)
-        const uint32_t cw = (mrow[kw + bit0 / 32] >> (bit0 % 32)) & (W == 32 ? 0xffffffffu : 0xffffu);
-        const uint32_t pw = has_pad ? (prow[kw + bit0 / 32] >> (bit0 % 32)) : 0u;
-        {
-          float s[W];
-          uint32_t rs[W], rc[W];
-          tmem_ld_n<W>(tS + W * ch, rs);
-          tmem_ld_n<W>(tS + kBox + W * ch, rc);
-          tmem_ld_wait();
-          tc_fence_before();
-          mbar_arrive(s_free);
+            for (int j = 0; j < W; ++j) s[j] = __uint_as_float(r[j]);
+            softmax_chunk<W, SQ>(s, has_pad ? prow[kw + ch] : 0u, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
+          }
+          if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
+          ok = see_o();
+          if (!ok) break;
+          tmem_st16(tP + (W / 2) * ch, pk);
+        } else {
+          // mixed entry of kBox keys: W = kBox / 2 logits per thread, selected between the self and cross logits
+          constexpr int W = kBox / 2;   // 32 (D <= 32) or 16 (D = 64)
+          float alpha; bool resc;
+          uint32_t pk[W / 2];
+          // mask and padding bits of this thread's W keys: key index of bit 0 is 32 kw + W ch
+          const int bit0 = W * ch;                       // offset inside the entry (entry starts on a 32-key boundary)
+          const uint32_t cw = (mrow[kw + bit0 / 32] >> (bit0 % 32)) & (W == 32 ? 0xffffffffu : 0xffffu);
+          const uint32_t pw = has_pad ? (prow[kw + bit0 / 32] >> (bit0 % 32)) : 0u;
+          {
+            float s[W];
+            uint32_t rs[W], rc[W];
+            tmem_ld_n<W>(tS + W * ch, rs);
+            tmem_ld_n<W>(tS + kBox + W * ch, rc);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(s_free);
 #pragma unroll
-          for (int j = 0; j < W; ++j) s[j] = __uint_as_float(((cw >> j) & 1u) ? rc[j] : rs[j]);
-          softmax_chunk<W, SQ>(s, pw, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
-        }
-        if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
-        // split by pathway: P o ~M multiplies V_self, P o M multiplies V_cross
-        uint32_t pi[W / 2], pe[W / 2];
+            for (int j = 0; j < W; ++j) s[j] = __uint_as_float(((cw >> j) & 1u) ? rc[j] : rs[j]);
+            softmax_chunk<W, SQ>(s, pw, has_pad, c2, c22, m_ref, l, alpha, resc, pk);
+          }
+          if (__any_sync(0xffffffffu, resc && it > 0)) { ok = see_o(); if (!ok) break; rescale_o(alpha); }
+          // split by pathway: P o ~M multiplies V_self, P o M multiplies V_cross
+          uint32_t pi[W / 2], pe[W / 2];
 #pragma unroll
-        for (int j = 0; j < W / 2; ++j) {
-          const uint32_t lo_x = (cw >> (2 * j)) & 1u, hi_x = (cw >> (2 * j + 1)) & 1u;
-          const uint32_t keep_e = (lo_x ? 0x0000ffffu : 0u) | (hi_x ? 0xffff0000u : 0u);
-          pe[j] = pk[j] & keep_e;
-          pi[j] = pk[j] & ~keep_e;
+          for (int j = 0; j < W / 2; ++j) {
+            const uint32_t lo_x = (cw >> (2 * j)) & 1u, hi_x = (cw >> (2 * j + 1)) & 1u;
+            const uint32_t keep_e = (lo_x ? 0x0000ffffu : 0u) | (hi_x ? 0xffff0000u : 0u);
+            pe[j] = pk[j] & keep_e;
+            pi[j] = pk[j] & ~keep_e;
+          }
+          ok = see_o();
+          if (!ok) break;
+          tmem_st_n<W / 2>(tP + (W / 2) * ch, pi);
+          tmem_st_n<W / 2>(tP + kBox / 2 + (W / 2) * ch, pe);
         }
-        ok = see_o();
-        if (!ok) break;
-        tmem_st_n<W / 2>(tP + (W / 2) * ch, pi);
-        tmem_st_n<W / 2>(tP + kBox / 2 + (W / 2) * ch, pe);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(p_full);
       }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(p_full);
-    }
-    // ---- epilogue: merge the two softmax states of each row, O / l -> bf16, lse
-    float* hm = hstat;          // [2][128] running maxima
-    float* hl = hstat + 256;    // [2][128] row sums
-    hm[ch * 128 + row] = m_ref;
-    hl[ch * 128 + row] = l;
-    named_bar_sync(1, 256);
-    const float m_other = hm[(ch ^ 1) * 128 + row], l_other = hl[(ch ^ 1) * 128 + row];
-    if (ok && n_ent > 0) ok = mbar_wait(o_ready, (n_ent - 1) & 1, p.status, 0x305);
-    tc_fence_after();
-    if (ok) {
-      constexpr int NC = D / 2;   // output columns written by this thread
-      __nv_bfloat16* orow = p.out + size_t(bh) * p.out_bh_stride + size_t(qi) * p.out_row_stride + ch * NC;
-      if (n_ent == 0) {
-        if (qi < p.T) {   // no unpadded key at all: NaN, as the softmax of an all -inf row gives in the PyTorch path
-          const uint32_t nan2 = 0x7FC07FC0u;
+      if (!ok) break;
+      // ---- epilogue of the item: merge the two softmax states of each row, O / l -> bf16, lse
+      // (the statistics are double buffered: every merge passes the h_full barrier, so a thread is at most one merge ahead of
+      // its row's other thread; the wait is an mbarrier so that it is bounded)
+      float* hm = hstat + (h_no & 1) * 512;   // [2][128] running maxima
+      float* hl = hm + 256;             // [2][128] row sums
+      hm[ch * 128 + row] = m_ref;
+      hl[ch * 128 + row] = l;
+      mbar_arrive(h_full);
+      ok = mbar_wait(h_full, h_no & 1, p.status, 0x307);
+      ++h_no;
+      if (!ok) break;
+      const float m_other = hm[(ch ^ 1) * 128 + row], l_other = hl[(ch ^ 1) * 128 + row];
+      if (n_ent > 0) ok = mbar_wait(o_ready, (g_it - 1) & 1, p.status, 0x305);
+      tc_fence_after();
+      if (ok) {
+        constexpr int NC = D / 2;   // output columns written by this thread
+        __nv_bfloat16* orow = p.out + size_t(bh) * p.out_bh_stride + size_t(qi) * p.out_row_stride + ch * NC;
+        if (n_ent == 0) {
+          if (qi < p.T) {   // no unpadded key at all: NaN, as the softmax of an all -inf row gives in the PyTorch path
+            const uint32_t nan2 = 0x7FC07FC0u;
 #pragma unroll
-          for (int d = 0; d < NC; d += 8) *reinterpret_cast<uint4*>(orow + d) = make_uint4(nan2, nan2, nan2, nan2);
-          if (ch == 0) p.lse[size_t(bh) * p.T + qi] = -INFINITY;
-        }
-      } else {
-        const float m_all = fmaxf(m_ref, m_other);                 // finite: an active tile has an unpadded key
-        const float w_self = ex2(m_ref - m_all), w_other = ex2(m_other - m_all);   // exp2(-inf) = 0 for an empty half
-        const float l_all = l * w_self + l_other * w_other;
-        // softmax: O / l.  square-root softmax: the accumulators hold sum exp2((s - m) / 2) v, so they are brought to the
-        // common maximum by the square roots of the weights and divided by sqrt(l)
-        const float inv = SQ ? rsqrtf(l_all) : 1.f / l_all;
-        const float f_self = (SQ ? ex2(0.5f * (m_ref - m_all)) : w_self) * inv;
-        const float f_other = (SQ ? ex2(0.5f * (m_other - m_all)) : w_other) * inv;
-        constexpr int CH = NC > 16 ? 16 : NC;   // columns per pass (keeps the register footprint small)
+            for (int d = 0; d < NC; d += 8) *reinterpret_cast<uint4*>(orow + d) = make_uint4(nan2, nan2, nan2, nan2);
+            if (ch == 0) p.lse[size_t(bh) * p.T + qi] = -INFINITY;
+          }
+        } else {
+          const float m_all = fmaxf(m_ref, m_other);                 // finite: an active tile has an unpadded key
+          const float w_self = ex2(m_ref - m_all), w_other = ex2(m_other - m_all);   // exp2(-inf) = 0 for an empty half
+          const float l_all = l * w_self + l_other * w_other;
+          // softmax: O / l.  square-root softmax: the accumulators hold sum exp2((s - m) / 2) v, so they are brought to the
+          // common maximum by the square roots of the weights and divided by sqrt(l)
+          const float inv = SQ ? rsqrtf(l_all) : 1.f / l_all;
+          const float f_self = (SQ ? ex2(0.5f * (m_ref - m_all)) : w_self) * inv;
+          const float f_other = (SQ ? ex2(0.5f * (m_other - m_all)) : w_other) * inv;
+          constexpr int CH = NC > 16 ? 16 : NC;   // columns per pass (keeps the register footprint small)
 #pragma unroll
-        for (int c0 = 0; c0 < NC; c0 += CH) {
-          uint32_t oa[CH], ob[CH];
-          tmem_ld_n<CH>(tO + ch * NC + c0, oa);                                                              // own accumulator
-          tmem_ld_n<CH>(tbase + lane_base + Cfg::kColO + Cfg::kOStride * (ch ^ 1) + ch * NC + c0, ob);       // the other half's
-          tmem_ld_wait();
+          for (int c0 = 0; c0 < NC; c0 += CH) {
+            uint32_t oa[CH], ob[CH];
+            tmem_ld_n<CH>(tO + ch * NC + c0, oa);                                                              // own accumulator
+            tmem_ld_n<CH>(tbase + lane_base + Cfg::kColO + Cfg::kOStride * (ch ^ 1) + ch * NC + c0, ob);       // the other half's
+            tmem_ld_wait();
+            if (qi < p.T) {
+              float v[CH];
+#pragma unroll
+              for (int j = 0; j < CH; ++j) {
+                // an empty half holds whatever was in TMEM: its weight is exactly 0, but 0 * NaN must not leak
+                const float a = w_self > 0.f ? __uint_as_float(oa[j]) * f_self : 0.f;
+                const float bb = w_other > 0.f ? __uint_as_float(ob[j]) * f_other : 0.f;
+                v[j] = a + bb;
+              }
+#pragma unroll
+              for (int j = 0; j < CH; j += 8)
+                *reinterpret_cast<uint4*>(orow + c0 + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                                                                      pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
+            }
+          }
           if (qi < p.T) {
-            float v[CH];
-#pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              // an empty half holds whatever was in TMEM: its weight is exactly 0, but 0 * NaN must not leak
-              const float a = w_self > 0.f ? __uint_as_float(oa[j]) * f_self : 0.f;
-              const float bb = w_other > 0.f ? __uint_as_float(ob[j]) * f_other : 0.f;
-              v[j] = a + bb;
-            }
-#pragma unroll
-            for (int j = 0; j < CH; j += 8)
-              *reinterpret_cast<uint4*>(orow + c0 + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
-                                                                    pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
+            if (ch == 0) p.lse[size_t(bh) * p.T + qi] = (m_all + log2f(l_all)) * kLn2;
           }
         }
-        if (qi < p.T) {
-          if (ch == 0) p.lse[size_t(bh) * p.T + qi] = (m_all + log2f(l_all)) * kLn2;
-        }
       }
+      if (!ok) break;
+      }
+      // O and the entry list of this slot are no longer read by this thread
+      tc_fence_before();
+      mbar_arrive(&item_free[slot]);
+      ++item_no;
     }
   }
   tc_fence_before();
@@ -661,7 +780,9 @@ bool tc_supported(int D, int dtype) { return dtype == MINTB_BF16 && (D == 16 || 
 
 static size_t rot_bytes(int B, int H, int T, int D) { return align256(size_t(B) * H * T * D * 2); }
 
-size_t tc_fwd_workspace_bytes(int B, int H, int T, int D, bool rope) { return rope ? 2 * rot_bytes(B, H, T, D) : 0; }
+// [rotated Q_self | rotated K_self] (with in-kernel RoPE only), then the work counter of the persistent forward kernel
+constexpr size_t kSchedBytes = 256;
+size_t tc_fwd_workspace_bytes(int B, int H, int T, int D, bool rope) { return (rope ? 2 * rot_bytes(B, H, T, D) : 0) + kSchedBytes; }
 
 template <int D, bool SQ>
 static int fwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s) {
@@ -678,12 +799,28 @@ static int fwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, SQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Cfg::kSmemBytes));
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   }
+  // the work counter follows the rotated copies in the workspace; it is zeroed in stream order before every launch
+  const bool rotated_here = a.rope && !a.qk_prerotated;
+  int* sched = reinterpret_cast<int*>(static_cast<char*>(a.workspace) + (rotated_here ? 2 * rot_bytes(a.B, a.H, a.T, a.D) : 0));
+  cudaError_t e = cudaMemsetAsync(sched, 0, kSchedBytes, a.stream);
+  if (e != cudaSuccess) { set_error("attention forward: clearing the work counter: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
+  const int NQ = (a.T + kBM - 1) / kBM;
+  const long long n_items = (long long)NQ * BH;
+  if (n_items > 0x7fff0000LL) { set_error("mintb_attn_fwd: %lld work items exceed the counter's range", n_items); return MINTB_EUNSUPPORTED; }
   FwdParams p{a.meta.bits, a.meta.kpad, a.meta.cls, static_cast<__nv_bfloat16*>(a.out), a.lse, a.H, a.T, a.meta.TW, a.meta.NT,
-              a.scale * kLog2e, a.dev_status, out_row_stride(a), out_bh_stride(a), a.skip_pad_queries ? 1 : 0};
-  dim3 grid((a.T + kBM - 1) / kBM, BH);
+              a.scale * kLog2e, a.dev_status, out_row_stride(a), out_bh_stride(a), a.skip_pad_queries ? 1 : 0,
+              sched, NQ, int(n_items)};
+  static int n_ctas = 0;   // two persistent CTAs per SM
+  if (n_ctas == 0) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    n_ctas = 2 * (sms > 0 ? sms : 148);
+  }
+  const unsigned grid = unsigned(n_items < n_ctas ? n_items : n_ctas);
   attn_fwd_tc_kernel<D, SQ><<<grid, kTcThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, p);
   count_launches(1);
-  cudaError_t e = cudaGetLastError();
+  e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("attention forward launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   return MINTB_OK;
 }
@@ -721,7 +858,7 @@ int launch_attn_fwd_tc(const AttnArgs& a) {
 // ------------------------------------------------------------------------------------------------ no-allocation forward
 // Scratch for mintb_attn_fwd_static: the rotated copies of Q_self and K_self that the forward pass with RoPE reads.
 // It is part of the loaded module, so every GPU that loads this library holds these bytes until the process exits.
-static __device__ __align__(256) unsigned char g_fwd_static_scratch[MINTB_STATIC_SCRATCH_BYTES];
+static __device__ __align__(256) unsigned char g_fwd_static_scratch[MINTB_STATIC_SCRATCH_BYTES + kSchedBytes];   // + the work counter
 
 // `g_fwd_static_scratch` names the array for DEVICE code only.  Host code must ask the runtime for the array's address on
 // the device that is current; the answer differs per device and is cached here after the first call on each device.
@@ -770,7 +907,7 @@ extern "C" int mintb_attn_fwd_static(const void* q_self, const void* k_self, con
     return MINTB_EINVAL;
   }
   const size_t need = tc_fwd_workspace_bytes(B, H, T, D, a.rope && !a.qk_prerotated);
-  if (need > size_t(MINTB_STATIC_SCRATCH_BYTES)) {
+  if (need > size_t(MINTB_STATIC_SCRATCH_BYTES) + kSchedBytes) {
     set_error("mintb_attn_fwd_static: B*H*T*D = %zu needs %zu bytes of scratch, the built-in array holds %zu; "
               "use mintb_attn_fwd with a caller-provided workspace",
               size_t(B) * H * T * D, need, size_t(MINTB_STATIC_SCRATCH_BYTES));
@@ -782,6 +919,6 @@ extern "C" int mintb_attn_fwd_static(const void* q_self, const void* k_self, con
   a.out = out;
   a.lse = lse;
   a.workspace = scratch;   // every byte the kernels read from it is written by the rotation pass of this same call
-  a.workspace_bytes = size_t(MINTB_STATIC_SCRATCH_BYTES);
+  a.workspace_bytes = size_t(MINTB_STATIC_SCRATCH_BYTES) + kSchedBytes;
   return launch_attn_fwd_tc(a);
 }

@@ -177,7 +177,7 @@ class _MultimerAttentionFn(torch.autograd.Function):
         ws_bytes = lib.mintb_attn_fwd_workspace_bytes(B, H, T, D, dt, flags)
         # With in-kernel RoPE the forward pass leaves rotated copies of Q_self and K_self at the start of its workspace.  When a
         # backward pass will follow, the workspace is sized for it and kept, so that pass starts from those copies.
-        keep_ws = bool(flags & L.FLAG_ROPE) and ws_bytes > 0 and any(ctx.needs_input_grad[:6])
+        keep_ws = bool(flags & L.FLAG_ROPE) and not (flags & L.FLAG_QK_PREROTATED) and any(ctx.needs_input_grad[:6])
         if keep_ws:
             ws_bytes = max(ws_bytes, lib.mintb_attn_bwd_workspace_bytes(B, H, T, D, dt, flags))
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q_s.device)
