@@ -119,9 +119,9 @@ MINTB_API int mintb_attn_fwd(const void* q_self, const void* k_self, const void*
  * memory at the point where they call it: code that runs while a CUDA graph is being captured, real-time or
  * fixed-memory-budget hosts that forbid cudaMalloc after start-up, and host languages whose bindings hand over
  * pre-pinned buffers only.  For them this variant of mintb_attn_fwd (bf16 tensor-core path) keeps the scratch it needs
- - the work counter and, with MINTB_FLAG_ROPE, the rotated copies of q_self and k_self - in an array of
- * MINTB_STATIC_SCRATCH_BYTES (plus the counter) inside the library image, so the caller passes inputs and outputs only and nothing is allocated or freed, here or in any
- * library routine it calls.  Limits and rules:
+ * (the work counter and, with MINTB_FLAG_ROPE, the rotated copies of q_self and k_self) in an array of
+ * MINTB_STATIC_SCRATCH_BYTES, plus the counter, inside the library image, so the caller passes inputs and outputs only
+ * and nothing is allocated or freed, here or in any library routine it calls.  Limits and rules:
  *   - 2 * B*H*T*D * 2 bytes must fit the array (B*H*T*D <= 8 Mi elements with rope); larger calls return
  *     MINTB_EWORKSPACE with a message and launch nothing.  Every GPU that loads the library holds the array until exit.
  *   - The first call on each device looks the array's device address up (with that device current); make that first
