@@ -365,35 +365,48 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   }
   int n_active = 0;
   for (int i = 0; i < nqt; ++i) n_active += tq[i] != 0;
+  n_active = __shfl_sync(0xffffffffu, n_active, 0);   // the same in every thread; the shuffle lets the compiler know it
+  // The MMA warps below run their loops with all lanes and let one elected lane issue: with warp-uniform control flow and
+  // operands the descriptors stay in uniform registers, which is what tcgen05.mma reads; issued from a divergent single-lane
+  // region every instruction first has to move its operands there.
+  auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, p.status, code));
+  };
+  const uint32_t tbase_u = __shfl_sync(0xffffffffu, tbase, 0);
   const int n_sub = 2 * n_active;   // 64-query halves, numbered u = 2 * tile + half; half u lives in buffer u % kNBuf
 
   if (warp == 1) {
     // ---------------------------------------------------------------- MMA stream A: S^T = K Q^T and dP^T = V dO^T
     // Issuing one tcgen05.mma costs its thread some 50 cycles whatever the tile size, and at small head sizes the
     // products are tiny, so the four families of products are issued by four warps in parallel (disjoint accumulators).
-    if (lane == 0 && n_active > 0) {
+    if (n_active > 0) {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_s = idesc_bf16(kBwdTile, kHalf, false, false);   // M = 128 keys, N = 64 queries
       constexpr uint32_t kHi = desc_hi32(8 * RB, swizzle_for_row_bytes(RB));
       constexpr uint32_t kLbo = desc_lbo32(16);
-      const uint32_t k_lo = desc_addr32(smem_u32(sK)) + kLbo, v_lo = desc_addr32(smem_u32(sV)) + kLbo;
-      const uint32_t q_lo = desc_addr32(smem_u32(sQ)) + kLbo;
+      const uint32_t k_lo = desc_addr32(__shfl_sync(0xffffffffu, smem_u32(sK), 0)) + kLbo;
+      const uint32_t v_lo = desc_addr32(__shfl_sync(0xffffffffu, smem_u32(sV), 0)) + kLbo;
+      const uint32_t q_lo = desc_addr32(__shfl_sync(0xffffffffu, smem_u32(sQ), 0)) + kLbo;
       constexpr uint32_t kTileU = Cfg::kTileBytes >> 4, kHalfU = (kHalf * RB) >> 4;
-      bool ok = mbar_wait(kv_full, 0, p.status, 0x501);
+      bool ok = wait_all(kv_full, 0, 0x501);
       Ring<kQStages> qr;     // query tile of the half being issued
       Ring<kNBuf> ib;        // buffer of the half being issued
       Ring<kNBuf> wb;        // buffer whose release is awaited next
       auto issue_sdp = [&](int u) -> bool {   // both products of half u
         const int h = u & 1;
-        if (h == 0 && !mbar_wait(&q_full[qr.pos], qr.phase, p.status, 0x502)) return false;
+        if (h == 0 && !wait_all(&q_full[qr.pos], qr.phase, 0x502)) return false;
         tc_fence_after();
         const uint32_t qs = q_lo + qr.pos * 2 * kTileU + h * kHalfU;
         const uint32_t dos = qs + kTileU;
-        const uint32_t col = tbase + kColBuf + ib.pos * 128;
+        const uint32_t col = tbase_u + kColBuf + ib.pos * 128;
+        if (leader) {
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_ss(col, make_desc(kHi, k_lo + 2 * k), make_desc(kHi, qs + 2 * k), idesc_s, k > 0);
+          for (int k = 0; k < D / 16; ++k) umma_ss(col, make_desc(kHi, k_lo + 2 * k), make_desc(kHi, qs + 2 * k), idesc_s, k > 0);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_ss(col + 64, make_desc(kHi, v_lo + 2 * k), make_desc(kHi, dos + 2 * k), idesc_s, k > 0);
-        umma_commit(&sdp_full[ib.pos]);
+          for (int k = 0; k < D / 16; ++k) umma_ss(col + 64, make_desc(kHi, v_lo + 2 * k), make_desc(kHi, dos + 2 * k), idesc_s, k > 0);
+          umma_commit(&sdp_full[ib.pos]);
+        }
+        __syncwarp();
         ib.advance();
         if (h == 1) qr.advance();
         return true;
@@ -401,7 +414,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       int issued = 0;
       for (; issued < kNBuf && issued < n_sub && ok; ++issued) ok = issue_sdp(issued);
       for (int u = 0; issued < n_sub && ok; ++u, ++issued) {
-        ok = mbar_wait(&buf_free[wb.pos], wb.phase, p.status, 0x505);   // dV and dK of half u have consumed P^T, dS^T
+        ok = wait_all(&buf_free[wb.pos], wb.phase, 0x505);   // dV and dK of half u have consumed P^T, dS^T
         if (!ok) break;
         wb.advance();
         ok = issue_sdp(issued);
@@ -409,51 +422,57 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     }
   } else if (warp == 2 || warp == 3) {
     // ---------------------------------------------------------------- MMA streams V and K: dV += P^T dO, dK += dS^T Q
-    if (lane == 0 && n_active > 0) {
+    if (n_active > 0) {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_acc = idesc_bf16(kBwdTile, D, false, true);      // A from TMEM, B rows of dO / Q (N = D contiguous)
       constexpr uint32_t kHi = desc_hi32(8 * RB, swizzle_for_row_bytes(RB));
       constexpr uint32_t kLbo = desc_lbo32(8 * RB);
       constexpr uint32_t kTileU = Cfg::kTileBytes >> 4, kHalfU = (kHalf * RB) >> 4, kStep = (16 * RB) >> 4;
-      const bool is_v = warp == 2;
+      const bool is_v = __shfl_sync(0xffffffffu, warp, 0) == 2;
       // dV reads P^T (over S^T) and dO; dK reads dS^T (over dP^T, 64 columns further) and Q
-      const uint32_t b_lo = desc_addr32(smem_u32(sQ)) + kLbo + (is_v ? kTileU : 0u);
-      const uint32_t a_col = tbase + kColBuf + (is_v ? 0u : 64u);
-      const uint32_t d_col = tbase + (is_v ? kColDV : kColDK);
+      const uint32_t b_lo = desc_addr32(__shfl_sync(0xffffffffu, smem_u32(sQ), 0)) + kLbo + (is_v ? kTileU : 0u);
+      const uint32_t a_col = tbase_u + kColBuf + (is_v ? 0u : 64u);
+      const uint32_t d_col = tbase_u + (is_v ? kColDV : kColDK);
       bool ok = true;
       Ring<kQStages> qr;
       Ring<kNBuf> br;
       for (int it = 0; it < n_active && ok; ++it) {
-        ok = mbar_wait(&q_full[qr.pos], qr.phase, p.status, 0x511);
+        ok = wait_all(&q_full[qr.pos], qr.phase, 0x511);
         for (int h = 0; h < 2 && ok; ++h) {
-          ok = mbar_wait(&pds_full[br.pos], br.phase, p.status, 0x512);
+          ok = wait_all(&pds_full[br.pos], br.phase, 0x512);
           if (!ok) break;
           tc_fence_after();
           const uint32_t rows = b_lo + qr.pos * 2 * kTileU + h * kHalfU;
+          if (leader) {
 #pragma unroll
-          for (int k = 0; k < kHalf / 16; ++k)
-            umma_ts(d_col, a_col + br.pos * 128 + k * 16, make_desc(kHi, rows + k * kStep), idesc_acc, it > 0 || h > 0 || k > 0);
-          umma_commit(&buf_free[br.pos]);
+            for (int k = 0; k < kHalf / 16; ++k)
+              umma_ts(d_col, a_col + br.pos * 128 + k * 16, make_desc(kHi, rows + k * kStep), idesc_acc, it > 0 || h > 0 || k > 0);
+            umma_commit(&buf_free[br.pos]);
+          }
+          __syncwarp();
           br.advance();
         }
-        if (ok) umma_commit(&q_empty[qr.pos]);
+        if (ok && leader) umma_commit(&q_empty[qr.pos]);
+        __syncwarp();
         qr.advance();
       }
-      if (ok) umma_commit(acc_full);
+      if (ok && leader) umma_commit(acc_full);
     }
   } else if (warp == 0) {
     // ---------------------------------------------------------------- TMA loads and MMA stream Q: dQ tile = dS K
     // One thread does both: it loads K, V and the first query tiles, then per tile issues the dQ product and
     // refills the stage that tile has just released with the tile kQStages steps ahead.
-    if (lane == 0 && n_active > 0) {
+    if (n_active > 0) {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_dq = idesc_bf16(kBwdTile, D, true, true);        // A = dS (queries contiguous), B = K (D contiguous)
       constexpr uint32_t kHiA = desc_hi32(8 * 128, kSw128), kHiB = desc_hi32(8 * RB, swizzle_for_row_bytes(RB));
-      const uint32_t ds_lo = desc_addr32(smem_u32(sDS)) + desc_lbo32(Cfg::kDsBlock);
-      const uint32_t kb_lo = desc_addr32(smem_u32(sK)) + desc_lbo32(8 * RB);
+      const uint32_t ds_lo = desc_addr32(__shfl_sync(0xffffffffu, smem_u32(sDS), 0)) + desc_lbo32(Cfg::kDsBlock);
+      const uint32_t kb_lo = desc_addr32(__shfl_sync(0xffffffffu, smem_u32(sK), 0)) + desc_lbo32(8 * RB);
       constexpr uint32_t kDsU = Cfg::kDsBytes >> 4, kAStep = (16 * 128) >> 4, kBStep = (16 * RB) >> 4;
-      prefetch_tensormap(mq); prefetch_tensormap(&map_do);      // (K and V were requested before the query-tile scan)
-      int next_q = 0;        // next query tile index to look at
-      Ring<kQStages> lr;     // stage the next load goes to
-      auto load_next = [&]() {   // issue the loads of the next active query tile
+      if (leader) { prefetch_tensormap(mq); prefetch_tensormap(&map_do); }      // (K and V were requested before the query-tile scan)
+      int next_q = 0;        // next query tile index to look at (the elected lane's copy is the one that counts)
+      Ring<kQStages> lr;     // stage the next load goes to (likewise)
+      auto load_next = [&]() {   // issue the loads of the next active query tile; called by the elected lane only
         while (next_q < nqt && tq[next_q] == 0) ++next_q;
         if (next_q >= nqt) return;
         unsigned char* dst = sQ + size_t(lr.pos) * 2 * Cfg::kTileBytes;
@@ -466,26 +485,33 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         ++next_q;
         lr.advance();
       };
-      for (int s = 0; s < kQStages; ++s) load_next();
-      bool ok = mbar_wait(kv_full, 0, p.status, 0x521);
+      if (leader) {
+        for (int s = 0; s < kQStages; ++s) load_next();
+      }
+      __syncwarp();
+      bool ok = wait_all(kv_full, 0, 0x521);
       Ring<kNBuf> br;        // buffers of the two halves of the tile
       Ring<kQStages> er;     // stage released by the tile
       for (int it = 0; it < n_active && ok; ++it) {
-        ok = mbar_wait(&pds_full[br.pos], br.phase, p.status, 0x522);
+        ok = wait_all(&pds_full[br.pos], br.phase, 0x522);
         br.advance();
-        if (ok) ok = mbar_wait(&pds_full[br.pos], br.phase, p.status, 0x523);
+        if (ok) ok = wait_all(&pds_full[br.pos], br.phase, 0x523);
         br.advance();
-        if (ok) ok = mbar_wait(&dq_empty[it % kNDq], ((it / kNDq) & 1) ^ 1, p.status, 0x524);   // buffer drained kNDq tiles ago
+        if (ok) ok = wait_all(&dq_empty[it % kNDq], ((it / kNDq) & 1) ^ 1, 0x524);   // buffer drained kNDq tiles ago
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_lo = ds_lo + uint32_t(it % kNDq) * kDsU;
+        if (leader) {
 #pragma unroll
-        for (int k = 0; k < kBwdTile / 16; ++k)
-          umma_ss(tbase + kColDQ + (it % kNDq) * kAcc, make_desc(kHiA, a_lo + k * kAStep), make_desc(kHiB, kb_lo + k * kBStep), idesc_dq, k > 0);
-        umma_commit(&dq_full[it % kNDq]);
+          for (int k = 0; k < kBwdTile / 16; ++k)
+            umma_ss(tbase_u + kColDQ + (it % kNDq) * kAcc, make_desc(kHiA, a_lo + k * kAStep), make_desc(kHiB, kb_lo + k * kBStep), idesc_dq, k > 0);
+          umma_commit(&dq_full[it % kNDq]);
+        }
+        __syncwarp();
         if (it + kQStages < n_active) {   // this tile's stage is released by its dV and dK streams
-          ok = mbar_wait(&q_empty[er.pos], er.phase, p.status, 0x525);
-          if (ok) load_next();
+          ok = wait_all(&q_empty[er.pos], er.phase, 0x525);
+          if (ok && leader) load_next();
+          __syncwarp();
         }
         er.advance();
       }
