@@ -79,6 +79,11 @@ MINTB_API unsigned long long mintb_kernel_launches(void);
  * spins on.  trail (device int[2], may be NULL) receives {2, 1}: the wait gave up, and TMEM was released after it. */
 MINTB_API int mintb_selftest_wait(unsigned long long limit_ns, int* dev_status, int* trail, void* stream);
 
+/* The persistent kernels (attention forward, the GEMMs) draw their work units from counters in the library image; the last
+ * CTA of a launch clears the launch's counter again.  After a launch gave up on a bounded wait (a device status was raised)
+ * some CTAs may not have left their counter: call this before launching again.  It synchronises the device. */
+MINTB_API int mintb_reset_work_counters(void);
+
 /* ---------------------------------------------------------------------------------------------------
  * Mask metadata.  Replaces the (B,T,T) bool tensor the reference builds every step (esm2.py:89) and
  * re-reads per head (modules.py:129-141; multi_pathway_attention.py:101-128): one bit per (query,key)
@@ -105,9 +110,7 @@ MINTB_API int mintb_rope_tables(const float* inv_freq, float* cos_tab, float* si
  * projections and scale = D^-0.5; without it the caller has already scaled and rotated
  * (multi_pathway_attention.py:199-202) — pass scale = 1.
  * lse [B][H][T] receives log(sum_j exp(logit_ij)) for the backward pass.
- * The workspace is never empty on the bf16 tensor-core path: the persistent kernel draws its (query tile, batch, head)
- * work items from a counter at the end of it, which each call clears in stream order; with MINTB_FLAG_ROPE the rotated
- * copies of q_self and k_self come first.  Calls that overlap on the GPU need separate workspaces.
+ * The workspace holds the rotated copies of q_self and k_self (MINTB_FLAG_ROPE only; otherwise none is needed).
  */
 MINTB_API size_t mintb_attn_fwd_workspace_bytes(int B, int H, int T, int D, int dtype, unsigned flags);
 MINTB_API int mintb_attn_fwd(const void* q_self, const void* k_self, const void* v_self, const void* q_cross,
@@ -119,9 +122,9 @@ MINTB_API int mintb_attn_fwd(const void* q_self, const void* k_self, const void*
  * memory at the point where they call it: code that runs while a CUDA graph is being captured, real-time or
  * fixed-memory-budget hosts that forbid cudaMalloc after start-up, and host languages whose bindings hand over
  * pre-pinned buffers only.  For them this variant of mintb_attn_fwd (bf16 tensor-core path) keeps the scratch it needs
- * (the work counter and, with MINTB_FLAG_ROPE, the rotated copies of q_self and k_self) in an array of
- * MINTB_STATIC_SCRATCH_BYTES, plus the counter, inside the library image, so the caller passes inputs and outputs only
- * and nothing is allocated or freed, here or in any library routine it calls.  Limits and rules:
+ * with MINTB_FLAG_ROPE - the rotated copies of q_self and k_self - in an array of MINTB_STATIC_SCRATCH_BYTES inside the
+ * library image, so the caller passes inputs and outputs only and nothing is allocated or freed, here or in any
+ * library routine it calls.  Limits and rules:
  *   - 2 * B*H*T*D * 2 bytes must fit the array (B*H*T*D <= 8 Mi elements with rope); larger calls return
  *     MINTB_EWORKSPACE with a message and launch nothing.  Every GPU that loads the library holds the array until exit.
  *   - The first call on each device looks the array's device address up (with that device current); make that first

@@ -28,6 +28,7 @@ PROTOTYPES = {
     "mintb_mask_meta_from_chain_ids": (c_int, [_P, _P, _P, c_int, c_int, _P]),
     "mintb_mask_meta_from_mask": (c_int, [_P, _P, _P, c_int, c_int, _P]),
     "mintb_rope_tables": (c_int, [_P, _P, _P, c_int, c_int, _P]),
+    "mintb_reset_work_counters": (c_int, []),
     "mintb_attn_fwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_uint]),
     "mintb_attn_fwd": (c_int, [_P] * 6 + [_P, _P, _P, _P, _P, _P, c_size_t, c_int, c_int, c_int, c_int, c_int, c_uint,
                                c_float, _P, _P]),

@@ -1,5 +1,6 @@
 // extern "C" entry points of libmintb: host-side validation and dispatch.  See include/mintb.h.
 #include <atomic>
+#include <mutex>
 #include <cstdarg>
 #include <cstdio>
 
@@ -17,6 +18,38 @@ void set_error(const char* fmt, ...) {
 }
 
 static std::atomic<unsigned long long> g_launches{0};
+// the pool of work counters (see common.cuh); zero-initialised with the module, each pair cleared again by its last user
+static __device__ int g_tile_counters[2 * kTileCounterSlots];
+
+int next_tile_counter(int** out) {
+  constexpr int kMaxDevices = 64;
+  static std::atomic<unsigned> next{0};
+  static std::mutex mu;
+  static int* base[kMaxDevices] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error("work counters: cudaGetDevice failed or device index %d is out of range", dev);
+    return MINTB_ECUDA;
+  }
+  int* b = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (base[dev] == nullptr) {   // the symbol's address differs per device; look it up once with that device current
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_tile_counters);
+      if (e != cudaSuccess || ptr == nullptr) {
+        set_error("work counters: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        return MINTB_ECUDA;
+      }
+      base[dev] = static_cast<int*>(ptr);
+    }
+    b = base[dev];
+  }
+  *out = b + 2 * (next.fetch_add(1, std::memory_order_relaxed) % kTileCounterSlots);
+  return MINTB_OK;
+}
+
 void count_launches(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
 
 static int cuda_fail(cudaError_t e, const char* what) {
@@ -55,6 +88,19 @@ static bool use_tc(int D, int dtype, unsigned flags) {
 using namespace mintb;
 
 extern "C" {
+
+// Clears every work counter of the current device.  Needed only after a kernel gave up on a bounded wait (a device status
+// was raised): its CTAs may not all have left their counter.  Synchronises the device.
+int mintb_reset_work_counters(void) {
+  int* first = nullptr;
+  int rc = next_tile_counter(&first);
+  if (rc != MINTB_OK) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  int* base = nullptr;
+  if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_tile_counters);
+  if (e == cudaSuccess) e = cudaMemset(base, 0, sizeof(int) * 2 * kTileCounterSlots);
+  return e == cudaSuccess ? MINTB_OK : cuda_fail(e, "mintb_reset_work_counters");
+}
 
 int mintb_version(void) { return 100; }
 

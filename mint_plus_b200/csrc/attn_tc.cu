@@ -159,7 +159,7 @@ struct FwdParams {
   int* status;
   size_t out_row_stride, out_bh_stride;   // elements between consecutive queries / (batch, head) pairs of `out`
   int skip_pad_queries;                   // leave out query tiles that hold only padded positions
-  int* sched;                             // work counter in global memory, zero when the kernel starts
+  int* sched;                             // work counter pair of this launch (common.cuh)
   int NQ, n_items;                        // query tiles per (batch, head); items = NQ * B * H, item = bh * NQ + qt
 };
 
@@ -296,7 +296,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     for (;;) {
       const int slot = item_no & 1;
       int item = 0;
-      if (lane == 0) item = atomicAdd(p.sched, 1);
+      if (lane == 0) item = item_no == 0 ? int(blockIdx.x) : int(gridDim.x) + atomicAdd(p.sched, 1);   // the first item is the CTA's own number
       item = __shfl_sync(0xffffffffu, item, 0);
       const bool have = item < p.n_items;
       if (item_no >= 2) {   // the slot was last used by item item_no - 2: the other roles must have left it
@@ -406,6 +406,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
       }
       ++item_no;
     }
+    if (lane == 0) leave_tile_counter(p.sched, int(gridDim.x));   // (after this CTA's last draw, whichever way the loop ended)
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     // The whole warp runs this loop and one elected lane issues: with warp-uniform control flow and operands the compiler
@@ -780,9 +781,8 @@ bool tc_supported(int D, int dtype) { return dtype == MINTB_BF16 && (D == 16 || 
 
 static size_t rot_bytes(int B, int H, int T, int D) { return align256(size_t(B) * H * T * D * 2); }
 
-// [rotated Q_self | rotated K_self] (with in-kernel RoPE only), then the work counter of the persistent forward kernel
-constexpr size_t kSchedBytes = 256;
-size_t tc_fwd_workspace_bytes(int B, int H, int T, int D, bool rope) { return (rope ? 2 * rot_bytes(B, H, T, D) : 0) + kSchedBytes; }
+// [rotated Q_self | rotated K_self] (with in-kernel RoPE only)
+size_t tc_fwd_workspace_bytes(int B, int H, int T, int D, bool rope) { return rope ? 2 * rot_bytes(B, H, T, D) : 0; }
 
 template <int D, bool SQ>
 static int fwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s) {
@@ -799,11 +799,8 @@ static int fwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, SQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Cfg::kSmemBytes));
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   }
-  // the work counter follows the rotated copies in the workspace; it is zeroed in stream order before every launch
-  const bool rotated_here = a.rope && !a.qk_prerotated;
-  int* sched = reinterpret_cast<int*>(static_cast<char*>(a.workspace) + (rotated_here ? 2 * rot_bytes(a.B, a.H, a.T, a.D) : 0));
-  cudaError_t e = cudaMemsetAsync(sched, 0, kSchedBytes, a.stream);
-  if (e != cudaSuccess) { set_error("attention forward: clearing the work counter: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
+  int* sched = nullptr;   // the launch's work counter pair (common.cuh)
+  if (int rc = next_tile_counter(&sched); rc != MINTB_OK) return rc;
   const int NQ = (a.T + kBM - 1) / kBM;
   const long long n_items = (long long)NQ * BH;
   if (n_items > 0x7fff0000LL) { set_error("mintb_attn_fwd: %lld work items exceed the counter's range", n_items); return MINTB_EUNSUPPORTED; }
@@ -820,7 +817,7 @@ static int fwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s) {
   const unsigned grid = unsigned(n_items < n_ctas ? n_items : n_ctas);
   attn_fwd_tc_kernel<D, SQ><<<grid, kTcThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, p);
   count_launches(1);
-  e = cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("attention forward launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   return MINTB_OK;
 }
@@ -858,7 +855,7 @@ int launch_attn_fwd_tc(const AttnArgs& a) {
 // ------------------------------------------------------------------------------------------------ no-allocation forward
 // Scratch for mintb_attn_fwd_static: the rotated copies of Q_self and K_self that the forward pass with RoPE reads.
 // It is part of the loaded module, so every GPU that loads this library holds these bytes until the process exits.
-static __device__ __align__(256) unsigned char g_fwd_static_scratch[MINTB_STATIC_SCRATCH_BYTES + kSchedBytes];   // + the work counter
+static __device__ __align__(256) unsigned char g_fwd_static_scratch[MINTB_STATIC_SCRATCH_BYTES];
 
 // `g_fwd_static_scratch` names the array for DEVICE code only.  Host code must ask the runtime for the array's address on
 // the device that is current; the answer differs per device and is cached here after the first call on each device.
@@ -907,7 +904,7 @@ extern "C" int mintb_attn_fwd_static(const void* q_self, const void* k_self, con
     return MINTB_EINVAL;
   }
   const size_t need = tc_fwd_workspace_bytes(B, H, T, D, a.rope && !a.qk_prerotated);
-  if (need > size_t(MINTB_STATIC_SCRATCH_BYTES) + kSchedBytes) {
+  if (need > size_t(MINTB_STATIC_SCRATCH_BYTES)) {
     set_error("mintb_attn_fwd_static: B*H*T*D = %zu needs %zu bytes of scratch, the built-in array holds %zu; "
               "use mintb_attn_fwd with a caller-provided workspace",
               size_t(B) * H * T * D, need, size_t(MINTB_STATIC_SCRATCH_BYTES));
@@ -919,6 +916,6 @@ extern "C" int mintb_attn_fwd_static(const void* q_self, const void* k_self, con
   a.out = out;
   a.lse = lse;
   a.workspace = scratch;   // every byte the kernels read from it is written by the rotation pass of this same call
-  a.workspace_bytes = size_t(MINTB_STATIC_SCRATCH_BYTES) + kSchedBytes;
+  a.workspace_bytes = size_t(MINTB_STATIC_SCRATCH_BYTES);
   return launch_attn_fwd_tc(a);
 }

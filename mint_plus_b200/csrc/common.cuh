@@ -97,6 +97,14 @@ inline size_t grad_h_stride(const AttnArgs& a) { return a.grad_rowmajor ? size_t
 void set_error(const char* fmt, ...);
 void count_launches(int n);  // process-wide tally of kernels launched by this library
 
+// Work counters of the persistent kernels.  A launch takes the next {next unit, CTAs that have left} pair of a pool in the
+// library image (zero when it gets it); its CTAs draw work units from the first word, and the last CTA to leave clears the
+// pair again, so no launch needs a clearing pass.  Launches that can run at the same time hold different pairs as long as
+// fewer than kTileCounterSlots launches lie between them; launches on one stream run one after the other and may share.
+constexpr int kTileCounterSlots = 4096;
+int next_tile_counter(int** out);      // MINTB_OK or an error code
+// (device side, in ptx.cuh: leave_tile_counter)
+
 // api.cu
 int check_attn_args(AttnArgs& a, const char* who, const void* q_s, const void* k_s, const void* v_s, const void* q_c,
                     const void* k_c, const void* v_c, const void* meta, const float* rope_cos, const float* rope_sin,

@@ -40,6 +40,7 @@ struct BwdGemmParams {
   int splits;            // aligned cuts of the reduction (wgrad); 1 for dgrad
   float alpha;
   int* status;
+  int* sched;            // work counter pair of this launch (common.cuh)
 };
 
 // 2-D tiled reduction shared memory -> global (fp32 add); rows / columns outside the tensor are dropped.
@@ -55,24 +56,24 @@ __device__ __forceinline__ uint32_t bwd_pack_bf16x2(float lo, float hi) {
   return r;
 }
 
-// Work units of one CTA: unit u = blockIdx.x + i gridDim.x; split = u / n_tiles (so the units of one split run together),
-// tile = u % n_tiles with the column index fastest.
-struct UnitIter {
-  int u, stride, n_units, n_tiles, n_slabs, per_split;
-  __device__ UnitIter(int n_tiles_, int n_slabs_, int splits) {
-    u = blockIdx.x; stride = gridDim.x; n_tiles = n_tiles_; n_slabs = n_slabs_;
+// Work unit u: split = u / n_tiles (so the units of one split run together), tile = u % n_tiles with the column index
+// fastest.  The loading warp draws unit numbers from the launch's work counter (the first one is the CTA's own number) and
+// hands them to the other roles through a small ring, so a CTA that shares its SM with another kernel for a while simply
+// takes fewer units instead of holding the whole grid up.
+constexpr int kBUnitRing = 4;
+struct UnitMap {
+  int n_units, n_tiles, n_slabs, per_split;
+  __device__ UnitMap(int n_tiles_, int n_slabs_, int splits) {
+    n_tiles = n_tiles_; n_slabs = n_slabs_;
     per_split = (n_slabs + splits - 1) / splits;
     n_units = n_tiles * splits;
   }
-  __device__ bool next(int& tile, int& kb0, int& kb1) {
-    while (u < n_units) {
-      tile = u % n_tiles;
-      kb0 = (u / n_tiles) * per_split;
-      kb1 = kb0 + per_split < n_slabs ? kb0 + per_split : n_slabs;
-      u += stride;
-      if (kb0 < kb1) return true;        // a split past the end of the reduction holds nothing
-    }
-    return false;
+  // false for a unit past the end of the reduction (it holds nothing)
+  __device__ bool decode(int u, int& tile, int& kb0, int& kb1) const {
+    tile = u % n_tiles;
+    kb0 = (u / n_tiles) * per_split;
+    kb1 = kb0 + per_split < n_slabs ? kb0 + per_split : n_slabs;
+    return kb0 < kb1;
   }
 };
 
@@ -89,7 +90,10 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
   uint64_t* empty = full + kBStages;                     // [kBStages]
   uint64_t* acc_full = empty + kBStages;                 // [2]
   uint64_t* acc_empty = acc_full + 2;                    // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* ur_full = acc_empty + 2;                     // [kBUnitRing] loading warp -> MMA, epilogue: a unit number is in the ring
+  uint64_t* ur_empty = ur_full + kBUnitRing;             // [kBUnitRing] MMA thread and one lane per epilogue warp have read it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ur_empty + kBUnitRing);
+  int* unit_ring = reinterpret_cast<int*>(tmem_slot + 2);   // [kBUnitRing] unit number, negative = no more units
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int tiles_n = (p.cols + kBN - 1) / kBN;
@@ -102,6 +106,7 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
   if (tid == 0) {
     for (int s = 0; s < kBStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], kBEpiThreads); }
+    for (int s = 0; s < kBUnitRing; ++s) { mbar_init(&ur_full[s], 1); mbar_init(&ur_empty[s], 1 + kBEpiWarps); }
     fence_mbar_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
@@ -114,11 +119,24 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
     if (lane == 0) {
       prefetch_tensormap(&map_a1);
       prefetch_tensormap(&map_b1);
-      uint32_t stage = 0, phase = 0;
-      bool ok = true;
-      UnitIter it(n_tiles, n_slabs, p.splits);
-      int tile, kb0, kb1;
-      while (ok && it.next(tile, kb0, kb1)) {
+      uint32_t stage = 0, phase = 0, n_drawn = 0;
+      bool ok = true, first = true;
+      const UnitMap um(n_tiles, n_slabs, p.splits);
+      int tile = 0, kb0 = 0, kb1 = 0;
+      for (;;) {
+        const uint32_t slot = n_drawn % kBUnitRing;
+        ok = mbar_wait(&ur_empty[slot], ((n_drawn / kBUnitRing) & 1) ^ 1, p.status, 0x805);
+        if (!ok) break;
+        int u;
+        do {   // the next unit that holds something
+          u = first ? int(blockIdx.x) : int(gridDim.x) + atomicAdd(p.sched, 1);
+          first = false;
+        } while (u < um.n_units && !um.decode(u, tile, kb0, kb1));
+        if (u >= um.n_units) u = -1;
+        unit_ring[slot] = u;
+        mbar_arrive(&ur_full[slot]);
+        ++n_drawn;
+        if (u < 0) break;
         const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * kBN;
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty[stage], phase ^ 1, p.status, 0x801);
@@ -140,7 +158,9 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
             tma_load_2d(b + blk * blk_bytes, mb, &full[stage], n0 + blk * epb, kk);
           if (++stage == kBStages) { stage = 0; phase ^= 1; }
         }
+        if (!ok) break;
       }
+      leave_tile_counter(p.sched, int(gridDim.x));
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -148,11 +168,19 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
       const uint32_t lo0 = desc_addr32(smem_u32(smem));
       const uint32_t lbo_k = desc_lbo32(16), lbo_mn = desc_lbo32(blk_bytes);
       const uint32_t step_mn = p.f8 ? (32u * 128u) >> 4 : (16u * 128u) >> 4;   // one MMA consumes 32 (8-bit) or 16 reduction rows
-      uint32_t stage = 0, phase = 0, ab = 0, ab_phase = 0;
+      uint32_t stage = 0, phase = 0, ab = 0, ab_phase = 0, n_seen = 0;
       bool ok = true;
-      UnitIter it(n_tiles, n_slabs, p.splits);
+      const UnitMap um(n_tiles, n_slabs, p.splits);
       int tile, kb0, kb1;
-      while (ok && it.next(tile, kb0, kb1)) {
+      for (;;) {
+        const uint32_t slot = n_seen % kBUnitRing;
+        ok = mbar_wait(&ur_full[slot], (n_seen / kBUnitRing) & 1, p.status, 0x806);
+        if (!ok) break;
+        const int u = unit_ring[slot];
+        mbar_arrive(&ur_empty[slot]);
+        ++n_seen;
+        if (u < 0) break;
+        um.decode(u, tile, kb0, kb1);
         ok = mbar_wait(&acc_empty[ab], ab_phase ^ 1, p.status, 0x802);
         if (!ok) break;
         tc_fence_after();
@@ -172,7 +200,8 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
           umma_commit(&empty[stage]);
           if (++stage == kBStages) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(&acc_full[ab]);
+        if (!ok) break;
+        umma_commit(&acc_full[ab]);
         if (++ab == 2) { ab = 0; ab_phase ^= 1; }
       }
     }
@@ -182,11 +211,20 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
     const int chalf = (warp - 2) / 4;
     unsigned char* my_out = s_out + size_t(warp - 2) * kBOutStageBytes;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    uint32_t ab = 0, ab_phase = 0;
+    uint32_t ab = 0, ab_phase = 0, n_seen = 0;
     bool ok = true;
-    UnitIter it(n_tiles, n_slabs, p.splits);
+    const UnitMap um(n_tiles, n_slabs, p.splits);
     int tile, kb0, kb1;
-    while (ok && it.next(tile, kb0, kb1)) {
+    for (;;) {
+      const uint32_t slot = n_seen % kBUnitRing;
+      ok = __all_sync(0xffffffffu, mbar_wait(&ur_full[slot], (n_seen / kBUnitRing) & 1, p.status, 0x807));
+      if (!ok) break;
+      const int u = unit_ring[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ur_empty[slot]);
+      ++n_seen;
+      if (u < 0) break;
+      um.decode(u, tile, kb0, kb1);
       const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * kBN;
       ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[ab], ab_phase, p.status, 0x804));
       if (!ok) break;
@@ -312,9 +350,11 @@ static bool is_f8(int dtype) { return dtype == MINTB_E4M3 || dtype == MINTB_E5M2
 
 template <int MODE>
 static int launch_bwd_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap& b2,
-                           const CUtensorMap& out, const BwdGemmParams& p, int grid, cudaStream_t stream) {
+                           const CUtensorMap& out, const BwdGemmParams& p_in, int grid, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(gemm_bwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kBwdGemmSmem));
   if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
+  BwdGemmParams p = p_in;
+  if (int rc = next_tile_counter(&p.sched); rc != MINTB_OK) return rc;
   gemm_bwd_kernel<MODE><<<grid, kBThreads, kBwdGemmSmem, stream>>>(a1, b1, a2, b2, out, p);
   count_launches(1);
   e = cudaGetLastError();

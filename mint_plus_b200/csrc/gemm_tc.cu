@@ -22,6 +22,7 @@ constexpr int kGEpiWarps = 8, kGEpiThreads = 32 * kGEpiWarps, kGThreads = 64 + k
 constexpr int kSlabBytes = 128;                       // bytes of K per stage and row (64 bf16 or 128 e4m3)
 constexpr int kABytes = kGM * kSlabBytes, kBBytes = kGN * kSlabBytes, kGStageBytes = kABytes + kBBytes;
 constexpr int kGStageOutBytes = 32 * 64;   // one epilogue warp's staging of 32 rows x 32 bf16 columns for a bulk store
+constexpr int kGTileRing = 4;   // tile numbers travel from the loading warp to the other roles through a ring this deep
 constexpr size_t kGemmSmem = 1024 + size_t(kGStages) * kGStageBytes + kGEpiWarps * kGStageOutBytes + 256 + 2 * kGN * sizeof(float);
 
 enum GemmEpilogue : int { kEpiBias = 0, kEpiBiasGelu = 1, kEpiHeadMajor = 2 };
@@ -49,6 +50,7 @@ struct GemmParams {
   int use_bulk_store;          // bf16 row-major outputs leave through shared memory and bulk tensor stores
   int use_bulk_f8;        // the e4m3 result leaves as bulk tensor stores too (32 x 32-byte boxes)
   int* status;
+  int* sched;                  // work counter pair of this launch (common.cuh)
 };
 
 // erf-GELU x/2 (1 + erf(x / sqrt 2)) with erf from the rational-exponential form 1 - (a1 t + ... + a5 t^5) exp(-z^2),
@@ -91,8 +93,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* empty = full + kGStages;                     // [kGStages]
   uint64_t* acc_full = empty + kGStages;                 // [2]
   uint64_t* acc_empty = acc_full + 2;                    // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-  float* s_bias = reinterpret_cast<float*>(tmem_slot + 2);   // [2][kGN] bias of the tile in flight (double buffered)
+  uint64_t* tr_full = acc_empty + 2;                     // [kGTileRing] loading warp -> MMA, epilogue: a tile number is in the ring
+  uint64_t* tr_empty = tr_full + kGTileRing;             // [kGTileRing] MMA thread and one lane per epilogue warp have read it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tr_empty + kGTileRing);
+  int* tile_ring = reinterpret_cast<int*>(tmem_slot + 2);    // [kGTileRing] tile number, negative = no more tiles
+  float* s_bias = reinterpret_cast<float*>(tile_ring + kGTileRing);   // [2][kGN] bias of the tile in flight (double buffered)
+  static_assert((2 * kGStages + 4 + 2 * kGTileRing) * 8 + 8 + kGTileRing * 4 <= 256, "barrier area of the shared-memory tail");
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int tiles_m = (p.M + kGM - 1) / kGM, tiles_n = (p.N + kGN - 1) / kGN;
@@ -103,6 +109,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (tid == 0) {
     for (int s = 0; s < kGStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], kGEpiThreads); }
+    for (int s = 0; s < kGTileRing; ++s) { mbar_init(&tr_full[s], 1); mbar_init(&tr_empty[s], 1 + kGEpiWarps); }
     fence_mbar_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
@@ -115,9 +122,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       prefetch_tensormap(&map_a);
       prefetch_tensormap(&map_b);
-      uint32_t stage = 0, phase = 0;
+      // Tiles are drawn from the launch's work counter (the first one is the CTA's own number), so a CTA that shares its SM
+      // with another kernel for a while - a collective of the gradient exchange, say - simply takes fewer tiles instead of
+      // holding the whole grid up.  The tile numbers reach the other roles through a small ring.
+      uint32_t stage = 0, phase = 0, n_drawn = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      for (;;) {
+        const uint32_t slot = n_drawn % kGTileRing;
+        ok = mbar_wait(&tr_empty[slot], ((n_drawn / kGTileRing) & 1) ^ 1, p.status, 0x705);
+        if (!ok) break;
+        int t = n_drawn == 0 ? int(blockIdx.x) : int(gridDim.x) + atomicAdd(p.sched, 1);
+        if (t >= n_tiles) t = -1;
+        tile_ring[slot] = t;
+        mbar_arrive(&tr_full[slot]);
+        ++n_drawn;
+        if (t < 0) break;
         const int m0 = (t / tiles_n) * kGM, n0 = (t % tiles_n) * kGN;
         for (int kb = 0; kb < n_slabs; ++kb) {
           ok = mbar_wait(&empty[stage], phase ^ 1, p.status, 0x701);
@@ -128,7 +147,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tma_load_2d(a + kABytes, &map_b, &full[stage], kb * elems_per_slab, n0);
           if (++stage == kGStages) { stage = 0; phase ^= 1; }
         }
+        if (!ok) break;
       }
+      leave_tile_counter(p.sched, int(gridDim.x));
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -136,9 +157,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t idesc = f8 ? idesc_e4m3(kGM, kGN) : idesc_bf16(kGM, kGN, false, false);
       constexpr uint32_t kHi = desc_hi32(8 * kSlabBytes, kSw128);
       const uint32_t a_lo0 = desc_addr32(smem_u32(smem)) + desc_lbo32(16);
-      uint32_t stage = 0, phase = 0, ab = 0, ab_phase = 0;
+      uint32_t stage = 0, phase = 0, ab = 0, ab_phase = 0, n_seen = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      for (;;) {
+        const uint32_t slot = n_seen % kGTileRing;
+        ok = mbar_wait(&tr_full[slot], (n_seen / kGTileRing) & 1, p.status, 0x706);
+        if (!ok) break;
+        const int t = tile_ring[slot];
+        mbar_arrive(&tr_empty[slot]);
+        ++n_seen;
+        if (t < 0) break;
         ok = mbar_wait(&acc_empty[ab], ab_phase ^ 1, p.status, 0x702);
         if (!ok) break;
         tc_fence_after();
@@ -158,7 +186,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           umma_commit(&empty[stage]);
           if (++stage == kGStages) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(&acc_full[ab]);
+        if (!ok) break;
+        umma_commit(&acc_full[ab]);
         if (++ab == 2) { ab = 0; ab_phase ^= 1; }
       }
     }
@@ -231,9 +260,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       __syncwarp();
     };
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    uint32_t ab = 0, ab_phase = 0;
+    uint32_t ab = 0, ab_phase = 0, n_seen = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+    for (;;) {
+      const uint32_t slot = n_seen % kGTileRing;
+      ok = mbar_wait(&tr_full[slot], (n_seen / kGTileRing) & 1, p.status, 0x707);
+      if (!ok) break;
+      const int t = tile_ring[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tr_empty[slot]);
+      ++n_seen;
+      if (t < 0) break;
       const int m0 = (t / tiles_n) * kGM, n0 = (t % tiles_n) * kGN;
       const int m = m0 + row;
       float* bias_t = s_bias + ab * kGN;
@@ -546,6 +583,7 @@ int launch_gemm(const GemmParams& p_in, const void* x, const void* w, cudaStream
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = ((p.M + kGM - 1) / kGM) * ((p.N + kGN - 1) / kGN);
   const int grid = tiles < sms ? tiles : sms;
+  if (int rc = next_tile_counter(&p.sched); rc != MINTB_OK) return rc;
   kern<<<grid, kGThreads, kGemmSmem, stream>>>(ma, mb, mo, mp, p);
   count_launches(1);
   e = cudaGetLastError();

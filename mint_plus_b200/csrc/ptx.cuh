@@ -85,6 +85,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   return mbar_wait_limit(bar, parity, status, code, kWaitLimitNs);
 }
 
+// One thread per CTA calls this after its CTA's last draw from the work counter `ctr` = {next unit, CTAs that have left}:
+// the last CTA of the grid clears the pair for the launch that gets it next.
+__device__ __forceinline__ void leave_tile_counter(int* ctr, int n_ctas) {
+  __threadfence();
+  if (atomicAdd(ctr + 1, 1) == n_ctas - 1) {
+    ctr[0] = 0;
+    ctr[1] = 0;
+    __threadfence();
+  }
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------- TMA

@@ -67,6 +67,8 @@ def check_device_status(device=None) -> None:
     code = int(_dev_status(device).item())
     if code != 0:
         _dev_status(device).zero_()
+        with _on(device):
+            L.lib().mintb_reset_work_counters()   # CTAs that gave up may not have left their work counter
         raise L.MintbError(f"a mintb kernel gave up a bounded wait (device status 0x{code:x})")
 
 
