@@ -233,10 +233,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="attn",
                     help="attn (default: the isolated attention op) or a whole-model workload of bench_model.py: "
-                         "mint650m_fp8, mint150m_lora, mint3b_infer, mint8m_fwd, mint650m_fp8_packed, mint3b_infer_packed")
+                         "mint650m_fp8, mint650m_fp8_optim, mint150m_lora, mint3b_infer, mint8m_fwd, mint650m_fp8_packed, mint3b_infer_packed")
     ap.add_argument("--no-model-metric", action="store_true",
                     help="attn workload: skip the model-level measurements that are added to the line as `model_650m`, "
-                         "`model_150m_lora` and `model_3b_infer`")
+                         "`model_650m_optim`, `model_150m_lora` and `model_3b_infer`")
     ap.add_argument("--layers", type=int, default=0,
                     help="whole-model workloads only: run this many layers instead of the configuration's (a smaller case for "
                          "profiler captures; the line is then not a benchmark value and says so)")
@@ -472,6 +472,7 @@ def main():
         torch.cuda.empty_cache()
         peaks_m, peak_src_m = load_peaks()
         for key, workload, k_steps in (("model_650m", "mint650m_fp8", max(2, min(steps, 4))),
+                                       ("model_650m_optim", "mint650m_fp8_optim", max(2, min(steps, 4))),
                                        ("model_150m_lora", "mint150m_lora", max(2, min(steps, 4))),
                                        ("model_3b_infer", "mint3b_infer", 2)):
             try:

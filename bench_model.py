@@ -29,6 +29,10 @@ WORKLOADS = {
     "mint3b_infer": dict(layers=36, embed=2560, heads=40, pairs=64, T=2048, lo=30, hi=80, lo2=800, hi2=1900, seed=5005,
                          train=False, kind="plus", dtype="bf16",
                          desc="MINT 36x2560 (40 heads) inference forward, bf16, 64 pairs with skewed chain lengths padded to 2048"),
+    # the 650M training step followed by a fused AdamW step and the re-cast of every e4m3 weight copy (Fp8WeightScaler)
+    "mint650m_fp8_optim": dict(layers=33, embed=1280, heads=20, pairs=16, T=2048, lo=100, hi=900, seed=4004, train=True,
+                               kind="mu_fp8", dtype="e4m3 GEMMs / bf16 attention", optimizer="adamw",
+                               desc="MINT-650M muS FP8 fwd+bwd + fused AdamW step + e4m3 weight re-cast, 16 pairs padded to 2048"),
     # the same two with padded positions dropped from the token-wise work and from the attention's query tiles
     # (MINT.pack_padding): same values at real positions, zeros at padded ones; FLOPs are counted on real tokens only
     "mint650m_fp8_packed": dict(layers=33, embed=1280, heads=20, pairs=16, T=2048, lo=100, hi=900, seed=4004, train=True,
@@ -213,6 +217,11 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
             sync_grads = ChunkedGradAllReduce(model, n_chunks=int(os.environ["MINTB_GRAD_CHUNKS"]), dtype=gdt)
         else:
             sync_grads = FlatGradAllReduce(trainable, dtype=gdt)
+    opt = scaler = None
+    if cfg.get("optimizer") == "adamw":
+        from mint_plus_b200 import Fp8WeightScaler
+        opt = torch.optim.AdamW(trainable, lr=1e-5, weight_decay=0.01, fused=True)
+        scaler = Fp8WeightScaler(model)
     lib = L.lib()
     loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
     out_host = None
@@ -226,6 +235,9 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
             loss.backward()
             if sync_grads is not None:
                 sync_grads.finish() if isinstance(sync_grads, ChunkedGradAllReduce) else sync_grads()
+            if opt is not None:
+                opt.step()
+                scaler.refresh()        # no host read: scales from the maxima measured one step earlier
             return loss.detach()
         with torch.no_grad():
             res = model(tok, cid, repr_layers=[cfg["layers"]])

@@ -231,7 +231,7 @@ def fused_fp8_weight(owner: nn.Module, mods):
     cached = getattr(owner, "_fp8_qkv_cache", None)
     if cached is None or cached[0] != key:
         w = torch.cat([m.weight.detach() for m in mods], dim=0)
-        w_scale = max(float(w.abs().amax()), 1e-12) / E4M3_MAX
+        w_scale = max(m._quantized_weight()[1] for m in mods)   # amax of the concatenation / 448; a host read only where a copy is stale
         cached = (key, ops.quantize_e4m3(w.to(torch.bfloat16).contiguous(), w_scale), w_scale)
         owner._fp8_qkv_cache = cached
     return cached[1], cached[2], max(m.x_scale for m in mods), mods[0].out_scale, (owner._fp8_qkv_grad_scale if f8_grads else None)
@@ -248,6 +248,49 @@ def refresh_fp8_weights(model: nn.Module) -> nn.Module:
         if getattr(m, "_fp8_qkv_cache", None) is not None:
             m._fp8_qkv_cache = None
     return model
+
+
+class Fp8WeightScaler:
+    """Re-casts the e4m3 weight copies of every Fp8Linear of `model` after an optimizer step WITHOUT a host
+    synchronisation in the step: `refresh()` measures all weight maxima with one multi-tensor pass on the device, starts
+    their copy to pinned host memory, and casts each weight with the scale of the maxima measured by the refresh BEFORE
+    (those arrived a whole step ago).  A weight that outgrew last step's maximum saturates at +-448 for one step, which an
+    optimizer step's relative change keeps to the last e4m3 step of the very largest entries.  This is the delayed-scaling
+    idea of the production FP8 recipe (transformer_engine's DelayedScaling keeps an amax history per tensor and derives the
+    scale of a step from earlier steps), restated for the per-tensor weight scale amax / 448 of
+    mint_plus/models/alt/munit_scaling.py:22-34.  The first refresh has no history and reads its maxima back at once.
+    Without a scaler the copies refresh lazily in the forward pass, with one host read per changed weight."""
+
+    def __init__(self, model: nn.Module):
+        self.mods = [m for m in model.modules() if isinstance(m, Fp8Linear)]
+        self.model = model
+        self._host = None
+        self._event = None
+
+    @torch.no_grad()
+    def refresh(self) -> None:
+        if not self.mods:
+            return
+        ws = [m.weight.detach() for m in self.mods]
+        amax = torch.stack([a.float() for a in torch._foreach_norm(ws, float("inf"))])
+        if self._host is None:
+            self._host = torch.empty(len(ws), dtype=torch.float32).pin_memory()
+            prev = amax.cpu().tolist()                   # first use: no history yet
+        else:
+            self._event.synchronize()                    # recorded a step ago
+            prev = self._host.tolist()
+        self._host.copy_(amax, non_blocking=True)
+        self._event = torch.cuda.Event()
+        self._event.record()
+        for m, w, a in zip(self.mods, ws, prev):
+            m._w_scale = max(a, 1e-12) / E4M3_MAX
+            m._wq = ops.quantize_e4m3(w.to(torch.bfloat16).contiguous(), m._w_scale)
+            m._wq_key = (m.weight.data_ptr(), m.weight._version, m.weight.device)
+        for m in self.model.modules():                   # concatenated copies are rebuilt from the new casts (no host read)
+            if getattr(m, "_fp8_qkv_cache", None) is not None:
+                m._fp8_qkv_cache = None
+            if getattr(m, "_qkv6_cache", None) is not None:
+                m._qkv6_cache = None
 
 
 def _sublayers(model):

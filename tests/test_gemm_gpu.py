@@ -323,3 +323,37 @@ def test_fp8_weight_cache_follows_in_place_updates_and_refresh():
     refresh_fp8_weights(lin)                        # ... until it is dropped
     y2 = lin(x).float()
     assert (y2 - y0).abs().max().item() <= 2e-2 * y0.abs().max().item()
+
+
+@pytest.mark.gpu
+def test_fp8_weight_scaler_uses_the_maxima_of_the_refresh_before():
+    """Fp8WeightScaler.refresh(): the first refresh reads its maxima back, every later one casts with the maxima the
+    refresh before it measured (no host read in the step), and the forward pass then finds fresh copies."""
+    import mint_plus_b200 as M
+    from mint_plus_b200 import mu_scaling as MU
+    torch.manual_seed(5)
+    model = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.Linear(128, 64)).cuda().bfloat16()
+    model[0] = M.Fp8Linear.from_linear(model[0])
+    model[1] = M.Fp8Linear.from_linear(model[1])
+    sc = M.Fp8WeightScaler(model)
+    sc.refresh()
+    a0 = [float(m.weight.abs().amax()) for m in model]
+    for m, a in zip(model, a0):
+        assert m._w_scale == pytest.approx(a / 448.0)
+        assert m._wq_key == (m.weight.data_ptr(), m.weight._version, m.weight.device)      # the forward pass will not re-cast
+    with torch.no_grad():
+        for m in model:
+            m.weight.mul_(2.0)
+    sc.refresh()                                      # weights doubled, scales still from the maxima before
+    for m, a in zip(model, a0):
+        assert m._w_scale == pytest.approx(a / 448.0)
+        want = (m.weight.float() / m._w_scale).clamp(-448, 448).to(torch.float8_e4m3fn)
+        assert torch.equal(m._wq.view(torch.uint8), want.view(torch.uint8))
+    sc.refresh()                                      # now the doubled maxima have arrived
+    for m, a in zip(model, a0):
+        assert m._w_scale == pytest.approx(2.0 * a / 448.0)
+    x = torch.randn(32, 64, device="cuda").bfloat16()
+    y = model(x)
+    ref = torch.nn.functional.linear(torch.nn.functional.linear(x.float(), model[0].weight.float(), model[0].bias.float()),
+                                     model[1].weight.float(), model[1].bias.float())
+    assert (y.float() - ref).abs().max() <= 0.08 * ref.abs().max()
