@@ -14,7 +14,9 @@ from torch import nn
 import mint_plus_b200 as M
 from mint_plus_b200 import esm2, mu_scaling
 
-REF_ROOT = "/root/reference/mint_plus/models/mu_scaling"
+# the reference checkout, when it sits beside this repository (or where MINT_REFERENCE_ROOT points)
+REF_ROOT = os.path.join(os.environ.get("MINT_REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference")),
+                        "mint_plus", "models", "mu_scaling")
 
 
 def _ref_module(name):
