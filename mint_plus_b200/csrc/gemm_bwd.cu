@@ -163,33 +163,40 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
       leave_tile_counter(p.sched, int(gridDim.x));
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t kHi = desc_hi32(8 * 128, kSw128);        // eight 128-byte rows per swizzle atom, either major
-      const uint32_t lo0 = desc_addr32(smem_u32(smem));
-      const uint32_t lbo_k = desc_lbo32(16), lbo_mn = desc_lbo32(blk_bytes);
-      const uint32_t step_mn = p.f8 ? (32u * 128u) >> 4 : (16u * 128u) >> 4;   // one MMA consumes 32 (8-bit) or 16 reduction rows
-      uint32_t stage = 0, phase = 0, ab = 0, ab_phase = 0, n_seen = 0;
-      bool ok = true;
-      const UnitMap um(n_tiles, n_slabs, p.splits);
-      int tile, kb0, kb1;
-      for (;;) {
-        const uint32_t slot = n_seen % kBUnitRing;
-        ok = mbar_wait(&ur_full[slot], (n_seen / kBUnitRing) & 1, p.status, 0x806);
-        if (!ok) break;
-        const int u = unit_ring[slot];
-        mbar_arrive(&ur_empty[slot]);
-        ++n_seen;
-        if (u < 0) break;
-        um.decode(u, tile, kb0, kb1);
-        ok = mbar_wait(&acc_empty[ab], ab_phase ^ 1, p.status, 0x802);
+    // All lanes run the loop and one elected lane issues (warp-uniform control flow and operands keep the descriptors in
+    // uniform registers; from a single-lane region the issuing thread is the bottleneck at 8-bit rates).
+    const bool leader = elect_one();
+    auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity, p.status, code));
+    };
+    constexpr uint32_t kHi = desc_hi32(8 * 128, kSw128);        // eight 128-byte rows per swizzle atom, either major
+    const uint32_t lo0 = desc_addr32(__shfl_sync(0xffffffffu, smem_u32(smem), 0));
+    const uint32_t tbase_u = __shfl_sync(0xffffffffu, tbase, 0);
+    const uint32_t lbo_k = desc_lbo32(16), lbo_mn = desc_lbo32(blk_bytes);
+    const uint32_t step_mn = p.f8 ? (32u * 128u) >> 4 : (16u * 128u) >> 4;   // one MMA consumes 32 (8-bit) or 16 reduction rows
+    uint32_t stage = 0, phase = 0, ab = 0, ab_phase = 0, n_seen = 0;
+    bool ok = true;
+    const UnitMap um(n_tiles, n_slabs, p.splits);
+    int tile, kb0, kb1;
+    for (;;) {
+      const uint32_t slot = n_seen % kBUnitRing;
+      ok = wait_all(&ur_full[slot], (n_seen / kBUnitRing) & 1, 0x806);
+      if (!ok) break;
+      const int u = __shfl_sync(0xffffffffu, unit_ring[slot], 0);
+      if (leader) mbar_arrive(&ur_empty[slot]);
+      ++n_seen;
+      if (u < 0) break;
+      um.decode(u, tile, kb0, kb1);
+      ok = wait_all(&acc_empty[ab], ab_phase ^ 1, 0x802);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d = tbase_u + ab * kBN;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        ok = wait_all(&full[stage], phase, 0x803);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d = tbase + ab * kBN;
-        for (int kb = kb0; kb < kb1; ++kb) {
-          ok = mbar_wait(&full[stage], phase, p.status, 0x803);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t a_lo = lo0 + stage * (kBStageBytes >> 4), b_lo = a_lo + (kBABytes >> 4);
+        const uint32_t a_lo = lo0 + stage * (kBStageBytes >> 4), b_lo = a_lo + (kBABytes >> 4);
+        if (leader) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint64_t da = MODE == kDgrad ? make_desc(kHi, a_lo + lbo_k + 2 * k) : make_desc(kHi, a_lo + lbo_mn + k * step_mn);
@@ -198,12 +205,14 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
             else umma_ss(d, da, db, p.idesc, kb > kb0 || k > 0);
           }
           umma_commit(&empty[stage]);
-          if (++stage == kBStages) { stage = 0; phase ^= 1; }
         }
-        if (!ok) break;
-        umma_commit(&acc_full[ab]);
-        if (++ab == 2) { ab = 0; ab_phase ^= 1; }
+        __syncwarp();
+        if (++stage == kBStages) { stage = 0; phase ^= 1; }
       }
+      if (!ok) break;
+      if (leader) umma_commit(&acc_full[ab]);
+      __syncwarp();
+      if (++ab == 2) { ab = 0; ab_phase ^= 1; }
     }
   } else {
     // eight warps: warp w works on TMEM lanes 32 (w % 4) ... and on column half (w - 2) / 4 of the tile

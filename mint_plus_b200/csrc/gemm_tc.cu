@@ -21,7 +21,7 @@ constexpr int kGM = 128, kGN = 256, kGStages = 4;
 constexpr int kGEpiWarps = 8, kGEpiThreads = 32 * kGEpiWarps, kGThreads = 64 + kGEpiThreads;   // TMA warp, MMA warp, epilogue warps
 constexpr int kSlabBytes = 128;                       // bytes of K per stage and row (64 bf16 or 128 e4m3)
 constexpr int kABytes = kGM * kSlabBytes, kBBytes = kGN * kSlabBytes, kGStageBytes = kABytes + kBBytes;
-constexpr int kGStageOutBytes = 32 * 64;   // one epilogue warp's staging of 32 rows x 32 bf16 columns for a bulk store
+constexpr int kGStageOutBytes = 32 * 64 + 32 * 32;   // one epilogue warp's staging: 32 rows x 32 bf16 columns, then 32 rows x 32 e4m3 columns, for bulk stores
 constexpr int kGTileRing = 4;   // tile numbers travel from the loading warp to the other roles through a ring this deep
 constexpr size_t kGemmSmem = 1024 + size_t(kGStages) * kGStageBytes + kGEpiWarps * kGStageOutBytes + 256 + 2 * kGN * sizeof(float);
 
@@ -49,6 +49,7 @@ struct GemmParams {
   const int32_t* row_map;             // packed input rows: row m of x is token row_map[m] = t * B + b (null: m itself)
   int use_bulk_store;          // bf16 row-major outputs leave through shared memory and bulk tensor stores
   int use_bulk_f8;        // the e4m3 result leaves as bulk tensor stores too (32 x 32-byte boxes)
+  int alt_stores;         // every chunk issues a bf16 bulk store (pre-activation copy) AND an e4m3 one: they alternate between two staging areas
   int* status;
   int* sched;                  // work counter pair of this launch (common.cuh)
 };
@@ -56,18 +57,45 @@ struct GemmParams {
 // erf-GELU x/2 (1 + erf(x / sqrt 2)) with erf from the rational-exponential form 1 - (a1 t + ... + a5 t^5) exp(-z^2),
 // t = 1 / (1 + p z) (absolute error below 1.5e-7, far inside the bf16 / e4m3 output precision): two special-function
 // operations and a short Horner chain per element keep the epilogue shorter than the products of a K = 1280 tile.
-__device__ __forceinline__ float gelu_erf_f(float x) {
-  const float z = fabsf(x) * 0.70710678118654752f;
-  float t;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.f)));
-  float poly = fmaf(1.061405429f, t, -1.453152027f);
-  poly = fmaf(poly, t, 1.421413741f);
-  poly = fmaf(poly, t, -0.284496736f);
-  poly = fmaf(poly, t, 0.254829592f);
-  float e;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * z * z));
-  const float erf_abs = fmaf(-poly * t, e, 1.f);          // erf(|x| / sqrt 2)
-  return 0.5f * x + 0.5f * fabsf(x) * erf_abs;            // x/2 (1 + sign(x) erf(|x|/sqrt 2))
+// two fp32 values in one 64-bit register for the packed fp32 instructions of sm_100
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// erf-GELU of two values: x/2 (1 + erf(x / sqrt 2)) = max(x, 0) - a 2^s(a), a = min(|x|, 5.75), where
+// s(a) = log2(erfc(a / sqrt 2)) - 1 is replaced by a polynomial of degree 6 (least squares on Chebyshev nodes of [0, 5.75],
+// weighted by the result's sensitivity a 2^s ln 2 and re-weighted towards the largest error).  Against the exact function in
+// fp32 arithmetic: largest absolute error 5.1e-7, largest error relative to max(|gelu|, 1e-3) 5.2e-5 (the Abramowitz-Stegun
+// 7.1.26 form it replaces: 6.6e-7 and 2.7e-4, with two MUFU operations and 16 instructions per value instead of one and 7).
+// Beyond 5.75 the subtracted term is below 6e-8 |x|.
+__device__ __forceinline__ void gelu_erf2(float& x0, float& x1) {
+  const float a0 = fminf(fabsf(x0), 5.75f), a1 = fminf(fabsf(x1), 5.75f);
+  const uint64_t a = pack2(a0, a1);
+  uint64_t s = ffma2(pack2(3.309347236e-05f, 3.309347236e-05f), a, pack2(-7.692253187e-04f, -7.692253187e-04f));
+  s = ffma2(s, a, pack2(8.080734485e-03f, 8.080734485e-03f));
+  s = ffma2(s, a, pack2(-5.341213111e-02f, -5.341213111e-02f));
+  s = ffma2(s, a, pack2(-4.587709539e-01f, -4.587709539e-01f));
+  s = ffma2(s, a, pack2(-1.151201708e+00f, -1.151201708e+00f));
+  s = ffma2(s, a, pack2(-9.999930604e-01f, -9.999930604e-01f));
+  float s0, s1, e0, e1;
+  unpack2(s, s0, s1);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(s0));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(s1));
+  x0 = fmaf(-a0, e0, fmaxf(x0, 0.f));
+  x1 = fmaf(-a1, e1, fmaxf(x1, 0.f));
 }
 
 __device__ __forceinline__ float load_bias(const void* bias, int dtype, int n) {
@@ -97,7 +125,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* tr_empty = tr_full + kGTileRing;             // [kGTileRing] MMA thread and one lane per epilogue warp have read it
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tr_empty + kGTileRing);
   int* tile_ring = reinterpret_cast<int*>(tmem_slot + 2);    // [kGTileRing] tile number, negative = no more tiles
-  float* s_bias = reinterpret_cast<float*>(tile_ring + kGTileRing);   // [2][kGN] bias of the tile in flight (double buffered)
+  float* s_bias = reinterpret_cast<float*>(tail + 256);   // [2][kGN] bias of the tile in flight (double buffered), 16-byte aligned
   static_assert((2 * kGStages + 4 + 2 * kGTileRing) * 8 + 8 + kGTileRing * 4 <= 256, "barrier area of the shared-memory tail");
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -152,30 +180,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       leave_tile_counter(p.sched, int(gridDim.x));
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const bool f8 = p.in_dtype == MINTB_E4M3;
-      const uint32_t idesc = f8 ? idesc_e4m3(kGM, kGN) : idesc_bf16(kGM, kGN, false, false);
-      constexpr uint32_t kHi = desc_hi32(8 * kSlabBytes, kSw128);
-      const uint32_t a_lo0 = desc_addr32(smem_u32(smem)) + desc_lbo32(16);
-      uint32_t stage = 0, phase = 0, ab = 0, ab_phase = 0, n_seen = 0;
-      bool ok = true;
-      for (;;) {
-        const uint32_t slot = n_seen % kGTileRing;
-        ok = mbar_wait(&tr_full[slot], (n_seen / kGTileRing) & 1, p.status, 0x706);
-        if (!ok) break;
-        const int t = tile_ring[slot];
-        mbar_arrive(&tr_empty[slot]);
-        ++n_seen;
-        if (t < 0) break;
-        ok = mbar_wait(&acc_empty[ab], ab_phase ^ 1, p.status, 0x702);
+    // All lanes run the loop and one elected lane issues: with warp-uniform control flow and operands the descriptors stay
+    // in uniform registers, which is what tcgen05.mma reads; issued from a single-lane region every instruction first has
+    // to move its operands there, and at 8-bit rates (one 128 x 256 x 32-byte instruction per 128 cycles) the issuing
+    // thread is then the bottleneck.
+    const bool leader = elect_one();
+    auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity, p.status, code));
+    };
+    const bool f8 = p.in_dtype == MINTB_E4M3;
+    const uint32_t idesc = f8 ? idesc_e4m3(kGM, kGN) : idesc_bf16(kGM, kGN, false, false);
+    constexpr uint32_t kHi = desc_hi32(8 * kSlabBytes, kSw128);
+    const uint32_t a_lo0 = desc_addr32(__shfl_sync(0xffffffffu, smem_u32(smem), 0)) + desc_lbo32(16);
+    const uint32_t tbase_u = __shfl_sync(0xffffffffu, tbase, 0);
+    uint32_t stage = 0, phase = 0, ab = 0, ab_phase = 0, n_seen = 0;
+    bool ok = true;
+    for (;;) {
+      const uint32_t slot = n_seen % kGTileRing;
+      ok = wait_all(&tr_full[slot], (n_seen / kGTileRing) & 1, 0x706);
+      if (!ok) break;
+      const int t = __shfl_sync(0xffffffffu, tile_ring[slot], 0);
+      if (leader) mbar_arrive(&tr_empty[slot]);
+      ++n_seen;
+      if (t < 0) break;
+      ok = wait_all(&acc_empty[ab], ab_phase ^ 1, 0x702);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d = tbase_u + ab * kGN;
+      for (int kb = 0; kb < n_slabs; ++kb) {
+        ok = wait_all(&full[stage], phase, 0x703);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d = tbase + ab * kGN;
-        for (int kb = 0; kb < n_slabs; ++kb) {
-          ok = mbar_wait(&full[stage], phase, p.status, 0x703);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t a_lo = a_lo0 + stage * (kGStageBytes >> 4), b_lo = a_lo + (kABytes >> 4);
+        const uint32_t a_lo = a_lo0 + stage * (kGStageBytes >> 4), b_lo = a_lo + (kABytes >> 4);
+        if (leader) {
           if (f8) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) umma_ss_f8(d, make_desc(kHi, a_lo + 2 * k), make_desc(kHi, b_lo + 2 * k), idesc, kb > 0 || k > 0);
@@ -184,12 +221,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int k = 0; k < 4; ++k) umma_ss(d, make_desc(kHi, a_lo + 2 * k), make_desc(kHi, b_lo + 2 * k), idesc, kb > 0 || k > 0);
           }
           umma_commit(&empty[stage]);
-          if (++stage == kGStages) { stage = 0; phase ^= 1; }
         }
-        if (!ok) break;
-        umma_commit(&acc_full[ab]);
-        if (++ab == 2) { ab = 0; ab_phase ^= 1; }
+        __syncwarp();
+        if (++stage == kGStages) { stage = 0; phase ^= 1; }
       }
+      if (!ok) break;
+      if (leader) umma_commit(&acc_full[ab]);
+      __syncwarp();
+      if (++ab == 2) { ab = 0; ab_phase ^= 1; }
     }
   } else {
     // eight warps: warp w works on TMEM lanes 32 (w % 4) ... (the quarter it may access) and on column half (w - 2) / 4
@@ -197,11 +236,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int chalf = (warp - 2) / 4;
     const int row = quarter * 32 + lane;
     const int et = (warp - 2) * 32 + lane;   // thread index among the epilogue threads
-    unsigned char* my_out = s_out + size_t(warp - 2) * kGStageOutBytes;
+    unsigned char* my_out = s_out + size_t(warp - 2) * kGStageOutBytes;   // bf16 rows (1024-byte aligned: 64-byte swizzle)
+    unsigned char* my_out8 = my_out + 32 * 64;                            // e4m3 rows
     // 32 columns of this warp's 32 rows as bf16 -> shared memory (row = lane) -> one bulk tensor store: whole 64-byte row
     // pieces reach L2 instead of one 16-byte piece per lane and instruction; rows / columns past the matrix are dropped.
+    // With an e4m3 result beside a bf16 one the two stores of a chunk alternate between the two staging areas, so each
+    // waits only for the store before the last one (its own area's previous use), not for the one just issued.
     auto bulk_store32 = [&](const CUtensorMap* map, const float (&val)[32], int n, int row0) {
-      if (lane == 0) bulk_wait_read_all();   // the previous store of this warp has read the staging rows
+      if (lane == 0) {   // the previous store from these staging rows has read them
+        if (p.alt_stores) bulk_wait_read_but_one(); else bulk_wait_read_all();
+      }
       __syncwarp();
 #pragma unroll
       for (int j = 0; j < 32; j += 8)
@@ -217,19 +261,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     };
     // the same for an e4m3 result: 32 rows x 32 bytes, rows unswizzled
     auto bulk_store32_f8 = [&](const CUtensorMap* map, const float (&val)[32], int n, int row0) {
-      if (lane == 0) bulk_wait_read_all();
+      if (lane == 0) {
+        if (p.alt_stores) bulk_wait_read_but_one(); else bulk_wait_read_all();
+      }
       __syncwarp();
       uint4 o[2];
       __nv_fp8x2_storage_t* op = reinterpret_cast<__nv_fp8x2_storage_t*>(o);
+      const uint64_t os2 = pack2(p.out_scale, p.out_scale);
 #pragma unroll
-      for (int j = 0; j < 32; j += 2)   // the conversion itself saturates at +-448
-        op[j / 2] = __nv_cvt_float2_to_fp8x2(make_float2(val[j] * p.out_scale, val[j + 1] * p.out_scale), __NV_SATFINITE, __NV_E4M3);
-      *reinterpret_cast<uint4*>(my_out + lane * 32) = o[0];
-      *reinterpret_cast<uint4*>(my_out + lane * 32 + 16) = o[1];
+      for (int j = 0; j < 32; j += 2) {   // the conversion itself saturates at +-448
+        float a, b;
+        unpack2(fmul2(pack2(val[j], val[j + 1]), os2), a, b);
+        op[j / 2] = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+      }
+      *reinterpret_cast<uint4*>(my_out8 + lane * 32) = o[0];
+      *reinterpret_cast<uint4*>(my_out8 + lane * 32 + 16) = o[1];
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        tma_store_2d(map, my_out, n, row0);
+        tma_store_2d(map, my_out8, n, row0);
         bulk_commit_group();
       }
     };
@@ -289,17 +339,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         hm_b = mo % p.B;
         if (m < p.M) hm_row = (static_cast<long long>(hm_b) * p.H * p.T + hm_t) * HD;
       }
-#pragma unroll 1
-      for (int c0 = chalf * (kGN / 2); c0 < (chalf + 1) * (kGN / 2); c0 += 32) {
-        if (n0 + c0 >= p.N) break;   // uniform
-        uint32_t r[32];
-        tmem_ld32(tacc + c0, r);
-        tmem_ld_wait();
+      // one chunk of 32 columns, its accumulator values already in registers
+      auto do_chunk = [&](const int c0, const uint32_t (&r)[32]) {
         float v[32];
-#pragma unroll
         // (two-pathway QKV projection: the columns of the second pathway carry their own multiplier)
         const float al = (EPI == kEpiHeadMajor && n0 + c0 >= 3 * p.H * HD) ? p.alpha2 : p.alpha;
-        for (int j = 0; j < 32; ++j) v[j] = fmaf(__uint_as_float(r[j]), al, bias_t[c0 + j]);
+        {
+          const uint64_t al2 = pack2(al, al);
+          const float4* b4 = reinterpret_cast<const float4*>(bias_t + c0);
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 bb = b4[j / 4];
+            unpack2(ffma2(pack2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), al2, pack2(bb.x, bb.y)), v[j], v[j + 1]);
+            unpack2(ffma2(pack2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])), al2, pack2(bb.z, bb.w)), v[j + 2], v[j + 3]);
+          }
+        }
         if constexpr (EPI == kEpiHeadMajor) {
           // column n = which * E + h * HD + d, which = 0..2 (q, k, v of the first pathway) or 3..5 (of the second, never
           // rotated).  E is a multiple of 32 (of 64 when HD = 64), so a 32-column chunk lies in one third and covers whole
@@ -413,7 +467,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               }
             }
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = gelu_erf_f(v[j]);
+            for (int j = 0; j < 32; j += 2) gelu_erf2(v[j], v[j + 1]);
           }
           if (p.use_bulk_store && p.out_dtype == MINTB_BF16) {
             bulk_store32(&map_out, v, n, m0 + quarter * 32);
@@ -451,6 +505,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           }
         }
+      };
+      // The TMEM load of the next chunk is issued before the arithmetic and the stores of the current one (not with
+      // head size 64, whose rotation reads the partner chunk as well and has no registers to spare).
+      const int cbeg = chalf * (kGN / 2), cend = (chalf + 1) * (kGN / 2);
+      if constexpr (EPI == kEpiHeadMajor && HD == 64) {
+#pragma unroll 1
+        for (int c0 = cbeg; c0 < cend; c0 += 32) {
+          if (n0 + c0 >= p.N) break;   // uniform
+          uint32_t r[32];
+          tmem_ld32(tacc + c0, r);
+          tmem_ld_wait();
+          do_chunk(c0, r);
+        }
+      } else {
+        uint32_t ra[32], rb[32];
+        tmem_ld32(tacc + cbeg, ra);
+#pragma unroll 1
+        for (int c0 = cbeg; c0 < cend; c0 += 64) {
+          if (n0 + c0 >= p.N) break;   // uniform
+          tmem_ld_wait();
+          tmem_ld32(tacc + c0 + 32, rb);
+          do_chunk(c0, ra);
+          if (n0 + c0 + 32 >= p.N) break;   // uniform
+          tmem_ld_wait();
+          if (c0 + 64 < cend) tmem_ld32(tacc + c0 + 64, ra);
+          do_chunk(c0 + 32, rb);
+        }
+        tmem_ld_wait();   // (a load issued ahead of a chunk that was not processed)
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[ab]);
@@ -570,6 +652,7 @@ int launch_gemm(const GemmParams& p_in, const void* x, const void* w, cudaStream
     }
     p.use_bulk_f8 = 1;
   }
+  p.alt_stores = (p.use_bulk_f8 && p.use_bulk_store && p.preact != nullptr) ? 1 : 0;
   void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, GemmParams) = nullptr;
   if (p.epilogue == kEpiBias) kern = gemm_tc_kernel<kEpiBias, 0>;
   else if (p.epilogue == kEpiBiasGelu) kern = gemm_tc_kernel<kEpiBiasGelu, 0>;
