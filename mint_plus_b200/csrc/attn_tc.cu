@@ -96,6 +96,7 @@ __global__ void __launch_bounds__(256) rope_rotate_kernel(const __nv_bfloat16* _
                                                           __nv_bfloat16* __restrict__ qr, __nv_bfloat16* __restrict__ kr,
                                                           const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
                                                           size_t rows, int T, int D) {
+  griddep_launch();   // the attention kernel's set-up may overlap this pass
   const int h = D / 2, cpr = h / 8;  // chunks per row
   const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= rows * cpr) return;
@@ -282,6 +283,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  griddep_wait();   // the set-up above may overlap the rotation pass before this kernel; its copies are read from here on
   const uint32_t tbase = *tmem_slot;
 
   if (warp == 0) {
@@ -815,9 +817,9 @@ static int fwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s) {
     n_ctas = 2 * (sms > 0 ? sms : 148);
   }
   const unsigned grid = unsigned(n_items < n_ctas ? n_items : n_ctas);
-  attn_fwd_tc_kernel<D, SQ><<<grid, kTcThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, p);
+  cudaError_t e = launch_dependent(attn_fwd_tc_kernel<D, SQ>, dim3(grid), dim3(kTcThreads), Cfg::kSmemBytes, a.stream, mqs, mks, mvs, mqc, mkc, mvc, p);
   count_launches(1);
-  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("attention forward launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   return MINTB_OK;
 }

@@ -107,10 +107,13 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
 // Per-query statistics for the backward pass: nl = -lse * log2 e and nd = -delta, delta = sum_d dO[i][d] * O[i][d], stored
 // for each pair of queries (2p, 2p+1) of a (batch, head) as the 16 bytes (nl0, nl1, nd0, nd1).
 // Rows are padded to a multiple of 128 per (batch, head); the pad entries are (-inf, 0), which makes exp2 give 0 there.
+// The pass also clears the two fp32 dQ accumulators that the main kernel adds to.
 // `factor` is 1, or 1/2 for the square-root softmax (whose kernel works with sqrt(p) = exp2((s c - lse) / 2) and delta / 2).
 __global__ void __launch_bounds__(256) bwd_stats_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                                         const float* __restrict__ lse, float2* __restrict__ stats, int BH, int T,
-                                                        int Tpad, int D, float factor, size_t row_stride, size_t bh_stride) {
+                                                        int Tpad, int D, float factor, size_t row_stride, size_t bh_stride,
+                                                        float* __restrict__ acc_s, float* __restrict__ acc_c) {
+  griddep_launch();       // the main kernel's set-up may overlap this pass; it waits for it before it reads the statistics
   const int lpr = D / 8;  // lanes per row
   const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   const size_t prow = idx / lpr;          // row in the padded layout
@@ -131,6 +134,13 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const __nv_bfloat16* __r
       acc = fmaf(x.x, y.x, acc);
       acc = fmaf(x.y, y.y, acc);
     }
+    // this thread's eight columns of the row in the two fp32 dQ accumulators [b h][T][D] start at zero
+    const size_t ao = (bh * T + t) * D + c * 8;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(acc_s + ao) = z;
+    *reinterpret_cast<float4*>(acc_s + ao + 4) = z;
+    *reinterpret_cast<float4*>(acc_c + ao) = z;
+    *reinterpret_cast<float4*>(acc_c + ao + 4) = z;
   }
   for (int off = lpr / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (bh < size_t(BH) && c == 0) {
@@ -148,6 +158,7 @@ __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __rest
                                                              const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
                                                              size_t rows, int T, int D, float scale, int H, size_t g_row,
                                                              size_t g_b, size_t g_h, const int32_t* __restrict__ token_row, int B) {
+  griddep_wait();   // launched while the main kernel may still be running: its additions have to be complete
   const int h = D / 2, cpr = h / 8;
   const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= rows * cpr) return;
@@ -350,6 +361,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   tc_fence_before();
   any_active = __syncthreads_or(any_active);
   tc_fence_after();
+  // Up to here nothing that the pass before this kernel writes (the statistics, the cleared dQ accumulators) has been
+  // touched, so all of it may overlap that pass; from here on it has to be complete.  The pass after this kernel (the dQ
+  // conversion) may be scheduled once every CTA has come this far; it waits for the whole grid itself.
+  griddep_wait();
+  if (tid == 0) griddep_launch();
   const uint32_t tbase = *tmem_slot;
   if (any_active == 0) {
     // no query tile holds a pair of this pathway (every query on the other side of the mask): zero gradients; the copies of
@@ -793,9 +809,9 @@ static int bwd_tc_t(const AttnArgs& a, const void* q_s, const void* k_s, const f
   p.g_row = grad_row_stride(a); p.g_b = grad_b_stride(a); p.g_h = grad_h_stride(a);
   p.token_row = a.token_row; p.B = a.B;
   dim3 grid((a.T + kBwdTile - 1) / kBwdTile, BH, 2);
-  attn_bwd_tc_kernel<D, SQ><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(mqs, mks, mvs, mqc, mkc, mvc, mdo, mdq_s, mdq_c, p);
+  e = launch_dependent(attn_bwd_tc_kernel<D, SQ>, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, a.stream, mqs, mks, mvs, mqc, mkc, mvc, mdo, mdq_s, mdq_c, p);
   count_launches(1);
-  e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("attention backward launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   return MINTB_OK;
 }
@@ -818,15 +834,13 @@ int launch_attn_bwd_tc(const AttnArgs& a) {
   ws += bwd_stats_bytes(a.B, a.H, a.T);
   float* acc_s = reinterpret_cast<float*>(ws);
   float* acc_c = reinterpret_cast<float*>(ws + bwd_acc_bytes(a.B, a.H, a.T, a.D));
-  cudaError_t e = cudaMemsetAsync(acc_s, 0, 2 * bwd_acc_bytes(a.B, a.H, a.T, a.D), a.stream);
-  if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   {
     const int tpad = bwd_tpad(a.T);
     const size_t n = size_t(a.B) * a.H * tpad * (a.D / 8);
     bwd_stats_kernel<<<unsigned((n + 255) / 256), 256, 0, a.stream>>>(static_cast<const __nv_bfloat16*>(a.out),
                                                                      static_cast<const __nv_bfloat16*>(a.d_out), a.lse, stats,
                                                                      a.B * a.H, a.T, tpad, a.D, a.sqrt_softmax ? 0.5f : 1.f, out_row_stride(a),
-                                                                     out_bh_stride(a));
+                                                                     out_bh_stride(a), acc_s, acc_c);
     count_launches(1);
   }
   int rc = MINTB_EUNSUPPORTED;
@@ -844,13 +858,14 @@ int launch_attn_bwd_tc(const AttnArgs& a) {
   if (rc != MINTB_OK) return rc;
   {
     const size_t n = rows * (a.D / 16);
-    bwd_dq_convert_kernel<<<unsigned((n + 255) / 256), 256, 0, a.stream>>>(
+    cudaError_t le = launch_dependent(bwd_dq_convert_kernel, dim3(unsigned((n + 255) / 256)), dim3(256), 0, a.stream,
         acc_s, acc_c, static_cast<__nv_bfloat16*>(a.dq_s), static_cast<__nv_bfloat16*>(a.dq_c),
         a.rope ? a.rope_cos : nullptr, a.rope ? a.rope_sin : nullptr, rows, a.T, a.D, a.scale, a.H, grad_row_stride(a),
         grad_b_stride(a), grad_h_stride(a), a.token_row, a.B);
     count_launches(1);
+    if (le != cudaSuccess) { set_error("attention backward launch: %s", cudaGetErrorString(le)); return MINTB_ECUDA; }
   }
-  e = cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("attention backward launch: %s", cudaGetErrorString(e)); return MINTB_ECUDA; }
   return MINTB_OK;
 }

@@ -95,6 +95,22 @@ inline size_t grad_b_stride(const AttnArgs& a) { return a.grad_rowmajor ? size_t
 inline size_t grad_h_stride(const AttnArgs& a) { return a.grad_rowmajor ? size_t(a.D) : size_t(a.T) * a.D; }
 
 void set_error(const char* fmt, ...);
+// Launch `kern` so that it may start while the kernel before it in the stream is still running (programmatic dependent
+// launch); the kernel calls ptx::griddep_wait() before it touches anything that kernel writes.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 void count_launches(int n);  // process-wide tally of kernels launched by this library
 
 // Work counters of the persistent kernels.  A launch takes the next {next unit, CTAs that have left} pair of a pool in the

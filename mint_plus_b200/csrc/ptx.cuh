@@ -19,6 +19,13 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Programmatic dependent launch: a kernel launched with the "programmatic stream serialization" attribute may start while
+// the kernel before it in the stream is still running; griddep_wait() returns once that kernel has completed and its writes
+// are visible (at once when the attribute was not set).  griddep_launch() in the earlier kernel says that the later one may
+// be scheduled as soon as every CTA of this grid has said so or has finished.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
