@@ -387,30 +387,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             // the chunk starts at head e / HD (HD = 16: and covers the next one too), heads are T * HD elements apart
             scatter_store32(p.qkv[which], v, hm_row, size_t(e / HD) * p.T * HD, size_t(p.T) * HD);
-          } else {
-            // HD = 64: this chunk is the lower or the upper half of one head; the rotation needs the partner half,
-            // which is read from TMEM as well (same tile: pairs of chunks are 64-column aligned)
-            const bool upper = (e % 64) != 0;
-            if (rot) {
-              const int c2 = upper ? c0 - 32 : c0 + 32;
-              uint32_t r2[32];
-              tmem_ld32(tacc + c2, r2);
-              tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.rope_cos + size_t(hm_t) * 32 + j));
-                const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.rope_sin + size_t(hm_t) * 32 + j));
-                const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float x = fmaf(__uint_as_float(r2[j + e]), al, bias_t[c2 + j + e]);
-                  if (which == 0) x *= p.q_scale;
-                  v[j + e] = upper ? v[j + e] * cs[e] + x * sn[e] : v[j + e] * cs[e] - x * sn[e];
-                }
-              }
-            }
-            scatter_store32(p.qkv[which], v, hm_row, size_t(e / 64) * p.T * 64 + (upper ? 32 : 0), 0);
           }
+          // (head size 64 does not come here: its loop below works on whole heads)
         } else {
           const int n = n0 + c0;
           if (p.resid != nullptr) {   // res_a * resid + res_b * (projection): the residual sum of the layer, formed here
@@ -506,17 +484,69 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
       };
-      // The TMEM load of the next chunk is issued before the arithmetic and the stores of the current one (not with
-      // head size 64, whose rotation reads the partner chunk as well and has no registers to spare).
+      // The TMEM load of the next chunk is issued before the arithmetic and the stores of the current one (head size 64
+      // has its own loop).
       const int cbeg = chalf * (kGN / 2), cend = (chalf + 1) * (kGN / 2);
       if constexpr (EPI == kEpiHeadMajor && HD == 64) {
+        // One head (64 columns: the lower and the upper half the rotation pairs up) of q, k or v per step: both halves
+        // arrive with one TMEM round trip and the table rows are on their way while it lasts.  (E is a multiple of 64 and
+        // the tile's columns start at a multiple of 256, so a step never straddles a head or a third.)
 #pragma unroll 1
-        for (int c0 = cbeg; c0 < cend; c0 += 32) {
+        for (int c0 = cbeg; c0 < cend; c0 += 64) {
           if (n0 + c0 >= p.N) break;   // uniform
-          uint32_t r[32];
-          tmem_ld32(tacc + c0, r);
+          uint32_t ra[32], rb[32];
+          tmem_ld32(tacc + c0, ra);
+          tmem_ld32(tacc + c0 + 32, rb);
+          const int E = p.H * 64;
+          const int n = n0 + c0;
+          const int which = n / E, e = n % E;
+          const bool rot = p.rope_cos != nullptr && which < 2;
+          const float al = n >= 3 * E ? p.alpha2 : p.alpha;
+          // the first halves of the token's two table rows (128 bytes each) now, the second halves (then in L1) when needed
+          const float4* cos4 = reinterpret_cast<const float4*>(p.rope_cos + size_t(hm_t) * 32);
+          const float4* sin4 = reinterpret_cast<const float4*>(p.rope_sin + size_t(hm_t) * 32);
+          float4 cs[4], sn[4];
+          if (rot) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { cs[j] = __ldg(cos4 + j); sn[j] = __ldg(sin4 + j); }
+          }
           tmem_ld_wait();
-          do_chunk(c0, r);
+          float lo[32], hi[32];
+          {
+            const float mul = (which == 0 || which == 3) ? p.q_scale : 1.f;   // (x al + b) q_scale
+            const uint64_t al2 = pack2(al * mul, al * mul), m2 = pack2(mul, mul);
+            const float4* b4 = reinterpret_cast<const float4*>(bias_t + c0);
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float4 bl = b4[j / 4], bh = b4[8 + j / 4];
+              unpack2(ffma2(pack2(__uint_as_float(ra[j]), __uint_as_float(ra[j + 1])), al2, fmul2(pack2(bl.x, bl.y), m2)), lo[j], lo[j + 1]);
+              unpack2(ffma2(pack2(__uint_as_float(ra[j + 2]), __uint_as_float(ra[j + 3])), al2, fmul2(pack2(bl.z, bl.w), m2)), lo[j + 2], lo[j + 3]);
+              unpack2(ffma2(pack2(__uint_as_float(rb[j]), __uint_as_float(rb[j + 1])), al2, fmul2(pack2(bh.x, bh.y), m2)), hi[j], hi[j + 1]);
+              unpack2(ffma2(pack2(__uint_as_float(rb[j + 2]), __uint_as_float(rb[j + 3])), al2, fmul2(pack2(bh.z, bh.w), m2)), hi[j + 2], hi[j + 3]);
+            }
+          }
+          if (rot) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              if (half == 1) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { cs[j] = __ldg(cos4 + 4 + j); sn[j] = __ldg(sin4 + 4 + j); }
+              }
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) {
+                const float c4[4] = {cs[j / 4].x, cs[j / 4].y, cs[j / 4].z, cs[j / 4].w};
+                const float s4[4] = {sn[j / 4].x, sn[j / 4].y, sn[j / 4].z, sn[j / 4].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float a = lo[16 * half + j + q], bb = hi[16 * half + j + q];
+                  lo[16 * half + j + q] = a * c4[q] - bb * s4[q];
+                  hi[16 * half + j + q] = bb * c4[q] + a * s4[q];
+                }
+              }
+            }
+          }
+          scatter_store32(p.qkv[which], lo, hm_row, size_t(e / 64) * p.T * 64, 0);
+          scatter_store32(p.qkv[which], hi, hm_row, size_t(e / 64) * p.T * 64 + 32, 0);
         }
       } else {
         uint32_t ra[32], rb[32];

@@ -145,8 +145,10 @@ def default_inv_freq(D: int, device) -> torch.Tensor:
     return (1.0 / (10000 ** (torch.arange(0, D, 2).float() / D))).to(device)
 
 
-def rope_tables(T: int, D: int, device, inv_freq: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """cos/sin tables (T, D/2) fp32 on `device`, cached per (T, D, device, inv_freq contents)."""
+def rope_tables(T: int, D: int, device,
+                inv_freq: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """(cos, sin, inv_freq): the cos/sin tables (T, D/2) fp32 on `device`, cached per (T, D, device, inv_freq contents); the
+    third entry is the caller's inv_freq (None for the default frequencies), held so that the cache key stays valid."""
     device = torch.device(device)
     key = (T, D, device.index, inv_freq.data_ptr() if inv_freq is not None else 0,
            inv_freq._version if inv_freq is not None else 0)
