@@ -379,3 +379,39 @@ def test_backward_writes_row_major_gradients_and_packed_rows(shape, sqrt_sm):
         ref = full.index_select(0, pack.rows64)
         torch.testing.assert_close(packed[:, E:], ref[:, E:], rtol=0, atol=0)            # dK, dV: fixed-order sums
         assert (packed[:, :E].float() - ref[:, :E].float()).abs().max().item() <= 1e-2 * ref[:, :E].float().abs().max().item() + 1e-6
+
+
+def test_back_to_back_calls_see_each_others_results_in_stream_order():
+    """The small passes (rotation, statistics + accumulator clearing, dQ conversion) and the main kernels overlap their
+    set-up with the pass before them (programmatic dependent launch).  Calls on two different input sets, issued back to
+    back without a synchronisation in between (workspaces are handed back and forth by the caching allocator), must give what each set gives alone:
+    outputs, dK and dV bit for bit (their sums have a fixed order), dQ within the run-to-run bound of its fp32 additions."""
+    sets = []
+    for seed in (11, 12):
+        ts, cid, pad, grad = O.make_op_inputs(2, 4, 700, 32, seed=seed)
+        leaves = [t.to(DEV, torch.bfloat16).requires_grad_(True) for t in ts]
+        meta = M.mask_meta_from_chain_ids(cid.to(DEV), pad.to(DEV))
+        sets.append((leaves, meta, grad.to(DEV, torch.bfloat16)))
+
+    def step(s):
+        leaves, meta, g = s
+        out = M.multimer_attention(*leaves, meta=meta, rope=True)
+        return out, torch.autograd.grad(out, leaves, g)
+
+    alone = []
+    for s in sets:
+        out, grads = step(s)
+        torch.cuda.synchronize()
+        alone.append((out.clone(), [x.clone() for x in grads]))
+    results = [step(sets[i % 2]) for i in range(24)]   # no synchronisation between the calls
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    for i, (out, grads) in enumerate(results):
+        want_out, want = alone[i % 2]
+        assert torch.equal(out, want_out), f"call {i}: output differs"
+        for j, (g, w) in enumerate(zip(grads, want)):
+            if j in (0, 3):   # dq_s, dq_c: fp32 additions in arrival order, then rounded to bf16
+                scale = w.float().abs().max().item()
+                assert (g.float() - w.float()).abs().max().item() <= 2e-2 * scale, f"call {i}: dq {j} differs"
+            else:
+                assert torch.equal(g, w), f"call {i}: gradient {j} differs"
