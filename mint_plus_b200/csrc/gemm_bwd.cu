@@ -38,6 +38,7 @@ struct BwdGemmParams {
   int f8;                // operands are 8-bit floats (else bf16)
   uint32_t idesc;        // instruction descriptor (formats, majors, M = 128, N = 256)
   int splits;            // aligned cuts of the reduction (wgrad); 1 for dgrad
+  int n_full, pieces;    // the first n_full (split, tile) units run whole, the others in `pieces` aligned pieces (UnitMap)
   float alpha;
   int* status;
   int* sched;            // work counter pair of this launch (common.cuh)
@@ -61,18 +62,32 @@ __device__ __forceinline__ uint32_t bwd_pack_bf16x2(float lo, float hi) {
 // hands them to the other roles through a small ring, so a CTA that shares its SM with another kernel for a while simply
 // takes fewer units instead of holding the whole grid up.
 constexpr int kBUnitRing = 4;
+// The units in launch order: first the n_full "large" units - (split, tile) pairs, split-major, each a tile's reduction over one
+// of `splits` aligned cuts - then the remaining large units cut once more into `pieces` aligned pieces each (piece-major, so
+// that the pieces in flight at one time cover the same reduction range).  The host chooses n_full as a whole number of
+// rounds of the grid and `pieces` so that the last, partial round of large units becomes rounds of short ones.
 struct UnitMap {
-  int n_units, n_tiles, n_slabs, per_split;
-  __device__ UnitMap(int n_tiles_, int n_slabs_, int splits) {
+  int n_units, n_tiles, n_slabs, per_split, n_full, rem, sub;
+  __device__ UnitMap(int n_tiles_, int n_slabs_, int splits, int n_full_, int pieces) {
     n_tiles = n_tiles_; n_slabs = n_slabs_;
     per_split = (n_slabs + splits - 1) / splits;
-    n_units = n_tiles * splits;
+    const int n_large = n_tiles * splits;
+    n_full = n_full_ < n_large ? n_full_ : n_large;
+    rem = n_large - n_full;
+    sub = (per_split + pieces - 1) / pieces;
+    n_units = n_full + rem * pieces;
   }
   // false for a unit past the end of the reduction (it holds nothing)
   __device__ bool decode(int u, int& tile, int& kb0, int& kb1) const {
-    tile = u % n_tiles;
-    kb0 = (u / n_tiles) * per_split;
+    int large = u, piece = -1;
+    if (u >= n_full) { large = n_full + (u - n_full) % rem; piece = (u - n_full) / rem; }
+    tile = large % n_tiles;
+    kb0 = (large / n_tiles) * per_split;
     kb1 = kb0 + per_split < n_slabs ? kb0 + per_split : n_slabs;
+    if (piece >= 0) {
+      kb0 += piece * sub;
+      kb1 = kb0 + sub < kb1 ? kb0 + sub : kb1;
+    }
     return kb0 < kb1;
   }
 };
@@ -121,7 +136,7 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
       prefetch_tensormap(&map_b1);
       uint32_t stage = 0, phase = 0, n_drawn = 0;
       bool ok = true, first = true;
-      const UnitMap um(n_tiles, n_slabs, p.splits);
+      const UnitMap um(n_tiles, n_slabs, p.splits, p.n_full, p.pieces);
       int tile = 0, kb0 = 0, kb1 = 0;
       for (;;) {
         const uint32_t slot = n_drawn % kBUnitRing;
@@ -176,7 +191,7 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
     const uint32_t step_mn = p.f8 ? (32u * 128u) >> 4 : (16u * 128u) >> 4;   // one MMA consumes 32 (8-bit) or 16 reduction rows
     uint32_t stage = 0, phase = 0, ab = 0, ab_phase = 0, n_seen = 0;
     bool ok = true;
-    const UnitMap um(n_tiles, n_slabs, p.splits);
+    const UnitMap um(n_tiles, n_slabs, p.splits, p.n_full, p.pieces);
     int tile, kb0, kb1;
     for (;;) {
       const uint32_t slot = n_seen % kBUnitRing;
@@ -222,7 +237,7 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constan
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     uint32_t ab = 0, ab_phase = 0, n_seen = 0;
     bool ok = true;
-    const UnitMap um(n_tiles, n_slabs, p.splits);
+    const UnitMap um(n_tiles, n_slabs, p.splits, p.n_full, p.pieces);
     int tile, kb0, kb1;
     for (;;) {
       const uint32_t slot = n_seen % kBUnitRing;
@@ -371,17 +386,34 @@ static int launch_bwd_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const C
   return MINTB_OK;
 }
 
-// Number of aligned cuts of a reduction of n_slabs slabs for n_tiles output tiles on `sms` CTAs: the count (at most 16, at
-// least 8 slabs per unit) with the fewest slab-times on the busiest CTA, an epilogue counted as six slab-times.
-static int choose_splits(int n_tiles, int n_slabs, int sms) {
-  int best = 1;
+// Plan of a weight-gradient launch: n_tiles output tiles, a reduction of n_slabs slabs, `sms` CTAs.  A tile's reduction is cut
+// into `splits` aligned parts (large units); as many large units as fill whole rounds of the grid run as they are, and the
+// left-over ones - which would occupy a round of their own with part of the grid idle - are cut again into `pieces` pieces
+// each, so that they spread over the whole grid as short units.  Cost model in slab-times on the busiest CTA: a round of
+// large units costs its slabs (the epilogue of a unit overlaps the next unit's products), a round of short units at least
+// an epilogue (six slab-times), one epilogue at the end.  At most 16 splits and 32 pieces, units of at least 8 slabs.
+struct WgradPlan { int splits, n_full, pieces; long long units; };
+static WgradPlan plan_wgrad(int n_tiles, int n_slabs, int sms) {
+  WgradPlan best{1, n_tiles, 1, n_tiles};
   long long best_cost = -1;
   for (int s = 1; s <= 16; ++s) {
     const int per = (n_slabs + s - 1) / s;
     if (s > 1 && per < 8) break;
-    const long long rounds = (static_cast<long long>(n_tiles) * s + sms - 1) / sms;
-    const long long cost = rounds * (per + 6);
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+    const int s_eff = (n_slabs + per - 1) / per;                 // cuts that hold something
+    const long long large = static_cast<long long>(n_tiles) * s_eff;
+    const long long full_rounds = large / sms, rem = large - full_rounds * sms;
+    for (int m = 1; m <= 32; ++m) {
+      const int sub = (per + m - 1) / m;
+      if (m > 1 && (sub < 8 || rem == 0)) break;
+      const int m_eff = (per + sub - 1) / sub;
+      const long long short_rounds = (rem * m_eff + sms - 1) / sms;
+      const long long cost = full_rounds * per + short_rounds * (sub > 6 ? sub : 6) + 6;
+      const long long units = full_rounds * sms + rem * m_eff;
+      if (best_cost < 0 || cost < best_cost || (cost == best_cost && units < best.units)) {
+        best_cost = cost;
+        best = WgradPlan{s_eff, int(full_rounds * sms), m_eff, units};
+      }
+    }
   }
   return best;
 }
@@ -419,8 +451,9 @@ extern "C" int mintb_linear_dgrad(const void* dz, const void* w, const void* dz2
   BwdGemmParams p{};
   p.rows = M; p.cols = K; p.red1 = N; p.red2 = N2; p.f8 = f8 ? 1 : 0;
   p.idesc = bwd_idesc(fmt_code(dz_dtype), fmt_code(w_dtype), false, true);
-  p.splits = 1; p.alpha = alpha; p.status = dev_status;
+  p.splits = 1; p.pieces = 1; p.alpha = alpha; p.status = dev_status;
   const int tiles = ((M + kBM - 1) / kBM) * ((K + kBN - 1) / kBN);
+  p.n_full = tiles;
   const int sms = sm_count();
   return launch_bwd_gemm<kDgrad>(a1, b1, a2, b2, mo, p, tiles < sms ? tiles : sms, static_cast<cudaStream_t>(stream));
 }
@@ -471,8 +504,9 @@ extern "C" int mintb_linear_wgrad(const void* dz, const void* x, void* dw, void*
   p.alpha = alpha; p.status = dev_status;
   const int tiles = ((N + kBM - 1) / kBM) * ((K + kBN - 1) / kBN);
   const int sms = sm_count();
-  p.splits = choose_splits(tiles, (M + epb - 1) / epb, sms);
-  const long long units = static_cast<long long>(tiles) * p.splits;
+  const WgradPlan plan = plan_wgrad(tiles, (M + epb - 1) / epb, sms);
+  p.splits = plan.splits; p.n_full = plan.n_full; p.pieces = plan.pieces;
+  const long long units = plan.units;
   int rc = launch_bwd_gemm<kWgrad>(a1, b1, a1, b1, mo, p, units < sms ? int(units) : sms, s);
   if (rc != MINTB_OK) return rc;
   if (out_dtype == MINTB_BF16) {
