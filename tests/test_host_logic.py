@@ -153,3 +153,30 @@ def test_e4m3_copy_rides_on_the_tensor_and_expires_when_it_is_written():
     t.add_(1.0)                                 # written since: the copy no longer describes it
     with pytest.raises(RuntimeError):
         ops.e4m3_of(t, 0.5)
+
+
+def test_gelu_polynomial_of_the_gemm_epilogue_matches_erf_gelu():
+    """The projection epilogue computes erf-GELU as max(x, 0) - a 2^s(a), a = min(|x|, 5.75), with a degree-6 polynomial s.
+    The coefficients are read from the CUDA source and the formula is evaluated here in fp32 steps (Horner form, as the
+    kernel does) against x/2 (1 + erf(x / sqrt 2)) in fp64: the absolute error stays below 1e-6 everywhere, which is the
+    accuracy the formula it replaced had (gelu_erf of mint_plus/models/modules.py:16-23 is the function approximated)."""
+    import os
+    import re
+    src = open(os.path.join(os.path.dirname(os.path.abspath(M.__file__)), "csrc", "gemm_tc.cu")).read()
+    body = src[src.index("void gelu_erf2("):]
+    body = body[:body.index("ex2.approx")]
+    coef = [float(c) for c in re.findall(r"pack2\((-?[0-9.]+e[-+][0-9]+)f,", body)]
+    assert len(coef) == 7, coef                     # c6 first, then c5 ... c0 (Horner order)
+    clamp = float(re.search(r"fminf\(fabsf\(x0\), ([0-9.]+)f\)", body).group(1))
+    x = torch.cat([torch.linspace(-12, 12, 200001, dtype=torch.float64), torch.randn(200000, dtype=torch.float64) * 1.5])
+    xf = x.float()
+    a = xf.abs().clamp(max=clamp)
+    s = torch.full_like(a, coef[0])
+    for c in coef[1:]:
+        s = s * a + torch.tensor(c, dtype=torch.float32)   # one rounding per step (the kernel's FMA rounds once as well)
+    got = (torch.clamp(xf, min=0) - a * torch.exp2(s.double()).float()).double()
+    want = 0.5 * x * (1.0 + torch.erf(x / 2.0 ** 0.5))
+    err = (got - want).abs()
+    assert err.max().item() < 1e-6, err.max().item()
+    big = want.abs() >= 1e-3
+    assert (err[big] / want[big].abs()).max().item() < 1e-4
