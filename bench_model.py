@@ -258,6 +258,30 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
     launches_per_step = lib.mintb_kernel_launches() - launches0
     barrier()
 
+    # Launch mode.  A training step whose weights do not change between steps (no optimiser in the timed loop) is captured
+    # once into a CUDA graph and replayed: the same kernels in the same order, launched by the host in one call.  With an
+    # optimiser the FP8 scales change from step to step and reach the kernels by value, so that variant stays eager, as
+    # does inference (a few hundred long kernels).  MINTB_BENCH_EAGER=1 forces eager launches.
+    launch_mode = "eager"
+    if cfg["train"] and opt is None and cfg.get("graph", True) and os.environ.get("MINTB_BENCH_EAGER", "0") == "0":
+        from mint_plus_b200.training import GraphedTrainStep
+        try:
+            after = None
+            if sync_grads is not None:
+                after = sync_grads.finish if isinstance(sync_grads, ChunkedGradAllReduce) else sync_grads
+            graphed = GraphedTrainStep(model, d_tok, d_cid, params=trainable, after_backward=after, warmup=1)
+            eager_step = step
+
+            def step(tok, cid, lab):        # noqa: F811 - same arguments as the eager step
+                return graphed.step(tok, cid)
+            launch_mode = "cuda graph (one captured step replayed)"
+            for _ in range(2):
+                step(d_tok, d_cid, d_lab)
+            barrier()
+        except Exception as exc:            # capture refused (an operation that is not capturable): stay eager, say why
+            launch_mode = f"eager (graph capture failed: {type(exc).__name__}: {str(exc)[:120]})"
+            torch.cuda.synchronize()
+
     sampler = ClockSampler(local)
     sampler.start()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
@@ -349,7 +373,7 @@ def run(name, args, rank, world, local, ClockSampler, peaks, peak_src, steps=Non
                 "warmup": warmup, "ms_per_step": ms_total / steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
                 "config": {"workload": cfg["desc"] + " per GPU", "l2": "working set per step far exceeds L2 (no flush)",
-                           "launch": "eager", "checkpointing": ("per layer" if getattr(model, "last_forward_checkpointed", False) else
+                           "launch": launch_mode, "checkpointing": ("per layer" if getattr(model, "last_forward_checkpointed", False) else
                                              "off (activations of all layers fit in HBM)") if cfg["train"] else "none",
                            "grad_allreduce_bytes": sync_grads.nbytes if sync_grads is not None else 0,
                            "dealing": "one seeded list of n_gpus x pairs, dealt to ranks in equal counts by squared length (snake order)"

@@ -12,7 +12,7 @@ from .modules_plus import (TransformerLayer_MINT_plus, VanillaFeedForward, build
                            enable_fused_multi_pathway)
 from .modules import CheckpointedBlock, RobertaLMHead, TransformerLayer_MINT, build_checkpointed_model
 from .esm2 import MINT, MODEL_REGISTRY, SUPPORTED_HEAD_DIMS, Alphabet
-from .training import mlm_corrupt, shared_step
+from .training import GraphedTrainStep, mlm_corrupt, shared_step
 from .rotary_embedding import RotaryEmbedding
 from .mu_scaling import (Fp8Linear, TransformerLayer_MINT_mu, apply_fp8_to_model, build_mint_fp8, build_mint_mu,
                          calibrate_fp8, compute_tau, refresh_fp8_weights, Fp8WeightScaler, set_unit_output_scales, unit_variance_init_)
@@ -24,6 +24,6 @@ __all__ = [
     "MultiHeadAttention", "MultimerAttention", "TransformerLayer_MINT_plus", "VanillaFeedForward",
     "build_mint_plus", "enable_fused_multi_pathway", "RotaryEmbedding", "Fp8Linear", "apply_fp8_to_model", "calibrate_fp8",
     "unit_variance_init_", "TransformerLayer_MINT", "TransformerLayer_MINT_mu", "RobertaLMHead", "MINT", "MODEL_REGISTRY",
-    "Alphabet", "build_mint_mu", "build_mint_fp8", "compute_tau", "mlm_corrupt", "shared_step", "CheckpointedBlock",
+    "Alphabet", "build_mint_mu", "build_mint_fp8", "compute_tau", "mlm_corrupt", "shared_step", "GraphedTrainStep", "CheckpointedBlock",
     "build_checkpointed_model", "set_unit_output_scales", "SUPPORTED_HEAD_DIMS", "refresh_fp8_weights", "Fp8WeightScaler",
 ]

@@ -139,3 +139,42 @@ def test_training_step_runs_on_library_kernels_from_tokens_to_loss():
     ref = F.cross_entropy(out.float().transpose(1, 2), tok, reduction="none")
     ref = (ref * target).sum() / target.sum()
     assert abs(loss.item() - ref.item()) <= 2e-3 * abs(ref.item())
+
+
+def test_graphed_training_step_replays_the_eager_step():
+    """A training step captured into a CUDA graph: replays give finite losses close to the eager step's (the MLM corruption
+    is redrawn every replay, so not equal), every trainable parameter gets a finite, non-zero gradient at an address that
+    does not move between replays, and a new batch copied into the graph's buffers changes the result."""
+    torch.manual_seed(9)
+    model = M.MINT(num_layers=2, embed_dim=128, attention_heads=4, use_multimer=True).to(DEV).to(torch.bfloat16).train()
+    tok = _tokens(2, 256, 13).to(DEV)
+    tok[tok == MASK] = 5
+    cid = torch.zeros_like(tok); cid[:, 120:] = 1
+    losses = []
+    for _ in range(4):
+        for p in model.parameters():
+            p.grad = None
+        loss, _ = M.shared_step(model, (tok, cid))
+        loss.backward()
+        losses.append(loss.item())
+    eager = sum(losses) / len(losses)
+    eager_norm = sum(p.grad.float().norm().item() for p in model.parameters())
+    del loss          # a live loss keeps the eager step's autograd graph (and its gradient-accumulation nodes, bound to the
+    # default stream) alive, which invalidates a capture on another stream
+    graphed = M.GraphedTrainStep(model, tok, cid)
+    l1 = graphed.step().item()
+    ptrs = [p.grad.data_ptr() for p in model.parameters()]
+    l2 = graphed.step(tok, cid).item()
+    ops.check_device_status()
+    assert [p.grad.data_ptr() for p in model.parameters()] == ptrs
+    for l in (l1, l2):
+        assert l == l and abs(l - eager) <= 0.15 * abs(eager), (l, eager)
+    norm = sum(p.grad.float().norm().item() for p in model.parameters())
+    assert all(torch.isfinite(p.grad).all() for p in model.parameters())
+    assert 0.5 * eager_norm <= norm <= 2.0 * eager_norm
+    tok2 = _tokens(2, 256, 14).to(DEV)
+    tok2[tok2 == MASK] = 7
+    g_before = [p.grad.clone() for p in model.parameters()]
+    graphed.step(tok2.cpu().pin_memory(), cid)      # a pinned host batch is copied in as well
+    torch.cuda.synchronize()
+    assert any(not torch.equal(a, p.grad) for a, p in zip(g_before, model.parameters()))
