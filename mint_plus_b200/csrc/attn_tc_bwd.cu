@@ -342,6 +342,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
   if (warp == 1) { tmem_alloc(tmem_slot, Cfg::kTmemCols); tmem_relinquish(); }
 
   int any_active = 0;
+  uint8_t my_flag = 0;   // flag of query tile `tid` (the loop below runs at most once per thread: nqt <= kBwdMaxTiles < kBwdThreads)
   for (int i = tid; i < nqt; i += kBwdThreads) {
     uint8_t c = 0;
 #pragma unroll
@@ -357,6 +358,25 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
     }
     tq[i] = f;
     any_active |= f;
+    my_flag = f;
+  }
+  // The first query tile's Q and dO do not wait for the CTA-wide barrier below: warp 0 holds the flags of tiles 0..31 and
+  // requests the first tile with work among them at once (the copy of its statistics follows after the wait for the pass
+  // before this kernel).  A TMA round trip is about as long as the whole set-up, so the first products start that much
+  // earlier.  Warp 0 remembers the tile; its loading loop then skips these two copies.
+  int early_q = -1;
+  if (warp == 0) {
+    const unsigned act = __ballot_sync(0xffffffffu, my_flag != 0);
+    if (act != 0u) {
+      early_q = __ffs(act) - 1;
+      if (lane == 0) {   // the thread that initialised the barriers
+        prefetch_tensormap(mq); prefetch_tensormap(&map_do);
+        mbar_expect_tx(&q_full[0], 2 * Cfg::kTileBytes + Cfg::kStatBytes);
+        tma_load_3d(sQ, mq, &q_full[0], 0, early_q * kBwdTile, bh);
+        if (p.do_seq_first) tma_load_3d(sQ + Cfg::kTileBytes, &map_do, &q_full[0], 0, bh, early_q * kBwdTile);
+        else tma_load_3d(sQ + Cfg::kTileBytes, &map_do, &q_full[0], 0, early_q * kBwdTile, bh);
+      }
+    }
   }
   tc_fence_before();
   any_active = __syncthreads_or(any_active);
@@ -492,12 +512,15 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qs, const __grid_cons
         while (next_q < nqt && tq[next_q] == 0) ++next_q;
         if (next_q >= nqt) return;
         unsigned char* dst = sQ + size_t(lr.pos) * 2 * Cfg::kTileBytes;
-        mbar_expect_tx(&q_full[lr.pos], 2 * Cfg::kTileBytes + Cfg::kStatBytes);
+        const bool early = next_q == early_q;   // Q and dO of this tile (the first one, stage 0) were requested during the set-up
+        if (!early) mbar_expect_tx(&q_full[lr.pos], 2 * Cfg::kTileBytes + Cfg::kStatBytes);
         bulk_load_1d(sStats + size_t(lr.pos) * Cfg::kStatBytes, p.stats + size_t(bh) * p.Tpad + size_t(next_q) * kBwdTile,
                      Cfg::kStatBytes, &q_full[lr.pos]);
-        tma_load_3d(dst, mq, &q_full[lr.pos], 0, next_q * kBwdTile, bh);
-        if (p.do_seq_first) tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[lr.pos], 0, bh, next_q * kBwdTile);
-        else tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[lr.pos], 0, next_q * kBwdTile, bh);
+        if (!early) {
+          tma_load_3d(dst, mq, &q_full[lr.pos], 0, next_q * kBwdTile, bh);
+          if (p.do_seq_first) tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[lr.pos], 0, bh, next_q * kBwdTile);
+          else tma_load_3d(dst + Cfg::kTileBytes, &map_do, &q_full[lr.pos], 0, next_q * kBwdTile, bh);
+        }
         ++next_q;
         lr.advance();
       };
