@@ -65,3 +65,38 @@ def test_backward_products(seed):
         tol = (2e-5 if odt == torch.float32 else 1e-2) * max(1.0, want_dw.abs().max().item())
         assert (dw - want_dw).abs().max().item() <= tol
     ops.check_device_status()
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_eight_bit_products(seed):
+    """e4m3 x e4m3 forward (bf16 result; e4m3 result with the bf16 pre-activation beside it, the fc1 configuration) and
+    e5m2 x e4m3 backward products on random shapes, against fp32 products of the SAME 8-bit values: only the order of the
+    fp32 additions and the final rounding differ."""
+    rng = random.Random(900 + seed)
+    Mr = 16 * rng.choice([rng.randint(1, 9), rng.randint(8, 60), rng.randint(40, 200)])
+    N = 16 * rng.choice([rng.randint(1, 20), rng.randint(16, 100)])
+    K = 16 * rng.choice([rng.randint(1, 12), rng.randint(8, 90)])
+    g = torch.Generator().manual_seed(seed)
+    x8 = (torch.randn(Mr, K, generator=g) * 2).to(torch.float8_e4m3fn)
+    w8 = (torch.randn(N, K, generator=g) * 2).to(torch.float8_e4m3fn)
+    b = torch.randn(N, generator=g)
+    alpha = 1.0 / (4.0 * K ** 0.5)
+    z = alpha * (x8.float() @ w8.float().t()) + b
+    got = ops.gemm_e4m3(x8.to(DEV), w8.to(DEV), alpha, b.to(DEV)).float().cpu()
+    torch.testing.assert_close(got, z, rtol=1e-2, atol=1e-2)
+    # GELU, e4m3 result and bf16 pre-activation from one launch
+    out_scale = max(float(O.gelu_erf(z).abs().max()), 1e-3) / 448.0
+    q, pre = ops.gemm_e4m3(x8.to(DEV), w8.to(DEV), alpha, b.to(DEV), gelu=True, out_e4m3_scale=out_scale, save_preact=True)
+    ops.check_device_status()
+    torch.testing.assert_close(pre.float().cpu(), z, rtol=1e-2, atol=1e-2)
+    want_q = O.gelu_erf(z)
+    assert (q.float().cpu() * out_scale - want_q).abs().max().item() <= 0.07 * max(float(want_q.abs().max()), 1e-3)   # 3 mantissa bits
+    # backward products: e5m2 gradient against the e4m3 operands
+    g8 = (torch.randn(Mr, N, generator=g) * 4).to(torch.float8_e5m2)
+    dx = ops.gemm_dgrad(g8.to(DEV), w8.to(DEV)).float().cpu()
+    want_dx = g8.float() @ w8.float()
+    assert (dx - want_dx).abs().max().item() <= 1e-2 * max(1.0, want_dx.abs().max().item())
+    dw = ops.gemm_wgrad(g8.to(DEV), x8.to(DEV), out_dtype=torch.float32).float().cpu()
+    want_dw = g8.float().t() @ x8.float()
+    assert (dw - want_dw).abs().max().item() <= 2e-5 * max(1.0, want_dw.abs().max().item())
+    ops.check_device_status()
